@@ -1,0 +1,170 @@
+"""Pins the CPU oracle to the reference's own golden vectors and known answers.
+
+Sources (paths inside the reference project):
+  src/backend/quant/encode_golden_test.zig:1010-1026  Q4_K/Q5_K encoder bytes = ggml
+  src/backend/quant/encode_golden_test.zig:1104-1140  round-trip RMSE bounds
+  src/backend/quant/q8_0_tests.zig:37-82              Q8_0 known answers, tie rounding
+  src/backend/quant/cold_tests.zig:1527-1529          TQ2_0 dequant = ggml bit patterns
+  src/backend/quant/q4_k.zig:2060-2082, q5_k.zig:1293-1315  pattern-block dot = dense dot
+"""
+import numpy as np
+import pytest
+
+import oracle
+
+
+def f2h_bits(x):
+    return int(np.array([x], dtype=np.float16).view(np.uint16)[0])
+
+
+def test_q4_k_encoder_matches_ggml_golden_bytes(goldens):
+    x = goldens["input_bits"].view(np.float32)
+    got = oracle.quantize_rows(oracle.Q4_K, x)
+    assert np.array_equal(got, goldens["q4_k_golden"])
+
+
+def test_q5_k_encoder_matches_ggml_golden_bytes(goldens):
+    x = goldens["input_bits"].view(np.float32)
+    got = oracle.quantize_rows(oracle.Q5_K, x)
+    assert np.array_equal(got, goldens["q5_k_golden"])
+
+
+def test_golden_inputs_follow_documented_generators(goldens):
+    # encode_golden_test.zig:16-31 documents the 8 input vectors; spot-check the
+    # ones with closed forms so a parsing slip cannot go unnoticed.
+    x = goldens["input_bits"].view(np.float32)
+    i = np.arange(256, dtype=np.float32)
+    assert np.array_equal(x[4], np.full(256, 0.75, np.float32))
+    assert np.array_equal(x[7], np.zeros(256, np.float32))
+    ramp = np.float32(-1.0) + np.float32(2.0) * i / np.float32(255.0)
+    assert np.array_equal(x[0], ramp.astype(np.float32))
+
+
+def test_tq2_0_dequant_matches_ggml_golden_bits(goldens):
+    blocks = goldens["tq2_0_bytes"]
+    d = oracle.dequantize_rows(oracle.TQ2_0, blocks.reshape(1, -1), 256 * blocks.shape[0])
+    assert np.array_equal(d.view(np.uint32).reshape(-1, 256), goldens["tq2_0_expected_bits"])
+
+
+def _mix32(s):
+    s = np.uint32(s)
+    s ^= s >> np.uint32(16)
+    s = np.uint32((int(s) * 0x85EBCA6B) & 0xFFFFFFFF)
+    s ^= s >> np.uint32(13)
+    s = np.uint32((int(s) * 0xC2B2AE35) & 0xFFFFFFFF)
+    s ^= s >> np.uint32(16)
+    return s
+
+
+@pytest.mark.parametrize("fmt,bound", [(oracle.Q4_K, 0.055), (oracle.Q5_K, 0.030)])
+def test_round_trip_rmse_bounds(fmt, bound):
+    # encode_golden_test.zig:1104-1140: U[-1,1] rows from the mix32 generator
+    n = 1024
+    x = np.empty(n, np.float32)
+    for i in range(n):
+        bits = _mix32((0x1234 + i * 0x9E3779B9) & 0xFFFFFFFF)
+        x[i] = np.float32(-1.0) + np.float32(2.0) * np.float32(bits) / np.float32(4294967295.0)
+    blocks = oracle.quantize_rows(fmt, x.reshape(1, n))
+    y = oracle.dequantize_rows(fmt, blocks, n).reshape(-1)
+    rmse = float(np.sqrt(np.mean((x.astype(np.float64) - y) ** 2)))
+    assert rmse < bound
+
+
+def test_q8_0_known_answer():
+    src = (np.arange(32) - 16).astype(np.float32)
+    expected = (np.arange(32) - 16).astype(np.int8)
+    src[0], expected[0] = -127, -127
+    src[31], expected[31] = 127, 127
+    blocks = oracle.quantize_rows(oracle.Q8_0, src.reshape(1, 32))
+    assert blocks.shape == (1, 34)
+    assert int(blocks[0, :2].view(np.uint16)[0]) == f2h_bits(1.0)
+    assert np.array_equal(blocks[0, 2:].view(np.int8), expected)
+    back = oracle.dequantize_rows(oracle.Q8_0, blocks, 32)
+    assert np.array_equal(back.reshape(-1), src)
+
+
+def test_q8_0_ties_round_away_from_zero():
+    src = np.zeros(32, np.float32)
+    src[:7] = [127, 0.5, 1.5, 2.5, -0.5, -1.5, -2.5]
+    q = oracle.quantize_rows(oracle.Q8_0, src.reshape(1, 32))[0, 2:].view(np.int8)
+    assert list(q[1:7]) == [1, 2, 3, -1, -2, -3]
+
+
+def _q8k_pattern():
+    # q8k.zig:819-827 fillQ8KPattern
+    qs = ((np.arange(256) % 17) - 8).astype(np.int8)
+    bsums = qs.reshape(16, 16).astype(np.int32).sum(1).astype(np.int16)
+    return np.concatenate([np.array([1.0], np.float32).view(np.uint8), qs.view(np.uint8), bsums.view(np.uint8)])
+
+
+def test_q4_k_pattern_block_dot_equals_dense_dot():
+    # q4_k.zig:2050-2058 fillQ4KPattern
+    blk = np.zeros(144, np.uint8)
+    blk[0:2] = np.array([f2h_bits(1.0)], np.uint16).view(np.uint8)
+    blk[2:4] = np.array([f2h_bits(1.0)], np.uint16).view(np.uint8)
+    blk[4:16] = [1, 1, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1]
+    i = np.arange(128)
+    blk[16:] = (i % 16) | (((i + 3) % 16) << 4)
+    a = _q8k_pattern()
+    dense_w = oracle.dequantize_rows(oracle.Q4_K, blk.reshape(1, -1), 256).reshape(-1)
+    dense_a = a[4:260].view(np.int8).astype(np.float32)
+    want = np.float32(0)
+    for wv, av in zip(dense_w, dense_a):
+        want = np.float32(want + np.float32(wv * av))
+    assert oracle.block_dot(oracle.Q4_K, blk, a) == want
+
+
+def test_q5_k_pattern_block_dot_equals_dense_dot():
+    # q5_k.zig:1281-1291 fillQ5KPattern
+    blk = np.zeros(176, np.uint8)
+    blk[0:2] = np.array([f2h_bits(1.0)], np.uint16).view(np.uint8)
+    blk[4:16] = [1, 2, 3, 4, 0, 0, 0, 0, 1, 2, 3, 4]
+    qh = np.zeros(32, np.uint8)
+    qs = np.zeros(128, np.uint8)
+    for s in range(8):
+        for o in range(32):
+            v = (s * 7 + o) % 32
+            bi = (s // 2) * 32 + o
+            if s % 2 == 0:
+                qs[bi] = (qs[bi] & 0xF0) | (v & 0x0F)
+            else:
+                qs[bi] = (qs[bi] & 0x0F) | ((v & 0x0F) << 4)
+            if v & 16:
+                qh[o] |= 1 << s
+    blk[16:48] = qh
+    blk[48:] = qs
+    a = _q8k_pattern()
+    dense_w = oracle.dequantize_rows(oracle.Q5_K, blk.reshape(1, -1), 256).reshape(-1)
+    # decode law check: element (s, o) carries level (s*7+o)%32 times scale s-th
+    dense_a = a[4:260].view(np.int8).astype(np.float32)
+    want = np.float32(0)
+    for wv, av in zip(dense_w, dense_a):
+        want = np.float32(want + np.float32(wv * av))
+    assert oracle.block_dot(oracle.Q5_K, blk, a) == want
+
+
+def test_dequant_agrees_with_gguf_py():
+    # independent third-party cross-check of the decode laws
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+
+    rng = np.random.default_rng(7)
+    w = (rng.standard_normal((8, 1024)) * 0.02).astype(np.float32)
+    for fmt, t in ((oracle.Q8_0, gguf.GGMLQuantizationType.Q8_0), (oracle.Q4_K, gguf.GGMLQuantizationType.Q4_K),
+                   (oracle.Q5_K, gguf.GGMLQuantizationType.Q5_K), (oracle.TQ2_0, gguf.GGMLQuantizationType.TQ2_0)):
+        blocks = oracle.quantize_rows(fmt, w)
+        ours = oracle.dequantize_rows(fmt, blocks, 1024)
+        theirs = quants.dequantize(blocks, t).reshape(8, 1024)
+        assert np.array_equal(ours.view(np.uint32), theirs.view(np.uint32)), fmt
+    # gguf-py can also encode Q8_0: bytes must agree
+    theirs = quants.quantize(w, gguf.GGMLQuantizationType.Q8_0)
+    assert np.array_equal(oracle.quantize_rows(oracle.Q8_0, w), theirs.reshape(8, -1))
+
+
+def test_oracle_reproduces_committed_cases(oracle_cases):
+    c = oracle_cases
+    for name, fmt in (("q8_0", oracle.Q8_0), ("q4_k", oracle.Q4_K), ("q5_k", oracle.Q5_K), ("tq2_0", oracle.TQ2_0)):
+        blocks, a = c[f"{name}_blocks"], c[f"{name}_a"]
+        k = a.shape[1]
+        assert np.array_equal(oracle.dequantize_rows(fmt, blocks, k).view(np.uint32), c[f"{name}_dequant"].view(np.uint32))
+        assert np.array_equal(oracle.matmul(fmt, blocks, a).view(np.uint32), c[f"{name}_matmul"].view(np.uint32))
