@@ -1,0 +1,89 @@
+// Shared device/host helpers for the sm_100a quantized-matmul kernels.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fucina_b200.h"
+
+namespace fq {
+
+// ---- GGUF block geometry (reference src/dtype.zig:78-86, :128-152, :215-218;
+//      src/backend/quant/types.zig:177-180) ---------------------------------
+struct FormatInfo {
+    int block_elems;  // weights per block
+    int block_bytes;  // GGUF bytes per block
+    int qs_bytes;     // payload bytes per block in the device layout
+    int sc_bytes;     // scale bytes per block in the device layout (0 = block kept whole)
+};
+
+__host__ __device__ inline FormatInfo format_info(int fmt) {
+    switch (fmt) {
+        case FQ_Q8_0: return {32, 34, 32, 2};
+        case FQ_Q4_K: return {256, 144, 144, 0};
+        case FQ_Q5_K: return {256, 176, 176, 0};
+        case FQ_TQ2_0: return {256, 66, 64, 2};
+        case FQ_TQ2_0_FOLDED: return {256, 130, 128, 2};
+        case FQ_Q2_0: return {128, 34, 32, 2};
+        default: return {0, 0, 0, 0};
+    }
+}
+
+// Device weight layout ("gpu_formats"). K-quant rows are the GGUF rows
+// unchanged (their 144/176-byte blocks are already 16-byte multiples). The
+// 34/66/130-byte formats are split per row into a payload plane followed by
+// an f16 scale plane so every payload chunk is 16-byte aligned:
+//   row = [ qs of block 0 | qs of block 1 | ... ][ d0 d1 ... ] padded to 16 B.
+struct DevWeights {
+    const uint8_t* base;
+    size_t row_stride;  // bytes between rows
+    size_t mat_stride;  // bytes between stacked matrices
+    int fmt;
+    int n;       // rows per matrix
+    int k;       // elements per row
+    int n_mats;
+};
+
+__host__ __device__ inline size_t dev_row_stride(int fmt, size_t k) {
+    const FormatInfo f = format_info(fmt);
+    if (f.block_elems == 0) return 0;
+    const size_t blocks = k / f.block_elems;
+    const size_t raw = blocks * (size_t)(f.qs_bytes + f.sc_bytes);
+    return (raw + 15) & ~(size_t)15;
+}
+
+// ---- small device helpers ---------------------------------------------------
+__device__ __forceinline__ float h2f(uint16_t bits) { return __half2float(__ushort_as_half(bits)); }
+
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+    // 128-bit read-only load that does not allocate in L1: weights are used once.
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg_cached16(const void* p) { return __ldg((const uint4*)p); }
+
+
+// K-quant 6-bit scale/min pair j of the 12-byte field held in three words
+// (reference backend/quant/q8k.zig:637-648).
+__device__ __forceinline__ void scale_min_k4(const uint32_t s[3], int j, int& sc, int& mn) {
+    const uint8_t* q = reinterpret_cast<const uint8_t*>(s);
+    if (j < 4) {
+        sc = q[j] & 63;
+        mn = q[j + 4] & 63;
+    } else {
+        sc = (q[j + 4] & 0x0f) | ((q[j - 4] >> 6) << 4);
+        mn = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+    }
+}
+
+template <int WIDTH>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+    for (int o = WIDTH / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+}  // namespace fq

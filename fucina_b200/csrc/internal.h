@@ -1,0 +1,53 @@
+// Launchers shared between the translation units of libfucina_b200.so.
+#pragma once
+#include "common.cuh"
+
+namespace fq {
+
+// formats.cu
+cudaError_t launch_repack(const DevWeights& w, const uint8_t* gguf_dev, size_t nb01, size_t nb02, bool to_device,
+                          cudaStream_t st);
+cudaError_t launch_dequant_rows(const DevWeights& w, int mat, int row0, int rows, float* out, cudaStream_t st);
+// row r of the output is quantised from source row (src_rows ? src_rows[r] / src_div : r)
+cudaError_t launch_quantize_acts_layout(const float* a, const int* src_rows, int src_div, int m, int k, int fmt, uint8_t* out,
+                                        cudaStream_t st);
+cudaError_t launch_quantize_acts_struct(const float* a, int m, int k, bool q8k, uint8_t* out, cudaStream_t st);
+cudaError_t launch_quantize_weights(int fmt, const float* src, size_t n, size_t k, uint8_t* dst, cudaStream_t st);
+
+// gemv.cu -- decode kernels over int8 activations in the acts.cuh layout.
+//
+// Plain form: `acts` holds m <= 16 rows of act_sizes(fmt,k).row bytes; all n
+// rows of matrix `mat` are multiplied; c is [m][ldc]. accumulate != 0 adds to
+// c instead of storing (PTQTP plane sums).
+//
+// Grouped form (table != nullptr): blockIdx.y walks a device-built table of
+// row groups; group g multiplies activation rows [row0, row0+m) -- and writes
+// the same rows of c -- with matrix `mat` of the expert stack. Entries at or
+// beyond *n_desc are skipped, so the host can launch an upper bound.
+//
+// Gated form (w2.base != nullptr): row j of `w` (gate) and row j of `w2` (up)
+// are dotted with the same activations and c receives
+// up * (gate * 1/(1+exp(-gate))) (reference backend/ops.zig:150-190, swiglu).
+struct GroupDesc {
+    int mat;
+    int row0;
+    int m;
+    int pad;
+};
+struct GemvArgs {
+    DevWeights w;
+    DevWeights w2;
+    int mat;
+    const uint8_t* acts;
+    float* c;
+    int m;
+    int ldc;
+    int accumulate;
+    const GroupDesc* table;
+    const int* n_desc;
+    int max_desc;
+};
+cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st);
+size_t gemv_max_rows();  // largest m one launch (or one table entry) handles
+
+}  // namespace fq

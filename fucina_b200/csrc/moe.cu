@@ -1,0 +1,376 @@
+// MoE expert layer on the device: router top-k, route plan, grouped expert
+// products with fused SwiGLU, weighted combine. Tokens stay in HBM across all
+// three expert products; the reference's GPU arm instead makes two PCIe round
+// trips per layer with CPU gather / activation / scatter phases between them
+// (src/llm/gemma/moe.zig:696-901, docs/GPU-OFFLOAD.md:191-203).
+//
+// Per (token, slot) pair p with expert e (reference src/exec/moe.zig:890-920,
+// :1334-1401, src/exec/moe_chain.zig:236-330):
+//   qx   = Q8_K(x[token])                       (Q8_0 blocks for Q8_0 experts)
+//   g    = swiglu(W_gate[e].qx, W_up[e].qx)
+//   qg   = Q8_K(g)
+//   down = W_down[e].qg
+//   out[token] = sum over the token's slots, in slot order, of w[p] * down
+#include <vector>
+
+#include "acts.cuh"
+#include "internal.h"
+#include "runtime.h"
+
+namespace fq {
+
+namespace {
+
+constexpr int kGroupRows = 16;  // activation rows one grouped-GEMV table entry covers
+
+// Counting sort of pairs by expert plus the grouped-GEMV table, one CTA.
+// Positions inside an expert's run are handed out by atomics: a pair's result
+// does not depend on its position, so the layer output is unaffected.
+__global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, int* __restrict__ order,
+                                  int* __restrict__ inv, GroupDesc* __restrict__ table, int* __restrict__ n_desc) {
+    extern __shared__ int sh[];
+    int* count = sh;                 // [n_expert]
+    int* place = sh + n_expert;      // [n_expert]
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = min(max(selected[p], 0), n_expert - 1);
+        atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, nd = 0;
+        for (int e = 0; e < n_expert; ++e) {
+            place[e] = off;
+            const int c = count[e];
+            for (int j = 0; j < c; j += kGroupRows) table[nd++] = {e, off + j, min(kGroupRows, c - j), 0};
+            off += c;
+        }
+        *n_desc = nd;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = min(max(selected[p], 0), n_expert - 1);
+        const int pos = atomicAdd(&place[e], 1);
+        order[pos] = p;
+        inv[p] = pos;
+    }
+}
+
+// out[t] = sum_k w[p] * down[inv[p]], slot order, first slot assigned
+// (src/exec/moe_chain.zig:307-330); multiply and add stay separate.
+__global__ void combine_kernel(const float* __restrict__ down, const float* __restrict__ weights, const int* __restrict__ inv,
+                               int seq, int hidden, int top_k, float* __restrict__ out) {
+    const size_t total = (size_t)seq * hidden;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / hidden), j = (int)(i % hidden);
+        float acc = 0.0f;
+        for (int kk = 0; kk < top_k; ++kk) {
+            const int p = t * top_k + kk;
+            const float v = __fmul_rn(weights[p], down[(size_t)inv[p] * hidden + j]);
+            acc = (kk == 0) ? v : __fadd_rn(acc, v);
+        }
+        out[i] = acc;
+    }
+}
+
+// Router (src/exec/topk.zig:50-86), one thread per token row: the k largest
+// logits in descending order, an equal logit never displaces an earlier one;
+// softmax over all experts with the row maximum subtracted; optional
+// renormalisation over the selected k.
+constexpr int kMaxTopK = 32;
+__global__ void router_topk_kernel(const float* __restrict__ logits, int rows, int experts, int k, int normalize,
+                                   int* __restrict__ selected, float* __restrict__ weights) {
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= rows) return;
+    const float* l = logits + (size_t)row * experts;
+    float w[kMaxTopK];
+    int sel[kMaxTopK];
+    for (int s = 0; s < k; ++s) {
+        sel[s] = 0;
+        w[s] = -INFINITY;
+    }
+    float mx = l[0];
+    for (int i = 0; i < experts; ++i) {
+        const float v = l[i];
+        if (v > mx) mx = v;
+        if (v <= w[k - 1]) continue;
+        int slot = k - 1;
+        while (slot > 0 && v > w[slot - 1]) {
+            w[slot] = w[slot - 1];
+            sel[slot] = sel[slot - 1];
+            --slot;
+        }
+        w[slot] = v;
+        sel[slot] = i;
+    }
+    float exp_sum = 0.0f;
+    for (int i = 0; i < experts; ++i) exp_sum = __fadd_rn(exp_sum, expf(__fsub_rn(l[i], mx)));
+    const float inv_sum = __fdiv_rn(1.0f, exp_sum);
+    float total = 0.0f;
+    for (int s = 0; s < k; ++s) {
+        w[s] = __fmul_rn(expf(__fsub_rn(w[s], mx)), inv_sum);
+        total = __fadd_rn(total, w[s]);
+    }
+    if (normalize && total > 0.0f) {
+        const float inv_total = __fdiv_rn(1.0f, total);
+        for (int s = 0; s < k; ++s) w[s] = __fmul_rn(w[s], inv_total);
+    }
+    for (int s = 0; s < k; ++s) {
+        selected[(size_t)row * k + s] = sel[s];
+        weights[(size_t)row * k + s] = w[s];
+    }
+}
+
+int max_desc_for(int pairs, int n_expert) { return (pairs < n_expert ? pairs : n_expert) + pairs / kGroupRows; }
+
+int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
+                       int seq, int top_k, const int* selected_dev, const float* weights_dev, float* out_dev, cudaStream_t st) {
+    const int hidden = gate.k, out_pe = gate.n, n_expert = gate.n_mats, fmt = gate.fmt;
+    const int pairs = seq * top_k;
+    const ActSizes Sx = act_sizes(fmt, hidden), Sg = act_sizes(fmt, out_pe);
+    const int max_desc = max_desc_for(pairs, n_expert);
+    // one scratch block: order, inv, n_desc, table, quantised x rows, g rows, quantised g rows, down rows
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += (bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    const size_t o_order = take(sizeof(int) * pairs), o_inv = take(sizeof(int) * pairs), o_nd = take(sizeof(int));
+    const size_t o_table = take(sizeof(GroupDesc) * max_desc), o_qx = take(Sx.row * pairs);
+    const size_t o_g = take(sizeof(float) * (size_t)pairs * out_pe), o_qg = take(Sg.row * pairs);
+    const size_t o_down = take(sizeof(float) * (size_t)pairs * hidden);
+    uint8_t* scratch = (uint8_t*)dev_alloc(off);
+    if (!scratch) return fail(FQ_DECLINED_BUDGET, "MoE scratch allocation of %zu bytes failed", off);
+    int* order = (int*)(scratch + o_order);
+    int* inv = (int*)(scratch + o_inv);
+    int* n_desc = (int*)(scratch + o_nd);
+    GroupDesc* table = (GroupDesc*)(scratch + o_table);
+    uint8_t* qx = scratch + o_qx;
+    float* g = (float*)(scratch + o_g);
+    uint8_t* qg = scratch + o_qg;
+    float* down_rows = (float*)(scratch + o_down);
+
+    cudaError_t e = cudaSuccess;
+    int rc = FQ_OK;
+    do {
+        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, order, inv, table, n_desc);
+        if ((e = cudaGetLastError()) != cudaSuccess) break;
+        // gather each pair's token row and quantise it, in expert order
+        if ((e = launch_quantize_acts_layout(x_dev, order, top_k, pairs, hidden, fmt, qx, st)) != cudaSuccess) break;
+        GemvArgs ga{gate, up, 0, qx, g, kGroupRows, out_pe, 0, table, n_desc, max_desc};
+        if ((e = launch_gemv(ga, ctx->sm_count, st)) != cudaSuccess) break;
+        if ((e = launch_quantize_acts_layout(g, nullptr, 1, pairs, out_pe, fmt, qg, st)) != cudaSuccess) break;
+        GemvArgs gd{down, DevWeights{}, 0, qg, down_rows, kGroupRows, hidden, 0, table, n_desc, max_desc};
+        if ((e = launch_gemv(gd, ctx->sm_count, st)) != cudaSuccess) break;
+        const size_t total = (size_t)seq * hidden;
+        int blocks = (int)((total + 255) / 256);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        combine_kernel<<<blocks, 256, 0, st>>>(down_rows, weights_dev, inv, seq, hidden, top_k, out_dev);
+        e = cudaGetLastError();
+    } while (false);
+    g_trace.launches += 6;
+    if (e != cudaSuccess) rc = cuda_fail(e, "MoE layer launch");
+    if (st != ctx->stream) cudaStreamSynchronize(st);
+    dev_free(scratch);
+    return rc;
+}
+
+int check_moe(const fq_weights* gate, const fq_weights* up, const fq_weights* down, size_t seq, size_t top_k, int gated_op) {
+    if (!gate || !up || !down) return fail(FQ_DECLINED_ARGS, "null weights");
+    if (gated_op != 0) return fail(FQ_DECLINED_ARGS, "only swiglu (gated_op 0) is served");
+    const DevWeights &g = gate->dw, &u = up->dw, &d = down->dw;
+    if (g.fmt != u.fmt || g.fmt != d.fmt) return fail(FQ_DECLINED_ARGS, "expert tensors must share one format");
+    if (g.n != u.n || g.k != u.k || g.n_mats != u.n_mats || d.n_mats != g.n_mats || d.n != g.k || d.k != g.n)
+        return fail(FQ_DECLINED_ARGS, "expert tensor shapes are inconsistent");
+    if (seq == 0 || top_k == 0 || top_k > (size_t)g.n_mats) return fail(FQ_DECLINED_ARGS, "bad seq/top_k");
+    if (seq * top_k > (size_t)1 << 24) return fail(FQ_DECLINED_ARGS, "too many routed pairs");
+    if (g.n_mats > 4096) return fail(FQ_DECLINED_ARGS, "too many experts");
+    const ActLayout L = act_layout(g.fmt);
+    if (g.n % L.act_block != 0 || g.n % format_info(g.fmt).block_elems != 0)
+        return fail(FQ_DECLINED_ARGS, "expert width %d is not a whole number of blocks", g.n);
+    return FQ_OK;
+}
+
+// grow-only staging panels of the grouped entry (backend/cuda.zig:2181-2234)
+std::mutex g_qmoe_lock;
+struct QMoeStage {
+    float *in = nullptr, *out = nullptr;
+    size_t in_bytes = 0, out_bytes = 0;
+} g_stage;
+
+}  // namespace
+}  // namespace fq
+
+using namespace fq;
+
+extern "C" {
+
+int fq_router_topk_dev(const float* logits_dev, size_t seq, size_t n_expert, size_t top_k, int normalize, int32_t* selected_dev,
+                       float* weights_dev, void* stream) {
+    if (!logits_dev || !selected_dev || !weights_dev) return fail(FQ_DECLINED_ARGS, "null pointer");
+    if (top_k == 0 || top_k > n_expert || top_k > (size_t)kMaxTopK || seq == 0) return fail(FQ_DECLINED_ARGS, "bad top_k");
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    cudaStream_t st = stream ? (cudaStream_t)stream : ctx->stream;
+    router_topk_kernel<<<(unsigned)((seq + 63) / 64), 64, 0, st>>>(logits_dev, (int)seq, (int)n_expert, (int)top_k, normalize, selected_dev, weights_dev);
+    g_trace.launches++;
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "router launch");
+}
+
+int fq_moe_layer_dev(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev, size_t seq,
+                     size_t top_k, const int32_t* selected_dev, const float* weights_dev, int gated_op, float* out_dev, void* stream) {
+    if (int rc = check_moe(gate, up, down, seq, top_k, gated_op)) return rc;
+    if (!x_dev || !selected_dev || !weights_dev || !out_dev) return fail(FQ_DECLINED_ARGS, "null pointer");
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    g_trace.calls++;
+    return moe_layer_dev_impl(ctx, gate->dw, up->dw, down->dw, x_dev, (int)seq, (int)top_k, selected_dev, weights_dev, out_dev,
+                              stream ? (cudaStream_t)stream : ctx->stream);
+}
+
+int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x, size_t seq, size_t top_k,
+                 const int64_t* selected, const float* weights, int gated_op, float* out) {
+    if (int rc = check_moe(gate, up, down, seq, top_k, gated_op)) return rc;
+    if (!x || !selected || !weights || !out) return fail(FQ_DECLINED_ARGS, "null pointer");
+    const size_t pairs = seq * top_k, hidden = (size_t)gate->dw.k;
+    std::vector<int32_t> sel32(pairs);
+    for (size_t p = 0; p < pairs; ++p) {
+        // the reference returns IndexOutOfBounds before doing any work (exec/moe_chain.zig:243)
+        if (selected[p] < 0 || selected[p] >= gate->dw.n_mats) return fail(FQ_DECLINED_ARGS, "selected[%zu]=%lld out of range", p, (long long)selected[p]);
+        sel32[p] = (int32_t)selected[p];
+    }
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    g_trace.calls++;
+    const size_t xb = seq * hidden * sizeof(float), sb = pairs * sizeof(int32_t), wb = pairs * sizeof(float);
+    const size_t o_sel = (xb + 255) & ~(size_t)255, o_w = o_sel + ((sb + 255) & ~(size_t)255), o_out = o_w + ((wb + 255) & ~(size_t)255);
+    const size_t total = o_out + xb;
+    uint8_t* dev = (uint8_t*)dev_alloc(total);
+    uint8_t* pin = (uint8_t*)pin_alloc(total);
+    int rc = FQ_OK;
+    if (!dev || !pin) rc = fail(FQ_DECLINED_BUDGET, "MoE staging allocation failed");
+    if (rc == FQ_OK) {
+        memcpy(pin, x, xb);
+        memcpy(pin + o_sel, sel32.data(), sb);
+        memcpy(pin + o_w, weights, wb);
+        cudaError_t e = cudaMemcpyAsync(dev, pin, o_out, cudaMemcpyHostToDevice, ctx->stream);
+        g_trace.h2d_bytes += xb + sb + wb;
+        if (e != cudaSuccess) rc = cuda_fail(e, "MoE upload");
+    }
+    if (rc == FQ_OK)
+        rc = moe_layer_dev_impl(ctx, gate->dw, up->dw, down->dw, (const float*)dev, (int)seq, (int)top_k, (const int*)(dev + o_sel),
+                                (const float*)(dev + o_w), (float*)(dev + o_out), ctx->stream);
+    if (rc == FQ_OK) {
+        cudaError_t e = cudaMemcpyAsync(pin + o_out, dev + o_out, xb, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        g_trace.d2h_bytes += xb;
+        if (e != cudaSuccess) rc = cuda_fail(e, "MoE download");
+        else memcpy(out, pin + o_out, xb);
+    }
+    cudaStreamSynchronize(ctx->stream);
+    dev_free(dev);
+    pin_free(pin);
+    return rc;
+}
+
+// ---- grouped GEMM over staged panels (backend/cuda.zig:2181-2333) ------------
+void fq_qmoe_lock(void) { g_qmoe_lock.lock(); }
+void fq_qmoe_unlock(void) { g_qmoe_lock.unlock(); }
+
+int fq_qmoe_stage(size_t in_bytes, size_t out_bytes, float** in, float** out) {
+    if (!in || !out || in_bytes == 0 || out_bytes == 0) return fail(FQ_DECLINED_ARGS, "bad stage request");
+    if (!context()) return FQ_DECLINED_NO_GPU;
+    if (g_stage.in_bytes < in_bytes) {
+        pin_free(g_stage.in);
+        g_stage.in = (float*)pin_alloc(in_bytes);
+        g_stage.in_bytes = g_stage.in ? in_bytes : 0;
+    }
+    if (g_stage.out_bytes < out_bytes) {
+        pin_free(g_stage.out);
+        g_stage.out = (float*)pin_alloc(out_bytes);
+        g_stage.out_bytes = g_stage.out ? out_bytes : 0;
+    }
+    if (!g_stage.in || !g_stage.out) return fail(FQ_DECLINED_BUDGET, "pinned panel allocation failed");
+    *in = g_stage.in;
+    *out = g_stage.out;
+    return FQ_OK;
+}
+
+}  // extern "C"
+
+extern "C" int fq_gemm_q_grouped_nt(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02, size_t n_out,
+                                    size_t k, const fq_qmm_tile* tiles, size_t n_tiles) {
+    // argument rules of backend/cuda.zig:2254-2257
+    const FormatInfo f = format_info(fmt);
+    if (!f.block_elems) return fail(FQ_DECLINED_ARGS, "format %d is not served", fmt);
+    if (k == 0 || k % 32 != 0 || k % f.block_elems != 0) return fail(FQ_DECLINED_ARGS, "k=%zu is not a whole number of blocks", k);
+    if (n_out == 0 || n_out % 4 != 0) return fail(FQ_DECLINED_ARGS, "n_out=%zu is not a multiple of 4", n_out);
+    if (!tiles || n_tiles == 0 || n_tiles > (1u << 24)) return fail(FQ_DECLINED_ARGS, "bad tile table");
+    if (!rhs || nb01 == 0 || nb02 < nb01 * n_out) return fail(FQ_DECLINED_ARGS, "bad rhs strides");
+    if (!g_stage.in || !g_stage.out) return fail(FQ_DECLINED_ARGS, "fq_qmoe_stage was not called");
+    int max_expert = 0;
+    size_t rows = 0;
+    std::vector<GroupDesc> descs;
+    for (size_t t = 0; t < n_tiles; ++t) {
+        const fq_qmm_tile& tl = tiles[t];
+        if (tl.expert < 0 || tl.base_row < 0 || tl.m <= 0 || tl.m > tl.tile_m) return fail(FQ_DECLINED_ARGS, "tile %zu is malformed", t);
+        if (tl.expert > max_expert) max_expert = tl.expert;
+        if ((size_t)tl.base_row + tl.m > rows) rows = (size_t)tl.base_row + tl.m;
+        for (int j = 0; j < tl.m; j += kGroupRows) descs.push_back({tl.expert, tl.base_row + j, tl.m - j < kGroupRows ? tl.m - j : kGroupRows, 0});
+    }
+    if (rows * k * sizeof(float) > g_stage.in_bytes || rows * n_out * sizeof(float) > g_stage.out_bytes)
+        return fail(FQ_DECLINED_ARGS, "tiles reach beyond the staged panels");
+    if (descs.size() > 65535) return fail(FQ_DECLINED_ARGS, "tile table too large for one launch (%zu row groups)", descs.size());
+    const size_t n_mats = (size_t)max_expert + 1;
+    if (rhs_len < nb02 * (n_mats - 1) + nb01 * n_out) return fail(FQ_DECLINED_ARGS, "rhs_len too short for expert %d", max_expert);
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    g_trace.calls++;
+    DevWeights view;
+    fq_weights* temp = nullptr;
+    int rc = resolve_rhs(ctx, fmt, rhs, rhs_len, cacheable, nb01, nb02, n_out, k, n_mats, &view, &temp);
+    if (rc != FQ_OK) return rc;
+    const ActSizes S = act_sizes(fmt, k);
+    const size_t in_b = rows * k * sizeof(float), out_b = rows * n_out * sizeof(float);
+    const size_t o_out = (in_b + 255) & ~(size_t)255, o_q = o_out + ((out_b + 255) & ~(size_t)255);
+    const size_t o_tab = o_q + ((S.row * rows + 255) & ~(size_t)255), o_nd = o_tab + ((descs.size() * sizeof(GroupDesc) + 255) & ~(size_t)255);
+    const size_t total = o_nd + 256;
+    uint8_t* dev = (uint8_t*)dev_alloc(total);
+    GroupDesc* pin_tab = (GroupDesc*)pin_alloc(descs.size() * sizeof(GroupDesc) + sizeof(int));
+    if (!dev || !pin_tab) rc = fail(FQ_DECLINED_BUDGET, "grouped staging allocation failed");
+    cudaError_t e = cudaSuccess;
+    if (rc == FQ_OK) {
+        memcpy(pin_tab, descs.data(), descs.size() * sizeof(GroupDesc));
+        int* pin_nd = (int*)(pin_tab + descs.size());
+        *pin_nd = (int)descs.size();
+        do {
+            if ((e = cudaMemcpyAsync(dev, g_stage.in, in_b, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
+            if ((e = cudaMemcpyAsync(dev + o_tab, pin_tab, descs.size() * sizeof(GroupDesc), cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
+            if ((e = cudaMemcpyAsync(dev + o_nd, pin_nd, sizeof(int), cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
+            // rows no tile names keep whatever the out panel held: copy it up first
+            if ((e = cudaMemcpyAsync(dev + o_out, g_stage.out, out_b, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
+            if ((e = launch_quantize_acts_layout((const float*)dev, nullptr, 1, (int)rows, (int)k, fmt, dev + o_q, ctx->stream)) != cudaSuccess) break;
+            GemvArgs ga{view, DevWeights{}, 0, dev + o_q, (float*)(dev + o_out), kGroupRows, (int)n_out, 0, (const GroupDesc*)(dev + o_tab),
+                        (const int*)(dev + o_nd), (int)descs.size()};
+            if ((e = launch_gemv(ga, ctx->sm_count, ctx->stream)) != cudaSuccess) break;
+            if ((e = cudaMemcpyAsync(g_stage.out, dev + o_out, out_b, cudaMemcpyDeviceToHost, ctx->stream)) != cudaSuccess) break;
+            e = cudaStreamSynchronize(ctx->stream);
+        } while (false);
+        g_trace.launches += 2;
+        g_trace.h2d_bytes += in_b + out_b;
+        g_trace.d2h_bytes += out_b;
+        if (e != cudaSuccess) rc = cuda_fail(e, "grouped GEMM");
+    }
+    cudaStreamSynchronize(ctx->stream);
+    dev_free(dev);
+    pin_free(pin_tab);
+    if (temp) fq_weights_free(temp);
+    return rc;
+}

@@ -1,0 +1,976 @@
+// Provider runtime behind the C ABI: lazy context, caching device / pinned
+// allocators, the resident-weight registry, completion tokens, gates and
+// trace counters. Mirrors the host side of the reference's CUDA provider
+// (src/backend/cuda.zig) on the CUDA runtime API; kernels live in formats.cu,
+// gemv.cu, gemm_tc.cu and moe.cu.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "acts.cuh"
+#include "internal.h"
+#include "runtime.h"
+
+namespace fq {
+
+// ---------------------------------------------------------------------------
+// error text
+// ---------------------------------------------------------------------------
+static std::mutex g_err_lock;
+static std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    std::lock_guard<std::mutex> g(g_err_lock);
+    g_last_error = buf;
+    return code;
+}
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(FQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+// ---------------------------------------------------------------------------
+// trace counters (backend/cuda.zig:191-317)
+// ---------------------------------------------------------------------------
+Trace g_trace;
+static bool g_trace_on = false;
+
+// ---------------------------------------------------------------------------
+// configuration read once from the environment (backend/cuda.zig:321-408)
+// ---------------------------------------------------------------------------
+struct Config {
+    bool gpu_enabled = true;
+    bool decode_enabled = true;  // the decode kernels match the CPU kernels' int8 arithmetic, so on by default
+    uint64_t min_work_qmoe = 1ull << 30;
+    uint64_t min_work_packed_q4 = 1ull << 27;
+    uint64_t min_work_packed_q5 = 1ull << 24;
+    uint64_t min_work_packed_q8 = 1ull << 24;
+    uint64_t min_work_decode_q5 = 3ull << 23;
+    uint64_t qmoe_min_fill_pct = 50;
+    size_t vram_budget_env = 0;
+};
+static Config g_cfg;
+static std::once_flag g_cfg_once;
+
+static bool env_u64(const char* name, uint64_t* out) {
+    const char* v = getenv(name);
+    if (!v || !*v) return false;
+    char* end = nullptr;
+    const unsigned long long x = strtoull(v, &end, 10);
+    if (end == v) return false;
+    *out = x;
+    return true;
+}
+static void ensure_config() {
+    std::call_once(g_cfg_once, [] {
+        uint64_t v;
+        if (env_u64("FUCINA_GPU", &v)) g_cfg.gpu_enabled = v != 0;
+        if (env_u64("FUCINA_GPU_DECODE", &v)) g_cfg.decode_enabled = v != 0;
+        if (env_u64("FUCINA_GPU_TRACE", &v)) g_trace_on = v != 0;
+        env_u64("FUCINA_GPU_MIN_WORK_QMOE", &g_cfg.min_work_qmoe);
+        env_u64("FUCINA_GPU_MIN_WORK_DENSE_Q4", &g_cfg.min_work_packed_q4);
+        env_u64("FUCINA_GPU_MIN_WORK_DENSE_Q5", &g_cfg.min_work_packed_q5);
+        env_u64("FUCINA_GPU_MIN_WORK_DENSE_Q8", &g_cfg.min_work_packed_q8);
+        env_u64("FUCINA_GPU_MIN_WORK_DECODE_Q5", &g_cfg.min_work_decode_q5);
+        env_u64("FUCINA_GPU_QMOE_MIN_FILL", &g_cfg.qmoe_min_fill_pct);
+        if (env_u64("FUCINA_GPU_VRAM_BUDGET", &v)) g_cfg.vram_budget_env = (size_t)v;
+    });
+}
+
+// ---------------------------------------------------------------------------
+// context (backend/cuda.zig:412-508)
+// ---------------------------------------------------------------------------
+static Ctx g_ctx;
+static std::mutex g_init_lock;
+static std::atomic<int> g_init_state{0};  // 0 = not tried, 1 = ok, 2 = failed
+std::recursive_mutex g_dispatch_lock;
+
+static int init_locked(int device) {
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) return fail(FQ_DECLINED_NO_GPU, "no CUDA device: %s", cudaGetErrorString(e));
+    if (device < 0) {
+        if (cudaGetDevice(&device) != cudaSuccess) device = 0;
+    }
+    if (device >= count) return fail(FQ_DECLINED_NO_GPU, "device %d out of range (%d present)", device, count);
+    if ((e = cudaSetDevice(device)) != cudaSuccess) return fail(FQ_DECLINED_NO_GPU, "cudaSetDevice: %s", cudaGetErrorString(e));
+    cudaDeviceProp prop;
+    if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess)
+        return fail(FQ_DECLINED_NO_GPU, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    if (prop.major != 10)
+        return fail(FQ_DECLINED_NO_GPU, "device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
+    g_ctx.device = device;
+    g_ctx.sm_count = prop.multiProcessorCount;
+    snprintf(g_ctx.name, sizeof g_ctx.name, "%s", prop.name);
+    if ((e = cudaStreamCreateWithFlags(&g_ctx.stream, cudaStreamNonBlocking)) != cudaSuccess)
+        return fail(FQ_DECLINED_NO_GPU, "cudaStreamCreate: %s", cudaGetErrorString(e));
+    if ((e = cudaStreamCreateWithFlags(&g_ctx.transfer, cudaStreamNonBlocking)) != cudaSuccess)
+        return fail(FQ_DECLINED_NO_GPU, "cudaStreamCreate: %s", cudaGetErrorString(e));
+    size_t free_b = 0, total_b = 0;
+    cudaMemGetInfo(&free_b, &total_b);
+    g_ctx.vram_budget = g_cfg.vram_budget_env ? g_cfg.vram_budget_env : (size_t)((double)free_b * 0.8);
+    return FQ_OK;
+}
+
+Ctx* context() {
+    ensure_config();
+    int st = g_init_state.load(std::memory_order_acquire);
+    if (st == 0) {
+        std::lock_guard<std::mutex> g(g_init_lock);
+        st = g_init_state.load(std::memory_order_relaxed);
+        if (st == 0) {
+            st = (init_locked(-1) == FQ_OK) ? 1 : 2;
+            g_init_state.store(st, std::memory_order_release);
+        }
+    }
+    if (st != 1) return nullptr;
+    // entries can arrive on arbitrary threads (backend/cuda.zig:1776-1779)
+    cudaSetDevice(g_ctx.device);
+    return &g_ctx;
+}
+
+// ---------------------------------------------------------------------------
+// caching allocators (the device-side twin of src/caching_allocator.zig's
+// size-class freelist; replaces the grow-only DeviceBuf / PinnedBuf of
+// backend/cuda.zig:873-890, :1026-1041). Blocks are recycled by class and
+// only returned to the driver by trim(). Reuse is safe because every consumer
+// of a recycled block is ordered on the library's compute stream.
+// ---------------------------------------------------------------------------
+static size_t size_class(size_t n) {
+    if (n <= 512) return 512;
+    if (n <= (1u << 20)) {
+        size_t c = 512;
+        while (c < n) c <<= 1;
+        return c;
+    }
+    const size_t mb2 = 2u << 20;
+    return (n + mb2 - 1) / mb2 * mb2;
+}
+
+class BlockCache {
+   public:
+    explicit BlockCache(bool pinned) : pinned_(pinned) {}
+    void* alloc(size_t n) {
+        const size_t c = size_class(n);
+        std::lock_guard<std::mutex> g(lock_);
+        auto it = free_.find(c);
+        if (it != free_.end() && !it->second.empty()) {
+            void* p = it->second.back();
+            it->second.pop_back();
+            live_[p] = c;
+            cached_ -= c;
+            return p;
+        }
+        void* p = nullptr;
+        cudaError_t e = pinned_ ? cudaHostAlloc(&p, c, cudaHostAllocDefault) : cudaMalloc(&p, c);
+        if (e != cudaSuccess) {
+            // give cached blocks back to the driver and retry once
+            trim_locked();
+            e = pinned_ ? cudaHostAlloc(&p, c, cudaHostAllocDefault) : cudaMalloc(&p, c);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                return nullptr;
+            }
+        }
+        live_[p] = c;
+        total_ += c;
+        return p;
+    }
+    void release(void* p) {
+        if (!p) return;
+        std::lock_guard<std::mutex> g(lock_);
+        auto it = live_.find(p);
+        if (it == live_.end()) return;
+        free_[it->second].push_back(p);
+        cached_ += it->second;
+        live_.erase(it);
+    }
+    void trim() {
+        std::lock_guard<std::mutex> g(lock_);
+        trim_locked();
+    }
+    size_t total() const { return total_; }
+
+   private:
+    void trim_locked() {
+        for (auto& kv : free_)
+            for (void* p : kv.second) {
+                if (pinned_) cudaFreeHost(p); else cudaFree(p);
+                total_ -= kv.first;
+            }
+        free_.clear();
+        cached_ = 0;
+    }
+    bool pinned_;
+    std::mutex lock_;
+    std::map<size_t, std::vector<void*>> free_;
+    std::unordered_map<void*, size_t> live_;
+    size_t total_ = 0, cached_ = 0;
+};
+static BlockCache g_dev_cache(false), g_pin_cache(true);
+
+void* dev_alloc(size_t n) { return g_dev_cache.alloc(n); }
+void dev_free(void* p) { g_dev_cache.release(p); }
+void* pin_alloc(size_t n) { return g_pin_cache.alloc(n); }
+void pin_free(void* p) { g_pin_cache.release(p); }
+
+// ---------------------------------------------------------------------------
+// weights
+// ---------------------------------------------------------------------------
+}  // namespace fq
+
+namespace fq {
+
+static int check_format(int fmt) {
+    return format_info(fmt).block_elems ? FQ_OK : fail(FQ_DECLINED_ARGS, "format %d is not served by this provider", fmt);
+}
+
+static int check_dims(int fmt, size_t n, size_t k, size_t n_mats, size_t nb01, size_t nb02) {
+    if (int rc = check_format(fmt)) return rc;
+    const FormatInfo f = format_info(fmt);
+    if (n == 0 || k == 0 || n_mats == 0) return fail(FQ_DECLINED_ARGS, "empty weight matrix");
+    if (n > INT32_MAX || k > INT32_MAX || n_mats > INT32_MAX) return fail(FQ_DECLINED_ARGS, "dimension exceeds int32");
+    if (k % 32 != 0 || k % f.block_elems != 0) return fail(FQ_DECLINED_ARGS, "k=%zu is not a whole number of %d-element blocks", k, f.block_elems);
+    const size_t row = k / f.block_elems * f.block_bytes;
+    if (nb01 < row || nb01 % 2 != 0) return fail(FQ_DECLINED_ARGS, "nb01=%zu too small or odd for k=%zu", nb01, k);
+    if (f.sc_bytes == 0 && nb01 % 16 != 0) return fail(FQ_DECLINED_ARGS, "K-quant row stride must be a multiple of 16 bytes");
+    if (n_mats > 1 && (nb02 < nb01 * n || nb02 % 2 != 0 || (f.sc_bytes == 0 && nb02 % 16 != 0)))
+        return fail(FQ_DECLINED_ARGS, "nb02=%zu inconsistent with n=%zu nb01=%zu", nb02, n, nb01);
+    return FQ_OK;
+}
+
+// Build the device layout from raw GGUF bytes already on the device.
+static int weights_from_dev_bytes(Ctx* ctx, int fmt, const uint8_t* raw_dev, size_t nb01, size_t nb02, size_t n, size_t k,
+                                  size_t n_mats, fq_weights** out) {
+    const size_t stride = dev_row_stride(fmt, k);
+    const size_t mat_stride = stride * n;
+    const size_t bytes = mat_stride * n_mats;
+    void* p = dev_alloc(bytes);
+    if (!p) return fail(FQ_DECLINED_BUDGET, "device allocation of %zu bytes failed", bytes);
+    fq_weights* w = new fq_weights();
+    w->dw = {(const uint8_t*)p, stride, mat_stride, fmt, (int)n, (int)k, (int)n_mats};
+    w->alloc = p;
+    w->bytes = bytes;
+    if ((stride * n) % 16 != 0 || ((uintptr_t)raw_dev % 2) != 0) {
+        dev_free(p);
+        delete w;
+        return fail(FQ_DECLINED_ARGS, "unaligned weight bytes");
+    }
+    // K-quant rows are copied in 16-byte units: the source must be 16-byte aligned
+    if (format_info(fmt).sc_bytes == 0 && ((uintptr_t)raw_dev % 16) != 0) {
+        dev_free(p);
+        delete w;
+        return fail(FQ_DECLINED_ARGS, "K-quant device bytes must be 16-byte aligned");
+    }
+    cudaError_t e = launch_repack(w->dw, raw_dev, nb01, n_mats > 1 ? nb02 : nb01 * n, true, ctx->stream);
+    g_trace.launches++;
+    if (e != cudaSuccess) {
+        dev_free(p);
+        delete w;
+        return cuda_fail(e, "repack launch");
+    }
+    *out = w;
+    return FQ_OK;
+}
+
+static int weights_upload_impl(Ctx* ctx, int fmt, const void* host, size_t nb01, size_t nb02, size_t n, size_t k, size_t n_mats,
+                               fq_weights** out) {
+    if (int rc = check_dims(fmt, n, k, n_mats, nb01, nb02)) return rc;
+    const size_t span = (n_mats > 1 ? nb02 * (n_mats - 1) : 0) + nb01 * n;
+    void* raw = dev_alloc(span);
+    if (!raw) return fail(FQ_DECLINED_BUDGET, "device allocation of %zu bytes failed", span);
+    cudaError_t e = cudaMemcpyAsync(raw, host, span, cudaMemcpyHostToDevice, ctx->stream);
+    g_trace.h2d_bytes += span;
+    if (e != cudaSuccess) {
+        dev_free(raw);
+        return cuda_fail(e, "weight upload");
+    }
+    int rc = weights_from_dev_bytes(ctx, fmt, (const uint8_t*)raw, nb01, nb02, n, k, n_mats, out);
+    // the raw copy is only read by the repack kernel queued above on the same stream
+    e = cudaStreamSynchronize(ctx->stream);
+    dev_free(raw);
+    if (rc == FQ_OK && e != cudaSuccess) {
+        fq_weights_free(*out);
+        *out = nullptr;
+        return cuda_fail(e, "weight repack");
+    }
+    return rc;
+}
+
+// ---------------------------------------------------------------------------
+// resident registry (backend/cuda.zig:1518-1611, :1733-1806): host source
+// range -> device twin, budgeted, 512 entries.
+// ---------------------------------------------------------------------------
+struct ResidentEntry {
+    uintptr_t src_base;
+    size_t len;
+    bool owned;          // fq_alloc_resident bytes (page-locked host memory we own)
+    fq_weights* twin;    // device copy, made on first use
+    size_t nb01;
+};
+static const size_t kResidentSlots = 512;
+static std::mutex g_res_lock;
+static std::vector<ResidentEntry> g_res;
+static size_t g_res_outstanding = 0;
+
+static int resident_find(uintptr_t p, size_t len) {
+    for (size_t i = 0; i < g_res.size(); ++i)
+        if (p >= g_res[i].src_base && p + len <= g_res[i].src_base + g_res[i].len) return (int)i;
+    return -1;
+}
+
+// Resolve host rhs bytes to a device view of `n` rows x `n_mats` matrices.
+// temp != nullptr on return means the caller must free it after the launch.
+int resolve_rhs(Ctx* ctx, int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02, size_t n,
+                       size_t k, size_t n_mats, DevWeights* view, fq_weights** temp) {
+    *temp = nullptr;
+    if (int rc = check_dims(fmt, n, k, n_mats, nb01, nb02)) return rc;
+    const size_t span = (n_mats > 1 ? nb02 * (n_mats - 1) : 0) + nb01 * n;
+    if (rhs_len < span) return fail(FQ_DECLINED_ARGS, "rhs_len=%zu shorter than the %zu bytes the shape needs", rhs_len, span);
+    const uintptr_t p = (uintptr_t)rhs;
+    {
+        std::unique_lock<std::mutex> g(g_res_lock);
+        int i = resident_find(p, span);
+        if (i < 0 && cacheable) {
+            // adopt by source address
+            if (g_res.size() >= kResidentSlots) return fail(FQ_DECLINED_BUDGET, "resident registry full");
+            const size_t need = dev_row_stride(fmt, k) * (rhs_len / nb01);
+            if (ctx->vram_budget > 0 && g_res_outstanding + need > ctx->vram_budget)
+                return fail(FQ_DECLINED_BUDGET, "resident budget exceeded (%zu + %zu > %zu)", g_res_outstanding, need, ctx->vram_budget);
+            g_res.push_back({p, rhs_len, false, nullptr, 0});
+            i = (int)g_res.size() - 1;
+            g_trace.resident_adopts++;
+        }
+        if (i >= 0) {
+            ResidentEntry& e = g_res[i];
+            if (!e.twin) {
+                // the whole range becomes rows of nb01 bytes (an expert stack is rows too when nb02 == n*nb01)
+                if (n_mats > 1 && nb02 != nb01 * n) return fail(FQ_DECLINED_ARGS, "resident expert stacks must be dense (nb02 == n*nb01)");
+                const size_t rows_total = e.len / nb01;
+                const size_t need = dev_row_stride(fmt, k) * rows_total;
+                if (ctx->vram_budget > 0 && g_res_outstanding + need > ctx->vram_budget)
+                    return fail(FQ_DECLINED_BUDGET, "resident budget exceeded (%zu + %zu > %zu)", g_res_outstanding, need, ctx->vram_budget);
+                fq_weights* w = nullptr;
+                const void* src_base = (const void*)e.src_base;  // `e` may move once the lock drops
+                g.unlock();
+                int rc = weights_upload_impl(ctx, fmt, src_base, nb01, 0, rows_total, k, 1, &w);
+                g.lock();
+                if (rc != FQ_OK) return rc;
+                ResidentEntry& e2 = g_res[resident_find(p, span)];
+                if (e2.twin) {
+                    fq_weights_free(w);  // raced with another adopter; keep theirs
+                } else {
+                    e2.twin = w;
+                    e2.nb01 = nb01;
+                    g_res_outstanding += w->bytes;
+                }
+            } else {
+                g_trace.resident_hits++;
+            }
+            ResidentEntry& e3 = g_res[resident_find(p, span)];
+            const fq_weights* tw = e3.twin;
+            if (tw->dw.fmt != fmt || tw->dw.k != (int)k || e3.nb01 != nb01)
+                return fail(FQ_DECLINED_ARGS, "resident bytes were registered with a different format or row shape");
+            const size_t off = p - e3.src_base;
+            if (off % nb01 != 0 || (n_mats > 1 && nb02 != nb01 * n))
+                return fail(FQ_DECLINED_ARGS, "rhs does not start on a weight row of its resident range");
+            *view = tw->dw;
+            view->base += (off / nb01) * tw->dw.row_stride;
+            view->n = (int)n;
+            view->n_mats = (int)n_mats;
+            view->mat_stride = tw->dw.row_stride * n;
+            return FQ_OK;
+        }
+    }
+    // transient: stream the bytes for this call only
+    fq_weights* w = nullptr;
+    int rc = weights_upload_impl(ctx, fmt, rhs, nb01, nb02, n, k, n_mats, &w);
+    if (rc != FQ_OK) return rc;
+    *view = w->dw;
+    *temp = w;
+    return FQ_OK;
+}
+
+// ---------------------------------------------------------------------------
+// dense matmul on device buffers
+// ---------------------------------------------------------------------------
+int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, int mode,
+             int accumulate, cudaStream_t st) {
+    if (m == 0) return fail(FQ_DECLINED_ARGS, "m == 0");
+    if (mat < 0 || mat >= w.n_mats) return fail(FQ_DECLINED_ARGS, "matrix index out of range");
+    if (mode == FQ_MODE_TENSOR || (mode == FQ_MODE_AUTO && m > gemv_max_rows() && !accumulate)) {
+        int rc = gemm_tensor_dev(ctx, w, mat, a_dev, c_dev, m, ldc, st);
+        if (rc != FQ_DECLINED_ARGS || mode == FQ_MODE_TENSOR) return rc;
+        // shapes the tensor-core kernel does not take fall through to the integer kernel
+    }
+    const ActSizes S = act_sizes(w.fmt, w.k);
+    const size_t chunk_max = gemv_max_rows();
+    const size_t rows_scratch = m < chunk_max ? m : chunk_max;
+    uint8_t* scratch = (uint8_t*)dev_alloc(S.row * rows_scratch);
+    if (!scratch) return fail(FQ_DECLINED_BUDGET, "activation scratch allocation failed");
+    int rc = FQ_OK;
+    for (size_t r0 = 0; r0 < m && rc == FQ_OK; r0 += chunk_max) {
+        const int rows = (int)((m - r0) < chunk_max ? (m - r0) : chunk_max);
+        cudaError_t e = launch_quantize_acts_layout(a_dev + r0 * w.k, nullptr, 1, rows, w.k, w.fmt, scratch, st);
+        g_trace.launches++;
+        if (e != cudaSuccess) { rc = cuda_fail(e, "activation quantise launch"); break; }
+        GemvArgs ga{w, DevWeights{}, mat, scratch, c_dev + r0 * ldc, rows, (int)ldc, accumulate, nullptr, nullptr, 0};
+        e = launch_gemv(ga, ctx->sm_count, st);
+        g_trace.launches++;
+        if (e != cudaSuccess) rc = cuda_fail(e, "gemv launch");
+    }
+    // the scratch block returns to the cache now; any later user is ordered after
+    // these kernels because all library work runs on one stream
+    if (st != ctx->stream) cudaStreamSynchronize(st);
+    dev_free(scratch);
+    return rc;
+}
+
+// ---------------------------------------------------------------------------
+// host-buffer helpers
+// ---------------------------------------------------------------------------
+static bool host_is_pinned(const void* p) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return attr.type == cudaMemoryTypeHost;
+}
+
+struct Staged {
+    void* dev = nullptr;
+    void* pin = nullptr;
+};
+
+static int upload_f32(Ctx* ctx, const float* host, size_t bytes, Staged* s) {
+    s->dev = dev_alloc(bytes);
+    if (!s->dev) return fail(FQ_DECLINED_BUDGET, "device allocation of %zu bytes failed", bytes);
+    const void* src = host;
+    if (!host_is_pinned(host)) {
+        s->pin = pin_alloc(bytes);
+        if (!s->pin) return fail(FQ_DECLINED_BUDGET, "pinned allocation of %zu bytes failed", bytes);
+        memcpy(s->pin, host, bytes);
+        src = s->pin;
+    }
+    cudaError_t e = cudaMemcpyAsync(s->dev, src, bytes, cudaMemcpyHostToDevice, ctx->stream);
+    g_trace.h2d_bytes += bytes;
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "activation upload");
+}
+
+static int download_f32(Ctx* ctx, const void* dev, float* host, size_t bytes) {
+    cudaError_t e;
+    if (host_is_pinned(host)) {
+        e = cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    } else {
+        void* pin = pin_alloc(bytes);
+        if (!pin) return fail(FQ_DECLINED_BUDGET, "pinned allocation of %zu bytes failed", bytes);
+        e = cudaMemcpyAsync(pin, dev, bytes, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e == cudaSuccess) memcpy(host, pin, bytes);
+        pin_free(pin);
+    }
+    g_trace.d2h_bytes += bytes;
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "result download");
+}
+
+static int gate_and_ctx(Ctx** out) {
+    ensure_config();
+    if (!g_cfg.gpu_enabled) return fail(FQ_DECLINED_GATE, "disabled by FUCINA_GPU=0");
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    *out = ctx;
+    return FQ_OK;
+}
+
+static int check_gemm_args(int fmt, size_t batch, size_t m, size_t n, size_t k) {
+    if (int rc = check_format(fmt)) return rc;
+    if (batch == 0 || m == 0 || n == 0 || k == 0) return fail(FQ_DECLINED_ARGS, "empty problem");
+    if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX || batch > INT32_MAX) return fail(FQ_DECLINED_ARGS, "dimension exceeds int32");
+    // backend/cuda.zig:2017: n % 4 == 0, k a whole number of blocks and of 32
+    if (n % 4 != 0) return fail(FQ_DECLINED_ARGS, "n=%zu is not a multiple of 4", n);
+    if (k % 32 != 0 || k % format_info(fmt).block_elems != 0) return fail(FQ_DECLINED_ARGS, "k=%zu is not a whole number of blocks", k);
+    return FQ_OK;
+}
+
+// shared body of the blocking host entries: batch weight matrices, one shared input
+static int gemm_host(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02, const float* a, float* c,
+                     size_t batch, size_t m, size_t n, size_t k) {
+    if (!rhs || !a || !c) return fail(FQ_DECLINED_ARGS, "null pointer");
+    if (int rc = check_gemm_args(fmt, batch, m, n, k)) return rc;
+    Ctx* ctx = nullptr;
+    if (int rc = gate_and_ctx(&ctx)) return rc;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    g_trace.calls++;
+    DevWeights view;
+    fq_weights* temp = nullptr;
+    int rc = resolve_rhs(ctx, fmt, rhs, rhs_len, cacheable, nb01, nb02, n, k, batch, &view, &temp);
+    if (rc != FQ_OK) return rc;
+    Staged in;
+    const size_t out_bytes = batch * m * n * sizeof(float);
+    void* c_dev = nullptr;
+    rc = upload_f32(ctx, a, m * k * sizeof(float), &in);
+    if (rc == FQ_OK) {
+        c_dev = dev_alloc(out_bytes);
+        if (!c_dev) rc = fail(FQ_DECLINED_BUDGET, "device allocation of %zu bytes failed", out_bytes);
+    }
+    bool submitted = false;
+    for (size_t b = 0; b < batch && rc == FQ_OK; ++b) {
+        rc = gemm_dev(ctx, view, (int)b, (const float*)in.dev, (float*)c_dev + b * m * n, m, n, FQ_MODE_AUTO, 0, ctx->stream);
+        submitted = true;
+    }
+    if (rc == FQ_OK) rc = download_f32(ctx, c_dev, c, out_bytes);
+    else if (submitted) cudaStreamSynchronize(ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    dev_free(c_dev);
+    dev_free(in.dev);
+    pin_free(in.pin);
+    if (temp) fq_weights_free(temp);
+    // a decline after kernels were queued wrote nothing to `c`; device failures stay negative
+    return rc;
+}
+
+// ---------------------------------------------------------------------------
+// async completion tokens (accelerator.zig:22-133; backend/cuda.zig:1087-1218)
+// ---------------------------------------------------------------------------
+static const int kAsyncSlots = 8;
+static std::atomic<int> g_slots_in_use{0};
+
+}  // namespace fq
+
+struct fq_work {
+    void* c_dev;
+    size_t bytes;
+    float* c_host;
+    cudaEvent_t done;
+    int state;  // 0 submitted, 1 host_ready, 2 discarded, -1 failed
+};
+
+using namespace fq;
+
+extern "C" {
+
+int fq_init(int device) {
+    ensure_config();
+    std::lock_guard<std::mutex> g(g_init_lock);
+    if (g_init_state.load() == 1) return (device < 0 || device == g_ctx.device) ? FQ_OK : fail(FQ_DECLINED_ARGS, "already initialised on device %d", g_ctx.device);
+    const int rc = init_locked(device);
+    g_init_state.store(rc == FQ_OK ? 1 : 2);
+    return rc;
+}
+int fq_device_count(void) {
+    int c = 0;
+    if (cudaGetDeviceCount(&c) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return c;
+}
+const char* fq_device_name(void) { return context() ? g_ctx.name : ""; }
+int fq_sm_count(void) { return context() ? g_ctx.sm_count : 0; }
+int fq_last_error(char* buf, size_t len) {
+    std::lock_guard<std::mutex> g(g_err_lock);
+    if (buf && len) snprintf(buf, len, "%s", g_last_error.c_str());
+    return (int)g_last_error.size();
+}
+void* fq_stream(void) { return context() ? (void*)g_ctx.stream : nullptr; }
+int fq_synchronize(void) {
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "synchronize");
+}
+
+size_t fq_block_elems(int fmt) { return format_info(fmt).block_elems; }
+size_t fq_block_bytes(int fmt) { return format_info(fmt).block_bytes; }
+size_t fq_row_bytes(int fmt, size_t k) {
+    const FormatInfo f = format_info(fmt);
+    return f.block_elems ? k / f.block_elems * f.block_bytes : 0;
+}
+
+// ---- residency ------------------------------------------------------------
+void* fq_alloc_resident(size_t len) {
+    Ctx* ctx = nullptr;
+    if (len == 0 || gate_and_ctx(&ctx) != FQ_OK) return nullptr;
+    {
+        std::lock_guard<std::mutex> g(g_res_lock);
+        if (g_res.size() >= kResidentSlots || (ctx->vram_budget > 0 && g_res_outstanding + len > ctx->vram_budget)) {
+            fail(FQ_DECLINED_BUDGET, "resident budget exceeded");
+            return nullptr;
+        }
+    }
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, len, cudaHostAllocDefault) != cudaSuccess) {
+        cudaGetLastError();
+        fail(FQ_DECLINED_BUDGET, "page-locked allocation of %zu bytes failed", len);
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> g(g_res_lock);
+    g_res.push_back({(uintptr_t)p, len, true, nullptr, 0});
+    return p;
+}
+static void drop_entry_locked(size_t i) {
+    ResidentEntry e = g_res[i];
+    g_res.erase(g_res.begin() + i);
+    if (e.twin) {
+        g_res_outstanding -= e.twin->bytes;
+        fq_weights_free(e.twin);
+    }
+    if (e.owned) cudaFreeHost((void*)e.src_base);
+}
+void fq_free_resident(const void* p) {
+    if (!p || !context()) return;
+    std::lock_guard<std::recursive_mutex> d(g_dispatch_lock);
+    cudaStreamSynchronize(g_ctx.stream);
+    std::lock_guard<std::mutex> g(g_res_lock);
+    for (size_t i = 0; i < g_res.size(); ++i)
+        if (g_res[i].src_base == (uintptr_t)p) {
+            drop_entry_locked(i);
+            return;
+        }
+}
+int fq_evict_resident(const void* host_ptr) {
+    if (!context()) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> d(g_dispatch_lock);
+    cudaStreamSynchronize(g_ctx.stream);
+    std::lock_guard<std::mutex> g(g_res_lock);
+    const int i = resident_find((uintptr_t)host_ptr, 1);
+    if (i < 0) return fail(FQ_DECLINED_ARGS, "address is not resident");
+    if (g_res[i].owned) return fail(FQ_DECLINED_ARGS, "owned resident bytes are released with fq_free_resident");
+    drop_entry_locked(i);
+    return FQ_OK;
+}
+size_t fq_resident_bytes(void) {
+    std::lock_guard<std::mutex> g(g_res_lock);
+    return g_res_outstanding;
+}
+int fq_set_vram_budget(size_t bytes) {
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    ctx->vram_budget = bytes;
+    return FQ_OK;
+}
+
+// ---- explicit device weights ----------------------------------------------
+int fq_weights_upload(int fmt, const void* host_blocks, size_t nb01, size_t nb02, size_t n, size_t k, size_t n_mats,
+                      fq_weights** out) {
+    if (!host_blocks || !out) return fail(FQ_DECLINED_ARGS, "null pointer");
+    Ctx* ctx = nullptr;
+    if (int rc = gate_and_ctx(&ctx)) return rc;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    return weights_upload_impl(ctx, fmt, host_blocks, nb01, nb02, n, k, n_mats, out);
+}
+int fq_weights_from_device(int fmt, const void* dev_blocks, size_t nb01, size_t nb02, size_t n, size_t k, size_t n_mats,
+                           fq_weights** out) {
+    if (!dev_blocks || !out) return fail(FQ_DECLINED_ARGS, "null pointer");
+    Ctx* ctx = nullptr;
+    if (int rc = gate_and_ctx(&ctx)) return rc;
+    if (int rc = check_dims(fmt, n, k, n_mats, nb01, nb02)) return rc;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    int rc = weights_from_dev_bytes(ctx, fmt, (const uint8_t*)dev_blocks, nb01, nb02, n, k, n_mats, out);
+    if (rc == FQ_OK) {
+        cudaError_t e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) return cuda_fail(e, "weight repack");
+    }
+    return rc;
+}
+void fq_weights_free(fq_weights* w) {
+    if (!w) return;
+    if (w->alloc) dev_free(w->alloc);
+    delete w;
+}
+size_t fq_weights_device_bytes(const fq_weights* w) { return w ? w->bytes : 0; }
+
+int fq_weights_download_gguf(const fq_weights* w, void* host_blocks, size_t len) {
+    if (!w || !host_blocks) return fail(FQ_DECLINED_ARGS, "null pointer");
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    const size_t nb01 = fq_row_bytes(w->dw.fmt, w->dw.k);
+    const size_t span = nb01 * w->dw.n * w->dw.n_mats;
+    if (len < span) return fail(FQ_DECLINED_ARGS, "buffer too small (%zu < %zu)", len, span);
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    void* raw = dev_alloc(span);
+    if (!raw) return fail(FQ_DECLINED_BUDGET, "device allocation failed");
+    cudaError_t e = launch_repack(w->dw, (const uint8_t*)raw, nb01, nb01 * w->dw.n, false, ctx->stream);
+    g_trace.launches++;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host_blocks, raw, span, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    dev_free(raw);
+    g_trace.d2h_bytes += span;
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "weight download");
+}
+
+int fq_dequantize_rows_dev(const fq_weights* w, size_t mat, size_t row0, size_t rows, float* dev_out) {
+    if (!w || !dev_out) return fail(FQ_DECLINED_ARGS, "null pointer");
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    if (mat >= (size_t)w->dw.n_mats || row0 + rows > (size_t)w->dw.n || rows == 0) return fail(FQ_DECLINED_ARGS, "row range out of bounds");
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    cudaError_t e = launch_dequant_rows(w->dw, (int)mat, (int)row0, (int)rows, dev_out, ctx->stream);
+    g_trace.launches++;
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "dequant launch");
+}
+int fq_dequantize_rows(const fq_weights* w, size_t mat, size_t row0, size_t rows, float* host_out) {
+    if (!w || !host_out) return fail(FQ_DECLINED_ARGS, "null pointer");
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    const size_t bytes = rows * (size_t)w->dw.k * sizeof(float);
+    void* d = dev_alloc(bytes);
+    if (!d) return fail(FQ_DECLINED_BUDGET, "device allocation failed");
+    int rc = fq_dequantize_rows_dev(w, mat, row0, rows, (float*)d);
+    if (rc == FQ_OK) rc = download_f32(ctx, d, host_out, bytes);
+    cudaStreamSynchronize(ctx->stream);
+    dev_free(d);
+    return rc;
+}
+
+int fq_quantize_rows_dev(int fmt, const float* dev_src, size_t n, size_t k, void* dev_blocks) {
+    if (!dev_src || !dev_blocks) return fail(FQ_DECLINED_ARGS, "null pointer");
+    if (fmt == FQ_TQ2_0_FOLDED) return fail(FQ_DECLINED_ARGS, "folded blocks are built from two planes, not from f32 rows");
+    const FormatInfo f = format_info(fmt);
+    if (!f.block_elems || k == 0 || n == 0 || k % f.block_elems != 0) return fail(FQ_DECLINED_ARGS, "k=%zu is not a whole number of blocks", k);
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    cudaError_t e = launch_quantize_weights(fmt, dev_src, n, k, (uint8_t*)dev_blocks, ctx->stream);
+    g_trace.launches++;
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "weight encoder launch");
+}
+
+// ---- dense, host buffers ----------------------------------------------------
+int fq_gemm_quant_nt(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, const float* a, float* c, size_t m,
+                     size_t n, size_t k) {
+    return gemm_host(fmt, rhs, rhs_len, cacheable, nb01, 0, a, c, 1, m, n, k);
+}
+int fq_gemm_quant_nt_shared_a_batch(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02,
+                                    const float* a, float* c, size_t batch, size_t m, size_t n, size_t k) {
+    return gemm_host(fmt, rhs, rhs_len, cacheable, nb01, nb02, a, c, batch, m, n, k);
+}
+
+// ---- async -------------------------------------------------------------------
+int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02, const float* a,
+                           fq_work* a_dep, float* c_host, size_t batch, size_t m, size_t n, size_t k, fq_work** out_work) {
+    if (!rhs || (!a && !a_dep) || !out_work) return fail(FQ_DECLINED_ARGS, "null pointer");
+    // the async arm only takes stable model weights (backend/cuda.zig:2014)
+    if (!cacheable) return fail(FQ_DECLINED_ARGS, "async submit needs a cacheable rhs");
+    if (int rc = check_gemm_args(fmt, batch, m, n, k)) return rc;
+    if (a_dep && (a_dep->state != 0 || a_dep->bytes < m * k * sizeof(float))) return fail(FQ_DECLINED_ARGS, "dependency is not a pending producer of m*k floats");
+    Ctx* ctx = nullptr;
+    if (int rc = gate_and_ctx(&ctx)) return rc;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    if (g_slots_in_use.load() >= kAsyncSlots) return fail(FQ_DECLINED_BUSY, "all %d async slots are in flight", kAsyncSlots);
+    g_trace.calls++;
+    DevWeights view;
+    fq_weights* temp = nullptr;
+    int rc = resolve_rhs(ctx, fmt, rhs, rhs_len, 1, nb01, nb02, n, k, batch, &view, &temp);
+    if (rc != FQ_OK) return rc;
+    Staged in;
+    const float* a_dev = a_dep ? (const float*)a_dep->c_dev : nullptr;
+    if (!a_dev) {
+        rc = upload_f32(ctx, a, m * k * sizeof(float), &in);
+        a_dev = (const float*)in.dev;
+    }
+    fq_work* w = nullptr;
+    if (rc == FQ_OK) {
+        w = new fq_work();
+        w->bytes = batch * m * n * sizeof(float);
+        w->c_dev = dev_alloc(w->bytes);
+        w->c_host = c_host;
+        w->state = 0;
+        w->done = nullptr;
+        if (!w->c_dev) rc = fail(FQ_DECLINED_BUDGET, "device allocation failed");
+        else if (cudaEventCreateWithFlags(&w->done, cudaEventDisableTiming) != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "event create");
+    }
+    for (size_t b = 0; b < batch && rc == FQ_OK; ++b)
+        rc = gemm_dev(ctx, view, (int)b, a_dev, (float*)w->c_dev + b * m * n, m, n, FQ_MODE_AUTO, 0, ctx->stream);
+    if (rc == FQ_OK) {
+        cudaError_t e = cudaEventRecord(w->done, ctx->stream);
+        if (e != cudaSuccess) rc = cuda_fail(e, "event record");
+    }
+    // staging blocks go back to the cache; later users are stream-ordered after this submit
+    dev_free(in.dev);
+    if (in.pin) {
+        cudaStreamSynchronize(ctx->stream);  // the pinned source must outlive its copy
+        pin_free(in.pin);
+    }
+    if (rc != FQ_OK) {
+        cudaStreamSynchronize(ctx->stream);
+        if (w) {
+            if (w->done) cudaEventDestroy(w->done);
+            dev_free(w->c_dev);
+            delete w;
+        }
+        return rc;
+    }
+    g_slots_in_use++;
+    *out_work = w;
+    return FQ_OK;
+}
+
+int fq_work_finish(fq_work* w, int copy_to_host) {
+    if (!w) return fail(FQ_DECLINED_ARGS, "null work");
+    if (w->state == 1 || w->state == 2) return FQ_OK;
+    if (w->state < 0) return FQ_ERR_CUDA;
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    cudaError_t e = cudaEventSynchronize(w->done);
+    if (e != cudaSuccess) {
+        w->state = -1;
+        return cuda_fail(e, "work wait");
+    }
+    if (copy_to_host && w->c_host) {
+        // order the copy after the producer on the compute stream
+        int rc = download_f32(ctx, w->c_dev, w->c_host, w->bytes);
+        if (rc != FQ_OK) {
+            w->state = -1;
+            return rc;
+        }
+        w->state = 1;
+    } else {
+        w->state = 2;
+    }
+    return FQ_OK;
+}
+uintptr_t fq_work_device_ptr(fq_work* w) { return w ? (uintptr_t)w->c_dev : 0; }
+void fq_work_destroy(fq_work* w) {
+    if (!w) return;
+    if (context()) {
+        std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+        if (w->state == 0) cudaEventSynchronize(w->done);
+        // a consumer chained on this output may still be queued on the stream
+        cudaStreamSynchronize(g_ctx.stream);
+        cudaEventDestroy(w->done);
+        dev_free(w->c_dev);
+    }
+    g_slots_in_use--;
+    delete w;
+}
+
+// ---- dense, device buffers ---------------------------------------------------
+int fq_gemm_quant_nt_dev(const fq_weights* w, size_t mat, const float* a_dev, float* c_dev, size_t m, int mode, void* stream) {
+    if (!w || !a_dev || !c_dev) return fail(FQ_DECLINED_ARGS, "null pointer");
+    Ctx* ctx = nullptr;
+    if (int rc = gate_and_ctx(&ctx)) return rc;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    g_trace.calls++;
+    return gemm_dev(ctx, w->dw, (int)mat, a_dev, c_dev, m, (size_t)w->dw.n, mode, 0, stream ? (cudaStream_t)stream : ctx->stream);
+}
+int fq_gemm_ptqtp_dev(const fq_weights* const* planes, int n_planes, const float* a_dev, float* c_dev, size_t m, void* stream) {
+    if (!planes || n_planes < 1 || n_planes > 3 || !a_dev || !c_dev) return fail(FQ_DECLINED_ARGS, "bad plane list");
+    for (int p = 0; p < n_planes; ++p) {
+        if (!planes[p] || planes[p]->dw.fmt != FQ_TQ2_0) return fail(FQ_DECLINED_ARGS, "PTQTP planes are TQ2_0 tensors");
+        if (planes[p]->dw.n != planes[0]->dw.n || planes[p]->dw.k != planes[0]->dw.k) return fail(FQ_DECLINED_ARGS, "plane shapes differ");
+    }
+    Ctx* ctx = nullptr;
+    if (int rc = gate_and_ctx(&ctx)) return rc;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    g_trace.calls++;
+    cudaStream_t st = stream ? (cudaStream_t)stream : ctx->stream;
+    for (int p = 0; p < n_planes; ++p) {
+        int rc = gemm_dev(ctx, planes[p]->dw, 0, a_dev, c_dev, m, (size_t)planes[0]->dw.n, FQ_MODE_INT8, p > 0, st);
+        if (rc != FQ_OK) return rc;
+    }
+    return FQ_OK;
+}
+static int quantize_acts_struct(const float* a_dev, size_t m, size_t k, void* dev_blocks, bool q8k) {
+    if (!a_dev || !dev_blocks || m == 0 || k == 0) return fail(FQ_DECLINED_ARGS, "bad arguments");
+    if (k % (q8k ? 256 : 32) != 0) return fail(FQ_DECLINED_ARGS, "k=%zu is not a whole number of activation blocks", k);
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    cudaError_t e = launch_quantize_acts_struct(a_dev, (int)m, (int)k, q8k, (uint8_t*)dev_blocks, ctx->stream);
+    g_trace.launches++;
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "activation quantise launch");
+}
+int fq_quantize_acts_q8_k_dev(const float* a_dev, size_t m, size_t k, void* dev_blocks) { return quantize_acts_struct(a_dev, m, k, dev_blocks, true); }
+int fq_quantize_acts_q8_0_dev(const float* a_dev, size_t m, size_t k, void* dev_blocks) { return quantize_acts_struct(a_dev, m, k, dev_blocks, false); }
+
+// ---- gates (backend/cuda.zig:2494-2554) --------------------------------------
+static int gate(bool pass) {
+    if (pass) g_trace.gate_pass++; else g_trace.gate_fail++;
+    return pass ? 1 : 0;
+}
+int fq_should_use_gpu_qmoe(uint64_t total_work) {
+    ensure_config();
+    return gate(g_cfg.gpu_enabled && total_work >= g_cfg.min_work_qmoe);
+}
+int fq_qmoe_fill_acceptable(size_t rows, size_t n_tiles) {
+    ensure_config();
+    if (n_tiles == 0) return 0;
+    return (uint64_t)rows * 100 >= (uint64_t)n_tiles * 32 * g_cfg.qmoe_min_fill_pct;
+}
+int fq_should_use_gpu_dense_quant(int fmt, uint64_t total_work) {
+    ensure_config();
+    uint64_t floor_;
+    switch (fmt) {
+        case FQ_Q5_K: floor_ = g_cfg.min_work_packed_q5; break;
+        case FQ_Q4_K: case FQ_Q8_0: floor_ = g_cfg.min_work_qmoe; break;
+        default: floor_ = g_cfg.min_work_packed_q8; break;
+    }
+    return gate(g_cfg.gpu_enabled && format_info(fmt).block_elems && total_work >= floor_);
+}
+int fq_should_use_gpu_dense_quant_packed(int fmt, uint64_t total_work) {
+    ensure_config();
+    uint64_t floor_;
+    switch (fmt) {
+        case FQ_Q4_K: floor_ = g_cfg.min_work_packed_q4; break;
+        case FQ_Q5_K: floor_ = g_cfg.min_work_packed_q5; break;
+        default: floor_ = g_cfg.min_work_packed_q8; break;
+    }
+    return gate(g_cfg.gpu_enabled && format_info(fmt).block_elems && total_work >= floor_);
+}
+int fq_should_use_gpu_quant_decode(int fmt, size_t m, size_t n, size_t k) {
+    ensure_config();
+    if (!g_cfg.gpu_enabled || !g_cfg.decode_enabled || !format_info(fmt).block_elems) return 0;
+    if (fmt != FQ_Q5_K) return 1;
+    const unsigned __int128 work = (unsigned __int128)m * n * k;
+    return gate(work >= g_cfg.min_work_decode_q5);
+}
+void fq_set_min_work_qmoe_for_test(uint64_t v) {
+    ensure_config();
+    g_cfg.min_work_qmoe = v;
+}
+void fq_set_decode_for_test(int enabled) {
+    ensure_config();
+    g_cfg.decode_enabled = enabled != 0;
+}
+
+// ---- trace -------------------------------------------------------------------
+int fq_trace_enabled(void) {
+    ensure_config();
+    return g_trace_on ? 1 : 0;
+}
+void fq_trace_reset(void) {
+    g_trace.calls = g_trace.launches = g_trace.h2d_bytes = g_trace.d2h_bytes = 0;
+    g_trace.resident_hits = g_trace.resident_adopts = g_trace.gate_pass = g_trace.gate_fail = 0;
+}
+void fq_trace_counters(uint64_t out[8]) {
+    out[0] = g_trace.calls, out[1] = g_trace.launches, out[2] = g_trace.h2d_bytes, out[3] = g_trace.d2h_bytes;
+    out[4] = g_trace.resident_hits, out[5] = g_trace.resident_adopts, out[6] = g_trace.gate_pass, out[7] = g_trace.gate_fail;
+}
+void fq_trace_dump(void) {
+    uint64_t c[8];
+    fq_trace_counters(c);
+    fprintf(stderr,
+            "[fucina_b200] calls=%llu launches=%llu h2d=%llu B d2h=%llu B resident hits=%llu adopts=%llu gate pass=%llu fail=%llu "
+            "resident=%zu B device cache=%zu B\n",
+            (unsigned long long)c[0], (unsigned long long)c[1], (unsigned long long)c[2], (unsigned long long)c[3],
+            (unsigned long long)c[4], (unsigned long long)c[5], (unsigned long long)c[6], (unsigned long long)c[7],
+            fq_resident_bytes(), g_dev_cache.total());
+}
+
+}  // extern "C"

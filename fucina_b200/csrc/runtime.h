@@ -1,0 +1,53 @@
+// Runtime services shared by the translation units (context, allocators,
+// error text, trace counters).
+#pragma once
+#include <atomic>
+#include <mutex>
+
+#include "common.cuh"
+
+struct fq_weights {
+    fq::DevWeights dw;
+    void* alloc;   // owning allocation (nullptr for views)
+    size_t bytes;  // device bytes of the allocation
+};
+
+namespace fq {
+
+struct Ctx {
+    int device = -1;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;    // compute stream: every library kernel and copy is ordered here
+    cudaStream_t transfer = nullptr;  // spare stream for overlapped host transfers
+    size_t vram_budget = 0;
+    char name[256] = {0};
+};
+
+struct Trace {
+    std::atomic<uint64_t> calls{0}, launches{0}, h2d_bytes{0}, d2h_bytes{0};
+    std::atomic<uint64_t> resident_hits{0}, resident_adopts{0}, gate_pass{0}, gate_fail{0};
+};
+extern Trace g_trace;
+extern std::recursive_mutex g_dispatch_lock;
+
+int fail(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+Ctx* context();
+void* dev_alloc(size_t n);
+void dev_free(void* p);
+void* pin_alloc(size_t n);
+void pin_free(void* p);
+
+// Host rhs bytes -> device view (resident registry hit, adoption, or a
+// transient upload the caller frees through *temp after its launches).
+int resolve_rhs(Ctx* ctx, int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02, size_t n, size_t k,
+                size_t n_mats, DevWeights* view, fq_weights** temp);
+
+// c[m, ldc] (+)= a[m, k] . dequant(W[mat])^T on device buffers.
+int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, int mode,
+             int accumulate, cudaStream_t st);
+// gemm_tc.cu: bf16 tensor-core path; returns FQ_DECLINED_ARGS for shapes it does not take.
+int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc,
+                    cudaStream_t st);
+
+}  // namespace fq

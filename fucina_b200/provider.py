@@ -1,0 +1,287 @@
+"""Python mirror of the provider interface (reference `src/backend/cuda.zig` pub surface).
+
+Function names follow the reference (`gemmQuantNt`, `gemmQuantNtAsync`,
+`gemmQGroupedNt`, `allocResidentBytes`, `shouldUseGpu*` ...) in snake case;
+arguments keep their meaning. Where the reference returns `false`/`null`
+("the GPU did not run, nothing was written") these raise `Declined`; a device
+failure after submission raises `DeviceError`. Nothing here computes on the
+CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import formats
+from ._lib import QmmTile, load
+
+MODE_AUTO, MODE_INT8, MODE_TENSOR = 0, 1, 2
+
+
+class Declined(RuntimeError):
+    """The provider refused before any side effect (the reference's `false`)."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"declined ({code}): {msg}")
+        self.code = code
+
+
+class DeviceError(RuntimeError):
+    """A CUDA failure after submission (a failed accelerator.Work)."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"device error ({code}): {msg}")
+        self.code = code
+
+
+def last_error() -> str:
+    buf = C.create_string_buffer(512)
+    load().fq_last_error(buf, 512)
+    return buf.value.decode(errors="replace")
+
+
+def _check(rc: int) -> None:
+    if rc == 0:
+        return
+    if rc > 0:
+        raise Declined(rc, last_error())
+    raise DeviceError(rc, last_error())
+
+
+def _vp(x) -> C.c_void_p:
+    """numpy array, torch tensor, int address or None -> void*."""
+    if x is None:
+        return C.c_void_p(0)
+    if isinstance(x, np.ndarray):
+        return C.c_void_p(x.ctypes.data)
+    if isinstance(x, int):
+        return C.c_void_p(x)
+    if hasattr(x, "data_ptr"):
+        return C.c_void_p(x.data_ptr())
+    raise TypeError(type(x))
+
+
+def init(device: int = -1) -> None:
+    _check(load().fq_init(device))
+
+
+def device_name() -> str:
+    return load().fq_device_name().decode()
+
+
+def sm_count() -> int:
+    return load().fq_sm_count()
+
+
+def stream_ptr() -> int:
+    return int(load().fq_stream() or 0)
+
+
+def synchronize() -> None:
+    _check(load().fq_synchronize())
+
+
+def trace_counters() -> dict:
+    arr = (C.c_uint64 * 8)()
+    load().fq_trace_counters(arr)
+    keys = ["calls", "launches", "h2d_bytes", "d2h_bytes", "resident_hits", "resident_adopts", "gate_pass", "gate_fail"]
+    return dict(zip(keys, [int(v) for v in arr]))
+
+
+# --------------------------------------------------------------------------- weights
+class Weights:
+    """Device-resident weights in the gpu_formats layout (`fq_weights`)."""
+
+    def __init__(self, handle: int, fmt: int, n: int, k: int, n_mats: int):
+        self.handle, self.fmt, self.n, self.k, self.n_mats = handle, fmt, n, k, n_mats
+
+    @classmethod
+    def upload(cls, fmt: int, blocks: np.ndarray, n: int, k: int, n_mats: int = 1) -> "Weights":
+        """blocks: uint8 raw GGUF rows, [n_mats*n, row_bytes] (dense strides)."""
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        nb01 = formats.row_bytes(fmt, k)
+        assert blocks.size == n_mats * n * nb01, (blocks.size, n_mats, n, nb01)
+        h = C.c_void_p()
+        _check(load().fq_weights_upload(fmt, _vp(blocks), nb01, nb01 * n, n, k, n_mats, C.byref(h)))
+        return cls(h.value, fmt, n, k, n_mats)
+
+    @classmethod
+    def from_device(cls, fmt: int, dev_blocks, n: int, k: int, n_mats: int = 1) -> "Weights":
+        nb01 = formats.row_bytes(fmt, k)
+        h = C.c_void_p()
+        _check(load().fq_weights_from_device(fmt, _vp(dev_blocks), nb01, nb01 * n, n, k, n_mats, C.byref(h)))
+        return cls(h.value, fmt, n, k, n_mats)
+
+    def device_bytes(self) -> int:
+        return int(load().fq_weights_device_bytes(self.handle))
+
+    def download_gguf(self) -> np.ndarray:
+        nb01 = formats.row_bytes(self.fmt, self.k)
+        out = np.zeros((self.n_mats * self.n, nb01), dtype=np.uint8)
+        _check(load().fq_weights_download_gguf(self.handle, _vp(out), out.size))
+        return out
+
+    def dequantize(self, mat: int = 0, row0: int = 0, rows: int | None = None) -> np.ndarray:
+        rows = self.n - row0 if rows is None else rows
+        out = np.zeros((rows, self.k), dtype=np.float32)
+        _check(load().fq_dequantize_rows(self.handle, mat, row0, rows, _vp(out)))
+        return out
+
+    def free(self) -> None:
+        if self.handle:
+            load().fq_weights_free(self.handle)
+            self.handle = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def quantize_rows_dev(fmt: int, dev_src, n: int, k: int, dev_blocks) -> None:
+    """Weight encoder on the device: f32 [n, k] in HBM -> raw GGUF blocks in HBM."""
+    _check(load().fq_quantize_rows_dev(fmt, _vp(dev_src), n, k, _vp(dev_blocks)))
+
+
+# --------------------------------------------------------------------------- dense, host buffers
+def gemm_quant_nt(fmt: int, rhs: np.ndarray, a: np.ndarray, n: int, cacheable: bool = False,
+                  nb01: int | None = None, out: np.ndarray | None = None) -> np.ndarray:
+    """`gemmQuantNt` (src/backend/cuda.zig:2398-2435): c[m,n] = a[m,k] . dequant(rhs)^T."""
+    assert rhs.dtype == np.uint8 and rhs.flags["C_CONTIGUOUS"]
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    m, k = a.shape
+    nb01 = formats.row_bytes(fmt, k) if nb01 is None else nb01
+    c = np.full((m, n), np.nan, dtype=np.float32) if out is None else out
+    _check(load().fq_gemm_quant_nt(fmt, _vp(rhs), rhs.size, int(cacheable), nb01, _vp(a), _vp(c), m, n, k))
+    return c
+
+
+def gemm_quant_nt_shared_a_batch(fmt: int, rhs: np.ndarray, a: np.ndarray, n: int, batch: int,
+                                 cacheable: bool = False) -> np.ndarray:
+    """`gemmQuantNtSharedABatch` (src/backend/cuda.zig:2441-2492): one input, `batch` stacked matrices."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    m, k = a.shape
+    nb01 = formats.row_bytes(fmt, k)
+    c = np.full((batch * m, n), np.nan, dtype=np.float32)
+    _check(load().fq_gemm_quant_nt_shared_a_batch(fmt, _vp(rhs), rhs.size, int(cacheable), nb01, nb01 * n, _vp(a),
+                                                  _vp(c), batch, m, n, k))
+    return c
+
+
+class Work:
+    """Completion token (`accelerator.Work`, src/accelerator.zig:22-133)."""
+
+    def __init__(self, handle: int, out: np.ndarray | None):
+        self.handle, self.out = handle, out
+
+    def finish(self, copy_to_host: bool = True) -> None:
+        _check(load().fq_work_finish(self.handle, int(copy_to_host)))
+
+    def device_ptr(self) -> int:
+        return int(load().fq_work_device_ptr(self.handle))
+
+    def destroy(self) -> None:
+        if self.handle:
+            load().fq_work_destroy(self.handle)
+            self.handle = 0
+
+
+def gemm_quant_nt_async(fmt: int, rhs: np.ndarray, a: np.ndarray | None, n: int, m: int, k: int, batch: int = 1,
+                        dep: Work | None = None, out: np.ndarray | None = None) -> Work:
+    """`gemmQuantNtAsync` (src/backend/cuda.zig:2001-2175); rhs must be process-stable bytes."""
+    nb01 = formats.row_bytes(fmt, k)
+    if a is not None:
+        a = np.ascontiguousarray(a, dtype=np.float32)
+    c = np.full((batch * m, n), np.nan, dtype=np.float32) if out is None else out
+    h = C.c_void_p()
+    _check(load().fq_gemm_quant_nt_async(fmt, _vp(rhs), rhs.size, 1, nb01, nb01 * n, _vp(a),
+                                         C.c_void_p(dep.handle if dep else 0), _vp(c), batch, m, n, k, C.byref(h)))
+    return Work(h.value, c)
+
+
+# --------------------------------------------------------------------------- dense, device buffers
+def gemm_quant_nt_dev(w: Weights, a_dev, c_dev, m: int, mat: int = 0, mode: int = MODE_AUTO, stream: int = 0) -> None:
+    _check(load().fq_gemm_quant_nt_dev(w.handle, mat, _vp(a_dev), _vp(c_dev), m, mode, C.c_void_p(stream)))
+
+
+def gemm_ptqtp_dev(planes: list[Weights], a_dev, c_dev, m: int, stream: int = 0) -> None:
+    """K ternary planes summed per element in plane order (src/weights.zig:204-300)."""
+    arr = (C.c_void_p * len(planes))(*[p.handle for p in planes])
+    _check(load().fq_gemm_ptqtp_dev(arr, len(planes), _vp(a_dev), _vp(c_dev), m, C.c_void_p(stream)))
+
+
+def quantize_acts_q8_k_dev(a_dev, m: int, k: int, dev_blocks) -> None:
+    _check(load().fq_quantize_acts_q8_k_dev(_vp(a_dev), m, k, _vp(dev_blocks)))
+
+
+def quantize_acts_q8_0_dev(a_dev, m: int, k: int, dev_blocks) -> None:
+    _check(load().fq_quantize_acts_q8_0_dev(_vp(a_dev), m, k, _vp(dev_blocks)))
+
+
+# --------------------------------------------------------------------------- MoE
+def qmoe_stage(in_floats: int, out_floats: int):
+    """`qmoeStage` (src/backend/cuda.zig:2221): the provider's pinned in/out panels as numpy views."""
+    pin, pout = C.c_void_p(), C.c_void_p()
+    _check(load().fq_qmoe_stage(in_floats * 4, out_floats * 4, C.byref(pin), C.byref(pout)))
+    a = np.ctypeslib.as_array(C.cast(pin, C.POINTER(C.c_float)), shape=(in_floats,))
+    b = np.ctypeslib.as_array(C.cast(pout, C.POINTER(C.c_float)), shape=(out_floats,))
+    return a, b
+
+
+def gemm_q_grouped_nt(fmt: int, rhs: np.ndarray, n_out: int, k: int, tiles: list[tuple[int, int, int, int]],
+                      cacheable: bool = False) -> None:
+    """`gemmQGroupedNt` (src/backend/cuda.zig:2244-2333) over the staged panels; caller holds the qmoe lock."""
+    nb01 = formats.row_bytes(fmt, k)
+    arr = (QmmTile * len(tiles))(*[QmmTile(*t) for t in tiles])
+    _check(load().fq_gemm_q_grouped_nt(fmt, _vp(rhs), rhs.size, int(cacheable), nb01, nb01 * n_out, n_out, k, arr,
+                                       len(tiles)))
+
+
+def moe_layer(gate: Weights, up: Weights, down: Weights, x: np.ndarray, selected: np.ndarray, weights: np.ndarray,
+              gated_op: int = 0) -> np.ndarray:
+    """Twin of `ExecContext.moeExpertFfn` / `moeExpertFfnBatch` (src/exec/moe.zig:1135-1298, :1865-2088)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    seq = x.shape[0]
+    selected = np.ascontiguousarray(selected, dtype=np.int64).reshape(seq, -1)
+    top_k = selected.shape[1]
+    weights = np.ascontiguousarray(weights, dtype=np.float32).reshape(seq, top_k)
+    out = np.full_like(x, np.nan)
+    _check(load().fq_moe_layer(gate.handle, up.handle, down.handle, _vp(x), seq, top_k, _vp(selected), _vp(weights),
+                               gated_op, _vp(out)))
+    return out
+
+
+def moe_layer_dev(gate: Weights, up: Weights, down: Weights, x_dev, seq: int, top_k: int, selected_dev, weights_dev,
+                  out_dev, gated_op: int = 0, stream: int = 0) -> None:
+    _check(load().fq_moe_layer_dev(gate.handle, up.handle, down.handle, _vp(x_dev), seq, top_k, _vp(selected_dev),
+                                   _vp(weights_dev), gated_op, _vp(out_dev), C.c_void_p(stream)))
+
+
+def router_topk_dev(logits_dev, seq: int, n_expert: int, top_k: int, normalize: bool, selected_dev, weights_dev,
+                    stream: int = 0) -> None:
+    """`routerTopK` (src/exec/topk.zig:21-86) on the device."""
+    _check(load().fq_router_topk_dev(_vp(logits_dev), seq, n_expert, top_k, int(normalize), _vp(selected_dev),
+                                     _vp(weights_dev), C.c_void_p(stream)))
+
+
+# --------------------------------------------------------------------------- gates
+def should_use_gpu_dense_quant(fmt: int, work: int) -> bool:
+    return bool(load().fq_should_use_gpu_dense_quant(fmt, work))
+
+
+def should_use_gpu_dense_quant_packed(fmt: int, work: int) -> bool:
+    return bool(load().fq_should_use_gpu_dense_quant_packed(fmt, work))
+
+
+def should_use_gpu_quant_decode(fmt: int, m: int, n: int, k: int) -> bool:
+    return bool(load().fq_should_use_gpu_quant_decode(fmt, m, n, k))
+
+
+def should_use_gpu_qmoe(work: int) -> bool:
+    return bool(load().fq_should_use_gpu_qmoe(work))
+
+
+def qmoe_fill_acceptable(rows: int, n_tiles: int) -> bool:
+    return bool(load().fq_qmoe_fill_acceptable(rows, n_tiles))

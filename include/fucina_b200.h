@@ -1,0 +1,212 @@
+/*
+ * fucina_b200 -- C ABI of the B200 (sm_100a) quantized-matmul provider.
+ *
+ * Drop-in for the GPU-offload seam of fucina's `src/backend/cuda.zig`
+ * (selected through `src/backend/gpu.zig:14-21`): the Zig host keeps calling
+ * the same provider functions, which forward to these entry points. Each
+ * declaration cites the reference interface it replaces (paths are relative
+ * to the reference project root).
+ *
+ * Conventions (same as the reference, backend/cuda.zig:2236-2243):
+ *   - RHS weights are row-major [n][k/B] raw GGUF blocks; `nb01` is the byte
+ *     stride between weight rows, `nb02` between stacked matrices (experts).
+ *   - c[m, n] = a[m, k] . dequant(W)^T, f32, "NT" product.
+ *   - return 0  : the GPU ran and the outputs are valid,
+ *     return >0 : declined before any side effect (the Zig `false`); nothing
+ *                 was written, see fq_last_error(),
+ *     return <0 : a CUDA error after submission (a failed accelerator.Work).
+ *   - There is no CPU fallback inside the library.
+ *   - Callable from any thread; entries serialise on one dispatch lock and
+ *     make the device current first (backend/cuda.zig:896, :1776-1779).
+ */
+#ifndef FUCINA_B200_H
+#define FUCINA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define FQ_API __attribute__((visibility("default")))
+#else
+#define FQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* backend/cuda.zig:1486-1499 `QFormat` (values 0..3 kept). The ternary
+ * formats have no CUDA counterpart in the reference (`has_tq2_0_quant =
+ * false`, backend/cuda.zig:69-71); their values stay clear of both
+ * providers' enums (backend/metal.zig:1275-1280 reuses 3 and 4). */
+typedef enum {
+    FQ_Q8_0 = 0,
+    FQ_Q6_K = 1, /* not implemented: every entry declines it */
+    FQ_Q4_K = 2,
+    FQ_Q5_K = 3,
+    FQ_TQ2_0 = 16,        /* dtype.zig:215-218, one PTQTP plane */
+    FQ_TQ2_0_FOLDED = 17, /* backend/quant/types.zig:177-180, tie-fitted K=2 fold */
+    FQ_Q2_0 = 18          /* dtype.zig:78-81, 128-element ternary groups */
+} fq_format;
+
+/* Status codes (>0 = declined, <0 = device failure). */
+enum {
+    FQ_OK = 0,
+    FQ_DECLINED_ARGS = 1,    /* shape / alignment / format rule violated */
+    FQ_DECLINED_NO_GPU = 2,  /* no device or initialisation failed */
+    FQ_DECLINED_BUDGET = 3,  /* resident budget or registry exhausted */
+    FQ_DECLINED_GATE = 4,    /* disabled by FUCINA_GPU=0 */
+    FQ_DECLINED_BUSY = 5,    /* all async slots in flight */
+    FQ_ERR_CUDA = -1,
+    FQ_ERR_TIMEOUT = -2      /* a bounded device-side wait gave up */
+};
+
+/* backend/cuda.zig:1503-1508 `QMMTile`: one output tile of one expert. */
+typedef struct {
+    int32_t expert;
+    int32_t base_row;
+    int32_t m;
+    int32_t tile_m;
+} fq_qmm_tile;
+
+/* ---- provider lifetime (backend/cuda.zig:412-508 `context`/`initOnce`,
+ *      :510 `deviceName`) ---- */
+FQ_API int fq_init(int device); /* idempotent; device <0 = current/0 */
+FQ_API int fq_device_count(void);
+FQ_API const char* fq_device_name(void);
+FQ_API int fq_sm_count(void);
+FQ_API int fq_last_error(char* buf, size_t len);
+/* The library's compute stream as a cudaStream_t, for callers that own
+ * device buffers and want to order their own work after ours. */
+FQ_API void* fq_stream(void);
+FQ_API int fq_synchronize(void);
+
+/* ---- block geometry (dtype.zig:230-239 size asserts) ---- */
+FQ_API size_t fq_block_elems(int fmt);
+FQ_API size_t fq_block_bytes(int fmt);
+FQ_API size_t fq_row_bytes(int fmt, size_t k); /* GGUF bytes of one weight row */
+
+/* ---- weight residency (backend/cuda.zig:1733 `allocResidentBytes`, :1780
+ *      `freeResidentBytes`, :1550-1611 `residentDevPtr`) ----
+ * fq_alloc_resident returns page-locked host bytes the loader fills; the
+ * device copy (in the gpu_formats layout) is made on first use.
+ * rhs pointers passed with cacheable=1 are adopted by source address: the
+ * caller promises they stay mapped and unchanged for the process lifetime
+ * (exec/quant_matmul.zig:22-36). fq_evict_resident drops one adopted range. */
+FQ_API void* fq_alloc_resident(size_t len);
+FQ_API void fq_free_resident(const void* p);
+FQ_API int fq_evict_resident(const void* host_ptr);
+FQ_API size_t fq_resident_bytes(void);
+FQ_API int fq_set_vram_budget(size_t bytes); /* FUCINA_GPU_VRAM_BUDGET twin; test seam of backend/cuda.zig:3639 */
+
+/* ---- gpu_formats: explicit device-resident weights ----
+ * Upload raw GGUF blocks once, repack to the device layout, and get a handle
+ * usable by the *_dev entries. `n_mats` stacked matrices (experts) of n rows.
+ * The reference reads raw blocks in place (backend/cuda.zig:2051); this is
+ * the new packing stage. */
+typedef struct fq_weights fq_weights;
+FQ_API int fq_weights_upload(int fmt, const void* host_blocks, size_t nb01, size_t nb02, size_t n, size_t k,
+                      size_t n_mats, fq_weights** out);
+FQ_API int fq_weights_from_device(int fmt, const void* dev_blocks, size_t nb01, size_t nb02, size_t n, size_t k,
+                           size_t n_mats, fq_weights** out); /* raw blocks already in HBM */
+FQ_API void fq_weights_free(fq_weights* w);
+FQ_API size_t fq_weights_device_bytes(const fq_weights* w);
+/* inverse of the repack, for round-trip checks: device layout -> GGUF bytes (host) */
+FQ_API int fq_weights_download_gguf(const fq_weights* w, void* host_blocks, size_t len);
+/* dequantise rows [row0, row0+rows) of matrix `mat` to f32 on the host or the
+ * device (kernels.cu:72-159 `dequant_*`; values are bit-identical to the CPU
+ * decoders q4_k.zig:1954-1972, q5_k.zig:1154-1167, q8k.zig:95-114,
+ * cold.zig:651-670, :289-301, ternary.zig:850-876). */
+FQ_API int fq_dequantize_rows(const fq_weights* w, size_t mat, size_t row0, size_t rows, float* host_out);
+FQ_API int fq_dequantize_rows_dev(const fq_weights* w, size_t mat, size_t row0, size_t rows, float* dev_out);
+/* Weight encoders on the device (q8k.zig:49-69, q4_k.zig:1977-2048,
+ * q5_k.zig:1172-1257, ternary.zig:79-144, cold.zig:309-332): f32 rows in HBM
+ * -> raw GGUF blocks in HBM, byte-identical to the CPU encoders. */
+FQ_API int fq_quantize_rows_dev(int fmt, const float* dev_src, size_t n, size_t k, void* dev_blocks);
+
+/* ---- dense quantized matmul, host buffers ----
+ * backend/cuda.zig:2398-2435 `gemmQuantNt` (blocking), :2441-2492
+ * `gemmQuantNtSharedABatch`. `rhs_len` is the byte length of the rhs range. */
+FQ_API int fq_gemm_quant_nt(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, const float* a,
+                     float* c, size_t m, size_t n, size_t k);
+FQ_API int fq_gemm_quant_nt_shared_a_batch(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01,
+                                    size_t nb02, const float* a, float* c, size_t batch, size_t m, size_t n,
+                                    size_t k);
+
+/* ---- eager async submit + completion token ----
+ * backend/cuda.zig:2001-2175 `gemmQuantNtAsync`; the token is the C twin of
+ * accelerator.Work's vtable {finish, device_ptr, destroy}
+ * (accelerator.zig:22-133, backend/cuda.zig:1145-1218). `a_dep` chains a
+ * pending producer's device output without a host round trip
+ * (backend/cuda.zig:1224-1230 `pendingDeviceInput`); pass NULL to read `a`. */
+typedef struct fq_work fq_work;
+FQ_API int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02,
+                           const float* a, fq_work* a_dep, float* c_host, size_t batch, size_t m, size_t n,
+                           size_t k, fq_work** out_work);
+FQ_API int fq_work_finish(fq_work* w, int copy_to_host); /* 0 ok; <0 failed */
+FQ_API uintptr_t fq_work_device_ptr(fq_work* w);
+FQ_API void fq_work_destroy(fq_work* w);
+
+/* ---- dense quantized matmul, device buffers (activation chaining and
+ *      kernel-only timing); a_dev/c_dev are f32 in HBM. Runs on `stream`
+ *      (NULL = the library stream). mode: see FQ_MODE_*. ---- */
+enum {
+    FQ_MODE_AUTO = 0,   /* m <= 16: integer decode kernel; larger: tensor cores */
+    FQ_MODE_INT8 = 1,   /* activations quantised like the CPU kernels (native.zig:427-490), dp4a dots */
+    FQ_MODE_TENSOR = 2  /* weights and activations rounded to bf16, tcgen05 MMA, f32 accumulate */
+};
+FQ_API int fq_gemm_quant_nt_dev(const fq_weights* w, size_t mat, const float* a_dev, float* c_dev, size_t m, int mode,
+                         void* stream);
+/* K planes of one PTQTP weight summed per element in plane order
+ * (weights.zig:204-300 `linearSeqPtqtpFused`). */
+FQ_API int fq_gemm_ptqtp_dev(const fq_weights* const* planes, int n_planes, const float* a_dev, float* c_dev, size_t m,
+                      void* stream);
+/* Activation quantisers on the device (q8k.zig:268-313 Q8_K, :49-69 Q8_0);
+ * outputs are the reference block structs (dtype.zig:148-152, :83-86). */
+FQ_API int fq_quantize_acts_q8_k_dev(const float* a_dev, size_t m, size_t k, void* dev_blocks);
+FQ_API int fq_quantize_acts_q8_0_dev(const float* a_dev, size_t m, size_t k, void* dev_blocks);
+
+/* ---- grouped MoE GEMM over a CPU-built tile table ----
+ * backend/cuda.zig:2181 `qmoe_lock`, :2221 `qmoeStage`, :2244-2333
+ * `gemmQGroupedNt`. The stage's host panels are owned by the library. */
+FQ_API void fq_qmoe_lock(void);
+FQ_API void fq_qmoe_unlock(void);
+FQ_API int fq_qmoe_stage(size_t in_bytes, size_t out_bytes, float** in, float** out);
+FQ_API int fq_gemm_q_grouped_nt(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02,
+                         size_t n_out, size_t k, const fq_qmm_tile* tiles, size_t n_tiles);
+
+/* ---- fused, device-resident MoE expert layer (new) ----
+ * Argument-for-argument twin of ExecContext.moeExpertFfn / moeExpertFfnBatch
+ * (exec/moe.zig:1135-1298, :1865-2088): x [seq, hidden], selected/weights
+ * [seq*top_k] row-major per token, out [seq, hidden]; gate/up are
+ * [E][out_pe][hidden], down is [E][hidden][out_pe]. gated_op 0 = swiglu
+ * (backend/ops.zig:150-190). Host-buffer and device-buffer forms. */
+FQ_API int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x, size_t seq,
+                 size_t top_k, const int64_t* selected, const float* weights, int gated_op, float* out);
+FQ_API int fq_moe_layer_dev(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev,
+                     size_t seq, size_t top_k, const int32_t* selected_dev, const float* weights_dev,
+                     int gated_op, float* out_dev, void* stream);
+/* exec/topk.zig:21-86 `routerTopK` on the device: logits [seq, E] -> selected/weights [seq, top_k]. */
+FQ_API int fq_router_topk_dev(const float* logits_dev, size_t seq, size_t n_expert, size_t top_k, int normalize,
+                       int32_t* selected_dev, float* weights_dev, void* stream);
+
+/* ---- gates (backend/cuda.zig:2494-2554) and test seams (:2537-2571) ---- */
+FQ_API int fq_should_use_gpu_dense_quant(int fmt, uint64_t total_work);
+FQ_API int fq_should_use_gpu_dense_quant_packed(int fmt, uint64_t total_work);
+FQ_API int fq_should_use_gpu_quant_decode(int fmt, size_t m, size_t n, size_t k);
+FQ_API int fq_should_use_gpu_qmoe(uint64_t total_work);
+FQ_API int fq_qmoe_fill_acceptable(size_t rows, size_t n_tiles);
+FQ_API void fq_set_min_work_qmoe_for_test(uint64_t v);
+FQ_API void fq_set_decode_for_test(int enabled);
+
+/* ---- trace counters (backend/cuda.zig:191-317) ---- */
+FQ_API int fq_trace_enabled(void);
+FQ_API void fq_trace_reset(void);
+FQ_API void fq_trace_dump(void);
+/* counter snapshot: calls, kernel launches, h2d bytes, d2h bytes, resident hits, resident adopts, gate pass, gate fail */
+FQ_API void fq_trace_counters(uint64_t out[8]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUCINA_B200_H */

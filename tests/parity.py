@@ -1,0 +1,60 @@
+"""Shared helpers for the parity tests."""
+from __future__ import annotations
+
+import numpy as np
+
+# north_star tolerances: max relative error 1e-3 for the f32-accumulate integer
+# path against the CPU-kernel oracle, 1e-2 for the bf16 tensor-core path
+# against the dequantised f64 oracle.
+TOL_INT8 = 1e-3
+TOL_TENSOR = 1e-2
+
+
+def rel_err(got: np.ndarray, want: np.ndarray) -> float:
+    """max over elements of |got-want| / max(|want|, |got|, floor).
+
+    The floor (1% of the RMS of `want`) keeps elements that cancel to ~0 from
+    turning f32 summation-order noise into a meaningless ratio; the reference's
+    own GPU tests use the same shape of bound with an absolute floor
+    (src/backend/cuda.zig:3034).
+    """
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert np.isfinite(got).all(), "non-finite output"
+    floor = 1e-2 * float(np.sqrt(np.mean(want**2))) + 1e-30
+    den = np.maximum(np.maximum(np.abs(want), np.abs(got)), floor)
+    return float(np.max(np.abs(got - want) / den))
+
+
+def assert_close(got, want, tol, what=""):
+    e = rel_err(got, want)
+    assert e <= tol, f"{what}: max relative error {e:.3e} > {tol:g}"
+    return e
+
+
+def bits_equal(a: np.ndarray, b: np.ndarray) -> bool:
+    return a.shape == b.shape and np.array_equal(np.ascontiguousarray(a).view(np.uint32), np.ascontiguousarray(b).view(np.uint32))
+
+
+def make_weights(fmt_name: str, n: int, k: int, seed: int):
+    """Seeded N(0, 0.02) weights through the oracle quantiser (or seeded trits for the ternary formats)."""
+    import oracle
+
+    rng = np.random.default_rng(seed)
+    fmt = oracle.FORMATS[fmt_name]
+    if fmt_name in ("q8_0", "q4_k", "q5_k"):
+        w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+        return oracle.quantize_rows(fmt, w)
+    trits = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+    if fmt_name == "tq2_0":
+        scales = np.abs(rng.standard_normal((n, k // 256)) * 0.02).astype(np.float32)
+        return oracle.pack_ptqtp_plane(trits, scales)
+    if fmt_name == "q2_0":
+        scales = np.abs(rng.standard_normal((n, k // 128)) * 0.02).astype(np.float32)
+        return oracle.pack_q2_0(trits, scales)
+    if fmt_name == "tq2_0_folded":
+        fine = np.abs(rng.standard_normal((n, k // 256)) * 0.02).astype(np.float32)
+        t2 = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+        return oracle.fold_planes(oracle.pack_ptqtp_plane(trits, fine * 3), oracle.pack_ptqtp_plane(t2, fine), k)
+    raise ValueError(fmt_name)
