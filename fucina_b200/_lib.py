@@ -76,6 +76,8 @@ SIGNATURES = {
     "fq_trace_reset": (None, []),
     "fq_trace_dump": (None, []),
     "fq_trace_counters": (None, [P(c_u64)]),
+    "fq_trace_kernel_timing": (None, [c_int]),
+    "fq_trace_kernel_times": (c_int, [P(C.c_double), P(c_u64)]),
 }
 
 _lib = None

@@ -46,6 +46,24 @@ int cuda_fail(cudaError_t e, const char* what) {
 Trace g_trace;
 static bool g_trace_on = false;
 
+// Device-side duration of the decode kernel, the CUDA-event twin of the
+// reference's per-kind nanosecond counters (backend/cuda.zig:231-257). While
+// enabled, every decode-kernel launch is bracketed by an event pair on its
+// stream; the pairs are read back when the totals are queried.
+static bool g_ktime_on = false;
+static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_ktime_events;
+static std::vector<cudaEvent_t> g_ktime_pool;
+static cudaEvent_t ktime_event() {
+    if (!g_ktime_pool.empty()) {
+        cudaEvent_t e = g_ktime_pool.back();
+        g_ktime_pool.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+
 // ---------------------------------------------------------------------------
 // configuration read once from the environment (backend/cuda.zig:321-408)
 // ---------------------------------------------------------------------------
@@ -426,7 +444,17 @@ int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* 
         g_trace.launches++;
         if (e != cudaSuccess) { rc = cuda_fail(e, "activation quantise launch"); break; }
         GemvArgs ga{w, DevWeights{}, mat, scratch, c_dev + r0 * ldc, rows, (int)ldc, accumulate, nullptr, nullptr, 0};
+        cudaEvent_t t0 = nullptr, t1 = nullptr;
+        if (g_ktime_on) {
+            t0 = ktime_event();
+            t1 = ktime_event();
+            cudaEventRecord(t0, st);
+        }
         e = launch_gemv(ga, ctx->sm_count, st);
+        if (g_ktime_on) {
+            cudaEventRecord(t1, st);
+            g_ktime_events.emplace_back(t0, t1);
+        }
         g_trace.launches++;
         if (e != cudaSuccess) rc = cuda_fail(e, "gemv launch");
     }
@@ -961,6 +989,31 @@ void fq_trace_reset(void) {
 void fq_trace_counters(uint64_t out[8]) {
     out[0] = g_trace.calls, out[1] = g_trace.launches, out[2] = g_trace.h2d_bytes, out[3] = g_trace.d2h_bytes;
     out[4] = g_trace.resident_hits, out[5] = g_trace.resident_adopts, out[6] = g_trace.gate_pass, out[7] = g_trace.gate_fail;
+}
+void fq_trace_kernel_timing(int enable) {
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    g_ktime_on = enable != 0;
+}
+int fq_trace_kernel_times(double* total_ms, uint64_t* launches) {
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    double sum = 0.0;
+    uint64_t n = 0;
+    for (auto& pr : g_ktime_events) {
+        float ms = 0.0f;
+        if (cudaEventSynchronize(pr.second) == cudaSuccess && cudaEventElapsedTime(&ms, pr.first, pr.second) == cudaSuccess) {
+            sum += ms;
+            ++n;
+        }
+        g_ktime_pool.push_back(pr.first);
+        g_ktime_pool.push_back(pr.second);
+    }
+    g_ktime_events.clear();
+    cudaGetLastError();
+    if (total_ms) *total_ms = sum;
+    if (launches) *launches = n;
+    return FQ_OK;
 }
 void fq_trace_dump(void) {
     uint64_t c[8];

@@ -89,6 +89,18 @@ def trace_counters() -> dict:
     return dict(zip(keys, [int(v) for v in arr]))
 
 
+def kernel_timing(enable: bool) -> None:
+    """Bracket every decode-kernel launch with CUDA events (off by default)."""
+    load().fq_trace_kernel_timing(int(enable))
+
+
+def kernel_times() -> tuple[float, int]:
+    """(summed device milliseconds, launches) of the decode kernel since the last query."""
+    ms, n = C.c_double(), C.c_uint64()
+    _check(load().fq_trace_kernel_times(C.byref(ms), C.byref(n)))
+    return ms.value, int(n.value)
+
+
 # --------------------------------------------------------------------------- weights
 class Weights:
     """Device-resident weights in the gpu_formats layout (`fq_weights`)."""

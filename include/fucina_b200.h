@@ -205,6 +205,12 @@ FQ_API void fq_trace_reset(void);
 FQ_API void fq_trace_dump(void);
 /* counter snapshot: calls, kernel launches, h2d bytes, d2h bytes, resident hits, resident adopts, gate pass, gate fail */
 FQ_API void fq_trace_counters(uint64_t out[8]);
+/* Device time of the decode kernel (CUDA events around each launch while
+ * enabled), the per-kind timing of backend/cuda.zig:231-257 taken on the
+ * device instead of the host clock. fq_trace_kernel_times waits for the
+ * recorded launches, returns their summed duration and count, and clears. */
+FQ_API void fq_trace_kernel_timing(int enable);
+FQ_API int fq_trace_kernel_times(double* total_ms, uint64_t* launches);
 
 #ifdef __cplusplus
 }
