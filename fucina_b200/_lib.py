@@ -58,6 +58,10 @@ SIGNATURES = {
     "fq_gemm_ptqtp_dev": (c_int, [P(c_void), c_int, c_void, c_void, c_size, c_void]),
     "fq_quantize_acts_q8_k_dev": (c_int, [c_void, c_size, c_size, c_void]),
     "fq_quantize_acts_q8_0_dev": (c_int, [c_void, c_size, c_size, c_void]),
+    "fq_capture_begin": (c_int, []),
+    "fq_capture_end": (c_int, [P(c_void)]),
+    "fq_graph_launch": (c_int, [c_void]),
+    "fq_graph_destroy": (None, [c_void]),
     "fq_qmoe_lock": (None, []),
     "fq_qmoe_unlock": (None, []),
     "fq_qmoe_stage": (c_int, [c_size, c_size, P(c_void), P(c_void)]),

@@ -1,0 +1,544 @@
+// Row-per-lane decode GEMV for sm_100a with TMA-staged weight streaming.
+//
+// c[b, j] = sum_e a[b, e] * dequant(W)[j, e], b < m <= 8, for the dense decode
+// shapes (K >= 2048, Q4_K / Q5_K / Q8_0). Same arithmetic as the reference's
+// CPU kernels: int8 activations, exact integer block dots, and per block the
+// f32 epilogue of q4_k.zig:895-913 / q5_k.zig:1093-1111 / q8_0.zig:1074-1089,
+// evaluated without fusing; only the order in which block terms are added
+// differs.
+//
+// Data movement. One persistent CTA per SM owns a contiguous range of weight
+// rows and walks it in tiles of 32 rows; lane l of every warp owns row l of
+// the tile, so no cross-lane reduction is needed and the block header is
+// decoded once per 256 weights. The eight warps split K: warp w takes the
+// slabs (groups of 1-2 blocks per row) w, w+8, ... . Every lane fetches its
+// own row's slab with one bulk async copy (cp.async.bulk, the non-tensor TMA
+// path) into a private shared-memory slot; the 32 copies of a warp complete on
+// one mbarrier. Slots are padded to an odd number of 16-byte units so the
+// 128-bit shared loads of a quarter warp hit 32 distinct banks. Copies for
+// the next slabs (also of the next tile) are in flight while a slab is
+// consumed, which keeps tens of KB per SM outstanding independent of register
+// count -- the thing an HBM-bound kernel needs. Activations are quantised once
+// per CTA in the prologue, while the first weight slabs are already in
+// flight, and are read as warp-wide broadcasts.
+//
+// Every wait on an mbarrier is bounded; a wait that gives up records
+// FQ_ERR_TIMEOUT in the status word and the CTA returns.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <cstring>
+
+#include "actquant.cuh"
+#include "internal.h"
+
+namespace fq {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = 8;
+constexpr int kMaxStages = 4;
+constexpr unsigned kWaitLimit = 1u << 20;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the barrier did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (unsigned i = 0; i < kWaitLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// Bulk async copy global -> this CTA's shared memory; bytes and both
+// addresses are multiples of 16.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dot16_ss(const uint32_t* w, const uint4& a, int acc) {
+    acc = dp4a_ss(w[0], a.x, acc);
+    acc = dp4a_ss(w[1], a.y, acc);
+    acc = dp4a_ss(w[2], a.z, acc);
+    return dp4a_ss(w[3], a.w, acc);
+}
+__device__ __forceinline__ int dot16_us(const uint32_t* w, const uint4& a, int acc) {
+    acc = dp4a_us(w[0], a.x, acc);
+    acc = dp4a_us(w[1], a.y, acc);
+    acc = dp4a_us(w[2], a.z, acc);
+    return dp4a_us(w[3], a.w, acc);
+}
+__device__ __forceinline__ int byte_of(uint32_t w, int i) { return (int)((w >> (8 * i)) & 0xffu); }
+
+// K-quant header: d, dmin and the eight 6-bit (scale, min) pairs as bytes
+// (reference backend/quant/q8k.zig:637-648, four pairs per word at a time).
+struct KHeader {
+    float d, dmin;
+    uint32_t sc[2], mn[2];
+    __device__ __forceinline__ void decode(const uint4& h) {
+        const __half2 dm = *reinterpret_cast<const __half2*>(&h.x);
+        d = __low2float(dm);
+        dmin = __high2float(dm);
+        sc[0] = h.y & 0x3f3f3f3fu;
+        mn[0] = h.z & 0x3f3f3f3fu;
+        sc[1] = (h.w & 0x0f0f0f0fu) | (((h.y >> 6) & 0x03030303u) << 4);
+        mn[1] = ((h.w >> 4) & 0x0f0f0f0fu) | (((h.z >> 6) & 0x03030303u) << 4);
+    }
+};
+
+// Per block epilogue shared by Q4_K and Q5_K, kept unfused like the CPU code.
+__device__ __forceinline__ float kquant_term(const KHeader& H, float da, int isc, int imn) {
+    return __fsub_rn(__fmul_rn(__fmul_rn(H.d, da), (float)isc), __fmul_rn(__fmul_rn(H.dmin, da), (float)imn));
+}
+
+__device__ __forceinline__ int min_term(const KHeader& H, uint32_t sums_addr) {
+    const uint4 s0 = lds128(sums_addr), s1 = lds128(sums_addr + 16);
+    int imn = byte_of(H.mn[0], 0) * (int)s0.x;
+    imn += byte_of(H.mn[0], 1) * (int)s0.y;
+    imn += byte_of(H.mn[0], 2) * (int)s0.z;
+    imn += byte_of(H.mn[0], 3) * (int)s0.w;
+    imn += byte_of(H.mn[1], 0) * (int)s1.x;
+    imn += byte_of(H.mn[1], 1) * (int)s1.y;
+    imn += byte_of(H.mn[1], 2) * (int)s1.z;
+    imn += byte_of(H.mn[1], 3) * (int)s1.w;
+    return imn;
+}
+
+// Shared-memory view of the MB activation records of this CTA.
+struct ActView {
+    uint32_t base;      // shared address of record 0
+    uint32_t row;       // bytes per record
+    uint32_t off_sums;  // Q8_K: int32 sub-block sums
+    uint32_t off_ad;    // f32 scales
+};
+
+// ---- one 256-weight Q4_K block of this lane's row against MB activation rows
+template <int MB>
+__device__ __forceinline__ void block_q4_k(uint32_t p, const ActView& V, int kb, float (&acc)[MB]) {
+    KHeader H;
+    H.decode(lds128(p));
+    int isc_lo[MB], isc_hi[MB];
+#pragma unroll
+    for (int b = 0; b < MB; ++b) isc_lo[b] = isc_hi[b] = 0;
+#pragma unroll
+    for (int pp = 0; pp < 4; ++pp) {
+        const uint4 q0 = lds128(p + 16 + pp * 32), q1 = lds128(p + 32 + pp * 32);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        uint32_t lo[8], hi[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            lo[j] = w[j] & 0x0f0f0f0fu;
+            hi[j] = w[j] & 0xf0f0f0f0u;  // 16 * nibble as an unsigned byte; the factor is shifted out below
+        }
+        const int sa = byte_of(H.sc[pp >> 1], (pp & 1) * 2), sb = byte_of(H.sc[pp >> 1], (pp & 1) * 2 + 1);
+#pragma unroll
+        for (int b = 0; b < MB; ++b) {
+            const uint32_t a = V.base + b * V.row + kb * 256 + pp * 64;
+            const uint4 a0 = lds128(a), a1 = lds128(a + 16), a2 = lds128(a + 32), a3 = lds128(a + 48);
+            int dlo = dot16_ss(lo, a0, 0);
+            dlo = dot16_ss(lo + 4, a1, dlo);
+            int dhi = dot16_us(hi, a2, 0);
+            dhi = dot16_us(hi + 4, a3, dhi);
+            isc_lo[b] += sa * dlo;
+            isc_hi[b] += sb * dhi;
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < MB; ++b) {
+        const uint32_t rec = V.base + b * V.row;
+        const int imn = min_term(H, rec + V.off_sums + kb * 32);
+        float da;
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(da) : "r"(rec + V.off_ad + kb * 4));
+        acc[b] = __fadd_rn(acc[b], kquant_term(H, da, isc_lo[b] + (isc_hi[b] >> 4), imn));
+    }
+}
+
+// ---- Q5_K: as Q4_K plus the fifth bits (bit s of qh[i] belongs to sub-block s)
+template <int MB>
+__device__ __forceinline__ void block_q5_k(uint32_t p, const ActView& V, int kb, float (&acc)[MB]) {
+    KHeader H;
+    H.decode(lds128(p));
+    const uint4 h0 = lds128(p + 16), h1 = lds128(p + 32);
+    const uint32_t hb[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+    int isc[MB];
+#pragma unroll
+    for (int b = 0; b < MB; ++b) isc[b] = 0;
+#pragma unroll
+    for (int pp = 0; pp < 4; ++pp) {
+        const uint4 q0 = lds128(p + 48 + pp * 32), q1 = lds128(p + 64 + pp * 32);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        uint32_t lo[8], hi[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            lo[j] = (w[j] & 0x0f0f0f0fu) | (((hb[j] >> (2 * pp)) & 0x01010101u) << 4);
+            hi[j] = ((w[j] >> 4) & 0x0f0f0f0fu) | (((hb[j] >> (2 * pp + 1)) & 0x01010101u) << 4);
+        }
+        const int sa = byte_of(H.sc[pp >> 1], (pp & 1) * 2), sb = byte_of(H.sc[pp >> 1], (pp & 1) * 2 + 1);
+#pragma unroll
+        for (int b = 0; b < MB; ++b) {
+            const uint32_t a = V.base + b * V.row + kb * 256 + pp * 64;
+            const uint4 a0 = lds128(a), a1 = lds128(a + 16), a2 = lds128(a + 32), a3 = lds128(a + 48);
+            int dlo = dot16_ss(lo, a0, 0);
+            dlo = dot16_ss(lo + 4, a1, dlo);
+            int dhi = dot16_ss(hi, a2, 0);
+            dhi = dot16_ss(hi + 4, a3, dhi);
+            isc[b] += sa * dlo + sb * dhi;
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < MB; ++b) {
+        const uint32_t rec = V.base + b * V.row;
+        const int imn = min_term(H, rec + V.off_sums + kb * 32);
+        float da;
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(da) : "r"(rec + V.off_ad + kb * 4));
+        acc[b] = __fadd_rn(acc[b], kquant_term(H, da, isc[b], imn));
+    }
+}
+
+// ---- Q8_0: one unit = 8 blocks of 32 weights; payload at p, the unit's eight
+// f16 scales at ps. Per block f32(idot) * (d_a * d_w)  (q8_0.zig:1074-1089).
+template <int MB>
+__device__ __forceinline__ void unit_q8_0(uint32_t p, uint32_t ps, const ActView& V, int kb, float (&acc)[MB]) {
+    const uint4 su = lds128(ps);
+    const uint32_t sw[4] = {su.x, su.y, su.z, su.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint4 w0 = lds128(p + j * 32), w1 = lds128(p + j * 32 + 16);
+        const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const float dw = __half2float(__ushort_as_half((unsigned short)((sw[j >> 1] >> ((j & 1) * 16)) & 0xffffu)));
+#pragma unroll
+        for (int b = 0; b < MB; ++b) {
+            const uint32_t rec = V.base + b * V.row;
+            const uint32_t a = rec + kb * 256 + j * 32;
+            const uint4 a0 = lds128(a), a1 = lds128(a + 16);
+            int dot = dot16_ss(w, a0, 0);
+            dot = dot16_ss(w + 4, a1, dot);
+            float da;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(da) : "r"(rec + V.off_ad + (kb * 8 + j) * 4));
+            acc[b] = __fadd_rn(acc[b], __fmul_rn((float)dot, __fmul_rn(da, dw)));
+        }
+    }
+}
+
+// Geometry of one slab (what a lane fetches per pipeline step).
+struct SlabGeom {
+    int unit_bytes;    // payload bytes per 256 weights
+    int scale_bytes;   // separate scale-plane bytes per 256 weights (0: scales travel inside the payload)
+    int slot_bytes;    // shared-memory slot per lane, an odd number of 16-byte units
+    int scale_off;     // offset of the scale bytes inside the slot
+};
+__host__ __device__ inline SlabGeom slab_geom(int fmt, int slab) {
+    SlabGeom g;
+    g.unit_bytes = fmt == FQ_Q4_K ? 144 : fmt == FQ_Q5_K ? 176 : 256;
+    g.scale_bytes = fmt == FQ_Q8_0 ? 16 : 0;
+    g.scale_off = slab * g.unit_bytes;
+    int bytes = slab * (g.unit_bytes + g.scale_bytes);
+    if (((bytes / 16) & 1) == 0) bytes += 16;
+    g.slot_bytes = bytes;
+    return g;
+}
+
+template <int FMT, int MB, bool FUSED>
+__global__ void __launch_bounds__(kThreads, 1) decode_rows_kernel(const RowsArgs A, const __grid_constant__ CUtensorMap tmap) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int k = A.w.k, n = A.w.n;
+    constexpr bool Q8K = FMT != FQ_Q8_0;
+    const NatSizes NS = nat_sizes(Q8K, k);
+    const SlabGeom G = slab_geom(FMT, A.slab);
+    const int units = k >> 8;                                // 256-weight units per row
+    const int nslabs = (units + A.slab - 1) / A.slab;        // slabs per row
+    const int my_slabs = warp < nslabs ? (nslabs - warp + kWarps - 1) / kWarps : 0;
+
+    // shared memory: barriers | activation records | reduction buffers | stage slots
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+    uint8_t* acts = smem + 256;
+    float* red = reinterpret_cast<float*>(acts + ((MB * NS.row + 127) & ~(size_t)127));
+    uint8_t* slots = reinterpret_cast<uint8_t*>(red) + 2 * kWarps * MB * 32 * sizeof(float);
+    const uint32_t slot0 = smem_u32(slots) + (uint32_t)((warp * A.stages) * 32 + lane) * G.slot_bytes;
+    const uint32_t bar0 = smem_u32(bars) + warp * kMaxStages * 8;
+
+    if (lane == 0)
+        for (int s = 0; s < A.stages; ++s) mbar_init(bar0 + s * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+
+    // this CTA's contiguous row range, balanced over the grid
+    const int r_begin = (int)((long long)n * blockIdx.x / gridDim.x);
+    const int r_end = (int)((long long)n * (blockIdx.x + 1) / gridDim.x);
+    const int ntiles = (r_end - r_begin + 31) / 32;
+    const int total = ntiles * my_slabs;  // pipeline steps of this warp
+    const uint8_t* wbase = A.w.base + (size_t)A.mat * A.w.mat_stride;
+
+    auto issue = [&](int it) {
+        const int tile = it / my_slabs, sl = warp + kWarps * (it % my_slabs);
+        const int stage = it % A.stages;
+        const int row0 = r_begin + tile * 32;
+        const int nvalid = min(32, r_end - row0);
+        const int nu = min(A.slab, units - sl * A.slab);  // units in this (possibly ragged) slab
+        const uint32_t bar = bar0 + stage * 8;
+        if (A.use_tmap) {
+            // one 2-D tensor copy per warp step: 32 rows x one unit, landing densely (the unit size is an
+            // odd number of 16-byte chunks, so the rows need no padding to stay bank-conflict free);
+            // rows past the end of the matrix arrive as zeros
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar, (uint32_t)(32 * G.unit_bytes));
+                const uint32_t dst = slot0 + (uint32_t)stage * 32 * G.slot_bytes;  // lane 0's slot = the stage base
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                    "l"(&tmap), "r"(sl * G.unit_bytes), "r"(row0), "r"(bar)
+                    : "memory");
+            }
+            return;
+        }
+        if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)(nvalid * nu * (G.unit_bytes + G.scale_bytes)));
+        __syncwarp();
+        if (lane < nvalid) {
+            const uint8_t* row = wbase + (size_t)(row0 + lane) * A.w.row_stride;
+            const uint32_t dst = slot0 + (uint32_t)stage * 32 * G.slot_bytes;
+            bulk_load(dst, row + (size_t)sl * A.slab * G.unit_bytes, (uint32_t)(nu * G.unit_bytes), bar);
+            if (G.scale_bytes)
+                bulk_load(dst + G.scale_off, row + (size_t)units * G.unit_bytes + (size_t)sl * A.slab * G.scale_bytes,
+                          (uint32_t)(nu * G.scale_bytes), bar);
+        }
+    };
+
+    // start streaming weights before touching the activations
+    const int prefetch = min(A.stages, total);
+    for (int it = 0; it < prefetch; ++it) issue(it);
+
+    // activation records: quantise here (FUSED) or copy the pre-quantised records
+    if (FUSED) {
+        const int nblk = k >> 8;
+        for (int i = warp; i < MB * nblk; i += kWarps) {
+            const int b = i / nblk, blk = i % nblk;
+            uint8_t* rec = acts + (size_t)b * NS.row;
+            if (b < A.m) {
+                quantize_block_natural(A.a_f32 + (size_t)b * k, blk, Q8K, k, rec, lane);
+            } else {  // padded batch slots contribute zeros
+                *reinterpret_cast<uint2*>(rec + (size_t)blk * 256 + lane * 8) = make_uint2(0, 0);
+                if (Q8K) {
+                    if (lane < 8) reinterpret_cast<int32_t*>(rec + NS.aq)[blk * 8 + lane] = 0;
+                    if (lane == 0) reinterpret_cast<float*>(rec + NS.aq + NS.sums)[blk] = 0.0f;
+                } else if (lane < 8) {
+                    reinterpret_cast<float*>(rec + NS.aq)[blk * 8 + lane] = 0.0f;
+                }
+            }
+        }
+    } else {
+        const int units_per_rec = (int)(NS.row / 16);
+        const uint4* src = reinterpret_cast<const uint4*>(A.acts_nat);
+        uint4* dst = reinterpret_cast<uint4*>(acts);
+        for (int i = threadIdx.x; i < MB * units_per_rec; i += kThreads)
+            dst[i] = (i / units_per_rec < A.m) ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+
+    const ActView V = {smem_u32(acts), (uint32_t)NS.row, (uint32_t)NS.aq, (uint32_t)(NS.aq + NS.sums)};
+    bool ok = true;
+    int it = 0;
+    for (int tile = 0; tile < ntiles; ++tile) {
+        float acc[MB];
+#pragma unroll
+        for (int b = 0; b < MB; ++b) acc[b] = 0.0f;
+        for (int j = 0; j < my_slabs && ok; ++j, ++it) {
+            const int sl = warp + kWarps * j;
+            const int stage = it % A.stages;
+            const uint32_t parity = (uint32_t)(it / A.stages) & 1u;
+            if (!mbar_wait(bar0 + stage * 8, parity)) {
+                ok = false;
+                break;
+            }
+            const int nu = min(A.slab, units - sl * A.slab);
+            const uint32_t p = slot0 + (uint32_t)stage * 32 * G.slot_bytes;
+            for (int u = 0; u < nu; ++u) {
+                const int kb = sl * A.slab + u;
+                if (FMT == FQ_Q4_K) block_q4_k<MB>(p + u * 144, V, kb, acc);
+                if (FMT == FQ_Q5_K) block_q5_k<MB>(p + u * 176, V, kb, acc);
+                if (FMT == FQ_Q8_0) unit_q8_0<MB>(p + u * 256, p + G.scale_off + u * 16, V, kb, acc);
+            }
+            __syncwarp();  // every lane is done with this stage before it is refilled
+            if (it + A.stages < total) issue(it + A.stages);
+        }
+        // cross-warp sum of the K slices; two reduction buffers alternate so one CTA barrier per tile is enough
+        float* rbuf = red + (size_t)(tile & 1) * kWarps * MB * 32;
+#pragma unroll
+        for (int b = 0; b < MB; ++b) rbuf[(warp * MB + b) * 32 + lane] = acc[b];
+        __syncthreads();
+        if (threadIdx.x < 32 * MB) {
+            const int b = threadIdx.x >> 5;
+            float s = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) s += rbuf[(w * MB + b) * 32 + lane];
+            const int row = r_begin + tile * 32 + lane;
+            if (row < r_end && b < A.m) A.c[(size_t)b * A.ldc + row] = s;
+        }
+    }
+    if (!ok) {
+        if (lane == 0) atomicExch(A.status, FQ_ERR_TIMEOUT);
+        // give copies still in flight a bounded chance to land before the CTA's shared memory is released
+        for (int s = 0; s < A.stages; ++s) mbar_wait(bar0 + s * 8, 0);
+    }
+}
+
+constexpr size_t kSmemLimit = 227 * 1024;
+constexpr int kFusedMaxRows = 4;  // up to here each CTA quantises the activations itself
+
+size_t smem_bytes(int fmt, int k, int mb, int slab, int stages) {
+    const NatSizes NS = nat_sizes(fmt != FQ_Q8_0, (size_t)k);
+    const SlabGeom G = slab_geom(fmt, slab);
+    return 256 + ((mb * NS.row + 127) & ~(size_t)127) + (size_t)2 * kWarps * mb * 32 * sizeof(float) +
+           (size_t)kWarps * stages * 32 * G.slot_bytes;
+}
+
+int pad_rows(size_t m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
+
+// deepest pipeline that fits: more bytes in flight per SM first, then fewer barriers per byte
+bool pick_config(int fmt, int k, int mb, int* slab, int* stages) {
+    static const int cand[][2] = {{1, 4}, {2, 2}, {1, 3}, {1, 2}};
+    static int force_slab = -1, force_stages = -1;
+    if (force_slab < 0) {
+        const char* a = getenv("FUCINA_B200_DECODE_SLAB");
+        const char* b = getenv("FUCINA_B200_DECODE_STAGES");
+        force_slab = a ? atoi(a) : 0;
+        force_stages = b ? atoi(b) : 0;
+    }
+    if (force_slab > 0 && force_stages > 0 && force_stages <= kMaxStages && smem_bytes(fmt, k, mb, force_slab, force_stages) <= kSmemLimit) {
+        *slab = force_slab, *stages = force_stages;
+        return true;
+    }
+    for (auto& c : cand)
+        if (smem_bytes(fmt, k, mb, c[0], c[1]) <= kSmemLimit) {
+            *slab = c[0], *stages = c[1];
+            return true;
+        }
+    return false;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link dependency).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+        cudaGetLastError();
+    }
+    return fn;
+}
+
+// 2-D byte view of one weight matrix: inner dimension = the used bytes of a row, outer = rows;
+// one box = one 256-weight unit of 32 consecutive rows.
+bool make_weight_tmap(const DevWeights& w, int mat, int unit_bytes, CUtensorMap* out) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)(w.k / 256) * unit_bytes, (cuuint64_t)w.n};
+    const cuuint64_t strides[1] = {(cuuint64_t)w.row_stride};
+    const cuuint32_t box[2] = {(cuuint32_t)unit_bytes, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    void* base = const_cast<uint8_t*>(w.base) + (size_t)mat * w.mat_stride;
+    return fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int FMT, int MB>
+cudaError_t launch_fmt_mb(const RowsArgs& a, const CUtensorMap& tmap, bool fused, int grid, size_t smem, cudaStream_t st) {
+    auto kern = fused ? decode_rows_kernel<FMT, MB, true> : decode_rows_kernel<FMT, MB, false>;
+    // opt in to the large dynamic shared memory once per instantiation, not per launch
+    static size_t granted[2] = {0, 0};
+    if (granted[fused] < smem) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
+        if (e != cudaSuccess) return e;
+        granted[fused] = kSmemLimit;
+    }
+    kern<<<grid, kThreads, smem, st>>>(a, tmap);
+    return cudaGetLastError();
+}
+
+template <int FMT>
+cudaError_t launch_fmt(const RowsArgs& a, const CUtensorMap& tmap, int mb, bool fused, int grid, size_t smem, cudaStream_t st) {
+    switch (mb) {
+        case 1: return launch_fmt_mb<FMT, 1>(a, tmap, fused, grid, smem, st);
+        case 2: return launch_fmt_mb<FMT, 2>(a, tmap, fused, grid, smem, st);
+        case 4: return launch_fmt_mb<FMT, 4>(a, tmap, fused, grid, smem, st);
+        default: return launch_fmt_mb<FMT, 8>(a, tmap, fused, grid, smem, st);
+    }
+}
+
+}  // namespace
+
+bool decode_rows_eligible(const DevWeights& w, size_t m) {
+    if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q8_0) return false;
+    if (m < 1 || m > 8 || w.k % 256 != 0 || w.k < 2048 || w.n < 64) return false;
+    int slab, stages;
+    return pick_config(w.fmt, w.k, pad_rows(m), &slab, &stages);
+}
+
+size_t decode_rows_scratch_bytes(const DevWeights& w, size_t m) {
+    if ((int)m <= kFusedMaxRows) return 0;
+    return nat_sizes(w.fmt != FQ_Q8_0, (size_t)w.k).row * m;
+}
+
+cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev, uint8_t* scratch, float* c, int m, int ldc,
+                               int sm_count, int* status, cudaStream_t st) {
+    const int mb = pad_rows((size_t)m);
+    RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0};
+    if (!pick_config(w.fmt, w.k, mb, &a.slab, &a.stages)) return cudaErrorInvalidValue;
+    // K-quant units are an odd number of 16-byte chunks: one tensor copy per warp step instead of 32
+    // per-lane bulk copies (small bulk copies are issue-rate bound in the copy engine)
+    CUtensorMap tmap;
+    memset(&tmap, 0, sizeof tmap);
+    static const bool no_tmap = getenv("FUCINA_B200_DECODE_NO_TMAP") != nullptr;
+    if (w.fmt != FQ_Q8_0 && a.slab == 1 && !no_tmap && make_weight_tmap(w, mat, slab_geom(w.fmt, 1).unit_bytes, &tmap)) a.use_tmap = 1;
+    const bool fused = m <= kFusedMaxRows;
+    if (!fused) {
+        cudaError_t e = launch_quantize_acts_natural(a_dev, m, w.k, w.fmt != FQ_Q8_0, scratch, st);
+        if (e != cudaSuccess) return e;
+    }
+    int grid = sm_count;
+    if (grid > (w.n + 7) / 8) grid = (w.n + 7) / 8;
+    const size_t smem = smem_bytes(w.fmt, w.k, mb, a.slab, a.stages);
+    switch (w.fmt) {
+        case FQ_Q4_K: return launch_fmt<FQ_Q4_K>(a, tmap, mb, fused, grid, smem, st);
+        case FQ_Q5_K: return launch_fmt<FQ_Q5_K>(a, tmap, mb, fused, grid, smem, st);
+        default: return launch_fmt<FQ_Q8_0>(a, tmap, mb, fused, grid, smem, st);
+    }
+}
+
+}  // namespace fq

@@ -6,6 +6,7 @@
 // multiply with an add (Zig does not contract). Division and square root are
 // IEEE-rounded under nvcc's defaults (-prec-div=true -prec-sqrt=true), and
 // denormals are kept (-ftz=false).
+#include "actquant.cuh"
 #include "acts.cuh"
 #include "internal.h"
 
@@ -178,67 +179,6 @@ cudaError_t launch_dequant_rows(const DevWeights& w, int mat, int row0, int rows
 // ===========================================================================
 // Activation quantisation.
 // ===========================================================================
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-__device__ __forceinline__ int warp_min_i(int v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-
-// Q8_K values of one 256-element block; lane owns elements 8*lane..8*lane+7.
-// Follows q8k.zig:268-313: the scale comes from the FIRST element whose
-// magnitude equals the block maximum, inv = -127/max_value, q =
-// min(127, round_even(inv * v)), d = 1/inv. Returns d; q[] per lane.
-__device__ __forceinline__ float q8k_block(const float v[8], int lane, int q[8]) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    amax = warp_max(amax);
-    int first = 1 << 20;
-    float cand = 0.0f;
-#pragma unroll
-    for (int j = 7; j >= 0; --j)
-        if (fabsf(v[j]) == amax) {
-            first = lane * 8 + j;
-            cand = v[j];
-        }
-    const int idx = warp_min_i(first);
-    const float max_value = __shfl_sync(0xffffffffu, cand, (idx >> 3) & 31);
-    if (amax == 0.0f) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) q[j] = 0;
-        return 0.0f;
-    }
-    const float inv = -127.0f / max_value;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) q[j] = (int)fminf(127.0f, rintf(inv * v[j]));
-    return 1.0f / inv;
-}
-
-// Q8_0 values (q8k.zig:49-69): d = amax/127 over 32 elements (4 lanes),
-// q = clamp(round_half_away(v * (1/d)), +-127); the stored scale is f16.
-__device__ __forceinline__ uint16_t q8_0_quarter(const float v[8], int q[8]) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    const float d = amax / 127.0f;
-    const float inv_d = (d == 0.0f) ? 0.0f : 1.0f / d;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) q[j] = (int)fmaxf(-127.0f, fminf(127.0f, roundf(v[j] * inv_d)));
-    return __half_as_ushort(__float2half_rn(d));
-}
-
-__device__ __forceinline__ uint32_t pack4(const int* q) {
-    return (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) |
-           ((uint32_t)(q[3] & 0xff) << 24);
-}
-
 // One warp per 256 activations of one row, written in the decode layout of
 // acts.cuh. grid.x covers rows * k/256 warps.
 __global__ void quantize_acts_layout_kernel(const float* __restrict__ a, const int* __restrict__ src_rows, int src_div, int m, int k,
@@ -377,6 +317,25 @@ cudaError_t launch_quantize_acts_struct(const float* a, int m, int k, bool q8k, 
     const int threads = 128;
     const size_t blocks = (warps * 32 + threads - 1) / threads;
     quantize_acts_struct_kernel<<<(unsigned)blocks, threads, 0, st>>>(a, m, k, q8k ? 1 : 0, out);
+    return cudaGetLastError();
+}
+
+// Natural-order records for the row-per-lane decode kernel (actquant.cuh).
+__global__ void quantize_acts_natural_kernel(const float* __restrict__ a, int m, int k, int q8k, uint8_t* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+    const int blocks_per_row = k >> 8;
+    if (warp >= (size_t)m * blocks_per_row) return;
+    const int row = (int)(warp / blocks_per_row), blk = (int)(warp % blocks_per_row);
+    const NatSizes S = nat_sizes(q8k != 0, k);
+    quantize_block_natural(a + (size_t)row * k, blk, q8k != 0, k, out + (size_t)row * S.row, lane);
+}
+
+cudaError_t launch_quantize_acts_natural(const float* a, int m, int k, bool q8k, uint8_t* out, cudaStream_t st) {
+    const size_t warps = (size_t)m * (k / 256);
+    const int threads = 128;
+    const size_t blocks = (warps * 32 + threads - 1) / threads;
+    quantize_acts_natural_kernel<<<(unsigned)blocks, threads, 0, st>>>(a, m, k, q8k ? 1 : 0, out);
     return cudaGetLastError();
 }
 

@@ -50,4 +50,28 @@ struct GemvArgs {
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st);
 size_t gemv_max_rows();  // largest m one launch (or one table entry) handles
 
+// formats.cu -- natural-order activation records (actquant.cuh)
+cudaError_t launch_quantize_acts_natural(const float* a, int m, int k, bool q8k, uint8_t* out, cudaStream_t st);
+
+// decode_rows.cu -- row-per-lane decode kernel with TMA-staged weights.
+struct RowsArgs {
+    DevWeights w;
+    int mat;
+    const float* a_f32;       // [m][k] f32 activations, quantised in the kernel prologue (fused form)
+    const uint8_t* acts_nat;  // or m pre-quantised natural records
+    float* c;                 // [m][ldc]
+    int m;
+    int ldc;
+    int slab;    // 256-weight units per row per pipeline step
+    int stages;  // pipeline depth per warp
+    int* status; // device-visible status word (FQ_ERR_TIMEOUT on a wait that gave up)
+    int use_tmap; // weights arrive by 2-D tensor copies (one per warp step) instead of per-lane bulk copies
+};
+// true when the shape is one the kernel serves (format, K, m, shared memory)
+bool decode_rows_eligible(const DevWeights& w, size_t m);
+// bytes of natural-record scratch the non-fused form needs (0 for the fused form)
+size_t decode_rows_scratch_bytes(const DevWeights& w, size_t m);
+cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev, uint8_t* scratch, float* c, int m, int ldc,
+                               int sm_count, int* status, cudaStream_t st);
+
 }  // namespace fq

@@ -45,6 +45,8 @@ int cuda_fail(cudaError_t e, const char* what) {
 // ---------------------------------------------------------------------------
 Trace g_trace;
 static bool g_trace_on = false;
+// FUCINA_B200_DECODE_ROWS=0 keeps every decode shape on the lane-per-chunk kernel (diagnosis switch)
+static bool g_decode_rows_on = true;
 
 // Device-side duration of the decode kernel, the CUDA-event twin of the
 // reference's per-kind nanosecond counters (backend/cuda.zig:231-257). While
@@ -96,6 +98,7 @@ static void ensure_config() {
         if (env_u64("FUCINA_GPU", &v)) g_cfg.gpu_enabled = v != 0;
         if (env_u64("FUCINA_GPU_DECODE", &v)) g_cfg.decode_enabled = v != 0;
         if (env_u64("FUCINA_GPU_TRACE", &v)) g_trace_on = v != 0;
+        if (env_u64("FUCINA_B200_DECODE_ROWS", &v)) g_decode_rows_on = v != 0;
         env_u64("FUCINA_GPU_MIN_WORK_QMOE", &g_cfg.min_work_qmoe);
         env_u64("FUCINA_GPU_MIN_WORK_DENSE_Q4", &g_cfg.min_work_packed_q4);
         env_u64("FUCINA_GPU_MIN_WORK_DENSE_Q5", &g_cfg.min_work_packed_q5);
@@ -138,6 +141,11 @@ static int init_locked(int device) {
     size_t free_b = 0, total_b = 0;
     cudaMemGetInfo(&free_b, &total_b);
     g_ctx.vram_budget = g_cfg.vram_budget_env ? g_cfg.vram_budget_env : (size_t)((double)free_b * 0.8);
+    // status word kernels write when a bounded wait gives up: mapped host memory, read without a copy
+    if ((e = cudaHostAlloc((void**)&g_ctx.status_host, sizeof(int), cudaHostAllocMapped)) != cudaSuccess ||
+        (e = cudaHostGetDevicePointer((void**)&g_ctx.status_dev, g_ctx.status_host, 0)) != cudaSuccess)
+        return fail(FQ_DECLINED_NO_GPU, "status word allocation: %s", cudaGetErrorString(e));
+    *g_ctx.status_host = 0;
     return FQ_OK;
 }
 
@@ -156,6 +164,15 @@ Ctx* context() {
     // entries can arrive on arbitrary threads (backend/cuda.zig:1776-1779)
     cudaSetDevice(g_ctx.device);
     return &g_ctx;
+}
+
+// A kernel whose bounded wait gave up leaves its code in the status word; the
+// host reports it at the next synchronisation point and clears it.
+int device_status(Ctx* ctx) {
+    const int s = *(volatile int*)ctx->status_host;
+    if (s == 0) return FQ_OK;
+    *(volatile int*)ctx->status_host = 0;
+    return fail(s, "a device-side wait gave up (status %d)", s);
 }
 
 // ---------------------------------------------------------------------------
@@ -432,6 +449,29 @@ int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* 
         if (rc != FQ_DECLINED_ARGS || mode == FQ_MODE_TENSOR) return rc;
         // shapes the tensor-core kernel does not take fall through to the integer kernel
     }
+    // dense decode shapes: the row-per-lane kernel with TMA-staged weights
+    if (!accumulate && g_decode_rows_on && decode_rows_eligible(w, m)) {
+        const size_t sb = decode_rows_scratch_bytes(w, m);
+        uint8_t* nat = sb ? (uint8_t*)dev_alloc(sb) : nullptr;
+        if (sb && !nat) return fail(FQ_DECLINED_BUDGET, "activation scratch allocation failed");
+        cudaEvent_t t0 = nullptr, t1 = nullptr;
+        if (g_ktime_on) {
+            t0 = ktime_event();
+            t1 = ktime_event();
+            cudaEventRecord(t0, st);
+        }
+        cudaError_t e = launch_decode_rows(w, mat, a_dev, nat, c_dev, (int)m, (int)ldc, ctx->sm_count, ctx->status_dev, st);
+        if (g_ktime_on) {
+            cudaEventRecord(t1, st);
+            g_ktime_events.emplace_back(t0, t1);
+        }
+        g_trace.launches += sb ? 2 : 1;
+        if (nat) {
+            if (st != ctx->stream) cudaStreamSynchronize(st);
+            dev_free(nat);
+        }
+        return e == cudaSuccess ? FQ_OK : cuda_fail(e, "decode launch");
+    }
     const ActSizes S = act_sizes(w.fmt, w.k);
     const size_t chunk_max = gemv_max_rows();
     const size_t rows_scratch = m < chunk_max ? m : chunk_max;
@@ -618,7 +658,8 @@ int fq_synchronize(void) {
     Ctx* ctx = context();
     if (!ctx) return FQ_DECLINED_NO_GPU;
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
-    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "synchronize");
+    if (e != cudaSuccess) return cuda_fail(e, "synchronize");
+    return device_status(ctx);
 }
 
 size_t fq_block_elems(int fmt) { return format_info(fmt).block_elems; }
@@ -990,6 +1031,47 @@ void fq_trace_counters(uint64_t out[8]) {
     out[0] = g_trace.calls, out[1] = g_trace.launches, out[2] = g_trace.h2d_bytes, out[3] = g_trace.d2h_bytes;
     out[4] = g_trace.resident_hits, out[5] = g_trace.resident_adopts, out[6] = g_trace.gate_pass, out[7] = g_trace.gate_fail;
 }
+// ---- CUDA graphs over the library stream ---------------------------------------
+// Decode steps are a handful of microsecond kernels; replaying them as one graph
+// removes the per-launch host cost. Only *_dev entries that neither allocate
+// nor synchronise may run between begin and end (the decode shapes with m <= 4).
+int fq_capture_begin(void) {
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    g_dispatch_lock.lock();  // held until fq_capture_end: nothing else may touch the stream while it captures
+    cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) {
+        g_dispatch_lock.unlock();
+        return cuda_fail(e, "begin capture");
+    }
+    return FQ_OK;
+}
+int fq_capture_end(fq_graph** out) {
+    Ctx* ctx = context();
+    if (!ctx || !out) {
+        return fail(FQ_DECLINED_ARGS, "no capture in progress");
+    }
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    cudaGraphExec_t exec = nullptr;
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&exec, graph, 0);
+    if (graph) cudaGraphDestroy(graph);
+    g_dispatch_lock.unlock();
+    if (e != cudaSuccess) return cuda_fail(e, "end capture");
+    *out = reinterpret_cast<fq_graph*>(exec);
+    return FQ_OK;
+}
+int fq_graph_launch(fq_graph* g) {
+    Ctx* ctx = context();
+    if (!ctx || !g) return fail(FQ_DECLINED_ARGS, "null graph");
+    std::lock_guard<std::recursive_mutex> lk(g_dispatch_lock);
+    cudaError_t e = cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(g), ctx->stream);
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "graph launch");
+}
+void fq_graph_destroy(fq_graph* g) {
+    if (g && context()) cudaGraphExecDestroy(reinterpret_cast<cudaGraphExec_t>(g));
+}
+
 void fq_trace_kernel_timing(int enable) {
     std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
     g_ktime_on = enable != 0;

@@ -20,6 +20,8 @@ struct Ctx {
     cudaStream_t stream = nullptr;    // compute stream: every library kernel and copy is ordered here
     cudaStream_t transfer = nullptr;  // spare stream for overlapped host transfers
     size_t vram_budget = 0;
+    int* status_host = nullptr;  // mapped status word, host view
+    int* status_dev = nullptr;   // and the pointer kernels receive
     char name[256] = {0};
 };
 
@@ -33,6 +35,7 @@ extern std::recursive_mutex g_dispatch_lock;
 int fail(int code, const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 Ctx* context();
+int device_status(Ctx* ctx);  // FQ_OK, or the code a kernel's bounded wait left behind (then cleared)
 void* dev_alloc(size_t n);
 void dev_free(void* p);
 void* pin_alloc(size_t n);

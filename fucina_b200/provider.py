@@ -232,6 +232,38 @@ def quantize_acts_q8_0_dev(a_dev, m: int, k: int, dev_blocks) -> None:
     _check(load().fq_quantize_acts_q8_0_dev(_vp(a_dev), m, k, _vp(dev_blocks)))
 
 
+class Graph:
+    """A captured sequence of *_dev calls on the library stream, replayed with one launch."""
+
+    def __init__(self, handle: int):
+        self.handle = handle
+
+    def launch(self) -> None:
+        _check(load().fq_graph_launch(self.handle))
+
+    def destroy(self) -> None:
+        if self.handle:
+            load().fq_graph_destroy(self.handle)
+            self.handle = 0
+
+
+class capture:
+    """`with capture() as cap: ...dev calls...` then `cap.graph.launch()`."""
+
+    def __enter__(self):
+        _check(load().fq_capture_begin())
+        self.graph = None
+        return self
+
+    def __exit__(self, et, ev, tb):
+        h = C.c_void_p()
+        rc = load().fq_capture_end(C.byref(h))
+        if et is None:
+            _check(rc)
+            self.graph = Graph(h.value)
+        return False
+
+
 # --------------------------------------------------------------------------- MoE
 def qmoe_stage(in_floats: int, out_floats: int):
     """`qmoeStage` (src/backend/cuda.zig:2221): the provider's pinned in/out panels as numpy views."""

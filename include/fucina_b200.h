@@ -166,6 +166,18 @@ FQ_API int fq_gemm_ptqtp_dev(const fq_weights* const* planes, int n_planes, cons
 FQ_API int fq_quantize_acts_q8_k_dev(const float* a_dev, size_t m, size_t k, void* dev_blocks);
 FQ_API int fq_quantize_acts_q8_0_dev(const float* a_dev, size_t m, size_t k, void* dev_blocks);
 
+/* ---- CUDA graphs over the library stream (new; the reference is eager and
+ *      pays 4-17 us of submit time per call, docs/GPU-OFFLOAD.md:376-390) ----
+ * Between fq_capture_begin and fq_capture_end only *_dev entries that neither
+ * allocate nor synchronise may be called from the capturing thread: the dense
+ * decode shapes with m <= 4 on the library stream (stream = NULL). The
+ * captured step replays with one launch. */
+typedef struct fq_graph fq_graph;
+FQ_API int fq_capture_begin(void);
+FQ_API int fq_capture_end(fq_graph** out);
+FQ_API int fq_graph_launch(fq_graph* g);
+FQ_API void fq_graph_destroy(fq_graph* g);
+
 /* ---- grouped MoE GEMM over a CPU-built tile table ----
  * backend/cuda.zig:2181 `qmoe_lock`, :2221 `qmoeStage`, :2244-2333
  * `gemmQGroupedNt`. The stage's host panels are owned by the library. */

@@ -171,6 +171,28 @@ def test_full_size_decode_against_oracle(P, torch):
     assert_close(got, oracle.matmul(oracle.Q8_0, blocks, a), TOL_INT8, "q8gemv shape")
 
 
+@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q8_0"])
+@pytest.mark.parametrize("n,k", [(64, 2048), (100, 2304), (333, 4096), (1000, 11008), (4096, 4096)])
+def test_dense_decode_kernel_shapes(P, torch, fmt_name, n, k):
+    # shapes the TMA-staged row-per-lane kernel takes: ragged row tiles (n not a
+    # multiple of 32), ragged K slabs (9 and 43 blocks per row), more CTAs than row tiles
+    fmt = oracle.FORMATS[fmt_name]
+    blocks = make_weights(fmt_name, n, k, seed=1400 + n)
+    for m in (1, 2, 3, 5, 8):
+        a = acts(m, k, 1500 + m)
+        got = run_dev(P, torch, fmt, blocks, a, n)
+        assert_close(got, oracle.matmul(fmt, blocks, a), TOL_INT8, f"{fmt_name} {m}x{n}x{k}")
+
+
+def test_dense_decode_is_deterministic(P, torch):
+    n, k = 4096, 4096
+    blocks = make_weights("q4_k", n, k, seed=1600)
+    a = acts(1, k, 1601)
+    y1 = run_dev(P, torch, oracle.Q4_K, blocks, a, n)
+    y2 = run_dev(P, torch, oracle.Q4_K, blocks, a, n)
+    assert np.array_equal(y1.view(np.uint32), y2.view(np.uint32))
+
+
 def test_int8_path_stays_near_the_dequantised_product(P, torch):
     # Oracle B (f64 over dequantised weights, exact f32 activations): the int8
     # activation quantisation moves outputs by well under 5% of the output RMS.
