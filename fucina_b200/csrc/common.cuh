@@ -34,15 +34,35 @@ __host__ __device__ inline FormatInfo format_info(int fmt) {
 // 34/66/130-byte formats are split per row into a payload plane followed by
 // an f16 scale plane so every payload chunk is 16-byte aligned:
 //   row = [ qs of block 0 | qs of block 1 | ... ][ d0 d1 ... ] padded to 16 B.
+//
+// Dense K-quant matrices that the streaming decode kernel serves (one matrix,
+// K >= 2048) are additionally stored TILE-MAJOR (tile_rows = 32): rows are
+// grouped 32 at a time and, inside a group, the 256-weight unit u of all 32
+// rows is contiguous:
+//   tile t = [ unit 0 of rows 32t..32t+31 | unit 1 of rows 32t.. | ... ]
+// so the 32 rows x one unit a warp consumes per step is ONE contiguous run of
+// 32*unit_bytes in HBM -- a single bulk copy that lands in shared memory as
+// 32 slots of unit_bytes (an odd number of 16-byte chunks: no bank conflicts).
+// Bytes only move; the byte count is unchanged apart from padding n to 32.
 struct DevWeights {
     const uint8_t* base;
-    size_t row_stride;  // bytes between rows
+    size_t row_stride;  // bytes between rows (row-major) / bytes of one row's units (tile-major)
     size_t mat_stride;  // bytes between stacked matrices
     int fmt;
     int n;       // rows per matrix
     int k;       // elements per row
     int n_mats;
+    int tile_rows;  // 0 = row-major, 32 = tile-major (K-quants only)
 };
+
+// Unit 0 of `row` and the byte distance between consecutive units of that row.
+__host__ __device__ inline const uint8_t* row_unit0(const DevWeights& w, const uint8_t* mat_base, int row, int unit_bytes) {
+    if (!w.tile_rows) return mat_base + (size_t)row * w.row_stride;
+    return mat_base + (size_t)(row >> 5) * ((size_t)32 * w.row_stride) + (size_t)(row & 31) * unit_bytes;
+}
+__host__ __device__ inline size_t unit_stride(const DevWeights& w, int unit_bytes) {
+    return w.tile_rows ? (size_t)32 * unit_bytes : (size_t)unit_bytes;
+}
 
 __host__ __device__ inline size_t dev_row_stride(int fmt, size_t k) {
     const FormatInfo f = format_info(fmt);

@@ -36,8 +36,6 @@ namespace fq {
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = 8;
 constexpr int kMaxStages = 4;
 constexpr unsigned kWaitLimit = 1u << 20;
 
@@ -74,10 +72,14 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                  : "memory");
 }
 
+// Shared-memory addresses are carried as 32-bit shared-window offsets; loads go through typed
+// pointers so constant offsets fold into the instruction and the scheduler may batch them. The
+// mbarrier wait's memory clobber keeps every load behind the wait that guards its stage.
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
+    return *reinterpret_cast<const uint4*>(__cvta_shared_to_generic(addr));
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+    return *reinterpret_cast<const float*>(__cvta_shared_to_generic(addr));
 }
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
 __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
@@ -85,17 +87,16 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
     asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
+// two independent chains per 16 bytes: dp4a results are needed soon and the chain latency shows
 __device__ __forceinline__ int dot16_ss(const uint32_t* w, const uint4& a, int acc) {
-    acc = dp4a_ss(w[0], a.x, acc);
-    acc = dp4a_ss(w[1], a.y, acc);
-    acc = dp4a_ss(w[2], a.z, acc);
-    return dp4a_ss(w[3], a.w, acc);
+    const int x = dp4a_ss(w[1], a.y, dp4a_ss(w[0], a.x, acc));
+    const int y = dp4a_ss(w[3], a.w, dp4a_ss(w[2], a.z, 0));
+    return x + y;
 }
 __device__ __forceinline__ int dot16_us(const uint32_t* w, const uint4& a, int acc) {
-    acc = dp4a_us(w[0], a.x, acc);
-    acc = dp4a_us(w[1], a.y, acc);
-    acc = dp4a_us(w[2], a.z, acc);
-    return dp4a_us(w[3], a.w, acc);
+    const int x = dp4a_us(w[1], a.y, dp4a_us(w[0], a.x, acc));
+    const int y = dp4a_us(w[3], a.w, dp4a_us(w[2], a.z, 0));
+    return x + y;
 }
 __device__ __forceinline__ int byte_of(uint32_t w, int i) { return (int)((w >> (8 * i)) & 0xffu); }
 
@@ -176,8 +177,7 @@ __device__ __forceinline__ void block_q4_k(uint32_t p, const ActView& V, int kb,
     for (int b = 0; b < MB; ++b) {
         const uint32_t rec = V.base + b * V.row;
         const int imn = min_term(H, rec + V.off_sums + kb * 32);
-        float da;
-        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(da) : "r"(rec + V.off_ad + kb * 4));
+        const float da = lds_f32(rec + V.off_ad + kb * 4);
         acc[b] = __fadd_rn(acc[b], kquant_term(H, da, isc_lo[b] + (isc_hi[b] >> 4), imn));
     }
 }
@@ -218,8 +218,7 @@ __device__ __forceinline__ void block_q5_k(uint32_t p, const ActView& V, int kb,
     for (int b = 0; b < MB; ++b) {
         const uint32_t rec = V.base + b * V.row;
         const int imn = min_term(H, rec + V.off_sums + kb * 32);
-        float da;
-        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(da) : "r"(rec + V.off_ad + kb * 4));
+        const float da = lds_f32(rec + V.off_ad + kb * 4);
         acc[b] = __fadd_rn(acc[b], kquant_term(H, da, isc[b], imn));
     }
 }
@@ -242,8 +241,7 @@ __device__ __forceinline__ void unit_q8_0(uint32_t p, uint32_t ps, const ActView
             const uint4 a0 = lds128(a), a1 = lds128(a + 16);
             int dot = dot16_ss(w, a0, 0);
             dot = dot16_ss(w + 4, a1, dot);
-            float da;
-            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(da) : "r"(rec + V.off_ad + (kb * 8 + j) * 4));
+            const float da = lds_f32(rec + V.off_ad + (kb * 8 + j) * 4);
             acc[b] = __fadd_rn(acc[b], __fmul_rn((float)dot, __fmul_rn(da, dw)));
         }
     }
@@ -267,9 +265,10 @@ __host__ __device__ inline SlabGeom slab_geom(int fmt, int slab) {
     return g;
 }
 
-template <int FMT, int MB, bool FUSED>
-__global__ void __launch_bounds__(kThreads, 1) decode_rows_kernel(const RowsArgs A, const __grid_constant__ CUtensorMap tmap) {
+template <int FMT, int MB, bool FUSED, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) decode_rows_kernel(const RowsArgs A, const __grid_constant__ CUtensorMap tmap) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int kWarps = WARPS, kThreads = WARPS * 32;  // the warps split K; 16 when a row has at least 16 units
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int k = A.w.k, n = A.w.n;
     constexpr bool Q8K = FMT != FQ_Q8_0;
@@ -281,7 +280,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_rows_kernel(const RowsArgs
 
     // shared memory: barriers | activation records | reduction buffers | stage slots
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-    uint8_t* acts = smem + 256;
+    uint8_t* acts = smem + 512;
     float* red = reinterpret_cast<float*>(acts + ((MB * NS.row + 127) & ~(size_t)127));
     uint8_t* slots = reinterpret_cast<uint8_t*>(red) + 2 * kWarps * MB * 32 * sizeof(float);
     const uint32_t slot0 = smem_u32(slots) + (uint32_t)((warp * A.stages) * 32 + lane) * G.slot_bytes;
@@ -295,17 +294,41 @@ __global__ void __launch_bounds__(kThreads, 1) decode_rows_kernel(const RowsArgs
     // this CTA's contiguous row range, balanced over the grid
     const int r_begin = (int)((long long)n * blockIdx.x / gridDim.x);
     const int r_end = (int)((long long)n * (blockIdx.x + 1) / gridDim.x);
-    const int ntiles = (r_end - r_begin + 31) / 32;
+    // row tiles of this CTA: 32 rows from r_begin on (row-major), or the pieces of its range inside
+    // each 32-row storage tile (tile-major: a piece is contiguous in HBM, a straddle is two pieces)
+    const bool tiled = A.w.tile_rows != 0;
+    const int first_tile = r_begin >> 5;
+    const int ntiles = r_end <= r_begin ? 0 : tiled ? ((r_end - 1) >> 5) - first_tile + 1 : (r_end - r_begin + 31) / 32;
+    auto tile_rows = [&](int tile, int& row0, int& nvalid) {
+        if (tiled) {
+            row0 = max(r_begin, (first_tile + tile) << 5);
+            nvalid = min(r_end, (first_tile + tile + 1) << 5) - row0;
+        } else {
+            row0 = r_begin + tile * 32;
+            nvalid = min(32, r_end - row0);
+        }
+    };
     const int total = ntiles * my_slabs;  // pipeline steps of this warp
     const uint8_t* wbase = A.w.base + (size_t)A.mat * A.w.mat_stride;
 
     auto issue = [&](int it) {
         const int tile = it / my_slabs, sl = warp + kWarps * (it % my_slabs);
         const int stage = it % A.stages;
-        const int row0 = r_begin + tile * 32;
-        const int nvalid = min(32, r_end - row0);
+        int row0, nvalid;
+        tile_rows(tile, row0, nvalid);
         const int nu = min(A.slab, units - sl * A.slab);  // units in this (possibly ragged) slab
         const uint32_t bar = bar0 + stage * 8;
+        if (tiled) {
+            // tile-major weights: unit `sl` of these rows is one contiguous run -> one bulk copy per warp step
+            if (lane == 0) {
+                const uint32_t bytes = (uint32_t)(nvalid * G.unit_bytes);
+                mbar_arrive_expect_tx(bar, bytes);
+                const uint8_t* src = wbase + (size_t)(row0 >> 5) * ((size_t)32 * A.w.row_stride) + (size_t)sl * 32 * G.unit_bytes +
+                                     (size_t)(row0 & 31) * G.unit_bytes;
+                bulk_load(slot0 + (uint32_t)stage * 32 * G.slot_bytes, src, bytes, bar);
+            }
+            return;
+        }
         if (A.use_tmap) {
             // one 2-D tensor copy per warp step: 32 rows x one unit, landing densely (the unit size is an
             // odd number of 16-byte chunks, so the rows need no padding to stay bank-conflict free);
@@ -332,15 +355,25 @@ __global__ void __launch_bounds__(kThreads, 1) decode_rows_kernel(const RowsArgs
         }
     };
 
+    // let the next kernel of the stream begin its own launch; it waits below before it reads or writes
+    // anything this kernel (or an earlier one) may still be producing
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     // start streaming weights before touching the activations
     const int prefetch = min(A.stages, total);
     for (int it = 0; it < prefetch; ++it) issue(it);
 
+    // everything before this point read only immutable weights; activations and outputs may belong
+    // to the preceding kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
     // activation records: quantise here (FUSED) or copy the pre-quantised records
     if (FUSED) {
+        // warp w quantises activation blocks w, w+kWarps, ...: with one-unit slabs these are exactly the
+        // blocks it consumes, so no CTA-wide barrier is needed before it starts on its weights
         const int nblk = k >> 8;
-        for (int i = warp; i < MB * nblk; i += kWarps) {
-            const int b = i / nblk, blk = i % nblk;
+        for (int i = 0; i < MB * ((nblk - warp + kWarps - 1) / kWarps); ++i) {
+            const int blk = warp + (i / MB) * kWarps, b = i % MB;
             uint8_t* rec = acts + (size_t)b * NS.row;
             if (b < A.m) {
                 quantize_block_natural(A.a_f32 + (size_t)b * k, blk, Q8K, k, rec, lane);
@@ -361,7 +394,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_rows_kernel(const RowsArgs
         for (int i = threadIdx.x; i < MB * units_per_rec; i += kThreads)
             dst[i] = (i / units_per_rec < A.m) ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
     }
-    __syncthreads();
+    if (FUSED && A.slab == 1)
+        __syncwarp();
+    else
+        __syncthreads();
 
     const ActView V = {smem_u32(acts), (uint32_t)NS.row, (uint32_t)NS.aq, (uint32_t)(NS.aq + NS.sums)};
     bool ok = true;
@@ -380,7 +416,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_rows_kernel(const RowsArgs
             }
             const int nu = min(A.slab, units - sl * A.slab);
             const uint32_t p = slot0 + (uint32_t)stage * 32 * G.slot_bytes;
-            for (int u = 0; u < nu; ++u) {
+            for (int u = 0; u < nu && !A.skip_compute; ++u) {
                 const int kb = sl * A.slab + u;
                 if (FMT == FQ_Q4_K) block_q4_k<MB>(p + u * 144, V, kb, acc);
                 if (FMT == FQ_Q5_K) block_q5_k<MB>(p + u * 176, V, kb, acc);
@@ -399,8 +435,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_rows_kernel(const RowsArgs
             float s = 0.0f;
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) s += rbuf[(w * MB + b) * 32 + lane];
-            const int row = r_begin + tile * 32 + lane;
-            if (row < r_end && b < A.m) A.c[(size_t)b * A.ldc + row] = s;
+            int row0, nvalid;
+            tile_rows(tile, row0, nvalid);
+            if (lane < nvalid && b < A.m) A.c[(size_t)b * A.ldc + row0 + lane] = s;
         }
     }
     if (!ok) {
@@ -413,17 +450,26 @@ __global__ void __launch_bounds__(kThreads, 1) decode_rows_kernel(const RowsArgs
 constexpr size_t kSmemLimit = 227 * 1024;
 constexpr int kFusedMaxRows = 4;  // up to here each CTA quantises the activations itself
 
-size_t smem_bytes(int fmt, int k, int mb, int slab, int stages) {
+size_t smem_bytes(int fmt, int k, int mb, int slab, int stages, int warps) {
     const NatSizes NS = nat_sizes(fmt != FQ_Q8_0, (size_t)k);
     const SlabGeom G = slab_geom(fmt, slab);
-    return 256 + ((mb * NS.row + 127) & ~(size_t)127) + (size_t)2 * kWarps * mb * 32 * sizeof(float) +
-           (size_t)kWarps * stages * 32 * G.slot_bytes;
+    return 512 + ((mb * NS.row + 127) & ~(size_t)127) + (size_t)2 * warps * mb * 32 * sizeof(float) +
+           (size_t)warps * stages * 32 * G.slot_bytes;
+}
+
+// 16 warps per CTA double the thread-level parallelism that hides shared-memory and dp4a latency;
+// they need 16 units per row to split and the register budget of the small-batch variants.
+int pick_warps(int k, int mb) {
+    static const int forced = getenv("FUCINA_B200_DECODE_WARPS") ? atoi(getenv("FUCINA_B200_DECODE_WARPS")) : 0;
+    if (forced == 8) return 8;
+    return (k / 256 >= 16 && mb <= 2) ? 16 : 8;
 }
 
 int pad_rows(size_t m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
 
 // deepest pipeline that fits: more bytes in flight per SM first, then fewer barriers per byte
 bool pick_config(int fmt, int k, int mb, int* slab, int* stages) {
+    const int warps = pick_warps(k, mb);
     static const int cand[][2] = {{1, 4}, {2, 2}, {1, 3}, {1, 2}};
     static int force_slab = -1, force_stages = -1;
     if (force_slab < 0) {
@@ -432,12 +478,12 @@ bool pick_config(int fmt, int k, int mb, int* slab, int* stages) {
         force_slab = a ? atoi(a) : 0;
         force_stages = b ? atoi(b) : 0;
     }
-    if (force_slab > 0 && force_stages > 0 && force_stages <= kMaxStages && smem_bytes(fmt, k, mb, force_slab, force_stages) <= kSmemLimit) {
+    if (force_slab > 0 && force_stages > 0 && force_stages <= kMaxStages && smem_bytes(fmt, k, mb, force_slab, force_stages, warps) <= kSmemLimit) {
         *slab = force_slab, *stages = force_stages;
         return true;
     }
     for (auto& c : cand)
-        if (smem_bytes(fmt, k, mb, c[0], c[1]) <= kSmemLimit) {
+        if (smem_bytes(fmt, k, mb, c[0], c[1], warps) <= kSmemLimit) {
             *slab = c[0], *stages = c[1];
             return true;
         }
@@ -479,16 +525,33 @@ bool make_weight_tmap(const DevWeights& w, int mat, int unit_bytes, CUtensorMap*
 
 template <int FMT, int MB>
 cudaError_t launch_fmt_mb(const RowsArgs& a, const CUtensorMap& tmap, bool fused, int grid, size_t smem, cudaStream_t st) {
-    auto kern = fused ? decode_rows_kernel<FMT, MB, true> : decode_rows_kernel<FMT, MB, false>;
+    constexpr bool kWide = MB <= 2;  // the 16-warp form exists for the small-batch variants only
+    const bool wide = kWide && pick_warps(a.w.k, MB) == 16;
+    void (*kern)(const RowsArgs, const CUtensorMap) =
+        wide ? (fused ? decode_rows_kernel<FMT, MB, true, kWide ? 16 : 8> : decode_rows_kernel<FMT, MB, false, kWide ? 16 : 8>)
+             : (fused ? decode_rows_kernel<FMT, MB, true, 8> : decode_rows_kernel<FMT, MB, false, 8>);
     // opt in to the large dynamic shared memory once per instantiation, not per launch
-    static size_t granted[2] = {0, 0};
-    if (granted[fused] < smem) {
+    static bool granted[2][2] = {{false, false}, {false, false}};
+    if (!granted[wide][fused]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
         if (e != cudaSuccess) return e;
-        granted[fused] = kSmemLimit;
+        granted[wide][fused] = true;
     }
-    kern<<<grid, kThreads, smem, st>>>(a, tmap);
-    return cudaGetLastError();
+    // Programmatic dependent launch: this grid may be scheduled while the previous kernel of the
+    // stream drains. It only touches read-only weights and its own shared memory before
+    // griddepcontrol.wait, so the launch latency and the first weight loads overlap the predecessor.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(wide ? 512 : 256);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    static const bool no_pdl = getenv("FUCINA_B200_NO_PDL") != nullptr;
+    cfg.attrs = attr;
+    cfg.numAttrs = no_pdl ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kern, a, tmap);
 }
 
 template <int FMT>
@@ -518,14 +581,16 @@ size_t decode_rows_scratch_bytes(const DevWeights& w, size_t m) {
 cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev, uint8_t* scratch, float* c, int m, int ldc,
                                int sm_count, int* status, cudaStream_t st) {
     const int mb = pad_rows((size_t)m);
-    RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0};
+    static const int skip = getenv("FUCINA_B200_DECODE_SKIP_COMPUTE") ? 1 : 0;  // diagnosis: copy pipeline only, outputs are garbage
+    RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0, skip};
     if (!pick_config(w.fmt, w.k, mb, &a.slab, &a.stages)) return cudaErrorInvalidValue;
     // K-quant units are an odd number of 16-byte chunks: one tensor copy per warp step instead of 32
     // per-lane bulk copies (small bulk copies are issue-rate bound in the copy engine)
     CUtensorMap tmap;
     memset(&tmap, 0, sizeof tmap);
     static const bool no_tmap = getenv("FUCINA_B200_DECODE_NO_TMAP") != nullptr;
-    if (w.fmt != FQ_Q8_0 && a.slab == 1 && !no_tmap && make_weight_tmap(w, mat, slab_geom(w.fmt, 1).unit_bytes, &tmap)) a.use_tmap = 1;
+    if (w.tile_rows) a.slab = 1;  // tile-major runs are one unit wide
+    if (!w.tile_rows && w.fmt != FQ_Q8_0 && a.slab == 1 && !no_tmap && make_weight_tmap(w, mat, slab_geom(w.fmt, 1).unit_bytes, &tmap)) a.use_tmap = 1;
     const bool fused = m <= kFusedMaxRows;
     if (!fused) {
         cudaError_t e = launch_quantize_acts_natural(a_dev, m, w.k, w.fmt != FQ_Q8_0, scratch, st);
@@ -533,7 +598,7 @@ cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev,
     }
     int grid = sm_count;
     if (grid > (w.n + 7) / 8) grid = (w.n + 7) / 8;
-    const size_t smem = smem_bytes(w.fmt, w.k, mb, a.slab, a.stages);
+    const size_t smem = smem_bytes(w.fmt, w.k, mb, a.slab, a.stages, pick_warps(w.k, mb));
     switch (w.fmt) {
         case FQ_Q4_K: return launch_fmt<FQ_Q4_K>(a, tmap, mb, fused, grid, smem, st);
         case FQ_Q5_K: return launch_fmt<FQ_Q5_K>(a, tmap, mb, fused, grid, smem, st);

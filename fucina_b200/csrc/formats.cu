@@ -45,17 +45,24 @@ __global__ void repack_split_kernel(uint8_t* dev, size_t dev_row_stride, size_t 
     }
 }
 
-// K-quant rows keep their bytes; only the strides may change (16-byte units).
-__global__ void copy_rows_kernel(uint8_t* dst, size_t dst_row, size_t dst_mat, const uint8_t* src, size_t src_row,
-                                 size_t src_mat, size_t row_bytes, int n, int n_mats) {
-    const size_t units = row_bytes / 16;
-    const size_t total = (size_t)n_mats * n * units;
+// K-quant rows keep their bytes; 16-byte pieces move between the GGUF rows and the
+// device layout (row-major or tile-major, see common.cuh).
+template <bool TO_DEVICE>
+__global__ void kquant_rows_kernel(DevWeights w, uint8_t* gguf, size_t nb01, size_t nb02, int unit_bytes) {
+    const size_t pieces = (size_t)(w.k >> 8) * unit_bytes / 16;
+    const size_t total = (size_t)w.n_mats * w.n * pieces;
+    const size_t ustride = unit_stride(w, unit_bytes);
     for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
-        const size_t u = t % units;
-        const size_t rowlin = t / units;
-        const size_t row = rowlin % n, mat = rowlin / n;
-        const uint4 v = *reinterpret_cast<const uint4*>(src + mat * src_mat + row * src_row + u * 16);
-        *reinterpret_cast<uint4*>(dst + mat * dst_mat + row * dst_row + u * 16) = v;
+        const size_t q = t % pieces;
+        const size_t rowlin = t / pieces;
+        const int row = (int)(rowlin % w.n), mat = (int)(rowlin / w.n);
+        const size_t byte = q * 16, u = byte / unit_bytes, off = byte % unit_bytes;
+        uint8_t* dev = const_cast<uint8_t*>(row_unit0(w, w.base + (size_t)mat * w.mat_stride, row, unit_bytes)) + u * ustride + off;
+        uint8_t* g = gguf + (size_t)mat * nb02 + (size_t)row * nb01 + byte;
+        if (TO_DEVICE)
+            *reinterpret_cast<uint4*>(dev) = *reinterpret_cast<const uint4*>(g);
+        else
+            *reinterpret_cast<uint4*>(g) = *reinterpret_cast<const uint4*>(dev);
     }
 }
 
@@ -75,10 +82,11 @@ cudaError_t launch_repack(const DevWeights& w, const uint8_t* gguf_dev, size_t n
     if (f.sc_bytes == 0) {
         const size_t row_bytes = (size_t)bpr * f.block_bytes;
         const size_t total = (size_t)w.n_mats * w.n * (row_bytes / 16);
+        (void)dev;
         if (to_device)
-            copy_rows_kernel<<<grid_for(total, 256), 256, 0, st>>>(dev, w.row_stride, w.mat_stride, gg, nb01, nb02, row_bytes, w.n, w.n_mats);
+            kquant_rows_kernel<true><<<grid_for(total, 256), 256, 0, st>>>(w, gg, nb01, nb02, f.block_bytes);
         else
-            copy_rows_kernel<<<grid_for(total, 256), 256, 0, st>>>(gg, nb01, nb02, dev, w.row_stride, w.mat_stride, row_bytes, w.n, w.n_mats);
+            kquant_rows_kernel<false><<<grid_for(total, 256), 256, 0, st>>>(w, gg, nb01, nb02, f.block_bytes);
     } else {
         const size_t total = (size_t)w.n_mats * w.n * bpr;
         if (to_device)
@@ -109,7 +117,7 @@ __device__ __forceinline__ void scale_min_one(const uint8_t* q, int j, int& sc, 
 //   TQ2_0  f32(code-1) * d                             (cold.zig:651-670)
 //   folded d * (f32(cu) - 4)                           (ternary.zig:850-876)
 //   Q2_0   f32(q-1) * d                                (cold.zig:289-301)
-__device__ float dequant_element(const uint8_t* row, int fmt, int k, int e) {
+__device__ float dequant_element(const uint8_t* row, size_t ustride, int fmt, int k, int e) {
     switch (fmt) {
         case FQ_Q8_0: {
             const int8_t q = (int8_t)row[e];
@@ -117,7 +125,7 @@ __device__ float dequant_element(const uint8_t* row, int fmt, int k, int e) {
             return (float)q * h2f(d);
         }
         case FQ_Q4_K: {
-            const uint8_t* b = row + (size_t)(e >> 8) * 144;
+            const uint8_t* b = row + (size_t)(e >> 8) * ustride;
             const int r = e & 255, s = r >> 5, i = r & 31;
             const float d = h2f(*reinterpret_cast<const uint16_t*>(b));
             const float dmin = h2f(*reinterpret_cast<const uint16_t*>(b + 2));
@@ -128,7 +136,7 @@ __device__ float dequant_element(const uint8_t* row, int fmt, int k, int e) {
             return d * (float)sc * (float)q - dmin * (float)mn;
         }
         case FQ_Q5_K: {
-            const uint8_t* b = row + (size_t)(e >> 8) * 176;
+            const uint8_t* b = row + (size_t)(e >> 8) * ustride;
             const int r = e & 255, s = r >> 5, i = r & 31;
             const float d = h2f(*reinterpret_cast<const uint16_t*>(b));
             const float dmin = h2f(*reinterpret_cast<const uint16_t*>(b + 2));
@@ -165,8 +173,9 @@ __global__ void dequant_rows_kernel(DevWeights w, int mat, int row0, int rows, f
     for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
         const int e = (int)(t % w.k);
         const int r = (int)(t / w.k);
-        const uint8_t* row = w.base + (size_t)mat * w.mat_stride + (size_t)(row0 + r) * w.row_stride;
-        out[t] = dequant_element(row, w.fmt, w.k, e);
+        const int ub = format_info(w.fmt).block_bytes;  // K-quants: the unit is the block
+        const uint8_t* row = row_unit0(w, w.base + (size_t)mat * w.mat_stride, row0 + r, ub);
+        out[t] = dequant_element(row, unit_stride(w, ub), w.fmt, w.k, e);
     }
 }
 

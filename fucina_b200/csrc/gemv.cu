@@ -57,7 +57,7 @@ template <>
 struct Chunk<FQ_Q8_0> {
     uint4 q;
     float d;
-    __device__ __forceinline__ void load(const uint8_t* row, int c, int k) {
+    __device__ __forceinline__ void load(const uint8_t* row, int c, int k, size_t) {
         q = ld_weight16(row + (size_t)c * 16);
         d = h2f(ld_scale16(row + k + (c >> 1) * 2));
     }
@@ -77,8 +77,8 @@ struct Chunk<FQ_Q4_K> {
     uint32_t lo[4], hi[4];
     int sc0, sc1, mn0, mn1;
     float d, dmin;
-    __device__ __forceinline__ void load(const uint8_t* row, int c, int) {
-        const uint8_t* b = row + (size_t)(c >> 3) * 144;
+    __device__ __forceinline__ void load(const uint8_t* row, int c, int, size_t ustride) {
+        const uint8_t* b = row + (size_t)(c >> 3) * ustride;
         hdr = ldg_cached16(b);  // shared by the 8 lanes of this block
         q = ld_weight16(b + 16 + (c & 7) * 16);
     }
@@ -124,8 +124,8 @@ struct Chunk<FQ_Q5_K> {
     uint32_t lo[4], hi[4];
     int sc0, sc1, mn0, mn1;
     float d, dmin;
-    __device__ __forceinline__ void load(const uint8_t* row, int c, int) {
-        const uint8_t* b = row + (size_t)(c >> 3) * 176;
+    __device__ __forceinline__ void load(const uint8_t* row, int c, int, size_t ustride) {
+        const uint8_t* b = row + (size_t)(c >> 3) * ustride;
         hdr = ldg_cached16(b);
         qh = ldg_cached16(b + 16 + (c & 1) * 16);  // fifth bits of elements h*16..h*16+15, all 8 sub-blocks
         q = ld_weight16(b + 48 + (c & 7) * 16);
@@ -169,7 +169,7 @@ template <>
 struct Chunk<FQ_TQ2_0> {
     uint4 q;
     float d;
-    __device__ __forceinline__ void load(const uint8_t* row, int c, int k) {
+    __device__ __forceinline__ void load(const uint8_t* row, int c, int k, size_t) {
         q = ld_weight16(row + (size_t)c * 16);
         d = h2f(ld_scale16(row + (k >> 2) + (c >> 2) * 2));
     }
@@ -192,7 +192,7 @@ template <>
 struct Chunk<FQ_TQ2_0_FOLDED> {
     uint4 q;
     float d;
-    __device__ __forceinline__ void load(const uint8_t* row, int c, int k) {
+    __device__ __forceinline__ void load(const uint8_t* row, int c, int k, size_t) {
         q = ld_weight16(row + (size_t)c * 16);
         d = h2f(ld_scale16(row + (k >> 1) + (c >> 3) * 2));
     }
@@ -214,7 +214,7 @@ template <>
 struct Chunk<FQ_Q2_0> {
     uint4 q;
     float d;
-    __device__ __forceinline__ void load(const uint8_t* row, int c, int k) {
+    __device__ __forceinline__ void load(const uint8_t* row, int c, int k, size_t) {
         q = ld_weight16(row + (size_t)c * 16);
         d = h2f(ld_scale16(row + (k >> 2) + (c >> 1) * 2));
     }
@@ -279,6 +279,8 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
     const int n_groups = gridDim.x * kWarps * GPW;
     const uint8_t* wbase = A.w.base + (size_t)mat * A.w.mat_stride;
     const uint8_t* wbase2 = GATED ? A.w2.base + (size_t)mat * A.w2.mat_stride : nullptr;
+    constexpr int ub = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 16;  // unit bytes (only K-quants can be tile-major)
+    const size_t ustride = unit_stride(A.w, ub);
 
     for (int row0 = group * RSTEP; row0 < n; row0 += n_groups * RSTEP) {
         float acc[R][MB];
@@ -288,18 +290,18 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
             for (int b = 0; b < MB; ++b) acc[r][b] = 0.0f;
         const uint8_t* wr[R];
         if (GATED) {
-            wr[0] = wbase + (size_t)row0 * A.w.row_stride;
-            wr[1] = wbase2 + (size_t)row0 * A.w2.row_stride;
+            wr[0] = row_unit0(A.w, wbase, row0, ub);
+            wr[1] = row_unit0(A.w2, wbase2, row0, ub);
         } else {
 #pragma unroll
-            for (int r = 0; r < R; ++r) wr[r] = wbase + (size_t)min(row0 + r, n - 1) * A.w.row_stride;
+            for (int r = 0; r < R; ++r) wr[r] = row_unit0(A.w, wbase, min(row0 + r, n - 1), ub);
         }
 
 #pragma unroll 2
         for (int c = gl; c < C; c += LPR) {
             Chunk<FMT> ch[R];
 #pragma unroll
-            for (int r = 0; r < R; ++r) ch[r].load(wr[r], c, k);
+            for (int r = 0; r < R; ++r) ch[r].load(wr[r], c, k, ustride);
 #pragma unroll
             for (int r = 0; r < R; ++r) ch[r].decode(c);
 #pragma unroll

@@ -66,6 +66,7 @@ struct RowsArgs {
     int stages;  // pipeline depth per warp
     int* status; // device-visible status word (FQ_ERR_TIMEOUT on a wait that gave up)
     int use_tmap; // weights arrive by 2-D tensor copies (one per warp step) instead of per-lane bulk copies
+    int skip_compute; // diagnosis only: stream the weights, skip the arithmetic
 };
 // true when the shape is one the kernel serves (format, K, m, shared memory)
 bool decode_rows_eligible(const DevWeights& w, size_t m);

@@ -286,15 +286,23 @@ static int check_dims(int fmt, size_t n, size_t k, size_t n_mats, size_t nb01, s
 }
 
 // Build the device layout from raw GGUF bytes already on the device.
+// Dense K-quant matrices the streaming decode kernel serves are stored tile-major (common.cuh).
+static bool want_tile_major(int fmt, size_t n, size_t k, size_t n_mats, bool allow) {
+    static const bool off = getenv("FUCINA_B200_NO_TILE") != nullptr;
+    return allow && !off && n_mats == 1 && (fmt == FQ_Q4_K || fmt == FQ_Q5_K) && k % 256 == 0 && k >= 2048 && n >= 64;
+}
+
 static int weights_from_dev_bytes(Ctx* ctx, int fmt, const uint8_t* raw_dev, size_t nb01, size_t nb02, size_t n, size_t k,
-                                  size_t n_mats, fq_weights** out) {
+                                  size_t n_mats, bool allow_tile, fq_weights** out) {
+    const bool tile = want_tile_major(fmt, n, k, n_mats, allow_tile);
     const size_t stride = dev_row_stride(fmt, k);
-    const size_t mat_stride = stride * n;
+    const size_t mat_stride = stride * (tile ? (n + 31) / 32 * 32 : n);
     const size_t bytes = mat_stride * n_mats;
     void* p = dev_alloc(bytes);
     if (!p) return fail(FQ_DECLINED_BUDGET, "device allocation of %zu bytes failed", bytes);
+    if (tile && n % 32 != 0) cudaMemsetAsync(p, 0, bytes, ctx->stream);  // rows padding the last tile read as zero blocks
     fq_weights* w = new fq_weights();
-    w->dw = {(const uint8_t*)p, stride, mat_stride, fmt, (int)n, (int)k, (int)n_mats};
+    w->dw = {(const uint8_t*)p, stride, mat_stride, fmt, (int)n, (int)k, (int)n_mats, tile ? 32 : 0};
     w->alloc = p;
     w->bytes = bytes;
     if ((stride * n) % 16 != 0 || ((uintptr_t)raw_dev % 2) != 0) {
@@ -320,7 +328,7 @@ static int weights_from_dev_bytes(Ctx* ctx, int fmt, const uint8_t* raw_dev, siz
 }
 
 static int weights_upload_impl(Ctx* ctx, int fmt, const void* host, size_t nb01, size_t nb02, size_t n, size_t k, size_t n_mats,
-                               fq_weights** out) {
+                               bool allow_tile, fq_weights** out) {
     if (int rc = check_dims(fmt, n, k, n_mats, nb01, nb02)) return rc;
     const size_t span = (n_mats > 1 ? nb02 * (n_mats - 1) : 0) + nb01 * n;
     void* raw = dev_alloc(span);
@@ -331,7 +339,7 @@ static int weights_upload_impl(Ctx* ctx, int fmt, const void* host, size_t nb01,
         dev_free(raw);
         return cuda_fail(e, "weight upload");
     }
-    int rc = weights_from_dev_bytes(ctx, fmt, (const uint8_t*)raw, nb01, nb02, n, k, n_mats, out);
+    int rc = weights_from_dev_bytes(ctx, fmt, (const uint8_t*)raw, nb01, nb02, n, k, n_mats, allow_tile, out);
     // the raw copy is only read by the repack kernel queued above on the same stream
     e = cudaStreamSynchronize(ctx->stream);
     dev_free(raw);
@@ -399,7 +407,7 @@ int resolve_rhs(Ctx* ctx, int fmt, const void* rhs, size_t rhs_len, int cacheabl
                 fq_weights* w = nullptr;
                 const void* src_base = (const void*)e.src_base;  // `e` may move once the lock drops
                 g.unlock();
-                int rc = weights_upload_impl(ctx, fmt, src_base, nb01, 0, rows_total, k, 1, &w);
+                int rc = weights_upload_impl(ctx, fmt, src_base, nb01, 0, rows_total, k, 1, n_mats == 1 && rows_total == n, &w);
                 g.lock();
                 if (rc != FQ_OK) return rc;
                 ResidentEntry& e2 = g_res[resident_find(p, span)];
@@ -420,6 +428,8 @@ int resolve_rhs(Ctx* ctx, int fmt, const void* rhs, size_t rhs_len, int cacheabl
             const size_t off = p - e3.src_base;
             if (off % nb01 != 0 || (n_mats > 1 && nb02 != nb01 * n))
                 return fail(FQ_DECLINED_ARGS, "rhs does not start on a weight row of its resident range");
+            if (tw->dw.tile_rows && ((off / nb01) % 32 != 0 || (n_mats > 1 && n % 32 != 0)))
+                return fail(FQ_DECLINED_ARGS, "a sub-range of tile-major resident weights must start on a 32-row boundary");
             *view = tw->dw;
             view->base += (off / nb01) * tw->dw.row_stride;
             view->n = (int)n;
@@ -430,7 +440,7 @@ int resolve_rhs(Ctx* ctx, int fmt, const void* rhs, size_t rhs_len, int cacheabl
     }
     // transient: stream the bytes for this call only
     fq_weights* w = nullptr;
-    int rc = weights_upload_impl(ctx, fmt, rhs, nb01, nb02, n, k, n_mats, &w);
+    int rc = weights_upload_impl(ctx, fmt, rhs, nb01, nb02, n, k, n_mats, true, &w);
     if (rc != FQ_OK) return rc;
     *view = w->dw;
     *temp = w;
@@ -739,7 +749,7 @@ int fq_weights_upload(int fmt, const void* host_blocks, size_t nb01, size_t nb02
     Ctx* ctx = nullptr;
     if (int rc = gate_and_ctx(&ctx)) return rc;
     std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
-    return weights_upload_impl(ctx, fmt, host_blocks, nb01, nb02, n, k, n_mats, out);
+    return weights_upload_impl(ctx, fmt, host_blocks, nb01, nb02, n, k, n_mats, true, out);
 }
 int fq_weights_from_device(int fmt, const void* dev_blocks, size_t nb01, size_t nb02, size_t n, size_t k, size_t n_mats,
                            fq_weights** out) {
@@ -748,7 +758,7 @@ int fq_weights_from_device(int fmt, const void* dev_blocks, size_t nb01, size_t 
     if (int rc = gate_and_ctx(&ctx)) return rc;
     if (int rc = check_dims(fmt, n, k, n_mats, nb01, nb02)) return rc;
     std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
-    int rc = weights_from_dev_bytes(ctx, fmt, (const uint8_t*)dev_blocks, nb01, nb02, n, k, n_mats, out);
+    int rc = weights_from_dev_bytes(ctx, fmt, (const uint8_t*)dev_blocks, nb01, nb02, n, k, n_mats, true, out);
     if (rc == FQ_OK) {
         cudaError_t e = cudaStreamSynchronize(ctx->stream);
         if (e != cudaSuccess) return cuda_fail(e, "weight repack");
