@@ -55,7 +55,8 @@ SIGNATURES = {
     "fq_work_device_ptr": (C.c_size_t, [c_void]),
     "fq_work_destroy": (None, [c_void]),
     "fq_gemm_quant_nt_dev": (c_int, [c_void, c_size, c_void, c_void, c_size, c_int, c_void]),
-    "fq_gemm_ptqtp_dev": (c_int, [P(c_void), c_int, c_void, c_void, c_size, c_void]),
+    "fq_gemm_quant_nt_dev_noalloc": (c_int, [c_void, c_size, c_void, c_void, c_size, c_void]),
+    "fq_gemm_ptqtp_dev":(c_int, [P(c_void), c_int, c_void, c_void, c_size, c_void]),
     "fq_quantize_acts_q8_k_dev": (c_int, [c_void, c_size, c_size, c_void]),
     "fq_quantize_acts_q8_0_dev": (c_int, [c_void, c_size, c_size, c_void]),
     "fq_capture_begin": (c_int, []),

@@ -166,6 +166,13 @@ Ctx* context() {
     return &g_ctx;
 }
 
+// The context if fq_init (or an earlier entry) already created it; never initialises.
+Ctx* context_if_ready() {
+    if (g_init_state.load(std::memory_order_acquire) != 1) return nullptr;
+    cudaSetDevice(g_ctx.device);
+    return &g_ctx;
+}
+
 // A kernel whose bounded wait gave up leaves its code in the status word; the
 // host reports it at the next synchronisation point and clears it.
 int device_status(Ctx* ctx) {

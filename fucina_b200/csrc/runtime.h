@@ -35,6 +35,7 @@ extern std::recursive_mutex g_dispatch_lock;
 int fail(int code, const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 Ctx* context();
+Ctx* context_if_ready();  // the context only if it already exists; never creates it
 int device_status(Ctx* ctx);  // FQ_OK, or the code a kernel's bounded wait left behind (then cleared)
 void* dev_alloc(size_t n);
 void dev_free(void* p);

@@ -218,6 +218,16 @@ def gemm_quant_nt_dev(w: Weights, a_dev, c_dev, m: int, mat: int = 0, mode: int 
     _check(load().fq_gemm_quant_nt_dev(w.handle, mat, _vp(a_dev), _vp(c_dev), m, mode, C.c_void_p(stream)))
 
 
+def gemm_quant_nt_dev_noalloc(w: Weights, a_dev, c_dev, m: int, mat: int = 0, stream: int = 0) -> None:
+    """Small-batch product for callers that may not allocate device memory while serving.
+
+    Same numbers as `gemm_quant_nt_dev(..., mode=MODE_INT8)` for m <= 16; the activation
+    scratch is a fixed 512 KiB array inside the library, shared by all calls (order
+    them on one stream). Declined when the activation records would not fit.
+    """
+    _check(load().fq_gemm_quant_nt_dev_noalloc(w.handle, mat, _vp(a_dev), _vp(c_dev), m, C.c_void_p(stream)))
+
+
 def gemm_ptqtp_dev(planes: list[Weights], a_dev, c_dev, m: int, stream: int = 0) -> None:
     """K ternary planes summed per element in plane order (src/weights.zig:204-300)."""
     arr = (C.c_void_p * len(planes))(*[p.handle for p in planes])

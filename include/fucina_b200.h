@@ -157,6 +157,21 @@ enum {
 };
 FQ_API int fq_gemm_quant_nt_dev(const fq_weights* w, size_t mat, const float* a_dev, float* c_dev, size_t m, int mode,
                          void* stream);
+/* Allocation-free small-batch product. No counterpart in the reference (its
+ * provider grows device buffers on demand, backend/cuda.zig:873-890). For
+ * hosts that must not allocate device memory once they are serving -- VRAM
+ * fully budgeted at start-up, a decode loop that cannot afford the device-wide
+ * stall of a cudaMalloc, memory owned by an external pool. Same result as
+ * fq_gemm_quant_nt_dev in FQ_MODE_INT8 for m <= 16, but the int8 activation
+ * records live in a fixed 512 KiB array inside the library image instead of
+ * the caching allocator: act bytes per row (about 1.4 * k) times m must fit,
+ * otherwise the call is declined. Every GPU that loads the library holds the
+ * array until exit. All calls share it, so calls that overlap on the GPU
+ * race; order them on one stream. The first call on a device resolves the
+ * array's address: make it before any stream capture. fq_init must have been
+ * called; this entry creates nothing. */
+FQ_API int fq_gemm_quant_nt_dev_noalloc(const fq_weights* w, size_t mat, const float* a_dev, float* c_dev, size_t m,
+                                        void* stream);
 /* K planes of one PTQTP weight summed per element in plane order
  * (weights.zig:204-300 `linearSeqPtqtpFused`). */
 FQ_API int fq_gemm_ptqtp_dev(const fq_weights* const* planes, int n_planes, const float* a_dev, float* c_dev, size_t m,
