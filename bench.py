@@ -380,9 +380,132 @@ def run_profile_case(args) -> dict:
             "avg_kernel_us": round(ms / max(cnt, 1) * 1e3, 2), "GBps": round(nbytes / (ms / max(cnt, 1) * 1e-3) / 1e9, 1)}
 
 
+def _timed(P, torch, fn, steps: int, warmup: int) -> float:
+    """milliseconds per call of fn() on the library stream (CUDA events)."""
+    ext = torch.cuda.ExternalStream(P.stream_ptr())
+    for _ in range(warmup):
+        fn()
+    P.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(ext):
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+    P.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def _dev_weights(P, torch, fmt: int, n: int, k: int, seed: int, n_mats: int = 1):
+    from fucina_b200 import formats as F
+
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    rb = F.row_bytes(fmt, k)
+    blocks = torch.empty(n_mats * n * rb, dtype=torch.uint8, device="cuda")
+    for e in range(n_mats):  # one matrix at a time keeps the f32 staging small
+        w = torch.randn((n, k), generator=g, device="cuda", dtype=torch.float32) * 0.02
+        torch.cuda.synchronize()
+        P.quantize_rows_dev(fmt, w, n, k, blocks[e * n * rb:(e + 1) * n * rb])
+        P.synchronize()
+    return P.Weights.from_device(fmt, blocks, n, k, n_mats)
+
+
+def run_extra(args) -> list[dict]:
+    """The other configurations of the hot path, one JSON line each (information; the
+    driver's headline run is the default workload)."""
+    import torch
+
+    from fucina_b200 import formats as F
+    from fucina_b200 import provider as P
+
+    P.init(0)
+    peak_hbm, _ = measured_peaks()
+    out = []
+    g = torch.Generator(device="cuda").manual_seed(5)
+    if args.workload in ("q8_0", "all"):
+        n = k = 4096
+        copies = [_dev_weights(P, torch, F.Q8_0, n, k, 1000 + i) for i in range(30)]  # 535 MB > 4x L2
+        x = torch.randn((1, k), generator=g, device="cuda")
+        y = torch.empty((1, n), device="cuda")
+        torch.cuda.synchronize()
+        with P.capture() as cap:
+            for w in copies:
+                P.gemm_quant_nt_dev(w, x, y, 1, mode=P.MODE_INT8)
+        ms = _timed(P, torch, cap.graph.launch, max(args.steps // 10, 5), 3) / len(copies)
+        nbytes = n * (k // 32 * 34) + 4 * k + 4 * n
+        out.append({"workload": "Q8_0 GEMV 4096x4096 batch 1 (30 rotated copies)", "us_per_launch": round(ms * 1e3, 3),
+                    "GBps": round(nbytes / ms / 1e6, 1), "frac_of_measured_hbm": round(nbytes / ms / 1e6 / peak_hbm, 4)})
+    if args.workload in ("prefill", "all"):
+        n, k = 14336, 4096
+        w = _dev_weights(P, torch, F.Q4_K, n, k, 1200)
+        for m in (512, 2048):
+            a = torch.randn((m, k), generator=g, device="cuda")
+            c = torch.empty((m, n), device="cuda")
+            torch.cuda.synchronize()
+            ms = _timed(P, torch, lambda: P.gemm_quant_nt_dev(w, a, c, m, mode=P.MODE_TENSOR), max(args.steps // 10, 5), 3)
+            tf = 2.0 * m * n * k / ms / 1e9
+            out.append({"workload": f"Q4_K prefill GEMM {m}x{n}x{k} (bf16 tcgen05, f32 out, f32->bf16 activation pass included)",
+                        "ms": round(ms, 4), "TFLOPS": round(tf, 1), "frac_of_measured_bf16_burst": round(tf / 1621.7, 4),
+                        "frac_of_nominal_2250": round(tf / 2250.0, 4)})
+    if args.workload in ("moe", "all"):
+        hidden, ffn, E, topk = 2048, 768, 128, 8
+        gate = _dev_weights(P, torch, F.Q5_K, ffn, hidden, 1300, E)
+        up = _dev_weights(P, torch, F.Q5_K, ffn, hidden, 1301, E)
+        down = _dev_weights(P, torch, F.Q5_K, hidden, ffn, 1302, E)
+        for T in (1, 8, 64, 1024):
+            x = torch.randn((T, hidden), generator=g, device="cuda")
+            logits = torch.randn((T, E), generator=g, device="cuda")
+            sel = torch.empty((T, topk), dtype=torch.int32, device="cuda")
+            wts = torch.empty((T, topk), device="cuda")
+            o = torch.empty((T, hidden), device="cuda")
+            torch.cuda.synchronize()
+
+            def layer():
+                P.router_topk_dev(logits, T, E, topk, True, sel, wts)
+                P.moe_layer_dev(gate, up, down, x, T, topk, sel, wts, o)
+
+            ms = _timed(P, torch, layer, max(args.steps // 10, 5), 3)
+            out.append({"workload": f"Q5_K MoE layer hidden 2048 ffn 768 128 experts top-8, {T} tokens (router + layer on device)",
+                        "ms": round(ms, 4), "tok_per_s": round(T / ms * 1e3, 1)})
+    if args.workload in ("ternary", "all"):
+        n = k = 8192
+        rng = np.random.default_rng(4000)
+        trits = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+        scales = np.abs(rng.standard_normal((n, k // 256)) * 0.02).astype(np.float32)
+        w = P.Weights.upload(F.TQ2_0, F.pack_ptqtp_plane(trits, scales), n, k)
+        for m in (1, 256):
+            a = torch.randn((m, k), generator=g, device="cuda")
+            c = torch.empty((m, n), device="cuda")
+            torch.cuda.synchronize()
+            ms = _timed(P, torch, lambda: P.gemm_quant_nt_dev(w, a, c, m, mode=P.MODE_INT8), max(args.steps // 10, 5), 3)
+            nbytes = n * (k // 256 * 66) + 4 * m * (k + n)
+            out.append({"workload": f"TQ2_0 (PTQTP plane) {m}x{n}x{k}, int8 path (weights fit L2: warm-L2 figure)", "ms": round(ms, 4),
+                        "GBps": round(nbytes / ms / 1e6, 1), "TFLOPS": round(2.0 * m * n * k / ms / 1e9, 2)})
+    return out
+
+
+def run_profile_tc(args) -> dict:
+    """A small case of the tensor-core prefill kernel for profiler captures: Q4_K 512 x 4096 x 4096."""
+    import torch
+
+    from fucina_b200 import formats as F
+    from fucina_b200 import provider as P
+
+    P.init(0)
+    m, n, k = 512, 4096, 4096
+    w = _dev_weights(P, torch, F.Q4_K, n, k, 91)
+    g = torch.Generator(device="cuda").manual_seed(92)
+    a = torch.randn((m, k), generator=g, device="cuda")
+    c = torch.empty((m, n), device="cuda")
+    torch.cuda.synchronize()
+    ms = _timed(P, torch, lambda: P.gemm_quant_nt_dev(w, a, c, m, mode=P.MODE_TENSOR), args.steps, args.warmup)
+    return {"workload": f"profile case: Q4_K prefill {m}x{n}x{k} tcgen05", "ms": round(ms, 4),
+            "TFLOPS": round(2.0 * m * n * k / ms / 1e9, 1)}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="stack", choices=["stack", "profile"])
+    ap.add_argument("--workload", default="stack", choices=["stack", "profile", "profile_tc", "q8_0", "prefill", "moe", "ternary", "all"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
@@ -392,6 +515,13 @@ def main() -> None:
     args.warmup = max(args.warmup, 3)
     if args.workload == "profile":
         print(json.dumps(run_profile_case(args)), flush=True)
+        return
+    if args.workload == "profile_tc":
+        print(json.dumps(run_profile_tc(args)), flush=True)
+        return
+    if args.workload != "stack":
+        for line in run_extra(args):
+            print(json.dumps(line), flush=True)
         return
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out:

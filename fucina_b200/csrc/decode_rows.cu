@@ -441,7 +441,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) decode_rows_kernel(const RowsAr
         }
     }
     if (!ok) {
-        if (lane == 0) atomicExch(A.status, FQ_ERR_TIMEOUT);
+        if (lane == 0) *(volatile int*)A.status = FQ_ERR_TIMEOUT;
         // give copies still in flight a bounded chance to land before the CTA's shared memory is released
         for (int s = 0; s < A.stages; ++s) mbar_wait(bar0 + s * 8, 0);
     }
@@ -459,17 +459,18 @@ size_t smem_bytes(int fmt, int k, int mb, int slab, int stages, int warps) {
 
 // 16 warps per CTA double the thread-level parallelism that hides shared-memory and dp4a latency;
 // they need 16 units per row to split and the register budget of the small-batch variants.
-int pick_warps(int k, int mb) {
+int pick_warps(int fmt, int k, int mb) {
     static const int forced = getenv("FUCINA_B200_DECODE_WARPS") ? atoi(getenv("FUCINA_B200_DECODE_WARPS")) : 0;
     if (forced == 8) return 8;
-    return (k / 256 >= 16 && mb <= 2) ? 16 : 8;
+    if (k / 256 < 16 || mb > 2) return 8;
+    return smem_bytes(fmt, k, mb, 1, 2, 16) <= 227 * 1024 ? 16 : 8;  // the smallest 16-warp ring must fit
 }
 
 int pad_rows(size_t m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
 
 // deepest pipeline that fits: more bytes in flight per SM first, then fewer barriers per byte
 bool pick_config(int fmt, int k, int mb, int* slab, int* stages) {
-    const int warps = pick_warps(k, mb);
+    const int warps = pick_warps(fmt, k, mb);
     static const int cand[][2] = {{1, 4}, {2, 2}, {1, 3}, {1, 2}};
     static int force_slab = -1, force_stages = -1;
     if (force_slab < 0) {
@@ -526,7 +527,7 @@ bool make_weight_tmap(const DevWeights& w, int mat, int unit_bytes, CUtensorMap*
 template <int FMT, int MB>
 cudaError_t launch_fmt_mb(const RowsArgs& a, const CUtensorMap& tmap, bool fused, int grid, size_t smem, cudaStream_t st) {
     constexpr bool kWide = MB <= 2;  // the 16-warp form exists for the small-batch variants only
-    const bool wide = kWide && pick_warps(a.w.k, MB) == 16;
+    const bool wide = kWide && pick_warps(FMT, a.w.k, MB) == 16;
     void (*kern)(const RowsArgs, const CUtensorMap) =
         wide ? (fused ? decode_rows_kernel<FMT, MB, true, kWide ? 16 : 8> : decode_rows_kernel<FMT, MB, false, kWide ? 16 : 8>)
              : (fused ? decode_rows_kernel<FMT, MB, true, 8> : decode_rows_kernel<FMT, MB, false, 8>);
@@ -598,7 +599,7 @@ cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev,
     }
     int grid = sm_count;
     if (grid > (w.n + 7) / 8) grid = (w.n + 7) / 8;
-    const size_t smem = smem_bytes(w.fmt, w.k, mb, a.slab, a.stages, pick_warps(w.k, mb));
+    const size_t smem = smem_bytes(w.fmt, w.k, mb, a.slab, a.stages, pick_warps(w.fmt, w.k, mb));
     switch (w.fmt) {
         case FQ_Q4_K: return launch_fmt<FQ_Q4_K>(a, tmap, mb, fused, grid, smem, st);
         case FQ_Q5_K: return launch_fmt<FQ_Q5_K>(a, tmap, mb, fused, grid, smem, st);

@@ -1,13 +1,450 @@
-// Prefill-shaped quantized GEMM on the 5th-generation tensor cores (tcgen05,
-// accumulators in TMEM). Placeholder translation unit: until the kernel lands
-// every shape is declined and callers use the integer decode kernel.
+// Prefill-shaped quantized GEMM on the 5th-generation tensor cores.
+//
+// c[t, j] = sum_e bf16(a[t, e]) * bf16(dequant(W)[j, e]), f32 accumulate, for
+// m > 16 token rows (reference role: fucina_mul_mm_mma_*, src/backend/cuda/
+// kernels.cu:302-427, which rounds both operands to f16 and uses wmma). The
+// dequantised f32 weight is computed with the CPU decoders' unfused formula
+// (q4_k.zig:1954-1972, q5_k.zig:1154-1167, q8k.zig:95-114) and rounded once to
+// bf16, so the operands equal those of the f64 reference over bf16-rounded
+// operands; results differ from it only by f32 accumulation.
+//
+// One persistent CTA per SM walks output tiles of 128 weight rows x 256 tokens.
+//   warp 0        TMA producer: 256 x 64 bf16 token tiles (128-byte swizzle) into a 4-stage ring
+//   warp 1        one thread issues tcgen05.mma (M=128 weight rows, N=256 tokens, K=16 per
+//                 instruction, bf16 x bf16 -> f32) with shared-memory descriptors; the accumulator
+//                 lives in 256 TMEM columns; tcgen05.commit releases ring stages and signals the epilogue
+//   warps 2..9    dequantise: two threads per weight row expand 64 weights of the current K slab
+//                 into the 128-byte-swizzled K-major A tile; after the last slab the same warps
+//                 read the accumulator with tcgen05.ld and store f32 results (coalesced along n)
+// Every mbarrier wait is bounded and also watches a CTA-wide abort flag; a wait that gives up sets
+// FQ_ERR_TIMEOUT in the status word, all roles fall through to the common exit, TMEM is freed.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstdlib>
+#include <cstring>
+
 #include "internal.h"
 #include "runtime.h"
 
 namespace fq {
 
-int gemm_tensor_dev(Ctx*, const DevWeights&, int, const float*, float*, size_t, size_t, cudaStream_t) {
-    return fail(FQ_DECLINED_ARGS, "tensor-core path not built");
+namespace {
+
+constexpr int BM = 128;        // weight rows per tile (UMMA M)
+constexpr int BN = 256;        // tokens per tile (UMMA N)
+constexpr int BK = 64;         // K elements per ring stage (128 bytes of bf16: one swizzle span)
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_BYTES = BN * BK * 2;   // 32 KB
+constexpr int kDequantWarps = 8;
+constexpr int kThreads = (2 + kDequantWarps) * 32;  // 320
+constexpr unsigned kWaitLimit = 1u << 20;
+constexpr int TMEM_COLS = 256;
+
+struct TcArgs {
+    DevWeights w;
+    int mat;
+    float* c;
+    int m;    // tokens
+    int ldc;
+    int* status;
+};
+
+struct __align__(8) Barriers {
+    uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES], tmem_full, tmem_empty;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait that also gives up when another role aborted. Returns false on abort/timeout.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Barriers* B, int* status) {
+    for (unsigned i = 0; i < kWaitLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (B->abort_flag) return false;
+    }
+    B->abort_flag = 1;
+    *(volatile int*)status = FQ_ERR_TIMEOUT;  // mapped host word: a plain store, device atomics on host memory are not portable
+    return false;
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, 8-row groups
+// 1024 bytes apart (stride byte offset), tile base 1024-byte aligned.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);       // start address
+    d |= (uint64_t)1 << 16;                             // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset
+    d |= (uint64_t)1 << 46;                             // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor, kind::f16: D = f32, A = B = bf16, both K-major, M = 128, N = 256.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// ---- 32 dequantised weights of one row as bf16 pairs -------------------------------------------
+// half h of the 64-element K slab `ks` (k0 = 64*ks) of weight row `row`; out[16] holds 32 bf16.
+template <int FMT>
+__device__ __forceinline__ void dequant32(const DevWeights& w, const uint8_t* unit0, size_t ustride, int ks, int h, uint32_t out[16]);
+
+template <>
+__device__ __forceinline__ void dequant32<FQ_Q4_K>(const DevWeights&, const uint8_t* unit0, size_t ustride, int ks, int h, uint32_t out[16]) {
+    const uint8_t* b = unit0 + (size_t)(ks >> 2) * ustride;
+    const int p = ks & 3, s = 2 * p + h;
+    const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(b));
+    const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(b + 16 + p * 32)), q1 = __ldg(reinterpret_cast<const uint4*>(b + 32 + p * 32));
+    const __half2 dm = *reinterpret_cast<const __half2*>(&hdr.x);
+    const uint8_t* sb = reinterpret_cast<const uint8_t*>(&hdr.y);
+    int sc, mn;
+    if (s < 4) {
+        sc = sb[s] & 63;
+        mn = sb[s + 4] & 63;
+    } else {
+        sc = (sb[s + 4] & 0x0f) | ((sb[s - 4] >> 6) << 4);
+        mn = (sb[s + 4] >> 4) | ((sb[s] >> 6) << 4);
+    }
+    const float dsc = __fmul_rn(__low2float(dm), (float)sc), off = __fmul_rn(__high2float(dm), (float)mn);
+    const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t v = h ? (wq[j] >> 4) : wq[j];
+        float f[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = __fsub_rn(__fmul_rn(dsc, (float)((v >> (8 * i)) & 15u)), off);
+        out[2 * j] = pack_bf16(f[0], f[1]);
+        out[2 * j + 1] = pack_bf16(f[2], f[3]);
+    }
+}
+
+template <>
+__device__ __forceinline__ void dequant32<FQ_Q5_K>(const DevWeights&, const uint8_t* unit0, size_t ustride, int ks, int h, uint32_t out[16]) {
+    const uint8_t* b = unit0 + (size_t)(ks >> 2) * ustride;
+    const int p = ks & 3, s = 2 * p + h;
+    const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(b));
+    const uint4 h0 = __ldg(reinterpret_cast<const uint4*>(b + 16)), h1 = __ldg(reinterpret_cast<const uint4*>(b + 32));
+    const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(b + 48 + p * 32)), q1 = __ldg(reinterpret_cast<const uint4*>(b + 64 + p * 32));
+    const __half2 dm = *reinterpret_cast<const __half2*>(&hdr.x);
+    const uint8_t* sb = reinterpret_cast<const uint8_t*>(&hdr.y);
+    int sc, mn;
+    if (s < 4) {
+        sc = sb[s] & 63;
+        mn = sb[s + 4] & 63;
+    } else {
+        sc = (sb[s + 4] & 0x0f) | ((sb[s - 4] >> 6) << 4);
+        mn = (sb[s + 4] >> 4) | ((sb[s] >> 6) << 4);
+    }
+    const float dsc = __fmul_rn(__low2float(dm), (float)sc), off = __fmul_rn(__high2float(dm), (float)mn);
+    const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const uint32_t hb[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t v = h ? (wq[j] >> 4) : wq[j];
+        const uint32_t hi = (hb[j] >> s) & 0x01010101u;
+        float f[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t q = ((v >> (8 * i)) & 15u) + (((hi >> (8 * i)) & 1u) << 4);
+            f[i] = __fsub_rn(__fmul_rn(dsc, (float)q), off);
+        }
+        out[2 * j] = pack_bf16(f[0], f[1]);
+        out[2 * j + 1] = pack_bf16(f[2], f[3]);
+    }
+}
+
+template <>
+__device__ __forceinline__ void dequant32<FQ_Q8_0>(const DevWeights& w, const uint8_t* unit0, size_t, int ks, int h, uint32_t out[16]) {
+    // row = [qs: K int8][d: K/32 f16]; one 32-weight block per call
+    const int blk = ks * 2 + h;
+    const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(unit0 + (size_t)blk * 32)), q1 = __ldg(reinterpret_cast<const uint4*>(unit0 + (size_t)blk * 32 + 16));
+    const float d = h2f(__ldg(reinterpret_cast<const uint16_t*>(unit0 + w.k) + blk));
+    const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float f[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = __fmul_rn((float)(int8_t)((wq[j] >> (8 * i)) & 0xffu), d);
+        out[2 * j] = pack_bf16(f[0], f[1]);
+        out[2 * j + 1] = pack_bf16(f[2], f[3]);
+    }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, const __grid_constant__ CUtensorMap tmap_tokens) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // 1024-byte aligned ring: [A stages][B stages][barriers]
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_BYTES;
+    Barriers* B = reinterpret_cast<Barriers*>(smem + STAGES * (A_BYTES + B_BYTES));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = A.w.n, k = A.w.k, m = A.m;
+    const int kslabs = k / BK;
+    const int row_tiles = (n + BM - 1) / BM, tok_tiles = (m + BN - 1) / BN;
+    const int n_tiles = row_tiles * tok_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&B->full_a[s]), kDequantWarps * 32);
+            mbar_init(smem_u32(&B->full_b[s]), 1);
+            mbar_init(smem_u32(&B->empty[s]), 1);
+        }
+        mbar_init(smem_u32(&B->tmem_full), 1);
+        mbar_init(smem_u32(&B->tmem_empty), kDequantWarps * 32);
+        B->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        // TMEM allocation by one full warp; the base address lands in shared memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&B->tmem_base)), "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = B->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer: token tiles ----------------
+        if (lane == 0) {
+            int g = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x) {
+                const int tt = tile / row_tiles;  // consecutive CTAs share the token tile (L2 reuse) and take different weight rows
+                for (int ks = 0; ks < kslabs; ++ks, ++g) {
+                    const int s = g % STAGES;
+                    if (!mbar_wait(smem_u32(&B->empty[s]), ((g / STAGES) & 1) ^ 1, B, A.status)) break;
+                    const uint32_t bar = smem_u32(&B->full_b[s]);
+                    mbar_arrive_expect_tx(bar, B_BYTES);
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                            smem_u32(sB + s * B_BYTES)),
+                        "l"(&tmap_tokens), "r"(ks * BK), "r"(tt * BN), "r"(bar)
+                        : "memory");
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int g = 0, t = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
+                // the epilogue of the previous tile must have drained the accumulator
+                if (!mbar_wait(smem_u32(&B->tmem_empty), (t & 1) ^ 1, B, A.status)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                bool ok = true;
+                for (int ks = 0; ks < kslabs; ++ks, ++g) {
+                    const int s = g % STAGES;
+                    const uint32_t ph = (g / STAGES) & 1;
+                    if (!mbar_wait(smem_u32(&B->full_a[s]), ph, B, A.status) || !mbar_wait(smem_u32(&B->full_b[s]), ph, B, A.status)) {
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = umma_desc(smem_u32(sA + s * A_BYTES)), db = umma_desc(smem_u32(sB + s * B_BYTES));
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk)  // 32 bytes along K per instruction: +2 in the 16-byte address field
+                        umma_bf16(tmem, da + 2 * kk, db + 2 * kk, (ks | kk) ? 1u : 0u);
+                    umma_commit(smem_u32(&B->empty[s]));  // the stage is free once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&B->tmem_full));
+            }
+        }
+    } else {
+        // ---------------- dequantise, then epilogue ----------------
+        const int dt = threadIdx.x - 64;   // 0..255
+        const int r = dt & (BM - 1);       // weight row inside the tile
+        const int h = dt >> 7;             // which 32-weight half of the 64-element slab
+        const int ew = warp - 2;           // epilogue: lane quarter = warp % 4, column half = ew / 4
+        const uint8_t* wbase = A.w.base + (size_t)A.mat * A.w.mat_stride;
+        constexpr int ub = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 256;
+        const size_t ustride = unit_stride(A.w, ub);
+        int g = 0, t = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
+            const int rt = tile % row_tiles, tt = tile / row_tiles;
+            const int row = min(rt * BM + r, n - 1);
+            const uint8_t* unit0 = row_unit0(A.w, wbase, row, ub);
+            bool ok = true;
+            for (int ks = 0; ks < kslabs; ++ks, ++g) {
+                const int s = g % STAGES;
+                uint32_t v[16];
+                dequant32<FMT>(A.w, unit0, ustride, ks, h, v);  // global loads and arithmetic overlap the wait below
+                if (!mbar_wait(smem_u32(&B->empty[s]), ((g / STAGES) & 1) ^ 1, B, A.status)) {
+                    ok = false;
+                    break;
+                }
+                // row r of the K-major tile: 128 bytes, 16-byte chunk j stored at j ^ (r % 8) (128-byte swizzle)
+                uint8_t* rowp = sA + s * A_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int chunk = (h * 4 + j) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA's async proxy
+                mbar_arrive(smem_u32(&B->full_a[s]));
+            }
+            if (!ok) break;
+            // epilogue: accumulator lane = weight row, column = token
+            if (!mbar_wait(smem_u32(&B->tmem_full), t & 1, B, A.status)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int q = warp & 3;                       // TMEM lane quarter this warp may read
+            const int out_row = rt * BM + q * 32 + lane;  // weight row = output column
+            for (int c0 = (ew >> 2) * (BN / 2); c0 < (ew >> 2) * (BN / 2) + BN / 2; c0 += 32) {
+                uint32_t acc[32];
+                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]), "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7]),
+                      "=r"(acc[8]), "=r"(acc[9]), "=r"(acc[10]), "=r"(acc[11]), "=r"(acc[12]), "=r"(acc[13]), "=r"(acc[14]), "=r"(acc[15]),
+                      "=r"(acc[16]), "=r"(acc[17]), "=r"(acc[18]), "=r"(acc[19]), "=r"(acc[20]), "=r"(acc[21]), "=r"(acc[22]), "=r"(acc[23]),
+                      "=r"(acc[24]), "=r"(acc[25]), "=r"(acc[26]), "=r"(acc[27]), "=r"(acc[28]), "=r"(acc[29]), "=r"(acc[30]), "=r"(acc[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (out_row < n) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int tok = tt * BN + c0 + j;
+                        if (tok < m) A.c[(size_t)tok * A.ldc + out_row] = __uint_as_float(acc[j]);
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(smem_u32(&B->tmem_empty));
+        }
+    }
+
+    // common exit: everyone meets here (also after an abort), then the allocating warp frees TMEM
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
+    for (size_t i = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(src + i);
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst + i) = o;
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+        cudaGetLastError();
+    }
+    return fn;
+}
+
+template <int FMT>
+cudaError_t launch_tc(const TcArgs& a, const CUtensorMap& tmap, int grid, cudaStream_t st) {
+    const size_t smem = (size_t)STAGES * (A_BYTES + B_BYTES) + sizeof(Barriers) + 1024;
+    static bool granted = false;
+    if (!granted) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        granted = true;
+    }
+    gemm_tc_kernel<FMT><<<grid, kThreads, smem, st>>>(a, tmap);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, cudaStream_t st) {
+    if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q8_0) return fail(FQ_DECLINED_ARGS, "tensor-core path serves Q4_K, Q5_K and Q8_0");
+    if (w.k % 256 != 0 || m < 1 || m > (size_t)1 << 24) return fail(FQ_DECLINED_ARGS, "tensor-core path needs k %% 256 == 0");
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(FQ_DECLINED_ARGS, "cuTensorMapEncodeTiled unavailable");
+    // bf16 copy of the activations: [m][k], read by TMA with a 128-byte swizzle
+    __nv_bfloat16* abf = (__nv_bfloat16*)dev_alloc(m * (size_t)w.k * 2);
+    if (!abf) return fail(FQ_DECLINED_BUDGET, "bf16 activation scratch allocation failed");
+    const size_t total = m * (size_t)w.k;
+    int blocks = (int)((total / 4 + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    f32_to_bf16_kernel<<<blocks, 256, 0, st>>>(a_dev, abf, total);
+    CUtensorMap tmap;
+    memset(&tmap, 0, sizeof tmap);
+    const cuuint64_t dims[2] = {(cuuint64_t)w.k, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)w.k * 2};
+    const cuuint32_t box[2] = {BK, BN};
+    const cuuint32_t estr[2] = {1, 1};
+    int rc = FQ_OK;
+    if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, abf, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        rc = fail(FQ_DECLINED_ARGS, "tensor map for the activations could not be encoded");
+    if (rc == FQ_OK) {
+        TcArgs a{w, mat, c_dev, (int)m, (int)ldc, ctx->status_dev};
+        const int tiles = ((w.n + BM - 1) / BM) * (int)((m + BN - 1) / BN);
+        const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+        cudaError_t e;
+        switch (w.fmt) {
+            case FQ_Q4_K: e = launch_tc<FQ_Q4_K>(a, tmap, grid, st); break;
+            case FQ_Q5_K: e = launch_tc<FQ_Q5_K>(a, tmap, grid, st); break;
+            default: e = launch_tc<FQ_Q8_0>(a, tmap, grid, st); break;
+        }
+        g_trace.launches += 2;
+        if (e != cudaSuccess) rc = cuda_fail(e, "tensor-core GEMM launch");
+    }
+    if (st != ctx->stream) cudaStreamSynchronize(st);
+    dev_free(abf);
+    return rc;
 }
 
 }  // namespace fq

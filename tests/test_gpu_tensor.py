@@ -1,0 +1,79 @@
+"""GPU parity, part 4: the bf16 tensor-core (tcgen05) prefill path against Oracle B --
+an f64 dot over the oracle-dequantised weights with both operands rounded to bf16,
+the reference's own GPU-test oracle (src/backend/cuda.zig:3016-3044) at this
+build's operand precision. Tolerance: max relative error 1e-2, as the target states."""
+import numpy as np
+import pytest
+
+import oracle
+from parity import TOL_TENSOR, assert_close, make_weights
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def P():
+    from fucina_b200 import provider
+
+    provider.init(0)
+    return provider
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+
+    return torch
+
+
+def run_tensor(P, torch, fmt, blocks, a, n, mode=None):
+    m, k = a.shape
+    w = P.Weights.upload(fmt, blocks, n, k)
+    ad = torch.from_numpy(a).cuda()
+    cd = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    P.gemm_quant_nt_dev(w, ad, cd, m, mode=P.MODE_TENSOR if mode is None else mode)
+    P.synchronize()
+    w.free()
+    return cd.cpu().numpy()
+
+
+@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q8_0"])
+@pytest.mark.parametrize("m,n,k", [
+    (64, 128, 256),      # one tile, one block of K
+    (33, 96, 512),       # the reference's ragged parity shape (cuda.zig:3084-3088): partial rows and tokens
+    (300, 388, 1024),    # two token tiles, four row tiles, ragged on both sides
+    (512, 1024, 4096),   # prefill width
+])
+def test_tensor_path_matches_bf16_oracle(P, torch, fmt_name, m, n, k):
+    fmt = oracle.FORMATS[fmt_name]
+    blocks = make_weights(fmt_name, n, k, seed=2000 + n)
+    a = np.random.default_rng(2100 + m).standard_normal((m, k)).astype(np.float32)
+    got = run_tensor(P, torch, fmt, blocks, a, n)
+    want = oracle.matmul_dequant_f64(fmt, blocks, a, round_bf16=True)
+    err = assert_close(got, want, TOL_TENSOR, f"{fmt_name} {m}x{n}x{k}")
+    assert err < 1e-3  # f32 accumulation over identical bf16 operands is far inside the bound
+
+
+def test_auto_mode_routes_large_m_to_tensor_cores(P, torch):
+    n, k, m = 256, 1024, 96
+    blocks = make_weights("q4_k", n, k, seed=2200)
+    a = np.random.default_rng(2201).standard_normal((m, k)).astype(np.float32)
+    auto = run_tensor(P, torch, oracle.Q4_K, blocks, a, n, mode=P.MODE_AUTO)
+    tens = run_tensor(P, torch, oracle.Q4_K, blocks, a, n)
+    assert np.array_equal(auto.view(np.uint32), tens.view(np.uint32))
+    # and it stays close to the CPU kernels' int8 result (information: activation quantisation noise,
+    # measured at matrix level because near-zero outputs have no meaningful relative error)
+    want = oracle.matmul(oracle.Q4_K, blocks, a)
+    assert float(np.max(np.abs(tens - want)) / np.max(np.abs(want))) < 5e-2
+
+
+def test_formats_without_a_tensor_kernel_are_declined_in_tensor_mode(P, torch):
+    n, k, m = 64, 512, 32
+    blocks = make_weights("tq2_0", n, k, seed=2300)
+    a = np.zeros((m, k), np.float32)
+    with pytest.raises(P.Declined):
+        run_tensor(P, torch, oracle.TQ2_0, blocks, a, n)
+    # AUTO falls back to the integer kernel in 16-row passes
+    got = run_tensor(P, torch, oracle.TQ2_0, blocks, a + 1.0, n, mode=P.MODE_AUTO)
+    assert_close(got, oracle.matmul(oracle.TQ2_0, blocks, a + 1.0), 1e-3, "tq2_0 auto")
