@@ -120,91 +120,121 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// ---- 32 dequantised weights of one row as bf16 pairs -------------------------------------------
-// half h of the 64-element K slab `ks` (k0 = 64*ks) of weight row `row`; out[16] holds 32 bf16.
+// ---- packed weights of one 64-element K slab of one row: loaded one slab ahead, expanded later ----
 template <int FMT>
-__device__ __forceinline__ void dequant32(const DevWeights& w, const uint8_t* unit0, size_t ustride, int ks, int h, uint32_t out[16]);
+struct Raw;
 
-template <>
-__device__ __forceinline__ void dequant32<FQ_Q4_K>(const DevWeights&, const uint8_t* unit0, size_t ustride, int ks, int h, uint32_t out[16]) {
-    const uint8_t* b = unit0 + (size_t)(ks >> 2) * ustride;
-    const int p = ks & 3, s = 2 * p + h;
-    const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(b));
-    const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(b + 16 + p * 32)), q1 = __ldg(reinterpret_cast<const uint4*>(b + 32 + p * 32));
-    const __half2 dm = *reinterpret_cast<const __half2*>(&hdr.x);
-    const uint8_t* sb = reinterpret_cast<const uint8_t*>(&hdr.y);
-    int sc, mn;
+__device__ __forceinline__ void scale_min(const uint4& hdr, int s, int& sc, int& mn) {
+    // K-quant 6-bit pair s from the 12 scale bytes in hdr.y/z/w (reference backend/quant/q8k.zig:637-648)
+    const uint32_t s0 = hdr.y, s1 = hdr.z, s2 = hdr.w;
     if (s < 4) {
-        sc = sb[s] & 63;
-        mn = sb[s + 4] & 63;
+        sc = (s0 >> (8 * s)) & 63;
+        mn = (s1 >> (8 * s)) & 63;
     } else {
-        sc = (sb[s + 4] & 0x0f) | ((sb[s - 4] >> 6) << 4);
-        mn = (sb[s + 4] >> 4) | ((sb[s] >> 6) << 4);
-    }
-    const float dsc = __fmul_rn(__low2float(dm), (float)sc), off = __fmul_rn(__high2float(dm), (float)mn);
-    const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const uint32_t v = h ? (wq[j] >> 4) : wq[j];
-        float f[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) f[i] = __fsub_rn(__fmul_rn(dsc, (float)((v >> (8 * i)) & 15u)), off);
-        out[2 * j] = pack_bf16(f[0], f[1]);
-        out[2 * j + 1] = pack_bf16(f[2], f[3]);
+        const int j = 8 * (s - 4);
+        sc = ((s2 >> j) & 0xf) | (((s0 >> (j + 6)) & 3) << 4);
+        mn = ((s2 >> (j + 4)) & 0xf) | (((s1 >> (j + 6)) & 3) << 4);
     }
 }
 
 template <>
-__device__ __forceinline__ void dequant32<FQ_Q5_K>(const DevWeights&, const uint8_t* unit0, size_t ustride, int ks, int h, uint32_t out[16]) {
-    const uint8_t* b = unit0 + (size_t)(ks >> 2) * ustride;
-    const int p = ks & 3, s = 2 * p + h;
-    const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(b));
-    const uint4 h0 = __ldg(reinterpret_cast<const uint4*>(b + 16)), h1 = __ldg(reinterpret_cast<const uint4*>(b + 32));
-    const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(b + 48 + p * 32)), q1 = __ldg(reinterpret_cast<const uint4*>(b + 64 + p * 32));
-    const __half2 dm = *reinterpret_cast<const __half2*>(&hdr.x);
-    const uint8_t* sb = reinterpret_cast<const uint8_t*>(&hdr.y);
-    int sc, mn;
-    if (s < 4) {
-        sc = sb[s] & 63;
-        mn = sb[s + 4] & 63;
-    } else {
-        sc = (sb[s + 4] & 0x0f) | ((sb[s - 4] >> 6) << 4);
-        mn = (sb[s + 4] >> 4) | ((sb[s] >> 6) << 4);
-    }
-    const float dsc = __fmul_rn(__low2float(dm), (float)sc), off = __fmul_rn(__high2float(dm), (float)mn);
-    const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-    const uint32_t hb[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const uint32_t v = h ? (wq[j] >> 4) : wq[j];
-        const uint32_t hi = (hb[j] >> s) & 0x01010101u;
-        float f[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t q = ((v >> (8 * i)) & 15u) + (((hi >> (8 * i)) & 1u) << 4);
-            f[i] = __fsub_rn(__fmul_rn(dsc, (float)q), off);
+struct Raw<FQ_Q4_K> {
+    uint4 hdr, q0, q1;
+    __device__ __forceinline__ void load(const DevWeights& w, const uint8_t* unit0, size_t ustride, int ks, int) {
+        const uint8_t* b = unit0 + (size_t)(ks >> 2) * ustride;
+        const int p = ks & 3;
+        hdr = __ldg(reinterpret_cast<const uint4*>(b));
+        q0 = __ldg(reinterpret_cast<const uint4*>(b + 16 + p * 32));
+        q1 = __ldg(reinterpret_cast<const uint4*>(b + 32 + p * 32));
+        if (p == 0 && (ks >> 2) + 1 < (w.k >> 8)) {  // pull the next block of this row towards the SM while this one is consumed
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(b + ustride));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(b + ustride + 128));
         }
-        out[2 * j] = pack_bf16(f[0], f[1]);
-        out[2 * j + 1] = pack_bf16(f[2], f[3]);
     }
-}
+    // d*sc*q - dmin*mn, unfused, rounded once to bf16 (q4_k.zig:1954-1972)
+    __device__ __forceinline__ void expand(int ks, int h, uint32_t out[16]) const {
+        const int s = 2 * (ks & 3) + h;
+        const __half2 dm = *reinterpret_cast<const __half2*>(&hdr.x);
+        int sc, mn;
+        scale_min(hdr, s, sc, mn);
+        const float dsc = __fmul_rn(__low2float(dm), (float)sc), off = __fmul_rn(__high2float(dm), (float)mn);
+        const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t v = h ? (wq[j] >> 4) : wq[j];
+            float f[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) f[i] = __fsub_rn(__fmul_rn(dsc, (float)((v >> (8 * i)) & 15u)), off);
+            out[2 * j] = pack_bf16(f[0], f[1]);
+            out[2 * j + 1] = pack_bf16(f[2], f[3]);
+        }
+    }
+};
 
 template <>
-__device__ __forceinline__ void dequant32<FQ_Q8_0>(const DevWeights& w, const uint8_t* unit0, size_t, int ks, int h, uint32_t out[16]) {
-    // row = [qs: K int8][d: K/32 f16]; one 32-weight block per call
-    const int blk = ks * 2 + h;
-    const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(unit0 + (size_t)blk * 32)), q1 = __ldg(reinterpret_cast<const uint4*>(unit0 + (size_t)blk * 32 + 16));
-    const float d = h2f(__ldg(reinterpret_cast<const uint16_t*>(unit0 + w.k) + blk));
-    const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        float f[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) f[i] = __fmul_rn((float)(int8_t)((wq[j] >> (8 * i)) & 0xffu), d);
-        out[2 * j] = pack_bf16(f[0], f[1]);
-        out[2 * j + 1] = pack_bf16(f[2], f[3]);
+struct Raw<FQ_Q5_K> {
+    uint4 hdr, h0, h1, q0, q1;
+    __device__ __forceinline__ void load(const DevWeights& w, const uint8_t* unit0, size_t ustride, int ks, int) {
+        const uint8_t* b = unit0 + (size_t)(ks >> 2) * ustride;
+        const int p = ks & 3;
+        hdr = __ldg(reinterpret_cast<const uint4*>(b));
+        h0 = __ldg(reinterpret_cast<const uint4*>(b + 16));
+        h1 = __ldg(reinterpret_cast<const uint4*>(b + 32));
+        q0 = __ldg(reinterpret_cast<const uint4*>(b + 48 + p * 32));
+        q1 = __ldg(reinterpret_cast<const uint4*>(b + 64 + p * 32));
+        if (p == 0 && (ks >> 2) + 1 < (w.k >> 8)) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(b + ustride));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(b + ustride + 128));
+        }
     }
-}
+    // as Q4_K with q = nibble + 16 * bit s of qh[i] (q5_k.zig:1154-1167, :1259-1264)
+    __device__ __forceinline__ void expand(int ks, int h, uint32_t out[16]) const {
+        const int s = 2 * (ks & 3) + h;
+        const __half2 dm = *reinterpret_cast<const __half2*>(&hdr.x);
+        int sc, mn;
+        scale_min(hdr, s, sc, mn);
+        const float dsc = __fmul_rn(__low2float(dm), (float)sc), off = __fmul_rn(__high2float(dm), (float)mn);
+        const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint32_t hb[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t v = h ? (wq[j] >> 4) : wq[j];
+            const uint32_t hi = (hb[j] >> s) & 0x01010101u;
+            float f[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t q = ((v >> (8 * i)) & 15u) + (((hi >> (8 * i)) & 1u) << 4);
+                f[i] = __fsub_rn(__fmul_rn(dsc, (float)q), off);
+            }
+            out[2 * j] = pack_bf16(f[0], f[1]);
+            out[2 * j + 1] = pack_bf16(f[2], f[3]);
+        }
+    }
+};
+
+template <>
+struct Raw<FQ_Q8_0> {
+    uint4 q0, q1;
+    float d;
+    // row = [qs: K int8][d: K/32 f16]; one 32-weight block per (slab, half)
+    __device__ __forceinline__ void load(const DevWeights& w, const uint8_t* unit0, size_t, int ks, int h) {
+        const int blk = ks * 2 + h;
+        q0 = __ldg(reinterpret_cast<const uint4*>(unit0 + (size_t)blk * 32));
+        q1 = __ldg(reinterpret_cast<const uint4*>(unit0 + (size_t)blk * 32 + 16));
+        d = h2f(__ldg(reinterpret_cast<const uint16_t*>(unit0 + w.k) + blk));
+    }
+    __device__ __forceinline__ void expand(int, int, uint32_t out[16]) const {  // f32(q) * d (q8k.zig:95-114)
+        const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float f[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) f[i] = __fmul_rn((float)(int8_t)((wq[j] >> (8 * i)) & 0xffu), d);
+            out[2 * j] = pack_bf16(f[0], f[1]);
+            out[2 * j + 1] = pack_bf16(f[2], f[3]);
+        }
+    }
+};
 
 template <int FMT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, const __grid_constant__ CUtensorMap tmap_tokens) {
@@ -303,10 +333,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             const int row = min(rt * BM + r, n - 1);
             const uint8_t* unit0 = row_unit0(A.w, wbase, row, ub);
             bool ok = true;
+            Raw<FMT> next;
+            next.load(A.w, unit0, ustride, 0, h);
             for (int ks = 0; ks < kslabs; ++ks, ++g) {
                 const int s = g % STAGES;
+                const Raw<FMT> cur = next;
+                if (ks + 1 < kslabs) next.load(A.w, unit0, ustride, ks + 1, h);  // one slab ahead: the loads fly while this slab is expanded
                 uint32_t v[16];
-                dequant32<FMT>(A.w, unit0, ustride, ks, h, v);  // global loads and arithmetic overlap the wait below
+                cur.expand(ks, h, v);
                 if (!mbar_wait(smem_u32(&B->empty[s]), ((g / STAGES) & 1) ^ 1, B, A.status)) {
                     ok = false;
                     break;
