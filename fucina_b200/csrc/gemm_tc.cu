@@ -14,8 +14,10 @@
 //                 instruction, bf16 x bf16 -> f32) with shared-memory descriptors; the accumulator
 //                 lives in 256 TMEM columns; tcgen05.commit releases ring stages and signals the epilogue
 //   warps 2..9    dequantise: two threads per weight row expand 64 weights of the current K slab
-//                 into the 128-byte-swizzled K-major A tile; after the last slab the same warps
-//                 read the accumulator with tcgen05.ld and store f32 results (coalesced along n)
+//                 into the 128-byte-swizzled K-major A tile
+//   warps 10..13  epilogue: read the finished accumulator with tcgen05.ld and store f32 results
+//                 (coalesced along n) while the other roles already work on the next tile (the
+//                 accumulator is double-buffered in 2 x 256 TMEM columns)
 // Every mbarrier wait is bounded and also watches a CTA-wide abort flag; a wait that gives up sets
 // FQ_ERR_TIMEOUT in the status word, all roles fall through to the common exit, TMEM is freed.
 #include <cuda.h>
@@ -38,9 +40,10 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_BYTES = BN * BK * 2;   // 32 KB
 constexpr int kDequantWarps = 8;
-constexpr int kThreads = (2 + kDequantWarps) * 32;  // 320
+constexpr int kEpilogueWarps = 4;
+constexpr int kThreads = (2 + kDequantWarps + kEpilogueWarps) * 32;  // 448
 constexpr unsigned kWaitLimit = 1u << 20;
-constexpr int TMEM_COLS = 256;
+constexpr int TMEM_COLS = 512;  // two 256-column accumulators: the epilogue of tile t overlaps the MMAs of tile t+1
 
 struct TcArgs {
     DevWeights w;
@@ -52,7 +55,7 @@ struct TcArgs {
 };
 
 struct __align__(8) Barriers {
-    uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES], tmem_full, tmem_empty;
+    uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -256,8 +259,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             mbar_init(smem_u32(&B->full_b[s]), 1);
             mbar_init(smem_u32(&B->empty[s]), 1);
         }
-        mbar_init(smem_u32(&B->tmem_full), 1);
-        mbar_init(smem_u32(&B->tmem_empty), kDequantWarps * 32);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&B->tmem_full[i]), 1);
+            mbar_init(smem_u32(&B->tmem_empty[i]), kEpilogueWarps * 32);
+        }
         B->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -296,8 +301,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         if (lane == 0) {
             int g = 0, t = 0;
             for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
-                // the epilogue of the previous tile must have drained the accumulator
-                if (!mbar_wait(smem_u32(&B->tmem_empty), (t & 1) ^ 1, B, A.status)) break;
+                // the epilogue of the tile that last used this accumulator must have drained it
+                const uint32_t acc = tmem + (uint32_t)(t & 1) * BN;
+                if (!mbar_wait(smem_u32(&B->tmem_empty[t & 1]), ((t >> 1) & 1) ^ 1, B, A.status)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 bool ok = true;
                 for (int ks = 0; ks < kslabs; ++ks, ++g) {
@@ -311,25 +317,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                     const uint64_t da = umma_desc(smem_u32(sA + s * A_BYTES)), db = umma_desc(smem_u32(sB + s * B_BYTES));
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk)  // 32 bytes along K per instruction: +2 in the 16-byte address field
-                        umma_bf16(tmem, da + 2 * kk, db + 2 * kk, (ks | kk) ? 1u : 0u);
+                        umma_bf16(acc, da + 2 * kk, db + 2 * kk, (ks | kk) ? 1u : 0u);
                     umma_commit(smem_u32(&B->empty[s]));  // the stage is free once these MMAs have read it
                 }
                 if (!ok) break;
-                umma_commit(smem_u32(&B->tmem_full));
+                umma_commit(smem_u32(&B->tmem_full[t & 1]));
             }
         }
-    } else {
-        // ---------------- dequantise, then epilogue ----------------
+    } else if (warp < 2 + kDequantWarps) {
+        // ---------------- dequantise ----------------
         const int dt = threadIdx.x - 64;   // 0..255
         const int r = dt & (BM - 1);       // weight row inside the tile
         const int h = dt >> 7;             // which 32-weight half of the 64-element slab
-        const int ew = warp - 2;           // epilogue: lane quarter = warp % 4, column half = ew / 4
         const uint8_t* wbase = A.w.base + (size_t)A.mat * A.w.mat_stride;
         constexpr int ub = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 256;
         const size_t ustride = unit_stride(A.w, ub);
-        int g = 0, t = 0;
-        for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
-            const int rt = tile % row_tiles, tt = tile / row_tiles;
+        int g = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x) {
+            const int rt = tile % row_tiles;
             const int row = min(rt * BM + r, n - 1);
             const uint8_t* unit0 = row_unit0(A.w, wbase, row, ub);
             bool ok = true;
@@ -356,14 +361,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 mbar_arrive(smem_u32(&B->full_a[s]));
             }
             if (!ok) break;
-            // epilogue: accumulator lane = weight row, column = token
-            if (!mbar_wait(smem_u32(&B->tmem_full), t & 1, B, A.status)) break;
+        }
+    } else {
+        // ---------------- epilogue: accumulator lane = weight row, column = token ----------------
+        int t = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
+            const int rt = tile % row_tiles, tt = tile / row_tiles;
+            if (!mbar_wait(smem_u32(&B->tmem_full[t & 1]), (t >> 1) & 1, B, A.status)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int q = warp & 3;                       // TMEM lane quarter this warp may read
             const int out_row = rt * BM + q * 32 + lane;  // weight row = output column
-            for (int c0 = (ew >> 2) * (BN / 2); c0 < (ew >> 2) * (BN / 2) + BN / 2; c0 += 32) {
+            for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t acc[32];
-                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)((t & 1) * BN + c0);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -384,7 +394,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(smem_u32(&B->tmem_empty));
+            mbar_arrive(smem_u32(&B->tmem_empty[t & 1]));
         }
     }
 
