@@ -484,6 +484,108 @@ def run_extra(args) -> list[dict]:
     return out
 
 
+def run_multi(args) -> list[dict]:
+    """Multi-GPU exchange forms under torchrun: column-sharded Q4_K prefill with an NCCL all-gather,
+    and the expert-parallel Q5_K MoE layer with NCCL all-to-all dispatch/combine."""
+    import torch
+    import torch.distributed as dist
+
+    from fucina_b200 import formats as F
+    from fucina_b200 import parallel as par
+    from fucina_b200 import provider as P
+
+    rank, world, local = dist_setup(args.gpus)
+    P.init(local)
+    ext = torch.cuda.ExternalStream(P.stream_ptr())
+    out = []
+    steps = max(args.steps // 10, 5)
+
+    def timed(fn) -> float:
+        for _ in range(3):
+            fn()
+        barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(ext):
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+        P.synchronize()
+        torch.cuda.synchronize()
+        barrier(world)
+        return max_over_ranks(e0.elapsed_time(e1), world) / steps
+
+    if args.workload in ("tp_prefill", "multi"):
+        n, k = 14336, 4096
+        lo, hi = par.shard_rows(n, world, rank)
+        w = _dev_weights(P, torch, F.Q4_K, hi - lo, k, 1200 + rank)
+        for m in (512, 2048):
+            g = torch.Generator(device="cuda").manual_seed(2200 + m)
+            a = torch.randn((m, k), generator=g, device="cuda")
+            y_local = torch.empty((m, hi - lo), device="cuda")
+            torch.cuda.synchronize()
+
+            def gemm(t):
+                P.gemm_quant_nt_dev(w, t, y_local, m, mode=P.MODE_TENSOR)
+                return y_local
+
+            lin = par.ColumnShardedLinear(n, gemm) if world > 1 else None
+
+            def step():
+                with torch.cuda.stream(ext):
+                    if lin is not None:
+                        lin.forward(a)
+                    else:
+                        gemm(a)
+
+            ms = timed(step)
+            ms_compute = timed(lambda: gemm(a))
+            tf = 2.0 * m * n * k / ms / 1e9
+            out.append({"workload": f"Q4_K prefill {m}x{n}x{k}, columns sharded over {world} GPU(s), f32 all-gather (NCCL)",
+                        "n_gpus": world, "ms": round(ms, 4), "ms_compute_only": round(ms_compute, 4), "TFLOPS_total": round(tf, 1),
+                        "gathered_MB_per_rank": round(m * n * 4 * (world - 1) / world / 1e6, 1)})
+    if args.workload in ("ep_moe", "multi"):
+        hidden, ffn, E, topk = 2048, 768, 128, 8
+        per = E // world
+        gate = _dev_weights(P, torch, F.Q5_K, ffn, hidden, 1300 + rank, per)
+        up = _dev_weights(P, torch, F.Q5_K, ffn, hidden, 1400 + rank, per)
+        down = _dev_weights(P, torch, F.Q5_K, hidden, ffn, 1500 + rank, per)
+
+        def ffn_rows(rows, local_expert):
+            R = rows.shape[0]
+            ones = torch.ones((R,), device="cuda")
+            o = torch.empty_like(rows)
+            P.moe_layer_dev(gate, up, down, rows, R, 1, local_expert, ones, o)
+            return o
+
+        moe = par.ExpertParallelMoE(E, topk, ffn_rows) if world > 1 else None
+        for T_total in (64, 1024):
+            T = T_total // world
+            g = torch.Generator(device="cuda").manual_seed(3000 + 10 * rank + T_total)
+            x = torch.randn((T, hidden), generator=g, device="cuda")
+            logits = torch.randn((T, E), generator=g, device="cuda")
+            sel = torch.empty((T, topk), dtype=torch.int32, device="cuda")
+            wts = torch.empty((T, topk), device="cuda")
+            o1 = torch.empty((T, hidden), device="cuda")
+            torch.cuda.synchronize()
+
+            def step():
+                with torch.cuda.stream(ext):
+                    P.router_topk_dev(logits, T, E, topk, True, sel, wts)
+                    if moe is not None:
+                        moe.forward(x, sel, wts)
+                    else:
+                        P.moe_layer_dev(gate, up, down, x, T, topk, sel, wts, o1)
+
+            ms = timed(step)
+            out.append({"workload": f"Q5_K MoE layer (hidden 2048, ffn 768, 128 experts, top-8), {T_total} tokens over {world} GPU(s), "
+                                    f"{per} experts per GPU, NCCL all-to-all", "n_gpus": world, "ms": round(ms, 4),
+                        "tok_per_s_total": round(T_total / ms * 1e3, 1)})
+    if world > 1:
+        dist.destroy_process_group()
+    return out if rank == 0 else []
+
+
 def run_profile_tc(args) -> dict:
     """A small case of the tensor-core prefill kernel for profiler captures: Q4_K 512 x 4096 x 4096."""
     import torch
@@ -505,7 +607,8 @@ def run_profile_tc(args) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="stack", choices=["stack", "profile", "profile_tc", "q8_0", "prefill", "moe", "ternary", "all"])
+    ap.add_argument("--workload", default="stack", choices=["stack", "profile", "profile_tc", "q8_0", "prefill", "moe", "ternary", "all",
+                                                                "tp_prefill", "ep_moe", "multi"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
@@ -518,6 +621,10 @@ def main() -> None:
         return
     if args.workload == "profile_tc":
         print(json.dumps(run_profile_tc(args)), flush=True)
+        return
+    if args.workload in ("tp_prefill", "ep_moe", "multi"):
+        for line in run_multi(args):
+            print(json.dumps(line), flush=True)
         return
     if args.workload != "stack":
         for line in run_extra(args):
