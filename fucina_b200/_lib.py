@@ -77,6 +77,7 @@ SIGNATURES = {
     "fq_qmoe_fill_acceptable": (c_int, [c_size, c_size]),
     "fq_set_min_work_qmoe_for_test": (None, [c_u64]),
     "fq_set_decode_for_test": (None, [c_int]),
+    "fq_set_moe_tensor_for_test": (None, [c_int]),
     "fq_trace_enabled": (c_int, []),
     "fq_trace_reset": (None, []),
     "fq_trace_dump": (None, []),

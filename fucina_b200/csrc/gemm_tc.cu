@@ -49,10 +49,27 @@ struct TcArgs {
     DevWeights w;
     int mat;
     float* c;
-    int m;    // tokens
+    int m;    // tokens (dense) / rows of the sorted pair list (grouped)
     int ldc;
     int* status;
+    // grouped form (MoE): a device-built list of output tiles, each naming its expert matrix, its
+    // 128-row weight tile and the run of consecutive activation rows it multiplies
+    const TcTile* table;
+    const int* n_tiles_dev;
 };
+
+// One output tile: weight rows [rt*128, +128) of matrix `mat` times activation rows [tok0, tok0+ntok).
+struct TileRef {
+    int mat, rt, tok0, ntok;
+};
+__device__ __forceinline__ TileRef tile_ref(const TcArgs& A, int tile, int row_tiles) {
+    if (A.table) {
+        const TcTile t = A.table[tile];
+        return {t.mat, t.rt, t.tok0, t.ntok};
+    }
+    const int tt = tile / row_tiles;  // consecutive CTAs share the token tile (L2 reuse) and take different weight rows
+    return {A.mat, tile % row_tiles, tt * BN, min(BN, A.m - tt * BN)};
+}
 
 struct __align__(8) Barriers {
     uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
@@ -251,7 +268,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
     const int n = A.w.n, k = A.w.k, m = A.m;
     const int kslabs = k / BK;
     const int row_tiles = (n + BM - 1) / BM, tok_tiles = (m + BN - 1) / BN;
-    const int n_tiles = row_tiles * tok_tiles;
+    const int n_tiles = A.table ? *A.n_tiles_dev : row_tiles * tok_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -282,7 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         if (lane == 0) {
             int g = 0;
             for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x) {
-                const int tt = tile / row_tiles;  // consecutive CTAs share the token tile (L2 reuse) and take different weight rows
+                const TileRef T = tile_ref(A, tile, row_tiles);
                 for (int ks = 0; ks < kslabs; ++ks, ++g) {
                     const int s = g % STAGES;
                     if (!mbar_wait(smem_u32(&B->empty[s]), ((g / STAGES) & 1) ^ 1, B, A.status)) break;
@@ -291,7 +308,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                     asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                             smem_u32(sB + s * B_BYTES)),
-                        "l"(&tmap_tokens), "r"(ks * BK), "r"(tt * BN), "r"(bar)
+                        "l"(&tmap_tokens), "r"(ks * BK), "r"(T.tok0), "r"(bar)
                         : "memory");
                 }
             }
@@ -329,13 +346,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         const int dt = threadIdx.x - 64;   // 0..255
         const int r = dt & (BM - 1);       // weight row inside the tile
         const int h = dt >> 7;             // which 32-weight half of the 64-element slab
-        const uint8_t* wbase = A.w.base + (size_t)A.mat * A.w.mat_stride;
         constexpr int ub = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 256;
         const size_t ustride = unit_stride(A.w, ub);
         int g = 0;
         for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x) {
-            const int rt = tile % row_tiles;
-            const int row = min(rt * BM + r, n - 1);
+            const TileRef T = tile_ref(A, tile, row_tiles);
+            const uint8_t* wbase = A.w.base + (size_t)T.mat * A.w.mat_stride;
+            const int row = min(T.rt * BM + r, n - 1);
             const uint8_t* unit0 = row_unit0(A.w, wbase, row, ub);
             bool ok = true;
             Raw<FMT> next;
@@ -366,7 +383,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         // ---------------- epilogue: accumulator lane = weight row, column = token ----------------
         int t = 0;
         for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
-            const int rt = tile % row_tiles, tt = tile / row_tiles;
+            const TileRef T = tile_ref(A, tile, row_tiles);
+            const int rt = T.rt;
             if (!mbar_wait(smem_u32(&B->tmem_full[t & 1]), (t >> 1) & 1, B, A.status)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int q = warp & 3;                       // TMEM lane quarter this warp may read
@@ -388,8 +406,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 if (out_row < n) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int tok = tt * BN + c0 + j;
-                        if (tok < m) A.c[(size_t)tok * A.ldc + out_row] = __uint_as_float(acc[j]);
+                        if (c0 + j < T.ntok) A.c[(size_t)(T.tok0 + c0 + j) * A.ldc + out_row] = __uint_as_float(acc[j]);
                     }
                 }
             }
@@ -451,41 +468,62 @@ cudaError_t launch_tc(const TcArgs& a, const CUtensorMap& tmap, int grid, cudaSt
 
 }  // namespace
 
-int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, cudaStream_t st) {
-    if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q8_0) return fail(FQ_DECLINED_ARGS, "tensor-core path serves Q4_K, Q5_K and Q8_0");
-    if (w.k % 256 != 0 || m < 1 || m > (size_t)1 << 24) return fail(FQ_DECLINED_ARGS, "tensor-core path needs k %% 256 == 0");
+bool tensor_path_serves(const DevWeights& w) {
+    return (w.fmt == FQ_Q4_K || w.fmt == FQ_Q5_K || w.fmt == FQ_Q8_0) && w.k % 256 == 0 && encode_fn() != nullptr;
+}
+
+// Launch over bf16 activation rows [rows][k]: dense tiles of matrix `mat` (table == nullptr) or a
+// device-built tile list (grouped MoE form; `max_tiles` bounds the list for the grid size).
+static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfloat16* abf, size_t rows, float* c_dev, size_t ldc,
+                          const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return fail(FQ_DECLINED_ARGS, "cuTensorMapEncodeTiled unavailable");
-    // bf16 copy of the activations: [m][k], read by TMA with a 128-byte swizzle
-    __nv_bfloat16* abf = (__nv_bfloat16*)dev_alloc(m * (size_t)w.k * 2);
-    if (!abf) return fail(FQ_DECLINED_BUDGET, "bf16 activation scratch allocation failed");
-    const size_t total = m * (size_t)w.k;
-    int blocks = (int)((total / 4 + 255) / 256);
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    f32_to_bf16_kernel<<<blocks, 256, 0, st>>>(a_dev, abf, total);
     CUtensorMap tmap;
     memset(&tmap, 0, sizeof tmap);
-    const cuuint64_t dims[2] = {(cuuint64_t)w.k, (cuuint64_t)m};
+    const cuuint64_t dims[2] = {(cuuint64_t)w.k, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)w.k * 2};
     const cuuint32_t box[2] = {BK, BN};
     const cuuint32_t estr[2] = {1, 1};
-    int rc = FQ_OK;
-    if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, abf, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        rc = fail(FQ_DECLINED_ARGS, "tensor map for the activations could not be encoded");
-    if (rc == FQ_OK) {
-        TcArgs a{w, mat, c_dev, (int)m, (int)ldc, ctx->status_dev};
-        const int tiles = ((w.n + BM - 1) / BM) * (int)((m + BN - 1) / BN);
-        const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-        cudaError_t e;
-        switch (w.fmt) {
-            case FQ_Q4_K: e = launch_tc<FQ_Q4_K>(a, tmap, grid, st); break;
-            case FQ_Q5_K: e = launch_tc<FQ_Q5_K>(a, tmap, grid, st); break;
-            default: e = launch_tc<FQ_Q8_0>(a, tmap, grid, st); break;
-        }
-        g_trace.launches += 2;
-        if (e != cudaSuccess) rc = cuda_fail(e, "tensor-core GEMM launch");
+    if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(abf), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return fail(FQ_DECLINED_ARGS, "tensor map for the activations could not be encoded");
+    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev};
+    const int tiles = table ? max_tiles : ((w.n + BM - 1) / BM) * (int)((rows + BN - 1) / BN);
+    const int grid = tiles < ctx->sm_count ? (tiles > 0 ? tiles : 1) : ctx->sm_count;
+    cudaError_t e;
+    switch (w.fmt) {
+        case FQ_Q4_K: e = launch_tc<FQ_Q4_K>(a, tmap, grid, st); break;
+        case FQ_Q5_K: e = launch_tc<FQ_Q5_K>(a, tmap, grid, st); break;
+        default: e = launch_tc<FQ_Q8_0>(a, tmap, grid, st); break;
     }
+    g_trace.launches++;
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "tensor-core GEMM launch");
+}
+
+int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, size_t rows, float* c_dev, size_t ldc,
+                            const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st) {
+    if (!tensor_path_serves(w)) return fail(FQ_DECLINED_ARGS, "tensor-core path serves Q4_K, Q5_K and Q8_0 with k %% 256 == 0");
+    return launch_tc_rows(ctx, w, 0, (const __nv_bfloat16*)a_bf16, rows, c_dev, ldc, table, n_tiles_dev, max_tiles, st);
+}
+
+cudaError_t launch_f32_to_bf16(const float* src, void* dst, size_t n, cudaStream_t st) {
+    int blocks = (int)((n / 4 + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks < 1) blocks = 1;
+    f32_to_bf16_kernel<<<blocks, 256, 0, st>>>(src, (__nv_bfloat16*)dst, n);
+    return cudaGetLastError();
+}
+
+int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, cudaStream_t st) {
+    if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q8_0) return fail(FQ_DECLINED_ARGS, "tensor-core path serves Q4_K, Q5_K and Q8_0");
+    if (w.k % 256 != 0 || m < 1 || m > (size_t)1 << 24) return fail(FQ_DECLINED_ARGS, "tensor-core path needs k %% 256 == 0");
+    // bf16 copy of the activations: [m][k], read by TMA with a 128-byte swizzle
+    __nv_bfloat16* abf = (__nv_bfloat16*)dev_alloc(m * (size_t)w.k * 2);
+    if (!abf) return fail(FQ_DECLINED_BUDGET, "bf16 activation scratch allocation failed");
+    launch_f32_to_bf16(a_dev, abf, m * (size_t)w.k, st);
+    g_trace.launches++;
+    const int rc = launch_tc_rows(ctx, w, mat, abf, m, c_dev, ldc, nullptr, nullptr, 0, st);
     if (st != ctx->stream) cudaStreamSynchronize(st);
     dev_free(abf);
     return rc;

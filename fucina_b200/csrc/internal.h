@@ -28,6 +28,7 @@ cudaError_t launch_quantize_weights(int fmt, const float* src, size_t n, size_t 
 // Gated form (w2.base != nullptr): row j of `w` (gate) and row j of `w2` (up)
 // are dotted with the same activations and c receives
 // up * (gate * 1/(1+exp(-gate))) (reference backend/ops.zig:150-190, swiglu).
+struct TcTile;
 struct GroupDesc {
     int mat;
     int row0;
@@ -74,5 +75,12 @@ bool decode_rows_eligible(const DevWeights& w, size_t m);
 size_t decode_rows_scratch_bytes(const DevWeights& w, size_t m);
 cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev, uint8_t* scratch, float* c, int m, int ldc,
                                int sm_count, int* status, cudaStream_t st);
+
+// gemm_tc.cu -- tcgen05 prefill GEMM. One output tile of the grouped (MoE) form: weight rows
+// [rt*128, +128) of expert matrix `mat` times the consecutive activation rows [tok0, tok0+ntok).
+struct TcTile {
+    int mat, rt, tok0, ntok;
+};
+cudaError_t launch_f32_to_bf16(const float* src, void* dst, size_t n, cudaStream_t st);
 
 }  // namespace fq

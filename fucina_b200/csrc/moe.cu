@@ -11,6 +11,8 @@
 //   qg   = Q8_K(g)
 //   down = W_down[e].qg
 //   out[token] = sum over the token's slots, in slot order, of w[p] * down
+#include <cuda_bf16.h>
+
 #include <vector>
 
 #include "acts.cuh"
@@ -122,12 +124,125 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int rows, i
     }
 }
 
+int max_desc_for(int pairs, int n_expert);
+
+// ---- tensor-core form for prefill-sized batches ------------------------------------------------
+// Tile lists for the grouped tcgen05 GEMM, one CTA: per expert run, ceil(count/256) token tiles
+// times the row tiles of the gate/up product (rt_gu) and of the down product (rt_dn).
+constexpr int kTcTokens = 256;
+__global__ void tc_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, int rt_gu, int rt_dn,
+                               TcTile* __restrict__ t_gu, int* __restrict__ n_gu, TcTile* __restrict__ t_dn, int* __restrict__ n_dn) {
+    extern __shared__ int sh[];
+    int* count = sh;
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[min(max(selected[p], 0), n_expert - 1)], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, a = 0, b = 0;
+        for (int e = 0; e < n_expert; ++e) {
+            const int c = count[e];
+            for (int t0 = 0; t0 < c; t0 += kTcTokens) {
+                const int nt = min(kTcTokens, c - t0);
+                for (int rt = 0; rt < rt_gu; ++rt) t_gu[a++] = {e, rt, off + t0, nt};
+                for (int rt = 0; rt < rt_dn; ++rt) t_dn[b++] = {e, rt, off + t0, nt};
+            }
+            off += c;
+        }
+        *n_gu = a;
+        *n_dn = b;
+    }
+}
+
+// sorted pair position -> bf16 copy of its token row
+__global__ void gather_bf16_kernel(const float* __restrict__ x, const int* __restrict__ order, int top_k, int pairs, int hidden,
+                                   __nv_bfloat16* __restrict__ out) {
+    const size_t total = (size_t)pairs * hidden / 4;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t pos = i * 4 / hidden, col = i * 4 % hidden;
+        const float4 v = *reinterpret_cast<const float4*>(x + (size_t)(order[pos] / top_k) * hidden + col);
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&lo);
+        o.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(out + pos * hidden + col) = o;
+    }
+}
+
+// g = up * (gate * 1/(1+exp(-gate))) in f32 (backend/ops.zig:150-190), rounded once to bf16
+__global__ void swiglu_bf16_kernel(const float* __restrict__ gate, const float* __restrict__ up, size_t n, __nv_bfloat16* __restrict__ out) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float gv = gate[i];
+        const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gv)));
+        out[i] = __float2bfloat16_rn(__fmul_rn(up[i], __fmul_rn(gv, sig)));
+    }
+}
+
+int g_moe_tensor_mode = -1;  // -1 auto (>= 16 rows per expert on average), 0 never, 1 whenever the format allows
+
+int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
+                          int seq, int top_k, const int* selected_dev, const float* weights_dev, float* out_dev, cudaStream_t st) {
+    const int hidden = gate.k, out_pe = gate.n, n_expert = gate.n_mats;
+    const int pairs = seq * top_k;
+    const int rt_gu = (out_pe + 127) / 128, rt_dn = (hidden + 127) / 128;
+    const int tok_tiles = (pairs < n_expert ? pairs : n_expert) + pairs / kTcTokens;
+    const int max_gu = rt_gu * tok_tiles, max_dn = rt_dn * tok_tiles;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += (bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    const size_t o_order = take(sizeof(int) * pairs), o_inv = take(sizeof(int) * pairs), o_cnt = take(sizeof(int) * 4);
+    const size_t o_desc = take(sizeof(GroupDesc) * max_desc_for(pairs, n_expert));
+    const size_t o_tgu = take(sizeof(TcTile) * max_gu), o_tdn = take(sizeof(TcTile) * max_dn);
+    const size_t o_xb = take((size_t)pairs * hidden * 2), o_gate = take(sizeof(float) * (size_t)pairs * out_pe);
+    const size_t o_up = take(sizeof(float) * (size_t)pairs * out_pe), o_gb = take((size_t)pairs * out_pe * 2);
+    const size_t o_down = take(sizeof(float) * (size_t)pairs * hidden);
+    uint8_t* s = (uint8_t*)dev_alloc(off);
+    if (!s) return fail(FQ_DECLINED_BUDGET, "MoE scratch allocation of %zu bytes failed", off);
+    int* order = (int*)(s + o_order);
+    int* inv = (int*)(s + o_inv);
+    int* cnt = (int*)(s + o_cnt);  // [0] row-group count (unused here), [1] gate/up tiles, [2] down tiles
+    cudaError_t e = cudaSuccess;
+    int rc = FQ_OK;
+    do {
+        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, order, inv, (GroupDesc*)(s + o_desc), cnt);
+        tc_plan_kernel<<<1, 1024, sizeof(int) * n_expert, st>>>(selected_dev, pairs, n_expert, rt_gu, rt_dn, (TcTile*)(s + o_tgu), cnt + 1,
+                                                                 (TcTile*)(s + o_tdn), cnt + 2);
+        int blocks = (int)(((size_t)pairs * hidden / 4 + 255) / 256);
+        gather_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>(x_dev, order, top_k, pairs, hidden, (__nv_bfloat16*)(s + o_xb));
+        if ((e = cudaGetLastError()) != cudaSuccess) break;
+        if ((rc = gemm_tensor_grouped_dev(ctx, gate, s + o_xb, pairs, (float*)(s + o_gate), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, st)) != FQ_OK) break;
+        if ((rc = gemm_tensor_grouped_dev(ctx, up, s + o_xb, pairs, (float*)(s + o_up), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, st)) != FQ_OK) break;
+        const size_t ng = (size_t)pairs * out_pe;
+        blocks = (int)((ng + 255) / 256);
+        swiglu_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>((const float*)(s + o_gate), (const float*)(s + o_up), ng, (__nv_bfloat16*)(s + o_gb));
+        if ((e = cudaGetLastError()) != cudaSuccess) break;
+        if ((rc = gemm_tensor_grouped_dev(ctx, down, s + o_gb, pairs, (float*)(s + o_down), hidden, (const TcTile*)(s + o_tdn), cnt + 2, max_dn, st)) != FQ_OK) break;
+        const size_t total = (size_t)seq * hidden;
+        blocks = (int)((total + 255) / 256);
+        combine_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>((const float*)(s + o_down), weights_dev, inv, seq, hidden, top_k, out_dev);
+        e = cudaGetLastError();
+    } while (false);
+    g_trace.launches += 6;
+    if (e != cudaSuccess) rc = cuda_fail(e, "MoE tensor-path launch");
+    if (st != ctx->stream) cudaStreamSynchronize(st);
+    dev_free(s);
+    return rc;
+}
+
 int max_desc_for(int pairs, int n_expert) { return (pairs < n_expert ? pairs : n_expert) + pairs / kGroupRows; }
 
 int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
                        int seq, int top_k, const int* selected_dev, const float* weights_dev, float* out_dev, cudaStream_t st) {
     const int hidden = gate.k, out_pe = gate.n, n_expert = gate.n_mats, fmt = gate.fmt;
     const int pairs = seq * top_k;
+    // prefill-sized batches: bf16 tensor-core products (the reference's own GPU arm multiplies rounded
+    // operands too); decode-sized batches keep the CPU kernels' int8 arithmetic
+    const bool tc_ok = tensor_path_serves(gate) && tensor_path_serves(down);
+    if (tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 16 * n_expert)))
+        return moe_layer_tensor_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, out_dev, st);
     const ActSizes Sx = act_sizes(fmt, hidden), Sg = act_sizes(fmt, out_pe);
     const int max_desc = max_desc_for(pairs, n_expert);
     // one scratch block: order, inv, n_desc, table, quantised x rows, g rows, quantised g rows, down rows
@@ -278,6 +393,9 @@ int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights*
     pin_free(pin);
     return rc;
 }
+
+// Test seam in the spirit of setQuantMmaForTest (backend/cuda.zig:2563): -1 auto, 0 integer path, 1 tensor path.
+void fq_set_moe_tensor_for_test(int mode) { g_moe_tensor_mode = mode < 0 ? -1 : (mode ? 1 : 0); }
 
 // ---- grouped GEMM over staged panels (backend/cuda.zig:2181-2333) ------------
 void fq_qmoe_lock(void) { g_qmoe_lock.lock(); }

@@ -54,4 +54,10 @@ int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* 
 int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc,
                     cudaStream_t st);
 
+// grouped form over bf16 activation rows and a device-built tile list (moe.cu)
+struct TcTile;
+bool tensor_path_serves(const DevWeights& w);
+int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, size_t rows, float* c_dev, size_t ldc,
+                            const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st);
+
 }  // namespace fq

@@ -177,7 +177,16 @@ def route_plan(selected: np.ndarray, n_expert: int):
     return count, offset, order, inv
 
 
+def moe_ffn_bf16(fmt, gate, up, down, x, selected, weights, n_expert, out_pe):
+    """Oracle B of the expert layer: bf16 operands, f64 dots, f32 activation (the tensor-core arm's reference)."""
+    return _moe(lib().orc_moe_ffn_bf16, fmt, gate, up, down, x, selected, weights, n_expert, out_pe)
+
+
 def moe_ffn(fmt, gate, up, down, x, selected, weights, n_expert, out_pe):
+    return _moe(lib().orc_moe_ffn, fmt, gate, up, down, x, selected, weights, n_expert, out_pe)
+
+
+def _moe(fn, fmt, gate, up, down, x, selected, weights, n_expert, out_pe):
     """gate/up: [E*out_pe, rb(hidden)] u8; down: [E*hidden, rb(out_pe)] u8; x [seq, hidden]."""
     x = np.ascontiguousarray(x, dtype=np.float32)
     seq, hidden = x.shape
@@ -188,7 +197,7 @@ def moe_ffn(fmt, gate, up, down, x, selected, weights, n_expert, out_pe):
     up = np.ascontiguousarray(up)
     down = np.ascontiguousarray(down)
     out = np.zeros((seq, hidden), dtype=np.float32)
-    rc = lib().orc_moe_ffn(
+    rc = fn(
         fmt, _p(gate), _p(up), _p(down), _p(x), _sz(seq), _sz(hidden), _sz(out_pe), _sz(n_expert), _sz(top_k),
         _p(sel), _p(w), _p(out),
     )

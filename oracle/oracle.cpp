@@ -881,4 +881,60 @@ int orc_moe_ffn(int fmt, const void* gate, const void* up, const void* down, con
     return 0;
 }
 
+// Oracle B for the expert layer: the reference's GPU arm multiplies operands rounded to the
+// tensor-core precision with wide accumulation and applies the activation in f32 between the two
+// products (src/llm/gemma/moe.zig:696-901, src/backend/cuda.zig:3016-3044). Here: bf16 operands,
+// f64 dots rounded to f32, swiglu in f32, g rounded to bf16, weighted combine in slot order.
+int orc_moe_ffn_bf16(int fmt, const void* gate, const void* up, const void* down, const float* x, size_t seq,
+                     size_t hidden, size_t out_pe, size_t n_expert, size_t top_k, const int64_t* selected,
+                     const float* weights, float* out) {
+    const size_t rb_in = row_bytes(fmt, hidden), rb_g = row_bytes(fmt, out_pe);
+    if (rb_in == 0 || rb_g == 0) return 1;
+    for (size_t p = 0; p < seq * top_k; ++p)
+        if (selected[p] < 0 || (size_t)selected[p] >= n_expert) return 1;
+    std::vector<float> pair_out(seq * top_k * hidden);
+#pragma omp parallel
+    {
+        std::vector<float> wrow(std::max(hidden, out_pe)), xb(hidden), g(out_pe), gate_v(out_pe), up_v(out_pe);
+#pragma omp for schedule(dynamic, 1)
+        for (long long p = 0; p < (long long)(seq * top_k); ++p) {
+            const size_t t = (size_t)p / top_k, e = (size_t)selected[p];
+            for (size_t i = 0; i < hidden; ++i) xb[i] = round_bf16(x[t * hidden + i]);
+            const uint8_t* wg = (const uint8_t*)gate + e * out_pe * rb_in;
+            const uint8_t* wu = (const uint8_t*)up + e * out_pe * rb_in;
+            const uint8_t* wd = (const uint8_t*)down + e * hidden * rb_g;
+            for (size_t j = 0; j < out_pe; ++j) {
+                dequantize_row(fmt, wrow.data(), wg + j * rb_in, hidden);
+                double acc = 0;
+                for (size_t i = 0; i < hidden; ++i) acc += (double)round_bf16(wrow[i]) * (double)xb[i];
+                gate_v[j] = (float)acc;
+                dequantize_row(fmt, wrow.data(), wu + j * rb_in, hidden);
+                acc = 0;
+                for (size_t i = 0; i < hidden; ++i) acc += (double)round_bf16(wrow[i]) * (double)xb[i];
+                up_v[j] = (float)acc;
+            }
+            for (size_t j = 0; j < out_pe; ++j) g[j] = round_bf16(swiglu_pair(gate_v[j], up_v[j]));
+            float* po = pair_out.data() + (size_t)p * hidden;
+            for (size_t j = 0; j < hidden; ++j) {
+                dequantize_row(fmt, wrow.data(), wd + j * rb_g, out_pe);
+                double acc = 0;
+                for (size_t i = 0; i < out_pe; ++i) acc += (double)round_bf16(wrow[i]) * (double)g[i];
+                po[j] = (float)acc;
+            }
+        }
+    }
+    for (size_t t = 0; t < seq; ++t)
+        for (size_t kk = 0; kk < top_k; ++kk) {
+            const size_t p = t * top_k + kk;
+            const float w = weights[p];
+            const float* src = pair_out.data() + p * hidden;
+            float* dst = out + t * hidden;
+            if (kk == 0)
+                for (size_t j = 0; j < hidden; ++j) dst[j] = w * src[j];
+            else
+                for (size_t j = 0; j < hidden; ++j) dst[j] += w * src[j];
+        }
+    return 0;
+}
+
 }  // extern "C"

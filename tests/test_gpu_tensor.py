@@ -68,6 +68,45 @@ def test_auto_mode_routes_large_m_to_tensor_cores(P, torch):
     assert float(np.max(np.abs(tens - want)) / np.max(np.abs(want))) < 5e-2
 
 
+@pytest.mark.parametrize("fmt_name,hidden,out_pe,n_expert,top_k,seq", [
+    ("q5_k", 256, 256, 4, 2, 37),      # ragged expert runs inside one token tile
+    ("q5_k", 512, 768, 8, 4, 300),     # runs of ~150 rows, several row tiles, Qwen3-MoE expert width
+    ("q4_k", 256, 512, 4, 2, 700),     # runs longer than one 256-token tile
+])
+def test_moe_tensor_arm_matches_bf16_oracle(P, fmt_name, hidden, out_pe, n_expert, top_k, seq):
+    from fucina_b200._lib import load
+
+    fmt = oracle.FORMATS[fmt_name]
+    rng = np.random.default_rng(2400)
+    gate = make_weights(fmt_name, n_expert * out_pe, hidden, 2401)
+    up = make_weights(fmt_name, n_expert * out_pe, hidden, 2402)
+    down = make_weights(fmt_name, n_expert * hidden, out_pe, 2403)
+    x = rng.standard_normal((seq, hidden)).astype(np.float32)
+    sel, w = oracle.router_topk(rng.standard_normal((seq, n_expert)).astype(np.float32), top_k, True)
+    wg = P.Weights.upload(fmt, gate, out_pe, hidden, n_expert)
+    wu = P.Weights.upload(fmt, up, out_pe, hidden, n_expert)
+    wd = P.Weights.upload(fmt, down, hidden, out_pe, n_expert)
+    load().fq_set_moe_tensor_for_test(1)
+    try:
+        got = P.moe_layer(wg, wu, wd, x, sel, w)
+    finally:
+        load().fq_set_moe_tensor_for_test(-1)
+    want = oracle.moe_ffn_bf16(fmt, gate, up, down, x, sel, w, n_expert, out_pe)
+    # The layer rounds the intermediate g to bf16. Kernel and oracle compute g with different
+    # accumulation (f32 tensor core vs f64), so a few g values land on the other side of a bf16
+    # rounding boundary; one such flip moves an output by ~3e-4 of the output RMS, which the
+    # per-element ratio would blow up on near-zero outputs. The bound is therefore on the error
+    # relative to the output scale: 1e-2 of the RMS (observed ~1e-3).
+    rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    err = float(np.max(np.abs(got - want))) / rms
+    assert np.isfinite(got).all() and err <= TOL_TENSOR, f"moe tensor arm {fmt_name} seq={seq}: {err:.3e} of output RMS"
+    # the two arms agree to activation-quantisation noise (matrix level)
+    int8 = oracle.moe_ffn(fmt, gate, up, down, x, sel, w, n_expert, out_pe)
+    assert float(np.max(np.abs(got - int8)) / np.max(np.abs(int8))) < 5e-2
+    for h in (wg, wu, wd):
+        h.free()
+
+
 def test_formats_without_a_tensor_kernel_are_declined_in_tensor_mode(P, torch):
     n, k, m = 64, 512, 32
     blocks = make_weights("tq2_0", n, k, seed=2300)
