@@ -616,6 +616,15 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    # Libraries (NCCL prints its version banner) may write to stdout; the contract is ONE JSON line
+    # there. Everything else goes to stderr: stdout is parked and only _emit writes to it.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def print(*a, **kw):  # noqa: A001 - shadows the builtin on purpose inside main
+        os.write(real_stdout, (" ".join(str(x) for x in a) + "\n").encode())
+
     if args.workload == "profile":
         print(json.dumps(run_profile_case(args)), flush=True)
         return
