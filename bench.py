@@ -559,7 +559,15 @@ def run_multi(args) -> list[dict]:
             return o
 
         moe = par.ExpertParallelMoE(E, topk, ffn_rows) if world > 1 else None
-        for T_total in (64, 1024):
+
+        def partial_rows(x_all, sel_all, w_all):
+            o = torch.empty_like(x_all)
+            P.moe_layer_ep_dev(gate, up, down, x_all, x_all.shape[0], topk, sel_all, w_all, rank * per, o)
+            return o
+
+        # strong scaling (64 and 1024 tokens in total) and weak scaling (1024 tokens per GPU)
+        cases = [(64, "strong"), (1024, "strong")] + ([(1024 * world, "weak")] if world > 1 else [])
+        for T_total, scaling in cases:
             T = T_total // world
             g = torch.Generator(device="cuda").manual_seed(3000 + 10 * rank + T_total)
             x = torch.randn((T, hidden), generator=g, device="cuda")
@@ -568,19 +576,22 @@ def run_multi(args) -> list[dict]:
             wts = torch.empty((T, topk), device="cuda")
             o1 = torch.empty((T, hidden), device="cuda")
             torch.cuda.synchronize()
+            forms = ["single GPU"] if moe is None else ["NCCL all-to-all dispatch/combine", "NCCL all-gather + reduce-scatter of partial sums"]
+            for form in forms:
+                def step():
+                    with torch.cuda.stream(ext):
+                        P.router_topk_dev(logits, T, E, topk, True, sel, wts)
+                        if moe is None:
+                            P.moe_layer_dev(gate, up, down, x, T, topk, sel, wts, o1)
+                        elif form.startswith("NCCL all-to-all"):
+                            moe.forward(x, sel, wts)
+                        else:
+                            moe.forward_gathered(x, sel, wts, partial_rows)
 
-            def step():
-                with torch.cuda.stream(ext):
-                    P.router_topk_dev(logits, T, E, topk, True, sel, wts)
-                    if moe is not None:
-                        moe.forward(x, sel, wts)
-                    else:
-                        P.moe_layer_dev(gate, up, down, x, T, topk, sel, wts, o1)
-
-            ms = timed(step)
-            out.append({"workload": f"Q5_K MoE layer (hidden 2048, ffn 768, 128 experts, top-8), {T_total} tokens over {world} GPU(s), "
-                                    f"{per} experts per GPU, NCCL all-to-all", "n_gpus": world, "ms": round(ms, 4),
-                        "tok_per_s_total": round(T_total / ms * 1e3, 1)})
+                ms = timed(step)
+                out.append({"workload": f"Q5_K MoE layer (hidden 2048, ffn 768, 128 experts, top-8), {T_total} tokens over {world} GPU(s), "
+                                        f"{per} experts per GPU, {form}", "scaling": scaling, "n_gpus": world, "ms": round(ms, 4),
+                            "tok_per_s_total": round(T_total / ms * 1e3, 1)})
     if world > 1:
         dist.destroy_process_group()
     return out if rank == 0 else []

@@ -69,6 +69,8 @@ SIGNATURES = {
     "fq_gemm_q_grouped_nt": (c_int, [c_int, c_void, c_size, c_int, c_size, c_size, c_size, c_size, P(QmmTile), c_size]),
     "fq_moe_layer": (c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_int, c_void]),
     "fq_moe_layer_dev": (c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_int, c_void, c_void]),
+    "fq_moe_layer_ep_dev": (
+        c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_int, c_int, c_void, c_void]),
     "fq_router_topk_dev": (c_int, [c_void, c_size, c_size, c_size, c_int, c_void, c_void, c_void]),
     "fq_should_use_gpu_dense_quant": (c_int, [c_int, c_u64]),
     "fq_should_use_gpu_dense_quant_packed": (c_int, [c_int, c_u64]),

@@ -28,16 +28,30 @@ constexpr int kGroupRows = 16;  // activation rows one grouped-GEMV table entry 
 // Counting sort of pairs by expert plus the grouped-GEMV table, one CTA.
 // Positions inside an expert's run are handed out by atomics: a pair's result
 // does not depend on its position, so the layer output is unaffected.
-__global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, int* __restrict__ order,
-                                  int* __restrict__ inv, GroupDesc* __restrict__ table, int* __restrict__ n_desc) {
+//
+// An expert shard (Shard.skip_foreign) serves experts [base, base + n_expert) of a larger layer:
+// pairs routed elsewhere get inv = -1, take no position, and contribute nothing to the combine.
+struct Shard {
+    int base;
+    int skip_foreign;
+};
+__device__ __forceinline__ int local_expert(int e, int n_expert, Shard sh) {
+    e -= sh.base;
+    if (e >= 0 && e < n_expert) return e;
+    return sh.skip_foreign ? -1 : min(max(e, 0), n_expert - 1);
+}
+
+__global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, Shard shard, int* __restrict__ order,
+                                  int* __restrict__ inv, GroupDesc* __restrict__ table, int* __restrict__ n_desc,
+                                  int* __restrict__ n_rows) {
     extern __shared__ int sh[];
     int* count = sh;                 // [n_expert]
     int* place = sh + n_expert;      // [n_expert]
     for (int e = threadIdx.x; e < n_expert; e += blockDim.x) count[e] = 0;
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const int e = min(max(selected[p], 0), n_expert - 1);
-        atomicAdd(&count[e], 1);
+        const int e = local_expert(selected[p], n_expert, shard);
+        if (e >= 0) atomicAdd(&count[e], 1);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -49,10 +63,15 @@ __global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, i
             off += c;
         }
         *n_desc = nd;
+        *n_rows = off;
     }
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const int e = min(max(selected[p], 0), n_expert - 1);
+        const int e = local_expert(selected[p], n_expert, shard);
+        if (e < 0) {
+            inv[p] = -1;
+            continue;
+        }
         const int pos = atomicAdd(&place[e], 1);
         order[pos] = p;
         inv[p] = pos;
@@ -67,10 +86,13 @@ __global__ void combine_kernel(const float* __restrict__ down, const float* __re
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(i / hidden), j = (int)(i % hidden);
         float acc = 0.0f;
+        bool first = true;
         for (int kk = 0; kk < top_k; ++kk) {
-            const int p = t * top_k + kk;
-            const float v = __fmul_rn(weights[p], down[(size_t)inv[p] * hidden + j]);
-            acc = (kk == 0) ? v : __fadd_rn(acc, v);
+            const int p = t * top_k + kk, pos = inv[p];
+            if (pos < 0) continue;  // another shard's expert
+            const float v = __fmul_rn(weights[p], down[(size_t)pos * hidden + j]);
+            acc = first ? v : __fadd_rn(acc, v);
+            first = false;
         }
         out[i] = acc;
     }
@@ -130,13 +152,16 @@ int max_desc_for(int pairs, int n_expert);
 // Tile lists for the grouped tcgen05 GEMM, one CTA: per expert run, ceil(count/256) token tiles
 // times the row tiles of the gate/up product (rt_gu) and of the down product (rt_dn).
 constexpr int kTcTokens = 256;
-__global__ void tc_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, int rt_gu, int rt_dn,
+__global__ void tc_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, Shard shard, int rt_gu, int rt_dn,
                                TcTile* __restrict__ t_gu, int* __restrict__ n_gu, TcTile* __restrict__ t_dn, int* __restrict__ n_dn) {
     extern __shared__ int sh[];
     int* count = sh;
     for (int e = threadIdx.x; e < n_expert; e += blockDim.x) count[e] = 0;
     __syncthreads();
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[min(max(selected[p], 0), n_expert - 1)], 1);
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = local_expert(selected[p], n_expert, shard);
+        if (e >= 0) atomicAdd(&count[e], 1);
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         int off = 0, a = 0, b = 0;
@@ -155,9 +180,9 @@ __global__ void tc_plan_kernel(const int* __restrict__ selected, int pairs, int 
 }
 
 // sorted pair position -> bf16 copy of its token row
-__global__ void gather_bf16_kernel(const float* __restrict__ x, const int* __restrict__ order, int top_k, int pairs, int hidden,
-                                   __nv_bfloat16* __restrict__ out) {
-    const size_t total = (size_t)pairs * hidden / 4;
+__global__ void gather_bf16_kernel(const float* __restrict__ x, const int* __restrict__ order, int top_k, const int* __restrict__ n_rows,
+                                   int hidden, __nv_bfloat16* __restrict__ out) {
+    const size_t total = (size_t)*n_rows * hidden / 4;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t pos = i * 4 / hidden, col = i * 4 % hidden;
         const float4 v = *reinterpret_cast<const float4*>(x + (size_t)(order[pos] / top_k) * hidden + col);
@@ -170,7 +195,9 @@ __global__ void gather_bf16_kernel(const float* __restrict__ x, const int* __res
 }
 
 // g = up * (gate * 1/(1+exp(-gate))) in f32 (backend/ops.zig:150-190), rounded once to bf16
-__global__ void swiglu_bf16_kernel(const float* __restrict__ gate, const float* __restrict__ up, size_t n, __nv_bfloat16* __restrict__ out) {
+__global__ void swiglu_bf16_kernel(const float* __restrict__ gate, const float* __restrict__ up, const int* __restrict__ n_rows, int width,
+                                   __nv_bfloat16* __restrict__ out) {
+    const size_t n = (size_t)*n_rows * width;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const float gv = gate[i];
         const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gv)));
@@ -181,7 +208,8 @@ __global__ void swiglu_bf16_kernel(const float* __restrict__ gate, const float* 
 int g_moe_tensor_mode = -1;  // -1 auto (>= 16 rows per expert on average), 0 never, 1 whenever the format allows
 
 int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
-                          int seq, int top_k, const int* selected_dev, const float* weights_dev, float* out_dev, cudaStream_t st) {
+                          int seq, int top_k, const int* selected_dev, const float* weights_dev, Shard shard, float* out_dev,
+                          cudaStream_t st) {
     const int hidden = gate.k, out_pe = gate.n, n_expert = gate.n_mats;
     const int pairs = seq * top_k;
     const int rt_gu = (out_pe + 127) / 128, rt_dn = (hidden + 127) / 128;
@@ -203,21 +231,21 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
     if (!s) return fail(FQ_DECLINED_BUDGET, "MoE scratch allocation of %zu bytes failed", off);
     int* order = (int*)(s + o_order);
     int* inv = (int*)(s + o_inv);
-    int* cnt = (int*)(s + o_cnt);  // [0] row-group count (unused here), [1] gate/up tiles, [2] down tiles
+    int* cnt = (int*)(s + o_cnt);  // [0] row-group count (unused here), [1] gate/up tiles, [2] down tiles, [3] rows this shard serves
     cudaError_t e = cudaSuccess;
     int rc = FQ_OK;
     do {
-        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, order, inv, (GroupDesc*)(s + o_desc), cnt);
-        tc_plan_kernel<<<1, 1024, sizeof(int) * n_expert, st>>>(selected_dev, pairs, n_expert, rt_gu, rt_dn, (TcTile*)(s + o_tgu), cnt + 1,
+        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, order, inv, (GroupDesc*)(s + o_desc), cnt, cnt + 3);
+        tc_plan_kernel<<<1, 1024, sizeof(int) * n_expert, st>>>(selected_dev, pairs, n_expert, shard, rt_gu, rt_dn, (TcTile*)(s + o_tgu), cnt + 1,
                                                                  (TcTile*)(s + o_tdn), cnt + 2);
         int blocks = (int)(((size_t)pairs * hidden / 4 + 255) / 256);
-        gather_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>(x_dev, order, top_k, pairs, hidden, (__nv_bfloat16*)(s + o_xb));
+        gather_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>(x_dev, order, top_k, cnt + 3, hidden, (__nv_bfloat16*)(s + o_xb));
         if ((e = cudaGetLastError()) != cudaSuccess) break;
         if ((rc = gemm_tensor_grouped_dev(ctx, gate, s + o_xb, pairs, (float*)(s + o_gate), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, st)) != FQ_OK) break;
         if ((rc = gemm_tensor_grouped_dev(ctx, up, s + o_xb, pairs, (float*)(s + o_up), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, st)) != FQ_OK) break;
         const size_t ng = (size_t)pairs * out_pe;
         blocks = (int)((ng + 255) / 256);
-        swiglu_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>((const float*)(s + o_gate), (const float*)(s + o_up), ng, (__nv_bfloat16*)(s + o_gb));
+        swiglu_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>((const float*)(s + o_gate), (const float*)(s + o_up), cnt + 3, out_pe, (__nv_bfloat16*)(s + o_gb));
         if ((e = cudaGetLastError()) != cudaSuccess) break;
         if ((rc = gemm_tensor_grouped_dev(ctx, down, s + o_gb, pairs, (float*)(s + o_down), hidden, (const TcTile*)(s + o_tdn), cnt + 2, max_dn, st)) != FQ_OK) break;
         const size_t total = (size_t)seq * hidden;
@@ -235,14 +263,15 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
 int max_desc_for(int pairs, int n_expert) { return (pairs < n_expert ? pairs : n_expert) + pairs / kGroupRows; }
 
 int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
-                       int seq, int top_k, const int* selected_dev, const float* weights_dev, float* out_dev, cudaStream_t st) {
+                       int seq, int top_k, const int* selected_dev, const float* weights_dev, Shard shard, float* out_dev,
+                       cudaStream_t st) {
     const int hidden = gate.k, out_pe = gate.n, n_expert = gate.n_mats, fmt = gate.fmt;
     const int pairs = seq * top_k;
     // prefill-sized batches: bf16 tensor-core products (the reference's own GPU arm multiplies rounded
     // operands too); decode-sized batches keep the CPU kernels' int8 arithmetic
     const bool tc_ok = tensor_path_serves(gate) && tensor_path_serves(down);
     if (tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 16 * n_expert)))
-        return moe_layer_tensor_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, out_dev, st);
+        return moe_layer_tensor_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, shard, out_dev, st);
     const ActSizes Sx = act_sizes(fmt, hidden), Sg = act_sizes(fmt, out_pe);
     const int max_desc = max_desc_for(pairs, n_expert);
     // one scratch block: order, inv, n_desc, table, quantised x rows, g rows, quantised g rows, down rows
@@ -252,7 +281,7 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
         off += (bytes + 255) & ~(size_t)255;
         return o;
     };
-    const size_t o_order = take(sizeof(int) * pairs), o_inv = take(sizeof(int) * pairs), o_nd = take(sizeof(int));
+    const size_t o_order = take(sizeof(int) * pairs), o_inv = take(sizeof(int) * pairs), o_nd = take(sizeof(int) * 2);
     const size_t o_table = take(sizeof(GroupDesc) * max_desc), o_qx = take(Sx.row * pairs);
     const size_t o_g = take(sizeof(float) * (size_t)pairs * out_pe), o_qg = take(Sg.row * pairs);
     const size_t o_down = take(sizeof(float) * (size_t)pairs * hidden);
@@ -270,7 +299,9 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     cudaError_t e = cudaSuccess;
     int rc = FQ_OK;
     do {
-        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, order, inv, table, n_desc);
+        // positions past a shard's own rows are read by the gather below: point them at pair 0
+        if (shard.skip_foreign && (e = cudaMemsetAsync(order, 0, sizeof(int) * pairs, st)) != cudaSuccess) break;
+        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, order, inv, table, n_desc, n_desc + 1);
         if ((e = cudaGetLastError()) != cudaSuccess) break;
         // gather each pair's token row and quantise it, in expert order
         if ((e = launch_quantize_acts_layout(x_dev, order, top_k, pairs, hidden, fmt, qx, st)) != cudaSuccess) break;
@@ -292,14 +323,15 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     return rc;
 }
 
-int check_moe(const fq_weights* gate, const fq_weights* up, const fq_weights* down, size_t seq, size_t top_k, int gated_op) {
+int check_moe(const fq_weights* gate, const fq_weights* up, const fq_weights* down, size_t seq, size_t top_k, int gated_op,
+              bool shard = false) {
     if (!gate || !up || !down) return fail(FQ_DECLINED_ARGS, "null weights");
     if (gated_op != 0) return fail(FQ_DECLINED_ARGS, "only swiglu (gated_op 0) is served");
     const DevWeights &g = gate->dw, &u = up->dw, &d = down->dw;
     if (g.fmt != u.fmt || g.fmt != d.fmt) return fail(FQ_DECLINED_ARGS, "expert tensors must share one format");
     if (g.n != u.n || g.k != u.k || g.n_mats != u.n_mats || d.n_mats != g.n_mats || d.n != g.k || d.k != g.n)
         return fail(FQ_DECLINED_ARGS, "expert tensor shapes are inconsistent");
-    if (seq == 0 || top_k == 0 || top_k > (size_t)g.n_mats) return fail(FQ_DECLINED_ARGS, "bad seq/top_k");
+    if (seq == 0 || top_k == 0 || (!shard && top_k > (size_t)g.n_mats)) return fail(FQ_DECLINED_ARGS, "bad seq/top_k");
     if (seq * top_k > (size_t)1 << 24) return fail(FQ_DECLINED_ARGS, "too many routed pairs");
     if (g.n_mats > 4096) return fail(FQ_DECLINED_ARGS, "too many experts");
     const ActLayout L = act_layout(g.fmt);
@@ -344,8 +376,22 @@ int fq_moe_layer_dev(const fq_weights* gate, const fq_weights* up, const fq_weig
     if (!ctx) return FQ_DECLINED_NO_GPU;
     std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
     g_trace.calls++;
-    return moe_layer_dev_impl(ctx, gate->dw, up->dw, down->dw, x_dev, (int)seq, (int)top_k, selected_dev, weights_dev, out_dev,
-                              stream ? (cudaStream_t)stream : ctx->stream);
+    return moe_layer_dev_impl(ctx, gate->dw, up->dw, down->dw, x_dev, (int)seq, (int)top_k, selected_dev, weights_dev, Shard{0, 0},
+                              out_dev, stream ? (cudaStream_t)stream : ctx->stream);
+}
+
+int fq_moe_layer_ep_dev(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev, size_t seq,
+                        size_t top_k, const int32_t* selected_dev, const float* weights_dev, int expert_base, int gated_op,
+                        float* partial_dev, void* stream) {
+    if (int rc = check_moe(gate, up, down, seq, top_k, gated_op, true)) return rc;
+    if (!x_dev || !selected_dev || !weights_dev || !partial_dev) return fail(FQ_DECLINED_ARGS, "null pointer");
+    if (expert_base < 0) return fail(FQ_DECLINED_ARGS, "negative expert_base");
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    g_trace.calls++;
+    return moe_layer_dev_impl(ctx, gate->dw, up->dw, down->dw, x_dev, (int)seq, (int)top_k, selected_dev, weights_dev,
+                              Shard{expert_base, 1}, partial_dev, stream ? (cudaStream_t)stream : ctx->stream);
 }
 
 int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x, size_t seq, size_t top_k,
@@ -380,7 +426,7 @@ int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights*
     }
     if (rc == FQ_OK)
         rc = moe_layer_dev_impl(ctx, gate->dw, up->dw, down->dw, (const float*)dev, (int)seq, (int)top_k, (const int*)(dev + o_sel),
-                                (const float*)(dev + o_w), (float*)(dev + o_out), ctx->stream);
+                                (const float*)(dev + o_w), Shard{0, 0}, (float*)(dev + o_out), ctx->stream);
     if (rc == FQ_OK) {
         cudaError_t e = cudaMemcpyAsync(pin + o_out, dev + o_out, xb, cudaMemcpyDeviceToHost, ctx->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);

@@ -131,6 +131,38 @@ class ExpertParallelMoE:
             out = out + w[:, j:j + 1] * pair_rows[:, j]
         return out
 
+    def forward_gathered(self, x: torch.Tensor, selected: torch.Tensor, weights: torch.Tensor,
+                         partial_ffn: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor]) -> torch.Tensor:
+        """The same layer with fixed-size exchanges and no host synchronisation: all-gather the token
+        rows and their routing, let every rank compute the partial sums of ITS experts for all
+        world*T tokens, and reduce-scatter the partial outputs back to the tokens' home ranks.
+
+        `partial_ffn(x_all [W*T, hidden], selected_all [W*T, k] (global expert ids), weights_all)
+        -> [W*T, hidden]` returns, per token, the slot-ordered weighted sum over the pairs this
+        rank's experts serve and zero rows elsewhere (on the GPU: `fq_moe_layer_ep_dev`).
+
+        Each token row crosses the links once per direction instead of once per routed pair, the
+        sizes never depend on the routing, and NVSwitch can do the reduction in the fabric. A token's
+        slots are summed per rank first and across ranks second, so the result differs from the
+        single-GPU slot-order sum by f32 rounding (not bit-identical, unlike `forward`)."""
+        T, hidden = x.shape
+        k = self.top_k
+        W = self.world
+        x_all = torch.empty((W * T, hidden), dtype=x.dtype, device=x.device)
+        sel_all = torch.empty((W * T, k), dtype=selected.dtype, device=x.device)
+        w_all = torch.empty((W * T, k), dtype=weights.dtype, device=x.device)
+        dist.all_gather_into_tensor(x_all, x.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(sel_all, selected.reshape(T, k).contiguous(), group=self.group)
+        dist.all_gather_into_tensor(w_all, weights.reshape(T, k).contiguous(), group=self.group)
+        partial = partial_ffn(x_all, sel_all, w_all)
+        out = torch.empty((T, hidden), dtype=partial.dtype, device=partial.device)
+        if dist.get_backend(self.group) == "gloo":   # gloo has no reduce-scatter
+            dist.all_reduce(partial, group=self.group)
+            out.copy_(partial[self.rank * T:(self.rank + 1) * T])
+        else:
+            dist.reduce_scatter_tensor(out, partial.contiguous(), group=self.group)
+        return out
+
     def exchange_bytes(self, T: int, hidden: int, elem: int = 4) -> int:
         """Upper bound of bytes one rank sends per direction: every routed pair leaves the rank."""
         return T * self.top_k * hidden * elem

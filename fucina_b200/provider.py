@@ -313,6 +313,14 @@ def moe_layer_dev(gate: Weights, up: Weights, down: Weights, x_dev, seq: int, to
                                    _vp(weights_dev), gated_op, _vp(out_dev), C.c_void_p(stream)))
 
 
+def moe_layer_ep_dev(gate: Weights, up: Weights, down: Weights, x_dev, seq: int, top_k: int, selected_dev, weights_dev,
+                     expert_base: int, partial_dev, gated_op: int = 0, stream: int = 0) -> None:
+    """This shard's partial output of the layer: experts [expert_base, expert_base + E_local), global ids in
+    `selected_dev`, pairs of other shards skipped."""
+    _check(load().fq_moe_layer_ep_dev(gate.handle, up.handle, down.handle, _vp(x_dev), seq, top_k, _vp(selected_dev),
+                                      _vp(weights_dev), expert_base, gated_op, _vp(partial_dev), C.c_void_p(stream)))
+
+
 def router_topk_dev(logits_dev, seq: int, n_expert: int, top_k: int, normalize: bool, selected_dev, weights_dev,
                     stream: int = 0) -> None:
     """`routerTopK` (src/exec/topk.zig:21-86) on the device."""

@@ -213,6 +213,15 @@ FQ_API int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_w
 FQ_API int fq_moe_layer_dev(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev,
                      size_t seq, size_t top_k, const int32_t* selected_dev, const float* weights_dev,
                      int gated_op, float* out_dev, void* stream);
+/* Expert-parallel shard of the same layer (the reference is single-device, backend/cuda.zig:439,
+ * so this has no counterpart there). gate/up/down hold experts [expert_base, expert_base + E_local)
+ * of the full layer; `selected_dev` carries GLOBAL expert ids. Pairs routed to other shards are
+ * skipped, and partial_dev [seq, hidden] receives, per token, the slot-ordered weighted sum over the
+ * pairs this shard serves (all zero when it serves none). Summing the shards' partial outputs gives
+ * the layer output; a reduce-scatter does that when tokens are sharded too. */
+FQ_API int fq_moe_layer_ep_dev(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev,
+                        size_t seq, size_t top_k, const int32_t* selected_dev, const float* weights_dev,
+                        int expert_base, int gated_op, float* partial_dev, void* stream);
 /* exec/topk.zig:21-86 `routerTopK` on the device: logits [seq, E] -> selected/weights [seq, top_k]. */
 FQ_API int fq_router_topk_dev(const float* logits_dev, size_t seq, size_t n_expert, size_t top_k, int normalize,
                        int32_t* selected_dev, float* weights_dev, void* stream);

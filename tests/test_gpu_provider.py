@@ -232,6 +232,51 @@ def test_moe_layer_matches_oracle(P, fmt_name, hidden, out_pe, n_expert, top_k, 
         h.free()
 
 
+@pytest.mark.parametrize("tensor_arm,seq", [(0, 5), (0, 40), (1, 300)])
+def test_moe_expert_shards_sum_to_the_layer(P, torch, tensor_arm, seq):
+    """Two expert shards on one device: each serves half the experts, skips the other half's
+    pairs, and the partial outputs add up to the unsharded layer (f32 summation order aside)."""
+    from fucina_b200._lib import load
+
+    hidden, out_pe, n_expert, top_k = 256, 512, 8, 3
+    fmt = oracle.Q5_K
+    gate, up, down, x, _, sel, w = _moe_case("q5_k", hidden, out_pe, n_expert, top_k, seq, seed=80)
+    sel[0, :] = (0, 1, 2)          # a token served by shard 0 alone: shard 1 must write zeros for it
+    xd = torch.from_numpy(x).cuda()
+    sd = torch.from_numpy(sel.astype(np.int32)).cuda()
+    wd_ = torch.from_numpy(w).cuda()
+    load().fq_set_moe_tensor_for_test(tensor_arm)
+    try:
+        full = P.Weights.upload(fmt, gate, out_pe, hidden, n_expert), P.Weights.upload(fmt, up, out_pe, hidden, n_expert), \
+            P.Weights.upload(fmt, down, hidden, out_pe, n_expert)
+        want = torch.full((seq, hidden), float("nan"), device="cuda")
+        P.moe_layer_dev(*full, xd, seq, top_k, sd, wd_, want)
+        total = torch.zeros((seq, hidden), device="cuda")
+        per = n_expert // 2
+        for r in range(2):
+            sl_gu = slice(r * per * out_pe, (r + 1) * per * out_pe)
+            sl_d = slice(r * per * hidden, (r + 1) * per * hidden)
+            shard = P.Weights.upload(fmt, gate[sl_gu], out_pe, hidden, per), P.Weights.upload(fmt, up[sl_gu], out_pe, hidden, per), \
+                P.Weights.upload(fmt, down[sl_d], hidden, out_pe, per)
+            part = torch.full((seq, hidden), float("nan"), device="cuda")
+            P.moe_layer_ep_dev(*shard, xd, seq, top_k, sd, wd_, r * per, part)
+            P.synchronize()
+            if r == 1:
+                assert float(part[0].abs().max()) == 0.0
+            total += part
+            for h in shard:
+                h.free()
+        P.synchronize()
+        got, ref = total.cpu().numpy(), want.cpu().numpy()
+        assert np.isfinite(got).all()
+        scale = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+        assert float(np.max(np.abs(got - ref))) <= 1e-5 * scale
+        for h in full:
+            h.free()
+    finally:
+        load().fq_set_moe_tensor_for_test(-1)
+
+
 def test_moe_rejects_bad_expert_index(P):
     gate, up, down, x, _, sel, w = _moe_case("q5_k", 256, 256, 4, 2, 3, seed=60)
     wg = P.Weights.upload(oracle.Q5_K, gate, 256, 256, 4)

@@ -76,7 +76,26 @@ def _worker(rank: int, world: int, port: int, case: str, q):
             moe = par.ExpertParallelMoE(E, topk, ffn_rows)
             got = moe.forward(torch.from_numpy(x), torch.from_numpy(sel), torch.from_numpy(w)).numpy()
             want = oracle.moe_ffn(oracle.Q5_K, gate, up, down, x, sel, w, E, ffn)
-            q.put((rank, bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))))
+            ok = bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))
+
+            # fixed-size exchange: every rank computes its experts' partial sums for all tokens
+            def partial(x_all: torch.Tensor, sel_all: torch.Tensor, w_all: torch.Tensor) -> torch.Tensor:
+                xa, sa, wa = x_all.numpy(), sel_all.numpy(), w_all.numpy()
+                acc = np.zeros_like(xa)
+                for j in range(topk):   # slot order; a slot of another rank's expert adds nothing
+                    mine = (sa[:, j] // per) == rank
+                    if not mine.any():
+                        continue
+                    rows = np.ascontiguousarray(xa[mine])
+                    e = (sa[mine, j] % per).astype(np.int64).reshape(-1, 1)
+                    y = oracle.moe_ffn(oracle.Q5_K, g_loc, u_loc, d_loc, rows, e, np.ascontiguousarray(wa[mine, j:j + 1]), per, ffn)
+                    acc[mine] += y
+                return torch.from_numpy(acc)
+
+            got2 = moe.forward_gathered(torch.from_numpy(x), torch.from_numpy(sel), torch.from_numpy(w), partial).numpy()
+            scale = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+            ok = ok and float(np.max(np.abs(got2 - want))) <= 1e-5 * scale   # only the f32 summation order differs
+            q.put((rank, ok))
     finally:
         dist.destroy_process_group()
 
