@@ -266,7 +266,7 @@ __host__ __device__ inline SlabGeom slab_geom(int fmt, int slab) {
 }
 
 template <int FMT, int MB, bool FUSED, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, 1) decode_rows_kernel(const RowsArgs A, const __grid_constant__ CUtensorMap tmap) {
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_kernel(const RowsArgs A, const __grid_constant__ CUtensorMap tmap) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int kWarps = WARPS, kThreads = WARPS * 32;  // the warps split K; 16 when a row has at least 16 units
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -468,6 +468,17 @@ int pick_warps(int fmt, int k, int mb) {
 
 int pad_rows(size_t m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
 
+// Two CTAs per SM (8 warps, 2 stages, at most half the SM's shared memory each) for tile-major
+// weights. In-flight bytes per SM stay the same as one 16-warp CTA with a deeper ring, but a CTA of
+// the NEXT launch (programmatic dependent launch) can take the place of a CTA that has finished while
+// its neighbour is still working, so its first weight stages are already in shared memory when the
+// predecessor drains: the per-launch ramp disappears from chains of decode products.
+constexpr size_t kHalfSmemLimit = 113 * 1024;
+bool half_sm_config(const DevWeights& w, int mb) {
+    static const int env = getenv("FUCINA_B200_DECODE_HALF") ? atoi(getenv("FUCINA_B200_DECODE_HALF")) : 0;
+    return env != 0 && w.tile_rows != 0 && smem_bytes(w.fmt, w.k, mb, 1, 2, 8) <= kHalfSmemLimit;
+}
+
 // deepest pipeline that fits: more bytes in flight per SM first, then fewer barriers per byte
 bool pick_config(int fmt, int k, int mb, int* slab, int* stages) {
     const int warps = pick_warps(fmt, k, mb);
@@ -525,9 +536,9 @@ bool make_weight_tmap(const DevWeights& w, int mat, int unit_bytes, CUtensorMap*
 }
 
 template <int FMT, int MB>
-cudaError_t launch_fmt_mb(const RowsArgs& a, const CUtensorMap& tmap, bool fused, int grid, size_t smem, cudaStream_t st) {
+cudaError_t launch_fmt_mb(const RowsArgs& a, const CUtensorMap& tmap, bool fused, bool half, int grid, size_t smem, cudaStream_t st) {
     constexpr bool kWide = MB <= 2;  // the 16-warp form exists for the small-batch variants only
-    const bool wide = kWide && pick_warps(FMT, a.w.k, MB) == 16;
+    const bool wide = kWide && !half && pick_warps(FMT, a.w.k, MB) == 16;
     void (*kern)(const RowsArgs, const CUtensorMap) =
         wide ? (fused ? decode_rows_kernel<FMT, MB, true, kWide ? 16 : 8> : decode_rows_kernel<FMT, MB, false, kWide ? 16 : 8>)
              : (fused ? decode_rows_kernel<FMT, MB, true, 8> : decode_rows_kernel<FMT, MB, false, 8>);
@@ -535,6 +546,9 @@ cudaError_t launch_fmt_mb(const RowsArgs& a, const CUtensorMap& tmap, bool fused
     static bool granted[2][2] = {{false, false}, {false, false}};
     if (!granted[wide][fused]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
+        if (e != cudaSuccess) return e;
+        // all of the SM's configurable memory as shared memory, so two half-size CTAs fit side by side
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return e;
         granted[wide][fused] = true;
     }
@@ -556,12 +570,12 @@ cudaError_t launch_fmt_mb(const RowsArgs& a, const CUtensorMap& tmap, bool fused
 }
 
 template <int FMT>
-cudaError_t launch_fmt(const RowsArgs& a, const CUtensorMap& tmap, int mb, bool fused, int grid, size_t smem, cudaStream_t st) {
+cudaError_t launch_fmt(const RowsArgs& a, const CUtensorMap& tmap, int mb, bool fused, bool half, int grid, size_t smem, cudaStream_t st) {
     switch (mb) {
-        case 1: return launch_fmt_mb<FMT, 1>(a, tmap, fused, grid, smem, st);
-        case 2: return launch_fmt_mb<FMT, 2>(a, tmap, fused, grid, smem, st);
-        case 4: return launch_fmt_mb<FMT, 4>(a, tmap, fused, grid, smem, st);
-        default: return launch_fmt_mb<FMT, 8>(a, tmap, fused, grid, smem, st);
+        case 1: return launch_fmt_mb<FMT, 1>(a, tmap, fused, half, grid, smem, st);
+        case 2: return launch_fmt_mb<FMT, 2>(a, tmap, fused, half, grid, smem, st);
+        case 4: return launch_fmt_mb<FMT, 4>(a, tmap, fused, half, grid, smem, st);
+        default: return launch_fmt_mb<FMT, 8>(a, tmap, fused, half, grid, smem, st);
     }
 }
 
@@ -597,13 +611,15 @@ cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev,
         cudaError_t e = launch_quantize_acts_natural(a_dev, m, w.k, w.fmt != FQ_Q8_0, scratch, st);
         if (e != cudaSuccess) return e;
     }
-    int grid = sm_count;
+    const bool half = half_sm_config(w, mb);
+    if (half) a.stages = 2;
+    int grid = half ? 2 * sm_count : sm_count;
     if (grid > (w.n + 7) / 8) grid = (w.n + 7) / 8;
-    const size_t smem = smem_bytes(w.fmt, w.k, mb, a.slab, a.stages, pick_warps(w.fmt, w.k, mb));
+    const size_t smem = smem_bytes(w.fmt, w.k, mb, a.slab, a.stages, half ? 8 : pick_warps(w.fmt, w.k, mb));
     switch (w.fmt) {
-        case FQ_Q4_K: return launch_fmt<FQ_Q4_K>(a, tmap, mb, fused, grid, smem, st);
-        case FQ_Q5_K: return launch_fmt<FQ_Q5_K>(a, tmap, mb, fused, grid, smem, st);
-        default: return launch_fmt<FQ_Q8_0>(a, tmap, mb, fused, grid, smem, st);
+        case FQ_Q4_K: return launch_fmt<FQ_Q4_K>(a, tmap, mb, fused, half, grid, smem, st);
+        case FQ_Q5_K: return launch_fmt<FQ_Q5_K>(a, tmap, mb, fused, half, grid, smem, st);
+        default: return launch_fmt<FQ_Q8_0>(a, tmap, mb, fused, half, grid, smem, st);
     }
 }
 
