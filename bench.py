@@ -196,11 +196,19 @@ def run_ours(args) -> dict:
 
     # One CUDA graph per weight copy: a step is four microsecond-scale kernels, so the
     # eager launch cost of a Python caller would otherwise be what gets timed.
+    # A decode loop replays one graph per token holding hundreds of such kernels; here one "cycle"
+    # graph holds a step over each weight copy in turn (n_copies steps), so consecutive kernels keep
+    # their programmatic-launch overlap across step boundaries as they would inside a model's graph.
+    # Single-step graphs serve the remainder when the step count is not a multiple of n_copies.
     step_graphs = []
     for c in range(n_copies):
         with P.capture() as cap:
             step_dev(c)
         step_graphs.append(cap.graph)
+    with P.capture() as cap:
+        for c in range(n_copies):
+            step_dev(c)
+    step_cycle = cap.graph
     # the dominant kernel alone (the 32000 x 4096 lm_head product), one launch per copy
     big = max(range(len(STACK_N)), key=lambda i: STACK_N[i])
     big_graphs = []
@@ -208,32 +216,40 @@ def run_ours(args) -> dict:
         with P.capture() as cap:
             P.gemm_quant_nt_dev(stacks[c].weights[big], xs[big], ys[big], batch, mode=P.MODE_INT8)
         big_graphs.append(cap.graph)
+    with P.capture() as cap:
+        for c in range(n_copies):
+            P.gemm_quant_nt_dev(stacks[c].weights[big], xs[big], ys[big], batch, mode=P.MODE_INT8)
+    big_cycle = cap.graph
 
-    def timed_graphs(graphs, steps: int) -> float:
+    def timed_graphs(cycle, graphs, steps: int) -> float:
+        """Exactly `steps` steps: whole cycles of n_copies steps, then single-step graphs."""
         barrier(world)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(ext):
             e0.record()
-            for i in range(steps):
-                graphs[i % n_copies].launch()
+            for _ in range(steps // n_copies):
+                cycle.launch()
+            for i in range(steps % n_copies):
+                graphs[i].launch()
             e1.record()
         P.synchronize()
         barrier(world)
         return max_over_ranks(e0.elapsed_time(e1), world)
 
-    for i in range(args.warmup):
+    for i in range(max(args.warmup, 3)):
         step_graphs[i % n_copies].launch()
         big_graphs[i % n_copies].launch()
+        step_cycle.launch()
+        big_cycle.launch()
     P.synchronize()
 
     # ---- value: resident inputs, CUDA events on the library stream ----
     with ClockSampler(local) as clk:
-        ms = timed_graphs(step_graphs, args.steps)
+        ms = timed_graphs(step_cycle, step_graphs, args.steps)
         # keep the sampler busy for short runs so it sees the clocks under load
         t_end = time.time() + 0.6
         while time.time() < t_end:
-            for gph in step_graphs:
-                gph.launch()
+            step_cycle.launch()
             P.synchronize()
     launches = args.steps * len(STACK_N)  # one decode kernel per product, activation quantisation fused in
     bytes_step = stack_bytes(batch)
@@ -241,14 +257,15 @@ def run_ours(args) -> dict:
 
     # ---- roofline: the dominant kernel alone, back-to-back launches over the rotated copies ----
     k_n = args.steps
-    k_ms = timed_graphs(big_graphs, k_n)
+    k_ms = timed_graphs(big_cycle, big_graphs, k_n)
     peak, peak_src = measured_peaks()
     per_launch_bytes = STACK_N[big] * ROW_BYTES + batch * K * 4 + batch * STACK_N[big] * 4
     achieved = per_launch_bytes / (k_ms / k_n * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "traffic": None,
                 "kernel": "decode_rows_kernel<Q4_K, MB=1, fused act-quant> on 32000x4096",
-                "peak_source": peak_src, "launches_timed": k_n, "us_per_launch": round(k_ms / k_n * 1e3, 3),
+                "peak_source": peak_src, "launches_timed": k_n,
+                "timing": "CUDA events around back-to-back launches (graph replay, consecutive launches overlap by programmatic dependent launch)", "us_per_launch": round(k_ms / k_n * 1e3, 3),
                 "bytes_per_launch": per_launch_bytes, "frac_of_8TBs": round(achieved / 8000.0, 4)}
 
     # ---- e2e: blocking C-ABI call, host buffers, resident weights ----

@@ -5,7 +5,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libfucina_b200.so")
+# FUCINA_B200_LIB points at another build of the same library (a diagnostic build, for instance)
+LIB_PATH = os.environ.get("FUCINA_B200_LIB") or os.path.join(_HERE, "lib", "libfucina_b200.so")
 
 c_size = C.c_size_t
 c_void = C.c_void_p

@@ -39,6 +39,29 @@ namespace {
 constexpr int kMaxStages = 4;
 constexpr unsigned kWaitLimit = 1u << 20;
 
+// Diagnostic build only (-DFQ_TIMELINE): thread 0 of every CTA stamps the phases of the last launch
+// into shared memory (a global store here would sit in front of the barrier-init fence and distort
+// what it measures) and copies them out when the CTA is done.
+#ifdef FQ_TIMELINE
+constexpr int kTimelineSlots = 16;
+__device__ unsigned long long g_timeline[1024 * kTimelineSlots];
+__shared__ unsigned long long s_timeline[kTimelineSlots];
+__device__ __forceinline__ void stamp(int slot) {
+    if (threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+        s_timeline[slot] = t;
+    }
+}
+__device__ __forceinline__ void stamp_flush() {
+    if (threadIdx.x == 0 && blockIdx.x < 1024)
+        for (int i = 0; i < kTimelineSlots; ++i) g_timeline[blockIdx.x * kTimelineSlots + i] = s_timeline[i];
+}
+#else
+__device__ __forceinline__ void stamp(int) {}
+__device__ __forceinline__ void stamp_flush() {}
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -69,6 +92,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
                  "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// The same copy marked evict-first in L2: decode weights are read once per token, so they should
+// not push the activations and outputs of the surrounding kernels out of the cache.
+__device__ __forceinline__ uint64_t evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_load_stream(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar), "l"(pol)
                  : "memory");
 }
 
@@ -286,14 +321,18 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
     const uint32_t slot0 = smem_u32(slots) + (uint32_t)((warp * A.stages) * 32 + lane) * G.slot_bytes;
     const uint32_t bar0 = smem_u32(bars) + warp * kMaxStages * 8;
 
+    stamp(0);
     if (lane == 0)
         for (int s = 0; s < A.stages; ++s) mbar_init(bar0 + s * 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncwarp();
+    stamp(7);
 
     // this CTA's contiguous row range, balanced over the grid
-    const int r_begin = (int)((long long)n * blockIdx.x / gridDim.x);
-    const int r_end = (int)((long long)n * (blockIdx.x + 1) / gridDim.x);
+    // (or, for a matrix with no more 32-row tiles than CTAs, exactly one storage tile each: one full-width
+    // pipeline step per warp instead of two partial ones)
+    const int r_begin = A.rows_per_cta ? (int)blockIdx.x * A.rows_per_cta : (int)((long long)n * blockIdx.x / gridDim.x);
+    const int r_end = A.rows_per_cta ? min(n, r_begin + A.rows_per_cta) : (int)((long long)n * (blockIdx.x + 1) / gridDim.x);
     // row tiles of this CTA: 32 rows from r_begin on (row-major), or the pieces of its range inside
     // each 32-row storage tile (tile-major: a piece is contiguous in HBM, a straddle is two pieces)
     const bool tiled = A.w.tile_rows != 0;
@@ -310,6 +349,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
     };
     const int total = ntiles * my_slabs;  // pipeline steps of this warp
     const uint8_t* wbase = A.w.base + (size_t)A.mat * A.w.mat_stride;
+    const uint64_t l2_policy = A.l2_stream ? evict_first_policy() : 0;
 
     auto issue = [&](int it) {
         const int tile = it / my_slabs, sl = warp + kWarps * (it % my_slabs);
@@ -325,7 +365,10 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
                 mbar_arrive_expect_tx(bar, bytes);
                 const uint8_t* src = wbase + (size_t)(row0 >> 5) * ((size_t)32 * A.w.row_stride) + (size_t)sl * 32 * G.unit_bytes +
                                      (size_t)(row0 & 31) * G.unit_bytes;
-                bulk_load(slot0 + (uint32_t)stage * 32 * G.slot_bytes, src, bytes, bar);
+                if (A.l2_stream)
+                    bulk_load_stream(slot0 + (uint32_t)stage * 32 * G.slot_bytes, src, bytes, bar, l2_policy);
+                else
+                    bulk_load(slot0 + (uint32_t)stage * 32 * G.slot_bytes, src, bytes, bar);
             }
             return;
         }
@@ -357,7 +400,9 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
 
     // let the next kernel of the stream begin its own launch; it waits below before it reads or writes
     // anything this kernel (or an earlier one) may still be producing
+    stamp(8);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    stamp(9);
 
     // start streaming weights before touching the activations
     const int prefetch = min(A.stages, total);
@@ -365,7 +410,9 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
 
     // everything before this point read only immutable weights; activations and outputs may belong
     // to the preceding kernel
+    stamp(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    stamp(2);
 
     // activation records: quantise here (FUSED) or copy the pre-quantised records
     if (FUSED) {
@@ -399,6 +446,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
     else
         __syncthreads();
 
+    stamp(3);
     const ActView V = {smem_u32(acts), (uint32_t)NS.row, (uint32_t)NS.aq, (uint32_t)(NS.aq + NS.sums)};
     bool ok = true;
     int it = 0;
@@ -414,6 +462,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
                 ok = false;
                 break;
             }
+            if (it == 0) stamp(4);
             const int nu = min(A.slab, units - sl * A.slab);
             const uint32_t p = slot0 + (uint32_t)stage * 32 * G.slot_bytes;
             for (int u = 0; u < nu && !A.skip_compute; ++u) {
@@ -426,6 +475,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
             if (it + A.stages < total) issue(it + A.stages);
         }
         // cross-warp sum of the K slices; two reduction buffers alternate so one CTA barrier per tile is enough
+        if (tile == ntiles - 1) stamp(5);
         float* rbuf = red + (size_t)(tile & 1) * kWarps * MB * 32;
 #pragma unroll
         for (int b = 0; b < MB; ++b) rbuf[(warp * MB + b) * 32 + lane] = acc[b];
@@ -440,6 +490,8 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
             if (lane < nvalid && b < A.m) A.c[(size_t)b * A.ldc + row0 + lane] = s;
         }
     }
+    stamp(6);
+    stamp_flush();
     if (!ok) {
         if (lane == 0) *(volatile int*)A.status = FQ_ERR_TIMEOUT;
         // give copies still in flight a bounded chance to land before the CTA's shared memory is released
@@ -447,7 +499,11 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
     }
 }
 
+#ifdef FQ_TIMELINE
+constexpr size_t kSmemLimit = 227 * 1024 - 256;  // the stamps live in static shared memory
+#else
 constexpr size_t kSmemLimit = 227 * 1024;
+#endif
 constexpr int kFusedMaxRows = 4;  // up to here each CTA quantises the activations itself
 
 size_t smem_bytes(int fmt, int k, int mb, int slab, int stages, int warps) {
@@ -597,14 +653,20 @@ cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev,
                                int sm_count, int* status, cudaStream_t st) {
     const int mb = pad_rows((size_t)m);
     static const int skip = getenv("FUCINA_B200_DECODE_SKIP_COMPUTE") ? 1 : 0;  // diagnosis: copy pipeline only, outputs are garbage
-    RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0, skip};
+    static const int l2_stream = getenv("FUCINA_B200_DECODE_L2_STREAM") ? atoi(getenv("FUCINA_B200_DECODE_L2_STREAM")) : 1;
+    RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0, skip, l2_stream, 0};
     if (!pick_config(w.fmt, w.k, mb, &a.slab, &a.stages)) return cudaErrorInvalidValue;
     // K-quant units are an odd number of 16-byte chunks: one tensor copy per warp step instead of 32
     // per-lane bulk copies (small bulk copies are issue-rate bound in the copy engine)
     CUtensorMap tmap;
     memset(&tmap, 0, sizeof tmap);
     static const bool no_tmap = getenv("FUCINA_B200_DECODE_NO_TMAP") != nullptr;
-    if (w.tile_rows) a.slab = 1;  // tile-major runs are one unit wide
+    if (w.tile_rows) {
+        a.slab = 1;  // tile-major runs are one unit wide
+        // two stages of 16 x 4608 bytes keep ~144 KB per SM in flight; a deeper queue measured slower
+        static const bool forced = getenv("FUCINA_B200_DECODE_STAGES") != nullptr;
+        if (!forced && a.stages > 2) a.stages = 2;
+    }
     if (!w.tile_rows && w.fmt != FQ_Q8_0 && a.slab == 1 && !no_tmap && make_weight_tmap(w, mat, slab_geom(w.fmt, 1).unit_bytes, &tmap)) a.use_tmap = 1;
     const bool fused = m <= kFusedMaxRows;
     if (!fused) {
@@ -615,6 +677,11 @@ cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev,
     if (half) a.stages = 2;
     int grid = half ? 2 * sm_count : sm_count;
     if (grid > (w.n + 7) / 8) grid = (w.n + 7) / 8;
+    static const bool no_align = getenv("FUCINA_B200_DECODE_NO_ALIGN") != nullptr;
+    if (w.tile_rows && !half && !no_align && (w.n + 31) / 32 <= sm_count) {
+        grid = (w.n + 31) / 32;
+        a.rows_per_cta = 32;
+    }
     const size_t smem = smem_bytes(w.fmt, w.k, mb, a.slab, a.stages, half ? 8 : pick_warps(w.fmt, w.k, mb));
     switch (w.fmt) {
         case FQ_Q4_K: return launch_fmt<FQ_Q4_K>(a, tmap, mb, fused, half, grid, smem, st);
@@ -622,5 +689,12 @@ cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev,
         default: return launch_fmt<FQ_Q8_0>(a, tmap, mb, fused, half, grid, smem, st);
     }
 }
+
+#ifdef FQ_TIMELINE
+// diagnostic build: copy the phase stamps of the last decode launch to the host
+extern "C" __attribute__((visibility("default"))) int fq_debug_timeline(unsigned long long* out, int ctas) {
+    return (int)cudaMemcpyFromSymbol(out, g_timeline, sizeof(unsigned long long) * kTimelineSlots * ctas);
+}
+#endif
 
 }  // namespace fq

@@ -68,6 +68,8 @@ struct RowsArgs {
     int* status; // device-visible status word (FQ_ERR_TIMEOUT on a wait that gave up)
     int use_tmap; // weights arrive by 2-D tensor copies (one per warp step) instead of per-lane bulk copies
     int skip_compute; // diagnosis only: stream the weights, skip the arithmetic
+    int l2_stream;    // weight copies carry an evict-first L2 hint (tile-major form)
+    int rows_per_cta; // 0: rows split evenly over the grid; else CTA b serves rows [b*rows_per_cta, +rows_per_cta)
 };
 // true when the shape is one the kernel serves (format, K, m, shared memory)
 bool decode_rows_eligible(const DevWeights& w, size_t m);

@@ -224,7 +224,13 @@ def test_moe_layer_matches_oracle(P, fmt_name, hidden, out_pe, n_expert, top_k, 
     wg = P.Weights.upload(fmt, gate, out_pe, hidden, n_expert)
     wu = P.Weights.upload(fmt, up, out_pe, hidden, n_expert)
     wd = P.Weights.upload(fmt, down, hidden, out_pe, n_expert)
-    got = P.moe_layer(wg, wu, wd, x, sel, w)
+    from fucina_b200._lib import load
+
+    load().fq_set_moe_tensor_for_test(0)   # the int8 arm is the one this oracle restates; larger batches would pick tensor cores
+    try:
+        got = P.moe_layer(wg, wu, wd, x, sel, w)
+    finally:
+        load().fq_set_moe_tensor_for_test(-1)
     want = oracle.moe_ffn(fmt, gate, up, down, x, sel, w, n_expert, out_pe)
     # expf on the device and in the oracle may differ by an ulp, and the requantisation
     # of g can turn that into one int8 step on isolated elements: the layer bound is the
