@@ -3,10 +3,13 @@
 // c[t, j] = sum_e bf16(a[t, e]) * bf16(dequant(W)[j, e]), f32 accumulate, for
 // m > 16 token rows (reference role: fucina_mul_mm_mma_*, src/backend/cuda/
 // kernels.cu:302-427, which rounds both operands to f16 and uses wmma). The
-// dequantised f32 weight is computed with the CPU decoders' unfused formula
-// (q4_k.zig:1954-1972, q5_k.zig:1154-1167, q8k.zig:95-114) and rounded once to
-// bf16, so the operands equal those of the f64 reference over bf16-rounded
-// operands; results differ from it only by f32 accumulation.
+// dequantised weight follows the CPU decoders' formula (q4_k.zig:1954-1972,
+// q5_k.zig:1154-1167, q8k.zig:95-114) evaluated with one fused multiply-add per
+// weight and rounded to bf16: it equals the bf16 rounding of the reference's
+// unfused f32 value except where that value lies within ~2^-20 (relative) of a
+// bf16 rounding boundary, about one weight in two thousand, and then by one bf16
+// ulp. Results differ from the f64 reference over bf16-rounded operands by that
+// and by f32 accumulation.
 //
 // One persistent CTA per SM walks output tiles of 128 weight rows x 256 tokens.
 //   warp 0        TMA producer: 256 x 64 bf16 token tiles (128-byte swizzle) into a 4-stage ring
@@ -36,9 +39,19 @@ namespace {
 constexpr int BM = 128;        // weight rows per tile (UMMA M)
 constexpr int BN = 256;        // tokens per tile (UMMA N)
 constexpr int BK = 64;         // K elements per ring stage (128 bytes of bf16: one swizzle span)
-constexpr int STAGES = 4;
+constexpr int A_STAGES = 3;    // ring of dequantised weight tiles
+constexpr int B_STAGES = 4;    // ring of token tiles
+constexpr int RAW_STAGES = 2;  // ring of packed K-quant units (one unit = 256 weights of 128 rows = four K slabs)
 constexpr int A_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_BYTES = BN * BK * 2;   // 32 KB
+// K-quant blocks are staged in shared memory by the copy engine (their 144/176 bytes are 16-byte
+// multiples); Q8_0's split rows are read by the dequantising threads themselves.
+template <int FMT>
+struct Staged {
+    static constexpr bool on = FMT == FQ_Q4_K || FMT == FQ_Q5_K;
+    static constexpr int unit_bytes = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 0;
+    static constexpr int raw_bytes = BM * unit_bytes;
+};
 constexpr int kDequantWarps = 8;
 constexpr int kEpilogueWarps = 4;
 constexpr int kThreads = (2 + kDequantWarps + kEpilogueWarps) * 32;  // 448
@@ -72,7 +85,8 @@ __device__ __forceinline__ TileRef tile_ref(const TcArgs& A, int tile, int row_t
 }
 
 struct __align__(8) Barriers {
-    uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
+    uint64_t full_a[A_STAGES], empty_a[A_STAGES], full_b[B_STAGES], empty_b[B_STAGES], raw_full[RAW_STAGES], raw_empty[RAW_STAGES],
+        tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -135,6 +149,17 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -143,6 +168,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // ---- packed weights of one 64-element K slab of one row: loaded one slab ahead, expanded later ----
 template <int FMT>
 struct Raw;
+
+// Four byte-sized levels q0..q3 of one word -> bf16(a * (B + q) + c), packed two per word. Byte i is
+// permuted straight into the mantissa of the f32 constant B, so no integer-to-float conversion is
+// issued, and the multiply-adds run two per instruction. Levels below 128 (K-quants) use B = 128.0f
+// (0x43000000 | q << 16 == 128 + q: mantissa bits 16..22); full bytes (Q8_0) use B = 32768.0f
+// (0x47000000 | q << 8 == 32768 + q: mantissa bits 8..15).
+template <bool FULL_BYTE>
+__device__ __forceinline__ void expand_bytes(uint32_t v, float2 a2, float2 c2, uint32_t& out01, uint32_t& out23) {
+    constexpr uint32_t base = FULL_BYTE ? 0x47000000u : 0x43000000u;
+    constexpr uint32_t s0 = FULL_BYTE ? 0x7404 : 0x7044, s1 = FULL_BYTE ? 0x7414 : 0x7144, s2 = FULL_BYTE ? 0x7424 : 0x7244,
+                       s3 = FULL_BYTE ? 0x7434 : 0x7344;
+    const float2 x01 = make_float2(__uint_as_float(__byte_perm(v, base, s0)), __uint_as_float(__byte_perm(v, base, s1)));
+    const float2 x23 = make_float2(__uint_as_float(__byte_perm(v, base, s2)), __uint_as_float(__byte_perm(v, base, s3)));
+    const float2 w01 = __ffma2_rn(a2, x01, c2), w23 = __ffma2_rn(a2, x23, c2);
+    out01 = pack_bf16(w01.x, w01.y);
+    out23 = pack_bf16(w23.x, w23.y);
+}
 
 __device__ __forceinline__ void scale_min(const uint4& hdr, int s, int& sc, int& mn) {
     // K-quant 6-bit pair s from the 12 scale bytes in hdr.y/z/w (reference backend/quant/q8k.zig:637-648)
@@ -171,22 +213,29 @@ struct Raw<FQ_Q4_K> {
             asm volatile("prefetch.global.L2 [%0];" ::"l"(b + ustride + 128));
         }
     }
-    // d*sc*q - dmin*mn, unfused, rounded once to bf16 (q4_k.zig:1954-1972)
+    // slab p (0..3) of the block staged at shared address `blk`
+    __device__ __forceinline__ void load_header(uint32_t blk) { hdr = lds128(blk); }
+    __device__ __forceinline__ void load_slab(uint32_t blk, int p) {
+        q0 = lds128(blk + 16 + p * 32);
+        q1 = lds128(blk + 32 + p * 32);
+    }
+    // w = d*sc*q - dmin*mn (q4_k.zig:1954-1972), rounded to bf16. No integer-to-float conversion:
+    // the nibble is dropped into the mantissa of 128.0f (f32 0x43000000 | q << 16 == 128 + q exactly)
+    // and one fused multiply-add per weight applies w = dsc * (128 + q) - (off + 128 * dsc).
     __device__ __forceinline__ void expand(int ks, int h, uint32_t out[16]) const {
         const int s = 2 * (ks & 3) + h;
         const __half2 dm = *reinterpret_cast<const __half2*>(&hdr.x);
         int sc, mn;
         scale_min(hdr, s, sc, mn);
         const float dsc = __fmul_rn(__low2float(dm), (float)sc), off = __fmul_rn(__high2float(dm), (float)mn);
+        const float2 a2 = make_float2(dsc, dsc);
+        const float cc = __fmaf_rn(dsc, -128.0f, -off);
+        const float2 c2 = make_float2(cc, cc);
         const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const uint32_t v = h ? (wq[j] >> 4) : wq[j];
-            float f[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) f[i] = __fsub_rn(__fmul_rn(dsc, (float)((v >> (8 * i)) & 15u)), off);
-            out[2 * j] = pack_bf16(f[0], f[1]);
-            out[2 * j + 1] = pack_bf16(f[2], f[3]);
+            const uint32_t v = (h ? (wq[j] >> 4) : wq[j]) & 0x0f0f0f0fu;
+            expand_bytes<false>(v, a2, c2, out[2 * j], out[2 * j + 1]);
         }
     }
 };
@@ -207,6 +256,15 @@ struct Raw<FQ_Q5_K> {
             asm volatile("prefetch.global.L2 [%0];" ::"l"(b + ustride + 128));
         }
     }
+    __device__ __forceinline__ void load_header(uint32_t blk) {
+        hdr = lds128(blk);
+        h0 = lds128(blk + 16);
+        h1 = lds128(blk + 32);
+    }
+    __device__ __forceinline__ void load_slab(uint32_t blk, int p) {
+        q0 = lds128(blk + 48 + p * 32);
+        q1 = lds128(blk + 64 + p * 32);
+    }
     // as Q4_K with q = nibble + 16 * bit s of qh[i] (q5_k.zig:1154-1167, :1259-1264)
     __device__ __forceinline__ void expand(int ks, int h, uint32_t out[16]) const {
         const int s = 2 * (ks & 3) + h;
@@ -214,20 +272,16 @@ struct Raw<FQ_Q5_K> {
         int sc, mn;
         scale_min(hdr, s, sc, mn);
         const float dsc = __fmul_rn(__low2float(dm), (float)sc), off = __fmul_rn(__high2float(dm), (float)mn);
+        const float2 a2 = make_float2(dsc, dsc);
+        const float cc = __fmaf_rn(dsc, -128.0f, -off);
+        const float2 c2 = make_float2(cc, cc);
         const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
         const uint32_t hb[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const uint32_t v = h ? (wq[j] >> 4) : wq[j];
-            const uint32_t hi = (hb[j] >> s) & 0x01010101u;
-            float f[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t q = ((v >> (8 * i)) & 15u) + (((hi >> (8 * i)) & 1u) << 4);
-                f[i] = __fsub_rn(__fmul_rn(dsc, (float)q), off);
-            }
-            out[2 * j] = pack_bf16(f[0], f[1]);
-            out[2 * j + 1] = pack_bf16(f[2], f[3]);
+            const uint32_t nib = (h ? (wq[j] >> 4) : wq[j]) & 0x0f0f0f0fu;
+            const uint32_t v = nib + ((hb[j] >> s) & 0x01010101u) * 16u;  // five-bit levels, one per byte
+            expand_bytes<false>(v, a2, c2, out[2 * j], out[2 * j + 1]);
         }
     }
 };
@@ -243,38 +297,49 @@ struct Raw<FQ_Q8_0> {
         q1 = __ldg(reinterpret_cast<const uint4*>(unit0 + (size_t)blk * 32 + 16));
         d = h2f(__ldg(reinterpret_cast<const uint16_t*>(unit0 + w.k) + blk));
     }
-    __device__ __forceinline__ void expand(int, int, uint32_t out[16]) const {  // f32(q) * d (q8k.zig:95-114)
+    // f32(q) * d (q8k.zig:95-114), exactly: u = q + 128 goes into the mantissa of 32768.0f and
+    // w = d * (32768 + u) - d * 32896 in one fused multiply-add (the constant term is exact in f32)
+    __device__ __forceinline__ void load_header(uint32_t) {}
+    __device__ __forceinline__ void load_slab(uint32_t, int) {}
+    __device__ __forceinline__ void expand(int, int, uint32_t out[16]) const {
         const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const float2 a2 = make_float2(d, d);
+        const float cc = __fmul_rn(d, -32896.0f);
+        const float2 c2 = make_float2(cc, cc);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float f[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) f[i] = __fmul_rn((float)(int8_t)((wq[j] >> (8 * i)) & 0xffu), d);
-            out[2 * j] = pack_bf16(f[0], f[1]);
-            out[2 * j + 1] = pack_bf16(f[2], f[3]);
-        }
+        for (int j = 0; j < 8; ++j) expand_bytes<true>(wq[j] ^ 0x80808080u, a2, c2, out[2 * j], out[2 * j + 1]);
     }
 };
 
 template <int FMT>
-__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, const __grid_constant__ CUtensorMap tmap_tokens) {
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, const __grid_constant__ CUtensorMap tmap_tokens,
+                                                              const __grid_constant__ CUtensorMap tmap_weights) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    // 1024-byte aligned ring: [A stages][B stages][barriers]
+    // 1024-byte aligned rings: [A stages][B stages][packed-weight stages][barriers]
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = smem;
-    uint8_t* sB = smem + STAGES * A_BYTES;
-    Barriers* B = reinterpret_cast<Barriers*>(smem + STAGES * (A_BYTES + B_BYTES));
+    uint8_t* sB = sA + A_STAGES * A_BYTES;
+    uint8_t* sRaw = sB + B_STAGES * B_BYTES;
+    Barriers* B = reinterpret_cast<Barriers*>(sRaw + RAW_STAGES * Staged<FMT>::raw_bytes);
+    constexpr bool kStaged = Staged<FMT>::on;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = A.w.n, k = A.w.k, m = A.m;
-    const int kslabs = k / BK;
+    const int kslabs = k / BK, units = k >> 8;
     const int row_tiles = (n + BM - 1) / BM, tok_tiles = (m + BN - 1) / BN;
     const int n_tiles = A.table ? *A.n_tiles_dev : row_tiles * tok_tiles;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < A_STAGES; ++s) {
             mbar_init(smem_u32(&B->full_a[s]), kDequantWarps * 32);
+            mbar_init(smem_u32(&B->empty_a[s]), 1);
+        }
+        for (int s = 0; s < B_STAGES; ++s) {
             mbar_init(smem_u32(&B->full_b[s]), 1);
-            mbar_init(smem_u32(&B->empty[s]), 1);
+            mbar_init(smem_u32(&B->empty_b[s]), 1);
+        }
+        for (int s = 0; s < RAW_STAGES; ++s) {
+            mbar_init(smem_u32(&B->raw_full[s]), 1);
+            mbar_init(smem_u32(&B->raw_empty[s]), kDequantWarps * 32);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&B->tmem_full[i]), 1);
@@ -295,47 +360,83 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
     const uint32_t tmem = B->tmem_base;
 
     if (warp == 0) {
-        // ---------------- TMA producer: token tiles ----------------
+        // ---------------- copy-engine producer: packed weight units (K-quants) and token tiles ----------------
         if (lane == 0) {
-            int g = 0;
-            for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x) {
+            constexpr int ub = Staged<FMT>::unit_bytes;
+            int gb = 0, gu = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
                 const TileRef T = tile_ref(A, tile, row_tiles);
-                for (int ks = 0; ks < kslabs; ++ks, ++g) {
-                    const int s = g % STAGES;
-                    if (!mbar_wait(smem_u32(&B->empty[s]), ((g / STAGES) & 1) ^ 1, B, A.status)) break;
-                    const uint32_t bar = smem_u32(&B->full_b[s]);
-                    mbar_arrive_expect_tx(bar, B_BYTES);
-                    asm volatile(
-                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                            smem_u32(sB + s * B_BYTES)),
-                        "l"(&tmap_tokens), "r"(ks * BK), "r"(T.tok0), "r"(bar)
-                        : "memory");
+                for (int u = 0; u < units && ok; ++u) {
+                    if (kStaged) {
+                        const int rs = gu % RAW_STAGES;
+                        if (!mbar_wait(smem_u32(&B->raw_empty[rs]), ((gu / RAW_STAGES) & 1) ^ 1, B, A.status)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t bar = smem_u32(&B->raw_full[rs]);
+                        const uint32_t dst = smem_u32(sRaw + rs * Staged<FMT>::raw_bytes);
+                        if (A.w.tile_rows) {
+                            // tile-major storage: unit u of 32 consecutive rows is one contiguous run
+                            const int n_store = (n + 31) >> 5;
+                            const int valid = min(BM / 32, n_store - T.rt * (BM / 32));
+                            mbar_arrive_expect_tx(bar, (uint32_t)(valid * 32 * ub));
+                            const uint8_t* wbase = A.w.base + (size_t)T.mat * A.w.mat_stride;
+                            for (int j = 0; j < valid; ++j)
+                                bulk_load(dst + j * 32 * ub, wbase + (size_t)(T.rt * (BM / 32) + j) * ((size_t)32 * A.w.row_stride) + (size_t)u * 32 * ub,
+                                          32 * ub, bar);
+                        } else {
+                            // row-major storage: a box of 128 rows x one unit; rows past the end of the tensor arrive as zeros
+                            mbar_arrive_expect_tx(bar, (uint32_t)(BM * ub));
+                            asm volatile(
+                                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                                "l"(&tmap_weights), "r"(u * ub), "r"(T.mat * n + T.rt * BM), "r"(bar)
+                                : "memory");
+                        }
+                        ++gu;
+                    }
+                    for (int p = 0; p < 4; ++p, ++gb) {
+                        const int s = gb % B_STAGES;
+                        if (!mbar_wait(smem_u32(&B->empty_b[s]), ((gb / B_STAGES) & 1) ^ 1, B, A.status)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t bar = smem_u32(&B->full_b[s]);
+                        mbar_arrive_expect_tx(bar, B_BYTES);
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                                smem_u32(sB + s * B_BYTES)),
+                            "l"(&tmap_tokens), "r"((u * 4 + p) * BK), "r"(T.tok0), "r"(bar)
+                            : "memory");
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            int g = 0, t = 0;
+            int ga = 0, gb = 0, t = 0;
             for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
                 // the epilogue of the tile that last used this accumulator must have drained it
                 const uint32_t acc = tmem + (uint32_t)(t & 1) * BN;
                 if (!mbar_wait(smem_u32(&B->tmem_empty[t & 1]), ((t >> 1) & 1) ^ 1, B, A.status)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 bool ok = true;
-                for (int ks = 0; ks < kslabs; ++ks, ++g) {
-                    const int s = g % STAGES;
-                    const uint32_t ph = (g / STAGES) & 1;
-                    if (!mbar_wait(smem_u32(&B->full_a[s]), ph, B, A.status) || !mbar_wait(smem_u32(&B->full_b[s]), ph, B, A.status)) {
+                for (int ks = 0; ks < kslabs; ++ks, ++ga, ++gb) {
+                    const int sa = ga % A_STAGES, sb = gb % B_STAGES;
+                    if (!mbar_wait(smem_u32(&B->full_a[sa]), (ga / A_STAGES) & 1, B, A.status) ||
+                        !mbar_wait(smem_u32(&B->full_b[sb]), (gb / B_STAGES) & 1, B, A.status)) {
                         ok = false;
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t da = umma_desc(smem_u32(sA + s * A_BYTES)), db = umma_desc(smem_u32(sB + s * B_BYTES));
+                    const uint64_t da = umma_desc(smem_u32(sA + sa * A_BYTES)), db = umma_desc(smem_u32(sB + sb * B_BYTES));
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk)  // 32 bytes along K per instruction: +2 in the 16-byte address field
                         umma_bf16(acc, da + 2 * kk, db + 2 * kk, (ks | kk) ? 1u : 0u);
-                    umma_commit(smem_u32(&B->empty[s]));  // the stage is free once these MMAs have read it
+                    // both stages are free once these MMAs have read them
+                    umma_commit(smem_u32(&B->empty_a[sa]));
+                    umma_commit(smem_u32(&B->empty_b[sb]));
                 }
                 if (!ok) break;
                 umma_commit(smem_u32(&B->tmem_full[t & 1]));
@@ -348,36 +449,62 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         const int h = dt >> 7;             // which 32-weight half of the 64-element slab
         constexpr int ub = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 256;
         const size_t ustride = unit_stride(A.w, ub);
-        int g = 0;
-        for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x) {
-            const TileRef T = tile_ref(A, tile, row_tiles);
-            const uint8_t* wbase = A.w.base + (size_t)T.mat * A.w.mat_stride;
-            const int row = min(T.rt * BM + r, n - 1);
-            const uint8_t* unit0 = row_unit0(A.w, wbase, row, ub);
-            bool ok = true;
-            Raw<FMT> next;
-            next.load(A.w, unit0, ustride, 0, h);
-            for (int ks = 0; ks < kslabs; ++ks, ++g) {
-                const int s = g % STAGES;
-                const Raw<FMT> cur = next;
-                if (ks + 1 < kslabs) next.load(A.w, unit0, ustride, ks + 1, h);  // one slab ahead: the loads fly while this slab is expanded
-                uint32_t v[16];
-                cur.expand(ks, h, v);
-                if (!mbar_wait(smem_u32(&B->empty[s]), ((g / STAGES) & 1) ^ 1, B, A.status)) {
-                    ok = false;
-                    break;
-                }
-                // row r of the K-major tile: 128 bytes, 16-byte chunk j stored at j ^ (r % 8) (128-byte swizzle)
-                uint8_t* rowp = sA + s * A_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+        int ga = 0, gu = 0;
+        bool ok = true;
+        // expand one slab into row r of A stage (ga % A_STAGES): 128 bytes, 16-byte chunk j stored at
+        // j ^ (r % 8) (128-byte swizzle); generic-proxy stores are fenced towards the MMA's async proxy
+        auto publish = [&](const uint32_t (&v)[16]) -> bool {
+            const int s = ga % A_STAGES;
+            if (!mbar_wait(smem_u32(&B->empty_a[s]), ((ga / A_STAGES) & 1) ^ 1, B, A.status)) return false;
+            uint8_t* rowp = sA + s * A_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int chunk = (h * 4 + j) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA's async proxy
-                mbar_arrive(smem_u32(&B->full_a[s]));
+            for (int j = 0; j < 4; ++j) {
+                const int chunk = (h * 4 + j) ^ (r & 7);
+                *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             }
-            if (!ok) break;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(smem_u32(&B->full_a[s]));
+            ++ga;
+            return true;
+        };
+        for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
+            const TileRef T = tile_ref(A, tile, row_tiles);
+            if (kStaged) {
+                for (int u = 0; u < units && ok; ++u, ++gu) {
+                    const int rs = gu % RAW_STAGES;
+                    if (!mbar_wait(smem_u32(&B->raw_full[rs]), (gu / RAW_STAGES) & 1, B, A.status)) {
+                        ok = false;
+                        break;
+                    }
+                    // this row's block: lanes are 144/176 bytes apart, an odd number of 16-byte chunks, so the
+                    // 128-bit shared loads of a quarter warp fall on distinct banks
+                    const uint32_t blk = smem_u32(sRaw + rs * Staged<FMT>::raw_bytes) + (uint32_t)r * Staged<FMT>::unit_bytes;
+                    Raw<FMT> raw;
+                    raw.load_header(blk);
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        raw.load_slab(blk, p);
+                        uint32_t v[16];
+                        raw.expand(p, h, v);
+                        if (!(ok = publish(v))) break;
+                    }
+                    // the loads above have returned (their values went into the stores): the unit may be overwritten
+                    mbar_arrive(smem_u32(&B->raw_empty[rs]));
+                }
+            } else {
+                const uint8_t* wbase = A.w.base + (size_t)T.mat * A.w.mat_stride;
+                const int row = min(T.rt * BM + r, n - 1);
+                const uint8_t* unit0 = row_unit0(A.w, wbase, row, ub);
+                Raw<FMT> next;
+                next.load(A.w, unit0, ustride, 0, h);
+                for (int ks = 0; ks < kslabs; ++ks) {
+                    const Raw<FMT> cur = next;
+                    if (ks + 1 < kslabs) next.load(A.w, unit0, ustride, ks + 1, h);  // one slab ahead: the loads fly while this slab is expanded
+                    uint32_t v[16];
+                    cur.expand(ks, h, v);
+                    if (!(ok = publish(v))) break;
+                }
+            }
         }
     } else {
         // ---------------- epilogue: accumulator lane = weight row, column = token ----------------
@@ -454,15 +581,15 @@ EncodeTiledFn encode_fn() {
 }
 
 template <int FMT>
-cudaError_t launch_tc(const TcArgs& a, const CUtensorMap& tmap, int grid, cudaStream_t st) {
-    const size_t smem = (size_t)STAGES * (A_BYTES + B_BYTES) + sizeof(Barriers) + 1024;
+cudaError_t launch_tc(const TcArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap_w, int grid, cudaStream_t st) {
+    const size_t smem = (size_t)A_STAGES * A_BYTES + (size_t)B_STAGES * B_BYTES + (size_t)RAW_STAGES * Staged<FMT>::raw_bytes + sizeof(Barriers) + 1024;
     static bool granted = false;
     if (!granted) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         granted = true;
     }
-    gemm_tc_kernel<FMT><<<grid, kThreads, smem, st>>>(a, tmap);
+    gemm_tc_kernel<FMT><<<grid, kThreads, smem, st>>>(a, tmap, tmap_w);
     return cudaGetLastError();
 }
 
@@ -488,14 +615,29 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return fail(FQ_DECLINED_ARGS, "tensor map for the activations could not be encoded");
+    // packed K-quant rows stored row-major (expert stacks, small matrices) reach shared memory through a
+    // second tensor map: all stacked matrices as one 2-D byte array, one box = one unit of 128 rows
+    CUtensorMap tmap_w;
+    memset(&tmap_w, 0, sizeof tmap_w);
+    if ((w.fmt == FQ_Q4_K || w.fmt == FQ_Q5_K) && !w.tile_rows) {
+        const int ub = w.fmt == FQ_Q4_K ? 144 : 176;
+        if (w.mat_stride != (size_t)w.n * w.row_stride && w.n_mats > 1) return fail(FQ_DECLINED_ARGS, "stacked matrices are not contiguous");
+        const cuuint64_t wdims[2] = {(cuuint64_t)(w.k / 256) * ub, (cuuint64_t)w.n * (cuuint64_t)w.n_mats};
+        const cuuint64_t wstrides[1] = {(cuuint64_t)w.row_stride};
+        const cuuint32_t wbox[2] = {(cuuint32_t)ub, BM};
+        if (enc(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w.base), wdims, wstrides, wbox, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return fail(FQ_DECLINED_ARGS, "tensor map for the packed weights could not be encoded");
+    }
     TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev};
     const int tiles = table ? max_tiles : ((w.n + BM - 1) / BM) * (int)((rows + BN - 1) / BN);
     const int grid = tiles < ctx->sm_count ? (tiles > 0 ? tiles : 1) : ctx->sm_count;
     cudaError_t e;
     switch (w.fmt) {
-        case FQ_Q4_K: e = launch_tc<FQ_Q4_K>(a, tmap, grid, st); break;
-        case FQ_Q5_K: e = launch_tc<FQ_Q5_K>(a, tmap, grid, st); break;
-        default: e = launch_tc<FQ_Q8_0>(a, tmap, grid, st); break;
+        case FQ_Q4_K: e = launch_tc<FQ_Q4_K>(a, tmap, tmap_w, grid, st); break;
+        case FQ_Q5_K: e = launch_tc<FQ_Q5_K>(a, tmap, tmap_w, grid, st); break;
+        default: e = launch_tc<FQ_Q8_0>(a, tmap, tmap_w, grid, st); break;
     }
     g_trace.launches++;
     return e == cudaSuccess ? FQ_OK : cuda_fail(e, "tensor-core GEMM launch");

@@ -306,14 +306,16 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
             for (int r = 0; r < R; ++r) ch[r].decode(c);
 #pragma unroll
             for (int b = 0; b < MB; ++b) {
-                const uint8_t* rec = smem + (size_t)b * S.row;
-                int4 a[L.segs];
+                if (b < m) {  // CTA-uniform: a short group (few tokens on this expert) pays for its own rows only
+                    const uint8_t* rec = smem + (size_t)b * S.row;
+                    int4 a[L.segs];
 #pragma unroll
-                for (int s = 0; s < L.segs; ++s) a[s] = *reinterpret_cast<const int4*>(rec + ((size_t)s * C + c) * 16);
-                const uint32_t aux = *reinterpret_cast<const uint32_t*>(rec + S.aq + (size_t)c * 4);
-                const float* ad = reinterpret_cast<const float*>(rec + S.aq + S.aaux);
+                    for (int s = 0; s < L.segs; ++s) a[s] = *reinterpret_cast<const int4*>(rec + ((size_t)s * C + c) * 16);
+                    const uint32_t aux = *reinterpret_cast<const uint32_t*>(rec + S.aq + (size_t)c * 4);
+                    const float* ad = reinterpret_cast<const float*>(rec + S.aq + S.aaux);
 #pragma unroll
-                for (int r = 0; r < R; ++r) acc[r][b] += ch[r].term(a, aux, ad, c);
+                    for (int r = 0; r < R; ++r) acc[r][b] += ch[r].term(a, aux, ad, c);
+                }
             }
         }
 
@@ -321,10 +323,12 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int b = 0; b < MB; ++b) {
-                float v = acc[r][b];
+                if (b < m) {
+                    float v = acc[r][b];
 #pragma unroll
-                for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(gmask, v, o);
-                acc[r][b] = v;
+                    for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(gmask, v, o);
+                    acc[r][b] = v;
+                }
             }
         if (gl == 0) {
             if (GATED) {

@@ -41,7 +41,7 @@ __device__ __forceinline__ int local_expert(int e, int n_expert, Shard sh) {
     return sh.skip_foreign ? -1 : min(max(e, 0), n_expert - 1);
 }
 
-__global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, Shard shard, int* __restrict__ order,
+__global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, Shard shard, int group_rows, int* __restrict__ order,
                                   int* __restrict__ inv, GroupDesc* __restrict__ table, int* __restrict__ n_desc,
                                   int* __restrict__ n_rows) {
     extern __shared__ int sh[];
@@ -59,7 +59,7 @@ __global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, i
         for (int e = 0; e < n_expert; ++e) {
             place[e] = off;
             const int c = count[e];
-            for (int j = 0; j < c; j += kGroupRows) table[nd++] = {e, off + j, min(kGroupRows, c - j), 0};
+            for (int j = 0; j < c; j += group_rows) table[nd++] = {e, off + j, min(group_rows, c - j), 0};
             off += c;
         }
         *n_desc = nd;
@@ -146,7 +146,7 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int rows, i
     }
 }
 
-int max_desc_for(int pairs, int n_expert);
+int max_desc_for(int pairs, int n_expert, int group_rows);
 
 // ---- tensor-core form for prefill-sized batches ------------------------------------------------
 // Tile lists for the grouped tcgen05 GEMM, one CTA: per expert run, ceil(count/256) token tiles
@@ -222,7 +222,7 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
         return o;
     };
     const size_t o_order = take(sizeof(int) * pairs), o_inv = take(sizeof(int) * pairs), o_cnt = take(sizeof(int) * 4);
-    const size_t o_desc = take(sizeof(GroupDesc) * max_desc_for(pairs, n_expert));
+    const size_t o_desc = take(sizeof(GroupDesc) * max_desc_for(pairs, n_expert, kGroupRows));
     const size_t o_tgu = take(sizeof(TcTile) * max_gu), o_tdn = take(sizeof(TcTile) * max_dn);
     const size_t o_xb = take((size_t)pairs * hidden * 2), o_gate = take(sizeof(float) * (size_t)pairs * out_pe);
     const size_t o_up = take(sizeof(float) * (size_t)pairs * out_pe), o_gb = take((size_t)pairs * out_pe * 2);
@@ -235,7 +235,7 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
     cudaError_t e = cudaSuccess;
     int rc = FQ_OK;
     do {
-        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, order, inv, (GroupDesc*)(s + o_desc), cnt, cnt + 3);
+        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, kGroupRows, order, inv, (GroupDesc*)(s + o_desc), cnt, cnt + 3);
         tc_plan_kernel<<<1, 1024, sizeof(int) * n_expert, st>>>(selected_dev, pairs, n_expert, shard, rt_gu, rt_dn, (TcTile*)(s + o_tgu), cnt + 1,
                                                                  (TcTile*)(s + o_tdn), cnt + 2);
         int blocks = (int)(((size_t)pairs * hidden / 4 + 255) / 256);
@@ -260,7 +260,7 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
     return rc;
 }
 
-int max_desc_for(int pairs, int n_expert) { return (pairs < n_expert ? pairs : n_expert) + pairs / kGroupRows; }
+int max_desc_for(int pairs, int n_expert, int group_rows) { return (pairs < n_expert ? pairs : n_expert) + pairs / group_rows; }
 
 int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
                        int seq, int top_k, const int* selected_dev, const float* weights_dev, Shard shard, float* out_dev,
@@ -273,7 +273,11 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     if (tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 16 * n_expert)))
         return moe_layer_tensor_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, shard, out_dev, st);
     const ActSizes Sx = act_sizes(fmt, hidden), Sg = act_sizes(fmt, out_pe);
-    const int max_desc = max_desc_for(pairs, n_expert);
+    // Row tile of the grouped kernel. A router sends a token to distinct experts, so an expert's run is
+    // normally no longer than the batch; runs are split at this size either way, so repeated experts in
+    // one token only cost an extra table entry.
+    const int group_rows = seq < kGroupRows ? seq : kGroupRows;
+    const int max_desc = max_desc_for(pairs, n_expert, group_rows);
     // one scratch block: order, inv, n_desc, table, quantised x rows, g rows, quantised g rows, down rows
     size_t off = 0;
     auto take = [&](size_t bytes) {
@@ -301,14 +305,14 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     do {
         // positions past a shard's own rows are read by the gather below: point them at pair 0
         if (shard.skip_foreign && (e = cudaMemsetAsync(order, 0, sizeof(int) * pairs, st)) != cudaSuccess) break;
-        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, order, inv, table, n_desc, n_desc + 1);
+        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, group_rows, order, inv, table, n_desc, n_desc + 1);
         if ((e = cudaGetLastError()) != cudaSuccess) break;
         // gather each pair's token row and quantise it, in expert order
         if ((e = launch_quantize_acts_layout(x_dev, order, top_k, pairs, hidden, fmt, qx, st)) != cudaSuccess) break;
-        GemvArgs ga{gate, up, 0, qx, g, kGroupRows, out_pe, 0, table, n_desc, max_desc};
+        GemvArgs ga{gate, up, 0, qx, g, group_rows, out_pe, 0, table, n_desc, max_desc};
         if ((e = launch_gemv(ga, ctx->sm_count, st)) != cudaSuccess) break;
         if ((e = launch_quantize_acts_layout(g, nullptr, 1, pairs, out_pe, fmt, qg, st)) != cudaSuccess) break;
-        GemvArgs gd{down, DevWeights{}, 0, qg, down_rows, kGroupRows, hidden, 0, table, n_desc, max_desc};
+        GemvArgs gd{down, DevWeights{}, 0, qg, down_rows, group_rows, hidden, 0, table, n_desc, max_desc};
         if ((e = launch_gemv(gd, ctx->sm_count, st)) != cudaSuccess) break;
         const size_t total = (size_t)seq * hidden;
         int blocks = (int)((total + 255) / 256);

@@ -285,6 +285,28 @@ def test_moe_expert_shards_sum_to_the_layer(P, torch, tensor_arm, seq):
         load().fq_set_moe_tensor_for_test(-1)
 
 
+def test_moe_token_may_name_an_expert_twice(P):
+    """A routing row that repeats an expert makes that expert's run longer than the batch; the
+    row-group table must split it rather than drop rows."""
+    from fucina_b200._lib import load
+
+    gate, up, down, x, _, sel, w = _moe_case("q5_k", 256, 256, 4, 2, 2, seed=61)
+    sel[0, :] = (1, 1)
+    sel[1, :] = (0, 1)
+    wg = P.Weights.upload(oracle.Q5_K, gate, 256, 256, 4)
+    wu = P.Weights.upload(oracle.Q5_K, up, 256, 256, 4)
+    wd = P.Weights.upload(oracle.Q5_K, down, 256, 256, 4)
+    load().fq_set_moe_tensor_for_test(0)
+    try:
+        got = P.moe_layer(wg, wu, wd, x, sel, w)
+    finally:
+        load().fq_set_moe_tensor_for_test(-1)
+    want = oracle.moe_ffn(oracle.Q5_K, gate, up, down, x, sel, w, 4, 256)
+    assert_close(got, want, 5e-3, "repeated expert")
+    for h in (wg, wu, wd):
+        h.free()
+
+
 def test_moe_rejects_bad_expert_index(P):
     gate, up, down, x, _, sel, w = _moe_case("q5_k", 256, 256, 4, 2, 3, seed=60)
     wg = P.Weights.upload(oracle.Q5_K, gate, 256, 256, 4)
