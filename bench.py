@@ -470,19 +470,38 @@ def run_extra(args) -> list[dict]:
         up = _dev_weights(P, torch, F.Q5_K, ffn, hidden, 1301, E)
         down = _dev_weights(P, torch, F.Q5_K, hidden, ffn, 1302, E)
         for T in (1, 8, 64, 1024):
-            x = torch.randn((T, hidden), generator=g, device="cuda")
-            logits = torch.randn((T, E), generator=g, device="cuda")
+            # 16 routing variants are rotated so a decode step does not find the previous step's experts in L2
+            # (16 x 8 expert slots at T = 1 touch ~80 distinct experts, ~260 MB); one CUDA graph per variant, as a
+            # decode loop would replay it
+            variants = 16 if T <= 64 else 2
+            xs_ = [torch.randn((T, hidden), generator=g, device="cuda") for _ in range(variants)]
+            lgs = [torch.randn((T, E), generator=g, device="cuda") for _ in range(variants)]
             sel = torch.empty((T, topk), dtype=torch.int32, device="cuda")
             wts = torch.empty((T, topk), device="cuda")
             o = torch.empty((T, hidden), device="cuda")
             torch.cuda.synchronize()
 
-            def layer():
-                P.router_topk_dev(logits, T, E, topk, True, sel, wts)
-                P.moe_layer_dev(gate, up, down, x, T, topk, sel, wts, o)
+            def layer(i):
+                P.router_topk_dev(lgs[i], T, E, topk, True, sel, wts)
+                P.moe_layer_dev(gate, up, down, xs_[i], T, topk, sel, wts, o)
 
-            ms = _timed(P, torch, layer, max(args.steps // 10, 5), 3)
-            out.append({"workload": f"Q5_K MoE layer hidden 2048 ffn 768 128 experts top-8, {T} tokens (router + layer on device)",
+            for i in range(variants):
+                layer(i)
+            P.synchronize()
+            graphs = []
+            for i in range(variants):
+                with P.capture() as cap:
+                    layer(i)
+                graphs.append(cap.graph)
+            it = [0]
+
+            def step():
+                graphs[it[0] % variants].launch()
+                it[0] += 1
+
+            ms = _timed(P, torch, step, max(args.steps // 2, 16), 3)
+            out.append({"workload": f"Q5_K MoE layer hidden 2048 ffn 768 128 experts top-8, {T} tokens (router + layer on device, "
+                                    f"graph replay, {variants} routing variants rotated)",
                         "ms": round(ms, 4), "tok_per_s": round(T / ms * 1e3, 1)})
     if args.workload in ("ternary", "all"):
         n = k = 8192

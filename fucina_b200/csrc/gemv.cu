@@ -258,15 +258,12 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
         cbase += (size_t)d.row0 * A.ldc;
     }
 
-    // stage the activation rows (zero rows beyond m so padded batch slots add nothing)
+    // stage the m activation rows of this group (rows beyond m are never read: the compute is guarded)
     {
-        const int units_per_row = (int)(S.row / 16);
+        const int units = m * (int)(S.row / 16);
         const uint4* src = reinterpret_cast<const uint4*>(acts);
         uint4* dst = reinterpret_cast<uint4*>(smem);
-        for (int i = threadIdx.x; i < MB * units_per_row; i += kThreads) {
-            const int r = i / units_per_row;
-            dst[i] = (r < m) ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
-        }
+        for (int i = threadIdx.x; i < units; i += kThreads) dst[i] = __ldg(src + i);
     }
     __syncthreads();
 
@@ -369,8 +366,9 @@ cudaError_t launch_one(const GemvArgs& a, int sm_count, cudaStream_t st) {
     const long long groups = ((long long)a.w.n + rows_per_group - 1) / rows_per_group;
     long long ctas = (groups + groups_per_cta - 1) / groups_per_cta;
     const long long ny = a.table ? (a.max_desc > 0 ? a.max_desc : 1) : 1;
-    // grouped launches spread the SM budget over the table entries
-    long long cap = (long long)sm_count * 8 / (ny > 8 ? 8 : ny);
+    // grouped launches spread the SM budget over the table entries: about eight CTAs per SM in total, so a
+    // CTA stages its group's activations once and then walks many weight rows
+    long long cap = (long long)sm_count * 8 / ny;
     if (cap < 1) cap = 1;
     if (ctas > cap) ctas = cap;
     if (ctas < 1) ctas = 1;

@@ -45,8 +45,10 @@ __global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, i
                                   int* __restrict__ inv, GroupDesc* __restrict__ table, int* __restrict__ n_desc,
                                   int* __restrict__ n_rows) {
     extern __shared__ int sh[];
-    int* count = sh;                 // [n_expert]
-    int* place = sh + n_expert;      // [n_expert]
+    int* count = sh;                   // [n_expert] pairs per expert
+    int* place = sh + n_expert;        // [n_expert] first sorted position of the expert's run
+    int* dstart = sh + 2 * n_expert;   // [n_expert] first table entry of the expert
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int e = threadIdx.x; e < n_expert; e += blockDim.x) count[e] = 0;
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
@@ -54,18 +56,38 @@ __global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, i
         if (e >= 0) atomicAdd(&count[e], 1);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int off = 0, nd = 0;
-        for (int e = 0; e < n_expert; ++e) {
-            place[e] = off;
-            const int c = count[e];
-            for (int j = 0; j < c; j += group_rows) table[nd++] = {e, off + j, min(group_rows, c - j), 0};
-            off += c;
+    if (warp == 0) {
+        // exclusive scans over the experts: run offsets and table offsets, 32 experts per step
+        int rows = 0, nd = 0;
+        for (int base = 0; base < n_expert; base += 32) {
+            const int e = base + lane;
+            const int c = e < n_expert ? count[e] : 0;
+            const int g = (c + group_rows - 1) / group_rows;
+            int ic = c, ig = g;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int tc = __shfl_up_sync(0xffffffffu, ic, o), tg = __shfl_up_sync(0xffffffffu, ig, o);
+                if (lane >= o) ic += tc, ig += tg;
+            }
+            if (e < n_expert) {
+                place[e] = rows + ic - c;
+                dstart[e] = nd + ig - g;
+            }
+            rows += __shfl_sync(0xffffffffu, ic, 31);
+            nd += __shfl_sync(0xffffffffu, ig, 31);
         }
-        *n_desc = nd;
-        *n_rows = off;
+        if (lane == 0) {
+            *n_desc = nd;
+            *n_rows = rows;
+        }
     }
     __syncthreads();
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+        const int c = count[e], off = place[e];
+        int d = dstart[e];
+        for (int j = 0; j < c; j += group_rows) table[d++] = {e, off + j, min(group_rows, c - j), 0};
+    }
+    __syncthreads();  // the pass below advances place[]
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = local_expert(selected[p], n_expert, shard);
         if (e < 0) {
@@ -98,51 +120,66 @@ __global__ void combine_kernel(const float* __restrict__ down, const float* __re
     }
 }
 
-// Router (src/exec/topk.zig:50-86), one thread per token row: the k largest
-// logits in descending order, an equal logit never displaces an earlier one;
-// softmax over all experts with the row maximum subtracted; optional
-// renormalisation over the selected k.
+// Router (src/exec/topk.zig:50-86), one warp per token row: the k largest logits in descending
+// order, an equal logit never displaces an earlier one; softmax over all experts with the row
+// maximum subtracted; optional renormalisation over the selected k. The lanes share the loads, the
+// exponentials and the k arg-max rounds; the sums that fix the result bits (over all experts, over
+// the selected k) are added by one lane in index order, as the scalar code does.
 constexpr int kMaxTopK = 32;
+constexpr int kMaxRouterExperts = 4096;
 __global__ void router_topk_kernel(const float* __restrict__ logits, int rows, int experts, int k, int normalize,
                                    int* __restrict__ selected, float* __restrict__ weights) {
-    const int row = blockIdx.x * blockDim.x + threadIdx.x;
-    if (row >= rows) return;
+    extern __shared__ float rsh[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int row = blockIdx.x * warps + warp;
+    if (row >= rows) return;  // whole warps leave together
+    float* lg = rsh + (size_t)warp * 2 * experts;  // logits; a taken entry becomes NaN and never compares true again
+    float* ex = lg + experts;                      // exp(logit - max)
     const float* l = logits + (size_t)row * experts;
-    float w[kMaxTopK];
-    int sel[kMaxTopK];
-    for (int s = 0; s < k; ++s) {
-        sel[s] = 0;
-        w[s] = -INFINITY;
-    }
-    float mx = l[0];
-    for (int i = 0; i < experts; ++i) {
+    float mx = -INFINITY;
+    for (int i = lane; i < experts; i += 32) {
         const float v = l[i];
-        if (v > mx) mx = v;
-        if (v <= w[k - 1]) continue;
-        int slot = k - 1;
-        while (slot > 0 && v > w[slot - 1]) {
-            w[slot] = w[slot - 1];
-            sel[slot] = sel[slot - 1];
-            --slot;
-        }
-        w[slot] = v;
-        sel[slot] = i;
+        lg[i] = v;
+        mx = fmaxf(mx, v);
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    for (int i = lane; i < experts; i += 32) ex[i] = expf(__fsub_rn(lg[i], mx));
+    __syncwarp();
     float exp_sum = 0.0f;
-    for (int i = 0; i < experts; ++i) exp_sum = __fadd_rn(exp_sum, expf(__fsub_rn(l[i], mx)));
-    const float inv_sum = __fdiv_rn(1.0f, exp_sum);
-    float total = 0.0f;
+    if (lane == 0)
+        for (int i = 0; i < experts; ++i) exp_sum = __fadd_rn(exp_sum, ex[i]);
+    float w_mine = 0.0f;  // lane s keeps slot s
+    int sel_mine = 0;
     for (int s = 0; s < k; ++s) {
-        w[s] = __fmul_rn(expf(__fsub_rn(w[s], mx)), inv_sum);
-        total = __fadd_rn(total, w[s]);
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = lane; i < experts; i += 32) {
+            const float v = lg[i];
+            if (v > bv) bv = v, bi = i;  // ascending i per lane: an equal later value does not displace
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+        }
+        if (bi == 0x7fffffff) bi = 0;  // nothing above -inf is left
+        if (lane == s) sel_mine = bi, w_mine = ex[bi];
+        __syncwarp();
+        if (lane == 0) lg[bi] = __int_as_float(0x7fc00000);
+        __syncwarp();
     }
-    if (normalize && total > 0.0f) {
-        const float inv_total = __fdiv_rn(1.0f, total);
-        for (int s = 0; s < k; ++s) w[s] = __fmul_rn(w[s], inv_total);
+    const float inv_sum = __fdiv_rn(1.0f, __shfl_sync(0xffffffffu, exp_sum, 0));
+    w_mine = __fmul_rn(w_mine, inv_sum);
+    if (normalize) {
+        float total = 0.0f;
+        for (int s = 0; s < k; ++s) total = __fadd_rn(total, __shfl_sync(0xffffffffu, w_mine, s));
+        if (total > 0.0f) w_mine = __fmul_rn(w_mine, __fdiv_rn(1.0f, total));
     }
-    for (int s = 0; s < k; ++s) {
-        selected[(size_t)row * k + s] = sel[s];
-        weights[(size_t)row * k + s] = w[s];
+    if (lane < k) {
+        selected[(size_t)row * k + lane] = sel_mine;
+        weights[(size_t)row * k + lane] = w_mine;
     }
 }
 
@@ -235,7 +272,7 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
     cudaError_t e = cudaSuccess;
     int rc = FQ_OK;
     do {
-        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, kGroupRows, order, inv, (GroupDesc*)(s + o_desc), cnt, cnt + 3);
+        route_plan_kernel<<<1, 1024, sizeof(int) * 3 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, kGroupRows, order, inv, (GroupDesc*)(s + o_desc), cnt, cnt + 3);
         tc_plan_kernel<<<1, 1024, sizeof(int) * n_expert, st>>>(selected_dev, pairs, n_expert, shard, rt_gu, rt_dn, (TcTile*)(s + o_tgu), cnt + 1,
                                                                  (TcTile*)(s + o_tdn), cnt + 2);
         int blocks = (int)(((size_t)pairs * hidden / 4 + 255) / 256);
@@ -305,7 +342,7 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     do {
         // positions past a shard's own rows are read by the gather below: point them at pair 0
         if (shard.skip_foreign && (e = cudaMemsetAsync(order, 0, sizeof(int) * pairs, st)) != cudaSuccess) break;
-        route_plan_kernel<<<1, 1024, sizeof(int) * 2 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, group_rows, order, inv, table, n_desc, n_desc + 1);
+        route_plan_kernel<<<1, 1024, sizeof(int) * 3 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, group_rows, order, inv, table, n_desc, n_desc + 1);
         if ((e = cudaGetLastError()) != cudaSuccess) break;
         // gather each pair's token row and quantise it, in expert order
         if ((e = launch_quantize_acts_layout(x_dev, order, top_k, pairs, hidden, fmt, qx, st)) != cudaSuccess) break;
@@ -362,11 +399,15 @@ int fq_router_topk_dev(const float* logits_dev, size_t seq, size_t n_expert, siz
                        float* weights_dev, void* stream) {
     if (!logits_dev || !selected_dev || !weights_dev) return fail(FQ_DECLINED_ARGS, "null pointer");
     if (top_k == 0 || top_k > n_expert || top_k > (size_t)kMaxTopK || seq == 0) return fail(FQ_DECLINED_ARGS, "bad top_k");
+    if (n_expert > (size_t)kMaxRouterExperts) return fail(FQ_DECLINED_ARGS, "more than %d experts", kMaxRouterExperts);
     Ctx* ctx = context();
     if (!ctx) return FQ_DECLINED_NO_GPU;
     std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
     cudaStream_t st = stream ? (cudaStream_t)stream : ctx->stream;
-    router_topk_kernel<<<(unsigned)((seq + 63) / 64), 64, 0, st>>>(logits_dev, (int)seq, (int)n_expert, (int)top_k, normalize, selected_dev, weights_dev);
+    // a warp per row with 2 x experts floats of shared memory each
+    const int warps = n_expert <= 1024 ? 4 : 1;
+    router_topk_kernel<<<(unsigned)((seq + warps - 1) / warps), warps * 32, sizeof(float) * 2 * n_expert * warps, st>>>(
+        logits_dev, (int)seq, (int)n_expert, (int)top_k, normalize, selected_dev, weights_dev);
     g_trace.launches++;
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FQ_OK : cuda_fail(e, "router launch");
