@@ -16,9 +16,9 @@ rotated so every step streams its weights from HBM.
 `e2e`     the same metric through the blocking C-ABI call with HOST buffers
           (resident weights; activations go up and results come down every
           call), wall-clock timed between device synchronisations.
-`roofline` achieved bytes/s of the decode kernel alone, from CUDA events the
-          library records around each launch in a second pass over the same
-          steps, against the measured HBM copy bandwidth.
+`roofline` achieved bytes/s of the dominant kernel alone (the 32000 x 4096
+          product), CUDA events around back-to-back graph replays over the
+          rotated weight copies, against the measured HBM copy bandwidth.
 `cpu_baseline` the CPU restatement of the reference kernels on the host cores.
 
 With --gpus N > 1 every rank serves its own decode stream from its own weight
@@ -262,7 +262,11 @@ def run_ours(args) -> dict:
     per_launch_bytes = STACK_N[big] * ROW_BYTES + batch * K * 4 + batch * STACK_N[big] * 4
     achieved = per_launch_bytes / (k_ms / k_n * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "traffic": None,
+                "frac": round(achieved / peak, 4),
+                # dram__bytes_read + dram__bytes_write of one profiler capture of the same kernel on a 65536-row
+                # matrix (151.31 MB + 3.46 MB), scaled to this launch by rows (traffic is proportional to rows)
+                "traffic": int((151_309_056 + 3_462_656) * STACK_N[big] / 65536),
+                "traffic_source": "ncu capture of a 65536 x 4096 case, scaled by rows",
                 "kernel": "decode_rows_kernel<Q4_K, MB=1, fused act-quant> on 32000x4096",
                 "peak_source": peak_src, "launches_timed": k_n,
                 "timing": "CUDA events around back-to-back launches (graph replay, consecutive launches overlap by programmatic dependent launch)", "us_per_launch": round(k_ms / k_n * 1e3, 3),
@@ -612,7 +616,10 @@ def run_multi(args) -> list[dict]:
             wts = torch.empty((T, topk), device="cuda")
             o1 = torch.empty((T, hidden), device="cuda")
             torch.cuda.synchronize()
-            forms = ["single GPU"] if moe is None else ["NCCL all-to-all dispatch/combine", "NCCL all-gather + reduce-scatter of partial sums"]
+            forms = ["single GPU"] if moe is None else ["NCCL all-to-all dispatch/combine", "NCCL all-gather + reduce-scatter of partial sums",
+                                                        "NCCL all-gather + reduce-scatter of partial sums, 2 token chunks pipelined"]
+            if T % 2 or T < 512:
+                forms = forms[:2]
             for form in forms:
                 def step():
                     with torch.cuda.stream(ext):
@@ -622,7 +629,7 @@ def run_multi(args) -> list[dict]:
                         elif form.startswith("NCCL all-to-all"):
                             moe.forward(x, sel, wts)
                         else:
-                            moe.forward_gathered(x, sel, wts, partial_rows)
+                            moe.forward_gathered(x, sel, wts, partial_rows, chunks=2 if form.endswith("pipelined") else 1)
 
                 ms = timed(step)
                 out.append({"workload": f"Q5_K MoE layer (hidden 2048, ffn 768, 128 experts, top-8), {T_total} tokens over {world} GPU(s), "

@@ -10,17 +10,22 @@
 // Data movement. One persistent CTA per SM owns a contiguous range of weight
 // rows and walks it in tiles of 32 rows; lane l of every warp owns row l of
 // the tile, so no cross-lane reduction is needed and the block header is
-// decoded once per 256 weights. The eight warps split K: warp w takes the
-// slabs (groups of 1-2 blocks per row) w, w+8, ... . Every lane fetches its
-// own row's slab with one bulk async copy (cp.async.bulk, the non-tensor TMA
-// path) into a private shared-memory slot; the 32 copies of a warp complete on
-// one mbarrier. Slots are padded to an odd number of 16-byte units so the
-// 128-bit shared loads of a quarter warp hit 32 distinct banks. Copies for
-// the next slabs (also of the next tile) are in flight while a slab is
-// consumed, which keeps tens of KB per SM outstanding independent of register
-// count -- the thing an HBM-bound kernel needs. Activations are quantised once
-// per CTA in the prologue, while the first weight slabs are already in
-// flight, and are read as warp-wide broadcasts.
+// decoded once per 256 weights. The warps (16, or 8 for wider batches) split
+// K: warp w takes the slabs (1-2 blocks per row) w, w+W, ... . A warp step
+// brings one slab of 32 rows into a ring of shared-memory stages and
+// completes on one mbarrier, by the cheapest copy the layout allows:
+//   tile-major K-quants   one bulk copy of the contiguous 32 x 144/176 bytes
+//   row-major K-quants    one 2-D tensor copy (32 rows x one unit)
+//   split rows (Q8_0)     one bulk copy per lane (payload + scales)
+// Slots are an odd number of 16-byte units wide so the 128-bit shared loads
+// of a quarter warp hit 32 distinct banks. Copies for the next slabs (also of
+// the next tile) are in flight while a slab is consumed, which keeps ~144 KB
+// per SM outstanding independent of register count -- the thing an HBM-bound
+// kernel needs. The kernel launches with programmatic stream serialisation:
+// its weight copies start before griddepcontrol.wait, so they overlap the
+// tail of the previous kernel. Activations are quantised per CTA after that
+// wait, while the first weight slabs are in flight, and are read as warp-wide
+// broadcasts.
 //
 // Every wait on an mbarrier is bounded; a wait that gives up records
 // FQ_ERR_TIMEOUT in the status word and the CTA returns.

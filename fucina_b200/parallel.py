@@ -132,7 +132,8 @@ class ExpertParallelMoE:
         return out
 
     def forward_gathered(self, x: torch.Tensor, selected: torch.Tensor, weights: torch.Tensor,
-                         partial_ffn: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor]) -> torch.Tensor:
+                         partial_ffn: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
+                         chunks: int = 1) -> torch.Tensor:
         """The same layer with fixed-size exchanges and no host synchronisation: all-gather the token
         rows and their routing, let every rank compute the partial sums of ITS experts for all
         world*T tokens, and reduce-scatter the partial outputs back to the tokens' home ranks.
@@ -148,19 +149,41 @@ class ExpertParallelMoE:
         T, hidden = x.shape
         k = self.top_k
         W = self.world
-        x_all = torch.empty((W * T, hidden), dtype=x.dtype, device=x.device)
-        sel_all = torch.empty((W * T, k), dtype=selected.dtype, device=x.device)
-        w_all = torch.empty((W * T, k), dtype=weights.dtype, device=x.device)
-        dist.all_gather_into_tensor(x_all, x.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(sel_all, selected.reshape(T, k).contiguous(), group=self.group)
-        dist.all_gather_into_tensor(w_all, weights.reshape(T, k).contiguous(), group=self.group)
-        partial = partial_ffn(x_all, sel_all, w_all)
-        out = torch.empty((T, hidden), dtype=partial.dtype, device=partial.device)
-        if dist.get_backend(self.group) == "gloo":   # gloo has no reduce-scatter
-            dist.all_reduce(partial, group=self.group)
-            out.copy_(partial[self.rank * T:(self.rank + 1) * T])
-        else:
-            dist.reduce_scatter_tensor(out, partial.contiguous(), group=self.group)
+        # routing of every token, once: selected and weights travel as one int32/float32 pair of small gathers
+        sel_all = torch.empty((W, T, k), dtype=selected.dtype, device=x.device)
+        w_all = torch.empty((W, T, k), dtype=weights.dtype, device=x.device)
+        dist.all_gather_into_tensor(sel_all.view(W * T, k), selected.reshape(T, k).contiguous(), group=self.group)
+        dist.all_gather_into_tensor(w_all.view(W * T, k), weights.reshape(T, k).contiguous(), group=self.group)
+        out = torch.empty((T, hidden), dtype=x.dtype, device=x.device)
+        gloo = dist.get_backend(self.group) == "gloo"   # gloo has no reduce-scatter and no async overlap worth having
+        if chunks <= 1 or T % chunks or gloo:
+            x_all = torch.empty((W * T, hidden), dtype=x.dtype, device=x.device)
+            dist.all_gather_into_tensor(x_all, x.contiguous(), group=self.group)
+            partial = partial_ffn(x_all, sel_all.view(W * T, k), w_all.view(W * T, k))
+            if gloo:
+                dist.all_reduce(partial, group=self.group)
+                out.copy_(partial[self.rank * T:(self.rank + 1) * T])
+            else:
+                dist.reduce_scatter_tensor(out, partial.contiguous(), group=self.group)
+            return out
+        # Token chunks pipeline the exchange against the expert products: while chunk c is multiplied, chunk c+1
+        # is being gathered and chunk c-1 reduced (collectives run on the communicator's own stream).
+        h = T // chunks
+        x = x.contiguous()
+        gathers, xs = [], []
+        for c in range(chunks):
+            xc = torch.empty((W * h, hidden), dtype=x.dtype, device=x.device)
+            gathers.append(dist.all_gather_into_tensor(xc, x[c * h:(c + 1) * h], group=self.group, async_op=True))
+            xs.append(xc)
+        reduces = []
+        for c in range(chunks):
+            gathers[c].wait()
+            sel_c = sel_all[:, c * h:(c + 1) * h].reshape(W * h, k)
+            w_c = w_all[:, c * h:(c + 1) * h].reshape(W * h, k)
+            partial = partial_ffn(xs[c], sel_c, w_c)
+            reduces.append((dist.reduce_scatter_tensor(out[c * h:(c + 1) * h], partial, group=self.group, async_op=True), partial))
+        for work, _keep in reduces:
+            work.wait()
         return out
 
     def exchange_bytes(self, T: int, hidden: int, elem: int = 4) -> int:
