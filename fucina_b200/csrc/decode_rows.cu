@@ -640,6 +640,227 @@ cudaError_t launch_fmt(const RowsArgs& a, const CUtensorMap& tmap, int mb, bool 
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Grouped form for MoE expert stacks at decode batch sizes: the same row-per-lane arithmetic over
+// a device-built table of (expert, run of <= 8 activation rows) entries.
+//
+// A work item is (table entry, group of TPI 32-row tiles of the expert's matrix), dealt round-robin
+// to one persistent CTA per SM. The 8 warps of the CTA are arranged as TPI tiles x (8 / TPI) K parts:
+// with many items every warp owns a whole tile and walks all of K by itself (no cross-warp sum);
+// with few items (a single token) the warps split K so that more SMs have work. Weights are
+// row-major expert stacks, fetched with one 2-D tensor copy per warp step (32 rows x one 256-weight
+// unit) into a per-warp ring; the copies of the next item are in flight while this one is consumed.
+// The entry's activation rows are quantised by the CTA itself (Q8_K, the CPU kernels' quantiser)
+// straight from f32: token rows through the sorted pair list for the gate/up product, pair rows for
+// the down product. GATED multiplies the gate and the up matrix in the same pass and stores
+// up * gate * sigmoid(gate).
+constexpr int kExpertWarps = 8;
+
+template <int FMT, int MB, bool GATED>
+__global__ void __launch_bounds__(kExpertWarps * 32, 1)
+    expert_rows_kernel(const ExpertArgs A, const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap2) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int NM = GATED ? 2 : 1;
+    constexpr int UB = FMT == FQ_Q4_K ? 144 : 176;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int k = A.w.k, n = A.w.n;
+    const NatSizes NS = nat_sizes(true, k);
+    const int units = k >> 8;
+    const int tpi = A.tiles_per_item, ksplit = kExpertWarps / tpi;
+    const int tsub = warp / ksplit, kpart = warp % ksplit;
+    const int my_units = kpart < units ? (units - kpart + ksplit - 1) / ksplit : 0;
+    const int spi = my_units * NM;  // pipeline steps of this warp per item
+    const int tiles_per_mat = (n + 31) >> 5;
+    const int items_per_desc = (tiles_per_mat + tpi - 1) / tpi;
+    const int n_desc = min(*A.n_desc, A.max_desc);
+    const int total_items = n_desc * items_per_desc;
+    const int my_items = (int)blockIdx.x < total_items ? (total_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+
+    // shared memory: barriers | activation records | reduction buffer | per-warp stage ring
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+    uint8_t* acts = smem + 512;
+    float* red = reinterpret_cast<float*>(acts + ((MB * NS.row + 127) & ~(size_t)127));
+    uint8_t* slots = reinterpret_cast<uint8_t*>(red) + (size_t)kExpertWarps * NM * MB * 32 * sizeof(float);
+    const uint32_t slot0 = smem_u32(slots) + (uint32_t)(warp * A.stages) * 32 * UB;
+    const uint32_t bar0 = smem_u32(bars) + warp * kMaxStages * 8;
+    if (lane == 0)
+        for (int s = 0; s < A.stages; ++s) mbar_init(bar0 + s * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+
+    // Step `it` of this warp: item it / spi, unit kpart + ksplit * (j / NM), matrix j % NM, j = it % spi.
+    // A warp whose tile lies past the end of the matrix (last group of a matrix) has no copies in that
+    // item, so ring slots and barrier phases are counted in copies actually issued, not in steps.
+    auto item_of = [&](int item_local, int& d, int& tile) {
+        const int item = blockIdx.x + item_local * gridDim.x;
+        d = item / items_per_desc;
+        tile = (item % items_per_desc) * tpi + tsub;
+    };
+    const int total = my_items * spi;
+    int next_it = 0, issued = 0, consumed = 0;
+    auto advance = [&]() {  // keep up to `stages` copies in flight
+        while (issued < consumed + A.stages && next_it < total) {
+            int d, tile;
+            item_of(next_it / spi, d, tile);
+            if (tile < tiles_per_mat) {
+                if (lane == 0) {
+                    const int j = next_it % spi, unit = kpart + ksplit * (j / NM);
+                    const int stage = issued % A.stages;
+                    const uint32_t bar = bar0 + stage * 8;
+                    const int row = A.table[d].mat * n + tile * 32;  // row in the stacked [experts * n] matrix
+                    mbar_arrive_expect_tx(bar, (uint32_t)(32 * UB));
+                    const CUtensorMap* tm = (GATED && (j % NM)) ? &tmap2 : &tmap;
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                            slot0 + (uint32_t)stage * 32 * UB),
+                        "l"(tm), "r"(unit * UB), "r"(row), "r"(bar)
+                        : "memory");
+                }
+                ++issued;
+            }
+            ++next_it;
+        }
+    };
+
+    // This kernel is launched without programmatic overlap: the table, the pair list and the activation
+    // rows were written by the kernels before it and are complete when it starts.
+    advance();
+
+    const ActView V = {smem_u32(acts), (uint32_t)NS.row, (uint32_t)NS.aq, (uint32_t)(NS.aq + NS.sums)};
+    bool ok = true;  // per warp; a warp that gave up still walks through every CTA barrier below
+    for (int il = 0; il < my_items; ++il) {
+        int d, tile;
+        item_of(il, d, tile);
+        const GroupDesc G = A.table[d];
+        if (il) __syncthreads();  // everyone is done with the previous item's activation records
+        // quantise this entry's rows: (row b, block blk) pairs over the warps; unused batch slots are zero
+        const int nblk = k >> 8;
+        for (int i = warp; i < MB * nblk; i += kExpertWarps) {
+            const int b = i / nblk, blk = i % nblk;
+            uint8_t* rec = acts + (size_t)b * NS.row;
+            if (b < G.m) {
+                const int pos = G.row0 + b;
+                const size_t src_row = A.src_index ? (size_t)(A.src_index[pos] / A.top_k) : (size_t)pos;
+                quantize_block_natural(A.src + src_row * k, blk, true, k, rec, lane);
+            } else {
+                *reinterpret_cast<uint2*>(rec + (size_t)blk * 256 + lane * 8) = make_uint2(0, 0);
+                if (lane < 8) reinterpret_cast<int32_t*>(rec + NS.aq)[blk * 8 + lane] = 0;
+                if (lane == 0) reinterpret_cast<float*>(rec + NS.aq + NS.sums)[blk] = 0.0f;
+            }
+        }
+        __syncthreads();
+
+        float acc[NM][MB];
+#pragma unroll
+        for (int q = 0; q < NM; ++q)
+#pragma unroll
+            for (int b = 0; b < MB; ++b) acc[q][b] = 0.0f;
+        const bool have_tile = tile < tiles_per_mat;
+        if (have_tile) {
+            for (int j = 0; j < spi; ++j) {
+                if (!ok) break;
+                const int unit = kpart + ksplit * (j / NM), stage = consumed % A.stages;
+                if (!mbar_wait(bar0 + stage * 8, (uint32_t)(consumed / A.stages) & 1u)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t p = slot0 + (uint32_t)stage * 32 * UB + (uint32_t)lane * UB;
+                if (!GATED || (j % NM) == 0) {
+                    if (FMT == FQ_Q4_K) block_q4_k<MB>(p, V, unit, acc[0]);
+                    if (FMT == FQ_Q5_K) block_q5_k<MB>(p, V, unit, acc[0]);
+                } else {
+                    if (FMT == FQ_Q4_K) block_q4_k<MB>(p, V, unit, acc[NM - 1]);
+                    if (FMT == FQ_Q5_K) block_q5_k<MB>(p, V, unit, acc[NM - 1]);
+                }
+                __syncwarp();  // every lane is done with this stage before it is refilled
+                ++consumed;
+                advance();
+            }
+        }
+
+        // K parts of a tile live in consecutive warps: sum them (ksplit > 1), then apply the gate and store
+        if (ksplit > 1) {
+#pragma unroll
+            for (int q = 0; q < NM; ++q)
+#pragma unroll
+                for (int b = 0; b < MB; ++b) red[((warp * NM + q) * MB + b) * 32 + lane] = acc[q][b];
+            __syncthreads();
+            if (kpart == 0) {
+#pragma unroll
+                for (int q = 0; q < NM; ++q)
+#pragma unroll
+                    for (int b = 0; b < MB; ++b) {
+                        float sum = 0.0f;
+                        for (int w2 = 0; w2 < ksplit; ++w2) sum += red[(((warp + w2) * NM + q) * MB + b) * 32 + lane];
+                        acc[q][b] = sum;
+                    }
+            }
+        }
+        const int row = tile * 32 + lane;
+        if (kpart == 0 && have_tile && row < n) {
+#pragma unroll
+            for (int b = 0; b < MB; ++b) {
+                if (b >= G.m) continue;
+                float v = acc[0][b];
+                if (GATED) {
+                    const float gate = acc[0][b], up = acc[NM - 1][b];
+                    const float sig = 1.0f / (1.0f + expf(-gate));
+                    v = up * (gate * sig);
+                }
+                A.out[(size_t)(G.row0 + b) * n + row] = v;
+            }
+        }
+    }
+    if (!ok) {
+        if (lane == 0) *(volatile int*)A.status = FQ_ERR_TIMEOUT;
+        // give copies still in flight a bounded chance to land before the CTA's shared memory is released
+        for (int s = 0; s < A.stages; ++s) mbar_wait(bar0 + s * 8, (uint32_t)((consumed + s) / A.stages) & 1u);
+    }
+}
+
+size_t expert_smem_bytes(int fmt, int k, int mb, int nm, int stages) {
+    const NatSizes NS = nat_sizes(true, (size_t)k);
+    const int ub = fmt == FQ_Q4_K ? 144 : 176;
+    return 512 + ((mb * NS.row + 127) & ~(size_t)127) + (size_t)kExpertWarps * nm * mb * 32 * sizeof(float) +
+           (size_t)kExpertWarps * stages * 32 * ub;
+}
+
+template <int FMT, int MB, bool GATED>
+cudaError_t launch_expert_t(const ExpertArgs& a, const CUtensorMap& t1, const CUtensorMap& t2, int grid, size_t smem, cudaStream_t st) {
+    auto kern = expert_rows_kernel<FMT, MB, GATED>;
+    static bool granted = false;
+    if (!granted) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
+        if (e != cudaSuccess) return e;
+        granted = true;
+    }
+    kern<<<grid, kExpertWarps * 32, smem, st>>>(a, t1, t2);
+    return cudaGetLastError();
+}
+
+template <int FMT, bool GATED>
+cudaError_t launch_expert_mb(const ExpertArgs& a, int mb, const CUtensorMap& t1, const CUtensorMap& t2, int grid, size_t smem, cudaStream_t st) {
+    switch (mb) {
+        case 1: return launch_expert_t<FMT, 1, GATED>(a, t1, t2, grid, smem, st);
+        case 2: return launch_expert_t<FMT, 2, GATED>(a, t1, t2, grid, smem, st);
+        case 4: return launch_expert_t<FMT, 4, GATED>(a, t1, t2, grid, smem, st);
+        default: return launch_expert_t<FMT, 8, GATED>(a, t1, t2, grid, smem, st);
+    }
+}
+
+// 2-D byte view of a whole expert stack: [experts * n rows][row bytes], box = 32 rows x one unit
+bool make_stack_tmap(const DevWeights& w, int unit_bytes, CUtensorMap* out) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)(w.k / 256) * unit_bytes, (cuuint64_t)w.n * (cuuint64_t)w.n_mats};
+    const cuuint64_t strides[1] = {(cuuint64_t)w.row_stride};
+    const cuuint32_t box[2] = {(cuuint32_t)unit_bytes, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 bool decode_rows_eligible(const DevWeights& w, size_t m) {
@@ -701,5 +922,45 @@ extern "C" __attribute__((visibility("default"))) int fq_debug_timeline(unsigned
     return (int)cudaMemcpyFromSymbol(out, g_timeline, sizeof(unsigned long long) * kTimelineSlots * ctas);
 }
 #endif
+
+// ---- grouped expert form (see expert_rows_kernel) --------------------------------------------
+int expert_rows_max_group() { return 8; }
+
+bool expert_rows_eligible(const DevWeights& w, const DevWeights* w2, int group_rows) {
+    if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K) return false;
+    if (w.tile_rows || w.k % 256 != 0 || w.k < 256 || group_rows < 1 || group_rows > 8) return false;
+    if (w.n_mats > 1 && w.mat_stride != (size_t)w.n * w.row_stride) return false;
+    if (w2 && (w2->fmt != w.fmt || w2->k != w.k || w2->n != w.n || w2->tile_rows || w2->row_stride != w.row_stride)) return false;
+    static const bool off = getenv("FUCINA_B200_NO_EXPERT_ROWS") != nullptr;
+    if (off || !encode_tiled_fn()) return false;
+    return expert_smem_bytes(w.fmt, w.k, pad_rows((size_t)group_rows), w2 ? 2 : 1, 2) <= kSmemLimit;
+}
+
+cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const float* src, const int* src_index, int top_k, float* out,
+                               const GroupDesc* table, const int* n_desc, int max_desc, int group_rows, int sm_count, int* status,
+                               cudaStream_t st) {
+    const int mb = pad_rows((size_t)group_rows), nm = w2 ? 2 : 1;
+    const int ub = w.fmt == FQ_Q4_K ? 144 : 176;
+    int stages = kMaxStages;
+    while (stages > 2 && expert_smem_bytes(w.fmt, w.k, mb, nm, stages) > kSmemLimit) --stages;
+    // tiles per item: whole tiles per warp when the table is long enough to fill the SMs, K split across
+    // warps when it is short (a single token names top_k experts only)
+    const int tiles_per_mat = (w.n + 31) / 32;
+    int tpi = 8;
+    while (tpi > 1 && (long long)max_desc * ((tiles_per_mat + tpi - 1) / tpi) < 2LL * sm_count) tpi >>= 1;
+    const int units = w.k / 256;
+    while (tpi < 8 && units < kExpertWarps / tpi) tpi <<= 1;  // no more K parts than units
+    CUtensorMap t1, t2;
+    memset(&t1, 0, sizeof t1);
+    memset(&t2, 0, sizeof t2);
+    if (!make_stack_tmap(w, ub, &t1) || (w2 && !make_stack_tmap(*w2, ub, &t2))) return cudaErrorInvalidValue;
+    ExpertArgs a{w, w2 ? *w2 : DevWeights{}, src, src_index, top_k, out, table, n_desc, max_desc, tpi, stages, status};
+    long long items = (long long)max_desc * ((tiles_per_mat + tpi - 1) / tpi);
+    const int grid = (int)(items < sm_count ? (items > 0 ? items : 1) : sm_count);
+    const size_t smem = expert_smem_bytes(w.fmt, w.k, mb, nm, stages);
+    if (w.fmt == FQ_Q4_K)
+        return w2 ? launch_expert_mb<FQ_Q4_K, true>(a, mb, t1, t2, grid, smem, st) : launch_expert_mb<FQ_Q4_K, false>(a, mb, t1, t2, grid, smem, st);
+    return w2 ? launch_expert_mb<FQ_Q5_K, true>(a, mb, t1, t2, grid, smem, st) : launch_expert_mb<FQ_Q5_K, false>(a, mb, t1, t2, grid, smem, st);
+}
 
 }  // namespace fq

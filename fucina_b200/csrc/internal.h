@@ -71,6 +71,28 @@ struct RowsArgs {
     int l2_stream;    // weight copies carry an evict-first L2 hint (tile-major form)
     int rows_per_cta; // 0: rows split evenly over the grid; else CTA b serves rows [b*rows_per_cta, +rows_per_cta)
 };
+// Grouped expert form of the row-per-lane kernel (MoE decode): a device-built table of (expert, run of
+// <= 8 activation rows) entries over a row-major expert stack; the f32 activation rows are quantised
+// by the kernel itself. With w2 the gate (w) and up (w2) matrices are multiplied together and the
+// SwiGLU product is stored.
+struct ExpertArgs {
+    DevWeights w, w2;
+    const float* src;       // f32 rows: token rows (src_index set) or one row per sorted pair position
+    const int* src_index;   // sorted position -> pair id; the token row is pair / top_k
+    int top_k;
+    float* out;             // [pairs][n]
+    const GroupDesc* table;
+    const int* n_desc;
+    int max_desc;
+    int tiles_per_item;     // 1, 2, 4 or 8 tiles of 32 rows per work item; 8 / tiles_per_item warps split K
+    int stages;
+    int* status;
+};
+int expert_rows_max_group();
+bool expert_rows_eligible(const DevWeights& w, const DevWeights* w2, int group_rows);
+cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const float* src, const int* src_index, int top_k, float* out,
+                               const GroupDesc* table, const int* n_desc, int max_desc, int group_rows, int sm_count, int* status,
+                               cudaStream_t st);
 // true when the shape is one the kernel serves (format, K, m, shared memory)
 bool decode_rows_eligible(const DevWeights& w, size_t m);
 // bytes of natural-record scratch the non-fused form needs (0 for the fused form)

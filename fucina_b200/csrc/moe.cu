@@ -313,7 +313,11 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     // Row tile of the grouped kernel. A router sends a token to distinct experts, so an expert's run is
     // normally no longer than the batch; runs are split at this size either way, so repeated experts in
     // one token only cost an extra table entry.
-    const int group_rows = seq < kGroupRows ? seq : kGroupRows;
+    // K-quant expert stacks stream through the row-per-lane kernel (runs of <= 8 rows, activations quantised
+    // inside the kernel); other formats take the lane-per-chunk kernel with pre-quantised rows
+    const int stream_rows = seq < expert_rows_max_group() ? seq : expert_rows_max_group();
+    const bool streaming = expert_rows_eligible(gate, &up, stream_rows) && expert_rows_eligible(down, nullptr, stream_rows);
+    const int group_rows = streaming ? stream_rows : (seq < kGroupRows ? seq : kGroupRows);
     const int max_desc = max_desc_for(pairs, n_expert, group_rows);
     // one scratch block: order, inv, n_desc, table, quantised x rows, g rows, quantised g rows, down rows
     size_t off = 0;
@@ -344,6 +348,20 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
         if (shard.skip_foreign && (e = cudaMemsetAsync(order, 0, sizeof(int) * pairs, st)) != cudaSuccess) break;
         route_plan_kernel<<<1, 1024, sizeof(int) * 3 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, group_rows, order, inv, table, n_desc, n_desc + 1);
         if ((e = cudaGetLastError()) != cudaSuccess) break;
+        if (streaming) {
+            if ((e = launch_expert_rows(gate, &up, x_dev, order, top_k, g, table, n_desc, max_desc, group_rows, ctx->sm_count, ctx->status_dev,
+                                        st)) != cudaSuccess)
+                break;
+            if ((e = launch_expert_rows(down, nullptr, g, nullptr, 1, down_rows, table, n_desc, max_desc, group_rows, ctx->sm_count,
+                                        ctx->status_dev, st)) != cudaSuccess)
+                break;
+            const size_t total = (size_t)seq * hidden;
+            int blocks = (int)((total + 255) / 256);
+            if (blocks > 148 * 8) blocks = 148 * 8;
+            combine_kernel<<<blocks, 256, 0, st>>>(down_rows, weights_dev, inv, seq, hidden, top_k, out_dev);
+            e = cudaGetLastError();
+            break;
+        }
         // gather each pair's token row and quantise it, in expert order
         if ((e = launch_quantize_acts_layout(x_dev, order, top_k, pairs, hidden, fmt, qx, st)) != cudaSuccess) break;
         GemvArgs ga{gate, up, 0, qx, g, group_rows, out_pe, 0, table, n_desc, max_desc};
