@@ -657,6 +657,24 @@ cudaError_t launch_fmt(const RowsArgs& a, const CUtensorMap& tmap, int mb, bool 
 // up * gate * sigmoid(gate).
 constexpr int kExpertWarps = 8;
 
+// One block of one row against the first M activation records, accumulators acc[0..M).
+template <int FMT, int M>
+__device__ __forceinline__ void expert_block(uint32_t p, const ActView& V, int unit, float* acc) {
+    float(&a)[M] = *reinterpret_cast<float(*)[M]>(acc);
+    if (FMT == FQ_Q4_K) block_q4_k<M>(p, V, unit, a);
+    if (FMT == FQ_Q5_K) block_q5_k<M>(p, V, unit, a);
+}
+// Entries mostly hold fewer rows than the launch-wide bound MB (a token batch spreads over many
+// experts), so the block product is instantiated for 1, 2, 4 and 8 rows and chosen per entry.
+__host__ __device__ inline int expert_rows_step(int m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
+template <int FMT, int MB>
+__device__ __forceinline__ void expert_block_m(int mstep, uint32_t p, const ActView& V, int unit, float* acc) {
+    if (MB >= 8 && mstep == 8) return expert_block<FMT, MB >= 8 ? 8 : MB>(p, V, unit, acc);
+    if (MB >= 4 && mstep == 4) return expert_block<FMT, MB >= 4 ? 4 : MB>(p, V, unit, acc);
+    if (MB >= 2 && mstep == 2) return expert_block<FMT, MB >= 2 ? 2 : MB>(p, V, unit, acc);
+    expert_block<FMT, 1>(p, V, unit, acc);
+}
+
 template <int FMT, int MB, bool GATED>
 __global__ void __launch_bounds__(kExpertWarps * 32, 1)
     expert_rows_kernel(const ExpertArgs A, const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap2) {
@@ -734,9 +752,11 @@ __global__ void __launch_bounds__(kExpertWarps * 32, 1)
         item_of(il, d, tile);
         const GroupDesc G = A.table[d];
         if (il) __syncthreads();  // everyone is done with the previous item's activation records
-        // quantise this entry's rows: (row b, block blk) pairs over the warps; unused batch slots are zero
+        // quantise this entry's rows: (row b, block blk) pairs over the warps; the slots up to the row count the
+        // block product is instantiated for are zero
         const int nblk = k >> 8;
-        for (int i = warp; i < MB * nblk; i += kExpertWarps) {
+        const int mstep = min(MB, expert_rows_step(G.m));
+        for (int i = warp; i < mstep * nblk; i += kExpertWarps) {
             const int b = i / nblk, blk = i % nblk;
             uint8_t* rec = acts + (size_t)b * NS.row;
             if (b < G.m) {
@@ -766,13 +786,10 @@ __global__ void __launch_bounds__(kExpertWarps * 32, 1)
                     break;
                 }
                 const uint32_t p = slot0 + (uint32_t)stage * 32 * UB + (uint32_t)lane * UB;
-                if (!GATED || (j % NM) == 0) {
-                    if (FMT == FQ_Q4_K) block_q4_k<MB>(p, V, unit, acc[0]);
-                    if (FMT == FQ_Q5_K) block_q5_k<MB>(p, V, unit, acc[0]);
-                } else {
-                    if (FMT == FQ_Q4_K) block_q4_k<MB>(p, V, unit, acc[NM - 1]);
-                    if (FMT == FQ_Q5_K) block_q5_k<MB>(p, V, unit, acc[NM - 1]);
-                }
+                if (!GATED || (j % NM) == 0)
+                    expert_block_m<FMT, MB>(mstep, p, V, unit, acc[0]);
+                else
+                    expert_block_m<FMT, MB>(mstep, p, V, unit, acc[NM - 1]);
                 __syncwarp();  // every lane is done with this stage before it is refilled
                 ++consumed;
                 advance();
@@ -954,9 +971,14 @@ cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const 
     memset(&t1, 0, sizeof t1);
     memset(&t2, 0, sizeof t2);
     if (!make_stack_tmap(w, ub, &t1) || (w2 && !make_stack_tmap(*w2, ub, &t2))) return cudaErrorInvalidValue;
-    ExpertArgs a{w, w2 ? *w2 : DevWeights{}, src, src_index, top_k, out, table, n_desc, max_desc, tpi, stages, status};
     long long items = (long long)max_desc * ((tiles_per_mat + tpi - 1) / tpi);
-    const int grid = (int)(items < sm_count ? (items > 0 ? items : 1) : sm_count);
+    int grid = (int)(items < sm_count ? (items > 0 ? items : 1) : sm_count);
+    // a short table (one token): one item per CTA and two half-size CTAs per SM instead of a second round
+    if (items > sm_count && items <= 2LL * sm_count && expert_smem_bytes(w.fmt, w.k, mb, nm, 2) <= 113 * 1024) {
+        grid = (int)items;
+        stages = 2;
+    }
+    ExpertArgs a{w, w2 ? *w2 : DevWeights{}, src, src_index, top_k, out, table, n_desc, max_desc, tpi, stages, status};
     const size_t smem = expert_smem_bytes(w.fmt, w.k, mb, nm, stages);
     if (w.fmt == FQ_Q4_K)
         return w2 ? launch_expert_mb<FQ_Q4_K, true>(a, mb, t1, t2, grid, smem, st) : launch_expert_mb<FQ_Q4_K, false>(a, mb, t1, t2, grid, smem, st);

@@ -297,7 +297,12 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
     return rc;
 }
 
-int max_desc_for(int pairs, int n_expert, int group_rows) { return (pairs < n_expert ? pairs : n_expert) + pairs / group_rows; }
+// Upper bound of table entries: every expert run ends in at most one partial group (no more runs than
+// experts or pairs) and holds count / group_rows full ones; never more entries than pairs.
+int max_desc_for(int pairs, int n_expert, int group_rows) {
+    const int bound = (pairs < n_expert ? pairs : n_expert) + pairs / group_rows;
+    return bound < pairs ? bound : pairs;
+}
 
 int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
                        int seq, int top_k, const int* selected_dev, const float* weights_dev, Shard shard, float* out_dev,
