@@ -39,8 +39,11 @@ namespace {
 constexpr int BM = 128;        // weight rows per tile (UMMA M)
 constexpr int BN = 256;        // tokens per tile (UMMA N)
 constexpr int BK = 64;         // K elements per ring stage (128 bytes of bf16: one swizzle span)
-constexpr int A_STAGES = 3;    // ring of dequantised weight tiles
-constexpr int B_STAGES = 4;    // ring of token tiles
+// One ring of K slabs: stage s holds the token tile in shared memory and the dequantised weight slab in
+// tensor memory (32 columns = 64 bf16 along K per lane). One "full" barrier per stage collects the copy
+// engine's bytes and the 256 dequantising threads, one "empty" barrier is signalled by the MMAs'
+// commit: the single issuing thread waits once and commits once per slab, which is what bounds its rate.
+constexpr int STAGES = 5;
 constexpr int RAW_STAGES = 2;  // ring of packed K-quant units (one unit = 256 weights of 128 rows = four K slabs)
 constexpr int A_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_BYTES = BN * BK * 2;   // 32 KB
@@ -56,7 +59,9 @@ constexpr int kDequantWarps = 8;
 constexpr int kEpilogueWarps = 4;
 constexpr int kThreads = (2 + kDequantWarps + kEpilogueWarps) * 32;  // 448
 constexpr unsigned kWaitLimit = 1u << 20;
-constexpr int TMEM_COLS = 512;  // two 256-column accumulators: the epilogue of tile t overlaps the MMAs of tile t+1
+constexpr int TMEM_COLS = 512;  // columns 0..255: the f32 accumulator; from column 256: the A ring (STAGES x 32)
+constexpr int A_COLS = BK / 2;  // tensor-memory columns of one A slab: two bf16 per 32-bit column
+constexpr int A_COL0 = BN;
 
 struct TcArgs {
     DevWeights w;
@@ -69,6 +74,7 @@ struct TcArgs {
     // 128-row weight tile and the run of consecutive activation rows it multiplies
     const TcTile* table;
     const int* n_tiles_dev;
+    int diag;  // diagnosis only (results are garbage): 1 = token tiles are not fetched, 2 = weights are not expanded
 };
 
 // One output tile: weight rows [rt*128, +128) of matrix `mat` times activation rows [tok0, tok0+ntok).
@@ -84,9 +90,28 @@ __device__ __forceinline__ TileRef tile_ref(const TcArgs& A, int tile, int row_t
     return {A.mat, tile % row_tiles, tt * BN, min(BN, A.m - tt * BN)};
 }
 
+// Diagnostic build only (-DFQ_TIMELINE): the MMA thread of CTA 0 stamps, for the first slabs of its first tile,
+// when it starts waiting for A, has A, has B, has issued the MMAs and has committed.
+#ifdef FQ_TIMELINE
+constexpr int kTlSlabs = 48;
+__device__ unsigned long long g_tc_timeline[kTlSlabs * 5];
+__device__ __forceinline__ unsigned long long tl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+    return t;
+}
+#define TL_STAMP(slab, what)                                                                          \
+    do {                                                                                              \
+        if (blockIdx.x == 0 && t == 0 && (slab) < kTlSlabs) g_tc_timeline[(slab) * 5 + (what)] = tl_now(); \
+    } while (0)
+#else
+#define TL_STAMP(slab, what) \
+    do {                     \
+    } while (0)
+#endif
+
 struct __align__(8) Barriers {
-    uint64_t full_a[A_STAGES], empty_a[A_STAGES], full_b[B_STAGES], empty_b[B_STAGES], raw_full[RAW_STAGES], raw_empty[RAW_STAGES],
-        tmem_full[2], tmem_empty[2];
+    uint64_t full[STAGES], empty[STAGES], raw_full[RAW_STAGES], raw_empty[RAW_STAGES], tmem_full[1], tmem_empty[1];
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -143,6 +168,15 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+        : "memory");
+}
+// The same MMA with A read from tensor memory (lane = row, 32-bit column = two consecutive bf16 along K).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -315,12 +349,12 @@ template <int FMT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, const __grid_constant__ CUtensorMap tmap_tokens,
                                                               const __grid_constant__ CUtensorMap tmap_weights) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    // 1024-byte aligned rings: [A stages][B stages][packed-weight stages][barriers]
+    // 1024-byte aligned rings: [B stages][packed-weight stages][barriers]; the dequantised A slabs live in tensor memory
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* sA = smem;
-    uint8_t* sB = sA + A_STAGES * A_BYTES;
-    uint8_t* sRaw = sB + B_STAGES * B_BYTES;
+    uint8_t* sB = smem;
+    uint8_t* sRaw = sB + STAGES * B_BYTES;
     Barriers* B = reinterpret_cast<Barriers*>(sRaw + RAW_STAGES * Staged<FMT>::raw_bytes);
+    static_assert(A_COL0 + STAGES * A_COLS <= TMEM_COLS, "A ring does not fit the tensor memory");
     constexpr bool kStaged = Staged<FMT>::on;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = A.w.n, k = A.w.k, m = A.m;
@@ -329,22 +363,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
     const int n_tiles = A.table ? *A.n_tiles_dev : row_tiles * tok_tiles;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < A_STAGES; ++s) {
-            mbar_init(smem_u32(&B->full_a[s]), kDequantWarps * 32);
-            mbar_init(smem_u32(&B->empty_a[s]), 1);
-        }
-        for (int s = 0; s < B_STAGES; ++s) {
-            mbar_init(smem_u32(&B->full_b[s]), 1);
-            mbar_init(smem_u32(&B->empty_b[s]), 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&B->full[s]), kDequantWarps * 32 + 1);  // the dequantising threads + the producer's expect_tx arrival
+            mbar_init(smem_u32(&B->empty[s]), 1);
         }
         for (int s = 0; s < RAW_STAGES; ++s) {
             mbar_init(smem_u32(&B->raw_full[s]), 1);
             mbar_init(smem_u32(&B->raw_empty[s]), kDequantWarps * 32);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&B->tmem_full[i]), 1);
-            mbar_init(smem_u32(&B->tmem_empty[i]), kEpilogueWarps * 32);
-        }
+        mbar_init(smem_u32(&B->tmem_full[0]), 1);
+        mbar_init(smem_u32(&B->tmem_empty[0]), kEpilogueWarps * 32);
         B->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -396,12 +424,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                         ++gu;
                     }
                     for (int p = 0; p < 4; ++p, ++gb) {
-                        const int s = gb % B_STAGES;
-                        if (!mbar_wait(smem_u32(&B->empty_b[s]), ((gb / B_STAGES) & 1) ^ 1, B, A.status)) {
+                        const int s = gb % STAGES;
+                        if (!mbar_wait(smem_u32(&B->empty[s]), ((gb / STAGES) & 1) ^ 1, B, A.status)) {
                             ok = false;
                             break;
                         }
-                        const uint32_t bar = smem_u32(&B->full_b[s]);
+                        const uint32_t bar = smem_u32(&B->full[s]);
+                        if (A.diag == 1) {
+                            mbar_arrive(bar);
+                            continue;
+                        }
                         mbar_arrive_expect_tx(bar, B_BYTES);
                         asm volatile(
                             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
@@ -415,55 +447,60 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            int ga = 0, gb = 0, t = 0;
+            int g = 0, t = 0;
             for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
-                // the epilogue of the tile that last used this accumulator must have drained it
-                const uint32_t acc = tmem + (uint32_t)(t & 1) * BN;
-                if (!mbar_wait(smem_u32(&B->tmem_empty[t & 1]), ((t >> 1) & 1) ^ 1, B, A.status)) break;
+                // the epilogue of the previous tile must have drained the accumulator
+                const uint32_t acc = tmem;
+                if (!mbar_wait(smem_u32(&B->tmem_empty[0]), (t & 1) ^ 1, B, A.status)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 bool ok = true;
-                for (int ks = 0; ks < kslabs; ++ks, ++ga, ++gb) {
-                    const int sa = ga % A_STAGES, sb = gb % B_STAGES;
-                    if (!mbar_wait(smem_u32(&B->full_a[sa]), (ga / A_STAGES) & 1, B, A.status) ||
-                        !mbar_wait(smem_u32(&B->full_b[sb]), (gb / B_STAGES) & 1, B, A.status)) {
+                for (int ks = 0; ks < kslabs; ++ks, ++g) {
+                    const int sa = g % STAGES, sb = sa;
+                    TL_STAMP(ks, 0);
+                    if (!mbar_wait(smem_u32(&B->full[sa]), (g / STAGES) & 1, B, A.status)) {
                         ok = false;
                         break;
                     }
+                    TL_STAMP(ks, 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t da = umma_desc(smem_u32(sA + sa * A_BYTES)), db = umma_desc(smem_u32(sB + sb * B_BYTES));
+                    const uint32_t ta = tmem + (uint32_t)(A_COL0 + sa * A_COLS);
+                    const uint64_t db = umma_desc(smem_u32(sB + sb * B_BYTES));
 #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk)  // 32 bytes along K per instruction: +2 in the 16-byte address field
-                        umma_bf16(acc, da + 2 * kk, db + 2 * kk, (ks | kk) ? 1u : 0u);
-                    // both stages are free once these MMAs have read them
-                    umma_commit(smem_u32(&B->empty_a[sa]));
-                    umma_commit(smem_u32(&B->empty_b[sb]));
+                    for (int kk = 0; kk < BK / 16; ++kk)  // 16 elements along K per instruction: 8 columns of A, 32 bytes of B
+                        umma_bf16_ts(acc, ta + 8 * kk, db + 2 * kk, (ks | kk) ? 1u : 0u);
+                    TL_STAMP(ks, 3);
+                    umma_commit(smem_u32(&B->empty[sa]));  // the stage is free once these MMAs have read it
+                    TL_STAMP(ks, 4);
                 }
                 if (!ok) break;
-                umma_commit(smem_u32(&B->tmem_full[t & 1]));
+                umma_commit(smem_u32(&B->tmem_full[0]));
             }
         }
     } else if (warp < 2 + kDequantWarps) {
         // ---------------- dequantise ----------------
-        const int dt = threadIdx.x - 64;   // 0..255
-        const int r = dt & (BM - 1);       // weight row inside the tile
-        const int h = dt >> 7;             // which 32-weight half of the 64-element slab
+        // a warp reaches the tensor-memory lanes 32 * (warp % 4) .. +31 only: that fixes its rows; the two warps
+        // of a lane quarter take the two 32-weight halves of the 64-element slab
+        const int r = 32 * (warp & 3) + lane;  // weight row inside the tile = tensor-memory lane
+        const int h = (warp - 2) >> 2;
         constexpr int ub = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 256;
         const size_t ustride = unit_stride(A.w, ub);
         int ga = 0, gu = 0;
         bool ok = true;
-        // expand one slab into row r of A stage (ga % A_STAGES): 128 bytes, 16-byte chunk j stored at
-        // j ^ (r % 8) (128-byte swizzle); generic-proxy stores are fenced towards the MMA's async proxy
+        // one slab of this row goes to A stage (ga % STAGES) in tensor memory: lane r, 16 columns from h * 16
         auto publish = [&](const uint32_t (&v)[16]) -> bool {
-            const int s = ga % A_STAGES;
-            if (!mbar_wait(smem_u32(&B->empty_a[s]), ((ga / A_STAGES) & 1) ^ 1, B, A.status)) return false;
-            uint8_t* rowp = sA + s * A_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int chunk = (h * 4 + j) ^ (r & 7);
-                *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(smem_u32(&B->full_a[s]));
+            const int s = ga % STAGES;
+            if (!mbar_wait(smem_u32(&B->empty[s]), ((ga / STAGES) & 1) ^ 1, B, A.status)) return false;
+            __syncwarp();  // the store below is a warp-wide (.aligned) instruction
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(A_COL0 + s * A_COLS + h * 16);
+            asm volatile(
+                "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+                "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+                "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+                : "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(smem_u32(&B->full[s]));
             ++ga;
             return true;
         };
@@ -485,7 +522,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                     for (int p = 0; p < 4; ++p) {
                         raw.load_slab(blk, p);
                         uint32_t v[16];
-                        raw.expand(p, h, v);
+                        if (A.diag == 2) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) v[i] = 0x3c003c00u;
+                        } else {
+                            raw.expand(p, h, v);
+                        }
                         if (!(ok = publish(v))) break;
                     }
                     // the loads above have returned (their values went into the stores): the unit may be overwritten
@@ -512,13 +554,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
             const TileRef T = tile_ref(A, tile, row_tiles);
             const int rt = T.rt;
-            if (!mbar_wait(smem_u32(&B->tmem_full[t & 1]), (t >> 1) & 1, B, A.status)) break;
+            if (!mbar_wait(smem_u32(&B->tmem_full[0]), t & 1, B, A.status)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int q = warp & 3;                       // TMEM lane quarter this warp may read
             const int out_row = rt * BM + q * 32 + lane;  // weight row = output column
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t acc[32];
-                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)((t & 1) * BN + c0);
+                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -538,7 +580,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(smem_u32(&B->tmem_empty[t & 1]));
+            mbar_arrive(smem_u32(&B->tmem_empty[0]));
         }
     }
 
@@ -582,7 +624,7 @@ EncodeTiledFn encode_fn() {
 
 template <int FMT>
 cudaError_t launch_tc(const TcArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap_w, int grid, cudaStream_t st) {
-    const size_t smem = (size_t)A_STAGES * A_BYTES + (size_t)B_STAGES * B_BYTES + (size_t)RAW_STAGES * Staged<FMT>::raw_bytes + sizeof(Barriers) + 1024;
+    const size_t smem = (size_t)STAGES * B_BYTES + (size_t)RAW_STAGES * Staged<FMT>::raw_bytes + sizeof(Barriers) + 1024;
     static bool granted = false;
     if (!granted) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -592,6 +634,12 @@ cudaError_t launch_tc(const TcArgs& a, const CUtensorMap& tmap, const CUtensorMa
     gemm_tc_kernel<FMT><<<grid, kThreads, smem, st>>>(a, tmap, tmap_w);
     return cudaGetLastError();
 }
+
+#ifdef FQ_TIMELINE
+extern "C" __attribute__((visibility("default"))) int fq_debug_tc_timeline(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_tc_timeline, sizeof(unsigned long long) * kTlSlabs * 5);
+}
+#endif
 
 }  // namespace
 
@@ -630,7 +678,8 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return fail(FQ_DECLINED_ARGS, "tensor map for the packed weights could not be encoded");
     }
-    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev};
+    static const int diag = getenv("FUCINA_B200_TC_DIAG") ? atoi(getenv("FUCINA_B200_TC_DIAG")) : 0;
+    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev, diag};
     const int tiles = table ? max_tiles : ((w.n + BM - 1) / BM) * (int)((rows + BN - 1) / BN);
     const int grid = tiles < ctx->sm_count ? (tiles > 0 ? tiles : 1) : ctx->sm_count;
     cudaError_t e;
