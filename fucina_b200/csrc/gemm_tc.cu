@@ -11,16 +11,22 @@
 // ulp. Results differ from the f64 reference over bf16-rounded operands by that
 // and by f32 accumulation.
 //
-// One persistent CTA per SM walks output tiles of 128 weight rows x 256 tokens.
-//   warp 0        TMA producer: 256 x 64 bf16 token tiles (128-byte swizzle) into a 4-stage ring
+// One persistent CTA per SM walks output tiles of 128 weight rows x 256 tokens in K slabs of 64.
+//   warp 0        copy-engine producer: 256 x 64 bf16 token tiles (128-byte swizzle) into a 5-stage
+//                 shared-memory ring, and the packed K-quant blocks of the tile's 128 rows (one
+//                 256-weight unit = four slabs at a time) into a 2-stage ring
 //   warp 1        one thread issues tcgen05.mma (M=128 weight rows, N=256 tokens, K=16 per
-//                 instruction, bf16 x bf16 -> f32) with shared-memory descriptors; the accumulator
-//                 lives in 256 TMEM columns; tcgen05.commit releases ring stages and signals the epilogue
-//   warps 2..9    dequantise: two threads per weight row expand 64 weights of the current K slab
-//                 into the 128-byte-swizzled K-major A tile
+//                 instruction, bf16 x bf16 -> f32): the A operand is read from TENSOR memory, the B
+//                 operand through a shared-memory descriptor; the accumulator lives in 256 TMEM
+//                 columns; tcgen05.commit releases a ring stage and signals the epilogue
+//   warps 2..9    dequantise: two threads per weight row expand 64 weights of the current slab and
+//                 store them with tcgen05.st into the A ring in tensor memory (32 columns per
+//                 stage, next to the accumulator): the dequantised weights never touch shared
+//                 memory, whose bandwidth the token tiles need
 //   warps 10..13  epilogue: read the finished accumulator with tcgen05.ld and store f32 results
-//                 (coalesced along n) while the other roles already work on the next tile (the
-//                 accumulator is double-buffered in 2 x 256 TMEM columns)
+//                 (coalesced along n)
+// A stage has one "full" barrier (copy-engine bytes + the 256 dequantising threads) and one "empty"
+// barrier (the MMAs' commit), so the issuing thread waits once and commits once per slab.
 // Every mbarrier wait is bounded and also watches a CTA-wide abort flag; a wait that gives up sets
 // FQ_ERR_TIMEOUT in the status word, all roles fall through to the common exit, TMEM is freed.
 #include <cuda.h>
