@@ -235,8 +235,11 @@ struct Chunk<FQ_Q2_0> {
     }
 };
 
-template <int FMT, int MB, int LPR, bool GATED>
+// MODE 0: dense (one matrix, MB >= m rows, padded rows are zero); 1: grouped table (MoE), a group
+// multiplies only its own m <= MB rows; 2: grouped with the fused gate/up pair.
+template <int FMT, int MB, int LPR, int MODE>
 __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
+    constexpr bool GATED = MODE == 2, GUARD = MODE >= 1;
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int R = 2;  // weight rows per lane group (gated: the gate row and the up row)
     constexpr ActLayout L = {FMT == FQ_Q8_0 ? 16 : (FMT == FQ_TQ2_0 || FMT == FQ_Q2_0) ? 64 : 32,
@@ -258,12 +261,13 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
         cbase += (size_t)d.row0 * A.ldc;
     }
 
-    // stage the m activation rows of this group (rows beyond m are never read: the compute is guarded)
+    // stage the m activation rows; the dense form zeroes the padded batch slots (they are multiplied), the
+    // grouped forms never read them
     {
-        const int units = m * (int)(S.row / 16);
+        const int units = m * (int)(S.row / 16), all = (GUARD ? m : MB) * (int)(S.row / 16);
         const uint4* src = reinterpret_cast<const uint4*>(acts);
         uint4* dst = reinterpret_cast<uint4*>(smem);
-        for (int i = threadIdx.x; i < units; i += kThreads) dst[i] = __ldg(src + i);
+        for (int i = threadIdx.x; i < all; i += kThreads) dst[i] = i < units ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
     }
     __syncthreads();
 
@@ -303,7 +307,7 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
             for (int r = 0; r < R; ++r) ch[r].decode(c);
 #pragma unroll
             for (int b = 0; b < MB; ++b) {
-                if (b < m) {  // CTA-uniform: a short group (few tokens on this expert) pays for its own rows only
+                if (!GUARD || b < m) {  // CTA-uniform: a short group (few tokens on this expert) pays for its own rows only
                     const uint8_t* rec = smem + (size_t)b * S.row;
                     int4 a[L.segs];
 #pragma unroll
@@ -320,7 +324,7 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int b = 0; b < MB; ++b) {
-                if (b < m) {
+                if (!GUARD || b < m) {
                     float v = acc[r][b];
 #pragma unroll
                     for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(gmask, v, o);
@@ -352,11 +356,12 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
     }
 }
 
-template <int FMT, int MB, int LPR, bool GATED>
+template <int FMT, int MB, int LPR, int MODE>
 cudaError_t launch_one(const GemvArgs& a, int sm_count, cudaStream_t st) {
+    constexpr bool GATED = MODE == 2;
     const ActSizes S = act_sizes(FMT, a.w.k);
     const size_t smem = (size_t)MB * S.row;
-    auto kern = gemv_kernel<FMT, MB, LPR, GATED>;
+    auto kern = gemv_kernel<FMT, MB, LPR, MODE>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
@@ -386,12 +391,16 @@ cudaError_t launch_lpr(const GemvArgs& a, int sm_count, cudaStream_t st) {
         const int cost = ((C + lpr - 1) / lpr) * lpr;
         if (cost < best_cost) best = lpr, best_cost = cost;
     }
-    const bool gated = a.w2.base != nullptr;
+    const int mode = a.w2.base != nullptr ? 2 : a.table != nullptr ? 1 : 0;
+#define FQ_LAUNCH_LPR(L)                                                    \
+    (mode == 2 ? launch_one<FMT, MB, L, 2>(a, sm_count, st)                  \
+               : mode == 1 ? launch_one<FMT, MB, L, 1>(a, sm_count, st) : launch_one<FMT, MB, L, 0>(a, sm_count, st))
     switch (best) {
-        case 32: return gated ? launch_one<FMT, MB, 32, true>(a, sm_count, st) : launch_one<FMT, MB, 32, false>(a, sm_count, st);
-        case 16: return gated ? launch_one<FMT, MB, 16, true>(a, sm_count, st) : launch_one<FMT, MB, 16, false>(a, sm_count, st);
-        default: return gated ? launch_one<FMT, MB, 8, true>(a, sm_count, st) : launch_one<FMT, MB, 8, false>(a, sm_count, st);
+        case 32: return FQ_LAUNCH_LPR(32);
+        case 16: return FQ_LAUNCH_LPR(16);
+        default: return FQ_LAUNCH_LPR(8);
     }
+#undef FQ_LAUNCH_LPR
 }
 
 template <int FMT>
