@@ -292,7 +292,31 @@ def run_ours(args) -> dict:
     barrier(world)
     e2e = {"value": round(world * bytes_step * args.steps / e2e_s / 1e9, 2), "unit": "GB/s",
            "h2d_bytes_per_step": len(STACK_N) * batch * K * 4, "d2h_bytes_per_step": sum(STACK_N) * batch * 4,
-           "ms_per_step": round(e2e_s / args.steps * 1e3, 4), "timing": "wall clock between device syncs"}
+           "ms_per_step": round(e2e_s / args.steps * 1e3, 4), "timing": "wall clock between device syncs",
+           "call": "fq_gemm_quant_nt (blocking), one call per product"}
+
+    # the same step through the asynchronous entry (the reference's gemmQuantNtAsync + Work.finish): the
+    # four products of a step are submitted back to back and finished afterwards, so uploads, kernels and
+    # downloads of different products overlap
+    def step_host_async(i: int):
+        st = stacks[i % n_copies]
+        works = [P.gemm_quant_nt_async(Q4_K, hw, x, n, batch, K, out=y) for hw, x, y, n in zip(st.host, host_x, host_y, STACK_N)]
+        for wk in works:
+            wk.finish(copy_to_host=True)
+            wk.destroy()
+
+    for i in range(max(args.warmup, n_copies)):
+        step_host_async(i)
+    barrier(world)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        step_host_async(i)
+    P.synchronize()
+    async_s = max_over_ranks(time.perf_counter() - t0, world)
+    barrier(world)
+    e2e["async_submit"] = {"value": round(world * bytes_step * args.steps / async_s / 1e9, 2), "unit": "GB/s",
+                           "ms_per_step": round(async_s / args.steps * 1e3, 4),
+                           "call": "fq_gemm_quant_nt_async x4, then fq_work_finish x4"}
 
     out = {
         "metric": "quant GEMV HBM GB/s", "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,

@@ -543,7 +543,8 @@ static int upload_f32(Ctx* ctx, const float* host, size_t bytes, Staged* s) {
     s->dev = dev_alloc(bytes);
     if (!s->dev) return fail(FQ_DECLINED_BUDGET, "device allocation of %zu bytes failed", bytes);
     const void* src = host;
-    if (!host_is_pinned(host)) {
+    // small rows are always staged: copying a few KB costs less than asking the driver what kind of memory it is
+    if (bytes <= 64 * 1024 || !host_is_pinned(host)) {
         s->pin = pin_alloc(bytes);
         if (!s->pin) return fail(FQ_DECLINED_BUDGET, "pinned allocation of %zu bytes failed", bytes);
         memcpy(s->pin, host, bytes);
@@ -606,20 +607,37 @@ static int gemm_host(int fmt, const void* rhs, size_t rhs_len, int cacheable, si
     Staged in;
     const size_t out_bytes = batch * m * n * sizeof(float);
     void* c_dev = nullptr;
+    void* c_pin = nullptr;
     rc = upload_f32(ctx, a, m * k * sizeof(float), &in);
+    // Decode-sized results are written by the kernel straight into page-locked host memory (device-visible
+    // under unified addressing): one copy operation and its latency less per call.
+    const bool direct_out = m <= 8 && out_bytes <= (size_t)1 << 20;
     if (rc == FQ_OK) {
-        c_dev = dev_alloc(out_bytes);
-        if (!c_dev) rc = fail(FQ_DECLINED_BUDGET, "device allocation of %zu bytes failed", out_bytes);
+        if (direct_out) {
+            c_pin = pin_alloc(out_bytes);
+            c_dev = c_pin;
+        } else {
+            c_dev = dev_alloc(out_bytes);
+        }
+        if (!c_dev) rc = fail(FQ_DECLINED_BUDGET, "result allocation of %zu bytes failed", out_bytes);
     }
     bool submitted = false;
     for (size_t b = 0; b < batch && rc == FQ_OK; ++b) {
         rc = gemm_dev(ctx, view, (int)b, (const float*)in.dev, (float*)c_dev + b * m * n, m, n, FQ_MODE_AUTO, 0, ctx->stream);
         submitted = true;
     }
-    if (rc == FQ_OK) rc = download_f32(ctx, c_dev, c, out_bytes);
-    else if (submitted) cudaStreamSynchronize(ctx->stream);
-    cudaStreamSynchronize(ctx->stream);
-    dev_free(c_dev);
+    if (rc == FQ_OK && direct_out) {
+        cudaError_t e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) rc = cuda_fail(e, "result wait");
+        else memcpy(c, c_pin, out_bytes);
+        g_trace.d2h_bytes += out_bytes;
+    } else if (rc == FQ_OK) {
+        rc = download_f32(ctx, c_dev, c, out_bytes);
+    } else if (submitted) {
+        cudaStreamSynchronize(ctx->stream);
+    }
+    if (direct_out) pin_free(c_pin);
+    else dev_free(c_dev);
     dev_free(in.dev);
     pin_free(in.pin);
     if (temp) fq_weights_free(temp);
@@ -641,6 +659,8 @@ struct fq_work {
     float* c_host;
     cudaEvent_t done;
     int state;  // 0 submitted, 1 host_ready, 2 discarded, -1 failed
+    void* in_dev;  // staged activations: released once the product has run (finish / destroy)
+    void* in_pin;
 };
 
 using namespace fq;
@@ -877,6 +897,8 @@ int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheab
         w->c_host = c_host;
         w->state = 0;
         w->done = nullptr;
+        w->in_dev = nullptr;
+        w->in_pin = nullptr;
         if (!w->c_dev) rc = fail(FQ_DECLINED_BUDGET, "device allocation failed");
         else if (cudaEventCreateWithFlags(&w->done, cudaEventDisableTiming) != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "event create");
     }
@@ -886,14 +908,15 @@ int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheab
         cudaError_t e = cudaEventRecord(w->done, ctx->stream);
         if (e != cudaSuccess) rc = cuda_fail(e, "event record");
     }
-    // staging blocks go back to the cache; later users are stream-ordered after this submit
-    dev_free(in.dev);
-    if (in.pin) {
-        cudaStreamSynchronize(ctx->stream);  // the pinned source must outlive its copy
-        pin_free(in.pin);
+    // the staged activations stay with the token until it is finished: no host wait inside a submit
+    if (rc == FQ_OK) {
+        w->in_dev = in.dev;
+        w->in_pin = in.pin;
     }
     if (rc != FQ_OK) {
         cudaStreamSynchronize(ctx->stream);
+        dev_free(in.dev);
+        pin_free(in.pin);
         if (w) {
             if (w->done) cudaEventDestroy(w->done);
             dev_free(w->c_dev);
@@ -918,6 +941,9 @@ int fq_work_finish(fq_work* w, int copy_to_host) {
         w->state = -1;
         return cuda_fail(e, "work wait");
     }
+    dev_free(w->in_dev);
+    pin_free(w->in_pin);
+    w->in_dev = w->in_pin = nullptr;
     if (copy_to_host && w->c_host) {
         // order the copy after the producer on the compute stream
         int rc = download_f32(ctx, w->c_dev, w->c_host, w->bytes);
@@ -941,6 +967,8 @@ void fq_work_destroy(fq_work* w) {
         cudaStreamSynchronize(g_ctx.stream);
         cudaEventDestroy(w->done);
         dev_free(w->c_dev);
+        dev_free(w->in_dev);
+        pin_free(w->in_pin);
     }
     g_slots_in_use--;
     delete w;

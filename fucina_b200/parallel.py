@@ -155,34 +155,33 @@ class ExpertParallelMoE:
         dist.all_gather_into_tensor(sel_all.view(W * T, k), selected.reshape(T, k).contiguous(), group=self.group)
         dist.all_gather_into_tensor(w_all.view(W * T, k), weights.reshape(T, k).contiguous(), group=self.group)
         out = torch.empty((T, hidden), dtype=x.dtype, device=x.device)
-        gloo = dist.get_backend(self.group) == "gloo"   # gloo has no reduce-scatter and no async overlap worth having
-        if chunks <= 1 or T % chunks or gloo:
-            x_all = torch.empty((W * T, hidden), dtype=x.dtype, device=x.device)
-            dist.all_gather_into_tensor(x_all, x.contiguous(), group=self.group)
-            partial = partial_ffn(x_all, sel_all.view(W * T, k), w_all.view(W * T, k))
-            if gloo:
-                dist.all_reduce(partial, group=self.group)
-                out.copy_(partial[self.rank * T:(self.rank + 1) * T])
-            else:
-                dist.reduce_scatter_tensor(out, partial.contiguous(), group=self.group)
-            return out
+        gloo = dist.get_backend(self.group) == "gloo"   # gloo has no reduce-scatter: all-reduce and keep this rank's rows
+        if chunks < 1 or T % chunks:
+            chunks = 1
         # Token chunks pipeline the exchange against the expert products: while chunk c is multiplied, chunk c+1
-        # is being gathered and chunk c-1 reduced (collectives run on the communicator's own stream).
+        # is being gathered and chunk c-1 reduced (asynchronous collectives run on the communicator's own stream).
         h = T // chunks
         x = x.contiguous()
         gathers, xs = [], []
         for c in range(chunks):
             xc = torch.empty((W * h, hidden), dtype=x.dtype, device=x.device)
-            gathers.append(dist.all_gather_into_tensor(xc, x[c * h:(c + 1) * h], group=self.group, async_op=True))
+            gathers.append(dist.all_gather_into_tensor(xc, x[c * h:(c + 1) * h], group=self.group, async_op=not gloo))
             xs.append(xc)
-        reduces = []
+        pending = []
         for c in range(chunks):
-            gathers[c].wait()
+            if gathers[c] is not None:
+                gathers[c].wait()
+            # rows of chunk c in rank-major order, as the gather lays the tokens out
             sel_c = sel_all[:, c * h:(c + 1) * h].reshape(W * h, k)
             w_c = w_all[:, c * h:(c + 1) * h].reshape(W * h, k)
             partial = partial_ffn(xs[c], sel_c, w_c)
-            reduces.append((dist.reduce_scatter_tensor(out[c * h:(c + 1) * h], partial, group=self.group, async_op=True), partial))
-        for work, _keep in reduces:
+            if gloo:
+                dist.all_reduce(partial, group=self.group)
+                out[c * h:(c + 1) * h].copy_(partial[self.rank * h:(self.rank + 1) * h])
+            else:
+                pending.append((dist.reduce_scatter_tensor(out[c * h:(c + 1) * h], partial.contiguous(), group=self.group, async_op=True),
+                                partial))
+        for work, _keep_alive in pending:
             work.wait()
         return out
 

@@ -92,9 +92,10 @@ def _worker(rank: int, world: int, port: int, case: str, q):
                     acc[mine] += y
                 return torch.from_numpy(acc)
 
-            got2 = moe.forward_gathered(torch.from_numpy(x), torch.from_numpy(sel), torch.from_numpy(w), partial).numpy()
             scale = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
-            ok = ok and float(np.max(np.abs(got2 - want))) <= 1e-5 * scale   # only the f32 summation order differs
+            for chunks in (1, 7):   # one exchange, and one per token (T = 7): the pipelined form's indexing
+                got2 = moe.forward_gathered(torch.from_numpy(x), torch.from_numpy(sel), torch.from_numpy(w), partial, chunks=chunks).numpy()
+                ok = ok and float(np.max(np.abs(got2 - want))) <= 1e-5 * scale   # only the f32 summation order differs
             q.put((rank, ok))
     finally:
         dist.destroy_process_group()
