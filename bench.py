@@ -341,18 +341,19 @@ def cpu_baseline(host_w, host_x, budget_s: float) -> dict:
 
     cores = os.cpu_count() or 1
     bytes_step = stack_bytes(1)
-    oracle.matmul(Q4_K, host_w[0][:256], host_x[0])  # load the library
+    oracle.matmul_fast(Q4_K, host_w[0][:256], host_x[0])  # load the library
     t0 = time.perf_counter()
     passes = 0
     while True:
         for w, x in zip(host_w, host_x):
-            oracle.matmul(Q4_K, w, x)
+            oracle.matmul_fast(Q4_K, w, x)
         passes += 1
         dt = time.perf_counter() - t0
         if dt > budget_s or passes >= 5000:
             break
     return {"value": round(bytes_step * passes / dt / 1e9, 3), "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": f"{passes} pass(es) of the full stack (4 products, batch 1), {dt:.1f} s",
+            "sample": f"{passes} pass(es) of the full stack (4 products, batch 1), {dt:.1f} s, "
+                      + ("AVX2 block dots" if oracle.has_simd(Q4_K) else "scalar block dots"),
             "ms_per_step": round(dt / passes * 1e3, 2)}
 
 
@@ -374,7 +375,7 @@ def run_reference(args) -> dict:
 
     def step():
         for w, x in zip(ws, xs):
-            oracle.matmul(Q4_K, w, x)
+            oracle.matmul_fast(Q4_K, w, x)
 
     for _ in range(args.warmup):
         step()
@@ -384,7 +385,8 @@ def run_reference(args) -> dict:
     dt = time.perf_counter() - t0
     value = round(bytes_step * args.steps / dt / 1e9, 3)
     cores = os.cpu_count() or 1
-    sample = f"rows/{frac} of each stack matrix per step, {args.steps} steps, {dt:.1f} s"
+    sample = (f"rows/{frac} of each stack matrix per step, {args.steps} steps, {dt:.1f} s, "
+              + ("AVX2 block dots" if oracle.has_simd(Q4_K) else "scalar block dots"))
     return {
         "impl": "reference", "metric": "quant GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 4),

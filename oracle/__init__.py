@@ -122,6 +122,43 @@ def matmul(fmt: int, blocks: np.ndarray, a: np.ndarray) -> np.ndarray:
     return c
 
 
+_fast = None
+
+
+def fast_lib():
+    """The SIMD restatement used as the TIMED CPU baseline (oracle/cpu_kernels.cpp), or None if it is not built."""
+    global _fast
+    if _fast is None:
+        path = os.path.join(_HERE, "libcpu_kernels.so")
+        if not os.path.exists(path):
+            from . import build as _b
+
+            _b.build()
+        _fast = ctypes.CDLL(path) if os.path.exists(path) else False
+    return _fast or None
+
+
+def has_simd(fmt: int) -> bool:
+    f = fast_lib()
+    return bool(f and f.cpuk_has_simd(fmt))
+
+
+def matmul_fast(fmt: int, blocks: np.ndarray, a: np.ndarray) -> np.ndarray:
+    """Same values as `matmul`, computed by the runtime-dispatched SIMD arm where one exists."""
+    f = fast_lib()
+    if f is None:
+        return matmul(fmt, blocks, a)
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    m, k = a.shape
+    n = blocks.shape[0]
+    assert blocks.shape[1] == row_bytes(fmt, k)
+    c = np.zeros((m, n), dtype=np.float32)
+    rc = f.cpuk_matmul(fmt, _p(blocks), _sz(blocks.shape[1]), _p(a), _p(c), _sz(m), _sz(n), _sz(k))
+    assert rc == 0
+    return c
+
+
 def matmul_ptqtp(planes: list[np.ndarray], a: np.ndarray) -> np.ndarray:
     planes = [np.ascontiguousarray(p, dtype=np.uint8) for p in planes]
     a = np.ascontiguousarray(a, dtype=np.float32)

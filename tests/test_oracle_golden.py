@@ -168,3 +168,17 @@ def test_oracle_reproduces_committed_cases(oracle_cases):
         k = a.shape[1]
         assert np.array_equal(oracle.dequantize_rows(fmt, blocks, k).view(np.uint32), c[f"{name}_dequant"].view(np.uint32))
         assert np.array_equal(oracle.matmul(fmt, blocks, a).view(np.uint32), c[f"{name}_matmul"].view(np.uint32))
+
+
+def test_simd_baseline_equals_the_scalar_oracle():
+    """The timed CPU baseline (oracle/cpu_kernels.cpp) must produce the scalar oracle's bits."""
+    from parity import make_weights
+
+    for n, k, m in ((64, 512, 3), (333, 2304, 5), (1000, 4096, 1)):
+        w = make_weights("q4_k", n, k, seed=n)
+        a = np.random.default_rng(k).standard_normal((m, k)).astype(np.float32)
+        assert np.array_equal(oracle.matmul(oracle.Q4_K, w, a).view(np.uint32), oracle.matmul_fast(oracle.Q4_K, w, a).view(np.uint32))
+    # formats without a SIMD arm fall back to the scalar code
+    w = make_weights("q8_0", 32, 256, seed=1)
+    a = np.random.default_rng(2).standard_normal((2, 256)).astype(np.float32)
+    assert np.array_equal(oracle.matmul(oracle.Q8_0, w, a), oracle.matmul_fast(oracle.Q8_0, w, a))
