@@ -23,8 +23,8 @@
 //                 store them with tcgen05.st into the A ring in tensor memory (32 columns per
 //                 stage, next to the accumulator): the dequantised weights never touch shared
 //                 memory, whose bandwidth the token tiles need
-//   warps 10..17  epilogue: read the finished accumulator with tcgen05.ld and store f32 results
-//                 (coalesced along n); two warps per tensor-memory lane quarter, half the columns each
+//   warps 10..13  epilogue: read the finished accumulator with tcgen05.ld and store f32 results
+//                 (coalesced along n)
 // A stage has one "full" barrier (copy-engine bytes + the 256 dequantising threads) and one "empty"
 // barrier (the MMAs' commit), so the issuing thread waits once and commits once per slab.
 // Every mbarrier wait is bounded and also watches a CTA-wide abort flag; a wait that gives up sets
@@ -62,8 +62,8 @@ struct Staged {
     static constexpr int raw_bytes = BM * unit_bytes;
 };
 constexpr int kDequantWarps = 8;
-constexpr int kEpilogueWarps = 8;  // two per tensor-memory lane quarter: each drains half of the accumulator's columns
-constexpr int kThreads = (2 + kDequantWarps + kEpilogueWarps) * 32;  // 576
+constexpr int kEpilogueWarps = 4;  // one per tensor-memory lane quarter (eight, splitting the columns, measured no faster)
+constexpr int kThreads = (2 + kDequantWarps + kEpilogueWarps) * 32;  // 448
 constexpr unsigned kWaitLimit = 1u << 20;
 constexpr int TMEM_COLS = 512;  // columns 0..255: the f32 accumulator; from column 256: the A ring (STAGES x 32)
 constexpr int A_COLS = BK / 2;  // tensor-memory columns of one A slab: two bf16 per 32-bit column
@@ -564,8 +564,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int q = warp & 3;                       // TMEM lane quarter this warp may read
             const int out_row = rt * BM + q * 32 + lane;  // weight row = output column
-            const int chalf = (warp - 2 - kDequantWarps) >> 2;  // which half of the columns this warp drains
-            for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2); c0 += 32) {
+            for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t acc[32];
                 const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
                 asm volatile(
