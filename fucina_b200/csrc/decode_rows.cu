@@ -675,6 +675,96 @@ __device__ __forceinline__ void expert_block_m(int mstep, uint32_t p, const ActV
     expert_block<FMT, 1>(p, V, unit, acc);
 }
 
+// ---- eight activation rows per entry: the block dots go through the warp-level int8 tensor-core
+// instruction (mma.sync m16n8k32, u8 levels x s8 activations -> s32, exact), 16 weight rows x 8 tokens x 32
+// weights at a time, instead of eight rounds of dp4a per row. The lane <-> (row, token) ownership is the
+// instruction's fragment layout, with g = lane / 4 and t = lane % 4:
+//   A (weights)      words of rows g and g + 8, elements 4t..4t+3 and 16+4t..16+4t+3 of the sub-block
+//   B (activations)  token g, the same element columns
+//   D (dots)         rows g and g + 8, tokens 2t and 2t + 1
+// A 32-row tile is two such row groups; acc[4 * group + {0,1}] belongs to row 16*group + g, tokens 2t and
+// 2t + 1, acc[4 * group + {2,3}] to row 16*group + 8 + g. Sub-block scales multiply the integer dots, the
+// min term and the f32 epilogue are those of block_q4_k / block_q5_k, so values are identical to them.
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) { return *reinterpret_cast<const uint32_t*>(__cvta_shared_to_generic(addr)); }
+
+template <int FMT>
+__device__ __forceinline__ void expert_block_mma(uint32_t tile_base, const ActView& V, int kb, int lane, float (&acc)[8]) {
+    constexpr int UB = FMT == FQ_Q4_K ? 144 : 176;
+    constexpr int QS = FMT == FQ_Q4_K ? 16 : 48;  // offset of the nibble payload inside a block
+    const int g = lane >> 2, t = lane & 3;
+    // headers of this lane's four rows: g, g + 8, g + 16, g + 24
+    KHeader H[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) H[i].decode(lds128(tile_base + (uint32_t)(g + 8 * i) * UB));
+    int isc[4][2], imn[4][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) isc[i][0] = isc[i][1] = imn[i][0] = imn[i][1] = 0;
+    uint32_t qh[4][2];  // Q5_K: fifth bits of elements 4t..4t+3 and 16+4t.. of the four rows, all eight sub-blocks
+    if (FMT == FQ_Q5_K) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            qh[i][0] = lds32(tile_base + (uint32_t)(g + 8 * i) * UB + 16 + 4 * t);
+            qh[i][1] = lds32(tile_base + (uint32_t)(g + 8 * i) * UB + 32 + 4 * t);
+        }
+    }
+    const uint32_t arow = V.base + (uint32_t)g * V.row + (uint32_t)kb * 256 + 4 * t;  // token g, this lane's columns
+#pragma unroll
+    for (int pp = 0; pp < 4; ++pp) {
+        // activations of sub-blocks 2pp (low nibbles) and 2pp + 1 (high nibbles)
+        const uint32_t b_lo0 = lds32(arow + pp * 64), b_lo1 = lds32(arow + pp * 64 + 16);
+        const uint32_t b_hi0 = lds32(arow + pp * 64 + 32), b_hi1 = lds32(arow + pp * 64 + 48);
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+            const int ia = 2 * grp, ib = 2 * grp + 1;  // rows 16*grp + g and 16*grp + 8 + g
+            const uint32_t pa = tile_base + (uint32_t)(g + 16 * grp) * UB + QS + pp * 32 + 4 * t;
+            const uint32_t pb = pa + 8 * UB;
+            const uint32_t w[4] = {lds32(pa), lds32(pb), lds32(pa + 16), lds32(pb + 16)};
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                lo[x] = w[x] & 0x0f0f0f0fu;
+                hi[x] = (w[x] >> 4) & 0x0f0f0f0fu;
+            }
+            if (FMT == FQ_Q5_K) {
+                const uint32_t h[4] = {qh[ia][0], qh[ib][0], qh[ia][1], qh[ib][1]};
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    lo[x] |= ((h[x] >> (2 * pp)) & 0x01010101u) << 4;
+                    hi[x] |= ((h[x] >> (2 * pp + 1)) & 0x01010101u) << 4;
+                }
+            }
+            int dlo[4], dhi[4];
+            mma_u8s8(dlo, lo, b_lo0, b_lo1);
+            mma_u8s8(dhi, hi, b_hi0, b_hi1);
+            const int sa_a = byte_of(H[ia].sc[pp >> 1], (pp & 1) * 2), sb_a = byte_of(H[ia].sc[pp >> 1], (pp & 1) * 2 + 1);
+            const int sa_b = byte_of(H[ib].sc[pp >> 1], (pp & 1) * 2), sb_b = byte_of(H[ib].sc[pp >> 1], (pp & 1) * 2 + 1);
+            isc[ia][0] += sa_a * dlo[0] + sb_a * dhi[0];
+            isc[ia][1] += sa_a * dlo[1] + sb_a * dhi[1];
+            isc[ib][0] += sa_b * dlo[2] + sb_b * dhi[2];
+            isc[ib][1] += sa_b * dlo[3] + sb_b * dhi[3];
+        }
+    }
+    // min term and f32 epilogue per (row, token), as in block_q4_k
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const uint32_t rec = V.base + (uint32_t)(2 * t + c) * V.row;
+        const float da = lds_f32(rec + V.off_ad + kb * 4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int mn_term = min_term(H[i], rec + V.off_sums + kb * 32);
+            const int grp = i >> 1, half = i & 1;  // rows g + 8*i = 16*grp + 8*half + g
+            float& a = acc[4 * grp + 2 * half + c];
+            a = __fadd_rn(a, kquant_term(H[i], da, isc[i][c], mn_term));
+        }
+    }
+}
+
 template <int FMT, int MB, bool GATED>
 __global__ void __launch_bounds__(kExpertWarps * 32, 1)
     expert_rows_kernel(const ExpertArgs A, const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap2) {
@@ -755,7 +845,9 @@ __global__ void __launch_bounds__(kExpertWarps * 32, 1)
         // quantise this entry's rows: (row b, block blk) pairs over the warps; the slots up to the row count the
         // block product is instantiated for are zero
         const int nblk = k >> 8;
-        const int mstep = min(MB, expert_rows_step(G.m));
+        // entries of three or more rows in an eight-row launch use the tensor-core block product (CTA-uniform choice)
+        const bool kMma = MB == 8 && G.m > 2;
+        const int mstep = kMma ? MB : min(MB, expert_rows_step(G.m));
         for (int i = warp; i < mstep * nblk; i += kExpertWarps) {
             const int b = i / nblk, blk = i % nblk;
             uint8_t* rec = acts + (size_t)b * NS.row;
@@ -785,11 +877,18 @@ __global__ void __launch_bounds__(kExpertWarps * 32, 1)
                     ok = false;
                     break;
                 }
-                const uint32_t p = slot0 + (uint32_t)stage * 32 * UB + (uint32_t)lane * UB;
-                if (!GATED || (j % NM) == 0)
+                const uint32_t tile_base = slot0 + (uint32_t)stage * 32 * UB;
+                const uint32_t p = tile_base + (uint32_t)lane * UB;
+                if (kMma) {
+                    if (!GATED || (j % NM) == 0)
+                        expert_block_mma<FMT>(tile_base, V, unit, lane, reinterpret_cast<float(&)[8]>(acc[0]));
+                    else
+                        expert_block_mma<FMT>(tile_base, V, unit, lane, reinterpret_cast<float(&)[8]>(acc[NM - 1]));
+                } else if (!GATED || (j % NM) == 0) {
                     expert_block_m<FMT, MB>(mstep, p, V, unit, acc[0]);
-                else
+                } else {
                     expert_block_m<FMT, MB>(mstep, p, V, unit, acc[NM - 1]);
+                }
                 __syncwarp();  // every lane is done with this stage before it is refilled
                 ++consumed;
                 advance();
@@ -813,6 +912,25 @@ __global__ void __launch_bounds__(kExpertWarps * 32, 1)
                         acc[q][b] = sum;
                     }
             }
+        }
+        if (kMma) {
+            // fragment layout: acc[4*grp + 2*half + c] = (row 16*grp + 8*half + lane/4, token 2*(lane%4) + c)
+            if (kpart == 0 && have_tile) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int row = tile * 32 + 16 * (i >> 2) + 8 * ((i >> 1) & 1) + (lane >> 2);
+                    const int b = 2 * (lane & 3) + (i & 1);
+                    if (row >= n || b >= G.m) continue;
+                    float v = acc[0][i < MB ? i : 0];
+                    if (GATED) {
+                        const float gate = v, up = acc[NM - 1][i < MB ? i : 0];
+                        const float sig = 1.0f / (1.0f + expf(-gate));
+                        v = up * (gate * sig);
+                    }
+                    A.out[(size_t)(G.row0 + b) * n + row] = v;
+                }
+            }
+            continue;
         }
         const int row = tile * 32 + lane;
         if (kpart == 0 && have_tile && row < n) {
