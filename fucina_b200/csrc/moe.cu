@@ -242,7 +242,7 @@ __global__ void swiglu_bf16_kernel(const float* __restrict__ gate, const float* 
     }
 }
 
-int g_moe_tensor_mode = -1;  // -1 auto (>= 16 rows per expert on average), 0 never, 1 whenever the format allows
+int g_moe_tensor_mode = -1;  // -1 auto (>= 20 rows per expert on average: the measured crossover of the two arms), 0 never, 1 whenever the format allows
 
 int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
                           int seq, int top_k, const int* selected_dev, const float* weights_dev, Shard shard, float* out_dev,
@@ -312,7 +312,7 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     // prefill-sized batches: bf16 tensor-core products (the reference's own GPU arm multiplies rounded
     // operands too); decode-sized batches keep the CPU kernels' int8 arithmetic
     const bool tc_ok = tensor_path_serves(gate) && tensor_path_serves(down);
-    if (tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 16 * n_expert)))
+    if (tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 20 * n_expert)))
         return moe_layer_tensor_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, shard, out_dev, st);
     const ActSizes Sx = act_sizes(fmt, hidden), Sg = act_sizes(fmt, out_pe);
     // Row tile of the grouped kernel. A router sends a token to distinct experts, so an expert's run is

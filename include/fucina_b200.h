@@ -235,7 +235,7 @@ FQ_API int fq_qmoe_fill_acceptable(size_t rows, size_t n_tiles);
 FQ_API void fq_set_min_work_qmoe_for_test(uint64_t v);
 FQ_API void fq_set_decode_for_test(int enabled);
 /* Arm selection of the fused MoE layer, in the spirit of setQuantMmaForTest (backend/cuda.zig:2563):
- * -1 automatic (tensor cores once a batch averages >= 16 rows per expert, else the int8 decode
+ * -1 automatic (tensor cores once a batch averages >= 20 rows per expert, else the int8 decode
  * arm), 0 always the int8 arm, 1 the tensor-core arm whenever the format has one. */
 FQ_API void fq_set_moe_tensor_for_test(int mode);
 
