@@ -216,6 +216,8 @@ def _moe_case(fmt_name, hidden, out_pe, n_expert, top_k, seq, seed):
     ("q5_k", 512, 768, 16, 4, 1),     # decode
     ("q5_k", 512, 768, 16, 4, 40),    # experts with more rows than one pass
     ("q4_k", 256, 512, 8, 2, 9),
+    ("q4_k", 2048, 768, 8, 4, 12),    # Qwen3-MoE expert shape: runs of 3-8 rows take the tensor-core block product
+    ("q5_k", 2048, 768, 32, 8, 2),    # two tokens, K split across the warps of an item
     ("q8_0", 256, 128, 8, 3, 5),
 ])
 def test_moe_layer_matches_oracle(P, fmt_name, hidden, out_pe, n_expert, top_k, seq):
