@@ -81,6 +81,7 @@ SIGNATURES = {
     "fq_set_min_work_qmoe_for_test": (None, [c_u64]),
     "fq_set_decode_for_test": (None, [c_int]),
     "fq_set_moe_tensor_for_test": (None, [c_int]),
+    "fq_selftest_bounded_wait": (c_int, [C.c_uint]),
     "fq_trace_enabled": (c_int, []),
     "fq_trace_reset": (None, []),
     "fq_trace_dump": (None, []),

@@ -996,7 +996,26 @@ bool make_stack_tmap(const DevWeights& w, int unit_bytes, CUtensorMap* out) {
               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Self-test of the bounded-wait mechanism every pipeline in this file relies on: one warp waits, with the
+// given iteration limit, on an mbarrier that nothing ever completes, records FQ_ERR_TIMEOUT in the status
+// word exactly as the kernels above do, and returns normally. No copy is in flight and nothing else is touched.
+__global__ void bounded_wait_probe_kernel(int* status, unsigned limit) {
+    __shared__ __align__(8) uint64_t bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+    bool done = false;
+    for (unsigned i = 0; i < limit && !done; ++i) done = mbar_try_wait(b, 0);
+    if (!done && threadIdx.x == 0) *(volatile int*)status = FQ_ERR_TIMEOUT;
+}
+
 }  // namespace
+
+cudaError_t launch_bounded_wait_probe(int* status, unsigned limit, cudaStream_t st) {
+    bounded_wait_probe_kernel<<<1, 32, 0, st>>>(status, limit);
+    return cudaGetLastError();
+}
 
 bool decode_rows_eligible(const DevWeights& w, size_t m) {
     if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q8_0) return false;

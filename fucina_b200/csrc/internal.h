@@ -88,6 +88,8 @@ struct ExpertArgs {
     int stages;
     int* status;
 };
+// one warp runs a bounded wait on a barrier nothing completes and reports through the status word
+cudaError_t launch_bounded_wait_probe(int* status, unsigned limit, cudaStream_t st);
 int expert_rows_max_group();
 bool expert_rows_eligible(const DevWeights& w, const DevWeights* w2, int group_rows);
 cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const float* src, const int* src_index, int top_k, float* out,

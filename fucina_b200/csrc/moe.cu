@@ -500,7 +500,7 @@ int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights*
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
         g_trace.d2h_bytes += xb;
         if (e != cudaSuccess) rc = cuda_fail(e, "MoE download");
-        else memcpy(out, pin + o_out, xb);
+        else if ((rc = device_status(ctx)) == FQ_OK) memcpy(out, pin + o_out, xb);
     }
     cudaStreamSynchronize(ctx->stream);
     dev_free(dev);

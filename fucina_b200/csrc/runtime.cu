@@ -636,6 +636,7 @@ static int gemm_host(int fmt, const void* rhs, size_t rhs_len, int cacheable, si
     } else if (submitted) {
         cudaStreamSynchronize(ctx->stream);
     }
+    if (rc == FQ_OK) rc = device_status(ctx);  // a bounded device-side wait that gave up invalidates the result
     if (direct_out) pin_free(c_pin);
     else dev_free(c_dev);
     dev_free(in.dev);
@@ -691,6 +692,17 @@ int fq_last_error(char* buf, size_t len) {
     return (int)g_last_error.size();
 }
 void* fq_stream(void) { return context() ? (void*)g_ctx.stream : nullptr; }
+// Test seam: exercise the device-side time-out path. A warp waits `limit` polls (at most 2^20) on a barrier
+// that is never completed, gives up and records FQ_ERR_TIMEOUT; the next fq_synchronize (or blocking entry)
+// returns it, and the context stays usable. No counterpart in the reference.
+int fq_selftest_bounded_wait(unsigned limit) {
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    if (limit == 0 || limit > (1u << 20)) return fail(FQ_DECLINED_ARGS, "limit must be in 1..2^20");
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    cudaError_t e = launch_bounded_wait_probe(ctx->status_dev, limit, ctx->stream);
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "bounded-wait probe launch");
+}
 int fq_synchronize(void) {
     Ctx* ctx = context();
     if (!ctx) return FQ_DECLINED_NO_GPU;
@@ -954,6 +966,10 @@ int fq_work_finish(fq_work* w, int copy_to_host) {
         w->state = 1;
     } else {
         w->state = 2;
+    }
+    if (int st = device_status(ctx)) {  // a bounded device-side wait gave up somewhere before this point
+        w->state = -1;
+        return st;
     }
     return FQ_OK;
 }

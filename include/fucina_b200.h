@@ -238,6 +238,11 @@ FQ_API void fq_set_decode_for_test(int enabled);
  * -1 automatic (tensor cores once a batch averages >= 20 rows per expert, else the int8 decode
  * arm), 0 always the int8 arm, 1 the tensor-core arm whenever the format has one. */
 FQ_API void fq_set_moe_tensor_for_test(int mode);
+/* Failure-detection seam (no counterpart in the reference): every device-side wait in this library is
+ * bounded and reports FQ_ERR_TIMEOUT through a status word instead of hanging. This launches one warp that
+ * polls `limit` times (1..2^20) a barrier nothing completes, gives up the same way and returns normally; the
+ * next fq_synchronize or blocking entry then returns FQ_ERR_TIMEOUT once, and the context stays usable. */
+FQ_API int fq_selftest_bounded_wait(unsigned limit);
 
 /* ---- trace counters (backend/cuda.zig:191-317) ---- */
 FQ_API int fq_trace_enabled(void);

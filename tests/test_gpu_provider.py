@@ -336,3 +336,21 @@ def test_router_topk_matches_oracle(P, torch):
         np.testing.assert_allclose(wd.cpu().numpy(), w, rtol=2e-6, atol=0)
     assert list(sel[1]) == list(range(8))
     assert sel[0, 0] == 5 and sel[0, 1] == 9
+
+
+def test_bounded_device_wait_reports_timeout_and_context_survives(P):
+    """Failure detection without a fault: a device-side wait that can never succeed gives up after its
+    limit, the host reads FQ_ERR_TIMEOUT (-2) at the next synchronisation, and later work runs normally."""
+    from fucina_b200._lib import load
+
+    lib = load()
+    P.synchronize()                              # nothing pending from earlier tests
+    assert lib.fq_selftest_bounded_wait(0) == 1  # declined: limit out of range
+    assert lib.fq_selftest_bounded_wait(20000) == 0
+    assert lib.fq_synchronize() == -2            # the wait ran out and said so
+    assert lib.fq_synchronize() == 0             # reported once, then cleared
+    n, k = 64, 512
+    blocks = make_weights("q4_k", n, k, seed=90)
+    a = acts(2, k, 91)
+    got = P.gemm_quant_nt(oracle.Q4_K, blocks, a, n, cacheable=False)
+    assert_close(got, oracle.matmul(oracle.Q4_K, blocks, a), TOL_INT8, "after a reported time-out")
