@@ -482,6 +482,19 @@ def run_extra(args) -> list[dict]:
         nbytes = n * (k // 32 * 34) + 4 * k + 4 * n
         out.append({"workload": "Q8_0 GEMV 4096x4096 batch 1 (30 rotated copies)", "us_per_launch": round(ms * 1e3, 3),
                     "GBps": round(nbytes / ms / 1e6, 1), "frac_of_measured_hbm": round(nbytes / ms / 1e6 / peak_hbm, 4)})
+        del copies, cap
+        # the lm_head-sized product, where launch and ramp no longer dominate: 139 MB per launch
+        n = 32000
+        copies = [_dev_weights(P, torch, F.Q8_0, n, k, 1100 + i) for i in range(4)]  # 557 MB > 4x L2
+        y = torch.empty((1, n), device="cuda")
+        torch.cuda.synchronize()
+        with P.capture() as cap:
+            for w in copies:
+                P.gemm_quant_nt_dev(w, x, y, 1, mode=P.MODE_INT8)
+        ms = _timed(P, torch, cap.graph.launch, max(args.steps // 10, 5), 3) / len(copies)
+        nbytes = n * (k // 32 * 34) + 4 * k + 4 * n
+        out.append({"workload": "Q8_0 GEMV 32000x4096 batch 1 (4 rotated copies)", "us_per_launch": round(ms * 1e3, 3),
+                    "GBps": round(nbytes / ms / 1e6, 1), "frac_of_measured_hbm": round(nbytes / ms / 1e6 / peak_hbm, 4)})
     if args.workload in ("prefill", "all"):
         n, k = 14336, 4096
         w = _dev_weights(P, torch, F.Q4_K, n, k, 1200)

@@ -287,6 +287,36 @@ __device__ __forceinline__ void unit_q8_0(uint32_t p, uint32_t ps, const ActView
     }
 }
 
+// The same unit when it was staged by tensor copies (RowsArgs.use_tmap == 2): per warp step the 32 rows x 256
+// payload bytes arrive as two boxes of 32 x 128 bytes with the 128-byte swizzle (16-byte chunk c of row r sits
+// at chunk c ^ (r % 8), so a quarter warp's 128-bit loads fall on distinct banks although rows are 128 bytes
+// apart), followed by the 32 x 16 scale bytes. `base` is the 1024-byte aligned start of the stage.
+constexpr int kQ8StageBytes = 9216;  // 2 x 4096 payload + 512 scales, padded to a multiple of 1024
+template <int MB>
+__device__ __forceinline__ void unit_q8_0_swz(uint32_t base, int lane, const ActView& V, int kb, float (&acc)[MB]) {
+    const uint4 su = lds128(base + 8192 + lane * 16);
+    const uint32_t sw[4] = {su.x, su.y, su.z, su.w};
+    const uint32_t x = (uint32_t)(lane & 7);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t rowp = base + (uint32_t)(j >> 2) * 4096 + (uint32_t)lane * 128;
+        const uint32_t c0 = (uint32_t)(j & 3) * 2;
+        const uint4 w0 = lds128(rowp + ((c0 ^ x) << 4)), w1 = lds128(rowp + (((c0 + 1) ^ x) << 4));
+        const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const float dw = __half2float(__ushort_as_half((unsigned short)((sw[j >> 1] >> ((j & 1) * 16)) & 0xffffu)));
+#pragma unroll
+        for (int b = 0; b < MB; ++b) {
+            const uint32_t rec = V.base + b * V.row;
+            const uint32_t a = rec + kb * 256 + j * 32;
+            const uint4 a0 = lds128(a), a1 = lds128(a + 16);
+            int dot = dot16_ss(w, a0, 0);
+            dot = dot16_ss(w + 4, a1, dot);
+            const float da = lds_f32(rec + V.off_ad + (kb * 8 + j) * 4);
+            acc[b] = __fadd_rn(acc[b], __fmul_rn((float)dot, __fmul_rn(da, dw)));
+        }
+    }
+}
+
 // Geometry of one slab (what a lane fetches per pipeline step).
 struct SlabGeom {
     int unit_bytes;    // payload bytes per 256 weights
@@ -306,7 +336,7 @@ __host__ __device__ inline SlabGeom slab_geom(int fmt, int slab) {
 }
 
 template <int FMT, int MB, bool FUSED, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_kernel(const RowsArgs A, const __grid_constant__ CUtensorMap tmap) {
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_kernel(const RowsArgs A, const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap2) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int kWarps = WARPS, kThreads = WARPS * 32;  // the warps split K; 16 when a row has at least 16 units
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -323,7 +353,11 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
     uint8_t* acts = smem + 512;
     float* red = reinterpret_cast<float*>(acts + ((MB * NS.row + 127) & ~(size_t)127));
     uint8_t* slots = reinterpret_cast<uint8_t*>(red) + 2 * kWarps * MB * 32 * sizeof(float);
-    const uint32_t slot0 = smem_u32(slots) + (uint32_t)((warp * A.stages) * 32 + lane) * G.slot_bytes;
+    // bytes between the stages of a warp; Q8_0 staged by tensor copies uses whole 1024-byte aligned stages
+    const bool q8_boxes = FMT == FQ_Q8_0 && A.use_tmap == 2;
+    const uint32_t stage_stride = q8_boxes ? (uint32_t)kQ8StageBytes : (uint32_t)(32 * G.slot_bytes);
+    const uint32_t slot0 = q8_boxes ? ((smem_u32(slots) + 1023u) & ~1023u) + (uint32_t)(warp * A.stages) * kQ8StageBytes
+                                    : smem_u32(slots) + (uint32_t)((warp * A.stages) * 32 + lane) * G.slot_bytes;
     const uint32_t bar0 = smem_u32(bars) + warp * kMaxStages * 8;
 
     stamp(0);
@@ -374,6 +408,26 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
                     bulk_load_stream(slot0 + (uint32_t)stage * 32 * G.slot_bytes, src, bytes, bar, l2_policy);
                 else
                     bulk_load(slot0 + (uint32_t)stage * 32 * G.slot_bytes, src, bytes, bar);
+            }
+            return;
+        }
+        if (q8_boxes) {
+            // Q8_0 split rows: two swizzled payload boxes (32 rows x 128 bytes) and the 32 x 16 scale bytes
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar, (uint32_t)(32 * 272));
+                const uint32_t dst = slot0 + (uint32_t)stage * stage_stride;
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                    "l"(&tmap), "r"(sl * 256), "r"(row0), "r"(bar)
+                    : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst + 4096),
+                    "l"(&tmap), "r"(sl * 256 + 128), "r"(row0), "r"(bar)
+                    : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst + 8192),
+                    "l"(&tmap2), "r"(sl * 16), "r"(row0), "r"(bar)
+                    : "memory");
             }
             return;
         }
@@ -469,12 +523,15 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
             }
             if (it == 0) stamp(4);
             const int nu = min(A.slab, units - sl * A.slab);
-            const uint32_t p = slot0 + (uint32_t)stage * 32 * G.slot_bytes;
+            const uint32_t p = slot0 + (uint32_t)stage * stage_stride;
             for (int u = 0; u < nu && !A.skip_compute; ++u) {
                 const int kb = sl * A.slab + u;
                 if (FMT == FQ_Q4_K) block_q4_k<MB>(p + u * 144, V, kb, acc);
                 if (FMT == FQ_Q5_K) block_q5_k<MB>(p + u * 176, V, kb, acc);
-                if (FMT == FQ_Q8_0) unit_q8_0<MB>(p + u * 256, p + G.scale_off + u * 16, V, kb, acc);
+                if (FMT == FQ_Q8_0) {
+                    if (q8_boxes) unit_q8_0_swz<MB>(p, lane, V, kb, acc);
+                    else unit_q8_0<MB>(p + u * 256, p + G.scale_off + u * 16, V, kb, acc);
+                }
             }
             __syncwarp();  // every lane is done with this stage before it is refilled
             if (it + A.stages < total) issue(it + A.stages);
@@ -596,11 +653,36 @@ bool make_weight_tmap(const DevWeights& w, int mat, int unit_bytes, CUtensorMap*
               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Q8_0 split rows [K payload bytes][K/16 scale bytes]: a payload map (box 128 bytes x 32 rows, 128-byte swizzle)
+// and a scale map over the second plane (box 16 bytes x 32 rows).
+bool make_q8_tmaps(const DevWeights& w, int mat, CUtensorMap* payload, CUtensorMap* scales) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    uint8_t* base = const_cast<uint8_t*>(w.base) + (size_t)mat * w.mat_stride;
+    if (((uintptr_t)base & 15) || (w.row_stride & 15)) return false;
+    const cuuint32_t estr[2] = {1, 1};
+    const cuuint64_t strides[1] = {(cuuint64_t)w.row_stride};
+    const cuuint64_t pdims[2] = {(cuuint64_t)w.k, (cuuint64_t)w.n};
+    const cuuint32_t pbox[2] = {128, 32};
+    if (fn(payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, pdims, strides, pbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    const cuuint64_t sdims[2] = {(cuuint64_t)w.k / 16, (cuuint64_t)w.n};
+    const cuuint32_t sbox[2] = {16, 32};
+    return fn(scales, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base + w.k, sdims, strides, sbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+size_t smem_bytes_q8_boxes(int k, int mb, int stages) {
+    const NatSizes NS = nat_sizes(false, (size_t)k);
+    return 512 + ((mb * NS.row + 127) & ~(size_t)127) + (size_t)2 * 8 * mb * 32 * sizeof(float) + 1024 + (size_t)8 * stages * kQ8StageBytes;
+}
+
 template <int FMT, int MB>
-cudaError_t launch_fmt_mb(const RowsArgs& a, const CUtensorMap& tmap, bool fused, bool half, int grid, size_t smem, cudaStream_t st) {
+cudaError_t launch_fmt_mb(const RowsArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap2, bool fused, bool half, int grid, size_t smem,
+                          cudaStream_t st) {
     constexpr bool kWide = MB <= 2;  // the 16-warp form exists for the small-batch variants only
     const bool wide = kWide && !half && pick_warps(FMT, a.w.k, MB) == 16;
-    void (*kern)(const RowsArgs, const CUtensorMap) =
+    void (*kern)(const RowsArgs, const CUtensorMap, const CUtensorMap) =
         wide ? (fused ? decode_rows_kernel<FMT, MB, true, kWide ? 16 : 8> : decode_rows_kernel<FMT, MB, false, kWide ? 16 : 8>)
              : (fused ? decode_rows_kernel<FMT, MB, true, 8> : decode_rows_kernel<FMT, MB, false, 8>);
     // opt in to the large dynamic shared memory once per instantiation, not per launch
@@ -627,16 +709,17 @@ cudaError_t launch_fmt_mb(const RowsArgs& a, const CUtensorMap& tmap, bool fused
     static const bool no_pdl = getenv("FUCINA_B200_NO_PDL") != nullptr;
     cfg.attrs = attr;
     cfg.numAttrs = no_pdl ? 0 : 1;
-    return cudaLaunchKernelEx(&cfg, kern, a, tmap);
+    return cudaLaunchKernelEx(&cfg, kern, a, tmap, tmap2);
 }
 
 template <int FMT>
-cudaError_t launch_fmt(const RowsArgs& a, const CUtensorMap& tmap, int mb, bool fused, bool half, int grid, size_t smem, cudaStream_t st) {
+cudaError_t launch_fmt(const RowsArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap2, int mb, bool fused, bool half, int grid, size_t smem,
+                       cudaStream_t st) {
     switch (mb) {
-        case 1: return launch_fmt_mb<FMT, 1>(a, tmap, fused, half, grid, smem, st);
-        case 2: return launch_fmt_mb<FMT, 2>(a, tmap, fused, half, grid, smem, st);
-        case 4: return launch_fmt_mb<FMT, 4>(a, tmap, fused, half, grid, smem, st);
-        default: return launch_fmt_mb<FMT, 8>(a, tmap, fused, half, grid, smem, st);
+        case 1: return launch_fmt_mb<FMT, 1>(a, tmap, tmap2, fused, half, grid, smem, st);
+        case 2: return launch_fmt_mb<FMT, 2>(a, tmap, tmap2, fused, half, grid, smem, st);
+        case 4: return launch_fmt_mb<FMT, 4>(a, tmap, tmap2, fused, half, grid, smem, st);
+        default: return launch_fmt_mb<FMT, 8>(a, tmap, tmap2, fused, half, grid, smem, st);
     }
 }
 
@@ -1048,6 +1131,19 @@ cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev,
         if (!forced && a.stages > 2) a.stages = 2;
     }
     if (!w.tile_rows && w.fmt != FQ_Q8_0 && a.slab == 1 && !no_tmap && make_weight_tmap(w, mat, slab_geom(w.fmt, 1).unit_bytes, &tmap)) a.use_tmap = 1;
+    // Q8_0 rows are a payload plane and a scale plane: three tensor copies per warp step (two swizzled payload
+    // boxes, one scale box) instead of 64 per-lane bulk copies
+    CUtensorMap tmap2;
+    memset(&tmap2, 0, sizeof tmap2);
+    size_t smem_q8 = 0;
+    if (w.fmt == FQ_Q8_0 && !no_tmap && w.k % 256 == 0 && make_q8_tmaps(w, mat, &tmap, &tmap2)) {
+        smem_q8 = smem_bytes_q8_boxes(w.k, mb, 2);
+        if (smem_q8 <= kSmemLimit) {
+            a.use_tmap = 2;
+            a.slab = 1;
+            a.stages = 2;
+        }
+    }
     const bool fused = m <= kFusedMaxRows;
     if (!fused) {
         cudaError_t e = launch_quantize_acts_natural(a_dev, m, w.k, w.fmt != FQ_Q8_0, scratch, st);
@@ -1062,11 +1158,11 @@ cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev,
         grid = (w.n + 31) / 32;
         a.rows_per_cta = 32;
     }
-    const size_t smem = smem_bytes(w.fmt, w.k, mb, a.slab, a.stages, half ? 8 : pick_warps(w.fmt, w.k, mb));
+    const size_t smem = a.use_tmap == 2 ? smem_q8 : smem_bytes(w.fmt, w.k, mb, a.slab, a.stages, half ? 8 : pick_warps(w.fmt, w.k, mb));
     switch (w.fmt) {
-        case FQ_Q4_K: return launch_fmt<FQ_Q4_K>(a, tmap, mb, fused, half, grid, smem, st);
-        case FQ_Q5_K: return launch_fmt<FQ_Q5_K>(a, tmap, mb, fused, half, grid, smem, st);
-        default: return launch_fmt<FQ_Q8_0>(a, tmap, mb, fused, half, grid, smem, st);
+        case FQ_Q4_K: return launch_fmt<FQ_Q4_K>(a, tmap, tmap2, mb, fused, half, grid, smem, st);
+        case FQ_Q5_K: return launch_fmt<FQ_Q5_K>(a, tmap, tmap2, mb, fused, half, grid, smem, st);
+        default: return launch_fmt<FQ_Q8_0>(a, tmap, tmap2, mb, fused, half, grid, smem, st);
     }
 }
 
