@@ -16,7 +16,8 @@
 // completes on one mbarrier, by the cheapest copy the layout allows:
 //   tile-major K-quants   one bulk copy of the contiguous 32 x 144/176 bytes
 //   row-major K-quants    one 2-D tensor copy (32 rows x one unit)
-//   split rows (Q8_0)     one bulk copy per lane (payload + scales)
+//   split rows (Q8_0)     three tensor copies: two 32 x 128-byte payload boxes (128-byte swizzle) and
+//                         the 32 x 16 scale bytes (per-lane bulk copies when no tensor map can be made)
 // Slots are an odd number of 16-byte units wide so the 128-bit shared loads
 // of a quarter warp hit 32 distinct banks. Copies for the next slabs (also of
 // the next tile) are in flight while a slab is consumed, which keeps ~144 KB
