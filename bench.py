@@ -560,6 +560,10 @@ def run_extra(args) -> list[dict]:
             nbytes = n * (k // 256 * 66) + 4 * m * (k + n)
             out.append({"workload": f"TQ2_0 (PTQTP plane) {m}x{n}x{k}, int8 path (weights fit L2: warm-L2 figure)", "ms": round(ms, 4),
                         "GBps": round(nbytes / ms / 1e6, 1), "TFLOPS": round(2.0 * m * n * k / ms / 1e9, 2)})
+            if m > 16:  # the automatic mode: bf16 tensor cores for prefill-sized batches
+                ms = _timed(P, torch, lambda: P.gemm_quant_nt_dev(w, a, c, m, mode=P.MODE_AUTO), max(args.steps // 10, 5), 3)
+                out.append({"workload": f"TQ2_0 (PTQTP plane) {m}x{n}x{k}, tcgen05 path (bf16 operands)", "ms": round(ms, 4),
+                            "TFLOPS": round(2.0 * m * n * k / ms / 1e9, 2)})
     return out
 
 

@@ -351,6 +351,35 @@ struct Raw<FQ_Q8_0> {
     }
 };
 
+template <>
+struct Raw<FQ_TQ2_0> {
+    uint4 q0, q1;
+    float d;
+    int shift;
+    // row = [crumbs: K/4 bytes][d: K/256 f16]. Byte hg*32 + m of a 64-byte block holds elements
+    // hg*128 + n*32 + m in crumb n (dtype.zig:215-218), so the 32 weights of one (slab, half) are crumb
+    // n of 32 consecutive bytes.
+    __device__ __forceinline__ void load(const DevWeights& w, const uint8_t* unit0, size_t, int ks, int h) {
+        const int blk = ks >> 2, sub = (ks & 3) * 2 + h;  // eight 32-weight groups per block
+        const uint8_t* p = unit0 + (size_t)blk * 64 + (sub >> 2) * 32;
+        q0 = __ldg(reinterpret_cast<const uint4*>(p));
+        q1 = __ldg(reinterpret_cast<const uint4*>(p + 16));
+        d = h2f(__ldg(reinterpret_cast<const uint16_t*>(unit0 + (w.k >> 2)) + blk));
+        shift = 2 * (sub & 3);
+    }
+    __device__ __forceinline__ void load_header(uint32_t) {}
+    __device__ __forceinline__ void load_slab(uint32_t, int) {}
+    // d * (code - 1), exactly (ternary.zig:850-876): d * (128 + code) - 129 * d in one fused multiply-add
+    __device__ __forceinline__ void expand(int, int, uint32_t out[16]) const {
+        const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const float2 a2 = make_float2(d, d);
+        const float cc = __fmul_rn(d, -129.0f);
+        const float2 c2 = make_float2(cc, cc);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) expand_bytes<false>((wq[j] >> shift) & 0x03030303u, a2, c2, out[2 * j], out[2 * j + 1]);
+    }
+};
+
 template <int FMT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, const __grid_constant__ CUtensorMap tmap_tokens,
                                                               const __grid_constant__ CUtensorMap tmap_weights) {
@@ -650,7 +679,7 @@ extern "C" __attribute__((visibility("default"))) int fq_debug_tc_timeline(unsig
 }  // namespace
 
 bool tensor_path_serves(const DevWeights& w) {
-    return (w.fmt == FQ_Q4_K || w.fmt == FQ_Q5_K || w.fmt == FQ_Q8_0) && w.k % 256 == 0 && encode_fn() != nullptr;
+    return (w.fmt == FQ_Q4_K || w.fmt == FQ_Q5_K || w.fmt == FQ_Q8_0 || w.fmt == FQ_TQ2_0) && w.k % 256 == 0 && encode_fn() != nullptr;
 }
 
 // Launch over bf16 activation rows [rows][k]: dense tiles of matrix `mat` (table == nullptr) or a
@@ -692,6 +721,7 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
     switch (w.fmt) {
         case FQ_Q4_K: e = launch_tc<FQ_Q4_K>(a, tmap, tmap_w, grid, st); break;
         case FQ_Q5_K: e = launch_tc<FQ_Q5_K>(a, tmap, tmap_w, grid, st); break;
+        case FQ_TQ2_0: e = launch_tc<FQ_TQ2_0>(a, tmap, tmap_w, grid, st); break;
         default: e = launch_tc<FQ_Q8_0>(a, tmap, tmap_w, grid, st); break;
     }
     g_trace.launches++;
@@ -700,8 +730,25 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
 
 int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, size_t rows, float* c_dev, size_t ldc,
                             const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st) {
-    if (!tensor_path_serves(w)) return fail(FQ_DECLINED_ARGS, "tensor-core path serves Q4_K, Q5_K and Q8_0 with k %% 256 == 0");
+    if (!tensor_path_serves(w)) return fail(FQ_DECLINED_ARGS, "tensor-core path serves Q4_K, Q5_K, Q8_0 and TQ2_0 with k %% 256 == 0");
     return launch_tc_rows(ctx, w, 0, (const __nv_bfloat16*)a_bf16, rows, c_dev, ldc, table, n_tiles_dev, max_tiles, st);
+}
+
+__global__ void add_f32_kernel(float* __restrict__ c, const float* __restrict__ t, size_t n) {
+    for (size_t i = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
+        float4 a = *reinterpret_cast<const float4*>(c + i);
+        const float4 b = *reinterpret_cast<const float4*>(t + i);
+        a.x = __fadd_rn(a.x, b.x), a.y = __fadd_rn(a.y, b.y), a.z = __fadd_rn(a.z, b.z), a.w = __fadd_rn(a.w, b.w);
+        *reinterpret_cast<float4*>(c + i) = a;
+    }
+}
+// c += t over n floats (n % 4 == 0, both 16-byte aligned): the plane sum of a multi-plane ternary product
+cudaError_t launch_add_f32(float* c, const float* t, size_t n, cudaStream_t st) {
+    int blocks = (int)((n / 4 + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks < 1) blocks = 1;
+    add_f32_kernel<<<blocks, 256, 0, st>>>(c, t, n);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_f32_to_bf16(const float* src, void* dst, size_t n, cudaStream_t st) {
@@ -713,7 +760,8 @@ cudaError_t launch_f32_to_bf16(const float* src, void* dst, size_t n, cudaStream
 }
 
 int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, cudaStream_t st) {
-    if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q8_0) return fail(FQ_DECLINED_ARGS, "tensor-core path serves Q4_K, Q5_K and Q8_0");
+    if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q8_0 && w.fmt != FQ_TQ2_0)
+        return fail(FQ_DECLINED_ARGS, "tensor-core path serves Q4_K, Q5_K, Q8_0 and TQ2_0");
     if (w.k % 256 != 0 || m < 1 || m > (size_t)1 << 24) return fail(FQ_DECLINED_ARGS, "tensor-core path needs k %% 256 == 0");
     // bf16 copy of the activations: [m][k], read by TMA with a 128-byte swizzle
     __nv_bfloat16* abf = (__nv_bfloat16*)dev_alloc(m * (size_t)w.k * 2);

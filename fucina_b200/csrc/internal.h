@@ -107,6 +107,7 @@ cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev,
 struct TcTile {
     int mat, rt, tok0, ntok;
 };
+cudaError_t launch_add_f32(float* c, const float* t, size_t n, cudaStream_t st);
 cudaError_t launch_f32_to_bf16(const float* src, void* dst, size_t n, cudaStream_t st);
 
 }  // namespace fq

@@ -1010,8 +1010,28 @@ int fq_gemm_ptqtp_dev(const fq_weights* const* planes, int n_planes, const float
     std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
     g_trace.calls++;
     cudaStream_t st = stream ? (cudaStream_t)stream : ctx->stream;
+    const size_t n = (size_t)planes[0]->dw.n;
+    if (m > gemv_max_rows() && tensor_path_serves(planes[0]->dw) && (m * n) % 4 == 0) {
+        // prefill-sized: each plane is a tensor-core product, summed per element in plane order (weights.zig:286-300)
+        float* tmp = n_planes > 1 ? (float*)dev_alloc(m * n * sizeof(float)) : nullptr;
+        if (n_planes > 1 && !tmp) return fail(FQ_DECLINED_BUDGET, "plane scratch allocation failed");
+        int rc = FQ_OK;
+        for (int p = 0; p < n_planes && rc == FQ_OK; ++p) {
+            rc = gemm_tensor_dev(ctx, planes[p]->dw, 0, a_dev, p ? tmp : c_dev, m, n, st);
+            if (rc == FQ_OK && p) {
+                cudaError_t e = launch_add_f32(c_dev, tmp, m * n, st);
+                g_trace.launches++;
+                if (e != cudaSuccess) rc = cuda_fail(e, "plane sum launch");
+            }
+        }
+        if (tmp) {
+            if (st != ctx->stream) cudaStreamSynchronize(st);
+            dev_free(tmp);
+        }
+        return rc;
+    }
     for (int p = 0; p < n_planes; ++p) {
-        int rc = gemm_dev(ctx, planes[p]->dw, 0, a_dev, c_dev, m, (size_t)planes[0]->dw.n, FQ_MODE_INT8, p > 0, st);
+        int rc = gemm_dev(ctx, planes[p]->dw, 0, a_dev, c_dev, m, n, FQ_MODE_INT8, p > 0, st);
         if (rc != FQ_OK) return rc;
     }
     return FQ_OK;

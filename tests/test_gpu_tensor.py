@@ -38,7 +38,7 @@ def run_tensor(P, torch, fmt, blocks, a, n, mode=None):
     return cd.cpu().numpy()
 
 
-@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q8_0"])
+@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q8_0", "tq2_0"])
 @pytest.mark.parametrize("m,n,k", [
     (64, 128, 256),      # one tile, one block of K
     (33, 96, 512),       # the reference's ragged parity shape (cuda.zig:3084-3088): partial rows and tokens
@@ -109,10 +109,34 @@ def test_moe_tensor_arm_matches_bf16_oracle(P, fmt_name, hidden, out_pe, n_exper
 
 def test_formats_without_a_tensor_kernel_are_declined_in_tensor_mode(P, torch):
     n, k, m = 64, 512, 32
-    blocks = make_weights("tq2_0", n, k, seed=2300)
+    blocks = make_weights("tq2_0_folded", n, k, seed=2300)
     a = np.zeros((m, k), np.float32)
     with pytest.raises(P.Declined):
-        run_tensor(P, torch, oracle.TQ2_0, blocks, a, n)
+        run_tensor(P, torch, oracle.TQ2_0_FOLDED, blocks, a, n)
     # AUTO falls back to the integer kernel in 16-row passes
-    got = run_tensor(P, torch, oracle.TQ2_0, blocks, a + 1.0, n, mode=P.MODE_AUTO)
-    assert_close(got, oracle.matmul(oracle.TQ2_0, blocks, a + 1.0), 1e-3, "tq2_0 auto")
+    got = run_tensor(P, torch, oracle.TQ2_0_FOLDED, blocks, a + 1.0, n, mode=P.MODE_AUTO)
+    assert_close(got, oracle.matmul(oracle.TQ2_0_FOLDED, blocks, a + 1.0), 1e-3, "folded auto")
+
+
+@pytest.mark.parametrize("planes", [1, 2])
+def test_ptqtp_planes_on_the_tensor_cores(P, torch, planes):
+    """A prefill-sized multi-plane ternary product: every plane is a tensor-core product over bf16-rounded
+    operands, the planes are added per element in plane order (src/weights.zig:286-300)."""
+    n, k, m = 192, 1024, 100
+    rng = np.random.default_rng(2500 + planes)
+    ps = []
+    for p in range(planes):
+        trits = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+        scales = np.abs(rng.standard_normal((n, k // 256)) * 0.02 / (3 ** p)).astype(np.float32)
+        ps.append(oracle.pack_ptqtp_plane(trits, scales))
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    ws = [P.Weights.upload(oracle.TQ2_0, b, n, k) for b in ps]
+    ad = torch.from_numpy(a).cuda()
+    cd = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    P.gemm_ptqtp_dev(ws, ad, cd, m)
+    P.synchronize()
+    want = sum(oracle.matmul_dequant_f64(oracle.TQ2_0, b, a, round_bf16=True) for b in ps)
+    assert_close(cd.cpu().numpy(), want, TOL_TENSOR, f"ptqtp tensor K={planes}")
+    for w in ws:
+        w.free()
