@@ -380,6 +380,68 @@ struct Raw<FQ_TQ2_0> {
     }
 };
 
+template <>
+struct Raw<FQ_TQ2_0_FOLDED> {
+    uint4 q;
+    float d;
+    // row = [nibbles: K/2 bytes][d: K/256 f16]. Sub-block s of a block is 16 bytes: low nibbles = its elements
+    // 0..15, high nibbles = elements 16..31; value d * (cu - 4) (types.zig:177-180, ternary.zig:850-876).
+    __device__ __forceinline__ void load(const DevWeights& w, const uint8_t* unit0, size_t, int ks, int h) {
+        const int blk = ks >> 2, sub = (ks & 3) * 2 + h;
+        q = __ldg(reinterpret_cast<const uint4*>(unit0 + (size_t)blk * 128 + sub * 16));
+        d = h2f(__ldg(reinterpret_cast<const uint16_t*>(unit0 + (w.k >> 1)) + blk));
+    }
+    __device__ __forceinline__ void load_header(uint32_t) {}
+    __device__ __forceinline__ void load_slab(uint32_t, int) {}
+    __device__ __forceinline__ void expand(int, int, uint32_t out[16]) const {
+        const uint32_t wq[4] = {q.x, q.y, q.z, q.w};
+        const float2 a2 = make_float2(d, d);
+        const float cc = __fmul_rn(d, -132.0f);  // d * (128 + cu) - 132 * d = d * (cu - 4), exact
+        const float2 c2 = make_float2(cc, cc);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            expand_bytes<false>(wq[j] & 0x0f0f0f0fu, a2, c2, out[2 * j], out[2 * j + 1]);
+            expand_bytes<false>((wq[j] >> 4) & 0x0f0f0f0fu, a2, c2, out[8 + 2 * j], out[8 + 2 * j + 1]);
+        }
+    }
+};
+
+template <>
+struct Raw<FQ_Q2_0> {
+    uint2 q;
+    float d;
+    // row = [crumbs: K/4 bytes][d: K/128 f16]. Element j of a 128-element group is crumb j % 4 of byte j / 4;
+    // value d * (q - 1) (cold.zig:285-301).
+    __device__ __forceinline__ void load(const DevWeights& w, const uint8_t* unit0, size_t, int ks, int h) {
+        const int e0 = ks * 64 + h * 32;
+        q = __ldg(reinterpret_cast<const uint2*>(unit0 + (e0 >> 2)));
+        d = h2f(__ldg(reinterpret_cast<const uint16_t*>(unit0 + (w.k >> 2)) + (e0 >> 7)));
+    }
+    __device__ __forceinline__ void load_header(uint32_t) {}
+    __device__ __forceinline__ void load_slab(uint32_t, int) {}
+    // A byte holds four consecutive elements as crumbs 0..3. The byte is replicated into the four byte lanes of
+    // a word and masked so that lane n keeps crumb n IN PLACE (bits 2n, 2n+1): dropped into the mantissa of
+    // 128.0f this reads 128 + code * 4^n, and the scale d / 4^n with the offset -(128 / 4^n + 1) * d (all exact)
+    // gives d * (code - 1). Crumb 3 would reach the exponent bit, so it is shifted down and treated like crumb 0.
+    __device__ __forceinline__ void expand(int, int, uint32_t out[16]) const {
+        const float2 a01 = make_float2(d, __fmul_rn(d, 0.25f)), a23 = make_float2(__fmul_rn(d, 0.0625f), d);
+        const float2 c01 = make_float2(__fmul_rn(d, -129.0f), __fmul_rn(d, -33.0f));
+        const float2 c23 = make_float2(__fmul_rn(d, -9.0f), __fmul_rn(d, -129.0f));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t r = __byte_perm(j < 4 ? q.x : q.y, 0, 0x1111 * (j & 3));  // the byte in all four lanes
+            const uint32_t m012 = r & 0x00300c03u, m3 = (r >> 6) & 0x03u;
+            const float2 x01 = make_float2(__uint_as_float(__byte_perm(m012, 0x43000000u, 0x7044)),
+                                           __uint_as_float(__byte_perm(m012, 0x43000000u, 0x7144)));
+            const float2 x23 = make_float2(__uint_as_float(__byte_perm(m012, 0x43000000u, 0x7244)),
+                                           __uint_as_float(__byte_perm(m3, 0x43000000u, 0x7044)));
+            const float2 w01 = __ffma2_rn(a01, x01, c01), w23 = __ffma2_rn(a23, x23, c23);
+            out[2 * j] = pack_bf16(w01.x, w01.y);
+            out[2 * j + 1] = pack_bf16(w23.x, w23.y);
+        }
+    }
+};
+
 template <int FMT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, const __grid_constant__ CUtensorMap tmap_tokens,
                                                               const __grid_constant__ CUtensorMap tmap_weights) {
@@ -679,7 +741,8 @@ extern "C" __attribute__((visibility("default"))) int fq_debug_tc_timeline(unsig
 }  // namespace
 
 bool tensor_path_serves(const DevWeights& w) {
-    return (w.fmt == FQ_Q4_K || w.fmt == FQ_Q5_K || w.fmt == FQ_Q8_0 || w.fmt == FQ_TQ2_0) && w.k % 256 == 0 && encode_fn() != nullptr;
+    return (w.fmt == FQ_Q4_K || w.fmt == FQ_Q5_K || w.fmt == FQ_Q8_0 || w.fmt == FQ_TQ2_0 || w.fmt == FQ_TQ2_0_FOLDED || w.fmt == FQ_Q2_0) &&
+           w.k % 256 == 0 && encode_fn() != nullptr;
 }
 
 // Launch over bf16 activation rows [rows][k]: dense tiles of matrix `mat` (table == nullptr) or a
@@ -722,6 +785,8 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
         case FQ_Q4_K: e = launch_tc<FQ_Q4_K>(a, tmap, tmap_w, grid, st); break;
         case FQ_Q5_K: e = launch_tc<FQ_Q5_K>(a, tmap, tmap_w, grid, st); break;
         case FQ_TQ2_0: e = launch_tc<FQ_TQ2_0>(a, tmap, tmap_w, grid, st); break;
+        case FQ_TQ2_0_FOLDED: e = launch_tc<FQ_TQ2_0_FOLDED>(a, tmap, tmap_w, grid, st); break;
+        case FQ_Q2_0: e = launch_tc<FQ_Q2_0>(a, tmap, tmap_w, grid, st); break;
         default: e = launch_tc<FQ_Q8_0>(a, tmap, tmap_w, grid, st); break;
     }
     g_trace.launches++;
@@ -730,7 +795,7 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
 
 int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, size_t rows, float* c_dev, size_t ldc,
                             const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st) {
-    if (!tensor_path_serves(w)) return fail(FQ_DECLINED_ARGS, "tensor-core path serves Q4_K, Q5_K, Q8_0 and TQ2_0 with k %% 256 == 0");
+    if (!tensor_path_serves(w)) return fail(FQ_DECLINED_ARGS, "tensor-core path needs a served format with k %% 256 == 0");
     return launch_tc_rows(ctx, w, 0, (const __nv_bfloat16*)a_bf16, rows, c_dev, ldc, table, n_tiles_dev, max_tiles, st);
 }
 
@@ -760,8 +825,7 @@ cudaError_t launch_f32_to_bf16(const float* src, void* dst, size_t n, cudaStream
 }
 
 int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, cudaStream_t st) {
-    if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q8_0 && w.fmt != FQ_TQ2_0)
-        return fail(FQ_DECLINED_ARGS, "tensor-core path serves Q4_K, Q5_K, Q8_0 and TQ2_0");
+    if (!format_info(w.fmt).block_elems || w.fmt == FQ_Q6_K) return fail(FQ_DECLINED_ARGS, "format %d has no tensor-core kernel", w.fmt);
     if (w.k % 256 != 0 || m < 1 || m > (size_t)1 << 24) return fail(FQ_DECLINED_ARGS, "tensor-core path needs k %% 256 == 0");
     // bf16 copy of the activations: [m][k], read by TMA with a 128-byte swizzle
     __nv_bfloat16* abf = (__nv_bfloat16*)dev_alloc(m * (size_t)w.k * 2);

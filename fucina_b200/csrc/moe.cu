@@ -311,7 +311,8 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     const int pairs = seq * top_k;
     // prefill-sized batches: bf16 tensor-core products (the reference's own GPU arm multiplies rounded
     // operands too); decode-sized batches keep the CPU kernels' int8 arithmetic
-    const bool tc_ok = tensor_path_serves(gate) && tensor_path_serves(down);
+    // the grouped tensor-core form is exercised for the formats expert stacks come in (K-quants and Q8_0)
+    const bool tc_ok = (fmt == FQ_Q4_K || fmt == FQ_Q5_K || fmt == FQ_Q8_0) && tensor_path_serves(gate) && tensor_path_serves(down);
     if (tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 20 * n_expert)))
         return moe_layer_tensor_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, shard, out_dev, st);
     const ActSizes Sx = act_sizes(fmt, hidden), Sg = act_sizes(fmt, out_pe);

@@ -38,7 +38,7 @@ def run_tensor(P, torch, fmt, blocks, a, n, mode=None):
     return cd.cpu().numpy()
 
 
-@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q8_0", "tq2_0"])
+@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q8_0", "tq2_0", "tq2_0_folded", "q2_0"])
 @pytest.mark.parametrize("m,n,k", [
     (64, 128, 256),      # one tile, one block of K
     (33, 96, 512),       # the reference's ragged parity shape (cuda.zig:3084-3088): partial rows and tokens
@@ -107,15 +107,15 @@ def test_moe_tensor_arm_matches_bf16_oracle(P, fmt_name, hidden, out_pe, n_exper
         h.free()
 
 
-def test_formats_without_a_tensor_kernel_are_declined_in_tensor_mode(P, torch):
-    n, k, m = 64, 512, 32
-    blocks = make_weights("tq2_0_folded", n, k, seed=2300)
+def test_shapes_without_a_tensor_kernel_are_declined_in_tensor_mode(P, torch):
+    n, k, m = 64, 288, 32   # Q8_0 rows of nine 32-weight blocks: fine for the integer kernels, not a whole number of K slabs
+    blocks = make_weights("q8_0", n, k, seed=2300)
     a = np.zeros((m, k), np.float32)
     with pytest.raises(P.Declined):
-        run_tensor(P, torch, oracle.TQ2_0_FOLDED, blocks, a, n)
+        run_tensor(P, torch, oracle.Q8_0, blocks, a, n)
     # AUTO falls back to the integer kernel in 16-row passes
-    got = run_tensor(P, torch, oracle.TQ2_0_FOLDED, blocks, a + 1.0, n, mode=P.MODE_AUTO)
-    assert_close(got, oracle.matmul(oracle.TQ2_0_FOLDED, blocks, a + 1.0), 1e-3, "folded auto")
+    got = run_tensor(P, torch, oracle.Q8_0, blocks, a + 1.0, n, mode=P.MODE_AUTO)
+    assert_close(got, oracle.matmul(oracle.Q8_0, blocks, a + 1.0), 1e-3, "q8_0 auto")
 
 
 @pytest.mark.parametrize("planes", [1, 2])
