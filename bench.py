@@ -177,7 +177,7 @@ def run_ours(args) -> dict:
     rank, world, local = dist_setup(args.gpus)
     P.init(local)
     ext = torch.cuda.ExternalStream(P.stream_ptr())
-    batch = 1
+    batch = max(1, min(16, getattr(args, "batch", 1)))  # 1 is the headline; 4 and 16 are the other decode batches of the config
     n_copies = max(2, -(-4 * L2_BYTES // sum(n * ROW_BYTES for n in STACK_N)))  # pool >= 4x L2
     stacks = [Stack(P, torch, s, keep_host=True) for s in range(n_copies)]
     g = torch.Generator(device="cuda").manual_seed(2000 + 100 * 1 + rank)
@@ -251,7 +251,9 @@ def run_ours(args) -> dict:
         while time.time() < t_end:
             step_cycle.launch()
             P.synchronize()
-    launches = args.steps * len(STACK_N)  # one decode kernel per product, activation quantisation fused in
+    # one decode kernel per product with the activation quantisation fused in (batch <= 4); wider batches
+    # quantise in a kernel of their own first
+    launches = args.steps * len(STACK_N) * (1 if batch <= 4 else 2)
     bytes_step = stack_bytes(batch)
     value = world * bytes_step * args.steps / (ms * 1e-3) / 1e9
 
@@ -322,7 +324,7 @@ def run_ours(args) -> dict:
         "metric": "quant GEMV HBM GB/s", "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8xq4 -> f32", "data": "synthetic",
-        "config": {"workload": "Q4_K decode GEMV stack, batch 1, K=4096 -> N in {4096,11008,4096,32000}",
+        "config": {"workload": f"Q4_K decode GEMV stack, batch {batch}, K=4096 -> N in {{4096,11008,4096,32000}}",
                    "bytes_per_step": bytes_step, "weight_copies_rotated": n_copies,
                    "l2_policy": f"inputs larger than L2: {n_copies} distinct weight copies ({n_copies * bytes_step >> 20} MiB) rotated",
                    "parallelism": f"dp{world} replicas" if world > 1 else "single GPU"},
@@ -711,6 +713,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--batch", type=int, default=1, help="activation rows per product of the decode stack (1, 4 or 16)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     # Libraries (NCCL prints its version banner) may write to stdout; the contract is ONE JSON line

@@ -288,6 +288,96 @@ __device__ __forceinline__ void unit_q8_0(uint32_t p, uint32_t ps, const ActView
     }
 }
 
+// ---- eight activation rows at a time: the block dots go through the warp-level int8 tensor-core
+// instruction (mma.sync m16n8k32, u8 levels x s8 activations -> s32, exact), 16 weight rows x 8 tokens x 32
+// weights at a time, instead of eight rounds of dp4a per row. The lane <-> (row, token) ownership is the
+// instruction's fragment layout, with g = lane / 4 and t = lane % 4:
+//   A (weights)      words of rows g and g + 8, elements 4t..4t+3 and 16+4t..16+4t+3 of the sub-block
+//   B (activations)  token g, the same element columns
+//   D (dots)         rows g and g + 8, tokens 2t and 2t + 1
+// A 32-row tile is two such row groups; acc[4 * group + {0,1}] belongs to row 16*group + g, tokens 2t and
+// 2t + 1, acc[4 * group + {2,3}] to row 16*group + 8 + g. Sub-block scales multiply the integer dots, the
+// min term and the f32 epilogue are those of block_q4_k / block_q5_k, so values are identical to them.
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) { return *reinterpret_cast<const uint32_t*>(__cvta_shared_to_generic(addr)); }
+
+template <int FMT>
+__device__ __forceinline__ void expert_block_mma(uint32_t tile_base, const ActView& V, int kb, int lane, float (&acc)[8]) {
+    constexpr int UB = FMT == FQ_Q4_K ? 144 : 176;
+    constexpr int QS = FMT == FQ_Q4_K ? 16 : 48;  // offset of the nibble payload inside a block
+    const int g = lane >> 2, t = lane & 3;
+    // headers of this lane's four rows: g, g + 8, g + 16, g + 24
+    KHeader H[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) H[i].decode(lds128(tile_base + (uint32_t)(g + 8 * i) * UB));
+    int isc[4][2], imn[4][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) isc[i][0] = isc[i][1] = imn[i][0] = imn[i][1] = 0;
+    uint32_t qh[4][2];  // Q5_K: fifth bits of elements 4t..4t+3 and 16+4t.. of the four rows, all eight sub-blocks
+    if (FMT == FQ_Q5_K) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            qh[i][0] = lds32(tile_base + (uint32_t)(g + 8 * i) * UB + 16 + 4 * t);
+            qh[i][1] = lds32(tile_base + (uint32_t)(g + 8 * i) * UB + 32 + 4 * t);
+        }
+    }
+    const uint32_t arow = V.base + (uint32_t)g * V.row + (uint32_t)kb * 256 + 4 * t;  // token g, this lane's columns
+#pragma unroll
+    for (int pp = 0; pp < 4; ++pp) {
+        // activations of sub-blocks 2pp (low nibbles) and 2pp + 1 (high nibbles)
+        const uint32_t b_lo0 = lds32(arow + pp * 64), b_lo1 = lds32(arow + pp * 64 + 16);
+        const uint32_t b_hi0 = lds32(arow + pp * 64 + 32), b_hi1 = lds32(arow + pp * 64 + 48);
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+            const int ia = 2 * grp, ib = 2 * grp + 1;  // rows 16*grp + g and 16*grp + 8 + g
+            const uint32_t pa = tile_base + (uint32_t)(g + 16 * grp) * UB + QS + pp * 32 + 4 * t;
+            const uint32_t pb = pa + 8 * UB;
+            const uint32_t w[4] = {lds32(pa), lds32(pb), lds32(pa + 16), lds32(pb + 16)};
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                lo[x] = w[x] & 0x0f0f0f0fu;
+                hi[x] = (w[x] >> 4) & 0x0f0f0f0fu;
+            }
+            if (FMT == FQ_Q5_K) {
+                const uint32_t h[4] = {qh[ia][0], qh[ib][0], qh[ia][1], qh[ib][1]};
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    lo[x] |= ((h[x] >> (2 * pp)) & 0x01010101u) << 4;
+                    hi[x] |= ((h[x] >> (2 * pp + 1)) & 0x01010101u) << 4;
+                }
+            }
+            int dlo[4], dhi[4];
+            mma_u8s8(dlo, lo, b_lo0, b_lo1);
+            mma_u8s8(dhi, hi, b_hi0, b_hi1);
+            const int sa_a = byte_of(H[ia].sc[pp >> 1], (pp & 1) * 2), sb_a = byte_of(H[ia].sc[pp >> 1], (pp & 1) * 2 + 1);
+            const int sa_b = byte_of(H[ib].sc[pp >> 1], (pp & 1) * 2), sb_b = byte_of(H[ib].sc[pp >> 1], (pp & 1) * 2 + 1);
+            isc[ia][0] += sa_a * dlo[0] + sb_a * dhi[0];
+            isc[ia][1] += sa_a * dlo[1] + sb_a * dhi[1];
+            isc[ib][0] += sa_b * dlo[2] + sb_b * dhi[2];
+            isc[ib][1] += sa_b * dlo[3] + sb_b * dhi[3];
+        }
+    }
+    // min term and f32 epilogue per (row, token), as in block_q4_k
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const uint32_t rec = V.base + (uint32_t)(2 * t + c) * V.row;
+        const float da = lds_f32(rec + V.off_ad + kb * 4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int mn_term = min_term(H[i], rec + V.off_sums + kb * 32);
+            const int grp = i >> 1, half = i & 1;  // rows g + 8*i = 16*grp + 8*half + g
+            float& a = acc[4 * grp + 2 * half + c];
+            a = __fadd_rn(a, kquant_term(H[i], da, isc[i][c], mn_term));
+        }
+    }
+}
+
 // The same unit when it was staged by tensor copies (RowsArgs.use_tmap == 2): per warp step the 32 rows x 256
 // payload bytes arrive as two boxes of 32 x 128 bytes with the 128-byte swizzle (16-byte chunk c of row r sits
 // at chunk c ^ (r % 8), so a quarter warp's 128-bit loads fall on distinct banks although rows are 128 bytes
@@ -337,7 +427,7 @@ __host__ __device__ inline SlabGeom slab_geom(int fmt, int slab) {
 }
 
 template <int FMT, int MB, bool FUSED, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_kernel(const RowsArgs A, const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap2) {
+__global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) decode_rows_kernel(const RowsArgs A, const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap2) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int kWarps = WARPS, kThreads = WARPS * 32;  // the warps split K; 16 when a row has at least 16 units
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -511,6 +601,9 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
     bool ok = true;
     int it = 0;
     for (int tile = 0; tile < ntiles; ++tile) {
+        // K-quant batches of 3..16 rows (MB = 8 or 16) multiply through the warp-level tensor-core instruction:
+        // acc then holds the fragment layout of expert_block_mma, eight values per group of eight rows
+        constexpr bool kMma = FMT != FQ_Q8_0 && MB >= 8;
         float acc[MB];
 #pragma unroll
         for (int b = 0; b < MB; ++b) acc[b] = 0.0f;
@@ -527,8 +620,19 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
             const uint32_t p = slot0 + (uint32_t)stage * stage_stride;
             for (int u = 0; u < nu && !A.skip_compute; ++u) {
                 const int kb = sl * A.slab + u;
-                if (FMT == FQ_Q4_K) block_q4_k<MB>(p + u * 144, V, kb, acc);
-                if (FMT == FQ_Q5_K) block_q5_k<MB>(p + u * 176, V, kb, acc);
+                if (kMma) {
+                    constexpr int UBK = FMT == FQ_Q4_K ? 144 : 176;
+#pragma unroll
+                    for (int tg = 0; tg < MB / 8; ++tg) {
+                        const ActView Vt = {V.base + (uint32_t)(tg * 8) * V.row, V.row, V.off_sums, V.off_ad};
+                        expert_block_mma<FMT == FQ_Q8_0 ? FQ_Q4_K : FMT>(p - (uint32_t)lane * G.slot_bytes + u * UBK * 32, Vt, kb, lane,
+                                                                        *reinterpret_cast<float(*)[8]>(&acc[tg * 8 < MB ? tg * 8 : 0]));
+                    }
+                } else if (FMT == FQ_Q4_K) {
+                    block_q4_k<MB>(p + u * 144, V, kb, acc);
+                } else if (FMT == FQ_Q5_K) {
+                    block_q5_k<MB>(p + u * 176, V, kb, acc);
+                }
                 if (FMT == FQ_Q8_0) {
                     if (q8_boxes) unit_q8_0_swz<MB>(p, lane, V, kb, acc);
                     else unit_q8_0<MB>(p + u * 256, p + G.scale_off + u * 16, V, kb, acc);
@@ -543,14 +647,21 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) decode_rows_ke
 #pragma unroll
         for (int b = 0; b < MB; ++b) rbuf[(warp * MB + b) * 32 + lane] = acc[b];
         __syncthreads();
-        if (threadIdx.x < 32 * MB) {
-            const int b = threadIdx.x >> 5;
+        for (int b = warp; b < MB; b += kWarps) {
             float s = 0.0f;
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) s += rbuf[(w * MB + b) * 32 + lane];
             int row0, nvalid;
             tile_rows(tile, row0, nvalid);
-            if (lane < nvalid && b < A.m) A.c[(size_t)b * A.ldc + row0 + lane] = s;
+            if (kMma) {
+                // value b of a lane: token group b / 8, fragment slot i = b % 8 -> (row, token) of expert_block_mma
+                const int i = b & 7;
+                const int r = 16 * (i >> 2) + 8 * ((i >> 1) & 1) + (lane >> 2);
+                const int tok = (b >> 3) * 8 + 2 * (lane & 3) + (i & 1);
+                if (r < nvalid && tok < A.m) A.c[(size_t)tok * A.ldc + row0 + r] = s;
+            } else if (lane < nvalid && b < A.m) {
+                A.c[(size_t)b * A.ldc + row0 + lane] = s;
+            }
         }
     }
     stamp(6);
@@ -581,11 +692,20 @@ size_t smem_bytes(int fmt, int k, int mb, int slab, int stages, int warps) {
 int pick_warps(int fmt, int k, int mb) {
     static const int forced = getenv("FUCINA_B200_DECODE_WARPS") ? atoi(getenv("FUCINA_B200_DECODE_WARPS")) : 0;
     if (forced == 8) return 8;
-    if (k / 256 < 16 || mb > 2) return 8;
+    static const bool wide8 = getenv("FUCINA_B200_DECODE_WIDE8") ? atoi(getenv("FUCINA_B200_DECODE_WIDE8")) != 0 : false;
+    const bool wide_ok = mb <= 2 || (mb == 8 && fmt != FQ_Q8_0 && wide8);  // the eight-row tensor-core variant also fits 16 warps
+    if (k / 256 < 16 || !wide_ok) return 8;
     return smem_bytes(fmt, k, mb, 1, 2, 16) <= 227 * 1024 ? 16 : 8;  // the smallest 16-warp ring must fit
 }
 
 int pad_rows(size_t m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
+// Row tile of the dense kernel: K-quant batches of 3..16 rows run the tensor-core block product in groups of
+// eight tokens; Q8_0 keeps dp4a up to eight rows.
+constexpr int kMaxDecodeRows = 16;
+int decode_pad_rows(int fmt, size_t m) {
+    if (fmt == FQ_Q8_0 || m <= 2) return pad_rows(m);
+    return m <= 8 ? 8 : 16;
+}
 
 // Two CTAs per SM (8 warps, 2 stages, at most half the SM's shared memory each) for tile-major
 // weights. In-flight bytes per SM stay the same as one 16-warp CTA with a deeper ring, but a CTA of
@@ -681,7 +801,7 @@ size_t smem_bytes_q8_boxes(int k, int mb, int stages) {
 template <int FMT, int MB>
 cudaError_t launch_fmt_mb(const RowsArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap2, bool fused, bool half, int grid, size_t smem,
                           cudaStream_t st) {
-    constexpr bool kWide = MB <= 2;  // the 16-warp form exists for the small-batch variants only
+    constexpr bool kWide = MB <= 2 || (MB == 8 && FMT != FQ_Q8_0);  // the 16-warp form exists for these variants only
     const bool wide = kWide && !half && pick_warps(FMT, a.w.k, MB) == 16;
     void (*kern)(const RowsArgs, const CUtensorMap, const CUtensorMap) =
         wide ? (fused ? decode_rows_kernel<FMT, MB, true, kWide ? 16 : 8> : decode_rows_kernel<FMT, MB, false, kWide ? 16 : 8>)
@@ -720,6 +840,7 @@ cudaError_t launch_fmt(const RowsArgs& a, const CUtensorMap& tmap, const CUtenso
         case 1: return launch_fmt_mb<FMT, 1>(a, tmap, tmap2, fused, half, grid, smem, st);
         case 2: return launch_fmt_mb<FMT, 2>(a, tmap, tmap2, fused, half, grid, smem, st);
         case 4: return launch_fmt_mb<FMT, 4>(a, tmap, tmap2, fused, half, grid, smem, st);
+        case 16: return launch_fmt_mb<FMT, 16>(a, tmap, tmap2, fused, half, grid, smem, st);
         default: return launch_fmt_mb<FMT, 8>(a, tmap, tmap2, fused, half, grid, smem, st);
     }
 }
@@ -757,96 +878,6 @@ __device__ __forceinline__ void expert_block_m(int mstep, uint32_t p, const ActV
     if (MB >= 4 && mstep == 4) return expert_block<FMT, MB >= 4 ? 4 : MB>(p, V, unit, acc);
     if (MB >= 2 && mstep == 2) return expert_block<FMT, MB >= 2 ? 2 : MB>(p, V, unit, acc);
     expert_block<FMT, 1>(p, V, unit, acc);
-}
-
-// ---- eight activation rows per entry: the block dots go through the warp-level int8 tensor-core
-// instruction (mma.sync m16n8k32, u8 levels x s8 activations -> s32, exact), 16 weight rows x 8 tokens x 32
-// weights at a time, instead of eight rounds of dp4a per row. The lane <-> (row, token) ownership is the
-// instruction's fragment layout, with g = lane / 4 and t = lane % 4:
-//   A (weights)      words of rows g and g + 8, elements 4t..4t+3 and 16+4t..16+4t+3 of the sub-block
-//   B (activations)  token g, the same element columns
-//   D (dots)         rows g and g + 8, tokens 2t and 2t + 1
-// A 32-row tile is two such row groups; acc[4 * group + {0,1}] belongs to row 16*group + g, tokens 2t and
-// 2t + 1, acc[4 * group + {2,3}] to row 16*group + 8 + g. Sub-block scales multiply the integer dots, the
-// min term and the f32 epilogue are those of block_q4_k / block_q5_k, so values are identical to them.
-__device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) { return *reinterpret_cast<const uint32_t*>(__cvta_shared_to_generic(addr)); }
-
-template <int FMT>
-__device__ __forceinline__ void expert_block_mma(uint32_t tile_base, const ActView& V, int kb, int lane, float (&acc)[8]) {
-    constexpr int UB = FMT == FQ_Q4_K ? 144 : 176;
-    constexpr int QS = FMT == FQ_Q4_K ? 16 : 48;  // offset of the nibble payload inside a block
-    const int g = lane >> 2, t = lane & 3;
-    // headers of this lane's four rows: g, g + 8, g + 16, g + 24
-    KHeader H[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) H[i].decode(lds128(tile_base + (uint32_t)(g + 8 * i) * UB));
-    int isc[4][2], imn[4][2];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) isc[i][0] = isc[i][1] = imn[i][0] = imn[i][1] = 0;
-    uint32_t qh[4][2];  // Q5_K: fifth bits of elements 4t..4t+3 and 16+4t.. of the four rows, all eight sub-blocks
-    if (FMT == FQ_Q5_K) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            qh[i][0] = lds32(tile_base + (uint32_t)(g + 8 * i) * UB + 16 + 4 * t);
-            qh[i][1] = lds32(tile_base + (uint32_t)(g + 8 * i) * UB + 32 + 4 * t);
-        }
-    }
-    const uint32_t arow = V.base + (uint32_t)g * V.row + (uint32_t)kb * 256 + 4 * t;  // token g, this lane's columns
-#pragma unroll
-    for (int pp = 0; pp < 4; ++pp) {
-        // activations of sub-blocks 2pp (low nibbles) and 2pp + 1 (high nibbles)
-        const uint32_t b_lo0 = lds32(arow + pp * 64), b_lo1 = lds32(arow + pp * 64 + 16);
-        const uint32_t b_hi0 = lds32(arow + pp * 64 + 32), b_hi1 = lds32(arow + pp * 64 + 48);
-#pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-            const int ia = 2 * grp, ib = 2 * grp + 1;  // rows 16*grp + g and 16*grp + 8 + g
-            const uint32_t pa = tile_base + (uint32_t)(g + 16 * grp) * UB + QS + pp * 32 + 4 * t;
-            const uint32_t pb = pa + 8 * UB;
-            const uint32_t w[4] = {lds32(pa), lds32(pb), lds32(pa + 16), lds32(pb + 16)};
-            uint32_t lo[4], hi[4];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                lo[x] = w[x] & 0x0f0f0f0fu;
-                hi[x] = (w[x] >> 4) & 0x0f0f0f0fu;
-            }
-            if (FMT == FQ_Q5_K) {
-                const uint32_t h[4] = {qh[ia][0], qh[ib][0], qh[ia][1], qh[ib][1]};
-#pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                    lo[x] |= ((h[x] >> (2 * pp)) & 0x01010101u) << 4;
-                    hi[x] |= ((h[x] >> (2 * pp + 1)) & 0x01010101u) << 4;
-                }
-            }
-            int dlo[4], dhi[4];
-            mma_u8s8(dlo, lo, b_lo0, b_lo1);
-            mma_u8s8(dhi, hi, b_hi0, b_hi1);
-            const int sa_a = byte_of(H[ia].sc[pp >> 1], (pp & 1) * 2), sb_a = byte_of(H[ia].sc[pp >> 1], (pp & 1) * 2 + 1);
-            const int sa_b = byte_of(H[ib].sc[pp >> 1], (pp & 1) * 2), sb_b = byte_of(H[ib].sc[pp >> 1], (pp & 1) * 2 + 1);
-            isc[ia][0] += sa_a * dlo[0] + sb_a * dhi[0];
-            isc[ia][1] += sa_a * dlo[1] + sb_a * dhi[1];
-            isc[ib][0] += sa_b * dlo[2] + sb_b * dhi[2];
-            isc[ib][1] += sa_b * dlo[3] + sb_b * dhi[3];
-        }
-    }
-    // min term and f32 epilogue per (row, token), as in block_q4_k
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-        const uint32_t rec = V.base + (uint32_t)(2 * t + c) * V.row;
-        const float da = lds_f32(rec + V.off_ad + kb * 4);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int mn_term = min_term(H[i], rec + V.off_sums + kb * 32);
-            const int grp = i >> 1, half = i & 1;  // rows g + 8*i = 16*grp + 8*half + g
-            float& a = acc[4 * grp + 2 * half + c];
-            a = __fadd_rn(a, kquant_term(H[i], da, isc[i][c], mn_term));
-        }
-    }
 }
 
 template <int FMT, int MB, bool GATED>
@@ -1103,9 +1134,9 @@ cudaError_t launch_bounded_wait_probe(int* status, unsigned limit, cudaStream_t 
 
 bool decode_rows_eligible(const DevWeights& w, size_t m) {
     if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q8_0) return false;
-    if (m < 1 || m > 8 || w.k % 256 != 0 || w.k < 2048 || w.n < 64) return false;
+    if (m < 1 || m > (size_t)(w.fmt == FQ_Q8_0 ? 8 : kMaxDecodeRows) || w.k % 256 != 0 || w.k < 2048 || w.n < 64) return false;
     int slab, stages;
-    return pick_config(w.fmt, w.k, pad_rows(m), &slab, &stages);
+    return pick_config(w.fmt, w.k, decode_pad_rows(w.fmt, m), &slab, &stages);
 }
 
 size_t decode_rows_scratch_bytes(const DevWeights& w, size_t m) {
@@ -1115,7 +1146,7 @@ size_t decode_rows_scratch_bytes(const DevWeights& w, size_t m) {
 
 cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev, uint8_t* scratch, float* c, int m, int ldc,
                                int sm_count, int* status, cudaStream_t st) {
-    const int mb = pad_rows((size_t)m);
+    const int mb = decode_pad_rows(w.fmt, (size_t)m);
     static const int skip = getenv("FUCINA_B200_DECODE_SKIP_COMPUTE") ? 1 : 0;  // diagnosis: copy pipeline only, outputs are garbage
     static const int l2_stream = getenv("FUCINA_B200_DECODE_L2_STREAM") ? atoi(getenv("FUCINA_B200_DECODE_L2_STREAM")) : 1;
     RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0, skip, l2_stream, 0};
@@ -1131,6 +1162,7 @@ cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev,
         static const bool forced = getenv("FUCINA_B200_DECODE_STAGES") != nullptr;
         if (!forced && a.stages > 2) a.stages = 2;
     }
+    if (w.fmt != FQ_Q8_0 && mb >= 8) a.slab = 1;  // the tensor-core block product reads one unit of 32 rows per stage
     if (!w.tile_rows && w.fmt != FQ_Q8_0 && a.slab == 1 && !no_tmap && make_weight_tmap(w, mat, slab_geom(w.fmt, 1).unit_bytes, &tmap)) a.use_tmap = 1;
     // Q8_0 rows are a payload plane and a scale plane: three tensor copies per warp step (two swizzled payload
     // boxes, one scale box) instead of 64 per-lane bulk copies
