@@ -339,22 +339,28 @@ __device__ __forceinline__ void expert_block_mma(uint32_t tile_base, const ActVi
             const uint32_t pb = pa + 8 * UB;
             const uint32_t w[4] = {lds32(pa), lds32(pb), lds32(pa + 16), lds32(pb + 16)};
             uint32_t lo[4], hi[4];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                lo[x] = w[x] & 0x0f0f0f0fu;
-                hi[x] = (w[x] >> 4) & 0x0f0f0f0fu;
-            }
+            int dlo[4], dhi[4];
             if (FMT == FQ_Q5_K) {
                 const uint32_t h[4] = {qh[ia][0], qh[ib][0], qh[ia][1], qh[ib][1]};
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
-                    lo[x] |= ((h[x] >> (2 * pp)) & 0x01010101u) << 4;
-                    hi[x] |= ((h[x] >> (2 * pp + 1)) & 0x01010101u) << 4;
+                    lo[x] = (w[x] & 0x0f0f0f0fu) | (((h[x] >> (2 * pp)) & 0x01010101u) << 4);
+                    hi[x] = ((w[x] >> 4) & 0x0f0f0f0fu) | (((h[x] >> (2 * pp + 1)) & 0x01010101u) << 4);
                 }
+                mma_u8s8(dlo, lo, b_lo0, b_lo1);
+                mma_u8s8(dhi, hi, b_hi0, b_hi1);
+            } else {
+                // Q4_K: the high nibbles stay in place as 16 * level (a u8 below 256); the factor is shifted out of the dots
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    lo[x] = w[x] & 0x0f0f0f0fu;
+                    hi[x] = w[x] & 0xf0f0f0f0u;
+                }
+                mma_u8s8(dlo, lo, b_lo0, b_lo1);
+                mma_u8s8(dhi, hi, b_hi0, b_hi1);
+#pragma unroll
+                for (int x = 0; x < 4; ++x) dhi[x] >>= 4;  // exact: every product carried the factor 16
             }
-            int dlo[4], dhi[4];
-            mma_u8s8(dlo, lo, b_lo0, b_lo1);
-            mma_u8s8(dhi, hi, b_hi0, b_hi1);
             const int sa_a = byte_of(H[ia].sc[pp >> 1], (pp & 1) * 2), sb_a = byte_of(H[ia].sc[pp >> 1], (pp & 1) * 2 + 1);
             const int sa_b = byte_of(H[ib].sc[pp >> 1], (pp & 1) * 2), sb_b = byte_of(H[ib].sc[pp >> 1], (pp & 1) * 2 + 1);
             isc[ia][0] += sa_a * dlo[0] + sb_a * dhi[0];
@@ -363,14 +369,21 @@ __device__ __forceinline__ void expert_block_mma(uint32_t tile_base, const ActVi
             isc[ib][1] += sa_b * dlo[3] + sb_b * dhi[3];
         }
     }
-    // min term and f32 epilogue per (row, token), as in block_q4_k
+    // min term and f32 epilogue per (row, token), as in block_q4_k. The eight sub-block sums of a token fit
+    // int16 (|sum of 32 int8| <= 4064), so sum(mn[s] * bsum[s]) is four 2-way int16 x int8 dot instructions.
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
         const uint32_t rec = V.base + (uint32_t)(2 * t + c) * V.row;
         const float da = lds_f32(rec + V.off_ad + kb * 4);
+        const uint4 s0 = lds128(rec + V.off_sums + kb * 32), s1 = lds128(rec + V.off_sums + kb * 32 + 16);
+        const int bs01 = (int)__byte_perm(s0.x, s0.y, 0x5410), bs23 = (int)__byte_perm(s0.z, s0.w, 0x5410);
+        const int bs45 = (int)__byte_perm(s1.x, s1.y, 0x5410), bs67 = (int)__byte_perm(s1.z, s1.w, 0x5410);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int mn_term = min_term(H[i], rec + V.off_sums + kb * 32);
+            int mn_term = __dp2a_lo(bs01, (int)H[i].mn[0], 0);
+            mn_term = __dp2a_hi(bs23, (int)H[i].mn[0], mn_term);
+            mn_term = __dp2a_lo(bs45, (int)H[i].mn[1], mn_term);
+            mn_term = __dp2a_hi(bs67, (int)H[i].mn[1], mn_term);
             const int grp = i >> 1, half = i & 1;  // rows g + 8*i = 16*grp + 8*half + g
             float& a = acc[4 * grp + 2 * half + c];
             a = __fadd_rn(a, kquant_term(H[i], da, isc[i][c], mn_term));
@@ -692,7 +705,7 @@ size_t smem_bytes(int fmt, int k, int mb, int slab, int stages, int warps) {
 int pick_warps(int fmt, int k, int mb) {
     static const int forced = getenv("FUCINA_B200_DECODE_WARPS") ? atoi(getenv("FUCINA_B200_DECODE_WARPS")) : 0;
     if (forced == 8) return 8;
-    static const bool wide8 = getenv("FUCINA_B200_DECODE_WIDE8") ? atoi(getenv("FUCINA_B200_DECODE_WIDE8")) != 0 : false;
+    static const bool wide8 = getenv("FUCINA_B200_DECODE_WIDE8") ? atoi(getenv("FUCINA_B200_DECODE_WIDE8")) != 0 : true;
     const bool wide_ok = mb <= 2 || (mb == 8 && fmt != FQ_Q8_0 && wide8);  // the eight-row tensor-core variant also fits 16 warps
     if (k / 256 < 16 || !wide_ok) return 8;
     return smem_bytes(fmt, k, mb, 1, 2, 16) <= 227 * 1024 ? 16 : 8;  // the smallest 16-warp ring must fit
