@@ -662,8 +662,10 @@ def run_multi(args) -> list[dict]:
             o1 = torch.empty((T, hidden), device="cuda")
             torch.cuda.synchronize()
             forms = ["single GPU"] if moe is None else ["NCCL all-to-all dispatch/combine", "NCCL all-gather + reduce-scatter of partial sums",
-                                                        "NCCL all-gather + reduce-scatter of partial sums, 2 token chunks pipelined"]
-            if T % 2 or T < 512:
+                                                        "NCCL all-gather + reduce-scatter of partial sums, 2 token chunks pipelined",
+                                                        "NCCL all-gather (bf16 tokens) + reduce-scatter of partial sums",
+                                                        "NCCL all-gather (bf16 tokens) + reduce-scatter of partial sums, 2 token chunks pipelined"]
+            if T % 2 or T < 512:   # decode-sized batches keep f32 tokens (the int8 arm quantises them) and one exchange
                 forms = forms[:2]
             for form in forms:
                 def step():
@@ -674,7 +676,8 @@ def run_multi(args) -> list[dict]:
                         elif form.startswith("NCCL all-to-all"):
                             moe.forward(x, sel, wts)
                         else:
-                            moe.forward_gathered(x, sel, wts, partial_rows, chunks=2 if form.endswith("pipelined") else 1)
+                            moe.forward_gathered(x, sel, wts, partial_rows, chunks=2 if form.endswith("pipelined") else 1,
+                                                 exchange_dtype=torch.bfloat16 if "bf16" in form else None)
 
                 ms = timed(step)
                 out.append({"workload": f"Q5_K MoE layer (hidden 2048, ffn 768, 128 experts, top-8), {T_total} tokens over {world} GPU(s), "

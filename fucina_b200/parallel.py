@@ -133,7 +133,7 @@ class ExpertParallelMoE:
 
     def forward_gathered(self, x: torch.Tensor, selected: torch.Tensor, weights: torch.Tensor,
                          partial_ffn: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
-                         chunks: int = 1) -> torch.Tensor:
+                         chunks: int = 1, exchange_dtype=None) -> torch.Tensor:
         """The same layer with fixed-size exchanges and no host synchronisation: all-gather the token
         rows and their routing, let every rank compute the partial sums of ITS experts for all
         world*T tokens, and reduce-scatter the partial outputs back to the tokens' home ranks.
@@ -149,11 +149,19 @@ class ExpertParallelMoE:
         T, hidden = x.shape
         k = self.top_k
         W = self.world
-        # routing of every token, once: selected and weights travel as one int32/float32 pair of small gathers
-        sel_all = torch.empty((W, T, k), dtype=selected.dtype, device=x.device)
-        w_all = torch.empty((W, T, k), dtype=weights.dtype, device=x.device)
-        dist.all_gather_into_tensor(sel_all.view(W * T, k), selected.reshape(T, k).contiguous(), group=self.group)
-        dist.all_gather_into_tensor(w_all.view(W * T, k), weights.reshape(T, k).contiguous(), group=self.group)
+        # routing of every token, once. int32 ids and float32 weights have the same width, so they travel as one
+        # [T, 2k] int32 tensor (one collective launch instead of two); other dtypes take two gathers.
+        if selected.dtype == torch.int32 and weights.dtype == torch.float32:
+            packed = torch.cat([selected.reshape(T, k), weights.reshape(T, k).view(torch.int32)], dim=1).contiguous()
+            packed_all = torch.empty((W, T, 2 * k), dtype=torch.int32, device=x.device)
+            dist.all_gather_into_tensor(packed_all.view(W * T, 2 * k), packed, group=self.group)
+            sel_all = packed_all[:, :, :k]
+            w_all = packed_all[:, :, k:].contiguous().view(torch.float32)
+        else:
+            sel_all = torch.empty((W, T, k), dtype=selected.dtype, device=x.device)
+            w_all = torch.empty((W, T, k), dtype=weights.dtype, device=x.device)
+            dist.all_gather_into_tensor(sel_all.view(W * T, k), selected.reshape(T, k).contiguous(), group=self.group)
+            dist.all_gather_into_tensor(w_all.view(W * T, k), weights.reshape(T, k).contiguous(), group=self.group)
         out = torch.empty((T, hidden), dtype=x.dtype, device=x.device)
         gloo = dist.get_backend(self.group) == "gloo"   # gloo has no reduce-scatter: all-reduce and keep this rank's rows
         if chunks < 1 or T % chunks:
@@ -161,11 +169,13 @@ class ExpertParallelMoE:
         # Token chunks pipeline the exchange against the expert products: while chunk c is multiplied, chunk c+1
         # is being gathered and chunk c-1 reduced (asynchronous collectives run on the communicator's own stream).
         h = T // chunks
-        x = x.contiguous()
+        # token rows may cross the links in a narrower type (bf16 halves the gather; the tensor-core arm rounds
+        # its activations to bf16 anyway, so prefill-sized batches lose nothing) and are widened again on arrival
+        x_send = x.contiguous() if exchange_dtype is None else x.to(exchange_dtype).contiguous()
         gathers, xs = [], []
         for c in range(chunks):
-            xc = torch.empty((W * h, hidden), dtype=x.dtype, device=x.device)
-            gathers.append(dist.all_gather_into_tensor(xc, x[c * h:(c + 1) * h], group=self.group, async_op=not gloo))
+            xc = torch.empty((W * h, hidden), dtype=x_send.dtype, device=x.device)
+            gathers.append(dist.all_gather_into_tensor(xc, x_send[c * h:(c + 1) * h], group=self.group, async_op=not gloo))
             xs.append(xc)
         pending = []
         for c in range(chunks):
@@ -174,7 +184,7 @@ class ExpertParallelMoE:
             # rows of chunk c in rank-major order, as the gather lays the tokens out
             sel_c = sel_all[:, c * h:(c + 1) * h].reshape(W * h, k)
             w_c = w_all[:, c * h:(c + 1) * h].reshape(W * h, k)
-            partial = partial_ffn(xs[c], sel_c, w_c)
+            partial = partial_ffn(xs[c] if exchange_dtype is None else xs[c].to(x.dtype), sel_c, w_c)
             if gloo:
                 dist.all_reduce(partial, group=self.group)
                 out[c * h:(c + 1) * h].copy_(partial[self.rank * h:(self.rank + 1) * h])

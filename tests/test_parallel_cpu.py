@@ -96,6 +96,9 @@ def _worker(rank: int, world: int, port: int, case: str, q):
             for chunks in (1, 7):   # one exchange, and one per token (T = 7): the pipelined form's indexing
                 got2 = moe.forward_gathered(torch.from_numpy(x), torch.from_numpy(sel), torch.from_numpy(w), partial, chunks=chunks).numpy()
                 ok = ok and float(np.max(np.abs(got2 - want))) <= 1e-5 * scale   # only the f32 summation order differs
+            # int32 ids + float32 weights travel packed in one gather
+            got3 = moe.forward_gathered(torch.from_numpy(x), torch.from_numpy(sel.astype(np.int32)), torch.from_numpy(w), partial).numpy()
+            ok = ok and float(np.max(np.abs(got3 - want))) <= 1e-5 * scale
             q.put((rank, ok))
     finally:
         dist.destroy_process_group()
