@@ -419,13 +419,44 @@ def run_profile_case(args) -> dict:
     x = torch.randn((1, K), generator=g, device="cuda", dtype=torch.float32)
     y = torch.empty((1, n), device="cuda", dtype=torch.float32)
     torch.cuda.synchronize()
+    for _ in range(args.warmup):
+        P.gemm_quant_nt_dev(wt, x, y, 1, mode=P.MODE_INT8)
+    P.synchronize()
     P.kernel_timing(True)
-    for _ in range(args.warmup + args.steps):
+    for _ in range(args.steps):
         P.gemm_quant_nt_dev(wt, x, y, 1, mode=P.MODE_INT8)
     P.synchronize()
     ms, cnt = P.kernel_times()
     nbytes = n * ROW_BYTES + K * 4 + n * 4
     return {"workload": "profile case: Q4_K GEMV 65536x4096 batch 1", "launches": cnt, "bytes_per_launch": nbytes,
+            "avg_kernel_us": round(ms / max(cnt, 1) * 1e3, 2), "GBps": round(nbytes / (ms / max(cnt, 1) * 1e-3) / 1e9, 1)}
+
+
+def run_profile_q8(args) -> dict:
+    """The Q8_0 decode kernel for profiler captures: one 32000 x 4096 matrix (139 MB, larger than
+    the L2), payload staged by 128-byte-swizzled tensor copies, a handful of launches."""
+    import torch
+
+    from fucina_b200 import formats as F
+    from fucina_b200 import provider as P
+
+    P.init(0)
+    n = 32000
+    w = _dev_weights(P, torch, F.Q8_0, n, K, 1100)
+    g = torch.Generator(device="cuda").manual_seed(78)
+    x = torch.randn((1, K), generator=g, device="cuda", dtype=torch.float32)
+    y = torch.empty((1, n), device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    for _ in range(args.warmup):
+        P.gemm_quant_nt_dev(w, x, y, 1, mode=P.MODE_INT8)
+    P.synchronize()
+    P.kernel_timing(True)
+    for _ in range(args.steps):
+        P.gemm_quant_nt_dev(w, x, y, 1, mode=P.MODE_INT8)
+    P.synchronize()
+    ms, cnt = P.kernel_times()
+    nbytes = n * (K // 32 * 34) + K * 4 + n * 4
+    return {"workload": "profile case: Q8_0 GEMV 32000x4096 batch 1", "launches": cnt, "bytes_per_launch": nbytes,
             "avg_kernel_us": round(ms / max(cnt, 1) * 1e3, 2), "GBps": round(nbytes / (ms / max(cnt, 1) * 1e-3) / 1e9, 1)}
 
 
@@ -709,7 +740,7 @@ def run_profile_tc(args) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="stack", choices=["stack", "profile", "profile_tc", "q8_0", "prefill", "moe", "ternary", "all",
+    ap.add_argument("--workload", default="stack", choices=["stack", "profile", "profile_q8", "profile_tc", "q8_0", "prefill", "moe", "ternary", "all",
                                                                 "tp_prefill", "ep_moe", "multi"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -733,6 +764,9 @@ def main() -> None:
         return
     if args.workload == "profile_tc":
         print(json.dumps(run_profile_tc(args)), flush=True)
+        return
+    if args.workload == "profile_q8":
+        print(json.dumps(run_profile_q8(args)), flush=True)
         return
     if args.workload in ("tp_prefill", "ep_moe", "multi"):
         for line in run_multi(args):
