@@ -11,14 +11,17 @@
 // ulp. Results differ from the f64 reference over bf16-rounded operands by that
 // and by f32 accumulation.
 //
-// One persistent CTA per SM walks output tiles of 128 weight rows x 256 tokens in K slabs of 64.
-//   warp 0        copy-engine producer: 256 x 64 bf16 token tiles (128-byte swizzle) into a 5-stage
+// One persistent CTA per SM walks output tiles of 128 weight rows x TN tokens (TN = 256, or 128 for small
+// batches and short expert runs) in K slabs of 64.
+//   warp 0        copy-engine producer: TN x 64 bf16 token tiles (128-byte swizzle) into a 5-stage
 //                 shared-memory ring, and the packed K-quant blocks of the tile's 128 rows (one
 //                 256-weight unit = four slabs at a time) into a 2-stage ring
-//   warp 1        one thread issues tcgen05.mma (M=128 weight rows, N=256 tokens, K=16 per
-//                 instruction, bf16 x bf16 -> f32): the A operand is read from TENSOR memory, the B
-//                 operand through a shared-memory descriptor; the accumulator lives in 256 TMEM
-//                 columns; tcgen05.commit releases a ring stage and signals the epilogue
+//   warp 1        one thread issues tcgen05.mma (M=128 weight rows, N = the tile's tokens rounded up to
+//                 16, K=16 per instruction, bf16 x bf16 -> f32): the A operand is read from TENSOR
+//                 memory, the B operand through a shared-memory descriptor; the accumulator lives in
+//                 256 TMEM columns (one of 256 tokens, or two of 128 that alternate between tiles so the
+//                 epilogue of one tile runs under the MMAs of the next); tcgen05.commit releases a ring
+//                 stage and signals the epilogue
 //   warps 2..9    dequantise: two threads per weight row expand 64 weights of the current slab and
 //                 store them with tcgen05.st into the A ring in tensor memory (32 columns per
 //                 stage, next to the accumulator): the dequantised weights never touch shared
@@ -43,7 +46,10 @@ namespace fq {
 namespace {
 
 constexpr int BM = 128;        // weight rows per tile (UMMA M)
-constexpr int BN = 256;        // tokens per tile (UMMA N)
+// Tokens per tile (UMMA N) is a kernel parameter TN: 256 with one accumulator (dense prefill, long expert
+// runs) or 128 with two accumulators that alternate between tiles, so the epilogue of one tile runs under
+// the MMAs of the next (short expert runs, small batches). A ragged last tile multiplies only the tokens it
+// has, rounded up to 16: the instruction's N is a run-time field.
 constexpr int BK = 64;         // K elements per ring stage (128 bytes of bf16: one swizzle span)
 // One ring of K slabs: stage s holds the token tile in shared memory and the dequantised weight slab in
 // tensor memory (32 columns = 64 bf16 along K per lane). One "full" barrier per stage collects the copy
@@ -51,8 +57,7 @@ constexpr int BK = 64;         // K elements per ring stage (128 bytes of bf16: 
 // commit: the single issuing thread waits once and commits once per slab, which is what bounds its rate.
 constexpr int STAGES = 5;
 constexpr int RAW_STAGES = 2;  // ring of packed K-quant units (one unit = 256 weights of 128 rows = four K slabs)
-constexpr int A_BYTES = BM * BK * 2;   // 16 KB
-constexpr int B_BYTES = BN * BK * 2;   // 32 KB
+constexpr int kAccCols = 256;  // tensor-memory columns of the f32 accumulator(s): one of 256 tokens or two of 128
 // K-quant blocks are staged in shared memory by the copy engine (their 144/176 bytes are 16-byte
 // multiples); Q8_0's split rows are read by the dequantising threads themselves.
 template <int FMT>
@@ -67,7 +72,7 @@ constexpr int kThreads = (2 + kDequantWarps + kEpilogueWarps) * 32;  // 448
 constexpr unsigned kWaitLimit = 1u << 20;
 constexpr int TMEM_COLS = 512;  // columns 0..255: the f32 accumulator; from column 256: the A ring (STAGES x 32)
 constexpr int A_COLS = BK / 2;  // tensor-memory columns of one A slab: two bf16 per 32-bit column
-constexpr int A_COL0 = BN;
+constexpr int A_COL0 = kAccCols;
 
 struct TcArgs {
     DevWeights w;
@@ -87,13 +92,14 @@ struct TcArgs {
 struct TileRef {
     int mat, rt, tok0, ntok;
 };
+template <int TN>
 __device__ __forceinline__ TileRef tile_ref(const TcArgs& A, int tile, int row_tiles) {
     if (A.table) {
         const TcTile t = A.table[tile];
         return {t.mat, t.rt, t.tok0, t.ntok};
     }
     const int tt = tile / row_tiles;  // consecutive CTAs share the token tile (L2 reuse) and take different weight rows
-    return {A.mat, tile % row_tiles, tt * BN, min(BN, A.m - tt * BN)};
+    return {A.mat, tile % row_tiles, tt * TN, min(TN, A.m - tt * TN)};
 }
 
 // Diagnostic build only (-DFQ_TIMELINE): the MMA thread of CTA 0 stamps, for the first slabs of its first tile,
@@ -117,7 +123,7 @@ __device__ __forceinline__ unsigned long long tl_now() {
 #endif
 
 struct __align__(8) Barriers {
-    uint64_t full[STAGES], empty[STAGES], raw_full[RAW_STAGES], raw_empty[RAW_STAGES], tmem_full[1], tmem_empty[1];
+    uint64_t full[STAGES], empty[STAGES], raw_full[RAW_STAGES], raw_empty[RAW_STAGES], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -165,24 +171,18 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor, kind::f16: D = f32, A = B = bf16, both K-major, M = 128, N = 256.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
-        : "memory");
+// Instruction descriptor, kind::f16: D = f32, A = B = bf16, both K-major, M = 128, N = n_tokens (a multiple of 16, 16..256).
+__device__ __forceinline__ uint32_t umma_idesc(int n_tokens) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n_tokens >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
-// The same MMA with A read from tensor memory (lane = row, 32-bit column = two consecutive bf16 along K).
-__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t accumulate) {
+// One MMA with A read from tensor memory (lane = row, 32-bit column = two consecutive bf16 along K) and B
+// through a shared-memory descriptor.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -442,12 +442,14 @@ struct Raw<FQ_Q2_0> {
     }
 };
 
-template <int FMT>
+template <int FMT, int TN>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, const __grid_constant__ CUtensorMap tmap_tokens,
                                                               const __grid_constant__ CUtensorMap tmap_weights) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte aligned rings: [B stages][packed-weight stages][barriers]; the dequantised A slabs live in tensor memory
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int B_BYTES = TN * BK * 2;   // one token tile of a K slab: 32 KB or 16 KB
+    constexpr int NACC = kAccCols / TN;    // accumulators alternating between tiles
     uint8_t* sB = smem;
     uint8_t* sRaw = sB + STAGES * B_BYTES;
     Barriers* B = reinterpret_cast<Barriers*>(sRaw + RAW_STAGES * Staged<FMT>::raw_bytes);
@@ -456,7 +458,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = A.w.n, k = A.w.k, m = A.m;
     const int kslabs = k / BK, units = k >> 8;
-    const int row_tiles = (n + BM - 1) / BM, tok_tiles = (m + BN - 1) / BN;
+    const int row_tiles = (n + BM - 1) / BM, tok_tiles = (m + TN - 1) / TN;
     const int n_tiles = A.table ? *A.n_tiles_dev : row_tiles * tok_tiles;
 
     if (threadIdx.x == 0) {
@@ -468,8 +470,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             mbar_init(smem_u32(&B->raw_full[s]), 1);
             mbar_init(smem_u32(&B->raw_empty[s]), kDequantWarps * 32);
         }
-        mbar_init(smem_u32(&B->tmem_full[0]), 1);
-        mbar_init(smem_u32(&B->tmem_empty[0]), kEpilogueWarps * 32);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&B->tmem_full[a]), 1);
+            mbar_init(smem_u32(&B->tmem_empty[a]), kEpilogueWarps * 32);
+        }
         B->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -491,7 +495,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             int gb = 0, gu = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
-                const TileRef T = tile_ref(A, tile, row_tiles);
+                const TileRef T = tile_ref<TN>(A, tile, row_tiles);
                 for (int u = 0; u < units && ok; ++u) {
                     if (kStaged) {
                         const int rs = gu % RAW_STAGES;
@@ -546,9 +550,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         if (lane == 0) {
             int g = 0, t = 0;
             for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
-                // the epilogue of the previous tile must have drained the accumulator
-                const uint32_t acc = tmem;
-                if (!mbar_wait(smem_u32(&B->tmem_empty[0]), (t & 1) ^ 1, B, A.status)) break;
+                // the epilogue of the tile that used this accumulator before must have drained it
+                const int ai = t % NACC;
+                const uint32_t acc = tmem + (uint32_t)(ai * TN);
+                if (!mbar_wait(smem_u32(&B->tmem_empty[ai]), ((t / NACC) & 1) ^ 1, B, A.status)) break;
+                const uint32_t idesc = umma_idesc(min(TN, (tile_ref<TN>(A, tile, row_tiles).ntok + 15) & ~15));
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 bool ok = true;
                 for (int ks = 0; ks < kslabs; ++ks, ++g) {
@@ -564,13 +570,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                     const uint64_t db = umma_desc(smem_u32(sB + sb * B_BYTES));
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk)  // 16 elements along K per instruction: 8 columns of A, 32 bytes of B
-                        umma_bf16_ts(acc, ta + 8 * kk, db + 2 * kk, (ks | kk) ? 1u : 0u);
+                        umma_bf16_ts(acc, ta + 8 * kk, db + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
                     TL_STAMP(ks, 3);
                     umma_commit(smem_u32(&B->empty[sa]));  // the stage is free once these MMAs have read it
                     TL_STAMP(ks, 4);
                 }
                 if (!ok) break;
-                umma_commit(smem_u32(&B->tmem_full[0]));
+                umma_commit(smem_u32(&B->tmem_full[ai]));
             }
         }
     } else if (warp < 2 + kDequantWarps) {
@@ -584,6 +590,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         int ga = 0, gu = 0;
         bool ok = true;
         // one slab of this row goes to A stage (ga % STAGES) in tensor memory: lane r, 16 columns from h * 16
+        // (awaiting the store only after the next slab's expansion was measured slightly slower)
         auto publish = [&](const uint32_t (&v)[16]) -> bool {
             const int s = ga % STAGES;
             if (!mbar_wait(smem_u32(&B->empty[s]), ((ga / STAGES) & 1) ^ 1, B, A.status)) return false;
@@ -602,7 +609,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             return true;
         };
         for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
-            const TileRef T = tile_ref(A, tile, row_tiles);
+            const TileRef T = tile_ref<TN>(A, tile, row_tiles);
             if (kStaged) {
                 for (int u = 0; u < units && ok; ++u, ++gu) {
                     const int rs = gu % RAW_STAGES;
@@ -649,15 +656,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         // ---------------- epilogue: accumulator lane = weight row, column = token ----------------
         int t = 0;
         for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
-            const TileRef T = tile_ref(A, tile, row_tiles);
+            const TileRef T = tile_ref<TN>(A, tile, row_tiles);
             const int rt = T.rt;
-            if (!mbar_wait(smem_u32(&B->tmem_full[0]), t & 1, B, A.status)) break;
+            const int ai = t % NACC;
+            if (!mbar_wait(smem_u32(&B->tmem_full[ai]), (t / NACC) & 1, B, A.status)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int q = warp & 3;                       // TMEM lane quarter this warp may read
             const int out_row = rt * BM + q * 32 + lane;  // weight row = output column
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+#pragma unroll
+            for (int c0 = 0; c0 < TN; c0 += 32) {
+                if (c0 >= T.ntok) break;  // warp-uniform: columns past the tile's tokens were not multiplied
                 uint32_t acc[32];
-                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ai * TN + c0);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -677,7 +687,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(smem_u32(&B->tmem_empty[0]));
+            mbar_arrive(smem_u32(&B->tmem_empty[ai]));
         }
     }
 
@@ -719,17 +729,21 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int FMT>
-cudaError_t launch_tc(const TcArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap_w, int grid, cudaStream_t st) {
-    const size_t smem = (size_t)STAGES * B_BYTES + (size_t)RAW_STAGES * Staged<FMT>::raw_bytes + sizeof(Barriers) + 1024;
+template <int FMT, int TN>
+cudaError_t launch_tc_tn(const TcArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap_w, int grid, cudaStream_t st) {
+    const size_t smem = (size_t)STAGES * TN * BK * 2 + (size_t)RAW_STAGES * Staged<FMT>::raw_bytes + sizeof(Barriers) + 1024;
     static bool granted = false;
     if (!granted) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         granted = true;
     }
-    gemm_tc_kernel<FMT><<<grid, kThreads, smem, st>>>(a, tmap, tmap_w);
+    gemm_tc_kernel<FMT, TN><<<grid, kThreads, smem, st>>>(a, tmap, tmap_w);
     return cudaGetLastError();
+}
+template <int FMT>
+cudaError_t launch_tc(const TcArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap_w, int grid, int tile_tokens, cudaStream_t st) {
+    return tile_tokens == 128 ? launch_tc_tn<FMT, 128>(a, tmap, tmap_w, grid, st) : launch_tc_tn<FMT, 256>(a, tmap, tmap_w, grid, st);
 }
 
 #ifdef FQ_TIMELINE
@@ -746,16 +760,18 @@ bool tensor_path_serves(const DevWeights& w) {
 }
 
 // Launch over bf16 activation rows [rows][k]: dense tiles of matrix `mat` (table == nullptr) or a
-// device-built tile list (grouped MoE form; `max_tiles` bounds the list for the grid size).
+// device-built tile list (grouped MoE form; `max_tiles` bounds the list for the grid size, and
+// `tile_tokens`, 128 or 256, is the token width its entries were cut to).
 static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfloat16* abf, size_t rows, float* c_dev, size_t ldc,
-                          const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st) {
+                          const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st) {
+    const int BN = tile_tokens;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return fail(FQ_DECLINED_ARGS, "cuTensorMapEncodeTiled unavailable");
     CUtensorMap tmap;
     memset(&tmap, 0, sizeof tmap);
     const cuuint64_t dims[2] = {(cuuint64_t)w.k, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)w.k * 2};
-    const cuuint32_t box[2] = {BK, BN};
+    const cuuint32_t box[2] = {BK, (cuuint32_t)BN};
     const cuuint32_t estr[2] = {1, 1};
     if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(abf), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -782,21 +798,22 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
     const int grid = tiles < ctx->sm_count ? (tiles > 0 ? tiles : 1) : ctx->sm_count;
     cudaError_t e;
     switch (w.fmt) {
-        case FQ_Q4_K: e = launch_tc<FQ_Q4_K>(a, tmap, tmap_w, grid, st); break;
-        case FQ_Q5_K: e = launch_tc<FQ_Q5_K>(a, tmap, tmap_w, grid, st); break;
-        case FQ_TQ2_0: e = launch_tc<FQ_TQ2_0>(a, tmap, tmap_w, grid, st); break;
-        case FQ_TQ2_0_FOLDED: e = launch_tc<FQ_TQ2_0_FOLDED>(a, tmap, tmap_w, grid, st); break;
-        case FQ_Q2_0: e = launch_tc<FQ_Q2_0>(a, tmap, tmap_w, grid, st); break;
-        default: e = launch_tc<FQ_Q8_0>(a, tmap, tmap_w, grid, st); break;
+        case FQ_Q4_K: e = launch_tc<FQ_Q4_K>(a, tmap, tmap_w, grid, tile_tokens, st); break;
+        case FQ_Q5_K: e = launch_tc<FQ_Q5_K>(a, tmap, tmap_w, grid, tile_tokens, st); break;
+        case FQ_TQ2_0: e = launch_tc<FQ_TQ2_0>(a, tmap, tmap_w, grid, tile_tokens, st); break;
+        case FQ_TQ2_0_FOLDED: e = launch_tc<FQ_TQ2_0_FOLDED>(a, tmap, tmap_w, grid, tile_tokens, st); break;
+        case FQ_Q2_0: e = launch_tc<FQ_Q2_0>(a, tmap, tmap_w, grid, tile_tokens, st); break;
+        default: e = launch_tc<FQ_Q8_0>(a, tmap, tmap_w, grid, tile_tokens, st); break;
     }
     g_trace.launches++;
     return e == cudaSuccess ? FQ_OK : cuda_fail(e, "tensor-core GEMM launch");
 }
 
 int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, size_t rows, float* c_dev, size_t ldc,
-                            const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st) {
+                            const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st) {
+    if (tile_tokens != 128 && tile_tokens != 256) return fail(FQ_DECLINED_ARGS, "token tiles are 128 or 256 rows");
     if (!tensor_path_serves(w)) return fail(FQ_DECLINED_ARGS, "tensor-core path needs a served format with k %% 256 == 0");
-    return launch_tc_rows(ctx, w, 0, (const __nv_bfloat16*)a_bf16, rows, c_dev, ldc, table, n_tiles_dev, max_tiles, st);
+    return launch_tc_rows(ctx, w, 0, (const __nv_bfloat16*)a_bf16, rows, c_dev, ldc, table, n_tiles_dev, max_tiles, tile_tokens, st);
 }
 
 __global__ void add_f32_kernel(float* __restrict__ c, const float* __restrict__ t, size_t n) {
@@ -832,7 +849,8 @@ int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, 
     if (!abf) return fail(FQ_DECLINED_BUDGET, "bf16 activation scratch allocation failed");
     launch_f32_to_bf16(a_dev, abf, m * (size_t)w.k, st);
     g_trace.launches++;
-    const int rc = launch_tc_rows(ctx, w, mat, abf, m, c_dev, ldc, nullptr, nullptr, 0, st);
+    // up to 128 tokens: one tile column of 128 with alternating accumulators; above that 256-token tiles
+    const int rc = launch_tc_rows(ctx, w, mat, abf, m, c_dev, ldc, nullptr, nullptr, 0, m <= 128 ? 128 : 256, st);
     if (st != ctx->stream) cudaStreamSynchronize(st);
     dev_free(abf);
     return rc;

@@ -186,13 +186,16 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int rows, i
 int max_desc_for(int pairs, int n_expert, int group_rows);
 
 // ---- tensor-core form for prefill-sized batches ------------------------------------------------
-// Tile lists for the grouped tcgen05 GEMM, one CTA: per expert run, ceil(count/256) token tiles
-// times the row tiles of the gate/up product (rt_gu) and of the down product (rt_dn).
-constexpr int kTcTokens = 256;
-__global__ void tc_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, Shard shard, int rt_gu, int rt_dn,
+// Tile lists for the grouped tcgen05 GEMM, one CTA: per expert run, ceil(count/tile_tokens) token tiles
+// times the row tiles of the gate/up product (rt_gu) and of the down product (rt_dn), in expert order
+// (the row tiles of one token tile are neighbours, so concurrent CTAs share its token rows in L2).
+// Shared memory: 3 * n_expert ints (count, first sorted row, first token tile of each expert).
+__global__ void tc_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, Shard shard, int rt_gu, int rt_dn, int tile_tokens,
                                TcTile* __restrict__ t_gu, int* __restrict__ n_gu, TcTile* __restrict__ t_dn, int* __restrict__ n_dn) {
     extern __shared__ int sh[];
     int* count = sh;
+    int* first_row = sh + n_expert;
+    int* first_tile = sh + 2 * n_expert;
     for (int e = threadIdx.x; e < n_expert; e += blockDim.x) count[e] = 0;
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
@@ -201,18 +204,26 @@ __global__ void tc_plan_kernel(const int* __restrict__ selected, int pairs, int 
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        int off = 0, a = 0, b = 0;
+        int off = 0, tiles = 0;
         for (int e = 0; e < n_expert; ++e) {
-            const int c = count[e];
-            for (int t0 = 0; t0 < c; t0 += kTcTokens) {
-                const int nt = min(kTcTokens, c - t0);
-                for (int rt = 0; rt < rt_gu; ++rt) t_gu[a++] = {e, rt, off + t0, nt};
-                for (int rt = 0; rt < rt_dn; ++rt) t_dn[b++] = {e, rt, off + t0, nt};
-            }
-            off += c;
+            first_row[e] = off;
+            first_tile[e] = tiles;
+            off += count[e];
+            tiles += (count[e] + tile_tokens - 1) / tile_tokens;
         }
-        *n_gu = a;
-        *n_dn = b;
+        *n_gu = tiles * rt_gu;
+        *n_dn = tiles * rt_dn;
+    }
+    __syncthreads();
+    // one warp per expert; the entries of a token tile are written by consecutive lanes
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int e = warp; e < n_expert; e += warps) {
+        const int c = count[e], row0 = first_row[e], tile0 = first_tile[e];
+        for (int t0 = 0, tt = 0; t0 < c; t0 += tile_tokens, ++tt) {
+            const int nt = min(tile_tokens, c - t0);
+            for (int rt = lane; rt < rt_gu; rt += 32) t_gu[(size_t)(tile0 + tt) * rt_gu + rt] = {e, rt, row0 + t0, nt};
+            for (int rt = lane; rt < rt_dn; rt += 32) t_dn[(size_t)(tile0 + tt) * rt_dn + rt] = {e, rt, row0 + t0, nt};
+        }
     }
 }
 
@@ -250,7 +261,10 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
     const int hidden = gate.k, out_pe = gate.n, n_expert = gate.n_mats;
     const int pairs = seq * top_k;
     const int rt_gu = (out_pe + 127) / 128, rt_dn = (hidden + 127) / 128;
-    const int tok_tiles = (pairs < n_expert ? pairs : n_expert) + pairs / kTcTokens;
+    // expert runs of up to 128 rows on average: 128-token tiles (two alternating accumulators hide the
+    // epilogue of these short tiles); longer runs: 256-token tiles
+    const int tile_tokens = pairs <= 128 * n_expert ? 128 : 256;
+    const int tok_tiles = (pairs < n_expert ? pairs : n_expert) + pairs / tile_tokens;
     const int max_gu = rt_gu * tok_tiles, max_dn = rt_dn * tok_tiles;
     size_t off = 0;
     auto take = [&](size_t bytes) {
@@ -273,18 +287,18 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
     int rc = FQ_OK;
     do {
         route_plan_kernel<<<1, 1024, sizeof(int) * 3 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, kGroupRows, order, inv, (GroupDesc*)(s + o_desc), cnt, cnt + 3);
-        tc_plan_kernel<<<1, 1024, sizeof(int) * n_expert, st>>>(selected_dev, pairs, n_expert, shard, rt_gu, rt_dn, (TcTile*)(s + o_tgu), cnt + 1,
+        tc_plan_kernel<<<1, 1024, sizeof(int) * 3 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, rt_gu, rt_dn, tile_tokens, (TcTile*)(s + o_tgu), cnt + 1,
                                                                  (TcTile*)(s + o_tdn), cnt + 2);
         int blocks = (int)(((size_t)pairs * hidden / 4 + 255) / 256);
         gather_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>(x_dev, order, top_k, cnt + 3, hidden, (__nv_bfloat16*)(s + o_xb));
         if ((e = cudaGetLastError()) != cudaSuccess) break;
-        if ((rc = gemm_tensor_grouped_dev(ctx, gate, s + o_xb, pairs, (float*)(s + o_gate), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, st)) != FQ_OK) break;
-        if ((rc = gemm_tensor_grouped_dev(ctx, up, s + o_xb, pairs, (float*)(s + o_up), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, st)) != FQ_OK) break;
+        if ((rc = gemm_tensor_grouped_dev(ctx, gate, s + o_xb, pairs, (float*)(s + o_gate), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, tile_tokens, st)) != FQ_OK) break;
+        if ((rc = gemm_tensor_grouped_dev(ctx, up, s + o_xb, pairs, (float*)(s + o_up), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, tile_tokens, st)) != FQ_OK) break;
         const size_t ng = (size_t)pairs * out_pe;
         blocks = (int)((ng + 255) / 256);
         swiglu_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>((const float*)(s + o_gate), (const float*)(s + o_up), cnt + 3, out_pe, (__nv_bfloat16*)(s + o_gb));
         if ((e = cudaGetLastError()) != cudaSuccess) break;
-        if ((rc = gemm_tensor_grouped_dev(ctx, down, s + o_gb, pairs, (float*)(s + o_down), hidden, (const TcTile*)(s + o_tdn), cnt + 2, max_dn, st)) != FQ_OK) break;
+        if ((rc = gemm_tensor_grouped_dev(ctx, down, s + o_gb, pairs, (float*)(s + o_down), hidden, (const TcTile*)(s + o_tdn), cnt + 2, max_dn, tile_tokens, st)) != FQ_OK) break;
         const size_t total = (size_t)seq * hidden;
         blocks = (int)((total + 255) / 256);
         combine_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>((const float*)(s + o_down), weights_dev, inv, seq, hidden, top_k, out_dev);

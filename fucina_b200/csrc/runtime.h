@@ -58,6 +58,6 @@ int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, 
 struct TcTile;
 bool tensor_path_serves(const DevWeights& w);
 int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, size_t rows, float* c_dev, size_t ldc,
-                            const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st);
+                            const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st);
 
 }  // namespace fq
