@@ -14,8 +14,10 @@
 // One persistent CTA per SM walks output tiles of 128 weight rows x TN tokens (TN = 256, or 128 for small
 // batches and short expert runs) in K slabs of 64.
 //   warp 0        copy-engine producer: TN x 64 bf16 token tiles (128-byte swizzle) into a 5-stage
-//                 shared-memory ring, and the packed K-quant blocks of the tile's 128 rows (one
-//                 256-weight unit = four slabs at a time) into a 2-stage ring
+//                 shared-memory ring
+//   warp 14       copy-engine producer of the packed K-quant blocks of the tile's 128 rows (one
+//                 256-weight unit = four slabs at a time) into a ring of its own (2 or 4 units), so
+//                 weight fetches are not held back by the token ring's pace
 //   warp 1        one thread issues tcgen05.mma (M=128 weight rows, N = the tile's tokens rounded up to
 //                 16, K=16 per instruction, bf16 x bf16 -> f32): the A operand is read from TENSOR
 //                 memory, the B operand through a shared-memory descriptor; the accumulator lives in
@@ -45,6 +47,9 @@ namespace fq {
 
 namespace {
 
+#ifndef FQ_TC_DEQUANT_WARPS
+#define FQ_TC_DEQUANT_WARPS 8  // 16 measured 4 % slower on dense and expert shapes alike: expansion is not the limit
+#endif
 constexpr int BM = 128;        // weight rows per tile (UMMA M)
 // Tokens per tile (UMMA N) is a kernel parameter TN: 256 with one accumulator (dense prefill, long expert
 // runs) or 128 with two accumulators that alternate between tiles, so the epilogue of one tile runs under
@@ -56,7 +61,13 @@ constexpr int BK = 64;         // K elements per ring stage (128 bytes of bf16: 
 // engine's bytes and the 256 dequantising threads, one "empty" barrier is signalled by the MMAs'
 // commit: the single issuing thread waits once and commits once per slab, which is what bounds its rate.
 constexpr int STAGES = 5;
-constexpr int RAW_STAGES = 2;  // ring of packed K-quant units (one unit = 256 weights of 128 rows = four K slabs)
+// Ring of packed K-quant units (one unit = 256 weights of 128 rows = four K slabs), filled by a copy-engine
+// producer of its own so that weight fetches run ahead of the token ring: as deep as shared memory allows.
+constexpr int kMaxRawStages = 4;
+template <int TN>
+struct RawRing {
+    static constexpr int stages = TN == 128 ? 4 : 2;
+};
 constexpr int kAccCols = 256;  // tensor-memory columns of the f32 accumulator(s): one of 256 tokens or two of 128
 // K-quant blocks are staged in shared memory by the copy engine (their 144/176 bytes are 16-byte
 // multiples); Q8_0's split rows are read by the dequantising threads themselves.
@@ -66,9 +77,15 @@ struct Staged {
     static constexpr int unit_bytes = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 0;
     static constexpr int raw_bytes = BM * unit_bytes;
 };
-constexpr int kDequantWarps = 8;
+constexpr int kRawWarp = 2 + FQ_TC_DEQUANT_WARPS + 4;  // the warp after the epilogue warps: its lane 0 fetches packed weights
+// Dequantising warps: a warp reaches one tensor-memory lane quarter (32 weight rows); eight warps cover the
+// four quarters x the two 32-weight halves of a slab, and each further group of eight takes every
+// kSlabSplit-th slab, so more slabs are expanded at once.
+constexpr int kDequantWarps = FQ_TC_DEQUANT_WARPS;
+constexpr int kSlabSplit = kDequantWarps / 8;
+static_assert(kDequantWarps == 8 || kDequantWarps == 16, "8 or 16 dequantising warps");
 constexpr int kEpilogueWarps = 4;  // one per tensor-memory lane quarter (eight, splitting the columns, measured no faster)
-constexpr int kThreads = (2 + kDequantWarps + kEpilogueWarps) * 32;  // 448
+constexpr int kThreads = (3 + kDequantWarps + kEpilogueWarps) * 32;
 constexpr unsigned kWaitLimit = 1u << 20;
 constexpr int TMEM_COLS = 512;  // columns 0..255: the f32 accumulator; from column 256: the A ring (STAGES x 32)
 constexpr int A_COLS = BK / 2;  // tensor-memory columns of one A slab: two bf16 per 32-bit column
@@ -123,7 +140,7 @@ __device__ __forceinline__ unsigned long long tl_now() {
 #endif
 
 struct __align__(8) Barriers {
-    uint64_t full[STAGES], empty[STAGES], raw_full[RAW_STAGES], raw_empty[RAW_STAGES], tmem_full[2], tmem_empty[2];
+    uint64_t full[STAGES], empty[STAGES], raw_full[kMaxRawStages], raw_empty[kMaxRawStages], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -450,6 +467,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int B_BYTES = TN * BK * 2;   // one token tile of a K slab: 32 KB or 16 KB
     constexpr int NACC = kAccCols / TN;    // accumulators alternating between tiles
+    constexpr int RAW_STAGES = RawRing<TN>::stages;
     uint8_t* sB = smem;
     uint8_t* sRaw = sB + STAGES * B_BYTES;
     Barriers* B = reinterpret_cast<Barriers*>(sRaw + RAW_STAGES * Staged<FMT>::raw_bytes);
@@ -463,16 +481,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&B->full[s]), kDequantWarps * 32 + 1);  // the dequantising threads + the producer's expect_tx arrival
+            mbar_init(smem_u32(&B->full[s]), 8 + 1);  // one arrival per warp that expands the slab + the producer's expect_tx arrival
             mbar_init(smem_u32(&B->empty[s]), 1);
         }
-        for (int s = 0; s < RAW_STAGES; ++s) {
+        for (int s = 0; s < kMaxRawStages; ++s) {
             mbar_init(smem_u32(&B->raw_full[s]), 1);
-            mbar_init(smem_u32(&B->raw_empty[s]), kDequantWarps * 32);
+            mbar_init(smem_u32(&B->raw_empty[s]), kDequantWarps);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&B->tmem_full[a]), 1);
-            mbar_init(smem_u32(&B->tmem_empty[a]), kEpilogueWarps * 32);
+            mbar_init(smem_u32(&B->tmem_empty[a]), kEpilogueWarps);
         }
         B->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -489,41 +507,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
     const uint32_t tmem = B->tmem_base;
 
     if (warp == 0) {
-        // ---------------- copy-engine producer: packed weight units (K-quants) and token tiles ----------------
+        // ---------------- copy-engine producer: token tiles ----------------
         if (lane == 0) {
-            constexpr int ub = Staged<FMT>::unit_bytes;
-            int gb = 0, gu = 0;
+            int gb = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
                 const TileRef T = tile_ref<TN>(A, tile, row_tiles);
                 for (int u = 0; u < units && ok; ++u) {
-                    if (kStaged) {
-                        const int rs = gu % RAW_STAGES;
-                        if (!mbar_wait(smem_u32(&B->raw_empty[rs]), ((gu / RAW_STAGES) & 1) ^ 1, B, A.status)) {
-                            ok = false;
-                            break;
-                        }
-                        const uint32_t bar = smem_u32(&B->raw_full[rs]);
-                        const uint32_t dst = smem_u32(sRaw + rs * Staged<FMT>::raw_bytes);
-                        if (A.w.tile_rows) {
-                            // tile-major storage: unit u of 32 consecutive rows is one contiguous run
-                            const int n_store = (n + 31) >> 5;
-                            const int valid = min(BM / 32, n_store - T.rt * (BM / 32));
-                            mbar_arrive_expect_tx(bar, (uint32_t)(valid * 32 * ub));
-                            const uint8_t* wbase = A.w.base + (size_t)T.mat * A.w.mat_stride;
-                            for (int j = 0; j < valid; ++j)
-                                bulk_load(dst + j * 32 * ub, wbase + (size_t)(T.rt * (BM / 32) + j) * ((size_t)32 * A.w.row_stride) + (size_t)u * 32 * ub,
-                                          32 * ub, bar);
-                        } else {
-                            // row-major storage: a box of 128 rows x one unit; rows past the end of the tensor arrive as zeros
-                            mbar_arrive_expect_tx(bar, (uint32_t)(BM * ub));
-                            asm volatile(
-                                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-                                "l"(&tmap_weights), "r"(u * ub), "r"(T.mat * n + T.rt * BM), "r"(bar)
-                                : "memory");
-                        }
-                        ++gu;
-                    }
                     for (int p = 0; p < 4; ++p, ++gb) {
                         const int s = gb % STAGES;
                         if (!mbar_wait(smem_u32(&B->empty[s]), ((gb / STAGES) & 1) ^ 1, B, A.status)) {
@@ -584,14 +574,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         // a warp reaches the tensor-memory lanes 32 * (warp % 4) .. +31 only: that fixes its rows; the two warps
         // of a lane quarter take the two 32-weight halves of the 64-element slab
         const int r = 32 * (warp & 3) + lane;  // weight row inside the tile = tensor-memory lane
-        const int h = (warp - 2) >> 2;
+        const int h = ((warp - 2) >> 2) & 1;
+        const int par = (warp - 2) >> 3;  // this warp expands the slabs ks with ks % kSlabSplit == par
         constexpr int ub = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 256;
         const size_t ustride = unit_stride(A.w, ub);
-        int ga = 0, gu = 0;
+        int gbase = 0, gu = 0;  // slabs of the tiles before this one; units consumed
         bool ok = true;
         // one slab of this row goes to A stage (ga % STAGES) in tensor memory: lane r, 16 columns from h * 16
         // (awaiting the store only after the next slab's expansion was measured slightly slower)
-        auto publish = [&](const uint32_t (&v)[16]) -> bool {
+        auto publish = [&](const uint32_t (&v)[16], int ga) -> bool {
             const int s = ga % STAGES;
             if (!mbar_wait(smem_u32(&B->empty[s]), ((ga / STAGES) & 1) ^ 1, B, A.status)) return false;
             __syncwarp();  // the store below is a warp-wide (.aligned) instruction
@@ -604,8 +595,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 : "memory");
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(smem_u32(&B->full[s]));
-            ++ga;
+            __syncwarp();  // every lane's store has completed: one arrival for the warp (arrivals on one barrier serialise)
+            if (lane == 0) mbar_arrive(smem_u32(&B->full[s]));
             return true;
         };
         for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
@@ -623,7 +614,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                     Raw<FMT> raw;
                     raw.load_header(blk);
 #pragma unroll
-                    for (int p = 0; p < 4; ++p) {
+                    for (int p0 = 0; p0 < 4; p0 += kSlabSplit) {
+                        const int p = p0 + par;
                         raw.load_slab(blk, p);
                         uint32_t v[16];
                         if (A.diag == 2) {
@@ -632,23 +624,62 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                         } else {
                             raw.expand(p, h, v);
                         }
-                        if (!(ok = publish(v))) break;
+                        if (!(ok = publish(v, gbase + 4 * u + p))) break;
                     }
                     // the loads above have returned (their values went into the stores): the unit may be overwritten
-                    mbar_arrive(smem_u32(&B->raw_empty[rs]));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&B->raw_empty[rs]));
                 }
             } else {
                 const uint8_t* wbase = A.w.base + (size_t)T.mat * A.w.mat_stride;
                 const int row = min(T.rt * BM + r, n - 1);
                 const uint8_t* unit0 = row_unit0(A.w, wbase, row, ub);
                 Raw<FMT> next;
-                next.load(A.w, unit0, ustride, 0, h);
-                for (int ks = 0; ks < kslabs; ++ks) {
+                next.load(A.w, unit0, ustride, par, h);
+                for (int ks = par; ks < kslabs; ks += kSlabSplit) {
                     const Raw<FMT> cur = next;
-                    if (ks + 1 < kslabs) next.load(A.w, unit0, ustride, ks + 1, h);  // one slab ahead: the loads fly while this slab is expanded
+                    if (ks + kSlabSplit < kslabs) next.load(A.w, unit0, ustride, ks + kSlabSplit, h);  // one slab ahead: the loads fly while this slab is expanded
                     uint32_t v[16];
                     cur.expand(ks, h, v);
-                    if (!(ok = publish(v))) break;
+                    if (!(ok = publish(v, gbase + ks))) break;
+                }
+            }
+            gbase += kslabs;
+        }
+    } else if (warp == kRawWarp) {
+        // ---------------- copy-engine producer: packed weight units (K-quants) ----------------
+        // its own thread, so the weight ring runs ahead of the token ring by as many units as it holds
+        if (kStaged && lane == 0) {
+            constexpr int ub = Staged<FMT>::unit_bytes;
+            int gu = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
+                const TileRef T = tile_ref<TN>(A, tile, row_tiles);
+                for (int u = 0; u < units; ++u, ++gu) {
+                    const int rs = gu % RAW_STAGES;
+                    if (!mbar_wait(smem_u32(&B->raw_empty[rs]), ((gu / RAW_STAGES) & 1) ^ 1, B, A.status)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = smem_u32(&B->raw_full[rs]);
+                    const uint32_t dst = smem_u32(sRaw + rs * Staged<FMT>::raw_bytes);
+                    if (A.w.tile_rows) {
+                        // tile-major storage: unit u of 32 consecutive rows is one contiguous run
+                        const int n_store = (n + 31) >> 5;
+                        const int valid = min(BM / 32, n_store - T.rt * (BM / 32));
+                        mbar_arrive_expect_tx(bar, (uint32_t)(valid * 32 * ub));
+                        const uint8_t* wbase = A.w.base + (size_t)T.mat * A.w.mat_stride;
+                        for (int j = 0; j < valid; ++j)
+                            bulk_load(dst + j * 32 * ub, wbase + (size_t)(T.rt * (BM / 32) + j) * ((size_t)32 * A.w.row_stride) + (size_t)u * 32 * ub,
+                                      32 * ub, bar);
+                    } else {
+                        // row-major storage: a box of 128 rows x one unit; rows past the end of the tensor arrive as zeros
+                        mbar_arrive_expect_tx(bar, (uint32_t)(BM * ub));
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                            "l"(&tmap_weights), "r"(u * ub), "r"(T.mat * n + T.rt * BM), "r"(bar)
+                            : "memory");
+                    }
                 }
             }
         }
@@ -687,7 +718,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(smem_u32(&B->tmem_empty[ai]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&B->tmem_empty[ai]));
         }
     }
 
@@ -731,7 +763,7 @@ EncodeTiledFn encode_fn() {
 
 template <int FMT, int TN>
 cudaError_t launch_tc_tn(const TcArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap_w, int grid, cudaStream_t st) {
-    const size_t smem = (size_t)STAGES * TN * BK * 2 + (size_t)RAW_STAGES * Staged<FMT>::raw_bytes + sizeof(Barriers) + 1024;
+    const size_t smem = (size_t)STAGES * TN * BK * 2 + (size_t)RawRing<TN>::stages * Staged<FMT>::raw_bytes + sizeof(Barriers) + 1024;
     static bool granted = false;
     if (!granted) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
