@@ -64,6 +64,8 @@ constexpr int STAGES = 5;
 // Ring of packed K-quant units (one unit = 256 weights of 128 rows = four K slabs), filled by a copy-engine
 // producer of its own so that weight fetches run ahead of the token ring: as deep as shared memory allows.
 constexpr int kMaxRawStages = 4;
+constexpr int kGatedRawStages = 3;        // the gated form gives 64 KB of shared memory to the parked gate values
+constexpr int kGateBytes = 128 * BM * 4;  // 128 tokens x 128 rows of f32
 template <int TN>
 struct RawRing {
     static constexpr int stages = TN == 128 ? 4 : 2;
@@ -103,6 +105,10 @@ struct TcArgs {
     const TcTile* table;
     const int* n_tiles_dev;
     int diag;  // diagnosis only (results are garbage): 1 = token tiles are not fetched, 2 = weights are not expanded
+    // gated form (MoE gate/up pair, 128-token tiles): every tile multiplies the same rows of `w` (gate, first
+    // accumulator) and `w2` (up, second accumulator); the epilogue writes bf16(up * silu(gate)) to g_out
+    DevWeights w2;
+    __nv_bfloat16* g_out;
 };
 
 // One output tile: weight rows [rt*128, +128) of matrix `mat` times activation rows [tok0, tok0+ntok).
@@ -133,8 +139,18 @@ __device__ __forceinline__ unsigned long long tl_now() {
     do {                                                                                              \
         if (blockIdx.x == 0 && t == 0 && (slab) < kTlSlabs) g_tc_timeline[(slab) * 5 + (what)] = tl_now(); \
     } while (0)
+// the first dequantising warp of CTA 0 stamps, for the slabs of its third tile: unit ready, slab loaded from
+// shared memory, expanded, ring stage free, stored, barrier signalled
+__device__ unsigned long long g_tc_timeline_dq[kTlSlabs * 6];
+#define DQ_STAMP(slab, what)                                                                                             \
+    do {                                                                                                                 \
+        if (blockIdx.x == 0 && dq_tile == 2 && warp == 2 && lane == 0 && (slab) < kTlSlabs) g_tc_timeline_dq[(slab) * 6 + (what)] = tl_now(); \
+    } while (0)
 #else
 #define TL_STAMP(slab, what) \
+    do {                     \
+    } while (0)
+#define DQ_STAMP(slab, what) \
     do {                     \
     } while (0)
 #endif
@@ -204,6 +220,20 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 consecutive 32-bit columns of this warp's tensor-memory lanes (asynchronous: tcgen05.wait::ld follows)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&acc)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]), "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7]),
+          "=r"(acc[8]), "=r"(acc[9]), "=r"(acc[10]), "=r"(acc[11]), "=r"(acc[12]), "=r"(acc[13]), "=r"(acc[14]), "=r"(acc[15]),
+          "=r"(acc[16]), "=r"(acc[17]), "=r"(acc[18]), "=r"(acc[19]), "=r"(acc[20]), "=r"(acc[21]), "=r"(acc[22]), "=r"(acc[23]),
+          "=r"(acc[24]), "=r"(acc[25]), "=r"(acc[26]), "=r"(acc[27]), "=r"(acc[28]), "=r"(acc[29]), "=r"(acc[30]), "=r"(acc[31])
+        : "r"(taddr)
+        : "memory");
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -459,18 +489,23 @@ struct Raw<FQ_Q2_0> {
     }
 };
 
-template <int FMT, int TN>
+template <int FMT, int TN, bool GATED>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, const __grid_constant__ CUtensorMap tmap_tokens,
-                                                              const __grid_constant__ CUtensorMap tmap_weights) {
+                                                              const __grid_constant__ CUtensorMap tmap_weights,
+                                                              const __grid_constant__ CUtensorMap tmap_weights2) {
+    static_assert(!GATED || TN == 128, "the gated form needs both accumulators of one tile");
+    constexpr int PASSES = GATED ? 2 : 1;  // passes over K per tile: gate weights, then up weights
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte aligned rings: [B stages][packed-weight stages][barriers]; the dequantised A slabs live in tensor memory
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int B_BYTES = TN * BK * 2;   // one token tile of a K slab: 32 KB or 16 KB
     constexpr int NACC = kAccCols / TN;    // accumulators alternating between tiles
-    constexpr int RAW_STAGES = RawRing<TN>::stages;
+    constexpr int RAW_STAGES = GATED ? kGatedRawStages : RawRing<TN>::stages;
     uint8_t* sB = smem;
     uint8_t* sRaw = sB + STAGES * B_BYTES;
-    Barriers* B = reinterpret_cast<Barriers*>(sRaw + RAW_STAGES * Staged<FMT>::raw_bytes);
+    // gated form: f32 gate * sigmoid(gate) of the tile, [token][row], parked between the two epilogues of a tile
+    float* sG = reinterpret_cast<float*>(sRaw + RAW_STAGES * Staged<FMT>::raw_bytes);
+    Barriers* B = reinterpret_cast<Barriers*>(reinterpret_cast<uint8_t*>(sG) + (GATED ? kGateBytes : 0));
     static_assert(A_COL0 + STAGES * A_COLS <= TMEM_COLS, "A ring does not fit the tensor memory");
     constexpr bool kStaged = Staged<FMT>::on;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -513,7 +548,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
                 const TileRef T = tile_ref<TN>(A, tile, row_tiles);
-                for (int u = 0; u < units && ok; ++u) {
+                for (int u = 0; u < PASSES * units && ok; ++u) {
                     for (int p = 0; p < 4; ++p, ++gb) {
                         const int s = gb % STAGES;
                         if (!mbar_wait(smem_u32(&B->empty[s]), ((gb / STAGES) & 1) ^ 1, B, A.status)) {
@@ -529,7 +564,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                         asm volatile(
                             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                                 smem_u32(sB + s * B_BYTES)),
-                            "l"(&tmap_tokens), "r"((u * 4 + p) * BK), "r"(T.tok0), "r"(bar)
+                            "l"(&tmap_tokens), "r"(((u % units) * 4 + p) * BK), "r"(T.tok0), "r"(bar)
                             : "memory");
                     }
                 }
@@ -541,12 +576,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             int g = 0, t = 0;
             for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
                 // the epilogue of the tile that used this accumulator before must have drained it
+                // (gated form: the gate pass of a tile fills the first accumulator, the up pass the second)
                 const int ai = t % NACC;
-                const uint32_t acc = tmem + (uint32_t)(ai * TN);
-                if (!mbar_wait(smem_u32(&B->tmem_empty[ai]), ((t / NACC) & 1) ^ 1, B, A.status)) break;
+                if (!GATED && !mbar_wait(smem_u32(&B->tmem_empty[ai]), ((t / NACC) & 1) ^ 1, B, A.status)) break;
                 const uint32_t idesc = umma_idesc(min(TN, (tile_ref<TN>(A, tile, row_tiles).ntok + 15) & ~15));
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 bool ok = true;
+                for (int ps = 0; ps < PASSES && ok; ++ps) {
+                const int aj = GATED ? ps : ai;
+                if (GATED && !mbar_wait(smem_u32(&B->tmem_empty[aj]), (t & 1) ^ 1, B, A.status)) {
+                    ok = false;
+                    break;
+                }
+                if (GATED) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem + (uint32_t)(aj * TN);
                 for (int ks = 0; ks < kslabs; ++ks, ++g) {
                     const int sa = g % STAGES, sb = sa;
                     TL_STAMP(ks, 0);
@@ -565,8 +608,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                     umma_commit(smem_u32(&B->empty[sa]));  // the stage is free once these MMAs have read it
                     TL_STAMP(ks, 4);
                 }
+                if (ok) umma_commit(smem_u32(&B->tmem_full[aj]));
+                }
                 if (!ok) break;
-                umma_commit(smem_u32(&B->tmem_full[ai]));
             }
         }
     } else if (warp < 2 + kDequantWarps) {
@@ -579,12 +623,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         constexpr int ub = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 256;
         const size_t ustride = unit_stride(A.w, ub);
         int gbase = 0, gu = 0;  // slabs of the tiles before this one; units consumed
+        int dq_tile = 0;        // tiles this CTA has started (diagnostic stamps only)
         bool ok = true;
         // one slab of this row goes to A stage (ga % STAGES) in tensor memory: lane r, 16 columns from h * 16
         // (awaiting the store only after the next slab's expansion was measured slightly slower)
         auto publish = [&](const uint32_t (&v)[16], int ga) -> bool {
             const int s = ga % STAGES;
             if (!mbar_wait(smem_u32(&B->empty[s]), ((ga / STAGES) & 1) ^ 1, B, A.status)) return false;
+            DQ_STAMP(ga - gbase, 3);
             __syncwarp();  // the store below is a warp-wide (.aligned) instruction
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(A_COL0 + s * A_COLS + h * 16);
@@ -595,12 +641,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 : "memory");
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            DQ_STAMP(ga - gbase, 4);
             __syncwarp();  // every lane's store has completed: one arrival for the warp (arrivals on one barrier serialise)
             if (lane == 0) mbar_arrive(smem_u32(&B->full[s]));
+            DQ_STAMP(ga - gbase, 5);
             return true;
         };
         for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
             const TileRef T = tile_ref<TN>(A, tile, row_tiles);
+            for (int ps = 0; ps < PASSES && ok; ++ps) {
+            const DevWeights& W = (GATED && ps) ? A.w2 : A.w;
             if (kStaged) {
                 for (int u = 0; u < units && ok; ++u, ++gu) {
                     const int rs = gu % RAW_STAGES;
@@ -616,7 +666,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
 #pragma unroll
                     for (int p0 = 0; p0 < 4; p0 += kSlabSplit) {
                         const int p = p0 + par;
+                        DQ_STAMP(4 * u + p, 0);
                         raw.load_slab(blk, p);
+                        DQ_STAMP(4 * u + p, 1);
                         uint32_t v[16];
                         if (A.diag == 2) {
 #pragma unroll
@@ -624,6 +676,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                         } else {
                             raw.expand(p, h, v);
                         }
+                        DQ_STAMP(4 * u + p, 2);
                         if (!(ok = publish(v, gbase + 4 * u + p))) break;
                     }
                     // the loads above have returned (their values went into the stores): the unit may be overwritten
@@ -631,20 +684,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                     if (lane == 0) mbar_arrive(smem_u32(&B->raw_empty[rs]));
                 }
             } else {
-                const uint8_t* wbase = A.w.base + (size_t)T.mat * A.w.mat_stride;
+                const uint8_t* wbase = W.base + (size_t)T.mat * W.mat_stride;
                 const int row = min(T.rt * BM + r, n - 1);
-                const uint8_t* unit0 = row_unit0(A.w, wbase, row, ub);
+                const uint8_t* unit0 = row_unit0(W, wbase, row, ub);
                 Raw<FMT> next;
-                next.load(A.w, unit0, ustride, par, h);
+                next.load(W, unit0, ustride, par, h);
                 for (int ks = par; ks < kslabs; ks += kSlabSplit) {
                     const Raw<FMT> cur = next;
-                    if (ks + kSlabSplit < kslabs) next.load(A.w, unit0, ustride, ks + kSlabSplit, h);  // one slab ahead: the loads fly while this slab is expanded
+                    if (ks + kSlabSplit < kslabs) next.load(W, unit0, ustride, ks + kSlabSplit, h);  // one slab ahead: the loads fly while this slab is expanded
                     uint32_t v[16];
                     cur.expand(ks, h, v);
                     if (!(ok = publish(v, gbase + ks))) break;
                 }
             }
             gbase += kslabs;
+            }
+            ++dq_tile;
         }
     } else if (warp == kRawWarp) {
         // ---------------- copy-engine producer: packed weight units (K-quants) ----------------
@@ -655,6 +710,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
                 const TileRef T = tile_ref<TN>(A, tile, row_tiles);
+                for (int ps = 0; ps < PASSES && ok; ++ps) {
+                const DevWeights& W = (GATED && ps) ? A.w2 : A.w;
+                const CUtensorMap* tmw = (GATED && ps) ? &tmap_weights2 : &tmap_weights;
                 for (int u = 0; u < units; ++u, ++gu) {
                     const int rs = gu % RAW_STAGES;
                     if (!mbar_wait(smem_u32(&B->raw_empty[rs]), ((gu / RAW_STAGES) & 1) ^ 1, B, A.status)) {
@@ -663,23 +721,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                     }
                     const uint32_t bar = smem_u32(&B->raw_full[rs]);
                     const uint32_t dst = smem_u32(sRaw + rs * Staged<FMT>::raw_bytes);
-                    if (A.w.tile_rows) {
+                    if (W.tile_rows) {
                         // tile-major storage: unit u of 32 consecutive rows is one contiguous run
                         const int n_store = (n + 31) >> 5;
                         const int valid = min(BM / 32, n_store - T.rt * (BM / 32));
                         mbar_arrive_expect_tx(bar, (uint32_t)(valid * 32 * ub));
-                        const uint8_t* wbase = A.w.base + (size_t)T.mat * A.w.mat_stride;
+                        const uint8_t* wbase = W.base + (size_t)T.mat * W.mat_stride;
                         for (int j = 0; j < valid; ++j)
-                            bulk_load(dst + j * 32 * ub, wbase + (size_t)(T.rt * (BM / 32) + j) * ((size_t)32 * A.w.row_stride) + (size_t)u * 32 * ub,
+                            bulk_load(dst + j * 32 * ub, wbase + (size_t)(T.rt * (BM / 32) + j) * ((size_t)32 * W.row_stride) + (size_t)u * 32 * ub,
                                       32 * ub, bar);
                     } else {
                         // row-major storage: a box of 128 rows x one unit; rows past the end of the tensor arrive as zeros
                         mbar_arrive_expect_tx(bar, (uint32_t)(BM * ub));
                         asm volatile(
                             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-                            "l"(&tmap_weights), "r"(u * ub), "r"(T.mat * n + T.rt * BM), "r"(bar)
+                            "l"(tmw), "r"(u * ub), "r"(T.mat * n + T.rt * BM), "r"(bar)
                             : "memory");
                     }
+                }
                 }
             }
         }
@@ -689,37 +748,54 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
             const TileRef T = tile_ref<TN>(A, tile, row_tiles);
             const int rt = T.rt;
-            const int ai = t % NACC;
-            if (!mbar_wait(smem_u32(&B->tmem_full[ai]), (t / NACC) & 1, B, A.status)) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int q = warp & 3;                       // TMEM lane quarter this warp may read
             const int out_row = rt * BM + q * 32 + lane;  // weight row = output column
+            bool ok = true;
+            for (int ps = 0; ps < PASSES; ++ps) {
+                const int ai = GATED ? ps : t % NACC;
+                if (!mbar_wait(smem_u32(&B->tmem_full[ai]), (GATED ? t : t / NACC) & 1, B, A.status)) {
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int c0 = 0; c0 < TN; c0 += 32) {
-                if (c0 >= T.ntok) break;  // warp-uniform: columns past the tile's tokens were not multiplied
-                uint32_t acc[32];
-                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ai * TN + c0);
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                    : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]), "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7]),
-                      "=r"(acc[8]), "=r"(acc[9]), "=r"(acc[10]), "=r"(acc[11]), "=r"(acc[12]), "=r"(acc[13]), "=r"(acc[14]), "=r"(acc[15]),
-                      "=r"(acc[16]), "=r"(acc[17]), "=r"(acc[18]), "=r"(acc[19]), "=r"(acc[20]), "=r"(acc[21]), "=r"(acc[22]), "=r"(acc[23]),
-                      "=r"(acc[24]), "=r"(acc[25]), "=r"(acc[26]), "=r"(acc[27]), "=r"(acc[28]), "=r"(acc[29]), "=r"(acc[30]), "=r"(acc[31])
-                    : "r"(taddr)
-                    : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (out_row < n) {
+                for (int c0 = 0; c0 < TN; c0 += 32) {
+                    if (c0 >= T.ntok) break;  // warp-uniform: columns past the tile's tokens were not multiplied
+                    uint32_t acc[32];
+                    tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ai * TN + c0), acc);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (GATED) {
+                        // g = up * (gate * 1/(1+exp(-gate))) in f32 (backend/ops.zig:150-190), rounded once to bf16.
+                        // The gate pass parks gate * sigmoid(gate) in shared memory (each thread re-reads only what
+                        // it wrote) while the MMAs of the up pass run; the up pass finishes the product.
+                        float* mine = sG + (size_t)c0 * BM + q * 32 + lane;
+                        if (ps == 0) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (c0 + j < T.ntok) A.c[(size_t)(T.tok0 + c0 + j) * A.ldc + out_row] = __uint_as_float(acc[j]);
+                            for (int j = 0; j < 32; ++j) {
+                                const float gv = __uint_as_float(acc[j]);
+                                const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gv)));
+                                mine[j * BM] = __fmul_rn(gv, sig);
+                            }
+                        } else if (out_row < n) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (c0 + j < T.ntok)
+                                    A.g_out[(size_t)(T.tok0 + c0 + j) * A.ldc + out_row] =
+                                        __float2bfloat16_rn(__fmul_rn(__uint_as_float(acc[j]), mine[j * BM]));
+                            }
+                        }
+                    } else if (out_row < n) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (c0 + j < T.ntok) A.c[(size_t)(T.tok0 + c0 + j) * A.ldc + out_row] = __uint_as_float(acc[j]);
+                        }
                     }
                 }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&B->tmem_empty[ai]));
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&B->tmem_empty[ai]));
+            if (!ok) break;
         }
     }
 
@@ -761,26 +837,30 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int FMT, int TN>
-cudaError_t launch_tc_tn(const TcArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap_w, int grid, cudaStream_t st) {
-    const size_t smem = (size_t)STAGES * TN * BK * 2 + (size_t)RawRing<TN>::stages * Staged<FMT>::raw_bytes + sizeof(Barriers) + 1024;
+template <int FMT, int TN, bool GATED = false>
+cudaError_t launch_tc_tn(const TcArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap_w, const CUtensorMap& tmap_w2, int grid, cudaStream_t st) {
+    const size_t smem = (size_t)STAGES * TN * BK * 2 + (size_t)(GATED ? kGatedRawStages : RawRing<TN>::stages) * Staged<FMT>::raw_bytes +
+                        (GATED ? kGateBytes : 0) + sizeof(Barriers) + 1024;
     static bool granted = false;
     if (!granted) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, TN, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         granted = true;
     }
-    gemm_tc_kernel<FMT, TN><<<grid, kThreads, smem, st>>>(a, tmap, tmap_w);
+    gemm_tc_kernel<FMT, TN, GATED><<<grid, kThreads, smem, st>>>(a, tmap, tmap_w, tmap_w2);
     return cudaGetLastError();
 }
 template <int FMT>
 cudaError_t launch_tc(const TcArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap_w, int grid, int tile_tokens, cudaStream_t st) {
-    return tile_tokens == 128 ? launch_tc_tn<FMT, 128>(a, tmap, tmap_w, grid, st) : launch_tc_tn<FMT, 256>(a, tmap, tmap_w, grid, st);
+    return tile_tokens == 128 ? launch_tc_tn<FMT, 128>(a, tmap, tmap_w, tmap_w, grid, st) : launch_tc_tn<FMT, 256>(a, tmap, tmap_w, tmap_w, grid, st);
 }
 
 #ifdef FQ_TIMELINE
 extern "C" __attribute__((visibility("default"))) int fq_debug_tc_timeline(unsigned long long* out) {
     return (int)cudaMemcpyFromSymbol(out, g_tc_timeline, sizeof(unsigned long long) * kTlSlabs * 5);
+}
+extern "C" __attribute__((visibility("default"))) int fq_debug_tc_timeline_dq(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_tc_timeline_dq, sizeof(unsigned long long) * kTlSlabs * 6);
 }
 #endif
 
@@ -794,8 +874,29 @@ bool tensor_path_serves(const DevWeights& w) {
 // Launch over bf16 activation rows [rows][k]: dense tiles of matrix `mat` (table == nullptr) or a
 // device-built tile list (grouped MoE form; `max_tiles` bounds the list for the grid size, and
 // `tile_tokens`, 128 or 256, is the token width its entries were cut to).
+// Tensor map over packed K-quant rows stored row-major (expert stacks, small matrices): all stacked matrices as
+// one 2-D byte array, one box = one 256-weight unit of 128 rows. Other layouts and formats need none (zeroed map).
+static int encode_packed_rows(EncodeTiledFn enc, const DevWeights& w, CUtensorMap* out) {
+    memset(out, 0, sizeof *out);
+    if (!((w.fmt == FQ_Q4_K || w.fmt == FQ_Q5_K) && !w.tile_rows)) return FQ_OK;
+    const int ub = w.fmt == FQ_Q4_K ? 144 : 176;
+    if (w.mat_stride != (size_t)w.n * w.row_stride && w.n_mats > 1) return fail(FQ_DECLINED_ARGS, "stacked matrices are not contiguous");
+    const cuuint64_t wdims[2] = {(cuuint64_t)(w.k / 256) * ub, (cuuint64_t)w.n * (cuuint64_t)w.n_mats};
+    const cuuint64_t wstrides[1] = {(cuuint64_t)w.row_stride};
+    const cuuint32_t wbox[2] = {(cuuint32_t)ub, BM};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w.base), wdims, wstrides, wbox, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return fail(FQ_DECLINED_ARGS, "tensor map for the packed weights could not be encoded");
+    return FQ_OK;
+}
+
+// `up` and `g_out` select the gated form (grouped, 128-token tiles): w is the gate stack, the result is
+// bf16(up * silu(gate)) in g_out instead of f32 products in c_dev.
 static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfloat16* abf, size_t rows, float* c_dev, size_t ldc,
-                          const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st) {
+                          const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st,
+                          const DevWeights* up = nullptr, __nv_bfloat16* g_out = nullptr) {
     const int BN = tile_tokens;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return fail(FQ_DECLINED_ARGS, "cuTensorMapEncodeTiled unavailable");
@@ -809,26 +910,23 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return fail(FQ_DECLINED_ARGS, "tensor map for the activations could not be encoded");
-    // packed K-quant rows stored row-major (expert stacks, small matrices) reach shared memory through a
-    // second tensor map: all stacked matrices as one 2-D byte array, one box = one unit of 128 rows
-    CUtensorMap tmap_w;
-    memset(&tmap_w, 0, sizeof tmap_w);
-    if ((w.fmt == FQ_Q4_K || w.fmt == FQ_Q5_K) && !w.tile_rows) {
-        const int ub = w.fmt == FQ_Q4_K ? 144 : 176;
-        if (w.mat_stride != (size_t)w.n * w.row_stride && w.n_mats > 1) return fail(FQ_DECLINED_ARGS, "stacked matrices are not contiguous");
-        const cuuint64_t wdims[2] = {(cuuint64_t)(w.k / 256) * ub, (cuuint64_t)w.n * (cuuint64_t)w.n_mats};
-        const cuuint64_t wstrides[1] = {(cuuint64_t)w.row_stride};
-        const cuuint32_t wbox[2] = {(cuuint32_t)ub, BM};
-        if (enc(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w.base), wdims, wstrides, wbox, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return fail(FQ_DECLINED_ARGS, "tensor map for the packed weights could not be encoded");
-    }
+    CUtensorMap tmap_w, tmap_w2;
+    if (int rc = encode_packed_rows(enc, w, &tmap_w)) return rc;
+    if (int rc = encode_packed_rows(enc, up ? *up : w, &tmap_w2)) return rc;
     static const int diag = getenv("FUCINA_B200_TC_DIAG") ? atoi(getenv("FUCINA_B200_TC_DIAG")) : 0;
-    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev, diag};
+    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev, diag, up ? *up : w, g_out};
     const int tiles = table ? max_tiles : ((w.n + BM - 1) / BM) * (int)((rows + BN - 1) / BN);
     const int grid = tiles < ctx->sm_count ? (tiles > 0 ? tiles : 1) : ctx->sm_count;
     cudaError_t e;
+    if (up) {  // gated form: the formats expert stacks come in
+        switch (w.fmt) {
+            case FQ_Q4_K: e = launch_tc_tn<FQ_Q4_K, 128, true>(a, tmap, tmap_w, tmap_w2, grid, st); break;
+            case FQ_Q5_K: e = launch_tc_tn<FQ_Q5_K, 128, true>(a, tmap, tmap_w, tmap_w2, grid, st); break;
+            default: e = launch_tc_tn<FQ_Q8_0, 128, true>(a, tmap, tmap_w, tmap_w2, grid, st); break;
+        }
+        g_trace.launches++;
+        return e == cudaSuccess ? FQ_OK : cuda_fail(e, "tensor-core GEMM launch");
+    }
     switch (w.fmt) {
         case FQ_Q4_K: e = launch_tc<FQ_Q4_K>(a, tmap, tmap_w, grid, tile_tokens, st); break;
         case FQ_Q5_K: e = launch_tc<FQ_Q5_K>(a, tmap, tmap_w, grid, tile_tokens, st); break;
@@ -846,6 +944,19 @@ int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, s
     if (tile_tokens != 128 && tile_tokens != 256) return fail(FQ_DECLINED_ARGS, "token tiles are 128 or 256 rows");
     if (!tensor_path_serves(w)) return fail(FQ_DECLINED_ARGS, "tensor-core path needs a served format with k %% 256 == 0");
     return launch_tc_rows(ctx, w, 0, (const __nv_bfloat16*)a_bf16, rows, c_dev, ldc, table, n_tiles_dev, max_tiles, tile_tokens, st);
+}
+
+// Gate and up products of one expert layer in one pass with the SwiGLU applied in the epilogue:
+// g[row, j] = bf16(up[row, j] * silu(gate[row, j])) over the tile list (128-token tiles).
+int gemm_tensor_grouped_gated_dev(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const void* a_bf16, size_t rows, void* g_bf16,
+                                  size_t ldc, const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st) {
+    if (!tensor_path_serves(gate) || (gate.fmt != FQ_Q4_K && gate.fmt != FQ_Q5_K && gate.fmt != FQ_Q8_0))
+        return fail(FQ_DECLINED_ARGS, "the gated tensor-core form serves Q4_K, Q5_K and Q8_0 with k %% 256 == 0");
+    if (up.fmt != gate.fmt || up.n != gate.n || up.k != gate.k || up.n_mats != gate.n_mats || up.tile_rows != gate.tile_rows ||
+        up.row_stride != gate.row_stride || up.mat_stride != gate.mat_stride)
+        return fail(FQ_DECLINED_ARGS, "gate and up stacks differ in shape or layout");
+    return launch_tc_rows(ctx, gate, 0, (const __nv_bfloat16*)a_bf16, rows, nullptr, ldc, table, n_tiles_dev, max_tiles, 128, st, &up,
+                          (__nv_bfloat16*)g_bf16);
 }
 
 __global__ void add_f32_kernel(float* __restrict__ c, const float* __restrict__ t, size_t n) {

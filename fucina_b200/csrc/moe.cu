@@ -292,12 +292,17 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
         int blocks = (int)(((size_t)pairs * hidden / 4 + 255) / 256);
         gather_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>(x_dev, order, top_k, cnt + 3, hidden, (__nv_bfloat16*)(s + o_xb));
         if ((e = cudaGetLastError()) != cudaSuccess) break;
-        if ((rc = gemm_tensor_grouped_dev(ctx, gate, s + o_xb, pairs, (float*)(s + o_gate), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, tile_tokens, st)) != FQ_OK) break;
-        if ((rc = gemm_tensor_grouped_dev(ctx, up, s + o_xb, pairs, (float*)(s + o_up), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, tile_tokens, st)) != FQ_OK) break;
-        const size_t ng = (size_t)pairs * out_pe;
-        blocks = (int)((ng + 255) / 256);
-        swiglu_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>((const float*)(s + o_gate), (const float*)(s + o_up), cnt + 3, out_pe, (__nv_bfloat16*)(s + o_gb));
-        if ((e = cudaGetLastError()) != cudaSuccess) break;
+        if (tile_tokens == 128) {
+            // short runs: gate and up of a tile share one pass, the SwiGLU runs in its epilogue
+            if ((rc = gemm_tensor_grouped_gated_dev(ctx, gate, up, s + o_xb, pairs, s + o_gb, out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, st)) != FQ_OK) break;
+        } else {
+            if ((rc = gemm_tensor_grouped_dev(ctx, gate, s + o_xb, pairs, (float*)(s + o_gate), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, tile_tokens, st)) != FQ_OK) break;
+            if ((rc = gemm_tensor_grouped_dev(ctx, up, s + o_xb, pairs, (float*)(s + o_up), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, tile_tokens, st)) != FQ_OK) break;
+            const size_t ng = (size_t)pairs * out_pe;
+            blocks = (int)((ng + 255) / 256);
+            swiglu_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>((const float*)(s + o_gate), (const float*)(s + o_up), cnt + 3, out_pe, (__nv_bfloat16*)(s + o_gb));
+            if ((e = cudaGetLastError()) != cudaSuccess) break;
+        }
         if ((rc = gemm_tensor_grouped_dev(ctx, down, s + o_gb, pairs, (float*)(s + o_down), hidden, (const TcTile*)(s + o_tdn), cnt + 2, max_dn, tile_tokens, st)) != FQ_OK) break;
         const size_t total = (size_t)seq * hidden;
         blocks = (int)((total + 255) / 256);

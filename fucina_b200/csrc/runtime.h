@@ -59,5 +59,7 @@ struct TcTile;
 bool tensor_path_serves(const DevWeights& w);
 int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, size_t rows, float* c_dev, size_t ldc,
                             const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st);
+int gemm_tensor_grouped_gated_dev(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const void* a_bf16, size_t rows, void* g_bf16,
+                                  size_t ldc, const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st);
 
 }  // namespace fq
