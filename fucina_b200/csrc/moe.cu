@@ -41,44 +41,68 @@ __device__ __forceinline__ int local_expert(int e, int n_expert, Shard sh) {
     return sh.skip_foreign ? -1 : min(max(e, 0), n_expert - 1);
 }
 
+// One CTA: counting sort of the routed pairs by expert (order / inv), the table of row groups for the
+// integer kernels and, when tile_tokens != 0, the tile lists of the grouped tensor-core GEMMs: per expert
+// run ceil(count / tile_tokens) token tiles times the row tiles of the gate/up product (rt_gu) and of the
+// down product (rt_dn), in expert order (the row tiles of one token tile are neighbours, so concurrent
+// CTAs share its token rows in L2). Each thread keeps eight loads of the pair list in flight per step.
+// Shared memory: 4 * n_expert ints.
+constexpr int kPlanBatch = 8;
 __global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, Shard shard, int group_rows, int* __restrict__ order,
                                   int* __restrict__ inv, GroupDesc* __restrict__ table, int* __restrict__ n_desc,
-                                  int* __restrict__ n_rows) {
+                                  int* __restrict__ n_rows, int tile_tokens, int rt_gu, int rt_dn, TcTile* __restrict__ t_gu,
+                                  int* __restrict__ n_gu, TcTile* __restrict__ t_dn, int* __restrict__ n_dn) {
     extern __shared__ int sh[];
     int* count = sh;                   // [n_expert] pairs per expert
     int* place = sh + n_expert;        // [n_expert] first sorted position of the expert's run
     int* dstart = sh + 2 * n_expert;   // [n_expert] first table entry of the expert
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int* tstart = sh + 3 * n_expert;   // [n_expert] first token tile of the expert
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     for (int e = threadIdx.x; e < n_expert; e += blockDim.x) count[e] = 0;
     __syncthreads();
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const int e = local_expert(selected[p], n_expert, shard);
-        if (e >= 0) atomicAdd(&count[e], 1);
+    for (int p0 = threadIdx.x; p0 < pairs; p0 += blockDim.x * kPlanBatch) {
+        int e[kPlanBatch];
+#pragma unroll
+        for (int i = 0; i < kPlanBatch; ++i) {
+            const int p = p0 + i * blockDim.x;
+            e[i] = p < pairs ? local_expert(selected[p], n_expert, shard) : -1;
+        }
+#pragma unroll
+        for (int i = 0; i < kPlanBatch; ++i)
+            if (e[i] >= 0) atomicAdd(&count[e[i]], 1);
     }
     __syncthreads();
     if (warp == 0) {
-        // exclusive scans over the experts: run offsets and table offsets, 32 experts per step
-        int rows = 0, nd = 0;
+        // exclusive scans over the experts: run offsets, table offsets and token-tile offsets, 32 experts per step
+        int rows = 0, nd = 0, nt = 0;
         for (int base = 0; base < n_expert; base += 32) {
             const int e = base + lane;
             const int c = e < n_expert ? count[e] : 0;
             const int g = (c + group_rows - 1) / group_rows;
-            int ic = c, ig = g;
+            const int tl = tile_tokens ? (c + tile_tokens - 1) / tile_tokens : 0;
+            int ic = c, ig = g, it = tl;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int tc = __shfl_up_sync(0xffffffffu, ic, o), tg = __shfl_up_sync(0xffffffffu, ig, o);
-                if (lane >= o) ic += tc, ig += tg;
+                const int tt = __shfl_up_sync(0xffffffffu, it, o);
+                if (lane >= o) ic += tc, ig += tg, it += tt;
             }
             if (e < n_expert) {
                 place[e] = rows + ic - c;
                 dstart[e] = nd + ig - g;
+                tstart[e] = nt + it - tl;
             }
             rows += __shfl_sync(0xffffffffu, ic, 31);
             nd += __shfl_sync(0xffffffffu, ig, 31);
+            nt += __shfl_sync(0xffffffffu, it, 31);
         }
         if (lane == 0) {
             *n_desc = nd;
             *n_rows = rows;
+            if (tile_tokens) {
+                *n_gu = nt * rt_gu;
+                *n_dn = nt * rt_dn;
+            }
         }
     }
     __syncthreads();
@@ -87,16 +111,37 @@ __global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, i
         int d = dstart[e];
         for (int j = 0; j < c; j += group_rows) table[d++] = {e, off + j, min(group_rows, c - j), 0};
     }
-    __syncthreads();  // the pass below advances place[]
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const int e = local_expert(selected[p], n_expert, shard);
-        if (e < 0) {
-            inv[p] = -1;
-            continue;
+    if (tile_tokens) {
+        // one warp per expert; the entries of a token tile are written by consecutive lanes
+        for (int e = warp; e < n_expert; e += warps) {
+            const int c = count[e], row0 = place[e], tile0 = tstart[e];
+            for (int t0 = 0, tt = 0; t0 < c; t0 += tile_tokens, ++tt) {
+                const int nt = min(tile_tokens, c - t0);
+                for (int rt = lane; rt < rt_gu; rt += 32) t_gu[(size_t)(tile0 + tt) * rt_gu + rt] = {e, rt, row0 + t0, nt};
+                for (int rt = lane; rt < rt_dn; rt += 32) t_dn[(size_t)(tile0 + tt) * rt_dn + rt] = {e, rt, row0 + t0, nt};
+            }
         }
-        const int pos = atomicAdd(&place[e], 1);
-        order[pos] = p;
-        inv[p] = pos;
+    }
+    __syncthreads();  // the pass below advances place[]
+    for (int p0 = threadIdx.x; p0 < pairs; p0 += blockDim.x * kPlanBatch) {
+        int e[kPlanBatch];
+#pragma unroll
+        for (int i = 0; i < kPlanBatch; ++i) {
+            const int p = p0 + i * blockDim.x;
+            e[i] = p < pairs ? local_expert(selected[p], n_expert, shard) : -2;
+        }
+#pragma unroll
+        for (int i = 0; i < kPlanBatch; ++i) {
+            const int p = p0 + i * blockDim.x;
+            if (e[i] == -2) continue;  // past the end of the list
+            if (e[i] < 0) {
+                inv[p] = -1;  // another shard's expert
+                continue;
+            }
+            const int pos = atomicAdd(&place[e[i]], 1);
+            order[pos] = p;
+            inv[p] = pos;
+        }
     }
 }
 
@@ -186,47 +231,6 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int rows, i
 int max_desc_for(int pairs, int n_expert, int group_rows);
 
 // ---- tensor-core form for prefill-sized batches ------------------------------------------------
-// Tile lists for the grouped tcgen05 GEMM, one CTA: per expert run, ceil(count/tile_tokens) token tiles
-// times the row tiles of the gate/up product (rt_gu) and of the down product (rt_dn), in expert order
-// (the row tiles of one token tile are neighbours, so concurrent CTAs share its token rows in L2).
-// Shared memory: 3 * n_expert ints (count, first sorted row, first token tile of each expert).
-__global__ void tc_plan_kernel(const int* __restrict__ selected, int pairs, int n_expert, Shard shard, int rt_gu, int rt_dn, int tile_tokens,
-                               TcTile* __restrict__ t_gu, int* __restrict__ n_gu, TcTile* __restrict__ t_dn, int* __restrict__ n_dn) {
-    extern __shared__ int sh[];
-    int* count = sh;
-    int* first_row = sh + n_expert;
-    int* first_tile = sh + 2 * n_expert;
-    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) count[e] = 0;
-    __syncthreads();
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const int e = local_expert(selected[p], n_expert, shard);
-        if (e >= 0) atomicAdd(&count[e], 1);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int off = 0, tiles = 0;
-        for (int e = 0; e < n_expert; ++e) {
-            first_row[e] = off;
-            first_tile[e] = tiles;
-            off += count[e];
-            tiles += (count[e] + tile_tokens - 1) / tile_tokens;
-        }
-        *n_gu = tiles * rt_gu;
-        *n_dn = tiles * rt_dn;
-    }
-    __syncthreads();
-    // one warp per expert; the entries of a token tile are written by consecutive lanes
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int e = warp; e < n_expert; e += warps) {
-        const int c = count[e], row0 = first_row[e], tile0 = first_tile[e];
-        for (int t0 = 0, tt = 0; t0 < c; t0 += tile_tokens, ++tt) {
-            const int nt = min(tile_tokens, c - t0);
-            for (int rt = lane; rt < rt_gu; rt += 32) t_gu[(size_t)(tile0 + tt) * rt_gu + rt] = {e, rt, row0 + t0, nt};
-            for (int rt = lane; rt < rt_dn; rt += 32) t_dn[(size_t)(tile0 + tt) * rt_dn + rt] = {e, rt, row0 + t0, nt};
-        }
-    }
-}
-
 // sorted pair position -> bf16 copy of its token row
 __global__ void gather_bf16_kernel(const float* __restrict__ x, const int* __restrict__ order, int top_k, const int* __restrict__ n_rows,
                                    int hidden, __nv_bfloat16* __restrict__ out) {
@@ -286,9 +290,8 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
     cudaError_t e = cudaSuccess;
     int rc = FQ_OK;
     do {
-        route_plan_kernel<<<1, 1024, sizeof(int) * 3 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, kGroupRows, order, inv, (GroupDesc*)(s + o_desc), cnt, cnt + 3);
-        tc_plan_kernel<<<1, 1024, sizeof(int) * 3 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, rt_gu, rt_dn, tile_tokens, (TcTile*)(s + o_tgu), cnt + 1,
-                                                                 (TcTile*)(s + o_tdn), cnt + 2);
+        route_plan_kernel<<<1, 1024, sizeof(int) * 4 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, kGroupRows, order, inv, (GroupDesc*)(s + o_desc), cnt, cnt + 3,
+                                                                    tile_tokens, rt_gu, rt_dn, (TcTile*)(s + o_tgu), cnt + 1, (TcTile*)(s + o_tdn), cnt + 2);
         int blocks = (int)(((size_t)pairs * hidden / 4 + 255) / 256);
         gather_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>(x_dev, order, top_k, cnt + 3, hidden, (__nv_bfloat16*)(s + o_xb));
         if ((e = cudaGetLastError()) != cudaSuccess) break;
@@ -371,7 +374,8 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     do {
         // positions past a shard's own rows are read by the gather below: point them at pair 0
         if (shard.skip_foreign && (e = cudaMemsetAsync(order, 0, sizeof(int) * pairs, st)) != cudaSuccess) break;
-        route_plan_kernel<<<1, 1024, sizeof(int) * 3 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, group_rows, order, inv, table, n_desc, n_desc + 1);
+        route_plan_kernel<<<1, 1024, sizeof(int) * 4 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, group_rows, order, inv, table, n_desc, n_desc + 1,
+                                                                    0, 0, 0, nullptr, nullptr, nullptr, nullptr);
         if ((e = cudaGetLastError()) != cudaSuccess) break;
         if (streaming) {
             if ((e = launch_expert_rows(gate, &up, x_dev, order, top_k, g, table, n_desc, max_desc, group_rows, ctx->sm_count, ctx->status_dev,
@@ -417,7 +421,7 @@ int check_moe(const fq_weights* gate, const fq_weights* up, const fq_weights* do
         return fail(FQ_DECLINED_ARGS, "expert tensor shapes are inconsistent");
     if (seq == 0 || top_k == 0 || (!shard && top_k > (size_t)g.n_mats)) return fail(FQ_DECLINED_ARGS, "bad seq/top_k");
     if (seq * top_k > (size_t)1 << 24) return fail(FQ_DECLINED_ARGS, "too many routed pairs");
-    if (g.n_mats > 4096) return fail(FQ_DECLINED_ARGS, "too many experts");
+    if (g.n_mats > 3072) return fail(FQ_DECLINED_ARGS, "too many experts");  // the route plan keeps four ints per expert in 48 KB of shared memory
     const ActLayout L = act_layout(g.fmt);
     if (g.n % L.act_block != 0 || g.n % format_info(g.fmt).block_elems != 0)
         return fail(FQ_DECLINED_ARGS, "expert width %d is not a whole number of blocks", g.n);
