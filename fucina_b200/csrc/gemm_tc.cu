@@ -89,6 +89,11 @@ static_assert(kDequantWarps == 8 || kDequantWarps == 16, "8 or 16 dequantising w
 constexpr int kEpilogueWarps = 4;  // one per tensor-memory lane quarter (eight, splitting the columns, measured no faster)
 constexpr int kThreads = (3 + kDequantWarps + kEpilogueWarps) * 32;
 constexpr unsigned kWaitLimit = 1u << 20;
+#ifndef FQ_TC_SLEEP_NS
+#define FQ_TC_SLEEP_NS 100
+#endif
+constexpr unsigned kProducerSleepNs = FQ_TC_SLEEP_NS;      // copy-engine producers waiting for a free ring stage
+constexpr unsigned kEpilogueSleepNs = 2 * FQ_TC_SLEEP_NS;  // epilogue warps waiting for a finished accumulator
 constexpr int TMEM_COLS = 512;  // columns 0..255: the f32 accumulator; from column 256: the A ring (STAGES x 32)
 constexpr int A_COLS = BK / 2;  // tensor-memory columns of one A slab: two bf16 per 32-bit column
 constexpr int A_COL0 = kAccCols;
@@ -183,10 +188,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait that also gives up when another role aborted. Returns false on abort/timeout.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Barriers* B, int* status) {
+// Roles that wait off the critical path (producers, epilogue) pass sleep_ns: a hot polling loop issues an
+// instruction every few cycles and takes issue slots and the integer pipe from the dequantising warps.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Barriers* B, int* status, unsigned sleep_ns = 0) {
     for (unsigned i = 0; i < kWaitLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (B->abort_flag) return false;
+        if (sleep_ns) __nanosleep(sleep_ns);
     }
     B->abort_flag = 1;
     *(volatile int*)status = FQ_ERR_TIMEOUT;  // mapped host word: a plain store, device atomics on host memory are not portable
@@ -551,7 +559,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 for (int u = 0; u < PASSES * units && ok; ++u) {
                     for (int p = 0; p < 4; ++p, ++gb) {
                         const int s = gb % STAGES;
-                        if (!mbar_wait(smem_u32(&B->empty[s]), ((gb / STAGES) & 1) ^ 1, B, A.status)) {
+                        if (!mbar_wait(smem_u32(&B->empty[s]), ((gb / STAGES) & 1) ^ 1, B, A.status, kProducerSleepNs)) {
                             ok = false;
                             break;
                         }
@@ -715,7 +723,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 const CUtensorMap* tmw = (GATED && ps) ? &tmap_weights2 : &tmap_weights;
                 for (int u = 0; u < units; ++u, ++gu) {
                     const int rs = gu % RAW_STAGES;
-                    if (!mbar_wait(smem_u32(&B->raw_empty[rs]), ((gu / RAW_STAGES) & 1) ^ 1, B, A.status)) {
+                    if (!mbar_wait(smem_u32(&B->raw_empty[rs]), ((gu / RAW_STAGES) & 1) ^ 1, B, A.status, kProducerSleepNs)) {
                         ok = false;
                         break;
                     }
@@ -753,7 +761,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             bool ok = true;
             for (int ps = 0; ps < PASSES; ++ps) {
                 const int ai = GATED ? ps : t % NACC;
-                if (!mbar_wait(smem_u32(&B->tmem_full[ai]), (GATED ? t : t / NACC) & 1, B, A.status)) {
+                if (!mbar_wait(smem_u32(&B->tmem_full[ai]), (GATED ? t : t / NACC) & 1, B, A.status, kEpilogueSleepNs)) {
                     ok = false;
                     break;
                 }
