@@ -164,31 +164,34 @@ __global__ void combine_kernel(const float* __restrict__ down, const float* __re
         out[i] = acc;
     }
 }
-// The same sum, one CTA per token and four columns per thread (hidden % 4 == 0, 16-byte aligned rows): the
-// token's slots are looked up once per four outputs instead of once per output.
+// The same sum, four columns per thread (hidden % 4 == 0, 16-byte aligned rows): the token's slots are looked
+// up once per four outputs instead of once per output.
 __global__ void combine4_kernel(const float* __restrict__ down, const float* __restrict__ weights, const int* __restrict__ inv,
                                 int seq, int hidden, int top_k, float* __restrict__ out) {
-    for (int t = blockIdx.x; t < seq; t += gridDim.x) {
-        for (int j = threadIdx.x * 4; j < hidden; j += blockDim.x * 4) {
-            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            bool first = true;
-            for (int kk = 0; kk < top_k; ++kk) {
-                const int p = t * top_k + kk, pos = inv[p];
-                if (pos < 0) continue;  // another shard's expert
-                const float wv = weights[p];
-                float4 v = *reinterpret_cast<const float4*>(down + (size_t)pos * hidden + j);
-                v.x = __fmul_rn(wv, v.x), v.y = __fmul_rn(wv, v.y), v.z = __fmul_rn(wv, v.z), v.w = __fmul_rn(wv, v.w);
-                if (first) acc = v;
-                else acc.x = __fadd_rn(acc.x, v.x), acc.y = __fadd_rn(acc.y, v.y), acc.z = __fadd_rn(acc.z, v.z), acc.w = __fadd_rn(acc.w, v.w);
-                first = false;
-            }
-            *reinterpret_cast<float4*>(out + (size_t)t * hidden + j) = acc;
+    const int h4 = hidden >> 2;
+    const size_t total = (size_t)seq * h4;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / h4), j = (int)(i % h4) * 4;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        bool first = true;
+        for (int kk = 0; kk < top_k; ++kk) {
+            const int p = t * top_k + kk, pos = inv[p];
+            if (pos < 0) continue;  // another shard's expert
+            const float wv = weights[p];
+            float4 v = *reinterpret_cast<const float4*>(down + (size_t)pos * hidden + j);
+            v.x = __fmul_rn(wv, v.x), v.y = __fmul_rn(wv, v.y), v.z = __fmul_rn(wv, v.z), v.w = __fmul_rn(wv, v.w);
+            if (first) acc = v;
+            else acc.x = __fadd_rn(acc.x, v.x), acc.y = __fadd_rn(acc.y, v.y), acc.z = __fadd_rn(acc.z, v.z), acc.w = __fadd_rn(acc.w, v.w);
+            first = false;
         }
+        *reinterpret_cast<float4*>(out + (size_t)t * hidden + j) = acc;
     }
 }
 static void launch_combine(const float* down, const float* weights, const int* inv, int seq, int hidden, int top_k, float* out, cudaStream_t st) {
     if (hidden % 4 == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)down & 15) == 0) {
-        combine4_kernel<<<seq < 148 * 8 ? seq : 148 * 8, 256, 0, st>>>(down, weights, inv, seq, hidden, top_k, out);
+        const size_t total4 = (size_t)seq * (hidden / 4);
+        const int blocks4 = (int)((total4 + 127) / 128);
+        combine4_kernel<<<blocks4 > 148 * 16 ? 148 * 16 : blocks4, 128, 0, st>>>(down, weights, inv, seq, hidden, top_k, out);
         return;
     }
     const size_t total = (size_t)seq * hidden;

@@ -69,9 +69,11 @@ def test_auto_mode_routes_large_m_to_tensor_cores(P, torch):
 
 
 @pytest.mark.parametrize("fmt_name,hidden,out_pe,n_expert,top_k,seq", [
-    ("q5_k", 256, 256, 4, 2, 37),      # ragged expert runs inside one token tile
+    ("q5_k", 256, 256, 4, 2, 37),      # ragged expert runs inside one 128-token tile: fused gate/up pass, SwiGLU in the epilogue
     ("q5_k", 512, 768, 8, 4, 300),     # runs of ~150 rows, several row tiles, Qwen3-MoE expert width
     ("q4_k", 256, 512, 4, 2, 700),     # runs longer than one 256-token tile
+    ("q8_0", 256, 256, 4, 2, 60),      # split rows read by the dequantising threads, fused gate/up pass on 128-token tiles
+    ("q8_0", 256, 256, 2, 2, 300),     # the same format on 256-token tiles (separate gate and up products)
 ])
 def test_moe_tensor_arm_matches_bf16_oracle(P, fmt_name, hidden, out_pe, n_expert, top_k, seq):
     from fucina_b200._lib import load
