@@ -287,6 +287,29 @@ def test_moe_expert_shards_sum_to_the_layer(P, torch, tensor_arm, seq):
         load().fq_set_moe_tensor_for_test(-1)
 
 
+def test_moe_output_need_not_be_16_byte_aligned(P, torch):
+    """The combine writes four columns per thread when the output rows are 16-byte aligned and one
+    column per thread otherwise; both give the same bits."""
+    hidden, out_pe, n_expert, top_k, seq = 256, 256, 4, 2, 9
+    gate, up, down, x, _, sel, w = _moe_case("q4_k", hidden, out_pe, n_expert, top_k, seq, seed=90)
+    ws = [P.Weights.upload(oracle.Q4_K, b, n, k, n_expert) for b, n, k in ((gate, out_pe, hidden), (up, out_pe, hidden), (down, hidden, out_pe))]
+    xd = torch.from_numpy(x).cuda()
+    sd = torch.from_numpy(sel.astype(np.int32)).cuda()
+    wd_ = torch.from_numpy(w).cuda()
+    aligned = torch.full((seq * hidden,), float("nan"), device="cuda")
+    backing = torch.full((seq * hidden + 4,), float("nan"), device="cuda")
+    shifted = backing[1:1 + seq * hidden]          # 4 bytes past a 16-byte boundary
+    assert aligned.data_ptr() % 16 == 0 and shifted.data_ptr() % 16 == 4
+    P.moe_layer_dev(*ws, xd, seq, top_k, sd, wd_, aligned)
+    P.moe_layer_dev(*ws, xd, seq, top_k, sd, wd_, shifted)
+    P.synchronize()
+    a, b = aligned.cpu().numpy(), shifted.cpu().numpy()
+    assert np.isfinite(a).all() and np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    assert np.isnan(backing[0].item()) and np.isnan(backing[-1].item())  # nothing written outside the rows
+    for h in ws:
+        h.free()
+
+
 def test_moe_token_may_name_an_expert_twice(P):
     """A routing row that repeats an expert makes that expert's run longer than the batch; the
     row-group table must split it rather than drop rows."""
