@@ -30,8 +30,11 @@
 //                 memory, whose bandwidth the token tiles need
 //   warps 10..13  epilogue: read the finished accumulator with tcgen05.ld and store f32 results
 //                 (coalesced along n)
-// A stage has one "full" barrier (copy-engine bytes + the 256 dequantising threads) and one "empty"
+// A stage has one "full" barrier (copy-engine bytes + one arrival per dequantising warp) and one "empty"
 // barrier (the MMAs' commit), so the issuing thread waits once and commits once per slab.
+// Gated form (MoE gate/up pair, 128-token tiles): every tile makes two passes over K, gate weights into the
+// first accumulator and up weights into the second; the epilogue of the gate pass parks gate * sigmoid(gate)
+// in shared memory while the up pass multiplies, the epilogue of the up pass writes bf16(up * that).
 // Every mbarrier wait is bounded and also watches a CTA-wide abort flag; a wait that gives up sets
 // FQ_ERR_TIMEOUT in the status word, all roles fall through to the common exit, TMEM is freed.
 #include <cuda.h>
@@ -58,7 +61,7 @@ constexpr int BM = 128;        // weight rows per tile (UMMA M)
 constexpr int BK = 64;         // K elements per ring stage (128 bytes of bf16: one swizzle span)
 // One ring of K slabs: stage s holds the token tile in shared memory and the dequantised weight slab in
 // tensor memory (32 columns = 64 bf16 along K per lane). One "full" barrier per stage collects the copy
-// engine's bytes and the 256 dequantising threads, one "empty" barrier is signalled by the MMAs'
+// engine's bytes and the eight dequantising warps, one "empty" barrier is signalled by the MMAs'
 // commit: the single issuing thread waits once and commits once per slab, which is what bounds its rate.
 constexpr int STAGES = 5;
 // Ring of packed K-quant units (one unit = 256 weights of 128 rows = four K slabs), filled by a copy-engine
