@@ -460,6 +460,37 @@ def run_profile_q8(args) -> dict:
             "avg_kernel_us": round(ms / max(cnt, 1) * 1e3, 2), "GBps": round(nbytes / (ms / max(cnt, 1) * 1e-3) / 1e9, 1)}
 
 
+def run_profile_moe(args) -> dict:
+    """One prefill-sized expert layer for profiler launch lists: Q5_K, hidden 2048, ffn 768, 128 experts, top-8,
+    1024 tokens (8192 routed rows), plain launches (no graph), router outside the timed loop."""
+    import torch
+
+    from fucina_b200 import formats as F
+    from fucina_b200 import provider as P
+
+    P.init(0)
+    hidden, ffn, n_expert, top_k, seq = 2048, 768, 128, 8, 1024
+    gate = _dev_weights(P, torch, F.Q5_K, ffn, hidden, 1300, n_expert)
+    up = _dev_weights(P, torch, F.Q5_K, ffn, hidden, 1301, n_expert)
+    down = _dev_weights(P, torch, F.Q5_K, hidden, ffn, 1302, n_expert)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((seq, hidden), generator=g, device="cuda")
+    logits = torch.randn((seq, n_expert), generator=g, device="cuda")
+    sel = torch.empty((seq, top_k), dtype=torch.int32, device="cuda")
+    w = torch.empty((seq, top_k), device="cuda")
+    out = torch.empty((seq, hidden), device="cuda")
+    torch.cuda.synchronize()
+    P.router_topk_dev(logits, seq, n_expert, top_k, True, sel, w)
+    P.synchronize()
+
+    def layer():
+        P.moe_layer_dev(gate, up, down, x, seq, top_k, sel, w, out)
+
+    ms = _timed(P, torch, layer, args.steps, args.warmup)
+    return {"workload": "profile case: Q5_K MoE layer 2048/768, 128 experts, top-8, 1024 tokens (plain launches)", "ms": round(ms, 4),
+            "tok_per_s": round(seq / ms * 1e3, 1)}
+
+
 def _timed(P, torch, fn, steps: int, warmup: int) -> float:
     """milliseconds per call of fn() on the library stream (CUDA events)."""
     ext = torch.cuda.ExternalStream(P.stream_ptr())
@@ -740,7 +771,7 @@ def run_profile_tc(args) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="stack", choices=["stack", "profile", "profile_q8", "profile_tc", "q8_0", "prefill", "moe", "ternary", "all",
+    ap.add_argument("--workload", default="stack", choices=["stack", "profile", "profile_q8", "profile_tc", "profile_moe", "q8_0", "prefill", "moe", "ternary", "all",
                                                                 "tp_prefill", "ep_moe", "multi"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -764,6 +795,9 @@ def main() -> None:
         return
     if args.workload == "profile_tc":
         print(json.dumps(run_profile_tc(args)), flush=True)
+        return
+    if args.workload == "profile_moe":
+        print(json.dumps(run_profile_moe(args)), flush=True)
         return
     if args.workload == "profile_q8":
         print(json.dumps(run_profile_q8(args)), flush=True)
