@@ -57,7 +57,8 @@ SIGNATURES = {
     "fq_work_destroy": (None, [c_void]),
     "fq_gemm_quant_nt_dev": (c_int, [c_void, c_size, c_void, c_void, c_size, c_int, c_void]),
     "fq_gemm_quant_nt_dev_noalloc": (c_int, [c_void, c_size, c_void, c_void, c_size, c_void]),
-    "fq_gemm_ptqtp_dev":(c_int, [P(c_void), c_int, c_void, c_void, c_size, c_void]),
+    "fq_small_batch_max_rows": (c_int, [c_int, c_size]),
+    "fq_gemm_ptqtp_dev": (c_int, [P(c_void), c_int, c_void, c_void, c_size, c_void]),
     "fq_quantize_acts_q8_k_dev": (c_int, [c_void, c_size, c_size, c_void]),
     "fq_quantize_acts_q8_0_dev": (c_int, [c_void, c_size, c_size, c_void]),
     "fq_capture_begin": (c_int, []),
@@ -81,6 +82,7 @@ SIGNATURES = {
     "fq_set_min_work_qmoe_for_test": (None, [c_u64]),
     "fq_set_decode_for_test": (None, [c_int]),
     "fq_set_moe_tensor_for_test": (None, [c_int]),
+    "fq_set_group_grid_limit_for_test": (None, [c_int]),
     "fq_selftest_bounded_wait": (c_int, [C.c_uint]),
     "fq_trace_enabled": (c_int, []),
     "fq_trace_reset": (None, []),

@@ -999,14 +999,13 @@ int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, 
     if (!format_info(w.fmt).block_elems || w.fmt == FQ_Q6_K) return fail(FQ_DECLINED_ARGS, "format %d has no tensor-core kernel", w.fmt);
     if (w.k % 256 != 0 || m < 1 || m > (size_t)1 << 24) return fail(FQ_DECLINED_ARGS, "tensor-core path needs k %% 256 == 0");
     // bf16 copy of the activations: [m][k], read by TMA with a 128-byte swizzle
-    __nv_bfloat16* abf = (__nv_bfloat16*)dev_alloc(m * (size_t)w.k * 2);
+    __nv_bfloat16* abf = (__nv_bfloat16*)dev_alloc_on(m * (size_t)w.k * 2, st);
     if (!abf) return fail(FQ_DECLINED_BUDGET, "bf16 activation scratch allocation failed");
     launch_f32_to_bf16(a_dev, abf, m * (size_t)w.k, st);
     g_trace.launches++;
     // up to 128 tokens: one tile column of 128 with alternating accumulators; above that 256-token tiles
     const int rc = launch_tc_rows(ctx, w, mat, abf, m, c_dev, ldc, nullptr, nullptr, 0, m <= 128 ? 128 : 256, st);
-    if (st != ctx->stream) cudaStreamSynchronize(st);
-    dev_free(abf);
+    dev_free_on(abf, st);  // stream-ordered reuse: no host wait
     return rc;
 }
 

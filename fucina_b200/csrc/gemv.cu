@@ -25,6 +25,9 @@
 
 namespace fq {
 
+// y extent of a grouped launch (the hardware limit; a test seam lowers it to exercise the striding walk)
+static int g_gemv_grid_y_limit = 65535;
+
 namespace {
 
 constexpr int kThreads = 256;
@@ -249,16 +252,19 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
     const ActSizes S = act_sizes(FMT, k);
     const int C = k / L.chunk_elems;
 
+    // grouped forms: blockIdx.y strides over the table entries (a table may be longer than the grid's y limit)
+    for (int entry = blockIdx.y;; entry += gridDim.y) {
     int mat = A.mat, m = A.m;
     const uint8_t* acts = A.acts;
     float* cbase = A.c;
     if (A.table != nullptr) {
-        if ((int)blockIdx.y >= *A.n_desc) return;
-        const GroupDesc d = A.table[blockIdx.y];
+        if (entry >= min(*A.n_desc, A.max_desc)) return;
+        const GroupDesc d = A.table[entry];
         mat = d.mat;
         m = d.m;
         acts += (size_t)d.row0 * S.row;
         cbase += (size_t)d.row0 * A.ldc;
+        if (entry != (int)blockIdx.y) __syncthreads();  // every thread is done with the previous entry's staged rows
     }
 
     // stage the m activation rows; the dense form zeroes the padded batch slots (they are multiplied), the
@@ -354,6 +360,8 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
             }
         }
     }
+    if (A.table == nullptr) return;
+    }
 }
 
 template <int FMT, int MB, int LPR, int MODE>
@@ -370,7 +378,8 @@ cudaError_t launch_one(const GemvArgs& a, int sm_count, cudaStream_t st) {
     const int groups_per_cta = kWarps * (32 / LPR);
     const long long groups = ((long long)a.w.n + rows_per_group - 1) / rows_per_group;
     long long ctas = (groups + groups_per_cta - 1) / groups_per_cta;
-    const long long ny = a.table ? (a.max_desc > 0 ? a.max_desc : 1) : 1;
+    long long ny = a.table ? (a.max_desc > 0 ? a.max_desc : 1) : 1;
+    if (ny > g_gemv_grid_y_limit) ny = g_gemv_grid_y_limit;  // the kernel strides over longer tables
     // grouped launches spread the SM budget over the table entries: about eight CTAs per SM in total, so a
     // CTA stages its group's activations once and then walks many weight rows
     long long cap = (long long)sm_count * 8 / ny;
@@ -415,9 +424,23 @@ cudaError_t launch_mb(const GemvArgs& a, int sm_count, cudaStream_t st) {
 }  // namespace
 
 size_t gemv_max_rows() { return 16; }
+void set_gemv_grid_y_limit(int limit) { g_gemv_grid_y_limit = limit < 1 ? 65535 : (limit > 65535 ? 65535 : limit); }
+
+// The kernel stages its (padded) activation rows in dynamic shared memory: pad(m) * act_sizes(fmt, k).row
+// bytes must fit the 227 KiB a CTA may opt in to.
+constexpr size_t kGemvSmemLimit = 227 * 1024;
+int gemv_padded_rows(size_t m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : m <= 8 ? 8 : 16; }
+int gemv_rows_that_fit(int fmt, size_t k) {
+    const ActSizes S = act_sizes(fmt, k);
+    if (S.row == 0) return 0;
+    for (int mb = 16; mb >= 1; mb >>= 1)
+        if ((size_t)mb * S.row <= kGemvSmemLimit) return mb;
+    return 0;
+}
 
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st) {
     if (a.m < 1 || a.m > 16) return cudaErrorInvalidValue;
+    if (gemv_padded_rows((size_t)a.m) > gemv_rows_that_fit(a.w.fmt, (size_t)a.w.k)) return cudaErrorInvalidValue;  // callers split or decline first
     switch (a.w.fmt) {
         case FQ_Q8_0: return launch_mb<FQ_Q8_0>(a, sm_count, st);
         case FQ_Q4_K: return launch_mb<FQ_Q4_K>(a, sm_count, st);

@@ -50,6 +50,11 @@ struct GemvArgs {
 };
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st);
 size_t gemv_max_rows();  // largest m one launch (or one table entry) handles
+// m padded to the row counts the kernel is instantiated for (1, 2, 4, 8, 16), and the largest such count whose
+// activation records fit a CTA's shared memory for this format and K (0: not even one row fits)
+void set_gemv_grid_y_limit(int limit);  // test seam: cap gridDim.y of grouped launches (<= 0 restores 65535)
+int gemv_padded_rows(size_t m);
+int gemv_rows_that_fit(int fmt, size_t k);
 
 // formats.cu -- natural-order activation records (actquant.cuh)
 cudaError_t launch_quantize_acts_natural(const float* a, int m, int k, bool q8k, uint8_t* out, cudaStream_t st);

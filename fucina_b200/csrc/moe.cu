@@ -316,7 +316,7 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
     const size_t o_xb = take((size_t)pairs * hidden * 2), o_gate = take(sizeof(float) * (size_t)pairs * out_pe);
     const size_t o_up = take(sizeof(float) * (size_t)pairs * out_pe), o_gb = take((size_t)pairs * out_pe * 2);
     const size_t o_down = take(sizeof(float) * (size_t)pairs * hidden);
-    uint8_t* s = (uint8_t*)dev_alloc(off);
+    uint8_t* s = (uint8_t*)dev_alloc_on(off, st);
     if (!s) return fail(FQ_DECLINED_BUDGET, "MoE scratch allocation of %zu bytes failed", off);
     int* order = (int*)(s + o_order);
     int* inv = (int*)(s + o_inv);
@@ -348,8 +348,7 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
     } while (false);
     g_trace.launches += 6;
     if (e != cudaSuccess) rc = cuda_fail(e, "MoE tensor-path launch");
-    if (st != ctx->stream) cudaStreamSynchronize(st);
-    dev_free(s);
+    dev_free_on(s, st);  // stream-ordered reuse: no host wait
     return rc;
 }
 
@@ -379,7 +378,12 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     // inside the kernel); other formats take the lane-per-chunk kernel with pre-quantised rows
     const int stream_rows = seq < expert_rows_max_group() ? seq : expert_rows_max_group();
     const bool streaming = expert_rows_eligible(gate, &up, stream_rows) && expert_rows_eligible(down, nullptr, stream_rows);
-    const int group_rows = streaming ? stream_rows : (seq < kGroupRows ? seq : kGroupRows);
+    // the lane-per-chunk kernel keeps a group's (padded) rows in shared memory: cut the group until both products fit
+    int fit_rows = gemv_rows_that_fit(fmt, (size_t)hidden);
+    if (gemv_rows_that_fit(fmt, (size_t)out_pe) < fit_rows) fit_rows = gemv_rows_that_fit(fmt, (size_t)out_pe);
+    if (!streaming && fit_rows == 0) return fail(FQ_DECLINED_ARGS, "expert rows of %d / %d elements are too long for the integer arm", hidden, out_pe);
+    const int int8_rows = kGroupRows < fit_rows ? kGroupRows : fit_rows;
+    const int group_rows = streaming ? stream_rows : (seq < int8_rows ? seq : int8_rows);
     const int max_desc = max_desc_for(pairs, n_expert, group_rows);
     // one scratch block: order, inv, n_desc, table, quantised x rows, g rows, quantised g rows, down rows
     size_t off = 0;
@@ -392,7 +396,7 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     const size_t o_table = take(sizeof(GroupDesc) * max_desc), o_qx = take(Sx.row * pairs);
     const size_t o_g = take(sizeof(float) * (size_t)pairs * out_pe), o_qg = take(Sg.row * pairs);
     const size_t o_down = take(sizeof(float) * (size_t)pairs * hidden);
-    uint8_t* scratch = (uint8_t*)dev_alloc(off);
+    uint8_t* scratch = (uint8_t*)dev_alloc_on(off, st);
     if (!scratch) return fail(FQ_DECLINED_BUDGET, "MoE scratch allocation of %zu bytes failed", off);
     int* order = (int*)(scratch + o_order);
     int* inv = (int*)(scratch + o_inv);
@@ -440,8 +444,7 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     } while (false);
     g_trace.launches += 6;
     if (e != cudaSuccess) rc = cuda_fail(e, "MoE layer launch");
-    if (st != ctx->stream) cudaStreamSynchronize(st);
-    dev_free(scratch);
+    dev_free_on(scratch, st);  // stream-ordered reuse: no host wait
     return rc;
 }
 
@@ -568,6 +571,7 @@ int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights*
 
 // Test seam in the spirit of setQuantMmaForTest (backend/cuda.zig:2563): -1 auto, 0 integer path, 1 tensor path.
 void fq_set_moe_tensor_for_test(int mode) { g_moe_tensor_mode = mode < 0 ? -1 : (mode ? 1 : 0); }
+void fq_set_group_grid_limit_for_test(int limit) { set_gemv_grid_y_limit(limit); }
 
 // ---- grouped GEMM over staged panels (backend/cuda.zig:2181-2333) ------------
 void fq_qmoe_lock(void) { g_qmoe_lock.lock(); }
@@ -607,16 +611,20 @@ extern "C" int fq_gemm_q_grouped_nt(int fmt, const void* rhs, size_t rhs_len, in
     int max_expert = 0;
     size_t rows = 0;
     std::vector<GroupDesc> descs;
+    // rows per table entry: as many as the kernel's shared memory holds for this K (at most 16)
+    const int fit_rows = gemv_rows_that_fit(fmt, k);
+    if (fit_rows == 0) return fail(FQ_DECLINED_ARGS, "k=%zu is too long for the grouped kernel", k);
+    const int group_rows = kGroupRows < fit_rows ? kGroupRows : fit_rows;
     for (size_t t = 0; t < n_tiles; ++t) {
         const fq_qmm_tile& tl = tiles[t];
         if (tl.expert < 0 || tl.base_row < 0 || tl.m <= 0 || tl.m > tl.tile_m) return fail(FQ_DECLINED_ARGS, "tile %zu is malformed", t);
         if (tl.expert > max_expert) max_expert = tl.expert;
         if ((size_t)tl.base_row + tl.m > rows) rows = (size_t)tl.base_row + tl.m;
-        for (int j = 0; j < tl.m; j += kGroupRows) descs.push_back({tl.expert, tl.base_row + j, tl.m - j < kGroupRows ? tl.m - j : kGroupRows, 0});
+        for (int j = 0; j < tl.m; j += group_rows) descs.push_back({tl.expert, tl.base_row + j, tl.m - j < group_rows ? tl.m - j : group_rows, 0});
     }
     if (rows * k * sizeof(float) > g_stage.in_bytes || rows * n_out * sizeof(float) > g_stage.out_bytes)
         return fail(FQ_DECLINED_ARGS, "tiles reach beyond the staged panels");
-    if (descs.size() > 65535) return fail(FQ_DECLINED_ARGS, "tile table too large for one launch (%zu row groups)", descs.size());
+    if (descs.size() > (size_t)INT32_MAX) return fail(FQ_DECLINED_ARGS, "tile table too large (%zu row groups)", descs.size());
     const size_t n_mats = (size_t)max_expert + 1;
     if (rhs_len < nb02 * (n_mats - 1) + nb01 * n_out) return fail(FQ_DECLINED_ARGS, "rhs_len too short for expert %d", max_expert);
     Ctx* ctx = context();
@@ -647,7 +655,7 @@ extern "C" int fq_gemm_q_grouped_nt(int fmt, const void* rhs, size_t rhs_len, in
             // rows no tile names keep whatever the out panel held: copy it up first
             if ((e = cudaMemcpyAsync(dev + o_out, g_stage.out, out_b, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
             if ((e = launch_quantize_acts_layout((const float*)dev, nullptr, 1, (int)rows, (int)k, fmt, dev + o_q, ctx->stream)) != cudaSuccess) break;
-            GemvArgs ga{view, DevWeights{}, 0, dev + o_q, (float*)(dev + o_out), kGroupRows, (int)n_out, 0, (const GroupDesc*)(dev + o_tab),
+            GemvArgs ga{view, DevWeights{}, 0, dev + o_q, (float*)(dev + o_out), group_rows, (int)n_out, 0, (const GroupDesc*)(dev + o_tab),
                         (const int*)(dev + o_nd), (int)descs.size()};
             if ((e = launch_gemv(ga, ctx->sm_count, ctx->stream)) != cudaSuccess) break;
             if ((e = cudaMemcpyAsync(g_stage.out, dev + o_out, out_b, cudaMemcpyDeviceToHost, ctx->stream)) != cudaSuccess) break;

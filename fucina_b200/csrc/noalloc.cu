@@ -11,8 +11,11 @@
 // decode kernel consumes live in one fixed array inside the library image.
 //
 // Limits and rules (also stated in include/fucina_b200.h):
-//   * m <= 16 activation rows and act_sizes(fmt, k).row * m <= kScratchBytes
-//     (512 KiB); larger requests are declined with a clear message.
+//   * m <= 16 activation rows; act_sizes(fmt, k).row * m <= kScratchBytes
+//     (512 KiB); and, because the kernel keeps the rows padded to 1/2/4/8/16
+//     in shared memory, act_sizes(fmt, k).row * pad(m) <= 227 KiB. A row is
+//     about 1.1 * k bytes (1.3 * k for Q8_0). Larger requests are declined
+//     with a clear message before anything is launched or written.
 //   * every GPU that loads the library holds the 512 KiB until process exit.
 //   * all calls share the array and it keeps the last call's contents; each
 //     call rewrites every byte it later reads, so nothing needs clearing, but
@@ -44,6 +47,7 @@ using namespace fq;
 extern "C" int fq_gemm_quant_nt_dev_noalloc(const fq_weights* w, size_t mat, const float* a_dev, float* c_dev, size_t m,
                                             void* stream) {
     if (!w || !a_dev || !c_dev) return fail(FQ_DECLINED_ARGS, "null pointer");
+    if (!gpu_enabled()) return fail(FQ_DECLINED_GATE, "disabled by FUCINA_GPU=0");
     Ctx* ctx = context_if_ready();
     if (!ctx) return fail(FQ_DECLINED_NO_GPU, "call fq_init before the allocation-free entry point");
     const DevWeights& dw = w->dw;
@@ -53,11 +57,16 @@ extern "C" int fq_gemm_quant_nt_dev_noalloc(const fq_weights* w, size_t mat, con
     const ActSizes S = act_sizes(dw.fmt, (size_t)dw.k);
     if (S.row == 0 || S.row * m > kScratchBytes)
         return fail(FQ_DECLINED_ARGS, "activation records need %zu bytes, the fixed scratch holds %zu", S.row * m, kScratchBytes);
+    // the kernel keeps the rows, padded to 1/2/4/8/16, in shared memory: that is the tighter bound for long rows
+    if (gemv_padded_rows(m) > gemv_rows_that_fit(dw.fmt, (size_t)dw.k))
+        return fail(FQ_DECLINED_ARGS, "%d padded activation rows of %zu bytes do not fit the kernel's 227 KiB of shared memory",
+                    gemv_padded_rows(m), S.row);
 
     std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cuda_fail(e, "cudaGetDevice");
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return fail(FQ_DECLINED_ARGS, "device ordinal %d is outside the %d this entry keeps an address for", dev, kMaxDevices);
     if (!g_scratch_ptr[dev]) {
         // set-up, once per device, with that device current
         void* p = nullptr;

@@ -37,6 +37,7 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 int cuda_fail(cudaError_t e, const char* what) {
+    cudaGetLastError();  // a launch or API error is reported once: the next healthy call must not find it
     return fail(FQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
@@ -149,6 +150,11 @@ static int init_locked(int device) {
     return FQ_OK;
 }
 
+bool gpu_enabled() {
+    ensure_config();
+    return g_cfg.gpu_enabled;
+}
+
 Ctx* context() {
     ensure_config();
     int st = g_init_state.load(std::memory_order_acquire);
@@ -186,8 +192,17 @@ int device_status(Ctx* ctx) {
 // caching allocators (the device-side twin of src/caching_allocator.zig's
 // size-class freelist; replaces the grow-only DeviceBuf / PinnedBuf of
 // backend/cuda.zig:873-890, :1026-1041). Blocks are recycled by class and
-// only returned to the driver by trim(). Reuse is safe because every consumer
-// of a recycled block is ordered on the library's compute stream.
+// only returned to the driver by trim().
+//
+// Reuse is stream-ordered: a block goes back to the cache together with the
+// stream of its last use and an event recorded there, and nothing waits on
+// the host. The next taker on the same stream is ordered by the stream
+// itself; a taker on another stream first makes its stream wait for that
+// event, so kernels still reading the block finish before the new owner's
+// first write. Blocks released while their stream is being captured into a
+// graph carry no event (an event recorded during capture cannot be waited on
+// outside it); a taker on another stream then waits for that stream on the
+// host.
 // ---------------------------------------------------------------------------
 static size_t size_class(size_t n) {
     if (n <= 512) return 512;
@@ -203,21 +218,40 @@ static size_t size_class(size_t n) {
 class BlockCache {
    public:
     explicit BlockCache(bool pinned) : pinned_(pinned) {}
-    void* alloc(size_t n) {
+    // `st`: the stream that touches the block first (ignored for pinned host blocks)
+    void* alloc(size_t n, cudaStream_t st) {
         const size_t c = size_class(n);
         std::lock_guard<std::mutex> g(lock_);
         auto it = free_.find(c);
         if (it != free_.end() && !it->second.empty()) {
-            void* p = it->second.back();
-            it->second.pop_back();
-            live_[p] = c;
+            std::vector<Cached>& v = it->second;
+            // a block whose last use is already ordered before `st` costs nothing
+            size_t pick = v.size() - 1;
+            for (size_t i = v.size(); i-- > 0;)
+                if (v[i].idle || v[i].stream == st) {
+                    pick = i;
+                    break;
+                }
+            Cached b = v[pick];
+            v.erase(v.begin() + pick);
+            if (!b.idle && b.stream != st) {
+                // a capturing stream cannot take an outside event as a dependency: wait on the host then
+                cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+                if (st && cudaStreamIsCapturing(st, &cs) != cudaSuccess) cudaGetLastError();
+                if (b.ev && cs == cudaStreamCaptureStatusNone) cudaStreamWaitEvent(st, b.ev, 0);
+                else if (b.ev) cudaEventSynchronize(b.ev);
+                else cudaStreamSynchronize(b.stream);
+            }
+            if (b.ev) events_.push_back(b.ev);
+            live_[b.p] = c;
             cached_ -= c;
-            return p;
+            return b.p;
         }
         void* p = nullptr;
         cudaError_t e = pinned_ ? cudaHostAlloc(&p, c, cudaHostAllocDefault) : cudaMalloc(&p, c);
         if (e != cudaSuccess) {
             // give cached blocks back to the driver and retry once
+            cudaGetLastError();
             trim_locked();
             e = pinned_ ? cudaHostAlloc(&p, c, cudaHostAllocDefault) : cudaMalloc(&p, c);
             if (e != cudaSuccess) {
@@ -229,12 +263,34 @@ class BlockCache {
         total_ += c;
         return p;
     }
-    void release(void* p) {
+    // `st`: the stream of the block's last use; `idle` = the host already waited for it
+    void release(void* p, cudaStream_t st, bool idle) {
         if (!p) return;
         std::lock_guard<std::mutex> g(lock_);
         auto it = live_.find(p);
         if (it == live_.end()) return;
-        free_[it->second].push_back(p);
+        Cached b{p, st, nullptr, idle || pinned_};
+        if (!b.idle) {
+            cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) cudaGetLastError();
+            if (cs == cudaStreamCaptureStatusNone) {
+                cudaEvent_t ev = nullptr;
+                if (!events_.empty()) {
+                    ev = events_.back();
+                    events_.pop_back();
+                } else if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) {
+                    cudaGetLastError();
+                    ev = nullptr;
+                }
+                if (ev && cudaEventRecord(ev, st) != cudaSuccess) {
+                    cudaGetLastError();
+                    events_.push_back(ev);
+                    ev = nullptr;
+                }
+                b.ev = ev;
+            }
+        }
+        free_[it->second].push_back(b);
         cached_ += it->second;
         live_.erase(it);
     }
@@ -245,10 +301,21 @@ class BlockCache {
     size_t total() const { return total_; }
 
    private:
+    struct Cached {
+        void* p;
+        cudaStream_t stream;
+        cudaEvent_t ev;
+        bool idle;
+    };
     void trim_locked() {
         for (auto& kv : free_)
-            for (void* p : kv.second) {
-                if (pinned_) cudaFreeHost(p); else cudaFree(p);
+            for (Cached& b : kv.second) {
+                if (!b.idle) {
+                    if (b.ev) cudaEventSynchronize(b.ev);
+                    else cudaStreamSynchronize(b.stream);
+                }
+                if (b.ev) events_.push_back(b.ev);
+                if (pinned_) cudaFreeHost(b.p); else cudaFree(b.p);
                 total_ -= kv.first;
             }
         free_.clear();
@@ -256,16 +323,20 @@ class BlockCache {
     }
     bool pinned_;
     std::mutex lock_;
-    std::map<size_t, std::vector<void*>> free_;
+    std::map<size_t, std::vector<Cached>> free_;
     std::unordered_map<void*, size_t> live_;
+    std::vector<cudaEvent_t> events_;
     size_t total_ = 0, cached_ = 0;
 };
 static BlockCache g_dev_cache(false), g_pin_cache(true);
 
-void* dev_alloc(size_t n) { return g_dev_cache.alloc(n); }
-void dev_free(void* p) { g_dev_cache.release(p); }
-void* pin_alloc(size_t n) { return g_pin_cache.alloc(n); }
-void pin_free(void* p) { g_pin_cache.release(p); }
+// Without a stream argument a block belongs to the library's compute stream.
+void* dev_alloc(size_t n) { return g_dev_cache.alloc(n, g_ctx.stream); }
+void dev_free(void* p) { g_dev_cache.release(p, g_ctx.stream, false); }
+void* dev_alloc_on(size_t n, cudaStream_t st) { return g_dev_cache.alloc(n, st); }
+void dev_free_on(void* p, cudaStream_t st) { g_dev_cache.release(p, st, false); }
+void* pin_alloc(size_t n) { return g_pin_cache.alloc(n, nullptr); }
+void pin_free(void* p) { g_pin_cache.release(p, nullptr, true); }
 
 // ---------------------------------------------------------------------------
 // weights
@@ -469,7 +540,7 @@ int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* 
     // dense decode shapes: the row-per-lane kernel with TMA-staged weights
     if (!accumulate && g_decode_rows_on && decode_rows_eligible(w, m)) {
         const size_t sb = decode_rows_scratch_bytes(w, m);
-        uint8_t* nat = sb ? (uint8_t*)dev_alloc(sb) : nullptr;
+        uint8_t* nat = sb ? (uint8_t*)dev_alloc_on(sb, st) : nullptr;
         if (sb && !nat) return fail(FQ_DECLINED_BUDGET, "activation scratch allocation failed");
         cudaEvent_t t0 = nullptr, t1 = nullptr;
         if (g_ktime_on) {
@@ -483,16 +554,15 @@ int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* 
             g_ktime_events.emplace_back(t0, t1);
         }
         g_trace.launches += sb ? 2 : 1;
-        if (nat) {
-            if (st != ctx->stream) cudaStreamSynchronize(st);
-            dev_free(nat);
-        }
+        dev_free_on(nat, st);  // stream-ordered reuse: no host wait
         return e == cudaSuccess ? FQ_OK : cuda_fail(e, "decode launch");
     }
     const ActSizes S = act_sizes(w.fmt, w.k);
-    const size_t chunk_max = gemv_max_rows();
+    // rows per launch: what the kernel is instantiated for, cut down until the padded rows fit its shared memory
+    const size_t chunk_max = (size_t)gemv_rows_that_fit(w.fmt, (size_t)w.k);
+    if (chunk_max == 0) return fail(FQ_DECLINED_ARGS, "k=%d is too long for the small-batch kernel (one activation row needs %zu bytes of shared memory)", w.k, S.row);
     const size_t rows_scratch = m < chunk_max ? m : chunk_max;
-    uint8_t* scratch = (uint8_t*)dev_alloc(S.row * rows_scratch);
+    uint8_t* scratch = (uint8_t*)dev_alloc_on(S.row * rows_scratch, st);
     if (!scratch) return fail(FQ_DECLINED_BUDGET, "activation scratch allocation failed");
     int rc = FQ_OK;
     for (size_t r0 = 0; r0 < m && rc == FQ_OK; r0 += chunk_max) {
@@ -515,10 +585,9 @@ int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* 
         g_trace.launches++;
         if (e != cudaSuccess) rc = cuda_fail(e, "gemv launch");
     }
-    // the scratch block returns to the cache now; any later user is ordered after
-    // these kernels because all library work runs on one stream
-    if (st != ctx->stream) cudaStreamSynchronize(st);
-    dev_free(scratch);
+    // the scratch block returns to the cache with its stream and an event: a later taker is
+    // ordered after these kernels without a host wait
+    dev_free_on(scratch, st);
     return rc;
 }
 
@@ -943,7 +1012,9 @@ int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheab
 
 int fq_work_finish(fq_work* w, int copy_to_host) {
     if (!w) return fail(FQ_DECLINED_ARGS, "null work");
-    if (w->state == 1 || w->state == 2) return FQ_OK;
+    // host_ready, or waited without a copy and still none asked for: nothing left to do. A token that was
+    // waited on first (copy_to_host = 0) and is now asked for the host copy falls through and downloads.
+    if (w->state == 1 || (w->state == 2 && !(copy_to_host && w->c_host))) return FQ_OK;
     if (w->state < 0) return FQ_ERR_CUDA;
     Ctx* ctx = context();
     if (!ctx) return FQ_DECLINED_NO_GPU;
@@ -999,6 +1070,11 @@ int fq_gemm_quant_nt_dev(const fq_weights* w, size_t mat, const float* a_dev, fl
     g_trace.calls++;
     return gemm_dev(ctx, w->dw, (int)mat, a_dev, c_dev, m, (size_t)w->dw.n, mode, 0, stream ? (cudaStream_t)stream : ctx->stream);
 }
+int fq_small_batch_max_rows(int fmt, size_t k) {
+    const FormatInfo f = format_info(fmt);
+    if (!f.block_elems || k == 0 || k % f.block_elems != 0 || k % 32 != 0) return 0;
+    return gemv_rows_that_fit(fmt, k);
+}
 int fq_gemm_ptqtp_dev(const fq_weights* const* planes, int n_planes, const float* a_dev, float* c_dev, size_t m, void* stream) {
     if (!planes || n_planes < 1 || n_planes > 3 || !a_dev || !c_dev) return fail(FQ_DECLINED_ARGS, "bad plane list");
     for (int p = 0; p < n_planes; ++p) {
@@ -1013,7 +1089,7 @@ int fq_gemm_ptqtp_dev(const fq_weights* const* planes, int n_planes, const float
     const size_t n = (size_t)planes[0]->dw.n;
     if (m > gemv_max_rows() && tensor_path_serves(planes[0]->dw) && (m * n) % 4 == 0) {
         // prefill-sized: each plane is a tensor-core product, summed per element in plane order (weights.zig:286-300)
-        float* tmp = n_planes > 1 ? (float*)dev_alloc(m * n * sizeof(float)) : nullptr;
+        float* tmp = n_planes > 1 ? (float*)dev_alloc_on(m * n * sizeof(float), st) : nullptr;
         if (n_planes > 1 && !tmp) return fail(FQ_DECLINED_BUDGET, "plane scratch allocation failed");
         int rc = FQ_OK;
         for (int p = 0; p < n_planes && rc == FQ_OK; ++p) {
@@ -1024,10 +1100,7 @@ int fq_gemm_ptqtp_dev(const fq_weights* const* planes, int n_planes, const float
                 if (e != cudaSuccess) rc = cuda_fail(e, "plane sum launch");
             }
         }
-        if (tmp) {
-            if (st != ctx->stream) cudaStreamSynchronize(st);
-            dev_free(tmp);
-        }
+        dev_free_on(tmp, st);
         return rc;
     }
     for (int p = 0; p < n_planes; ++p) {

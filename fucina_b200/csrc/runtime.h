@@ -34,11 +34,17 @@ extern std::recursive_mutex g_dispatch_lock;
 
 int fail(int code, const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
+bool gpu_enabled();  // false when FUCINA_GPU=0 switched the provider off
 Ctx* context();
 Ctx* context_if_ready();  // the context only if it already exists; never creates it
 int device_status(Ctx* ctx);  // FQ_OK, or the code a kernel's bounded wait left behind (then cleared)
+// Device blocks from the caching allocator. Reuse is stream-ordered: the plain forms belong to the
+// library's compute stream, the *_on forms name the stream that touches the block first (alloc) or
+// last (free); neither waits on the host.
 void* dev_alloc(size_t n);
 void dev_free(void* p);
+void* dev_alloc_on(size_t n, cudaStream_t st);
+void dev_free_on(void* p, cudaStream_t st);
 void* pin_alloc(size_t n);
 void pin_free(void* p);
 

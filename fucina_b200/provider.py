@@ -228,6 +228,11 @@ def gemm_quant_nt_dev_noalloc(w: Weights, a_dev, c_dev, m: int, mat: int = 0, st
     _check(load().fq_gemm_quant_nt_dev_noalloc(w.handle, mat, _vp(a_dev), _vp(c_dev), m, C.c_void_p(stream)))
 
 
+def small_batch_max_rows(fmt: int, k: int) -> int:
+    """Rows one launch of the small-batch integer kernel takes for this format and k (0: none fit)."""
+    return int(load().fq_small_batch_max_rows(fmt, k))
+
+
 def gemm_ptqtp_dev(planes: list[Weights], a_dev, c_dev, m: int, stream: int = 0) -> None:
     """K ternary planes summed per element in plane order (src/weights.zig:204-300)."""
     arr = (C.c_void_p * len(planes))(*[p.handle for p in planes])

@@ -164,14 +164,23 @@ FQ_API int fq_gemm_quant_nt_dev(const fq_weights* w, size_t mat, const float* a_
  * stall of a cudaMalloc, memory owned by an external pool. Same result as
  * fq_gemm_quant_nt_dev in FQ_MODE_INT8 for m <= 16, but the int8 activation
  * records live in a fixed 512 KiB array inside the library image instead of
- * the caching allocator: act bytes per row (about 1.4 * k) times m must fit,
- * otherwise the call is declined. Every GPU that loads the library holds the
+ * the caching allocator. Two bounds, both checked before anything is launched
+ * or written: the records of the m rows must fit the array (a record is about
+ * 1.1 * k bytes, 1.4 * k for Q8_0), and the kernel keeps the rows -- padded to
+ * 1, 2, 4, 8 or 16 -- in shared memory, so pad(m) records must fit 227 KiB
+ * (fq_small_batch_max_rows gives the largest m for a format and k); otherwise
+ * the call is declined. Every GPU that loads the library holds the
  * array until exit. All calls share it, so calls that overlap on the GPU
  * race; order them on one stream. The first call on a device resolves the
  * array's address: make it before any stream capture. fq_init must have been
  * called; this entry creates nothing. */
 FQ_API int fq_gemm_quant_nt_dev_noalloc(const fq_weights* w, size_t mat, const float* a_dev, float* c_dev, size_t m,
                                         void* stream);
+/* Largest number of activation rows one launch of the small-batch integer
+ * kernel takes for this format and k: 16, 8, 4, 2, 1, or 0 when not even one
+ * row's int8 records fit a CTA's shared memory. Larger batches are served in
+ * chunks of this size by fq_gemm_quant_nt_dev; needs no device. (New.) */
+FQ_API int fq_small_batch_max_rows(int fmt, size_t k);
 /* K planes of one PTQTP weight summed per element in plane order
  * (weights.zig:204-300 `linearSeqPtqtpFused`). */
 FQ_API int fq_gemm_ptqtp_dev(const fq_weights* const* planes, int n_planes, const float* a_dev, float* c_dev, size_t m,
@@ -238,6 +247,9 @@ FQ_API void fq_set_decode_for_test(int enabled);
  * -1 automatic (tensor cores once a batch averages >= 20 rows per expert, else the int8 decode
  * arm), 0 always the int8 arm, 1 the tensor-core arm whenever the format has one. */
 FQ_API void fq_set_moe_tensor_for_test(int mode);
+/* Grouped integer launches put one table entry per grid row and stride over tables longer than the
+ * grid's y limit (65535); this lowers the limit so a small case walks the striding path (<= 0 restores it). */
+FQ_API void fq_set_group_grid_limit_for_test(int limit);
 /* Failure-detection seam (no counterpart in the reference): every device-side wait in this library is
  * bounded and reports FQ_ERR_TIMEOUT through a status word instead of hanging. This launches one warp that
  * polls `limit` times (1..2^20) a barrier nothing completes, gives up the same way and returns normally; the

@@ -128,3 +128,25 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(L, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(ImportError):
         L.load()
+
+
+def test_small_batch_row_limit_follows_shared_memory(lib):
+    # the small-batch kernel keeps pad(m) activation records in <= 227 KiB of shared memory
+    from fucina_b200 import formats as F
+
+    def record(fmt, k):
+        chunk, act_block = {F.Q8_0: (16, 32), F.Q4_K: (32, 256), F.Q5_K: (32, 256), F.TQ2_0: (64, 256),
+                            F.TQ2_0_FOLDED: (32, 256), F.Q2_0: (64, 32)}[fmt]
+        pad16 = lambda v: (v + 15) & ~15
+        return k + pad16(k // chunk * 4) + pad16(k // act_block * 4)
+
+    for fmt in (F.Q8_0, F.Q4_K, F.Q5_K, F.TQ2_0, F.TQ2_0_FOLDED, F.Q2_0):
+        for k in (256, 4096, 11008 - 11008 % 256, 14336, 16384, 28672, 65536, 262144):
+            want = next((mb for mb in (16, 8, 4, 2, 1) if mb * record(fmt, k) <= 227 * 1024), 0)
+            assert lib.fq_small_batch_max_rows(fmt, k) == want, (fmt, k)
+    assert lib.fq_small_batch_max_rows(F.Q4_K, 4096) == 16
+    assert lib.fq_small_batch_max_rows(F.Q4_K, 28672) == 4       # the window the shared-memory rule closes
+    assert lib.fq_small_batch_max_rows(F.Q8_0, 16384) == 8
+    assert lib.fq_small_batch_max_rows(F.Q4_K, 262144) == 0
+    assert lib.fq_small_batch_max_rows(F.Q6_K, 4096) == 0        # format not served
+    assert lib.fq_small_batch_max_rows(F.Q4_K, 100) == 0         # not a whole number of blocks

@@ -84,3 +84,24 @@ def test_sizes_beyond_the_fixed_scratch_are_declined(P, torch):
     P.synchronize()
     assert float(c.min()) == 7.0  # nothing was written
     w.free()
+
+
+def test_rows_that_fit_the_array_but_not_shared_memory_are_declined(P, torch):
+    # 16 rows of k = 16384 (Q8_0) are 352 KiB of records -- inside the 512 KiB array -- but the kernel keeps
+    # them in shared memory, which holds 227 KiB: declined before anything is launched or written
+    n, k = 64, 16384
+    assert 8 <= P.small_batch_max_rows(oracle.Q8_0, k) < 16
+    blocks = make_weights("q8_0", n, k, seed=36)
+    w = P.Weights.upload(oracle.Q8_0, blocks, n, k)
+    a = np.random.default_rng(37).standard_normal((16, k)).astype(np.float32)
+    ad = torch.from_numpy(a).cuda()
+    c = torch.full((16, n), 7.0, dtype=torch.float32, device="cuda")
+    with pytest.raises(P.Declined) as e:
+        P.gemm_quant_nt_dev_noalloc(w, ad, c, 16)
+    assert e.value.code == 1 and "shared memory" in str(e.value)
+    P.synchronize()
+    assert float(c.min()) == 7.0 and float(c.max()) == 7.0
+    # eight rows fit both bounds and still give the regular entry's numbers
+    got, ref = _both(P, torch, w, a[:8], n)
+    assert_close(got, ref, TOL_INT8, "m=8 after the decline")
+    w.free()
