@@ -83,6 +83,7 @@ SIGNATURES = {
     "fq_set_decode_for_test": (None, [c_int]),
     "fq_set_moe_tensor_for_test": (None, [c_int]),
     "fq_set_group_grid_limit_for_test": (None, [c_int]),
+    "fq_moe_layer_stages_for_test": (c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_void, c_void, c_void]),
     "fq_selftest_bounded_wait": (c_int, [C.c_uint]),
     "fq_trace_enabled": (c_int, []),
     "fq_trace_reset": (None, []),

@@ -264,6 +264,21 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int rows, i
 
 int max_desc_for(int pairs, int n_expert, int group_rows);
 
+// Test seam of the integer arm: copy the per-pair intermediates out in PAIR order (row p = token p / top_k,
+// slot p % top_k): g = swiglu(gate . qx, up . qx) and the unweighted down rows. Pairs another shard serves get zeros.
+__global__ void stages_to_pair_order_kernel(const float* __restrict__ sorted_rows, const int* __restrict__ inv, int pairs, int width,
+                                            float* __restrict__ out) {
+    const size_t total = (size_t)pairs * width;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int p = (int)(i / width), pos = inv[p];
+        out[i] = pos < 0 ? 0.0f : sorted_rows[(size_t)pos * width + i % width];
+    }
+}
+struct StageTaps {
+    float* g_pairs;     // [pairs][out_pe] or nullptr
+    float* down_pairs;  // [pairs][hidden] or nullptr
+};
+
 // ---- tensor-core form for prefill-sized batches ------------------------------------------------
 // sorted pair position -> bf16 copy of its token row
 __global__ void gather_bf16_kernel(const float* __restrict__ x, const int* __restrict__ order, int top_k, const int* __restrict__ n_rows,
@@ -361,14 +376,15 @@ int max_desc_for(int pairs, int n_expert, int group_rows) {
 
 int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
                        int seq, int top_k, const int* selected_dev, const float* weights_dev, Shard shard, float* out_dev,
-                       cudaStream_t st) {
+                       cudaStream_t st, StageTaps taps = StageTaps{nullptr, nullptr}) {
     const int hidden = gate.k, out_pe = gate.n, n_expert = gate.n_mats, fmt = gate.fmt;
     const int pairs = seq * top_k;
     // prefill-sized batches: bf16 tensor-core products (the reference's own GPU arm multiplies rounded
     // operands too); decode-sized batches keep the CPU kernels' int8 arithmetic
     // the grouped tensor-core form is exercised for the formats expert stacks come in (K-quants and Q8_0)
     const bool tc_ok = (fmt == FQ_Q4_K || fmt == FQ_Q5_K || fmt == FQ_Q8_0) && tensor_path_serves(gate) && tensor_path_serves(down);
-    if (tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 14 * n_expert)))
+    const bool tapped = taps.g_pairs || taps.down_pairs;  // the taps read the integer arm's intermediates
+    if (!tapped && tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 14 * n_expert)))
         return moe_layer_tensor_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, shard, out_dev, st);
     const ActSizes Sx = act_sizes(fmt, hidden), Sg = act_sizes(fmt, out_pe);
     // Row tile of the grouped kernel. A router sends a token to distinct experts, so an expert's run is
@@ -443,6 +459,11 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
         e = cudaGetLastError();
     } while (false);
     g_trace.launches += 6;
+    if (e == cudaSuccess && rc == FQ_OK && tapped) {
+        if (taps.g_pairs) stages_to_pair_order_kernel<<<148 * 4, 256, 0, st>>>(g, inv, pairs, out_pe, taps.g_pairs);
+        if (taps.down_pairs) stages_to_pair_order_kernel<<<148 * 4, 256, 0, st>>>(down_rows, inv, pairs, hidden, taps.down_pairs);
+        e = cudaGetLastError();
+    }
     if (e != cudaSuccess) rc = cuda_fail(e, "MoE layer launch");
     dev_free_on(scratch, st);  // stream-ordered reuse: no host wait
     return rc;
@@ -567,6 +588,21 @@ int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights*
     dev_free(dev);
     pin_free(pin);
     return rc;
+}
+
+// Test seam: the integer arm of the layer with its two intermediates copied out in pair order, so a test
+// can hold each stage to the f32 tolerance separately (g against the CPU kernels' g; the down product
+// fed the device's own g against the CPU kernels fed the same g).
+int fq_moe_layer_stages_for_test(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev, size_t seq,
+                                 size_t top_k, const int32_t* selected_dev, const float* weights_dev, float* g_pairs_dev,
+                                 float* down_pairs_dev, float* out_dev) {
+    if (int rc = check_moe(gate, up, down, seq, top_k, 0)) return rc;
+    if (!x_dev || !selected_dev || !weights_dev || !out_dev) return fail(FQ_DECLINED_ARGS, "null pointer");
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    return moe_layer_dev_impl(ctx, gate->dw, up->dw, down->dw, x_dev, (int)seq, (int)top_k, selected_dev, weights_dev, Shard{0, 0},
+                              out_dev, ctx->stream, StageTaps{g_pairs_dev, down_pairs_dev});
 }
 
 // Test seam in the spirit of setQuantMmaForTest (backend/cuda.zig:2563): -1 auto, 0 integer path, 1 tensor path.

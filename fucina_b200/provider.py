@@ -318,6 +318,14 @@ def moe_layer_dev(gate: Weights, up: Weights, down: Weights, x_dev, seq: int, to
                                    _vp(weights_dev), gated_op, _vp(out_dev), C.c_void_p(stream)))
 
 
+def moe_layer_stages_for_test(gate: Weights, up: Weights, down: Weights, x_dev, seq: int, top_k: int, selected_dev,
+                              weights_dev, g_pairs_dev, down_pairs_dev, out_dev) -> None:
+    """The layer's integer arm with g and the unweighted down rows copied out in pair order (test seam)."""
+    _check(load().fq_moe_layer_stages_for_test(gate.handle, up.handle, down.handle, _vp(x_dev), seq, top_k,
+                                               _vp(selected_dev), _vp(weights_dev), _vp(g_pairs_dev),
+                                               _vp(down_pairs_dev), _vp(out_dev)))
+
+
 def moe_layer_ep_dev(gate: Weights, up: Weights, down: Weights, x_dev, seq: int, top_k: int, selected_dev, weights_dev,
                      expert_base: int, partial_dev, gated_op: int = 0, stream: int = 0) -> None:
     """This shard's partial output of the layer: experts [expert_base, expert_base + E_local), global ids in

@@ -247,6 +247,14 @@ FQ_API void fq_set_decode_for_test(int enabled);
  * -1 automatic (tensor cores once a batch averages >= 20 rows per expert, else the int8 decode
  * arm), 0 always the int8 arm, 1 the tensor-core arm whenever the format has one. */
 FQ_API void fq_set_moe_tensor_for_test(int mode);
+/* The integer arm of fq_moe_layer_dev with its two intermediates copied out in pair order
+ * (row p = token p / top_k, slot p % top_k): g_pairs_dev [seq*top_k, out_pe] receives
+ * swiglu(gate . qx, up . qx) (exec/moe.zig:890-920 before the requantisation of g) and
+ * down_pairs_dev [seq*top_k, hidden] the unweighted down rows; either may be NULL. Lets a test hold
+ * each stage to the f32 tolerance on its own. Library stream. */
+FQ_API int fq_moe_layer_stages_for_test(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev,
+                                        size_t seq, size_t top_k, const int32_t* selected_dev, const float* weights_dev,
+                                        float* g_pairs_dev, float* down_pairs_dev, float* out_dev);
 /* Grouped integer launches put one table entry per grid row and stride over tables longer than the
  * grid's y limit (65535); this lowers the limit so a small case walks the striding path (<= 0 restores it). */
 FQ_API void fq_set_group_grid_limit_for_test(int limit);

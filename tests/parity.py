@@ -58,3 +58,20 @@ def make_weights(fmt_name: str, n: int, k: int, seed: int):
         t2 = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
         return oracle.fold_planes(oracle.pack_ptqtp_plane(trits, fine * 3), oracle.pack_ptqtp_plane(t2, fine), k)
     raise ValueError(fmt_name)
+
+
+def round_bf16(a: np.ndarray) -> np.ndarray:
+    """f32 -> nearest bf16 (ties to even) -> f32, the rounding the tensor-core path applies to its operands."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    r = ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)).astype(np.uint32)
+    return r.view(np.float32)
+
+
+def oracle_b(fmt: int, blocks: np.ndarray, a: np.ndarray, k: int) -> np.ndarray:
+    """Oracle B at sizes the scalar C loop would take minutes for: f64 BLAS product of the oracle-dequantised
+    weights and the activations, both rounded to bf16 first (the reference's GPU-test oracle,
+    src/backend/cuda.zig:3016-3044, with the tensor-core operand precision)."""
+    import oracle
+
+    w = round_bf16(oracle.dequantize_rows(fmt, blocks, k)).astype(np.float64)
+    return round_bf16(a).astype(np.float64) @ w.T

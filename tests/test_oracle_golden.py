@@ -182,3 +182,19 @@ def test_simd_baseline_equals_the_scalar_oracle():
     w = make_weights("q8_0", 32, 256, seed=1)
     a = np.random.default_rng(2).standard_normal((2, 256)).astype(np.float32)
     assert np.array_equal(oracle.matmul(oracle.Q8_0, w, a), oracle.matmul_fast(oracle.Q8_0, w, a))
+
+
+def test_blas_form_of_oracle_b_equals_the_scalar_one():
+    # tests/parity.py:oracle_b is what the full-size GPU cases use; on a small case it must be the C oracle's number
+    from parity import make_weights, oracle_b, round_bf16
+
+    for name, k in (("q4_k", 512), ("q5_k", 256), ("q8_0", 96), ("tq2_0", 512)):
+        fmt = oracle.FORMATS[name]
+        b = make_weights(name, 24, k, seed=5)
+        a = np.random.default_rng(6).standard_normal((7, k)).astype(np.float32)
+        want = oracle.matmul_dequant_f64(fmt, b, a, round_bf16=True)
+        got = oracle_b(fmt, b, a, k)
+        assert np.abs(got - want).max() <= 1e-12 * max(1.0, np.abs(want).max())
+    x = np.array([1.0, 1.00390625, 1.01171875, -3.0e-39, 65504.0], np.float32)  # exact, tie to even, tie up, subnormal, large
+    r = round_bf16(x)
+    assert r[0] == 1.0 and r[1] == 1.0 and r[2] == np.float32(1.015625)
