@@ -21,9 +21,21 @@ rotated so every step streams its weights from HBM.
           rotated weight copies, against the measured HBM copy bandwidth.
 `cpu_baseline` the CPU restatement of the reference kernels on the host cores.
 
+`sub`     one record per other configuration of the metric, measured in the same
+          run: Q8_0 GEMV 4096^2 (GB/s), Q4_K prefill 512 / 2048 x 14336 x 4096
+          (TFLOP/s), the Q5_K MoE layer at 1 / 64 / 1024 tokens (tok/s) and the
+          ternary 8192^2 products, each with its roofline fraction and its own
+          CPU baseline (all host threads and one thread).
+
+The timed region of `value` is R repeats of the K-step sequence between one
+pair of CUDA events (R chosen so that the region lasts about half a second and
+the clock sampler sees it); ms_per_step = elapsed / (R * K).
+
 With --gpus N > 1 every rank serves its own decode stream from its own weight
 replica (weak scaling, no collective on the data path); time is the max over
-ranks.
+ranks. `sub` then carries the two exchange forms instead: the expert-parallel
+MoE layer (weak: 1024 tokens per GPU; strong: 1024 in total) and the
+column-sharded prefill with its all-gather.
 """
 from __future__ import annotations
 
@@ -61,6 +73,18 @@ def measured_peaks() -> tuple[float, str]:
         except Exception:
             pass
     return 6650.0, "fallback"
+
+
+def measured_tflops() -> tuple[float, float, str]:
+    """(burst, sustained) dense bf16 TFLOP/s of this pool's B200s, and where the numbers come from."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+        except Exception:
+            pass
+    return 1590.0, 1400.0, "fallback"
 
 
 class ClockSampler:
@@ -125,8 +149,11 @@ def dist_setup(n_gpus: int):
     if world > 1:
         import torch.distributed as dist
 
+        import datetime
+
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # a bounded group timeout: a rank that failed must end the others' next collective, not hang them
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=300))
     return rank, world, local
 
 
@@ -209,28 +236,30 @@ def run_ours(args) -> dict:
         for c in range(n_copies):
             step_dev(c)
     step_cycle = cap.graph
-    # the dominant kernel alone (the 32000 x 4096 lm_head product), one launch per copy
-    big = max(range(len(STACK_N)), key=lambda i: STACK_N[i])
-    big_graphs = []
-    for c in range(n_copies):
-        with P.capture() as cap:
-            P.gemm_quant_nt_dev(stacks[c].weights[big], xs[big], ys[big], batch, mode=P.MODE_INT8)
-        big_graphs.append(cap.graph)
-    with P.capture() as cap:
-        for c in range(n_copies):
-            P.gemm_quant_nt_dev(stacks[c].weights[big], xs[big], ys[big], batch, mode=P.MODE_INT8)
-    big_cycle = cap.graph
 
-    def timed_graphs(cycle, graphs, steps: int) -> float:
-        """Exactly `steps` steps: whole cycles of n_copies steps, then single-step graphs."""
+    def product_graphs(i: int):
+        """Product i of the stack alone: one launch per weight copy, and the cycle over all copies."""
+        singles = []
+        for c in range(n_copies):
+            with P.capture() as cap:
+                P.gemm_quant_nt_dev(stacks[c].weights[i], xs[i], ys[i], batch, mode=P.MODE_INT8)
+            singles.append(cap.graph)
+        with P.capture() as cap:
+            for c in range(n_copies):
+                P.gemm_quant_nt_dev(stacks[c].weights[i], xs[i], ys[i], batch, mode=P.MODE_INT8)
+        return cap.graph, singles
+
+    def timed_graphs(cycle, graphs, steps: int, repeats: int = 1) -> float:
+        """milliseconds of `repeats` x (exactly `steps` steps: whole cycles of n_copies steps, then single-step graphs)."""
         barrier(world)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(ext):
             e0.record()
-            for _ in range(steps // n_copies):
-                cycle.launch()
-            for i in range(steps % n_copies):
-                graphs[i].launch()
+            for _ in range(repeats):
+                for _ in range(steps // n_copies):
+                    cycle.launch()
+                for i in range(steps % n_copies):
+                    graphs[i].launch()
             e1.record()
         P.synchronize()
         barrier(world)
@@ -238,41 +267,52 @@ def run_ours(args) -> dict:
 
     for i in range(max(args.warmup, 3)):
         step_graphs[i % n_copies].launch()
-        big_graphs[i % n_copies].launch()
         step_cycle.launch()
-        big_cycle.launch()
     P.synchronize()
 
     # ---- value: resident inputs, CUDA events on the library stream ----
+    # R repeats of the K-step sequence inside one timed region of about half a second, so the clock
+    # sampler (100 ms period) describes the region that was timed
+    est = timed_graphs(step_cycle, step_graphs, args.steps) / args.steps  # ms per step, first estimate
+    repeats = max(1, min(200000, int(500.0 / max(est * args.steps, 1e-3))))
     with ClockSampler(local) as clk:
-        ms = timed_graphs(step_cycle, step_graphs, args.steps)
-        # keep the sampler busy for short runs so it sees the clocks under load
-        t_end = time.time() + 0.6
-        while time.time() < t_end:
-            step_cycle.launch()
-            P.synchronize()
+        ms = timed_graphs(step_cycle, step_graphs, args.steps, repeats)
     # one decode kernel per product with the activation quantisation fused in (batch <= 4); wider batches
     # quantise in a kernel of their own first
-    launches = args.steps * len(STACK_N) * (1 if batch <= 4 else 2)
+    launches = repeats * args.steps * len(STACK_N) * (1 if batch <= 4 else 2)
     bytes_step = stack_bytes(batch)
-    value = world * bytes_step * args.steps / (ms * 1e-3) / 1e9
+    ms_step = ms / (repeats * args.steps)
+    value = world * bytes_step / (ms_step * 1e-3) / 1e9
 
-    # ---- roofline: the dominant kernel alone, back-to-back launches over the rotated copies ----
-    k_n = args.steps
-    k_ms = timed_graphs(big_cycle, big_graphs, k_n)
+    # ---- roofline: each product alone, back-to-back launches over the rotated copies; the dominant one is the headline kernel ----
     peak, peak_src = measured_peaks()
-    per_launch_bytes = STACK_N[big] * ROW_BYTES + batch * K * 4 + batch * STACK_N[big] * 4
-    achieved = per_launch_bytes / (k_ms / k_n * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                "frac": round(achieved / peak, 4),
+    big = max(range(len(STACK_N)), key=lambda i: STACK_N[i])
+    per_product = []
+    k_n = max(args.steps, n_copies)
+    for i, n in enumerate(STACK_N):
+        cyc, singles = product_graphs(i)
+        for _ in range(3):
+            cyc.launch()
+        P.synchronize()
+        one = timed_graphs(cyc, singles, k_n) / k_n
+        reps = max(1, min(200000, int(100.0 / max(one * k_n, 1e-3))))  # about 0.1 s per product
+        k_ms = timed_graphs(cyc, singles, k_n, reps) / (reps * k_n)
+        nbytes = n * ROW_BYTES + batch * K * 4 + batch * n * 4
+        per_product.append({"n": n, "k": K, "us_per_launch": round(k_ms * 1e3, 3), "bytes_per_launch": nbytes,
+                            "GBps": round(nbytes / (k_ms * 1e-3) / 1e9, 1), "frac": round(nbytes / (k_ms * 1e-3) / 1e9 / peak, 4),
+                            "launches_timed": reps * k_n})
+        del cyc, singles
+    dom = per_product[big]
+    roofline = {"bound": "hbm", "achieved": dom["GBps"], "peak": peak, "unit": "GB/s", "frac": dom["frac"],
                 # dram__bytes_read + dram__bytes_write of one profiler capture of the same kernel on a 65536-row
                 # matrix (151.31 MB + 3.46 MB), scaled to this launch by rows (traffic is proportional to rows)
                 "traffic": int((151_309_056 + 3_462_656) * STACK_N[big] / 65536),
                 "traffic_source": "ncu capture of a 65536 x 4096 case, scaled by rows",
-                "kernel": "decode_rows_kernel<Q4_K, MB=1, fused act-quant> on 32000x4096",
-                "peak_source": peak_src, "launches_timed": k_n,
-                "timing": "CUDA events around back-to-back launches (graph replay, consecutive launches overlap by programmatic dependent launch)", "us_per_launch": round(k_ms / k_n * 1e3, 3),
-                "bytes_per_launch": per_launch_bytes, "frac_of_8TBs": round(achieved / 8000.0, 4)}
+                "kernel": f"decode_rows_kernel<Q4_K, MB={batch}, fused act-quant> on 32000x4096",
+                "peak_source": peak_src, "launches_timed": dom["launches_timed"],
+                "timing": "CUDA events around back-to-back launches (graph replay, consecutive launches overlap by programmatic dependent launch)",
+                "us_per_launch": dom["us_per_launch"], "bytes_per_launch": dom["bytes_per_launch"],
+                "frac_of_8TBs": round(dom["GBps"] / 8000.0, 4), "per_product": per_product}
 
     # ---- e2e: blocking C-ABI call, host buffers, resident weights ----
     host_x = [x.cpu().numpy() for x in xs]
@@ -283,19 +323,20 @@ def run_ours(args) -> dict:
         for hw, x, y, n in zip(st.host, host_x, host_y, STACK_N):
             P.gemm_quant_nt(Q4_K, hw, x, n, cacheable=True, out=y)
 
+    e2e_steps = max(args.steps, 200)  # a step is ~0.1 ms of wall clock: enough of them for a steady figure
     for i in range(max(args.warmup, n_copies)):  # first touch adopts each copy's weights
         step_host(i)
     barrier(world)
     t0 = time.perf_counter()
-    for i in range(args.steps):
+    for i in range(e2e_steps):
         step_host(i)
     P.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0, world)
     barrier(world)
-    e2e = {"value": round(world * bytes_step * args.steps / e2e_s / 1e9, 2), "unit": "GB/s",
+    e2e = {"value": round(world * bytes_step * e2e_steps / e2e_s / 1e9, 2), "unit": "GB/s",
            "h2d_bytes_per_step": len(STACK_N) * batch * K * 4, "d2h_bytes_per_step": sum(STACK_N) * batch * 4,
-           "ms_per_step": round(e2e_s / args.steps * 1e3, 4), "timing": "wall clock between device syncs",
-           "call": "fq_gemm_quant_nt (blocking), one call per product"}
+           "ms_per_step": round(e2e_s / e2e_steps * 1e3, 4), "steps_timed": e2e_steps, "timing": "wall clock between device syncs",
+           "call": "fq_gemm_quant_nt (blocking), one call per product, from Python through ctypes"}
 
     # the same step through the asynchronous entry (the reference's gemmQuantNtAsync + Work.finish): the
     # four products of a step are submitted back to back and finished afterwards, so uploads, kernels and
@@ -311,69 +352,111 @@ def run_ours(args) -> dict:
         step_host_async(i)
     barrier(world)
     t0 = time.perf_counter()
-    for i in range(args.steps):
+    for i in range(e2e_steps):
         step_host_async(i)
     P.synchronize()
     async_s = max_over_ranks(time.perf_counter() - t0, world)
     barrier(world)
-    e2e["async_submit"] = {"value": round(world * bytes_step * args.steps / async_s / 1e9, 2), "unit": "GB/s",
-                           "ms_per_step": round(async_s / args.steps * 1e3, 4),
+    e2e["async_submit"] = {"value": round(world * bytes_step * e2e_steps / async_s / 1e9, 2), "unit": "GB/s",
+                           "ms_per_step": round(async_s / e2e_steps * 1e3, 4),
                            "call": "fq_gemm_quant_nt_async x4, then fq_work_finish x4"}
+    if rank == 0:
+        native = native_e2e(batch)
+        if native:
+            e2e["native_caller"] = native
 
     out = {
         "metric": "quant GEMV HBM GB/s", "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8xq4 -> f32", "data": "synthetic",
         "config": {"workload": f"Q4_K decode GEMV stack, batch {batch}, K=4096 -> N in {{4096,11008,4096,32000}}",
                    "bytes_per_step": bytes_step, "weight_copies_rotated": n_copies,
                    "l2_policy": f"inputs larger than L2: {n_copies} distinct weight copies ({n_copies * bytes_step >> 20} MiB) rotated",
+                   "timed_region": f"{repeats} repeats of the {args.steps}-step sequence between one pair of CUDA events ({ms:.0f} ms)",
                    "parallelism": f"dp{world} replicas" if world > 1 else "single GPU"},
         "frac_of_8TBs": round(value / world / 8000.0, 4),
         "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clk.summary(),
     }
+    # ---- the other configurations of the metric, in the same line ----
+    del step_graphs, step_cycle
+    host_stack = stacks[0].host
+    stacks = None
+    torch.cuda.empty_cache()
+    if not args.no_sub:
+        want_cpu = rank == 0 and world == 1 and not args.no_cpu
+        out["sub"] = sub_records(args, P, torch, rank, world, local, want_cpu)
     if rank == 0 and world == 1 and not args.no_cpu:
-        out["cpu_baseline"] = cpu_baseline(stacks[0].host, host_x, budget_s=10.0)
+        out["cpu_baseline"] = cpu_baseline(host_stack, host_x, budget_s=8.0)
     return out if rank == 0 else {}
+
+
+def native_e2e(batch: int) -> dict | None:
+    """The same blocking host-buffer step from a C caller (no interpreter between the calls): the harness built
+    beside the library, run as a child process. Separates the library's per-call cost from Python's."""
+    exe = os.path.join(ROOT, "fucina_b200", "lib", "e2e_harness")
+    if not os.path.exists(exe):
+        return None
+    try:
+        r = subprocess.run([exe, str(batch)], capture_output=True, text=True, timeout=120,
+                           env={**os.environ, "CUDA_VISIBLE_DEVICES": os.environ.get("CUDA_VISIBLE_DEVICES", "")} if os.environ.get("CUDA_VISIBLE_DEVICES") else None)
+        line = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+        return json.loads(line[-1]) if line else {"error": (r.stderr or r.stdout)[-200:]}
+    except Exception as e:  # noqa: BLE001 - the harness is information, never fatal
+        return {"error": str(e)[:200]}
+
+
+def _cpu_time(fn, budget_s: float, max_calls: int = 100000) -> tuple[float, int]:
+    """seconds per call of fn() over about budget_s of wall clock (at least one call)."""
+    fn()
+    t0 = time.perf_counter()
+    calls = 0
+    while True:
+        fn()
+        calls += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or calls >= max_calls:
+            return dt / calls, calls
 
 
 def cpu_baseline(host_w, host_x, budget_s: float) -> dict:
     """The CPU restatement of the reference kernels (activations to Q8_K, dotQ4_KQ8_K rows,
-    output columns split over the host threads) on one stack copy, a few passes."""
+    output columns split over the host threads) on one stack copy, a few passes; all host threads, then one."""
     import oracle
 
-    cores = os.cpu_count() or 1
     bytes_step = stack_bytes(1)
-    oracle.matmul_fast(Q4_K, host_w[0][:256], host_x[0])  # load the library
-    t0 = time.perf_counter()
-    passes = 0
-    while True:
+    cores = oracle.set_threads(0)
+
+    def step():
         for w, x in zip(host_w, host_x):
             oracle.matmul_fast(Q4_K, w, x)
-        passes += 1
-        dt = time.perf_counter() - t0
-        if dt > budget_s or passes >= 5000:
-            break
-    return {"value": round(bytes_step * passes / dt / 1e9, 3), "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": f"{passes} pass(es) of the full stack (4 products, batch 1), {dt:.1f} s, "
+
+    sec, passes = _cpu_time(step, budget_s, 5000)
+    oracle.set_threads(1)
+    sec1, passes1 = _cpu_time(step, min(budget_s, 3.0), 5000)
+    oracle.set_threads(0)
+    return {"value": round(bytes_step / sec / 1e9, 3), "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"{passes} pass(es) of the full stack (4 products, batch 1), {sec * passes:.1f} s, "
                       + ("AVX2 block dots" if oracle.has_simd(Q4_K) else "scalar block dots"),
-            "ms_per_step": round(dt / passes * 1e3, 2)}
+            "ms_per_step": round(sec * 1e3, 3),
+            "single_thread": {"value": round(bytes_step / sec1 / 1e9, 3), "unit": "GB/s", "ms_per_step": round(sec1 * 1e3, 3), "passes": passes1}}
 
 
 def run_reference(args) -> dict:
-    """The reference's CPU path for the same workload: its Zig kernels cannot be built here
-    (no Zig toolchain), so the timed code is their C++ restatement in oracle/."""
+    """The reference's CPU path for the same workload and the same bytes per step: its Zig kernels cannot be
+    built here (no Zig toolchain), so the timed code is their C++ restatement in oracle/ (SIMD block dots,
+    columns split over the host threads as QuantizedRhsParallel does). The worker count is set explicitly:
+    launchers such as torchrun export OMP_NUM_THREADS=1."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return {}
     import oracle
 
+    cores = oracle.set_threads(0)
     rng = np.random.default_rng(1100)
-    # seeded N(0,0.02) weights through the restated reference encoder; a bounded row sample
-    # of each matrix keeps a step short (all host threads are used)
-    frac = 8
-    ws = [oracle.quantize_rows(Q4_K, (rng.standard_normal((n // frac, K)) * 0.02).astype(np.float32)) for n in STACK_N]
+    # seeded N(0,0.02) weights through the restated reference encoder, the full stack
+    ws = [oracle.quantize_rows(Q4_K, (rng.standard_normal((n, K)) * 0.02).astype(np.float32)) for n in STACK_N]
     xs = [rng.standard_normal((1, K)).astype(np.float32) for _ in STACK_N]
-    bytes_step = sum(w.shape[0] * ROW_BYTES + K * 4 + w.shape[0] * 4 for w in ws)
+    bytes_step = stack_bytes(1)
 
     def step():
         for w, x in zip(ws, xs):
@@ -381,20 +464,26 @@ def run_reference(args) -> dict:
 
     for _ in range(args.warmup):
         step()
+    # R repeats of the K-step sequence, at least a second of wall clock
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    step()
+    one = time.perf_counter() - t0
+    repeats = max(1, int(1.0 / max(one * args.steps, 1e-6)) + 1)
+    t0 = time.perf_counter()
+    for _ in range(repeats * args.steps):
         step()
     dt = time.perf_counter() - t0
-    value = round(bytes_step * args.steps / dt / 1e9, 3)
-    cores = os.cpu_count() or 1
-    sample = (f"rows/{frac} of each stack matrix per step, {args.steps} steps, {dt:.1f} s, "
+    n_steps = repeats * args.steps
+    value = round(bytes_step * n_steps / dt / 1e9, 3)
+    sample = (f"the full stack (4 products, batch 1) per step, {repeats} x {args.steps} steps, {dt:.1f} s, {cores} threads, "
               + ("AVX2 block dots" if oracle.has_simd(Q4_K) else "scalar block dots"))
     return {
         "impl": "reference", "metric": "quant GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 4),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / n_steps * 1e3, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xq4 -> f32", "data": "synthetic",
         "config": {"workload": "Q4_K decode GEMV stack, batch 1, K=4096 -> N in {4096,11008,4096,32000}",
-                   "bytes_per_step": bytes_step, "note": "CPU restatement of the reference kernels; Zig toolchain absent"},
+                   "bytes_per_step": bytes_step, "threads": cores,
+                   "note": "CPU restatement of the reference kernels; Zig toolchain absent"},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -507,7 +596,9 @@ def _timed(P, torch, fn, steps: int, warmup: int) -> float:
     return e0.elapsed_time(e1) / steps
 
 
-def _dev_weights(P, torch, fmt: int, n: int, k: int, seed: int, n_mats: int = 1):
+def _dev_weights(P, torch, fmt: int, n: int, k: int, seed: int, n_mats: int = 1, keep_host: bool = False):
+    """Seeded N(0, 0.02) f32 rows through the library's device encoder -> device-resident weights; with keep_host
+    the raw GGUF bytes are also kept on the host (`.host`, [n_mats * n, row_bytes]) for the CPU baseline."""
     from fucina_b200 import formats as F
 
     g = torch.Generator(device="cuda").manual_seed(seed)
@@ -518,7 +609,391 @@ def _dev_weights(P, torch, fmt: int, n: int, k: int, seed: int, n_mats: int = 1)
         torch.cuda.synchronize()
         P.quantize_rows_dev(fmt, w, n, k, blocks[e * n * rb:(e + 1) * n * rb])
         P.synchronize()
-    return P.Weights.from_device(fmt, blocks, n, k, n_mats)
+    wt = P.Weights.from_device(fmt, blocks, n, k, n_mats)
+    if keep_host:
+        wt.host = blocks.cpu().numpy().reshape(n_mats * n, rb)
+    return wt
+
+
+# ----------------------------------------------------------------------------------------------
+# The other configurations of the metric: one record each inside the default line's `sub` list.
+# ----------------------------------------------------------------------------------------------
+def _graph_ms(P, torch, graphs, target_ms: float = 150.0) -> float:
+    """milliseconds per launch over the rotated graphs, timed for about target_ms on the library stream."""
+    it = [0]
+
+    def step():
+        graphs[it[0] % len(graphs)].launch()
+        it[0] += 1
+
+    one = _timed(P, torch, step, len(graphs), 3)
+    steps = max(len(graphs), min(200000, int(target_ms / max(one, 1e-4))))
+    return _timed(P, torch, step, steps, 0)
+
+
+def sub_q8_0(args, P, torch, want_cpu: bool) -> list[dict]:
+    """Q8_0 GEMV 4096 x 4096, batch 1 (the bench/q8gemv.zig shape): 30 rotated weight copies (535 MB > 4x L2)."""
+    import oracle
+    from fucina_b200 import formats as F
+
+    n = k = 4096
+    peak, src = measured_peaks()
+    host = oracle.quantize_rows(F.Q8_0, (np.random.default_rng(1000).standard_normal((n, k)) * 0.02).astype(np.float32))
+    copies = [_dev_weights(P, torch, F.Q8_0, n, k, 1001 + i) for i in range(30)]
+    g = torch.Generator(device="cuda").manual_seed(2000)
+    x = torch.randn((1, k), generator=g, device="cuda")
+    y = torch.empty((1, n), device="cuda")
+    torch.cuda.synchronize()
+    with P.capture() as cap:
+        for w in copies:
+            P.gemm_quant_nt_dev(w, x, y, 1, mode=P.MODE_INT8)
+    ms = _graph_ms(P, torch, [cap.graph]) / len(copies)
+    nbytes = n * (k // 32 * 34) + 4 * k + 4 * n
+    gbs = nbytes / ms / 1e6
+    rec = {"workload": "Q8_0 GEMV 4096x4096 batch 1 (30 rotated weight copies, graph replay)", "metric": "quant GEMV HBM GB/s",
+           "value": round(gbs, 1), "unit": "GB/s", "us_per_launch": round(ms * 1e3, 3), "bytes_per_launch": nbytes,
+           "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
+                        "peak_source": src, "frac_of_8TBs": round(gbs / 8000.0, 4), "kernel": "decode_rows_kernel<Q8_0, MB=1>"}}
+    if want_cpu:
+        xh = x.cpu().numpy()
+        cores = oracle.set_threads(0)
+        sec, calls = _cpu_time(lambda: oracle.matmul_fast(F.Q8_0, host, xh), 1.5)
+        oracle.set_threads(1)
+        sec1, _ = _cpu_time(lambda: oracle.matmul_fast(F.Q8_0, host, xh), 1.0)
+        oracle.set_threads(0)
+        rec["cpu_baseline"] = {"value": round(nbytes / sec / 1e9, 2), "unit": "GB/s", "cores": cores, "kind": "port",
+                               "sample": f"{calls} products, {sec * calls:.1f} s, " + ("AVX2 block dots" if oracle.has_simd(F.Q8_0) else "scalar"),
+                               "single_thread": {"value": round(nbytes / sec1 / 1e9, 2), "unit": "GB/s"}}
+    return [rec]
+
+
+def sub_prefill(args, P, torch, want_cpu: bool) -> list[dict]:
+    """Q4_K prefill GEMM, M in {512, 2048} x N 14336 x K 4096: bf16 tcgen05 MMA, f32 accumulate and output."""
+    import oracle
+    from fucina_b200 import formats as F
+
+    n, k = 14336, 4096
+    burst, sustained, src = measured_tflops()
+    w = _dev_weights(P, torch, F.Q4_K, n, k, 1200)
+    g = torch.Generator(device="cuda").manual_seed(2200)
+    recs = []
+    for m in (512, 2048):
+        a = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16).to(torch.float32)  # bf16 activations of the config
+        c = torch.empty((m, n), device="cuda")
+        torch.cuda.synchronize()
+        fn = lambda: P.gemm_quant_nt_dev(w, a, c, m, mode=P.MODE_TENSOR)  # noqa: E731
+        one = _timed(P, torch, fn, 5, 3)
+        ms = _timed(P, torch, fn, max(5, min(2000, int(150.0 / one))), 0)
+        tf = 2.0 * m * n * k / ms / 1e9
+        recs.append({"workload": f"Q4_K prefill GEMM {m}x{n}x{k} (bf16 tcgen05, f32 out; the f32->bf16 activation pass is inside the timed call)",
+                     "metric": "Q4_K prefill TFLOPS", "value": round(tf, 1), "unit": "TFLOP/s", "ms": round(ms, 4),
+                     "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": burst, "unit": "TFLOP/s", "frac": round(tf / burst, 4),
+                                  "peak_source": src + " (burst)", "frac_of_sustained": round(tf / sustained, 4),
+                                  "frac_of_nominal_2250": round(tf / 2250.0, 4), "kernel": "gemm_tc_kernel<Q4_K, TN=256>"}})
+    if want_cpu:
+        # bounded sample: 32 of the activation rows against the whole matrix (the row arm of the CPU threading)
+        rng = np.random.default_rng(1200)
+        host = oracle.quantize_rows(F.Q4_K, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+        ah = rng.standard_normal((32, k)).astype(np.float32)
+        cores = oracle.set_threads(0)
+        sec, calls = _cpu_time(lambda: oracle.matmul_fast(F.Q4_K, host, ah), 2.0)
+        oracle.set_threads(1)
+        sec1, _ = _cpu_time(lambda: oracle.matmul_fast(F.Q4_K, host[:2048], ah), 1.0)
+        oracle.set_threads(0)
+        cpu = {"value": round(2.0 * 32 * n * k / sec / 1e12, 4), "unit": "TFLOP/s", "cores": cores, "kind": "port",
+               "sample": f"32 activation rows x the whole 14336 x 4096 matrix, {calls} passes, {sec * calls:.1f} s, int8 block dots",
+               "single_thread": {"value": round(2.0 * 32 * 2048 * k / sec1 / 1e12, 4), "unit": "TFLOP/s", "sample": "32 rows x 2048 weight rows"}}
+        for r in recs:
+            r["cpu_baseline"] = cpu
+    return recs
+
+
+MOE = {"hidden": 2048, "ffn": 768, "experts": 128, "top_k": 8}
+
+
+def _moe_stacks(P, torch, experts: int, seed0: int, keep_host: bool = False):
+    from fucina_b200 import formats as F
+
+    h, f = MOE["hidden"], MOE["ffn"]
+    gate = _dev_weights(P, torch, F.Q5_K, f, h, seed0, experts, keep_host)
+    up = _dev_weights(P, torch, F.Q5_K, f, h, seed0 + 1, experts, keep_host)
+    down = _dev_weights(P, torch, F.Q5_K, h, f, seed0 + 2, experts, keep_host)
+    return gate, up, down
+
+
+def _moe_layer_ms(P, torch, stacks, T: int, variants: int, seed: int):
+    """ms per router+layer step over `variants` rotated routings (one CUDA graph each), and the experts touched per step."""
+    h, E, topk = MOE["hidden"], stacks[0].n_mats, MOE["top_k"]
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    xs_ = [torch.randn((T, h), generator=g, device="cuda") for _ in range(variants)]
+    lgs = [torch.randn((T, E), generator=g, device="cuda") for _ in range(variants)]
+    sel = torch.empty((T, topk), dtype=torch.int32, device="cuda")
+    wts = torch.empty((T, topk), device="cuda")
+    o = torch.empty((T, h), device="cuda")
+    torch.cuda.synchronize()
+
+    def layer(i):
+        P.router_topk_dev(lgs[i], T, E, topk, True, sel, wts)
+        P.moe_layer_dev(*stacks, xs_[i], T, topk, sel, wts, o)
+
+    touched = []
+    for i in range(variants):
+        layer(i)
+        P.synchronize()
+        touched.append(int(torch.unique(sel).numel()))
+    graphs = []
+    for i in range(variants):
+        with P.capture() as cap:
+            layer(i)
+        graphs.append(cap.graph)
+    ms = _graph_ms(P, torch, graphs)
+    return ms, float(np.mean(touched))
+
+
+def sub_moe(args, P, torch, want_cpu: bool) -> list[dict]:
+    """Q5_K MoE expert layer (hidden 2048, ffn 768, 128 experts, top-8; router on the device, softmax top-8
+    renormalised): decode batches 1 and 64 and the 1024-token prefill. Routing variants are rotated so a decode
+    step does not find the previous step's experts in L2."""
+    import oracle
+    from fucina_b200 import formats as F
+
+    peak, src = measured_peaks()
+    burst, _, tsrc = measured_tflops()
+    stacks = _moe_stacks(P, torch, MOE["experts"], 1300, keep_host=want_cpu)
+    per_expert = 3 * MOE["ffn"] * (MOE["hidden"] // 256) * 176  # 3 244 032 bytes of Q5_K blocks
+    flop_tok = 2.0 * MOE["top_k"] * 3 * MOE["ffn"] * MOE["hidden"]
+    recs = []
+    for T in (1, 64, 1024):
+        ms, touched = _moe_layer_ms(P, torch, stacks, T, 16 if T <= 64 else 2, 3000 + T)
+        rec = {"workload": f"Q5_K MoE layer hidden 2048 ffn 768, 128 experts, top-8, {T} token(s) (router + layer on device, graph replay, "
+                           f"{16 if T <= 64 else 2} routing variants rotated)",
+               "metric": "MoE layer tok/s", "value": round(T / ms * 1e3, 1), "unit": "tok/s", "ms": round(ms, 4)}
+        if T <= 64:
+            gbs = touched * per_expert / ms / 1e6
+            rec["roofline"] = {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
+                               "peak_source": src, "experts_touched": round(touched, 1), "bytes": "expert weight bytes touched per step",
+                               "kernel": "expert_rows_kernel<Q5_K> (gate/up fused, then down)"}
+        else:
+            tf = T * flop_tok / ms / 1e9
+            rec["roofline"] = {"bound": "tensor", "achieved": round(tf, 1), "peak": burst, "unit": "TFLOP/s", "frac": round(tf / burst, 4),
+                               "peak_source": tsrc + " (burst)", "kernel": "gemm_tc_kernel<Q5_K, TN=128> (gated pair, then down)"}
+        recs.append(rec)
+    if want_cpu:
+        hg, hu, hd = (w.host for w in stacks)
+        rng = np.random.default_rng(3000)
+        cores = oracle.set_threads(0)
+        for rec, T, Ts in zip(recs, (1, 64, 1024), (1, 64, 64)):
+            x = rng.standard_normal((Ts, MOE["hidden"])).astype(np.float32)
+            sel, wts = oracle.router_topk(rng.standard_normal((Ts, MOE["experts"])).astype(np.float32), MOE["top_k"], True)
+            fn = lambda: oracle.moe_ffn_fast(F.Q5_K, hg, hu, hd, x, sel, wts, MOE["experts"], MOE["ffn"])  # noqa: E731
+            sec, calls = _cpu_time(fn, 2.0)
+            rec["cpu_baseline"] = {"value": round(Ts / sec, 1), "unit": "tok/s", "cores": cores, "kind": "port",
+                                   "sample": f"{Ts} token(s) per pass" + (" (a 64-token sample of the 1024)" if T != Ts else "") + f", {calls} passes, {sec * calls:.1f} s"}
+            if T == 1:
+                oracle.set_threads(1)
+                sec1, _ = _cpu_time(fn, 1.0)
+                oracle.set_threads(0)
+                rec["cpu_baseline"]["single_thread"] = {"value": round(Ts / sec1, 1), "unit": "tok/s"}
+    return recs
+
+
+def sub_ternary(args, P, torch, want_cpu: bool) -> list[dict]:
+    """PTQTP ternary plane (TQ2_0, one f16 scale per 256) 8192 x 8192: batch 1 on the integer kernel over 30 rotated
+    copies (519 MB > 4x L2), batch 256 on the tensor cores."""
+    import oracle
+    from fucina_b200 import formats as F
+
+    n = k = 8192
+    peak, src = measured_peaks()
+    burst, _, tsrc = measured_tflops()
+    rng = np.random.default_rng(4000)
+    trits = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+    scales = np.abs(rng.standard_normal((n, k // 256)) * 0.02).astype(np.float32)
+    host = F.pack_ptqtp_plane(trits, scales)
+    del trits
+    hd = torch.from_numpy(host).cuda()
+    copies = []
+    for i in range(30):
+        blk = torch.roll(hd, shifts=i, dims=0).contiguous()  # the same rows in another order: distinct addresses, same arithmetic
+        copies.append(P.Weights.from_device(F.TQ2_0, blk, n, k))
+    g = torch.Generator(device="cuda").manual_seed(2400)
+    x = torch.randn((1, k), generator=g, device="cuda")
+    y = torch.empty((1, n), device="cuda")
+    torch.cuda.synchronize()
+    with P.capture() as cap:
+        for w in copies:
+            P.gemm_quant_nt_dev(w, x, y, 1, mode=P.MODE_INT8)
+    ms = _graph_ms(P, torch, [cap.graph]) / len(copies)
+    nbytes = n * (k // 256 * 66) + 4 * (k + n)
+    gbs = nbytes / ms / 1e6
+    recs = [{"workload": "TQ2_0 (PTQTP plane) GEMV 8192x8192 batch 1 (30 rotated weight copies, graph replay)", "metric": "quant GEMV HBM GB/s",
+             "value": round(gbs, 1), "unit": "GB/s", "us_per_launch": round(ms * 1e3, 3), "bytes_per_launch": nbytes,
+             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
+                          "peak_source": src, "kernel": "gemv_kernel<TQ2_0, MB=1>"}}]
+    m = 256
+    a = torch.randn((m, k), generator=g, device="cuda")
+    c = torch.empty((m, n), device="cuda")
+    torch.cuda.synchronize()
+    fn = lambda: P.gemm_quant_nt_dev(copies[0], a, c, m, mode=P.MODE_AUTO)  # noqa: E731
+    one = _timed(P, torch, fn, 5, 3)
+    ms = _timed(P, torch, fn, max(5, min(5000, int(150.0 / one))), 0)
+    tf = 2.0 * m * n * k / ms / 1e9
+    recs.append({"workload": "TQ2_0 (PTQTP plane) GEMM 256x8192x8192 (bf16 tcgen05; the f32->bf16 activation pass is inside the timed call)",
+                 "metric": "ternary GEMM TFLOPS", "value": round(tf, 1), "unit": "TFLOP/s", "ms": round(ms, 4),
+                 "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": burst, "unit": "TFLOP/s", "frac": round(tf / burst, 4),
+                              "peak_source": tsrc + " (burst)", "kernel": "gemm_tc_kernel<TQ2_0, TN=256>"}})
+    if want_cpu:
+        xh = x.cpu().numpy()
+        cores = oracle.set_threads(0)
+        sec, calls = _cpu_time(lambda: oracle.matmul_fast(F.TQ2_0, host, xh), 1.5)
+        oracle.set_threads(1)
+        sec1, _ = _cpu_time(lambda: oracle.matmul_fast(F.TQ2_0, host, xh), 1.0)
+        oracle.set_threads(0)
+        recs[0]["cpu_baseline"] = {"value": round(nbytes / sec / 1e9, 2), "unit": "GB/s", "cores": cores, "kind": "port",
+                                   "sample": f"{calls} products, {sec * calls:.1f} s, " + ("AVX2 block dots" if oracle.has_simd(F.TQ2_0) else "scalar"),
+                                   "single_thread": {"value": round(nbytes / sec1 / 1e9, 2), "unit": "GB/s"}}
+        ah = a[:32].cpu().numpy()
+        sec, calls = _cpu_time(lambda: oracle.matmul_fast(F.TQ2_0, host, ah), 1.5)
+        recs[1]["cpu_baseline"] = {"value": round(2.0 * 32 * n * k / sec / 1e12, 4), "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                   "sample": f"32 of the 256 activation rows x the whole matrix, {calls} passes, {sec * calls:.1f} s"}
+    return recs
+
+
+def sub_multi(args, P, torch, rank: int, world: int, local: int) -> list[dict]:
+    """The two exchange forms of the path over `world` GPUs (NVLink): the expert-parallel Q5_K MoE layer (128 / world
+    experts per GPU) and the column-sharded Q4_K prefill with an all-gather of the output columns. Every rank
+    also times the whole layer alone on its own GPU, so the speed-up is taken inside one run."""
+    import torch.distributed as dist
+
+    from fucina_b200 import formats as F
+    from fucina_b200 import parallel as par
+
+    ext = torch.cuda.ExternalStream(P.stream_ptr())
+    h, f, E, topk = MOE["hidden"], MOE["ffn"], MOE["experts"], MOE["top_k"]
+    recs = []
+
+    def timed(fn, target_ms: float = 150.0) -> float:
+        for _ in range(3):
+            fn()
+        P.synchronize()
+        torch.cuda.synchronize()
+
+        def run(steps):
+            barrier(world)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(ext):
+                e0.record()
+                for _ in range(steps):
+                    fn()
+                e1.record()
+            P.synchronize()
+            torch.cuda.synchronize()
+            barrier(world)
+            return max_over_ranks(e0.elapsed_time(e1), world) / steps
+
+        one = run(5)
+        return run(max(5, min(2000, int(target_ms / max(one, 1e-3)))))
+
+    # ---- the whole layer on one GPU (every rank, independently): the N = 1 figure of this very run ----
+    full = _moe_stacks(P, torch, E, 1300)
+    single_ms, _ = _moe_layer_ms(P, torch, full, 1024, 2, 3000 + 1024)
+    single_ms = max_over_ranks(single_ms, world)
+    single_tps = 1024 / single_ms * 1e3
+    del full
+    torch.cuda.empty_cache()
+
+    per = E // world
+    gate, up, down = _moe_stacks(P, torch, per, 1300 + 10 * rank)
+    ep = P.ExpertParallel.create(rank, world, dist) if hasattr(P, "ExpertParallel") else None
+
+    def partial_rows(x_all, sel_all, w_all):
+        o = torch.empty_like(x_all)
+        P.moe_layer_ep_dev(gate, up, down, x_all, x_all.shape[0], topk, sel_all, w_all, rank * per, o)
+        return o
+
+    moe = par.ExpertParallelMoE(E, topk, lambda rows, le: rows)
+    for T_total, scaling in ((1024 * world, "weak"), (1024, "strong")):
+        T = T_total // world
+        g = torch.Generator(device="cuda").manual_seed(3000 + 10 * rank + T_total)
+        x = torch.randn((T, h), generator=g, device="cuda")
+        logits = torch.randn((T, E), generator=g, device="cuda")
+        sel = torch.empty((T, topk), dtype=torch.int32, device="cuda")
+        wts = torch.empty((T, topk), device="cuda")
+        out = torch.empty((T, h), device="cuda")
+        torch.cuda.synchronize()
+        forms = []
+        if ep is not None:
+            def step_fused():
+                P.router_topk_dev(logits, T, E, topk, True, sel, wts)
+                ep.moe_layer(gate, up, down, x, T, topk, sel, wts, out)
+
+            forms.append(("fused dispatch / return over peer memory (fq_moe_layer_ep)", step_fused))
+
+        def step_nccl():
+            with torch.cuda.stream(ext):
+                P.router_topk_dev(logits, T, E, topk, True, sel, wts)
+                moe.forward_gathered(x, sel, wts, partial_rows, exchange_dtype=torch.bfloat16 if T >= 512 else None)
+
+        forms.append(("NCCL all-gather of token rows + reduce-scatter of partial sums", step_nccl))
+        for name, fn in forms:
+            try:
+                ms = timed(fn)
+                rec = {"workload": f"Q5_K MoE layer (hidden 2048, ffn 768, 128 experts, top-8), {T_total} tokens over {world} GPUs, {per} experts per GPU, {name}",
+                       "metric": "MoE layer tok/s", "scaling": scaling, "n_gpus": world, "value": round(T_total / ms * 1e3, 1), "unit": "tok/s",
+                       "ms": round(ms, 4), "single_gpu_1024_tokens": {"tok_per_s": round(single_tps, 1), "ms": round(single_ms, 4)},
+                       "speedup_vs_single_gpu": round(T_total / ms * 1e3 / single_tps, 3)}
+            except Exception as e:  # noqa: BLE001
+                rec = {"workload": f"MoE expert-parallel, {name}", "error": str(e)[:300]}
+            recs.append(rec)
+
+    # ---- column-sharded prefill ----
+    n, k = 14336, 4096
+    lo, hi = par.shard_rows(n, world, rank)
+    w = _dev_weights(P, torch, F.Q4_K, hi - lo, k, 1200 + rank)
+    for m in (512, 2048):
+        g = torch.Generator(device="cuda").manual_seed(2200 + m)
+        a = torch.randn((m, k), generator=g, device="cuda")
+        y_local = torch.empty((m, hi - lo), device="cuda")
+        torch.cuda.synchronize()
+
+        def gemm(t):
+            P.gemm_quant_nt_dev(w, t, y_local, m, mode=P.MODE_TENSOR)
+            return y_local
+
+        lin = par.ColumnShardedLinear(n, gemm)
+
+        def step():
+            with torch.cuda.stream(ext):
+                lin.forward(a)
+
+        try:
+            ms = timed(step)
+            ms_compute = timed(lambda: gemm(a))
+            recs.append({"workload": f"Q4_K prefill {m}x{n}x{k}, output columns sharded over {world} GPUs, f32 all-gather (NCCL)",
+                         "metric": "Q4_K prefill TFLOPS", "n_gpus": world, "value": round(2.0 * m * n * k / ms / 1e9, 1), "unit": "TFLOP/s",
+                         "ms": round(ms, 4), "ms_compute_only": round(ms_compute, 4),
+                         "gathered_MB_per_rank": round(m * n * 4 * (world - 1) / world / 1e6, 1)})
+        except Exception as e:  # noqa: BLE001
+            recs.append({"workload": f"column-sharded prefill {m}", "error": str(e)[:300]})
+    return recs
+
+
+def sub_records(args, P, torch, rank: int, world: int, local: int, want_cpu: bool) -> list[dict]:
+    recs: list[dict] = []
+    if world > 1:
+        try:
+            recs = sub_multi(args, P, torch, rank, world, local)
+        except Exception as e:  # noqa: BLE001 - the headline value must survive a failing side record
+            recs = [{"workload": "multi-GPU exchange forms", "error": str(e)[:300]}]
+        return recs
+    for fn in (sub_q8_0, sub_prefill, sub_moe, sub_ternary):
+        try:
+            recs.extend(fn(args, P, torch, want_cpu))
+        except Exception as e:  # noqa: BLE001
+            recs.append({"workload": fn.__name__, "error": str(e)[:300]})
+        P.synchronize()
+        torch.cuda.empty_cache()
+    return recs
 
 
 def run_extra(args) -> list[dict]:
@@ -777,7 +1252,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
+    ap.add_argument("--no-sub", action="store_true", help="skip the records of the other configurations")
     ap.add_argument("--batch", type=int, default=1, help="activation rows per product of the decode stack (1, 4 or 16)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

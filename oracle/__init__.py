@@ -159,6 +159,26 @@ def matmul_fast(fmt: int, blocks: np.ndarray, a: np.ndarray) -> np.ndarray:
     return c
 
 
+def set_threads(n: int = 0) -> int:
+    """Worker threads of the timed SIMD restatement (0 = all logical CPUs); returns the count in use. Set
+    explicitly because launchers such as torchrun export OMP_NUM_THREADS=1."""
+    f = fast_lib()
+    return int(f.cpuk_set_threads(int(n))) if f is not None else 1
+
+
+def threads() -> int:
+    f = fast_lib()
+    return int(f.cpuk_threads()) if f is not None else 1
+
+
+def moe_ffn_fast(fmt, gate, up, down, x, selected, weights, n_expert, out_pe):
+    """Same values as `moe_ffn`, block dots by the SIMD arms, pairs over the worker threads (the timed CPU baseline)."""
+    f = fast_lib()
+    if f is None:
+        return moe_ffn(fmt, gate, up, down, x, selected, weights, n_expert, out_pe)
+    return _moe(f.cpuk_moe_ffn, fmt, gate, up, down, x, selected, weights, n_expert, out_pe)
+
+
 def matmul_ptqtp(planes: list[np.ndarray], a: np.ndarray) -> np.ndarray:
     planes = [np.ascontiguousarray(p, dtype=np.uint8) for p in planes]
     a = np.ascontiguousarray(a, dtype=np.float32)

@@ -211,8 +211,17 @@ def test_moe_prefill_full_config_tensor_arm(P, torch, moe_weights):
     sample = np.random.default_rng(7).choice(seq, 64, replace=False)
     sample.sort()
     want = oracle.moe_ffn_bf16(oracle.Q5_K, gate, up, down, x[sample], sel[sample], wts[sample], N_EXPERT, FFN)
-    e = assert_close(got[sample], want, TOL_TENSOR, "MoE 1024 tokens, tensor arm vs bf16 oracle")
-    print(f"MoE 1024 tokens (tensor arm): max relative error {e:.2e} on 64 sampled tokens")
+    # The layer rounds the intermediate g to bf16; kernel (f32 tensor-core accumulation) and oracle (f64) put a few
+    # g values on opposite sides of a bf16 rounding boundary, and one such flip moves an output by ~3e-4 of the
+    # output RMS, which a per-element ratio would blow up on near-zero outputs. The bound is therefore on the
+    # error relative to the output scale: 1e-2 of the RMS, as in tests/test_gpu_tensor.py.
+    rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    err = float(np.max(np.abs(got[sample] - want))) / rms
+    print(f"MoE 1024 tokens (tensor arm): max error {err:.2e} of the output RMS on 64 sampled tokens")
+    assert err <= TOL_TENSOR
+    # and the two arms agree to activation-quantisation noise (matrix level)
+    int8 = oracle.moe_ffn_fast(oracle.Q5_K, gate, up, down, x[sample], sel[sample], wts[sample], N_EXPERT, FFN)
+    assert float(np.max(np.abs(got[sample] - int8)) / np.max(np.abs(int8))) < 5e-2
 
 
 # ---------------------------------------------------------------- ternary 8192 x 8192

@@ -171,17 +171,48 @@ def test_oracle_reproduces_committed_cases(oracle_cases):
 
 
 def test_simd_baseline_equals_the_scalar_oracle():
-    """The timed CPU baseline (oracle/cpu_kernels.cpp) must produce the scalar oracle's bits."""
+    """The timed CPU baseline (oracle/cpu_kernels.cpp) must produce the scalar oracle's bits, for every format
+    with a SIMD arm, on both threading arms (columns split for m < 32, rows split beyond) and any worker count."""
     from parity import make_weights
 
-    for n, k, m in ((64, 512, 3), (333, 2304, 5), (1000, 4096, 1)):
-        w = make_weights("q4_k", n, k, seed=n)
-        a = np.random.default_rng(k).standard_normal((m, k)).astype(np.float32)
-        assert np.array_equal(oracle.matmul(oracle.Q4_K, w, a).view(np.uint32), oracle.matmul_fast(oracle.Q4_K, w, a).view(np.uint32))
-    # formats without a SIMD arm fall back to the scalar code
-    w = make_weights("q8_0", 32, 256, seed=1)
-    a = np.random.default_rng(2).standard_normal((2, 256)).astype(np.float32)
-    assert np.array_equal(oracle.matmul(oracle.Q8_0, w, a), oracle.matmul_fast(oracle.Q8_0, w, a))
+    def same(x, y):
+        return np.array_equal(x.view(np.uint32), y.view(np.uint32))
+
+    for name in ("q4_k", "q5_k", "q8_0", "tq2_0", "tq2_0_folded", "q2_0"):
+        fmt = oracle.FORMATS[name]
+        for n, k, m in ((64, 512, 3), (333, 2304, 5), (1000, 4096, 1), (96, 768, 40)):
+            w = make_weights(name, n, k, seed=n)
+            a = np.random.default_rng(k).standard_normal((m, k)).astype(np.float32)
+            a[0, :8] = (1e4, -1e4, 0, 127.5, -127.5, 1e-30, 3.0, -3.0)  # saturating and tie-prone values
+            want = oracle.matmul(fmt, w, a)
+            for t in (1, 3, 0):
+                oracle.set_threads(t)
+                assert same(want, oracle.matmul_fast(fmt, w, a)), (name, n, k, m, t)
+    oracle.set_threads(0)
+    assert oracle.threads() >= 1
+    assert all(oracle.has_simd(oracle.FORMATS[f]) == bool(oracle.has_simd(oracle.Q4_K)) for f in ("q5_k", "q8_0", "tq2_0"))
+    # a malformed TQ2_0 block may carry code 3 (+2d): the SIMD arm must follow the scalar law there too
+    w = np.random.default_rng(9).integers(0, 256, size=(16, 2 * 66), dtype=np.uint8)
+    w[:, 64:66] = w[:, 130:132] = np.frombuffer(np.float16(0.01).tobytes(), np.uint8)
+    a = np.random.default_rng(10).standard_normal((2, 512)).astype(np.float32)
+    assert same(oracle.matmul(oracle.TQ2_0, w, a), oracle.matmul_fast(oracle.TQ2_0, w, a))
+
+
+def test_simd_moe_baseline_equals_the_scalar_oracle():
+    from parity import make_weights
+
+    hidden, out_pe, n_expert, top_k, seq = 512, 256, 6, 3, 7
+    for name in ("q5_k", "q4_k", "q8_0"):
+        fmt = oracle.FORMATS[name]
+        gate = make_weights(name, n_expert * out_pe, hidden, seed=1)
+        up = make_weights(name, n_expert * out_pe, hidden, seed=2)
+        down = make_weights(name, n_expert * hidden, out_pe, seed=3)
+        rng = np.random.default_rng(4)
+        x = rng.standard_normal((seq, hidden)).astype(np.float32)
+        sel, wts = oracle.router_topk(rng.standard_normal((seq, n_expert)).astype(np.float32), top_k, True)
+        want = oracle.moe_ffn(fmt, gate, up, down, x, sel, wts, n_expert, out_pe)
+        got = oracle.moe_ffn_fast(fmt, gate, up, down, x, sel, wts, n_expert, out_pe)
+        assert np.array_equal(want.view(np.uint32), got.view(np.uint32)), name
 
 
 def test_blas_form_of_oracle_b_equals_the_scalar_one():
