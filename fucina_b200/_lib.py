@@ -73,6 +73,16 @@ SIGNATURES = {
     "fq_moe_layer_dev": (c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_int, c_void, c_void]),
     "fq_moe_layer_ep_dev": (
         c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_int, c_int, c_void, c_void]),
+    "fq_tp_unique_id": (c_int, [c_void]),
+    "fq_tp_init": (c_int, [c_int, c_int, c_void, c_size]),
+    "fq_tp_shutdown": (c_int, []),
+    "fq_tp_ranks": (c_int, []),
+    "fq_tp_rank": (c_int, []),
+    "fq_tp_peer_access": (c_int, []),
+    "fq_gemm_quant_nt_tp": (c_int, [c_void, c_void, c_void, c_size, c_int, c_void]),
+    "fq_moe_layer_ep": (c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_int, c_void, c_int, c_void]),
+    "fq_ep_emulate_for_test": (c_int, [c_int, P(c_void), P(c_void), P(c_void), P(c_void), c_size, c_size, P(c_void), P(c_void), P(c_void),
+                                       c_size, c_int]),
     "fq_router_topk_dev": (c_int, [c_void, c_size, c_size, c_size, c_int, c_void, c_void, c_void]),
     "fq_should_use_gpu_dense_quant": (c_int, [c_int, c_u64]),
     "fq_should_use_gpu_dense_quant_packed": (c_int, [c_int, c_u64]),

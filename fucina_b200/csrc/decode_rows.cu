@@ -439,6 +439,14 @@ __host__ __device__ inline SlabGeom slab_geom(int fmt, int slab) {
     return g;
 }
 
+// where the product of token `tok` and weight row `row` goes: c[tok][row], or, for stacked matrices that share
+// the activations, the [matrix][token][row inside the matrix] layout of the shared-input batch
+__device__ __forceinline__ size_t out_index(const RowsArgs& A, int tok, int row) {
+    if (A.split_n == 0) return (size_t)tok * A.ldc + row;
+    const int mat = row / A.split_n;
+    return ((size_t)mat * A.m + tok) * A.split_n + (row - mat * A.split_n);
+}
+
 template <int FMT, int MB, bool FUSED, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) decode_rows_kernel(const RowsArgs A, const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap2) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -671,9 +679,9 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
                 const int i = b & 7;
                 const int r = 16 * (i >> 2) + 8 * ((i >> 1) & 1) + (lane >> 2);
                 const int tok = (b >> 3) * 8 + 2 * (lane & 3) + (i & 1);
-                if (r < nvalid && tok < A.m) A.c[(size_t)tok * A.ldc + row0 + r] = s;
+                if (r < nvalid && tok < A.m) A.c[out_index(A, tok, row0 + r)] = s;
             } else if (lane < nvalid && b < A.m) {
-                A.c[(size_t)b * A.ldc + row0 + lane] = s;
+                A.c[out_index(A, b, row0 + lane)] = s;
             }
         }
     }
@@ -1158,11 +1166,11 @@ size_t decode_rows_scratch_bytes(const DevWeights& w, size_t m) {
 }
 
 cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev, uint8_t* scratch, float* c, int m, int ldc,
-                               int sm_count, int* status, cudaStream_t st) {
+                               int sm_count, int* status, cudaStream_t st, int split_n) {
     const int mb = decode_pad_rows(w.fmt, (size_t)m);
     static const int skip = getenv("FUCINA_B200_DECODE_SKIP_COMPUTE") ? 1 : 0;  // diagnosis: copy pipeline only, outputs are garbage
     static const int l2_stream = getenv("FUCINA_B200_DECODE_L2_STREAM") ? atoi(getenv("FUCINA_B200_DECODE_L2_STREAM")) : 1;
-    RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0, skip, l2_stream, 0};
+    RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0, skip, l2_stream, 0, split_n};
     if (!pick_config(w.fmt, w.k, mb, &a.slab, &a.stages)) return cudaErrorInvalidValue;
     // K-quant units are an odd number of 16-byte chunks: one tensor copy per warp step instead of 32
     // per-lane bulk copies (small bulk copies are issue-rate bound in the copy engine)

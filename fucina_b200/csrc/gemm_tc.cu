@@ -117,6 +117,7 @@ struct TcArgs {
     // accumulator) and `w2` (up, second accumulator); the epilogue writes bf16(up * silu(gate)) to g_out
     DevWeights w2;
     __nv_bfloat16* g_out;
+    TcPeer peer;  // multi-GPU hooks (all null / zero on one GPU)
 };
 
 // One output tile: weight rows [rt*128, +128) of matrix `mat` times activation rows [tok0, tok0+ntok).
@@ -170,6 +171,13 @@ struct __align__(8) Barriers {
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// a flag another GPU writes: system-scope acquire, so the data it guards is visible once the value is seen
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+constexpr unsigned kPeerWaitLimit = 1u << 22;  // x ~0.2 us of sleep per poll: about a second
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -557,6 +565,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         if (lane == 0) {
             int gb = 0;
             bool ok = true;
+            // expert parallelism: the token rows of this GPU's panel are written by other ranks; every source
+            // posts a flag once its rows are visible. Bounded: a flag that never comes aborts the CTA.
+            for (int i = 0; i < A.peer.n_wait && ok; ++i) {
+                unsigned spins = 0;
+                while (ld_acquire_sys(A.peer.wait_flags + i) < A.peer.wait_value) {
+                    if (B->abort_flag || ++spins > kPeerWaitLimit) {
+                        ok = false;
+                        break;
+                    }
+                    __nanosleep(200);
+                }
+            }
+            if (!ok) {
+                B->abort_flag = 1;
+                *(volatile int*)A.status = FQ_ERR_TIMEOUT;
+            }
             for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
                 const TileRef T = tile_ref<TN>(A, tile, row_tiles);
                 for (int u = 0; u < PASSES * units && ok; ++u) {
@@ -796,9 +820,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                             }
                         }
                     } else if (out_row < n) {
+                        if (A.peer.row_meta) {
+                            // every row goes to the panel of the rank that owns its token: lanes hold consecutive
+                            // columns of one row, so a warp writes 128 contiguous bytes per row (plain peer stores)
+#pragma unroll 8
+                            for (int j = 0; j < 32; ++j) {
+                                if (c0 + j < T.ntok) {
+                                    const int2 mt = __ldg(A.peer.row_meta + T.tok0 + c0 + j);
+                                    A.peer.dst_base[mt.x & (kMaxPeers - 1)][(size_t)mt.y * A.ldc + out_row] = __uint_as_float(acc[j]);
+                                }
+                            }
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (c0 + j < T.ntok) A.c[(size_t)(T.tok0 + c0 + j) * A.ldc + out_row] = __uint_as_float(acc[j]);
+                            for (int j = 0; j < 32; ++j) {
+                                if (c0 + j < T.ntok) A.c[(size_t)(T.tok0 + c0 + j) * A.ldc + out_row] = __uint_as_float(acc[j]);
+                            }
                         }
                     }
                 }
@@ -907,7 +943,7 @@ static int encode_packed_rows(EncodeTiledFn enc, const DevWeights& w, CUtensorMa
 // bf16(up * silu(gate)) in g_out instead of f32 products in c_dev.
 static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfloat16* abf, size_t rows, float* c_dev, size_t ldc,
                           const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st,
-                          const DevWeights* up = nullptr, __nv_bfloat16* g_out = nullptr) {
+                          const DevWeights* up = nullptr, __nv_bfloat16* g_out = nullptr, const TcPeer* peer = nullptr) {
     const int BN = tile_tokens;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return fail(FQ_DECLINED_ARGS, "cuTensorMapEncodeTiled unavailable");
@@ -925,7 +961,7 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
     if (int rc = encode_packed_rows(enc, w, &tmap_w)) return rc;
     if (int rc = encode_packed_rows(enc, up ? *up : w, &tmap_w2)) return rc;
     static const int diag = getenv("FUCINA_B200_TC_DIAG") ? atoi(getenv("FUCINA_B200_TC_DIAG")) : 0;
-    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev, diag, up ? *up : w, g_out};
+    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev, diag, up ? *up : w, g_out, peer ? *peer : TcPeer{}};
     const int tiles = table ? max_tiles : ((w.n + BM - 1) / BM) * (int)((rows + BN - 1) / BN);
     const int grid = tiles < ctx->sm_count ? (tiles > 0 ? tiles : 1) : ctx->sm_count;
     cudaError_t e;
@@ -951,23 +987,26 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
 }
 
 int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, size_t rows, float* c_dev, size_t ldc,
-                            const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st) {
+                            const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st,
+                            const TcPeer* peer) {
     if (tile_tokens != 128 && tile_tokens != 256) return fail(FQ_DECLINED_ARGS, "token tiles are 128 or 256 rows");
     if (!tensor_path_serves(w)) return fail(FQ_DECLINED_ARGS, "tensor-core path needs a served format with k %% 256 == 0");
-    return launch_tc_rows(ctx, w, 0, (const __nv_bfloat16*)a_bf16, rows, c_dev, ldc, table, n_tiles_dev, max_tiles, tile_tokens, st);
+    return launch_tc_rows(ctx, w, 0, (const __nv_bfloat16*)a_bf16, rows, c_dev, ldc, table, n_tiles_dev, max_tiles, tile_tokens, st,
+                          nullptr, nullptr, peer);
 }
 
 // Gate and up products of one expert layer in one pass with the SwiGLU applied in the epilogue:
 // g[row, j] = bf16(up[row, j] * silu(gate[row, j])) over the tile list (128-token tiles).
 int gemm_tensor_grouped_gated_dev(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const void* a_bf16, size_t rows, void* g_bf16,
-                                  size_t ldc, const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st) {
+                                  size_t ldc, const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st,
+                                  const TcPeer* peer) {
     if (!tensor_path_serves(gate) || (gate.fmt != FQ_Q4_K && gate.fmt != FQ_Q5_K && gate.fmt != FQ_Q8_0))
         return fail(FQ_DECLINED_ARGS, "the gated tensor-core form serves Q4_K, Q5_K and Q8_0 with k %% 256 == 0");
     if (up.fmt != gate.fmt || up.n != gate.n || up.k != gate.k || up.n_mats != gate.n_mats || up.tile_rows != gate.tile_rows ||
         up.row_stride != gate.row_stride || up.mat_stride != gate.mat_stride)
         return fail(FQ_DECLINED_ARGS, "gate and up stacks differ in shape or layout");
     return launch_tc_rows(ctx, gate, 0, (const __nv_bfloat16*)a_bf16, rows, nullptr, ldc, table, n_tiles_dev, max_tiles, 128, st, &up,
-                          (__nv_bfloat16*)g_bf16);
+                          (__nv_bfloat16*)g_bf16, peer);
 }
 
 __global__ void add_f32_kernel(float* __restrict__ c, const float* __restrict__ t, size_t n) {

@@ -75,6 +75,8 @@ struct RowsArgs {
     int skip_compute; // diagnosis only: stream the weights, skip the arithmetic
     int l2_stream;    // weight copies carry an evict-first L2 hint (tile-major form)
     int rows_per_cta; // 0: rows split evenly over the grid; else CTA b serves rows [b*rows_per_cta, +rows_per_cta)
+    int split_n;      // 0, or the rows of ONE matrix when w stacks several that share the activations: weight row r
+                      // of token b lands at c[((r / split_n) * m + b) * split_n + r % split_n] (the [batch][m][n] layout)
 };
 // Grouped expert form of the row-per-lane kernel (MoE decode): a device-built table of (expert, run of
 // <= 8 activation rows) entries over a row-major expert stack; the f32 activation rows are quantised
@@ -105,12 +107,26 @@ bool decode_rows_eligible(const DevWeights& w, size_t m);
 // bytes of natural-record scratch the non-fused form needs (0 for the fused form)
 size_t decode_rows_scratch_bytes(const DevWeights& w, size_t m);
 cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev, uint8_t* scratch, float* c, int m, int ldc,
-                               int sm_count, int* status, cudaStream_t st);
+                               int sm_count, int* status, cudaStream_t st, int split_n = 0);
 
 // gemm_tc.cu -- tcgen05 prefill GEMM. One output tile of the grouped (MoE) form: weight rows
 // [rt*128, +128) of expert matrix `mat` times the consecutive activation rows [tok0, tok0+ntok).
 struct TcTile {
     int mat, rt, tok0, ntok;
+};
+// Optional multi-GPU hooks of the grouped tensor-core GEMM (expert parallelism over peer memory).
+//  * wait_flags: the token-tile producer does not issue its first load before wait_flags[i] >= wait_value for
+//    every i < n_wait (other ranks' dispatch kernels post these after writing their token rows into this GPU's
+//    panel). The wait is bounded; a timeout aborts the CTA and records FQ_ERR_TIMEOUT.
+//  * row_meta: the f32 epilogue does not write c[row][col] but dst_base[meta.x][meta.y * ldc + col]: each output
+//    row goes straight to the panel of the rank that owns its token (plain peer stores over NVLink).
+constexpr int kMaxPeers = 8;
+struct TcPeer {
+    const int* wait_flags = nullptr;
+    int n_wait = 0;
+    int wait_value = 0;
+    const int2* row_meta = nullptr;
+    float* dst_base[kMaxPeers] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 cudaError_t launch_add_f32(float* c, const float* t, size_t n, cudaStream_t st);
 cudaError_t launch_f32_to_bf16(const float* src, void* dst, size_t n, cudaStream_t st);

@@ -17,6 +17,7 @@
 
 #include "acts.cuh"
 #include "internal.h"
+#include "multi.h"
 #include "runtime.h"
 
 namespace fq {
@@ -494,6 +495,12 @@ struct QMoeStage {
 } g_stage;
 
 }  // namespace
+
+int moe_layer_shard_dev(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev, int seq,
+                        int top_k, const int* selected_dev, const float* weights_dev, int expert_base, float* partial_dev, cudaStream_t st) {
+    return moe_layer_dev_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, Shard{expert_base, 1}, partial_dev, st);
+}
+
 }  // namespace fq
 
 using namespace fq;

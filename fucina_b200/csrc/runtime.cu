@@ -185,6 +185,7 @@ int device_status(Ctx* ctx) {
     const int s = *(volatile int*)ctx->status_host;
     if (s == 0) return FQ_OK;
     *(volatile int*)ctx->status_host = 0;
+    if (s == FQ_ERR_CAPACITY) return fail(s, "the routing sent a GPU more rows than its exchange arena holds");
     return fail(s, "a device-side wait gave up (status %d)", s);
 }
 
@@ -529,9 +530,12 @@ int resolve_rhs(Ctx* ctx, int fmt, const void* rhs, size_t rhs_len, int cacheabl
 // dense matmul on device buffers
 // ---------------------------------------------------------------------------
 int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, int mode,
-             int accumulate, cudaStream_t st) {
+             int accumulate, cudaStream_t st, int split_n) {
     if (m == 0) return fail(FQ_DECLINED_ARGS, "m == 0");
     if (mat < 0 || mat >= w.n_mats) return fail(FQ_DECLINED_ARGS, "matrix index out of range");
+    if (split_n && !(g_decode_rows_on && !accumulate && decode_rows_eligible(w, m) && w.n % split_n == 0))
+        return fail(FQ_DECLINED_ARGS, "stacked matrices are served by the decode kernel only");
+    if (split_n) mode = FQ_MODE_INT8;
     if (mode == FQ_MODE_TENSOR || (mode == FQ_MODE_AUTO && m > gemv_max_rows() && !accumulate)) {
         int rc = gemm_tensor_dev(ctx, w, mat, a_dev, c_dev, m, ldc, st);
         if (rc != FQ_DECLINED_ARGS || mode == FQ_MODE_TENSOR) return rc;
@@ -548,7 +552,7 @@ int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* 
             t1 = ktime_event();
             cudaEventRecord(t0, st);
         }
-        cudaError_t e = launch_decode_rows(w, mat, a_dev, nat, c_dev, (int)m, (int)ldc, ctx->sm_count, ctx->status_dev, st);
+        cudaError_t e = launch_decode_rows(w, mat, a_dev, nat, c_dev, (int)m, (int)ldc, ctx->sm_count, ctx->status_dev, st, split_n);
         if (g_ktime_on) {
             cudaEventRecord(t1, st);
             g_ktime_events.emplace_back(t0, t1);
@@ -671,7 +675,17 @@ static int gemm_host(int fmt, const void* rhs, size_t rhs_len, int cacheable, si
     g_trace.calls++;
     DevWeights view;
     fq_weights* temp = nullptr;
-    int rc = resolve_rhs(ctx, fmt, rhs, rhs_len, cacheable, nb01, nb02, n, k, batch, &view, &temp);
+    // A dense stack of matrices that share a decode-sized input (Q/K/V, gate/up) is one matrix of batch * n
+    // rows to the streaming kernel: one launch, activations quantised once per CTA, every SM busy
+    // (backend/cuda.zig:2441-2492 launches per matrix).
+    bool stacked = false;
+    if (batch > 1 && nb02 == nb01 * n && g_decode_rows_on && batch * n <= (size_t)INT32_MAX) {
+        DevWeights probe{};
+        probe.fmt = fmt, probe.n = (int)(batch * n), probe.k = (int)k, probe.n_mats = 1;
+        stacked = decode_rows_eligible(probe, m);
+    }
+    int rc = stacked ? resolve_rhs(ctx, fmt, rhs, rhs_len, cacheable, nb01, 0, batch * n, k, 1, &view, &temp)
+                     : resolve_rhs(ctx, fmt, rhs, rhs_len, cacheable, nb01, nb02, n, k, batch, &view, &temp);
     if (rc != FQ_OK) return rc;
     Staged in;
     const size_t out_bytes = batch * m * n * sizeof(float);
@@ -691,7 +705,11 @@ static int gemm_host(int fmt, const void* rhs, size_t rhs_len, int cacheable, si
         if (!c_dev) rc = fail(FQ_DECLINED_BUDGET, "result allocation of %zu bytes failed", out_bytes);
     }
     bool submitted = false;
-    for (size_t b = 0; b < batch && rc == FQ_OK; ++b) {
+    if (stacked && rc == FQ_OK) {
+        rc = gemm_dev(ctx, view, 0, (const float*)in.dev, (float*)c_dev, m, n, FQ_MODE_INT8, 0, ctx->stream, (int)n);
+        submitted = true;
+    }
+    for (size_t b = 0; b < batch && rc == FQ_OK && !stacked; ++b) {
         rc = gemm_dev(ctx, view, (int)b, (const float*)in.dev, (float*)c_dev + b * m * n, m, n, FQ_MODE_AUTO, 0, ctx->stream);
         submitted = true;
     }
@@ -962,7 +980,14 @@ int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheab
     g_trace.calls++;
     DevWeights view;
     fq_weights* temp = nullptr;
-    int rc = resolve_rhs(ctx, fmt, rhs, rhs_len, 1, nb01, nb02, n, k, batch, &view, &temp);
+    bool stacked = false;  // a dense stack sharing a decode-sized input runs as one launch (see gemm_host)
+    if (batch > 1 && nb02 == nb01 * n && g_decode_rows_on && batch * n <= (size_t)INT32_MAX) {
+        DevWeights probe{};
+        probe.fmt = fmt, probe.n = (int)(batch * n), probe.k = (int)k, probe.n_mats = 1;
+        stacked = decode_rows_eligible(probe, m);
+    }
+    int rc = stacked ? resolve_rhs(ctx, fmt, rhs, rhs_len, 1, nb01, 0, batch * n, k, 1, &view, &temp)
+                     : resolve_rhs(ctx, fmt, rhs, rhs_len, 1, nb01, nb02, n, k, batch, &view, &temp);
     if (rc != FQ_OK) return rc;
     Staged in;
     const float* a_dev = a_dep ? (const float*)a_dep->c_dev : nullptr;
@@ -983,7 +1008,8 @@ int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheab
         if (!w->c_dev) rc = fail(FQ_DECLINED_BUDGET, "device allocation failed");
         else if (cudaEventCreateWithFlags(&w->done, cudaEventDisableTiming) != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "event create");
     }
-    for (size_t b = 0; b < batch && rc == FQ_OK; ++b)
+    if (stacked && rc == FQ_OK) rc = gemm_dev(ctx, view, 0, a_dev, (float*)w->c_dev, m, n, FQ_MODE_INT8, 0, ctx->stream, (int)n);
+    for (size_t b = 0; b < batch && rc == FQ_OK && !stacked; ++b)
         rc = gemm_dev(ctx, view, (int)b, a_dev, (float*)w->c_dev + b * m * n, m, n, FQ_MODE_AUTO, 0, ctx->stream);
     if (rc == FQ_OK) {
         cudaError_t e = cudaEventRecord(w->done, ctx->stream);

@@ -54,18 +54,23 @@ int resolve_rhs(Ctx* ctx, int fmt, const void* rhs, size_t rhs_len, int cacheabl
                 size_t n_mats, DevWeights* view, fq_weights** temp);
 
 // c[m, ldc] (+)= a[m, k] . dequant(W[mat])^T on device buffers.
+// split_n != 0: `w` stacks several matrices of split_n rows that share the activations (decode shapes only) and
+// c_dev is laid out [matrix][m][split_n].
 int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, int mode,
-             int accumulate, cudaStream_t st);
+             int accumulate, cudaStream_t st, int split_n = 0);
 // gemm_tc.cu: bf16 tensor-core path; returns FQ_DECLINED_ARGS for shapes it does not take.
 int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc,
                     cudaStream_t st);
 
 // grouped form over bf16 activation rows and a device-built tile list (moe.cu)
 struct TcTile;
+struct TcPeer;
 bool tensor_path_serves(const DevWeights& w);
 int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, size_t rows, float* c_dev, size_t ldc,
-                            const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st);
+                            const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st,
+                            const TcPeer* peer = nullptr);
 int gemm_tensor_grouped_gated_dev(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const void* a_bf16, size_t rows, void* g_bf16,
-                                  size_t ldc, const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st);
+                                  size_t ldc, const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st,
+                                  const TcPeer* peer = nullptr);
 
 }  // namespace fq

@@ -334,6 +334,63 @@ def moe_layer_ep_dev(gate: Weights, up: Weights, down: Weights, x_dev, seq: int,
                                       _vp(weights_dev), expert_base, gated_op, _vp(partial_dev), C.c_void_p(stream)))
 
 
+# --------------------------------------------------------------------------- several GPUs, one process each
+EP_AUTO, EP_NCCL, EP_FUSED = 0, 1, 2
+
+
+def tp_unique_id() -> bytes:
+    """The 128-byte rendezvous id rank 0 makes; the host carries it to the other ranks."""
+    buf = C.create_string_buffer(128)
+    _check(load().fq_tp_unique_id(buf))
+    return buf.raw
+
+
+def tp_init(n_ranks: int, rank: int, unique_id: bytes, arena_bytes: int = 0) -> None:
+    assert len(unique_id) == 128
+    _check(load().fq_tp_init(n_ranks, rank, C.c_char_p(unique_id), arena_bytes))
+
+
+def tp_init_torch(dist, arena_bytes: int = 0) -> None:
+    """fq_tp_init with the id carried by an initialised torch.distributed group (any backend)."""
+    rank, world = dist.get_rank(), dist.get_world_size()
+    box = [tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    tp_init(world, rank, box[0], arena_bytes)
+
+
+def tp_shutdown() -> None:
+    _check(load().fq_tp_shutdown())
+
+
+def tp_peer_access() -> bool:
+    return bool(load().fq_tp_peer_access())
+
+
+def gemm_quant_nt_tp(w_shard: Weights, a_dev, c_dev, m: int, mode: int = MODE_AUTO, stream: int = 0) -> None:
+    """Column-sharded product + all-gather: c_dev [rank][m][n_shard] on every rank (collective)."""
+    _check(load().fq_gemm_quant_nt_tp(w_shard.handle, _vp(a_dev), _vp(c_dev), m, mode, C.c_void_p(stream)))
+
+
+def moe_layer_ep(gate: Weights, up: Weights, down: Weights, x_dev, seq: int, top_k: int, selected_dev, weights_dev, out_dev,
+                 flags: int = EP_AUTO, gated_op: int = 0, stream: int = 0) -> None:
+    """Expert-parallel MoE layer over the ranks of `tp_init` (collective): this rank's tokens in, this rank's tokens out."""
+    _check(load().fq_moe_layer_ep(gate.handle, up.handle, down.handle, _vp(x_dev), seq, top_k, _vp(selected_dev), _vp(weights_dev),
+                                  gated_op, _vp(out_dev), flags, C.c_void_p(stream)))
+
+
+def ep_emulate_for_test(gates: list[Weights], ups: list[Weights], downs: list[Weights], xs: list, seq: int, top_k: int, sels: list,
+                        wts: list, outs: list, arena_bytes: int, layers: int = 1) -> None:
+    """`len(gates)` ranks of the fused expert-parallel layer emulated on one GPU (test seam)."""
+    world = len(gates)
+
+    def arr(items, ptr=lambda t: t.data_ptr()):
+        return (C.c_void_p * world)(*[ptr(t) for t in items])
+
+    h = lambda w: w.handle  # noqa: E731
+    _check(load().fq_ep_emulate_for_test(world, arr(gates, h), arr(ups, h), arr(downs, h), arr(xs), seq, top_k, arr(sels), arr(wts),
+                                         arr(outs), arena_bytes, layers))
+
+
 def router_topk_dev(logits_dev, seq: int, n_expert: int, top_k: int, normalize: bool, selected_dev, weights_dev,
                     stream: int = 0) -> None:
     """`routerTopK` (src/exec/topk.zig:21-86) on the device."""

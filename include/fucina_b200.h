@@ -58,7 +58,8 @@ enum {
     FQ_DECLINED_GATE = 4,    /* disabled by FUCINA_GPU=0 */
     FQ_DECLINED_BUSY = 5,    /* all async slots in flight */
     FQ_ERR_CUDA = -1,
-    FQ_ERR_TIMEOUT = -2      /* a bounded device-side wait gave up */
+    FQ_ERR_TIMEOUT = -2,     /* a bounded device-side wait gave up */
+    FQ_ERR_CAPACITY = -3     /* the routing sent more rows to a GPU than its exchange arena holds */
 };
 
 /* backend/cuda.zig:1503-1508 `QMMTile`: one output tile of one expert. */
@@ -231,6 +232,47 @@ FQ_API int fq_moe_layer_dev(const fq_weights* gate, const fq_weights* up, const 
 FQ_API int fq_moe_layer_ep_dev(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev,
                         size_t seq, size_t top_k, const int32_t* selected_dev, const float* weights_dev,
                         int expert_base, int gated_op, float* partial_dev, void* stream);
+/* ---- several GPUs of one node, one process per GPU (new: the reference takes device 0 only,
+ *      backend/cuda.zig:439) ----
+ * Rank 0 makes a 128-byte rendezvous id (fq_tp_unique_id); the host carries it to the other processes; every
+ * rank then calls fq_tp_init (collective). It creates an NCCL communicator (libnccl.so.2 is loaded at run
+ * time) and an exchange arena of `arena_bytes` (0 = 1 GiB) per rank whose CUDA IPC handle every peer opens,
+ * so kernels store into other GPUs' memory over NVLink. fq_tp_peer_access tells whether that mapping
+ * succeeded; without it only the NCCL forms run. fq_init must name this process's GPU first. */
+#define FQ_TP_ID_BYTES 128
+FQ_API int fq_tp_unique_id(void* id128);
+FQ_API int fq_tp_init(int n_ranks, int rank, const void* id128, size_t arena_bytes);
+FQ_API int fq_tp_shutdown(void);
+FQ_API int fq_tp_ranks(void);       /* 0 before fq_tp_init */
+FQ_API int fq_tp_rank(void);        /* -1 before fq_tp_init */
+FQ_API int fq_tp_peer_access(void); /* 1 when every peer's arena is mapped */
+/* Column-sharded (tensor-parallel) product: `w_shard` holds this rank's contiguous slice of the weight rows
+ * (every rank the same number), the activations are replicated, and one all-gather assembles
+ * c_dev [rank][m][n_shard] on every rank. No reduction crosses ranks: each element is computed exactly as on
+ * one GPU (fq_gemm_quant_nt_dev semantics for a_dev, mode and stream). Collective. */
+FQ_API int fq_gemm_quant_nt_tp(const fq_weights* w_shard, const float* a_dev, float* c_dev, size_t m, int mode, void* stream);
+/* Expert-parallel MoE layer. gate/up/down hold experts [rank * E_local, (rank + 1) * E_local) of the layer;
+ * x_dev [seq, hidden] are THIS rank's tokens, selected_dev carries global expert ids, out_dev [seq, hidden].
+ * Collective: every rank calls it once per layer (seq may differ between ranks in the fused form).
+ * flags: 0 = the fused form when the peers' arenas are mapped (token rows are stored straight into the
+ * owning GPU's panel by the gather kernel, the down product's epilogue stores result rows straight into the
+ * home GPU's return panel, flags with bounded waits order the phases; bf16 tensor-core arithmetic for every
+ * batch size, bit-identical to the one-GPU tensor arm), else the baseline; FQ_EP_NCCL = the baseline (NCCL
+ * all-gather of tokens and routing, partial sums per rank, NCCL reduce-scatter; needs the same seq on every
+ * rank); FQ_EP_FUSED = the fused form or a decline. A routing that sends a rank more rows than its arena
+ * holds ends the layer with FQ_ERR_CAPACITY at the next synchronisation (size the arena for
+ * n_ranks * seq * top_k rows of 2 * hidden + 8 bytes, plus seq * top_k * hidden * 4). */
+enum { FQ_EP_AUTO = 0, FQ_EP_NCCL = 1, FQ_EP_FUSED = 2 };
+FQ_API int fq_moe_layer_ep(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev, size_t seq,
+                           size_t top_k, const int32_t* selected_dev, const float* weights_dev, int gated_op, float* out_dev,
+                           int flags, void* stream);
+/* Test seam: `world` ranks of the fused form emulated on ONE GPU (arrays of `world` pointers; every rank
+ * has `seq` tokens). The phases run in lockstep on the library stream, so every wait finds its flags posted
+ * by kernels that have already finished. Runs `layers` layers back to back over the same arenas and waits. */
+FQ_API int fq_ep_emulate_for_test(int world, const fq_weights* const* gate, const fq_weights* const* up,
+                                  const fq_weights* const* down, const float* const* x_dev, size_t seq, size_t top_k,
+                                  const int32_t* const* selected_dev, const float* const* weights_dev, float* const* out_dev,
+                                  size_t arena_bytes, int layers);
 /* exec/topk.zig:21-86 `routerTopK` on the device: logits [seq, E] -> selected/weights [seq, top_k]. */
 FQ_API int fq_router_topk_dev(const float* logits_dev, size_t seq, size_t n_expert, size_t top_k, int normalize,
                        int32_t* selected_dev, float* weights_dev, void* stream);

@@ -1,8 +1,10 @@
-"""GPU parity of the multi-GPU forms over NCCL, one process per GPU (skipped with fewer than two GPUs):
-column-sharded linear and the expert-parallel MoE layer against the same layer on one GPU.
+"""GPU parity of the multi-GPU forms, one process per GPU (skipped with fewer than two GPUs): the
+column-sharded linear and the expert-parallel MoE layer against the same layer on one GPU, through the
+Python host logic over torch.distributed and through the C ABI (fq_tp_init, fq_gemm_quant_nt_tp,
+fq_moe_layer_ep in its fused peer-memory form and its NCCL form).
 
-Exchanges use plain NCCL collectives; NVLS is switched off in the children so that a rank that dies
-in a failing test cannot leave a multicast binding behind."""
+NVLS is switched off in the children so that a rank that dies in a failing test cannot leave a multicast
+binding behind; the library's own kernels use plain peer stores and loads only."""
 import os
 import socket
 import sys
@@ -110,6 +112,42 @@ def _worker(rank: int, world: int, port: int, q):
         ok["ep_all_to_all"] = float((got_a2a - want_m).abs().max()) <= 1e-5 * scale
         ok["ep_gathered"] = float((got_g1 - want_m).abs().max()) <= 1e-5 * scale
         ok["ep_gathered_chunked"] = float((got_g2 - want_m).abs().max()) <= 1e-5 * scale
+
+        # ---- the same two exchanges behind the C ABI: fq_tp_init (NCCL inside the library, peer-mapped arenas),
+        # fq_gemm_quant_nt_tp and fq_moe_layer_ep in its fused form (peer stores + bounded flag waits) and its
+        # NCCL baseline form
+        from fucina_b200._lib import load
+
+        P.tp_init_torch(dist, arena_bytes=256 << 20)
+        ok["tp_init"] = load().fq_tp_ranks() == world and load().fq_tp_rank() == rank
+        ok["peer_access"] = P.tp_peer_access()
+        gathered = torch.full((world, m, hi - lo), float("nan"), device="cuda")
+        P.gemm_quant_nt_tp(shard, a, gathered, m, mode=P.MODE_INT8)
+        P.synchronize()
+        ok["tp_c_abi"] = bool(torch.equal(gathered.permute(1, 0, 2).reshape(m, n), want))
+        # tensor-arm reference of this rank's tokens on one GPU: the fused form must reproduce its bits
+        T2 = 150
+        rng2 = np.random.default_rng(60 + rank)
+        x2 = torch.from_numpy(rng2.standard_normal((T2, hidden)).astype(np.float32)).cuda()
+        s2, w2 = oracle.router_topk(rng2.standard_normal((T2, E)).astype(np.float32), topk, True)
+        s2d, w2d = torch.from_numpy(s2.astype(np.int32)).cuda(), torch.from_numpy(w2).cuda()
+        ref2 = torch.empty((T2, hidden), device="cuda")
+        load().fq_set_moe_tensor_for_test(1)
+        P.moe_layer_dev(*wfull, x2, T2, topk, s2d, w2d, ref2)
+        load().fq_set_moe_tensor_for_test(-1)
+        P.synchronize()
+        for layer in range(3):  # consecutive layers reuse the arenas: epochs order them
+            out2 = torch.full((T2, hidden), float("nan"), device="cuda")
+            P.moe_layer_ep(*wloc, x2, T2, topk, s2d, w2d, out2, flags=P.EP_FUSED)
+            P.synchronize()
+            ok[f"ep_fused_bits_layer{layer}"] = bool(torch.equal(out2, ref2))
+        out3 = torch.full((T2, hidden), float("nan"), device="cuda")
+        P.moe_layer_ep(*wloc, x2, T2, topk, s2d, w2d, out3, flags=P.EP_NCCL)
+        P.synchronize()
+        scale2 = float(ref2.pow(2).mean().sqrt())
+        ok["ep_nccl_form"] = float((out3 - ref2).abs().max()) <= 1e-5 * scale2
+        dist.barrier()
+        P.tp_shutdown()
     except Exception as e:  # report instead of hanging the peers
         ok["error"] = repr(e)
     finally:

@@ -152,3 +152,28 @@ def test_work_finish_wait_then_copy(P):
     from fucina_b200._lib import load
 
     load().fq_evict_resident(wts.ctypes.data)
+
+
+@pytest.mark.parametrize("fmt_name,n,m", [("q4_k", 4096, 1), ("q4_k", 4096, 4), ("q5_k", 1024, 9), ("q8_0", 4096, 2), ("q4_k", 1000, 3)])
+def test_shared_input_batch_of_decode_shapes_is_one_stacked_launch(P, fmt_name, n, m):
+    # Q/K/V-style batch: three matrices, one decode-sized input (src/backend/cuda.zig:2441-2492). The stack runs as
+    # ONE launch of the streaming kernel; c keeps the [matrix][m][n] layout of the per-matrix form.
+    fmt = oracle.FORMATS[fmt_name]
+    k, batch = 4096, 3
+    blocks = make_weights(fmt_name, n * batch, k, seed=53)
+    a = acts(m, k, 54)
+    before = P.trace_counters()["launches"]
+    got = P.gemm_quant_nt_shared_a_batch(fmt, blocks, a, n, batch, cacheable=False)
+    after = P.trace_counters()["launches"]
+    for b in range(batch):
+        want = oracle.matmul_fast(fmt, blocks[b * n:(b + 1) * n], a)
+        assert_close(got[b * m:(b + 1) * m], want, TOL_INT8, f"{fmt_name} matrix {b} of the stack, m={m}")
+    assert after - before <= 3  # repack + (quantise) + one product, not one product per matrix
+    # the asynchronous entry takes the same route (resident weights)
+    wk = P.gemm_quant_nt_async(fmt, blocks, a, n, m, k, batch=batch)
+    wk.finish(copy_to_host=True)
+    assert np.array_equal(wk.out.view(np.uint32), got.view(np.uint32))
+    wk.destroy()
+    from fucina_b200._lib import load
+
+    load().fq_evict_resident(blocks.ctypes.data)
