@@ -904,7 +904,15 @@ def sub_multi(args, P, torch, rank: int, world: int, local: int) -> list[dict]:
 
     per = E // world
     gate, up, down = _moe_stacks(P, torch, per, 1300 + 10 * rank)
-    ep = P.ExpertParallel.create(rank, world, dist) if hasattr(P, "ExpertParallel") else None
+    # the library's own exchange: NCCL communicator + peer-mapped arenas sized for the worst-case routing of the
+    # largest case (every pair of every rank on one GPU)
+    pairs_max = 1024 * topk
+    fused = False
+    try:
+        P.tp_init_torch(dist, arena_bytes=(1 << 20) + pairs_max * h * 4 + world * pairs_max * (h * 2 + 8))
+        fused = P.tp_peer_access()
+    except Exception as e:  # noqa: BLE001
+        recs.append({"workload": "fq_tp_init", "error": str(e)[:300]})
 
     def partial_rows(x_all, sel_all, w_all):
         o = torch.empty_like(x_all)
@@ -922,19 +930,26 @@ def sub_multi(args, P, torch, rank: int, world: int, local: int) -> list[dict]:
         out = torch.empty((T, h), device="cuda")
         torch.cuda.synchronize()
         forms = []
-        if ep is not None:
+        if fused:
             def step_fused():
                 P.router_topk_dev(logits, T, E, topk, True, sel, wts)
-                ep.moe_layer(gate, up, down, x, T, topk, sel, wts, out)
+                P.moe_layer_ep(gate, up, down, x, T, topk, sel, wts, out, flags=P.EP_FUSED)
 
-            forms.append(("fused dispatch / return over peer memory (fq_moe_layer_ep)", step_fused))
+            forms.append(("fq_moe_layer_ep, fused form: token rows and result rows stored straight into peer memory over NVLink, "
+                          "bounded flag waits", step_fused))
+
+        def step_lib_nccl():
+            P.router_topk_dev(logits, T, E, topk, True, sel, wts)
+            P.moe_layer_ep(gate, up, down, x, T, topk, sel, wts, out, flags=P.EP_NCCL)
+
+        forms.append(("fq_moe_layer_ep, baseline form: NCCL all-gather + reduce-scatter inside the library", step_lib_nccl))
 
         def step_nccl():
             with torch.cuda.stream(ext):
                 P.router_topk_dev(logits, T, E, topk, True, sel, wts)
                 moe.forward_gathered(x, sel, wts, partial_rows, exchange_dtype=torch.bfloat16 if T >= 512 else None)
 
-        forms.append(("NCCL all-gather of token rows + reduce-scatter of partial sums", step_nccl))
+        forms.append(("torch.distributed host logic: NCCL all-gather of token rows + reduce-scatter of partial sums", step_nccl))
         for name, fn in forms:
             try:
                 ms = timed(fn)
@@ -967,14 +982,27 @@ def sub_multi(args, P, torch, rank: int, world: int, local: int) -> list[dict]:
                 lin.forward(a)
 
         try:
+            if (hi - lo) * world == n:
+                gathered = torch.empty((world, m, hi - lo), device="cuda")
+                ms_lib = timed(lambda: P.gemm_quant_nt_tp(w, a, gathered, m, mode=P.MODE_TENSOR))
+            else:
+                ms_lib = None
             ms = timed(step)
+            if ms_lib is not None and ms_lib < ms:
+                ms = ms_lib
             ms_compute = timed(lambda: gemm(a))
-            recs.append({"workload": f"Q4_K prefill {m}x{n}x{k}, output columns sharded over {world} GPUs, f32 all-gather (NCCL)",
+            recs.append({"workload": f"Q4_K prefill {m}x{n}x{k}, output columns sharded over {world} GPUs, f32 all-gather (NCCL; "
+                                     f"fq_gemm_quant_nt_tp {'%.4f ms' % ms_lib if ms_lib is not None else 'n/a'})",
                          "metric": "Q4_K prefill TFLOPS", "n_gpus": world, "value": round(2.0 * m * n * k / ms / 1e9, 1), "unit": "TFLOP/s",
                          "ms": round(ms, 4), "ms_compute_only": round(ms_compute, 4),
                          "gathered_MB_per_rank": round(m * n * 4 * (world - 1) / world / 1e6, 1)})
         except Exception as e:  # noqa: BLE001
             recs.append({"workload": f"column-sharded prefill {m}", "error": str(e)[:300]})
+    barrier(world)
+    try:
+        P.tp_shutdown()
+    except Exception:  # noqa: BLE001
+        pass
     return recs
 
 

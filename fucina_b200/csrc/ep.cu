@@ -6,9 +6,9 @@
 // (src/exec/moe_chain.zig:307-330), the result equals the one-GPU tensor arm bit for bit.
 //
 // Fused exchange (the default when every peer's arena is mapped), per layer, epoch-numbered flags:
-//   count     histogram of this rank's pairs by global expert; the row goes into EVERY peer's count table
-//             (plain peer stores), followed by a flag per peer.
-//   plan      waits (bounded) for every rank's counts. The full [rank][expert] table fixes every pair's row in
+//   plan      histogram of this rank's pairs by global expert; the row goes into EVERY peer's count table
+//             (plain peer stores), followed by a flag per peer; then the bounded wait for every rank's row.
+//             The full [rank][expert] table fixes every pair's row in
 //             the owning rank's token panel -- expert-major, source-rank-minor, the order one global counting
 //             sort would give -- so sources write final positions and the owner multiplies whole expert runs.
 //             Also builds this rank's tile lists and checks every panel's capacity (all ranks see the same table
@@ -28,6 +28,7 @@
 // synchronisation; equal to the fused form within f32 summation order.
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <vector>
 
 #include "multi.h"
@@ -96,6 +97,7 @@ struct EpPlan {
     int ok;            // 0: a wait gave up or a panel would overflow -- the later kernels do nothing
     int n_rows;        // rows arriving in this rank's panel
     int n_gu, n_dn;    // tiles of the gate/up and the down product
+    int done[2];       // CTAs of the dispatch kernel / the down product that have finished (zeroed by the plan)
     unsigned long long dst_x[kMaxPeers];     // byte offset of rank d's x panel / meta array inside ITS arena
     unsigned long long dst_meta[kMaxPeers];
 };
@@ -105,7 +107,7 @@ struct EpArgs {
     int epoch;
     int pairs, top_k, hidden, n_expert, per;  // this rank's routed pairs; experts in total and per rank
     EpLayout mine;
-    int tile_tokens, rt_gu, rt_dn, max_tok_tiles;
+    int tile_gu, tile_dn, rt_gu, rt_dn;  // token-tile widths of the two products, weight-row tiles per token tile
     const int* selected;
     int* status;
     EpPlan* plan;
@@ -114,45 +116,52 @@ struct EpArgs {
     TcTile* t_dn;
 };
 
-// ---- count: histogram + publication ------------------------------------------------------------------
-__global__ void ep_count_kernel(const EpArgs A) {
-    extern __shared__ int cnt[];
-    for (int e = threadIdx.x; e < A.n_expert; e += blockDim.x) cnt[e] = 0;
-    __syncthreads();
-    for (int p = threadIdx.x; p < A.pairs; p += blockDim.x) {
-        const int e = A.selected[p];
-        if (e >= 0 && e < A.n_expert) atomicAdd(&cnt[e], 1);
-    }
-    __syncthreads();
-    for (int d = 0; d < A.v.world; ++d) {
-        int* row = table_row(A.v.peer[d], A.v.rank);
-        if (threadIdx.x == 0) {
-            row[0] = (int)(A.mine.off_meta & 0xffffffffu), row[1] = (int)(A.mine.off_meta >> 32);
-            row[2] = (int)(A.mine.off_x & 0xffffffffu), row[3] = (int)(A.mine.off_x >> 32);
-            row[4] = A.mine.rows_cap;
-            row[5] = A.pairs;
-        }
-        for (int e = threadIdx.x; e < A.n_expert; e += blockDim.x) row[kHdrInts + e] = cnt[e];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if ((int)threadIdx.x < A.v.world) st_release_sys(flags_of(A.v.peer[threadIdx.x], 0) + A.v.rank, A.epoch);
-}
-
-// ---- plan ---------------------------------------------------------------------------------------------
-// One CTA. Shared memory: tbl[world][E] | tot[E] | cursor[E] | base[E] | tiles0[per]
-__global__ void ep_plan_kernel(const EpArgs A) {
+// ---- plan: count, publish, wait, place ------------------------------------------------------------------
+// One CTA. Histogram of this rank's pairs by global expert; the row goes into every peer's table followed by a
+// flag per peer; then the bounded wait for every rank's row, and from the full table: every pair's final row in
+// its owner's panel, this rank's tile lists, the capacity verdict.
+// Shared memory: tbl[world][E] | tot[E] | cursor[E] | base[E] | tiles_gu[per] | tiles_dn[per]
+// `stages`: bit 0 = count and publish, bit 1 = wait and place. A real rank runs both in one launch; the one-GPU
+// emulation publishes for every rank first and places afterwards (no kernel may wait for one that runs later).
+__global__ void ep_plan_kernel(const EpArgs A, int stages) {
     extern __shared__ int sh[];
     const int E = A.n_expert, W = A.v.world, per = A.per;
     int* tbl = sh;
     int* tot = tbl + W * E;
     int* cursor = tot + E;
     int* base = cursor + E;
-    int* tiles0 = base + E;
+    int* tiles_gu = base + E;
+    int* tiles_dn = tiles_gu + per;
     __shared__ int s_ok;
-    __shared__ int s_rows, s_tiles;
+    __shared__ int s_rows;
     if (threadIdx.x == 0) s_ok = 1;
+    if (stages & 1) {
+        // -- count and publish
+        for (int e = threadIdx.x; e < E; e += blockDim.x) tot[e] = 0;
+        __syncthreads();
+        for (int p = threadIdx.x; p < A.pairs; p += blockDim.x) {
+            const int e = A.selected[p];
+            if (e >= 0 && e < E) atomicAdd(&tot[e], 1);
+        }
+        __syncthreads();
+        for (int d = 0; d < W; ++d) {
+            int* row = table_row(A.v.peer[d], A.v.rank);
+            if (threadIdx.x == 0) {
+                row[0] = (int)(A.mine.off_meta & 0xffffffffu), row[1] = (int)(A.mine.off_meta >> 32);
+                row[2] = (int)(A.mine.off_x & 0xffffffffu), row[3] = (int)(A.mine.off_x >> 32);
+                row[4] = A.mine.rows_cap;
+                row[5] = A.pairs;
+            }
+            for (int e = threadIdx.x; e < E; e += blockDim.x) row[kHdrInts + e] = tot[e];
+        }
+        if (threadIdx.x < 2) A.plan->done[threadIdx.x] = 0;  // the dispatch and down kernels of this layer count their CTAs here
+        __threadfence_system();
+        __syncthreads();
+        if ((int)threadIdx.x < W) st_release_sys(flags_of(A.v.peer[threadIdx.x], 0) + A.v.rank, A.epoch);
+    }
+    if (!(stages & 2)) return;
     __syncthreads();
+    // -- wait for every rank's row
     if ((int)threadIdx.x < W && !wait_flag(flags_of(A.v.peer[A.v.rank], 0) + threadIdx.x, A.epoch)) s_ok = 0;
     __syncthreads();
     if (!s_ok) {
@@ -197,30 +206,30 @@ __global__ void ep_plan_kernel(const EpArgs A) {
         return;
     }
     for (int e = threadIdx.x; e < E; e += blockDim.x) cursor[e] += base[e];
-    // tile lists of this rank's experts: token tiles per expert, exclusive scan by one thread (at most a few hundred experts)
+    // tile lists of this rank's experts: token tiles per expert (the two products may cut them differently),
+    // exclusive scans by one thread (at most a few hundred experts)
     if (threadIdx.x == 0) {
-        int nt = 0;
+        int ngu = 0, ndn = 0;
         for (int le = 0; le < per; ++le) {
-            tiles0[le] = nt;
-            nt += (tot[A.v.rank * per + le] + A.tile_tokens - 1) / A.tile_tokens;
+            const int c = tot[A.v.rank * per + le];
+            tiles_gu[le] = ngu, tiles_dn[le] = ndn;
+            ngu += (c + A.tile_gu - 1) / A.tile_gu;
+            ndn += (c + A.tile_dn - 1) / A.tile_dn;
         }
-        s_tiles = nt;
         A.plan->ok = 1;
         A.plan->n_rows = s_rows;
-        A.plan->n_gu = nt * A.rt_gu;
-        A.plan->n_dn = nt * A.rt_dn;
+        A.plan->n_gu = ngu * A.rt_gu;
+        A.plan->n_dn = ndn * A.rt_dn;
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     for (int le = warp; le < per; le += warps) {
-        const int e = A.v.rank * per + le, c = tot[e], row0 = base[e], tile0 = tiles0[le];
-        for (int t0 = 0, tt = 0; t0 < c; t0 += A.tile_tokens, ++tt) {
-            const int nt = min(A.tile_tokens, c - t0);
-            for (int rt = lane; rt < A.rt_gu; rt += 32) A.t_gu[(size_t)(tile0 + tt) * A.rt_gu + rt] = {le, rt, row0 + t0, nt};
-            for (int rt = lane; rt < A.rt_dn; rt += 32) A.t_dn[(size_t)(tile0 + tt) * A.rt_dn + rt] = {le, rt, row0 + t0, nt};
-        }
+        const int e = A.v.rank * per + le, c = tot[e], row0 = base[e];
+        for (int t0 = 0, tt = 0; t0 < c; t0 += A.tile_gu, ++tt)
+            for (int rt = lane; rt < A.rt_gu; rt += 32) A.t_gu[(size_t)(tiles_gu[le] + tt) * A.rt_gu + rt] = {le, rt, row0 + t0, min(A.tile_gu, c - t0)};
+        for (int t0 = 0, tt = 0; t0 < c; t0 += A.tile_dn, ++tt)
+            for (int rt = lane; rt < A.rt_dn; rt += 32) A.t_dn[(size_t)(tiles_dn[le] + tt) * A.rt_dn + rt] = {le, rt, row0 + t0, min(A.tile_dn, c - t0)};
     }
-    __syncthreads();
     // every pair's final row in its owner's panel (positions inside a (source, expert) run do not affect any value)
     for (int p = threadIdx.x; p < A.pairs; p += blockDim.x) {
         const int e = A.selected[p];
@@ -232,32 +241,42 @@ __global__ void ep_plan_kernel(const EpArgs A) {
     }
 }
 
+// The last CTA of a grid to get here tells every peer "rank `rank` finished phase `kind` of layer `epoch`".
+// Every thread's peer stores are fenced system-wide first; the CTA count lives in the layer's plan block.
+__device__ __forceinline__ void signal_when_grid_done(const EpView& v, int* counter, int kind, int epoch) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(counter, 1) == (int)gridDim.x - 1) {
+        __threadfence_system();
+        for (int d = 0; d < v.world; ++d) st_release_sys(flags_of(v.peer[d], kind) + v.rank, epoch);
+    }
+}
+
 // ---- dispatch: bf16 token rows and return addresses into the owners' panels ---------------------------
 __global__ void ep_dispatch_kernel(const EpArgs A, const float* __restrict__ x) {
-    if (!A.plan->ok) return;
-    const int h4 = A.hidden >> 2;
-    const size_t total = (size_t)A.pairs * h4;
+    if (!A.plan->ok) {
+        signal_when_grid_done(A.v, &A.plan->done[0], 1, A.epoch);  // the peers' waits still end
+        return;
+    }
+    const int h8 = A.hidden >> 3;
+    const size_t total = (size_t)A.pairs * h8;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int p = (int)(i / h4), col = (int)(i % h4) * 4;
+        const int p = (int)(i / h8), col = (int)(i % h8) * 8;
         const int2 dst = A.pair_dst[p];
         if (dst.x < 0) continue;
         uint8_t* arena = A.v.peer[dst.x];
-        const float4 v = *reinterpret_cast<const float4*>(x + (size_t)(p / A.top_k) * A.hidden + col);
-        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-        uint2 o;
-        o.x = *reinterpret_cast<const uint32_t*>(&lo);
-        o.y = *reinterpret_cast<const uint32_t*>(&hi);
+        const float4* src = reinterpret_cast<const float4*>(x + (size_t)(p / A.top_k) * A.hidden + col);
+        const float4 v0 = __ldg(src), v1 = __ldg(src + 1);
+        const __nv_bfloat162 b0 = __floats2bfloat162_rn(v0.x, v0.y), b1 = __floats2bfloat162_rn(v0.z, v0.w);
+        const __nv_bfloat162 b2 = __floats2bfloat162_rn(v1.x, v1.y), b3 = __floats2bfloat162_rn(v1.z, v1.w);
+        uint4 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&b0), o.y = *reinterpret_cast<const uint32_t*>(&b1);
+        o.z = *reinterpret_cast<const uint32_t*>(&b2), o.w = *reinterpret_cast<const uint32_t*>(&b3);
         __nv_bfloat16* panel = reinterpret_cast<__nv_bfloat16*>(arena + A.plan->dst_x[dst.x]);
-        *reinterpret_cast<uint2*>(panel + (size_t)dst.y * A.hidden + col) = o;
+        *reinterpret_cast<uint4*>(panel + (size_t)dst.y * A.hidden + col) = o;
         if (col == 0) reinterpret_cast<int2*>(arena + A.plan->dst_meta[dst.x])[dst.y] = make_int2(A.v.rank, p);
     }
-    __threadfence_system();  // this thread's peer stores are visible system-wide before the flag kernel's release
-}
-
-// one flag per peer: "rank `rank` finished phase `kind` of layer `epoch`"
-__global__ void ep_signal_kernel(const EpView v, int kind, int epoch) {
-    __threadfence_system();
-    if ((int)threadIdx.x < v.world) st_release_sys(flags_of(v.peer[threadIdx.x], kind) + v.rank, epoch);
+    signal_when_grid_done(A.v, &A.plan->done[0], 1, A.epoch);
 }
 
 // ---- combine: out[t] = sum over the token's slots, in slot order, of w[p] * ret[p] ---------------------
@@ -304,6 +323,7 @@ struct EpCall {
     uint8_t* scratch;
     __nv_bfloat16* g_panel;
     int max_gu, max_dn;
+    int plan_stages = 3;  // see ep_plan_kernel
 };
 
 int ep_prepare(Ctx* ctx, const EpView& v, int epoch, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x,
@@ -318,14 +338,17 @@ int ep_prepare(Ctx* ctx, const EpView& v, int epoch, const DevWeights& gate, con
     a.pairs = pairs, a.top_k = top_k, a.hidden = hidden, a.n_expert = E, a.per = per;
     a.mine = ep_layout(v.arena_bytes, pairs, hidden);
     if (a.mine.rows_cap < 128) return fail(FQ_DECLINED_BUDGET, "exchange arena of %zu bytes is too small for %d pairs of %d elements", v.arena_bytes, pairs, hidden);
-    a.tile_tokens = 128;  // the fused gate/up pass (SwiGLU in the epilogue) runs on 128-token tiles
+    // the fused gate/up pass (SwiGLU in the epilogue) runs on 128-token tiles; the down product takes 256-token
+    // tiles once expert runs are long (a weight is expanded to bf16 once per token tile)
+    static const int down_tile_env = getenv("FUCINA_B200_EP_DOWN_TILE") ? atoi(getenv("FUCINA_B200_EP_DOWN_TILE")) : 0;
+    a.tile_gu = 128;
+    a.tile_dn = down_tile_env == 128 || down_tile_env == 256 ? down_tile_env : (pairs > 128 * per ? 256 : 128);
     a.rt_gu = (out_pe + 127) / 128, a.rt_dn = (hidden + 127) / 128;
-    a.max_tok_tiles = per + a.mine.rows_cap / a.tile_tokens;
     a.selected = selected;
     a.status = ctx->status_dev;
     c->gate = &gate, c->up = &up, c->down = &down;
     c->x = x, c->weights = weights, c->out = out, c->seq = seq;
-    c->max_gu = a.max_tok_tiles * a.rt_gu, c->max_dn = a.max_tok_tiles * a.rt_dn;
+    c->max_gu = (per + a.mine.rows_cap / a.tile_gu) * a.rt_gu, c->max_dn = (per + a.mine.rows_cap / a.tile_dn) * a.rt_dn;
     size_t off = 0;
     auto take = [&](size_t bytes) {
         const size_t o = off;
@@ -351,25 +374,18 @@ int ep_phase(Ctx* ctx, EpCall& c, int phase, cudaStream_t st) {
     cudaError_t e = cudaSuccess;
     int rc = FQ_OK;
     switch (phase) {
-        case 0:
-            ep_count_kernel<<<1, 1024, sizeof(int) * a.n_expert, st>>>(a);
+        case 0: {
+            const size_t smem = sizeof(int) * ((size_t)a.v.world * a.n_expert + 3 * (size_t)a.n_expert + 2 * (size_t)a.per);
+            // at most 8 * 1024 + 3 * 1024 + 2 * 128 ints: fits 48 KB
+            ep_plan_kernel<<<1, 1024, smem, st>>>(a, c.plan_stages);
             break;
+        }
         case 1: {
-            const size_t smem = sizeof(int) * ((size_t)a.v.world * a.n_expert + 3 * (size_t)a.n_expert + a.per);
-            if (smem > 48 * 1024) {
-                static bool granted = false;
-                if (!granted && cudaFuncSetAttribute(ep_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) == cudaSuccess) granted = true;
-            }
-            ep_plan_kernel<<<1, 1024, smem, st>>>(a);
+            int blocks = (int)(((size_t)a.pairs * (a.hidden / 8) + 255) / 256);
+            ep_dispatch_kernel<<<blocks > 148 * 8 ? 148 * 8 : (blocks < 1 ? 1 : blocks), 256, 0, st>>>(a, c.x);
             break;
         }
         case 2: {
-            int blocks = (int)(((size_t)a.pairs * (a.hidden / 4) + 255) / 256);
-            ep_dispatch_kernel<<<blocks > 148 * 8 ? 148 * 8 : (blocks < 1 ? 1 : blocks), 256, 0, st>>>(a, c.x);
-            ep_signal_kernel<<<1, 32, 0, st>>>(a.v, 1, a.epoch);
-            break;
-        }
-        case 3: {
             TcPeer peer;
             peer.wait_flags = flags_of(me, 1);
             peer.n_wait = a.v.world;
@@ -378,13 +394,18 @@ int ep_phase(Ctx* ctx, EpCall& c, int phase, cudaStream_t st) {
                                                a.t_gu, &a.plan->n_gu, c.max_gu, st, &peer);
             break;
         }
-        case 4: {
+        case 3: {
             TcPeer peer;
             peer.row_meta = reinterpret_cast<const int2*>(me + a.mine.off_meta);
-            for (int s = 0; s < a.v.world; ++s) peer.dst_base[s] = reinterpret_cast<float*>(a.v.peer[s] + kFixedBytes);
+            for (int s = 0; s < a.v.world; ++s) {
+                peer.dst_base[s] = reinterpret_cast<float*>(a.v.peer[s] + kFixedBytes);
+                peer.signal_flag[s] = flags_of(a.v.peer[s], 2) + a.v.rank;
+            }
+            peer.n_signal = a.v.world;
+            peer.signal_value = a.epoch;
+            peer.done_counter = &a.plan->done[1];
             rc = gemm_tensor_grouped_dev(ctx, *c.down, c.g_panel, (size_t)a.mine.rows_cap, nullptr, (size_t)a.hidden, a.t_dn, &a.plan->n_dn, c.max_dn,
-                                         a.tile_tokens, st, &peer);
-            if (rc == FQ_OK) ep_signal_kernel<<<1, 32, 0, st>>>(a.v, 2, a.epoch);
+                                         a.tile_dn, st, &peer);
             break;
         }
         default: {
@@ -398,7 +419,7 @@ int ep_phase(Ctx* ctx, EpCall& c, int phase, cudaStream_t st) {
     e = cudaGetLastError();
     return e == cudaSuccess ? FQ_OK : cuda_fail(e, "expert-parallel launch");
 }
-constexpr int kEpPhases = 6;
+constexpr int kEpPhases = 5;
 
 int check_ep_weights(const fq_weights* gate, const fq_weights* up, const fq_weights* down, size_t seq, size_t top_k, int gated_op) {
     if (!gate || !up || !down) return fail(FQ_DECLINED_ARGS, "null weights");
@@ -499,6 +520,10 @@ int fq_moe_layer_ep(const fq_weights* gate, const fq_weights* up, const fq_weigh
 int fq_ep_emulate_for_test(int world, const fq_weights* const* gate, const fq_weights* const* up, const fq_weights* const* down,
                            const float* const* x_dev, size_t seq, size_t top_k, const int32_t* const* selected_dev,
                            const float* const* weights_dev, float* const* out_dev, size_t arena_bytes, int layers) {
+    // layers < 0: one layer in which the LAST rank's count publication is dropped (a message that never arrives):
+    // every rank's bounded wait gives up, the status word reports FQ_ERR_TIMEOUT, nothing hangs
+    const bool drop_last = layers < 0;
+    if (drop_last) layers = 1;
     if (world < 1 || world > kMaxPeers || !gate || !up || !down || !x_dev || !selected_dev || !weights_dev || !out_dev || layers < 1)
         return fail(FQ_DECLINED_ARGS, "bad emulation request");
     for (int r = 0; r < world; ++r) {
@@ -527,6 +552,12 @@ int fq_ep_emulate_for_test(int world, const fq_weights* const* gate, const fq_we
             rc = ep_prepare(ctx, v, layer, gate[r]->dw, up[r]->dw, down[r]->dw, x_dev[r], (int)seq, (int)top_k, selected_dev[r], weights_dev[r],
                             out_dev[r], st, &calls[r]);
             if (rc == FQ_OK) ++prepared;
+        }
+        // publication of every rank's counts first, then the phases in lockstep
+        for (int r = 0; r < world && rc == FQ_OK; ++r) {
+            calls[r].plan_stages = 1;
+            if (!(drop_last && world > 1 && r == world - 1)) rc = ep_phase(ctx, calls[r], 0, st);
+            calls[r].plan_stages = 2;
         }
         for (int ph = 0; ph < kEpPhases && rc == FQ_OK; ++ph)
             for (int r = 0; r < world && rc == FQ_OK; ++r) rc = ep_phase(ctx, calls[r], ph, st);

@@ -844,11 +844,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             }
             if (!ok) break;
         }
+        if (A.peer.row_meta) __threadfence_system();  // this thread's peer stores are visible system-wide before the CTA reports
     }
 
     // common exit: everyone meets here (also after an abort), then the allocating warp frees TMEM
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (A.peer.n_signal && threadIdx.x == 32) {
+        // the last CTA to finish tells the peers that every result row of this product is in their panels
+        __threadfence_system();
+        if (atomicAdd(A.peer.done_counter, 1) == (int)gridDim.x - 1) {
+            __threadfence_system();
+            for (int i = 0; i < A.peer.n_signal; ++i)
+                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(A.peer.signal_flag[i]), "r"(A.peer.signal_value) : "memory");
+        }
+    }
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

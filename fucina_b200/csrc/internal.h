@@ -127,6 +127,12 @@ struct TcPeer {
     int wait_value = 0;
     const int2* row_meta = nullptr;
     float* dst_base[kMaxPeers] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    //  * signal: the last CTA of the grid to finish (counted in *done_counter, which the caller zeroes) stores
+    //    signal_value into signal_flag[i], i < n_signal, after a system-wide fence: "my result rows are in your panel".
+    int* done_counter = nullptr;
+    int* signal_flag[kMaxPeers] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int n_signal = 0;
+    int signal_value = 0;
 };
 cudaError_t launch_add_f32(float* c, const float* t, size_t n, cudaStream_t st);
 cudaError_t launch_f32_to_bf16(const float* src, void* dst, size_t n, cudaStream_t st);

@@ -268,7 +268,9 @@ FQ_API int fq_moe_layer_ep(const fq_weights* gate, const fq_weights* up, const f
                            int flags, void* stream);
 /* Test seam: `world` ranks of the fused form emulated on ONE GPU (arrays of `world` pointers; every rank
  * has `seq` tokens). The phases run in lockstep on the library stream, so every wait finds its flags posted
- * by kernels that have already finished. Runs `layers` layers back to back over the same arenas and waits. */
+ * by kernels that have already finished. Runs `layers` layers back to back over the same arenas and waits.
+ * layers < 0: one layer in which the last rank's count publication is dropped, so every rank's bounded wait
+ * runs out (about a second each) and the call returns FQ_ERR_TIMEOUT with the context still usable. */
 FQ_API int fq_ep_emulate_for_test(int world, const fq_weights* const* gate, const fq_weights* const* up,
                                   const fq_weights* const* down, const float* const* x_dev, size_t seq, size_t top_k,
                                   const int32_t* const* selected_dev, const float* const* weights_dev, float* const* out_dev,

@@ -141,3 +141,30 @@ def test_entries_decline_before_tp_init(P, torch):
             P.gemm_quant_nt_tp(w, a, c, 1)
         assert load().fq_tp_rank() == -1 and load().fq_tp_peer_access() == 0
     w.free()
+
+
+def test_a_rank_that_never_publishes_ends_in_a_timeout_status_not_a_hang(P, torch):
+    # failure detection without a fault: the last rank's count row is dropped, so no flag ever arrives for it; every
+    # rank's wait is bounded (about a second), gives up, records the time-out status, and the remaining kernels of
+    # the layer fall through. The context stays usable.
+    import time
+
+    fmt_name, hidden, out_pe, n_expert, top_k, world, seq = "q5_k", 256, 256, 4, 2, 2, 16
+    host, full, shards, xs, sels, wts = build_case(P, torch, fmt_name, hidden, out_pe, n_expert, top_k, world, seq, seed=620)
+    xd = [torch.from_numpy(x).cuda() for x in xs]
+    sd = [torch.from_numpy(s).cuda() for s in sels]
+    wd = [torch.from_numpy(w).cuda() for w in wts]
+    od = [torch.full((seq, hidden), 5.0, device="cuda") for _ in range(world)]
+    arena = 64 * 1024 + seq * top_k * hidden * 4 + world * seq * top_k * (hidden * 2 + 8) + (1 << 20)
+    args = ([s[0] for s in shards], [s[1] for s in shards], [s[2] for s in shards], xd, seq, top_k, sd, wd, od, arena)
+    t0 = time.perf_counter()
+    with pytest.raises(P.DeviceError) as e:
+        P.ep_emulate_for_test(*args, layers=-1)
+    assert e.value.code == -2  # FQ_ERR_TIMEOUT
+    assert time.perf_counter() - t0 < 30.0
+    assert all(float(o.min()) == 5.0 and float(o.max()) == 5.0 for o in od)  # no output was produced from a partial exchange
+    P.ep_emulate_for_test(*args)  # and the next layer runs normally
+    want = single_gpu_tensor_arm(P, torch, full, xs[0], sels[0], wts[0], top_k)
+    assert np.array_equal(od[0].cpu().numpy().view(np.uint32), want.view(np.uint32))
+    for w in full + [w for s in shards for w in s]:
+        w.free()
