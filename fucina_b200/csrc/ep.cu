@@ -28,6 +28,7 @@
 // synchronisation; equal to the fused form within f32 summation order.
 #include <cuda_bf16.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <vector>
 
@@ -420,6 +421,7 @@ int ep_phase(Ctx* ctx, EpCall& c, int phase, cudaStream_t st) {
     return e == cudaSuccess ? FQ_OK : cuda_fail(e, "expert-parallel launch");
 }
 constexpr int kEpPhases = 5;
+std::vector<std::vector<cudaEvent_t>> g_ep_events;  // FUCINA_B200_EP_TRACE: one set of phase events per layer
 
 int check_ep_weights(const fq_weights* gate, const fq_weights* up, const fq_weights* down, size_t seq, size_t top_k, int gated_op) {
     if (!gate || !up || !down) return fail(FQ_DECLINED_ARGS, "null weights");
@@ -437,6 +439,32 @@ bool fused_form_serves(const DevWeights& g, const DevWeights& d) {
 }
 
 }  // namespace
+
+void ep_trace_dump(int rank) {
+    if (g_ep_events.empty()) return;
+    static const char* names[kEpPhases] = {"plan", "dispatch", "gate/up", "down", "combine"};
+    double sum[kEpPhases] = {0, 0, 0, 0, 0};
+    long long layers = 0;
+    // the second half of the recorded layers: steady state, the host running ahead of the device
+    for (size_t i = 0; i < g_ep_events.size(); ++i) {
+        auto& ev = g_ep_events[i];
+        if (i >= g_ep_events.size() / 2 && cudaEventSynchronize(ev[kEpPhases]) == cudaSuccess) {
+            for (int ph = 0; ph < kEpPhases; ++ph) {
+                float ms = 0.0f;
+                if (cudaEventElapsedTime(&ms, ev[ph], ev[ph + 1]) == cudaSuccess) sum[ph] += ms;
+            }
+            ++layers;
+        }
+        for (auto& e : ev) cudaEventDestroy(e);
+    }
+    g_ep_events.clear();
+    cudaGetLastError();
+    char line[512];
+    int n = snprintf(line, sizeof line, "[fucina_b200] rank %d expert-parallel layers=%lld, mean device ms per phase:", rank, layers);
+    for (int ph = 0; ph < kEpPhases && layers; ++ph) n += snprintf(line + n, sizeof line - n, " %s=%.4f", names[ph], sum[ph] / (double)layers);
+    fprintf(stderr, "%s\n", line);
+}
+
 }  // namespace fq
 
 using namespace fq;
@@ -469,7 +497,20 @@ int fq_moe_layer_ep(const fq_weights* gate, const fq_weights* up, const fq_weigh
             return rc;
         }
         int rc = FQ_OK;
-        for (int ph = 0; ph < kEpPhases && rc == FQ_OK; ++ph) rc = ep_phase(ctx, c, ph, st);
+        // FUCINA_B200_EP_TRACE=1: device time of each phase (CUDA events on the layer's stream), summed per phase and
+        // printed by fq_tp_shutdown -- the per-kind timing of backend/cuda.zig:231-257 for this layer
+        static const bool trace = getenv("FUCINA_B200_EP_TRACE") != nullptr;
+        std::vector<cudaEvent_t> ev;
+        if (trace && g_ep_events.size() < 4096) {
+            ev.resize(kEpPhases + 1);
+            for (auto& e : ev) cudaEventCreate(&e);
+            cudaEventRecord(ev[0], st);
+        }
+        for (int ph = 0; ph < kEpPhases && rc == FQ_OK; ++ph) {
+            rc = ep_phase(ctx, c, ph, st);
+            if (!ev.empty()) cudaEventRecord(ev[ph + 1], st);
+        }
+        if (!ev.empty()) g_ep_events.push_back(ev);  // read when the trace is dumped: no host wait per layer
         dev_free_on(c.scratch, st);
         return rc;
     }

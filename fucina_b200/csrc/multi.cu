@@ -184,6 +184,7 @@ int fq_tp_shutdown(void) {
     if (!g_tp_ready) return FQ_OK;
     Ctx* ctx = context();
     if (ctx) cudaStreamSynchronize(ctx->stream);
+    ep_trace_dump(g_tp.rank);
     unmap_peers(g_tp);
     if (g_tp.arena) cudaFree(g_tp.arena);
     if (g_tp.comm) g_nccl.comm_destroy(g_tp.comm);

@@ -29,4 +29,7 @@ int tp_reduce_scatter_f32(const float* send, float* recv, size_t count_per_rank,
 int moe_layer_shard_dev(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev, int seq,
                         int top_k, const int* selected_dev, const float* weights_dev, int expert_base, float* partial_dev, cudaStream_t st);
 
+// ep.cu: print and clear the per-phase device times gathered under FUCINA_B200_EP_TRACE
+void ep_trace_dump(int rank);
+
 }  // namespace fq
