@@ -317,6 +317,10 @@ def run_ours(args) -> dict:
     # ---- e2e: blocking C-ABI call, host buffers, resident weights ----
     host_x = [x.cpu().numpy() for x in xs]
     host_y = [np.empty((batch, n), np.float32) for n in STACK_N]
+    # the caller's activation and result storage is registered once, as the reference registers tensor storage
+    # for its lifetime (src/backend/cuda.zig:1047-1082): DMA reads it and the kernels write it without a bounce
+    for arr in host_x + host_y:
+        P.host_register(arr)
 
     def step_host(i: int):
         st = stacks[i % n_copies]
@@ -333,10 +337,8 @@ def run_ours(args) -> dict:
     P.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0, world)
     barrier(world)
-    e2e = {"value": round(world * bytes_step * e2e_steps / e2e_s / 1e9, 2), "unit": "GB/s",
-           "h2d_bytes_per_step": len(STACK_N) * batch * K * 4, "d2h_bytes_per_step": sum(STACK_N) * batch * 4,
-           "ms_per_step": round(e2e_s / e2e_steps * 1e3, 4), "steps_timed": e2e_steps, "timing": "wall clock between device syncs",
-           "call": "fq_gemm_quant_nt (blocking), one call per product, from Python through ctypes"}
+    blocking = {"value": round(world * bytes_step * e2e_steps / e2e_s / 1e9, 2), "unit": "GB/s", "ms_per_step": round(e2e_s / e2e_steps * 1e3, 4),
+                "call": "fq_gemm_quant_nt (blocking), one call per product, from Python through ctypes"}
 
     # the same step through the asynchronous entry (the reference's gemmQuantNtAsync + Work.finish): the
     # four products of a step are submitted back to back and finished afterwards, so uploads, kernels and
@@ -357,9 +359,17 @@ def run_ours(args) -> dict:
     P.synchronize()
     async_s = max_over_ranks(time.perf_counter() - t0, world)
     barrier(world)
-    e2e["async_submit"] = {"value": round(world * bytes_step * e2e_steps / async_s / 1e9, 2), "unit": "GB/s",
-                           "ms_per_step": round(async_s / e2e_steps * 1e3, 4),
-                           "call": "fq_gemm_quant_nt_async x4, then fq_work_finish x4"}
+    queued = {"value": round(world * bytes_step * e2e_steps / async_s / 1e9, 2), "unit": "GB/s", "ms_per_step": round(async_s / e2e_steps * 1e3, 4),
+              "call": "fq_gemm_quant_nt_async x4, then fq_work_finish x4 (the reference's own first choice, exec/quant_matmul.zig:959-1051), "
+                      "from Python through ctypes"}
+    # the headline end-to-end figure is the faster of the two public forms; both are reported
+    best = queued if queued["value"] > blocking["value"] else blocking
+    e2e = {"value": best["value"], "unit": "GB/s", "h2d_bytes_per_step": len(STACK_N) * batch * K * 4,
+           "d2h_bytes_per_step": sum(STACK_N) * batch * 4, "ms_per_step": best["ms_per_step"], "steps_timed": e2e_steps,
+           "timing": "wall clock between device syncs; host activation and result storage registered once (fq_host_register)",
+           "call": best["call"], "blocking": blocking, "async_queue": queued}
+    for arr in host_x + host_y:
+        P.host_unregister(arr)
     if rank == 0:
         native = native_e2e(batch)
         if native:

@@ -37,6 +37,8 @@ SIGNATURES = {
     "fq_free_resident": (None, [c_void]),
     "fq_evict_resident": (c_int, [c_void]),
     "fq_resident_bytes": (c_size, []),
+    "fq_host_register": (c_int, [c_void, c_size]),
+    "fq_host_unregister": (c_int, [c_void]),
     "fq_set_vram_budget": (c_int, [c_size]),
     "fq_weights_upload": (c_int, [c_int, c_void, c_size, c_size, c_size, c_size, c_size, P(c_void)]),
     "fq_weights_from_device": (c_int, [c_int, c_void, c_size, c_size, c_size, c_size, c_size, P(c_void)]),

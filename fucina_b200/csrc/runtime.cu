@@ -336,6 +336,7 @@ void* dev_alloc(size_t n) { return g_dev_cache.alloc(n, g_ctx.stream); }
 void dev_free(void* p) { g_dev_cache.release(p, g_ctx.stream, false); }
 void* dev_alloc_on(size_t n, cudaStream_t st) { return g_dev_cache.alloc(n, st); }
 void dev_free_on(void* p, cudaStream_t st) { g_dev_cache.release(p, st, false); }
+void dev_free_idle(void* p) { g_dev_cache.release(p, nullptr, true); }  // the host already waited for the block's last use
 void* pin_alloc(size_t n) { return g_pin_cache.alloc(n, nullptr); }
 void pin_free(void* p) { g_pin_cache.release(p, nullptr, true); }
 
@@ -607,6 +608,28 @@ static bool host_is_pinned(const void* p) {
     return attr.type == cudaMemoryTypeHost;
 }
 
+// ---------------------------------------------------------------------------
+// host registration (backend/cuda.zig:1047-1082 `ensureHostRegistered`): the caller page-locks a storage range
+// once; activations are then copied by DMA straight from it and decode-sized results are written by the kernel
+// straight into it -- no bounce through a staging buffer.
+// ---------------------------------------------------------------------------
+struct HostRange {
+    uintptr_t base;
+    size_t len;
+    uint8_t* dev;  // the range as the device addresses it
+};
+static std::mutex g_host_lock;
+static std::vector<HostRange> g_host_ranges;
+
+// device view of [p, p + len) when it lies inside a registered range, else nullptr
+static void* registered_dev_ptr(const void* p, size_t len) {
+    const uintptr_t a = (uintptr_t)p;
+    std::lock_guard<std::mutex> g(g_host_lock);
+    for (const HostRange& r : g_host_ranges)
+        if (a >= r.base && a + len <= r.base + r.len) return r.dev + (a - r.base);
+    return nullptr;
+}
+
 struct Staged {
     void* dev = nullptr;
     void* pin = nullptr;
@@ -616,8 +639,10 @@ static int upload_f32(Ctx* ctx, const float* host, size_t bytes, Staged* s) {
     s->dev = dev_alloc(bytes);
     if (!s->dev) return fail(FQ_DECLINED_BUDGET, "device allocation of %zu bytes failed", bytes);
     const void* src = host;
-    // small rows are always staged: copying a few KB costs less than asking the driver what kind of memory it is
-    if (bytes <= 64 * 1024 || !host_is_pinned(host)) {
+    // registered storage is DMA-able as it is; other small rows are always staged (copying a few KB costs less
+    // than asking the driver what kind of memory it is)
+    if (registered_dev_ptr(host, bytes)) {
+    } else if (bytes <= 64 * 1024 || !host_is_pinned(host)) {
         s->pin = pin_alloc(bytes);
         if (!s->pin) return fail(FQ_DECLINED_BUDGET, "pinned allocation of %zu bytes failed", bytes);
         memcpy(s->pin, host, bytes);
@@ -695,8 +720,11 @@ static int gemm_host(int fmt, const void* rhs, size_t rhs_len, int cacheable, si
     // Decode-sized results are written by the kernel straight into page-locked host memory (device-visible
     // under unified addressing): one copy operation and its latency less per call.
     const bool direct_out = m <= 8 && out_bytes <= (size_t)1 << 20;
+    void* c_reg = direct_out ? registered_dev_ptr(c, out_bytes) : nullptr;  // registered result storage: the kernel writes it in place
     if (rc == FQ_OK) {
-        if (direct_out) {
+        if (c_reg) {
+            c_dev = c_reg;
+        } else if (direct_out) {
             c_pin = pin_alloc(out_bytes);
             c_dev = c_pin;
         } else {
@@ -716,7 +744,7 @@ static int gemm_host(int fmt, const void* rhs, size_t rhs_len, int cacheable, si
     if (rc == FQ_OK && direct_out) {
         cudaError_t e = cudaStreamSynchronize(ctx->stream);
         if (e != cudaSuccess) rc = cuda_fail(e, "result wait");
-        else memcpy(c, c_pin, out_bytes);
+        else if (!c_reg) memcpy(c, c_pin, out_bytes);
         g_trace.d2h_bytes += out_bytes;
     } else if (rc == FQ_OK) {
         rc = download_f32(ctx, c_dev, c, out_bytes);
@@ -724,9 +752,11 @@ static int gemm_host(int fmt, const void* rhs, size_t rhs_len, int cacheable, si
         cudaStreamSynchronize(ctx->stream);
     }
     if (rc == FQ_OK) rc = device_status(ctx);  // a bounded device-side wait that gave up invalidates the result
-    if (direct_out) pin_free(c_pin);
-    else dev_free(c_dev);
-    dev_free(in.dev);
+    // every path above ended in a host wait on the stream: the blocks go back idle (no event to record)
+    if (c_reg) {
+    } else if (direct_out) pin_free(c_pin);
+    else dev_free_idle(c_dev);
+    dev_free_idle(in.dev);
     pin_free(in.pin);
     if (temp) fq_weights_free(temp);
     // a decline after kernels were queued wrote nothing to `c`; device failures stay negative
@@ -749,6 +779,8 @@ struct fq_work {
     int state;  // 0 submitted, 1 host_ready, 2 discarded, -1 failed
     void* in_dev;  // staged activations: released once the product has run (finish / destroy)
     void* in_pin;
+    void* c_pin;   // decode-sized results are copied out at submit time: page-locked staging (or nullptr)
+    int early_copy;  // 1: the device-to-host copy was queued behind the product (into c_pin, or into registered c_host)
 };
 
 using namespace fq;
@@ -860,6 +892,46 @@ int fq_evict_resident(const void* host_ptr) {
 size_t fq_resident_bytes(void) {
     std::lock_guard<std::mutex> g(g_res_lock);
     return g_res_outstanding;
+}
+int fq_host_register(void* host_ptr, size_t len) {
+    if (!host_ptr || len == 0) return fail(FQ_DECLINED_ARGS, "null range");
+    Ctx* ctx = nullptr;
+    if (int rc = gate_and_ctx(&ctx)) return rc;
+    {
+        std::lock_guard<std::mutex> g(g_host_lock);
+        for (const HostRange& r : g_host_ranges)
+            if ((uintptr_t)host_ptr >= r.base && (uintptr_t)host_ptr + len <= r.base + r.len) return FQ_OK;  // already covered
+        if (g_host_ranges.size() >= 4096) return fail(FQ_DECLINED_BUDGET, "too many registered host ranges");
+    }
+    cudaError_t e = cudaHostRegister(host_ptr, len, cudaHostRegisterMapped | cudaHostRegisterPortable);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(FQ_DECLINED_ARGS, "cudaHostRegister of %zu bytes: %s", len, cudaGetErrorString(e));
+    }
+    void* dev = nullptr;
+    if (cudaHostGetDevicePointer(&dev, host_ptr, 0) != cudaSuccess || !dev) {
+        cudaGetLastError();
+        cudaHostUnregister(host_ptr);
+        return fail(FQ_DECLINED_ARGS, "registered memory has no device address");
+    }
+    std::lock_guard<std::mutex> g(g_host_lock);
+    g_host_ranges.push_back({(uintptr_t)host_ptr, len, (uint8_t*)dev});
+    return FQ_OK;
+}
+int fq_host_unregister(void* host_ptr) {
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> d(g_dispatch_lock);
+    cudaStreamSynchronize(ctx->stream);  // no copy or kernel may still address the range
+    std::lock_guard<std::mutex> g(g_host_lock);
+    for (size_t i = 0; i < g_host_ranges.size(); ++i)
+        if (g_host_ranges[i].base == (uintptr_t)host_ptr) {
+            g_host_ranges.erase(g_host_ranges.begin() + i);
+            cudaHostUnregister(host_ptr);
+            cudaGetLastError();
+            return FQ_OK;
+        }
+    return fail(FQ_DECLINED_ARGS, "address is not the start of a registered range");
 }
 int fq_set_vram_budget(size_t bytes) {
     Ctx* ctx = context();
@@ -1005,12 +1077,27 @@ int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheab
         w->done = nullptr;
         w->in_dev = nullptr;
         w->in_pin = nullptr;
+        w->c_pin = nullptr;
+        w->early_copy = 0;
         if (!w->c_dev) rc = fail(FQ_DECLINED_BUDGET, "device allocation failed");
         else if (cudaEventCreateWithFlags(&w->done, cudaEventDisableTiming) != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "event create");
     }
     if (stacked && rc == FQ_OK) rc = gemm_dev(ctx, view, 0, a_dev, (float*)w->c_dev, m, n, FQ_MODE_INT8, 0, ctx->stream, (int)n);
     for (size_t b = 0; b < batch && rc == FQ_OK && !stacked; ++b)
         rc = gemm_dev(ctx, view, (int)b, a_dev, (float*)w->c_dev + b * m * n, m, n, FQ_MODE_AUTO, 0, ctx->stream);
+    // Decode-sized results start their way to the host right behind the product, so a later finish only waits:
+    // into the caller's registered storage directly, else into page-locked staging copied out by finish.
+    if (rc == FQ_OK && c_host && w->bytes <= (size_t)1 << 20) {
+        void* dst = registered_dev_ptr(c_host, w->bytes) ? (void*)c_host : (w->c_pin = pin_alloc(w->bytes));
+        if (dst && cudaMemcpyAsync(dst, w->c_dev, w->bytes, cudaMemcpyDeviceToHost, ctx->stream) == cudaSuccess) {
+            w->early_copy = 1;
+            g_trace.d2h_bytes += w->bytes;
+        } else {
+            cudaGetLastError();
+            pin_free(w->c_pin);
+            w->c_pin = nullptr;
+        }
+    }
     if (rc == FQ_OK) {
         cudaError_t e = cudaEventRecord(w->done, ctx->stream);
         if (e != cudaSuccess) rc = cuda_fail(e, "event record");
@@ -1026,7 +1113,8 @@ int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheab
         pin_free(in.pin);
         if (w) {
             if (w->done) cudaEventDestroy(w->done);
-            dev_free(w->c_dev);
+            dev_free_idle(w->c_dev);
+            pin_free(w->c_pin);
             delete w;
         }
         return rc;
@@ -1050,10 +1138,14 @@ int fq_work_finish(fq_work* w, int copy_to_host) {
         w->state = -1;
         return cuda_fail(e, "work wait");
     }
-    dev_free(w->in_dev);
+    dev_free_idle(w->in_dev);  // the product that read them has finished (the event above)
     pin_free(w->in_pin);
     w->in_dev = w->in_pin = nullptr;
-    if (copy_to_host && w->c_host) {
+    if (copy_to_host && w->c_host && w->early_copy) {
+        // the copy was queued with the product and has landed: in place (registered storage) or in the staging block
+        if (w->c_pin) memcpy(w->c_host, w->c_pin, w->bytes);
+        w->state = 1;
+    } else if (copy_to_host && w->c_host) {
         // order the copy after the producer on the compute stream
         int rc = download_f32(ctx, w->c_dev, w->c_host, w->bytes);
         if (rc != FQ_OK) {
@@ -1076,12 +1168,13 @@ void fq_work_destroy(fq_work* w) {
     if (context()) {
         std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
         if (w->state == 0) cudaEventSynchronize(w->done);
-        // a consumer chained on this output may still be queued on the stream
-        cudaStreamSynchronize(g_ctx.stream);
         cudaEventDestroy(w->done);
+        // a consumer chained on this output may still be queued on the library stream: the block returns
+        // stream-ordered (an event, no host wait), so a later taker runs after that consumer
         dev_free(w->c_dev);
-        dev_free(w->in_dev);
+        dev_free_idle(w->in_dev);  // its reader finished before `done`
         pin_free(w->in_pin);
+        pin_free(w->c_pin);
     }
     g_slots_in_use--;
     delete w;

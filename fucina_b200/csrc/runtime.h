@@ -45,6 +45,7 @@ void* dev_alloc(size_t n);
 void dev_free(void* p);
 void* dev_alloc_on(size_t n, cudaStream_t st);
 void dev_free_on(void* p, cudaStream_t st);
+void dev_free_idle(void* p);  // for a block whose last use the host has already waited for
 void* pin_alloc(size_t n);
 void pin_free(void* p);
 

@@ -82,6 +82,15 @@ def synchronize() -> None:
     _check(load().fq_synchronize())
 
 
+def host_register(a: np.ndarray) -> None:
+    """`ensureHostRegistered` (src/backend/cuda.zig:1047-1082): page-lock a numpy array's storage for its lifetime."""
+    _check(load().fq_host_register(_vp(a), a.nbytes))
+
+
+def host_unregister(a: np.ndarray) -> None:
+    _check(load().fq_host_unregister(_vp(a)))
+
+
 def trace_counters() -> dict:
     arr = (C.c_uint64 * 8)()
     load().fq_trace_counters(arr)

@@ -98,6 +98,12 @@ FQ_API void* fq_alloc_resident(size_t len);
 FQ_API void fq_free_resident(const void* p);
 FQ_API int fq_evict_resident(const void* host_ptr);
 FQ_API size_t fq_resident_bytes(void);
+/* Page-lock a range of the caller's tensor storage once, for its lifetime (backend/cuda.zig:1047-1082
+ * `ensureHostRegistered`): activations inside it are copied by DMA without a staging copy, and decode-sized
+ * results inside it are written by the kernel in place. fq_host_unregister takes the range's start address and
+ * waits for the library stream first. Ranges already covered are accepted again at no cost. */
+FQ_API int fq_host_register(void* host_ptr, size_t len);
+FQ_API int fq_host_unregister(void* host_ptr);
 FQ_API int fq_set_vram_budget(size_t bytes); /* FUCINA_GPU_VRAM_BUDGET twin; test seam of backend/cuda.zig:3639 */
 
 /* ---- gpu_formats: explicit device-resident weights ----

@@ -177,3 +177,36 @@ def test_shared_input_batch_of_decode_shapes_is_one_stacked_launch(P, fmt_name, 
     from fucina_b200._lib import load
 
     load().fq_evict_resident(blocks.ctypes.data)
+
+
+def test_registered_host_storage_is_used_in_place(P):
+    # ensureHostRegistered (src/backend/cuda.zig:1047-1082): activations and decode-sized results in registered
+    # storage skip the staging copies; results are identical, and the range can be released afterwards
+    n, k = 4096, 4096
+    blocks = make_weights("q4_k", n, k, seed=55)
+    pool = np.zeros((1 << 20,), np.float32)  # one registered allocation holding both the input and the result
+    P.host_register(pool)
+    P.host_register(pool)  # a covered range is accepted again
+    a = pool[1000:1000 + k].reshape(1, k)
+    a[:] = acts(1, k, 56)
+    c = pool[300000:300000 + n].reshape(1, n)
+    c[:] = np.nan
+    want = oracle.matmul_fast(oracle.Q4_K, blocks, a)
+    before = P.trace_counters()
+    got = P.gemm_quant_nt(oracle.Q4_K, blocks, a, n, cacheable=True, out=c)
+    assert got is c
+    assert_close(c, want, TOL_INT8, "blocking call on registered storage")
+    wk = P.gemm_quant_nt_async(oracle.Q4_K, blocks, a, n, 1, k, out=c)
+    c[:] = np.nan
+    wk.finish(copy_to_host=True)
+    assert_close(c, want, TOL_INT8, "async call on registered storage")
+    wk.destroy()
+    # unregistered storage gives the same bits
+    plain = P.gemm_quant_nt(oracle.Q4_K, blocks, np.array(a), n, cacheable=True)
+    assert np.array_equal(plain.view(np.uint32), c.view(np.uint32))
+    P.host_unregister(pool)
+    with pytest.raises(P.Declined):
+        P.host_unregister(pool)
+    from fucina_b200._lib import load
+
+    load().fq_evict_resident(blocks.ctypes.data)
