@@ -768,6 +768,24 @@ static int gemm_host(int fmt, const void* rhs, size_t rhs_len, int cacheable, si
 // ---------------------------------------------------------------------------
 static const int kAsyncSlots = 8;
 static std::atomic<int> g_slots_in_use{0};
+// completion events are recycled: creating and destroying one per submit costs microseconds of driver time
+static std::vector<cudaEvent_t> g_token_events;
+static cudaEvent_t token_event_get() {
+    if (!g_token_events.empty()) {
+        cudaEvent_t e = g_token_events.back();
+        g_token_events.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return e;
+}
+static void token_event_put(cudaEvent_t e) {
+    if (e) g_token_events.push_back(e);
+}
 
 }  // namespace fq
 
@@ -826,6 +844,7 @@ int fq_synchronize(void) {
     Ctx* ctx = context();
     if (!ctx) return FQ_DECLINED_NO_GPU;
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->transfer);  // result copies of asynchronous submits
     if (e != cudaSuccess) return cuda_fail(e, "synchronize");
     return device_status(ctx);
 }
@@ -923,6 +942,7 @@ int fq_host_unregister(void* host_ptr) {
     if (!ctx) return FQ_DECLINED_NO_GPU;
     std::lock_guard<std::recursive_mutex> d(g_dispatch_lock);
     cudaStreamSynchronize(ctx->stream);  // no copy or kernel may still address the range
+    cudaStreamSynchronize(ctx->transfer);
     std::lock_guard<std::mutex> g(g_host_lock);
     for (size_t i = 0; i < g_host_ranges.size(); ++i)
         if (g_host_ranges[i].base == (uintptr_t)host_ptr) {
@@ -1080,27 +1100,34 @@ int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheab
         w->c_pin = nullptr;
         w->early_copy = 0;
         if (!w->c_dev) rc = fail(FQ_DECLINED_BUDGET, "device allocation failed");
-        else if (cudaEventCreateWithFlags(&w->done, cudaEventDisableTiming) != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "event create");
+        else if (!(w->done = token_event_get())) rc = fail(FQ_ERR_CUDA, "event create failed");
     }
     if (stacked && rc == FQ_OK) rc = gemm_dev(ctx, view, 0, a_dev, (float*)w->c_dev, m, n, FQ_MODE_INT8, 0, ctx->stream, (int)n);
     for (size_t b = 0; b < batch && rc == FQ_OK && !stacked; ++b)
         rc = gemm_dev(ctx, view, (int)b, a_dev, (float*)w->c_dev + b * m * n, m, n, FQ_MODE_AUTO, 0, ctx->stream);
     // Decode-sized results start their way to the host right behind the product, so a later finish only waits:
     // into the caller's registered storage directly, else into page-locked staging copied out by finish.
-    if (rc == FQ_OK && c_host && w->bytes <= (size_t)1 << 20) {
-        void* dst = registered_dev_ptr(c_host, w->bytes) ? (void*)c_host : (w->c_pin = pin_alloc(w->bytes));
-        if (dst && cudaMemcpyAsync(dst, w->c_dev, w->bytes, cudaMemcpyDeviceToHost, ctx->stream) == cudaSuccess) {
-            w->early_copy = 1;
-            g_trace.d2h_bytes += w->bytes;
-        } else {
-            cudaGetLastError();
-            pin_free(w->c_pin);
-            w->c_pin = nullptr;
-        }
-    }
+    // The copy runs on the transfer stream behind an event of the product, so the next product queued on the
+    // compute stream does not wait for it; `done` then marks the end of the copy.
     if (rc == FQ_OK) {
         cudaError_t e = cudaEventRecord(w->done, ctx->stream);
         if (e != cudaSuccess) rc = cuda_fail(e, "event record");
+    }
+    if (rc == FQ_OK && c_host && w->bytes <= (size_t)1 << 20) {
+        void* dst = registered_dev_ptr(c_host, w->bytes) ? (void*)c_host : (w->c_pin = pin_alloc(w->bytes));
+        if (dst && cudaStreamWaitEvent(ctx->transfer, w->done, 0) == cudaSuccess &&
+            cudaMemcpyAsync(dst, w->c_dev, w->bytes, cudaMemcpyDeviceToHost, ctx->transfer) == cudaSuccess &&
+            cudaEventRecord(w->done, ctx->transfer) == cudaSuccess) {
+            w->early_copy = 1;
+            g_trace.d2h_bytes += w->bytes;
+        } else {
+            // `done` may have been left unrecorded on the transfer stream: mark the product's end again
+            cudaGetLastError();
+            cudaStreamSynchronize(ctx->transfer);
+            cudaEventRecord(w->done, ctx->stream);
+            pin_free(w->c_pin);
+            w->c_pin = nullptr;
+        }
     }
     // the staged activations stay with the token until it is finished: no host wait inside a submit
     if (rc == FQ_OK) {
@@ -1112,7 +1139,7 @@ int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheab
         dev_free(in.dev);
         pin_free(in.pin);
         if (w) {
-            if (w->done) cudaEventDestroy(w->done);
+            token_event_put(w->done);
             dev_free_idle(w->c_dev);
             pin_free(w->c_pin);
             delete w;
@@ -1168,7 +1195,7 @@ void fq_work_destroy(fq_work* w) {
     if (context()) {
         std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
         if (w->state == 0) cudaEventSynchronize(w->done);
-        cudaEventDestroy(w->done);
+        token_event_put(w->done);
         // a consumer chained on this output may still be queued on the library stream: the block returns
         // stream-ordered (an event, no host wait), so a later taker runs after that consumer
         dev_free(w->c_dev);

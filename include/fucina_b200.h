@@ -145,7 +145,9 @@ FQ_API int fq_gemm_quant_nt_shared_a_batch(int fmt, const void* rhs, size_t rhs_
  * accelerator.Work's vtable {finish, device_ptr, destroy}
  * (accelerator.zig:22-133, backend/cuda.zig:1145-1218). `a_dep` chains a
  * pending producer's device output without a host round trip
- * (backend/cuda.zig:1224-1230 `pendingDeviceInput`); pass NULL to read `a`. */
+ * (backend/cuda.zig:1224-1230 `pendingDeviceInput`); pass NULL to read `a`.
+ * c_host belongs to the token from the submit until fq_work_finish returns: decode-sized results are copied
+ * out behind the product (on a transfer stream of their own), so they may land there before finish is called. */
 typedef struct fq_work fq_work;
 FQ_API int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02,
                            const float* a, fq_work* a_dep, float* c_host, size_t batch, size_t m, size_t n,

@@ -196,8 +196,8 @@ def test_registered_host_storage_is_used_in_place(P):
     got = P.gemm_quant_nt(oracle.Q4_K, blocks, a, n, cacheable=True, out=c)
     assert got is c
     assert_close(c, want, TOL_INT8, "blocking call on registered storage")
+    c[:] = np.nan  # before the submit: the result may land in registered storage any time between submit and finish
     wk = P.gemm_quant_nt_async(oracle.Q4_K, blocks, a, n, 1, k, out=c)
-    c[:] = np.nan
     wk.finish(copy_to_host=True)
     assert_close(c, want, TOL_INT8, "async call on registered storage")
     wk.destroy()
