@@ -42,6 +42,7 @@ SIGNATURES = {
     "fq_set_vram_budget": (c_int, [c_size]),
     "fq_weights_upload": (c_int, [c_int, c_void, c_size, c_size, c_size, c_size, c_size, P(c_void)]),
     "fq_weights_from_device": (c_int, [c_int, c_void, c_size, c_size, c_size, c_size, c_size, P(c_void)]),
+    "fq_weights_view": (c_int, [c_void, c_size, c_size, P(c_void)]),
     "fq_weights_free": (None, [c_void]),
     "fq_weights_device_bytes": (c_size, [c_void]),
     "fq_weights_download_gguf": (c_int, [c_void, c_void, c_size]),

@@ -75,6 +75,32 @@ __host__ __device__ inline size_t dev_row_stride(int fmt, size_t k) {
 // ---- small device helpers ---------------------------------------------------
 __device__ __forceinline__ float h2f(uint16_t bits) { return __half2float(__ushort_as_half(bits)); }
 
+// Gated pair of an FFN (reference backend/ops.zig:150-190): g = source(up) * activation(gate), every product
+// rounded on its own as the scalar code does. `op` is one of FQ_GATED_*.
+__device__ __forceinline__ float fq_sigmoid(float v) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v))); }
+__device__ __forceinline__ float gated_activation(int op, float g) {
+    switch (op) {
+        case FQ_GATED_GEGLU: {
+            // 0.5 * v * (1 + tanh(sqrt(2/pi) * (v + 0.044715 v^3))), left to right
+            const float arg = __fmul_rn(0.7978845608028654f, __fadd_rn(g, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, g), g), g)));
+            return __fmul_rn(__fmul_rn(0.5f, g), __fadd_rn(1.0f, tanhf(arg)));
+        }
+        case FQ_GATED_SWIGLU_CLAMP10: {
+            const float c = fminf(g, 10.0f);
+            return __fmul_rn(c, fq_sigmoid(c));
+        }
+        case FQ_GATED_GLU: return fq_sigmoid(g);
+        case FQ_GATED_SITU: return __fmul_rn(__fmul_rn(4.0f, tanhf(__fmul_rn(g, 0.25f))), fq_sigmoid(g));
+        default: return __fmul_rn(g, fq_sigmoid(g));
+    }
+}
+__device__ __forceinline__ float gated_source(int op, float u) {
+    if (op == FQ_GATED_SWIGLU_CLAMP10) return fminf(fmaxf(u, -10.0f), 10.0f);
+    if (op == FQ_GATED_SITU) return __fmul_rn(25.0f, tanhf(__fmul_rn(u, 0.04f)));
+    return u;
+}
+__device__ __forceinline__ float gated_pair(int op, float gate, float up) { return __fmul_rn(gated_source(op, up), gated_activation(op, gate)); }
+
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
     // 128-bit read-only load that does not allocate in L1: weights are used once.
     uint4 v;

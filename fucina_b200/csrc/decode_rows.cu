@@ -909,6 +909,7 @@ __global__ void __launch_bounds__(kExpertWarps * 32, 1)
     constexpr int UB = FMT == FQ_Q4_K ? 144 : 176;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int k = A.w.k, n = A.w.n;
+    const int mat_rows = A.w.n_mats > 1 ? (int)(A.w.mat_stride / A.w.row_stride) : n;
     const NatSizes NS = nat_sizes(true, k);
     const int units = k >> 8;
     const int tpi = A.tiles_per_item, ksplit = kExpertWarps / tpi;
@@ -952,7 +953,8 @@ __global__ void __launch_bounds__(kExpertWarps * 32, 1)
                     const int j = next_it % spi, unit = kpart + ksplit * (j / NM);
                     const int stage = issued % A.stages;
                     const uint32_t bar = bar0 + stage * 8;
-                    const int row = A.table[d].mat * n + tile * 32;  // row in the stacked [experts * n] matrix
+                    // row in the stacked matrix: experts are mat_rows rows apart (n for a dense stack, more for a row view of a wider one)
+                    const int row = A.table[d].mat * mat_rows + tile * 32;
                     mbar_arrive_expect_tx(bar, (uint32_t)(32 * UB));
                     const CUtensorMap* tm = (GATED && (j % NM)) ? &tmap2 : &tmap;
                     asm volatile(
@@ -1058,11 +1060,7 @@ __global__ void __launch_bounds__(kExpertWarps * 32, 1)
                     const int b = 2 * (lane & 3) + (i & 1);
                     if (row >= n || b >= G.m) continue;
                     float v = acc[0][i < MB ? i : 0];
-                    if (GATED) {
-                        const float gate = v, up = acc[NM - 1][i < MB ? i : 0];
-                        const float sig = 1.0f / (1.0f + expf(-gate));
-                        v = up * (gate * sig);
-                    }
+                    if (GATED) v = gated_pair(A.gated_op, v, acc[NM - 1][i < MB ? i : 0]);
                     A.out[(size_t)(G.row0 + b) * n + row] = v;
                 }
             }
@@ -1074,11 +1072,7 @@ __global__ void __launch_bounds__(kExpertWarps * 32, 1)
             for (int b = 0; b < MB; ++b) {
                 if (b >= G.m) continue;
                 float v = acc[0][b];
-                if (GATED) {
-                    const float gate = acc[0][b], up = acc[NM - 1][b];
-                    const float sig = 1.0f / (1.0f + expf(-gate));
-                    v = up * (gate * sig);
-                }
+                if (GATED) v = gated_pair(A.gated_op, acc[0][b], acc[NM - 1][b]);
                 A.out[(size_t)(G.row0 + b) * n + row] = v;
             }
         }
@@ -1124,7 +1118,8 @@ cudaError_t launch_expert_mb(const ExpertArgs& a, int mb, const CUtensorMap& t1,
 bool make_stack_tmap(const DevWeights& w, int unit_bytes, CUtensorMap* out) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)(w.k / 256) * unit_bytes, (cuuint64_t)w.n * (cuuint64_t)w.n_mats};
+    const cuuint64_t mat_rows = w.n_mats > 1 ? w.mat_stride / w.row_stride : (cuuint64_t)w.n;
+    const cuuint64_t dims[2] = {(cuuint64_t)(w.k / 256) * unit_bytes, mat_rows * (cuuint64_t)(w.n_mats - 1) + (cuuint64_t)w.n};
     const cuuint64_t strides[1] = {(cuuint64_t)w.row_stride};
     const cuuint32_t box[2] = {(cuuint32_t)unit_bytes, 32};
     const cuuint32_t estr[2] = {1, 1};
@@ -1233,8 +1228,11 @@ int expert_rows_max_group() { return 8; }
 bool expert_rows_eligible(const DevWeights& w, const DevWeights* w2, int group_rows) {
     if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K) return false;
     if (w.tile_rows || w.k % 256 != 0 || w.k < 256 || group_rows < 1 || group_rows > 8) return false;
-    if (w.n_mats > 1 && w.mat_stride != (size_t)w.n * w.row_stride) return false;
-    if (w2 && (w2->fmt != w.fmt || w2->k != w.k || w2->n != w.n || w2->tile_rows || w2->row_stride != w.row_stride)) return false;
+    if (w.n_mats > 1 && (w.mat_stride % w.row_stride != 0 || w.mat_stride < (size_t)w.n * w.row_stride)) return false;
+    if (((uintptr_t)w.base & 15) || (w.row_stride & 15)) return false;  // tensor-map base and stride rules
+    if (w2 && (w2->fmt != w.fmt || w2->k != w.k || w2->n != w.n || w2->tile_rows || w2->row_stride != w.row_stride || w2->mat_stride != w.mat_stride ||
+               ((uintptr_t)w2->base & 15)))
+        return false;
     static const bool off = getenv("FUCINA_B200_NO_EXPERT_ROWS") != nullptr;
     if (off || !encode_tiled_fn()) return false;
     return expert_smem_bytes(w.fmt, w.k, pad_rows((size_t)group_rows), w2 ? 2 : 1, 2) <= kSmemLimit;
@@ -1242,7 +1240,7 @@ bool expert_rows_eligible(const DevWeights& w, const DevWeights* w2, int group_r
 
 cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const float* src, const int* src_index, int top_k, float* out,
                                const GroupDesc* table, const int* n_desc, int max_desc, int group_rows, int sm_count, int* status,
-                               cudaStream_t st) {
+                               cudaStream_t st, int gated_op) {
     const int mb = pad_rows((size_t)group_rows), nm = w2 ? 2 : 1;
     const int ub = w.fmt == FQ_Q4_K ? 144 : 176;
     int stages = kMaxStages;
@@ -1265,7 +1263,7 @@ cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const 
         grid = (int)items;
         stages = 2;
     }
-    ExpertArgs a{w, w2 ? *w2 : DevWeights{}, src, src_index, top_k, out, table, n_desc, max_desc, tpi, stages, status};
+    ExpertArgs a{w, w2 ? *w2 : DevWeights{}, src, src_index, top_k, out, table, n_desc, max_desc, tpi, stages, status, gated_op};
     const size_t smem = expert_smem_bytes(w.fmt, w.k, mb, nm, stages);
     if (w.fmt == FQ_Q4_K)
         return w2 ? launch_expert_mb<FQ_Q4_K, true>(a, mb, t1, t2, grid, smem, st) : launch_expert_mb<FQ_Q4_K, false>(a, mb, t1, t2, grid, smem, st);

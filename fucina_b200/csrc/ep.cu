@@ -325,6 +325,7 @@ struct EpCall {
     __nv_bfloat16* g_panel;
     int max_gu, max_dn;
     int plan_stages = 3;  // see ep_plan_kernel
+    int gated_op = 0;
 };
 
 int ep_prepare(Ctx* ctx, const EpView& v, int epoch, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x,
@@ -392,7 +393,7 @@ int ep_phase(Ctx* ctx, EpCall& c, int phase, cudaStream_t st) {
             peer.n_wait = a.v.world;
             peer.wait_value = a.epoch;
             rc = gemm_tensor_grouped_gated_dev(ctx, *c.gate, *c.up, me + a.mine.off_x, (size_t)a.mine.rows_cap, c.g_panel, (size_t)c.gate->n,
-                                               a.t_gu, &a.plan->n_gu, c.max_gu, st, &peer);
+                                               a.t_gu, &a.plan->n_gu, c.max_gu, st, &peer, c.gated_op);
             break;
         }
         case 3: {
@@ -425,9 +426,9 @@ std::vector<std::vector<cudaEvent_t>> g_ep_events;  // FUCINA_B200_EP_TRACE: one
 
 int check_ep_weights(const fq_weights* gate, const fq_weights* up, const fq_weights* down, size_t seq, size_t top_k, int gated_op) {
     if (!gate || !up || !down) return fail(FQ_DECLINED_ARGS, "null weights");
-    if (gated_op != 0) return fail(FQ_DECLINED_ARGS, "only swiglu (gated_op 0) is served");
+    if (gated_op < FQ_GATED_SWIGLU || gated_op > FQ_GATED_SITU) return fail(FQ_DECLINED_ARGS, "gated_op %d is not one of FQ_GATED_*", gated_op);
     const DevWeights &g = gate->dw, &u = up->dw, &d = down->dw;
-    if (g.fmt != u.fmt || g.fmt != d.fmt) return fail(FQ_DECLINED_ARGS, "expert tensors must share one format");
+    if (g.fmt != u.fmt) return fail(FQ_DECLINED_ARGS, "gate and up must share one format");
     if (g.n != u.n || g.k != u.k || g.n_mats != u.n_mats || d.n_mats != g.n_mats || d.n != g.k || d.k != g.n)
         return fail(FQ_DECLINED_ARGS, "expert tensor shapes are inconsistent");
     if (seq == 0 || top_k == 0 || seq * top_k > (size_t)1 << 22) return fail(FQ_DECLINED_ARGS, "bad seq/top_k");
@@ -435,7 +436,8 @@ int check_ep_weights(const fq_weights* gate, const fq_weights* up, const fq_weig
 }
 
 bool fused_form_serves(const DevWeights& g, const DevWeights& d) {
-    return (g.fmt == FQ_Q4_K || g.fmt == FQ_Q5_K || g.fmt == FQ_Q8_0) && tensor_path_serves(g) && tensor_path_serves(d) && g.k % 8 == 0;
+    return (g.fmt == FQ_Q4_K || g.fmt == FQ_Q5_K || g.fmt == FQ_Q8_0) && (d.fmt == FQ_Q4_K || d.fmt == FQ_Q5_K || d.fmt == FQ_Q8_0) &&
+           tensor_path_serves(g) && tensor_path_serves(d) && g.k % 8 == 0;
 }
 
 }  // namespace
@@ -496,6 +498,7 @@ int fq_moe_layer_ep(const fq_weights* gate, const fq_weights* up, const fq_weigh
             --t->epoch;
             return rc;
         }
+        c.gated_op = gated_op;
         int rc = FQ_OK;
         // FUCINA_B200_EP_TRACE=1: device time of each phase (CUDA events on the layer's stream), summed per phase and
         // printed by fq_tp_shutdown -- the per-kind timing of backend/cuda.zig:231-257 for this layer
@@ -546,7 +549,7 @@ int fq_moe_layer_ep(const fq_weights* gate, const fq_weights* up, const fq_weigh
         if (e != cudaSuccess) rc = cuda_fail(e, "routing repack");
     }
     if (rc == FQ_OK)
-        rc = moe_layer_shard_dev(ctx, gw, uw, dw, x_all, (int)rows, (int)top_k, sel_all, w_all, t->rank * gw.n_mats, partial, st);
+        rc = moe_layer_shard_dev(ctx, gw, uw, dw, x_all, (int)rows, (int)top_k, sel_all, w_all, t->rank * gw.n_mats, partial, st, gated_op);
     if (rc == FQ_OK) rc = tp_reduce_scatter_f32(partial, out_dev, seq * hidden, st);
     dev_free_on(sel_all, st);
     dev_free_on(s, st);

@@ -118,6 +118,7 @@ struct TcArgs {
     DevWeights w2;
     __nv_bfloat16* g_out;
     TcPeer peer;  // multi-GPU hooks (all null / zero on one GPU)
+    int gated_op; // FQ_GATED_* of the gated form
 };
 
 // One output tile: weight rows [rt*128, +128) of matrix `mat` times activation rows [tok0, tok0+ntok).
@@ -529,6 +530,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
     constexpr bool kStaged = Staged<FMT>::on;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = A.w.n, k = A.w.k, m = A.m;
+    const int mat_rows = A.w.n_mats > 1 ? (int)(A.w.mat_stride / A.w.row_stride) : n;  // rows between stacked matrices (n when dense)
     const int kslabs = k / BK, units = k >> 8;
     const int row_tiles = (n + BM - 1) / BM, tok_tiles = (m + TN - 1) / TN;
     const int n_tiles = A.table ? *A.n_tiles_dev : row_tiles * tok_tiles;
@@ -770,7 +772,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                         mbar_arrive_expect_tx(bar, (uint32_t)(BM * ub));
                         asm volatile(
                             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-                            "l"(tmw), "r"(u * ub), "r"(T.mat * n + T.rt * BM), "r"(bar)
+                            "l"(tmw), "r"(u * ub), "r"(T.mat * mat_rows + T.rt * BM), "r"(bar)
                             : "memory");
                     }
                 }
@@ -807,16 +809,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                         if (ps == 0) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
-                                const float gv = __uint_as_float(acc[j]);
-                                const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gv)));
-                                mine[j * BM] = __fmul_rn(gv, sig);
+                                mine[j * BM] = gated_activation(A.gated_op, __uint_as_float(acc[j]));
                             }
                         } else if (out_row < n) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
                                 if (c0 + j < T.ntok)
                                     A.g_out[(size_t)(T.tok0 + c0 + j) * A.ldc + out_row] =
-                                        __float2bfloat16_rn(__fmul_rn(__uint_as_float(acc[j]), mine[j * BM]));
+                                        __float2bfloat16_rn(__fmul_rn(gated_source(A.gated_op, __uint_as_float(acc[j])), mine[j * BM]));
                             }
                         }
                     } else if (out_row < n) {
@@ -937,8 +937,11 @@ static int encode_packed_rows(EncodeTiledFn enc, const DevWeights& w, CUtensorMa
     memset(out, 0, sizeof *out);
     if (!((w.fmt == FQ_Q4_K || w.fmt == FQ_Q5_K) && !w.tile_rows)) return FQ_OK;
     const int ub = w.fmt == FQ_Q4_K ? 144 : 176;
-    if (w.mat_stride != (size_t)w.n * w.row_stride && w.n_mats > 1) return fail(FQ_DECLINED_ARGS, "stacked matrices are not contiguous");
-    const cuuint64_t wdims[2] = {(cuuint64_t)(w.k / 256) * ub, (cuuint64_t)w.n * (cuuint64_t)w.n_mats};
+    if (w.n_mats > 1 && (w.mat_stride % w.row_stride != 0 || w.mat_stride < (size_t)w.n * w.row_stride))
+        return fail(FQ_DECLINED_ARGS, "stacked matrices are not a whole number of rows apart");
+    if (((uintptr_t)w.base & 15) || (w.row_stride & 15)) return fail(FQ_DECLINED_ARGS, "packed rows are not 16-byte aligned");
+    const cuuint64_t mat_rows = w.n_mats > 1 ? w.mat_stride / w.row_stride : (cuuint64_t)w.n;
+    const cuuint64_t wdims[2] = {(cuuint64_t)(w.k / 256) * ub, mat_rows * (cuuint64_t)(w.n_mats - 1) + (cuuint64_t)w.n};
     const cuuint64_t wstrides[1] = {(cuuint64_t)w.row_stride};
     const cuuint32_t wbox[2] = {(cuuint32_t)ub, BM};
     const cuuint32_t estr[2] = {1, 1};
@@ -953,7 +956,7 @@ static int encode_packed_rows(EncodeTiledFn enc, const DevWeights& w, CUtensorMa
 // bf16(up * silu(gate)) in g_out instead of f32 products in c_dev.
 static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfloat16* abf, size_t rows, float* c_dev, size_t ldc,
                           const TcTile* table, const int* n_tiles_dev, int max_tiles, int tile_tokens, cudaStream_t st,
-                          const DevWeights* up = nullptr, __nv_bfloat16* g_out = nullptr, const TcPeer* peer = nullptr) {
+                          const DevWeights* up = nullptr, __nv_bfloat16* g_out = nullptr, const TcPeer* peer = nullptr, int gated_op = 0) {
     const int BN = tile_tokens;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return fail(FQ_DECLINED_ARGS, "cuTensorMapEncodeTiled unavailable");
@@ -971,7 +974,7 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
     if (int rc = encode_packed_rows(enc, w, &tmap_w)) return rc;
     if (int rc = encode_packed_rows(enc, up ? *up : w, &tmap_w2)) return rc;
     static const int diag = getenv("FUCINA_B200_TC_DIAG") ? atoi(getenv("FUCINA_B200_TC_DIAG")) : 0;
-    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev, diag, up ? *up : w, g_out, peer ? *peer : TcPeer{}};
+    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev, diag, up ? *up : w, g_out, peer ? *peer : TcPeer{}, gated_op};
     const int tiles = table ? max_tiles : ((w.n + BM - 1) / BM) * (int)((rows + BN - 1) / BN);
     const int grid = tiles < ctx->sm_count ? (tiles > 0 ? tiles : 1) : ctx->sm_count;
     cudaError_t e;
@@ -1009,14 +1012,14 @@ int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, s
 // g[row, j] = bf16(up[row, j] * silu(gate[row, j])) over the tile list (128-token tiles).
 int gemm_tensor_grouped_gated_dev(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const void* a_bf16, size_t rows, void* g_bf16,
                                   size_t ldc, const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st,
-                                  const TcPeer* peer) {
+                                  const TcPeer* peer, int gated_op) {
     if (!tensor_path_serves(gate) || (gate.fmt != FQ_Q4_K && gate.fmt != FQ_Q5_K && gate.fmt != FQ_Q8_0))
         return fail(FQ_DECLINED_ARGS, "the gated tensor-core form serves Q4_K, Q5_K and Q8_0 with k %% 256 == 0");
     if (up.fmt != gate.fmt || up.n != gate.n || up.k != gate.k || up.n_mats != gate.n_mats || up.tile_rows != gate.tile_rows ||
         up.row_stride != gate.row_stride || up.mat_stride != gate.mat_stride)
         return fail(FQ_DECLINED_ARGS, "gate and up stacks differ in shape or layout");
     return launch_tc_rows(ctx, gate, 0, (const __nv_bfloat16*)a_bf16, rows, nullptr, ldc, table, n_tiles_dev, max_tiles, 128, st, &up,
-                          (__nv_bfloat16*)g_bf16, peer);
+                          (__nv_bfloat16*)g_bf16, peer, gated_op);
 }
 
 __global__ void add_f32_kernel(float* __restrict__ c, const float* __restrict__ t, size_t n) {

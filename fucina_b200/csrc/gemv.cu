@@ -342,9 +342,7 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs A) {
 #pragma unroll
                 for (int b = 0; b < MB; ++b) {
                     if (b >= m) continue;
-                    const float gate = acc[0][b], up = acc[1][b];
-                    const float sig = 1.0f / (1.0f + expf(-gate));
-                    cbase[(size_t)b * A.ldc + row0] = up * (gate * sig);
+                    cbase[(size_t)b * A.ldc + row0] = gated_pair(A.gated_op, acc[0][b], acc[1][b]);
                 }
             } else {
 #pragma unroll

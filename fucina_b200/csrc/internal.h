@@ -47,6 +47,7 @@ struct GemvArgs {
     const GroupDesc* table;
     const int* n_desc;
     int max_desc;
+    int gated_op = 0;  // FQ_GATED_* of the gated form
 };
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st);
 size_t gemv_max_rows();  // largest m one launch (or one table entry) handles
@@ -94,6 +95,7 @@ struct ExpertArgs {
     int tiles_per_item;     // 1, 2, 4 or 8 tiles of 32 rows per work item; 8 / tiles_per_item warps split K
     int stages;
     int* status;
+    int gated_op;           // FQ_GATED_* of the gate/up pair (w2 set)
 };
 // one warp runs a bounded wait on a barrier nothing completes and reports through the status word
 cudaError_t launch_bounded_wait_probe(int* status, unsigned limit, cudaStream_t st);
@@ -101,7 +103,7 @@ int expert_rows_max_group();
 bool expert_rows_eligible(const DevWeights& w, const DevWeights* w2, int group_rows);
 cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const float* src, const int* src_index, int top_k, float* out,
                                const GroupDesc* table, const int* n_desc, int max_desc, int group_rows, int sm_count, int* status,
-                               cudaStream_t st);
+                               cudaStream_t st, int gated_op = 0);
 // true when the shape is one the kernel serves (format, K, m, shared memory)
 bool decode_rows_eligible(const DevWeights& w, size_t m);
 // bytes of natural-record scratch the non-fused form needs (0 for the fused form)

@@ -296,22 +296,25 @@ __global__ void gather_bf16_kernel(const float* __restrict__ x, const int* __res
     }
 }
 
-// g = up * (gate * 1/(1+exp(-gate))) in f32 (backend/ops.zig:150-190), rounded once to bf16
-__global__ void swiglu_bf16_kernel(const float* __restrict__ gate, const float* __restrict__ up, const int* __restrict__ n_rows, int width,
-                                   __nv_bfloat16* __restrict__ out) {
+// g = source(up) * activation(gate) in f32 (backend/ops.zig:150-190), rounded once to bf16
+__global__ void gated_bf16_kernel(const float* __restrict__ gate, const float* __restrict__ up, const int* __restrict__ n_rows, int width,
+                                  int gated_op, __nv_bfloat16* __restrict__ out) {
     const size_t n = (size_t)*n_rows * width;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const float gv = gate[i];
-        const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gv)));
-        out[i] = __float2bfloat16_rn(__fmul_rn(up[i], __fmul_rn(gv, sig)));
-    }
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = __float2bfloat16_rn(gated_pair(gated_op, gate[i], up[i]));
+}
+// the same pair in f32 over a fixed number of elements (multi-plane ternary experts: the planes of gate and of up are
+// summed first, the activation follows)
+__global__ void gated_f32_kernel(const float* __restrict__ gate, const float* __restrict__ up, size_t n, int gated_op, float* __restrict__ out) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = gated_pair(gated_op, gate[i], up[i]);
 }
 
 int g_moe_tensor_mode = -1;  // -1 auto (>= 14 rows per expert on average: the measured crossover of the two arms), 0 never, 1 whenever the format allows
 
 int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
                           int seq, int top_k, const int* selected_dev, const float* weights_dev, Shard shard, float* out_dev,
-                          cudaStream_t st) {
+                          cudaStream_t st, int gated_op) {
     const int hidden = gate.k, out_pe = gate.n, n_expert = gate.n_mats;
     const int pairs = seq * top_k;
     const int rt_gu = (out_pe + 127) / 128, rt_dn = (hidden + 127) / 128;
@@ -347,13 +350,16 @@ int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up
         if ((e = cudaGetLastError()) != cudaSuccess) break;
         if (tile_tokens == 128) {
             // short runs: gate and up of a tile share one pass, the SwiGLU runs in its epilogue
-            if ((rc = gemm_tensor_grouped_gated_dev(ctx, gate, up, s + o_xb, pairs, s + o_gb, out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, st)) != FQ_OK) break;
+            if ((rc = gemm_tensor_grouped_gated_dev(ctx, gate, up, s + o_xb, pairs, s + o_gb, out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, st, nullptr,
+                                                    gated_op)) != FQ_OK)
+                break;
         } else {
             if ((rc = gemm_tensor_grouped_dev(ctx, gate, s + o_xb, pairs, (float*)(s + o_gate), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, tile_tokens, st)) != FQ_OK) break;
             if ((rc = gemm_tensor_grouped_dev(ctx, up, s + o_xb, pairs, (float*)(s + o_up), out_pe, (const TcTile*)(s + o_tgu), cnt + 1, max_gu, tile_tokens, st)) != FQ_OK) break;
             const size_t ng = (size_t)pairs * out_pe;
             blocks = (int)((ng + 255) / 256);
-            swiglu_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>((const float*)(s + o_gate), (const float*)(s + o_up), cnt + 3, out_pe, (__nv_bfloat16*)(s + o_gb));
+            gated_bf16_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>((const float*)(s + o_gate), (const float*)(s + o_up), cnt + 3, out_pe, gated_op,
+                                                                                      (__nv_bfloat16*)(s + o_gb));
             if ((e = cudaGetLastError()) != cudaSuccess) break;
         }
         if ((rc = gemm_tensor_grouped_dev(ctx, down, s + o_gb, pairs, (float*)(s + o_down), hidden, (const TcTile*)(s + o_tdn), cnt + 2, max_dn, tile_tokens, st)) != FQ_OK) break;
@@ -377,17 +383,19 @@ int max_desc_for(int pairs, int n_expert, int group_rows) {
 
 int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
                        int seq, int top_k, const int* selected_dev, const float* weights_dev, Shard shard, float* out_dev,
-                       cudaStream_t st, StageTaps taps = StageTaps{nullptr, nullptr}) {
-    const int hidden = gate.k, out_pe = gate.n, n_expert = gate.n_mats, fmt = gate.fmt;
+                       cudaStream_t st, int gated_op = 0, StageTaps taps = StageTaps{nullptr, nullptr}) {
+    // gate and up share a format; down may come in another (Gemma: Q4_K gate/up, Q8_0 down)
+    const int hidden = gate.k, out_pe = gate.n, n_expert = gate.n_mats, fmt = gate.fmt, fmt_dn = down.fmt;
     const int pairs = seq * top_k;
     // prefill-sized batches: bf16 tensor-core products (the reference's own GPU arm multiplies rounded
     // operands too); decode-sized batches keep the CPU kernels' int8 arithmetic
     // the grouped tensor-core form is exercised for the formats expert stacks come in (K-quants and Q8_0)
-    const bool tc_ok = (fmt == FQ_Q4_K || fmt == FQ_Q5_K || fmt == FQ_Q8_0) && tensor_path_serves(gate) && tensor_path_serves(down);
+    const bool tc_ok = (fmt == FQ_Q4_K || fmt == FQ_Q5_K || fmt == FQ_Q8_0) && tensor_path_serves(gate) && tensor_path_serves(down) &&
+                       (fmt_dn == FQ_Q4_K || fmt_dn == FQ_Q5_K || fmt_dn == FQ_Q8_0);
     const bool tapped = taps.g_pairs || taps.down_pairs;  // the taps read the integer arm's intermediates
     if (!tapped && tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 14 * n_expert)))
-        return moe_layer_tensor_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, shard, out_dev, st);
-    const ActSizes Sx = act_sizes(fmt, hidden), Sg = act_sizes(fmt, out_pe);
+        return moe_layer_tensor_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, shard, out_dev, st, gated_op);
+    const ActSizes Sx = act_sizes(fmt, hidden), Sg = act_sizes(fmt_dn, out_pe);
     // Row tile of the grouped kernel. A router sends a token to distinct experts, so an expert's run is
     // normally no longer than the batch; runs are split at this size either way, so repeated experts in
     // one token only cost an extra table entry.
@@ -397,7 +405,7 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     const bool streaming = expert_rows_eligible(gate, &up, stream_rows) && expert_rows_eligible(down, nullptr, stream_rows);
     // the lane-per-chunk kernel keeps a group's (padded) rows in shared memory: cut the group until both products fit
     int fit_rows = gemv_rows_that_fit(fmt, (size_t)hidden);
-    if (gemv_rows_that_fit(fmt, (size_t)out_pe) < fit_rows) fit_rows = gemv_rows_that_fit(fmt, (size_t)out_pe);
+    if (gemv_rows_that_fit(fmt_dn, (size_t)out_pe) < fit_rows) fit_rows = gemv_rows_that_fit(fmt_dn, (size_t)out_pe);
     if (!streaming && fit_rows == 0) return fail(FQ_DECLINED_ARGS, "expert rows of %d / %d elements are too long for the integer arm", hidden, out_pe);
     const int int8_rows = kGroupRows < fit_rows ? kGroupRows : fit_rows;
     const int group_rows = streaming ? stream_rows : (seq < int8_rows ? seq : int8_rows);
@@ -434,7 +442,7 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
         if ((e = cudaGetLastError()) != cudaSuccess) break;
         if (streaming) {
             if ((e = launch_expert_rows(gate, &up, x_dev, order, top_k, g, table, n_desc, max_desc, group_rows, ctx->sm_count, ctx->status_dev,
-                                        st)) != cudaSuccess)
+                                        st, gated_op)) != cudaSuccess)
                 break;
             if ((e = launch_expert_rows(down, nullptr, g, nullptr, 1, down_rows, table, n_desc, max_desc, group_rows, ctx->sm_count,
                                         ctx->status_dev, st)) != cudaSuccess)
@@ -448,9 +456,9 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
         }
         // gather each pair's token row and quantise it, in expert order
         if ((e = launch_quantize_acts_layout(x_dev, order, top_k, pairs, hidden, fmt, qx, st)) != cudaSuccess) break;
-        GemvArgs ga{gate, up, 0, qx, g, group_rows, out_pe, 0, table, n_desc, max_desc};
+        GemvArgs ga{gate, up, 0, qx, g, group_rows, out_pe, 0, table, n_desc, max_desc, gated_op};
         if ((e = launch_gemv(ga, ctx->sm_count, st)) != cudaSuccess) break;
-        if ((e = launch_quantize_acts_layout(g, nullptr, 1, pairs, out_pe, fmt, qg, st)) != cudaSuccess) break;
+        if ((e = launch_quantize_acts_layout(g, nullptr, 1, pairs, out_pe, fmt_dn, qg, st)) != cudaSuccess) break;
         GemvArgs gd{down, DevWeights{}, 0, qg, down_rows, group_rows, hidden, 0, table, n_desc, max_desc};
         if ((e = launch_gemv(gd, ctx->sm_count, st)) != cudaSuccess) break;
         const size_t total = (size_t)seq * hidden;
@@ -473,16 +481,16 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
 int check_moe(const fq_weights* gate, const fq_weights* up, const fq_weights* down, size_t seq, size_t top_k, int gated_op,
               bool shard = false) {
     if (!gate || !up || !down) return fail(FQ_DECLINED_ARGS, "null weights");
-    if (gated_op != 0) return fail(FQ_DECLINED_ARGS, "only swiglu (gated_op 0) is served");
+    if (gated_op < FQ_GATED_SWIGLU || gated_op > FQ_GATED_SITU) return fail(FQ_DECLINED_ARGS, "gated_op %d is not one of FQ_GATED_*", gated_op);
     const DevWeights &g = gate->dw, &u = up->dw, &d = down->dw;
-    if (g.fmt != u.fmt || g.fmt != d.fmt) return fail(FQ_DECLINED_ARGS, "expert tensors must share one format");
+    if (g.fmt != u.fmt) return fail(FQ_DECLINED_ARGS, "gate and up must share one format");
     if (g.n != u.n || g.k != u.k || g.n_mats != u.n_mats || d.n_mats != g.n_mats || d.n != g.k || d.k != g.n)
         return fail(FQ_DECLINED_ARGS, "expert tensor shapes are inconsistent");
     if (seq == 0 || top_k == 0 || (!shard && top_k > (size_t)g.n_mats)) return fail(FQ_DECLINED_ARGS, "bad seq/top_k");
     if (seq * top_k > (size_t)1 << 24) return fail(FQ_DECLINED_ARGS, "too many routed pairs");
     if (g.n_mats > 3072) return fail(FQ_DECLINED_ARGS, "too many experts");  // the route plan keeps four ints per expert in 48 KB of shared memory
-    const ActLayout L = act_layout(g.fmt);
-    if (g.n % L.act_block != 0 || g.n % format_info(g.fmt).block_elems != 0)
+    const ActLayout L = act_layout(d.fmt);
+    if (g.n % L.act_block != 0 || g.n % format_info(d.fmt).block_elems != 0)
         return fail(FQ_DECLINED_ARGS, "expert width %d is not a whole number of blocks", g.n);
     return FQ_OK;
 }
@@ -497,8 +505,9 @@ struct QMoeStage {
 }  // namespace
 
 int moe_layer_shard_dev(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev, int seq,
-                        int top_k, const int* selected_dev, const float* weights_dev, int expert_base, float* partial_dev, cudaStream_t st) {
-    return moe_layer_dev_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, Shard{expert_base, 1}, partial_dev, st);
+                        int top_k, const int* selected_dev, const float* weights_dev, int expert_base, float* partial_dev, cudaStream_t st,
+                        int gated_op) {
+    return moe_layer_dev_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, Shard{expert_base, 1}, partial_dev, st, gated_op);
 }
 
 }  // namespace fq
@@ -534,7 +543,7 @@ int fq_moe_layer_dev(const fq_weights* gate, const fq_weights* up, const fq_weig
     std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
     g_trace.calls++;
     return moe_layer_dev_impl(ctx, gate->dw, up->dw, down->dw, x_dev, (int)seq, (int)top_k, selected_dev, weights_dev, Shard{0, 0},
-                              out_dev, stream ? (cudaStream_t)stream : ctx->stream);
+                              out_dev, stream ? (cudaStream_t)stream : ctx->stream, gated_op);
 }
 
 int fq_moe_layer_ep_dev(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev, size_t seq,
@@ -548,7 +557,7 @@ int fq_moe_layer_ep_dev(const fq_weights* gate, const fq_weights* up, const fq_w
     std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
     g_trace.calls++;
     return moe_layer_dev_impl(ctx, gate->dw, up->dw, down->dw, x_dev, (int)seq, (int)top_k, selected_dev, weights_dev,
-                              Shard{expert_base, 1}, partial_dev, stream ? (cudaStream_t)stream : ctx->stream);
+                              Shard{expert_base, 1}, partial_dev, stream ? (cudaStream_t)stream : ctx->stream, gated_op);
 }
 
 int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x, size_t seq, size_t top_k,
@@ -583,7 +592,7 @@ int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights*
     }
     if (rc == FQ_OK)
         rc = moe_layer_dev_impl(ctx, gate->dw, up->dw, down->dw, (const float*)dev, (int)seq, (int)top_k, (const int*)(dev + o_sel),
-                                (const float*)(dev + o_w), Shard{0, 0}, (float*)(dev + o_out), ctx->stream);
+                                (const float*)(dev + o_w), Shard{0, 0}, (float*)(dev + o_out), ctx->stream, gated_op);
     if (rc == FQ_OK) {
         cudaError_t e = cudaMemcpyAsync(pin + o_out, dev + o_out, xb, cudaMemcpyDeviceToHost, ctx->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
@@ -609,7 +618,7 @@ int fq_moe_layer_stages_for_test(const fq_weights* gate, const fq_weights* up, c
     if (!ctx) return FQ_DECLINED_NO_GPU;
     std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
     return moe_layer_dev_impl(ctx, gate->dw, up->dw, down->dw, x_dev, (int)seq, (int)top_k, selected_dev, weights_dev, Shard{0, 0},
-                              out_dev, ctx->stream, StageTaps{g_pairs_dev, down_pairs_dev});
+                              out_dev, ctx->stream, 0, StageTaps{g_pairs_dev, down_pairs_dev});
 }
 
 // Test seam in the spirit of setQuantMmaForTest (backend/cuda.zig:2563): -1 auto, 0 integer path, 1 tensor path.

@@ -27,7 +27,8 @@ int tp_reduce_scatter_f32(const float* send, float* recv, size_t count_per_rank,
 // moe.cu: one expert shard of the layer (experts [expert_base, expert_base + E_local) of the full layer, global ids
 // in selected_dev, other shards' pairs skipped): partial sums per token.
 int moe_layer_shard_dev(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev, int seq,
-                        int top_k, const int* selected_dev, const float* weights_dev, int expert_base, float* partial_dev, cudaStream_t st);
+                        int top_k, const int* selected_dev, const float* weights_dev, int expert_base, float* partial_dev, cudaStream_t st,
+                        int gated_op = 0);
 
 // ep.cu: print and clear the per-phase device times gathered under FUCINA_B200_EP_TRACE
 void ep_trace_dump(int rank);

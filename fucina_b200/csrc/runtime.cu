@@ -983,6 +983,24 @@ int fq_weights_from_device(int fmt, const void* dev_blocks, size_t nb01, size_t 
     }
     return rc;
 }
+// Rows [row0, row0 + rows) of every matrix of `w` as weights of their own (no copy; `w` must outlive the view and is
+// freed separately). A fused gate_up tensor [E][2 * out_pe][hidden] splits into its gate and up halves this way
+// (llm/gemma/moe.zig:696-901), and a resident matrix into column shards.
+int fq_weights_view(const fq_weights* w, size_t row0, size_t rows, fq_weights** out) {
+    if (!w || !out) return fail(FQ_DECLINED_ARGS, "null pointer");
+    const DevWeights& d = w->dw;
+    if (rows == 0 || row0 + rows > (size_t)d.n) return fail(FQ_DECLINED_ARGS, "row range [%zu, %zu) outside the %d rows of the matrix", row0, row0 + rows, d.n);
+    if (d.tile_rows && (row0 % 32 != 0 || (d.n_mats > 1 && rows % 32 != 0)))
+        return fail(FQ_DECLINED_ARGS, "a view of tile-major weights must start on a 32-row boundary");
+    fq_weights* v = new fq_weights();
+    v->dw = d;
+    v->dw.base = d.base + (d.tile_rows ? (row0 / 32) * ((size_t)32 * d.row_stride) : row0 * d.row_stride);
+    v->dw.n = (int)rows;
+    v->alloc = nullptr;  // a view owns nothing
+    v->bytes = 0;
+    *out = v;
+    return FQ_OK;
+}
 void fq_weights_free(fq_weights* w) {
     if (!w) return;
     if (w->alloc) dev_free(w->alloc);

@@ -72,6 +72,6 @@ int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, s
                             const TcPeer* peer = nullptr);
 int gemm_tensor_grouped_gated_dev(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const void* a_bf16, size_t rows, void* g_bf16,
                                   size_t ldc, const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st,
-                                  const TcPeer* peer = nullptr);
+                                  const TcPeer* peer = nullptr, int gated_op = 0);
 
 }  // namespace fq

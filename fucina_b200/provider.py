@@ -134,6 +134,14 @@ class Weights:
         _check(load().fq_weights_from_device(fmt, _vp(dev_blocks), nb01, nb01 * n, n, k, n_mats, C.byref(h)))
         return cls(h.value, fmt, n, k, n_mats)
 
+    def view(self, row0: int, rows: int) -> "Weights":
+        """Rows [row0, row0 + rows) of every stacked matrix, without a copy (keep `self` alive while the view is used)."""
+        h = C.c_void_p()
+        _check(load().fq_weights_view(self.handle, row0, rows, C.byref(h)))
+        v = Weights(h.value, self.fmt, rows, self.k, self.n_mats)
+        v.parent = self
+        return v
+
     def device_bytes(self) -> int:
         return int(load().fq_weights_device_bytes(self.handle))
 

@@ -62,6 +62,11 @@ enum {
     FQ_ERR_CAPACITY = -3     /* the routing sent more rows to a GPU than its exchange arena holds */
 };
 
+/* backend/ops.zig:89-107 `GatedOp`: g = source(up) * activation(gate) (ops.zig:150-190).
+ * swiglu up * gate*sigmoid(gate); geglu up * gelu_tanh(gate) (Gemma); swiglu_clamp10 clamp(up, +-10) *
+ * silu(min(gate, 10)) (DeepSeek V4); glu up * sigmoid(gate); situ 25 tanh(up/25) * 4 tanh(gate/4) sigmoid(gate). */
+enum { FQ_GATED_SWIGLU = 0, FQ_GATED_GEGLU = 1, FQ_GATED_SWIGLU_CLAMP10 = 2, FQ_GATED_GLU = 3, FQ_GATED_SITU = 4 };
+
 /* backend/cuda.zig:1503-1508 `QMMTile`: one output tile of one expert. */
 typedef struct {
     int32_t expert;
@@ -116,6 +121,10 @@ FQ_API int fq_weights_upload(int fmt, const void* host_blocks, size_t nb01, size
                       size_t n_mats, fq_weights** out);
 FQ_API int fq_weights_from_device(int fmt, const void* dev_blocks, size_t nb01, size_t nb02, size_t n, size_t k,
                            size_t n_mats, fq_weights** out); /* raw blocks already in HBM */
+/* Rows [row0, row0 + rows) of every stacked matrix as weights of their own: no copy, the parent must outlive the
+ * view, both are freed with fq_weights_free. The two halves of a fused gate_up expert tensor
+ * [E][2 * out_pe][hidden] (llm/gemma/moe.zig:717) and the column shards of a resident matrix are such views. (New.) */
+FQ_API int fq_weights_view(const fq_weights* w, size_t row0, size_t rows, fq_weights** out);
 FQ_API void fq_weights_free(fq_weights* w);
 FQ_API size_t fq_weights_device_bytes(const fq_weights* w);
 /* inverse of the repack, for round-trip checks: device layout -> GGUF bytes (host) */
@@ -224,8 +233,10 @@ FQ_API int fq_gemm_q_grouped_nt(int fmt, const void* rhs, size_t rhs_len, int ca
  * Argument-for-argument twin of ExecContext.moeExpertFfn / moeExpertFfnBatch
  * (exec/moe.zig:1135-1298, :1865-2088): x [seq, hidden], selected/weights
  * [seq*top_k] row-major per token, out [seq, hidden]; gate/up are
- * [E][out_pe][hidden], down is [E][hidden][out_pe]. gated_op 0 = swiglu
- * (backend/ops.zig:150-190). Host-buffer and device-buffer forms. */
+ * [E][out_pe][hidden], down is [E][hidden][out_pe]. gated_op is one of FQ_GATED_*
+ * (backend/ops.zig:150-190). gate and up share one format; down may come in another (Gemma pairs Q4_K
+ * gate/up with Q8_0 down, llm/gemma/moe.zig:696-901); a fused [2 * out_pe] gate_up tensor is passed as the two
+ * row views fq_weights_view makes of it. Host-buffer and device-buffer forms. */
 FQ_API int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x, size_t seq,
                  size_t top_k, const int64_t* selected, const float* weights, int gated_op, float* out);
 FQ_API int fq_moe_layer_dev(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev,

@@ -234,13 +234,20 @@ def route_plan(selected: np.ndarray, n_expert: int):
     return count, offset, order, inv
 
 
-def moe_ffn_bf16(fmt, gate, up, down, x, selected, weights, n_expert, out_pe):
+GATED_SWIGLU, GATED_GEGLU, GATED_SWIGLU_CLAMP10, GATED_GLU, GATED_SITU = range(5)
+
+
+def moe_ffn_bf16(fmt, gate, up, down, x, selected, weights, n_expert, out_pe, gated_op=0, fmt_down=None):
     """Oracle B of the expert layer: bf16 operands, f64 dots, f32 activation (the tensor-core arm's reference)."""
-    return _moe(lib().orc_moe_ffn_bf16, fmt, gate, up, down, x, selected, weights, n_expert, out_pe)
+    fn = lambda *a: lib().orc_moe_ffn_bf16_gated(fmt, fmt if fmt_down is None else fmt_down, gated_op, *a[1:])  # noqa: E731
+    return _moe(fn, fmt, gate, up, down, x, selected, weights, n_expert, out_pe)
 
 
-def moe_ffn(fmt, gate, up, down, x, selected, weights, n_expert, out_pe):
-    return _moe(lib().orc_moe_ffn, fmt, gate, up, down, x, selected, weights, n_expert, out_pe)
+def moe_ffn(fmt, gate, up, down, x, selected, weights, n_expert, out_pe, gated_op=0, fmt_down=None):
+    """Oracle A of the expert layer (exec/moe.zig:890-920, :1287-1292); `gated_op` follows backend/ops.zig:89-107,
+    `fmt_down` is the down tensor's format when it differs from gate/up."""
+    fn = lambda *a: lib().orc_moe_ffn_gated(fmt, fmt if fmt_down is None else fmt_down, gated_op, *a[1:])  # noqa: E731
+    return _moe(fn, fmt, gate, up, down, x, selected, weights, n_expert, out_pe)
 
 
 def _moe(fn, fmt, gate, up, down, x, selected, weights, n_expert, out_pe):

@@ -514,6 +514,31 @@ inline float swiglu_pair(float gate, float up) {
     const float sig = 1 / (1 + std::exp(-gate));
     return up * (gate * sig);
 }
+// backend/ops.zig:89-107 `GatedOp`, :150-190 `gatedActivationScalar` / `gatedSourceScalar` / `gatedPairScalar`.
+// Codes: 0 swiglu, 1 geglu, 2 swiglu_clamp10, 3 glu, 4 situ.
+inline float sigmoid_scalar(float v) { return 1 / (1 + std::exp(-v)); }
+inline float gated_activation(int op, float v) {
+    switch (op) {
+        case 1: {  // geluScalar: 0.5 * v * (1 + tanh(sqrt(2/pi) * (v + 0.044715 v^3)))  (ops.zig:200-213)
+            const float sqrt_2_over_pi = 0.7978845608028654f;
+            const float arg = sqrt_2_over_pi * (v + 0.044715f * v * v * v);
+            return 0.5f * v * (1 + std::tanh(arg));
+        }
+        case 2: {
+            const float g = std::min(v, 10.0f);
+            return g * sigmoid_scalar(g);
+        }
+        case 3: return sigmoid_scalar(v);
+        case 4: return 4.0f * std::tanh(v * 0.25f) * sigmoid_scalar(v);
+        default: return v * sigmoid_scalar(v);
+    }
+}
+inline float gated_source(int op, float up) {
+    if (op == 2) return std::min(std::max(up, -10.0f), 10.0f);
+    if (op == 4) return 25.0f * std::tanh(up * 0.04f);
+    return up;
+}
+inline float gated_pair(int op, float gate, float up) { return gated_source(op, up) * gated_activation(op, gate); }
 
 enum Fmt { Q8_0 = 0, Q6_K = 1, Q4_K = 2, Q5_K = 3, TQ2_0 = 16, TQ2_0_FOLDED = 17, Q2_0 = 18 };
 
@@ -837,10 +862,21 @@ int orc_route_plan(const int64_t* selected, size_t pairs, size_t n_expert, int64
 // Decode and batched forms produce the same numbers per element: quantise the
 // token row, gate/up dots, swiglu, requantise, down dot, w*row, add in slot
 // order with the first slot assigned.
+int orc_moe_ffn_gated(int fmt, int fmt_down, int gated_op, const void* gate, const void* up, const void* down, const float* x, size_t seq,
+                      size_t hidden, size_t out_pe, size_t n_expert, size_t top_k, const int64_t* selected,
+                      const float* weights, float* out);
 int orc_moe_ffn(int fmt, const void* gate, const void* up, const void* down, const float* x, size_t seq,
                 size_t hidden, size_t out_pe, size_t n_expert, size_t top_k, const int64_t* selected,
                 const float* weights, float* out) {
-    const size_t rb_in = row_bytes(fmt, hidden), rb_g = row_bytes(fmt, out_pe);
+    return orc_moe_ffn_gated(fmt, fmt, 0, gate, up, down, x, seq, hidden, out_pe, n_expert, top_k, selected, weights, out);
+}
+// The same layer with any gated op (0 swiglu, 1 geglu, 2 swiglu_clamp10, 3 glu, 4 situ) and a down tensor that may
+// come in another format than gate/up (g is then requantised the way that format's kernels want it,
+// exec/moe.zig:904-907).
+int orc_moe_ffn_gated(int fmt, int fmt_down, int gated_op, const void* gate, const void* up, const void* down, const float* x, size_t seq,
+                      size_t hidden, size_t out_pe, size_t n_expert, size_t top_k, const int64_t* selected,
+                      const float* weights, float* out) {
+    const size_t rb_in = row_bytes(fmt, hidden), rb_g = row_bytes(fmt_down, out_pe);
     if (rb_in == 0 || rb_g == 0) return 1;
     for (size_t p = 0; p < seq * top_k; ++p)
         if (selected[p] < 0 || (size_t)selected[p] >= n_expert) return 1;
@@ -861,10 +897,10 @@ int orc_moe_ffn(int fmt, const void* gate, const void* up, const void* down, con
                 gate_v[j] = row_dot(fmt, wg + j * rb_in, qx.data(), hidden);
                 up_v[j] = row_dot(fmt, wu + j * rb_in, qx.data(), hidden);
             }
-            for (size_t j = 0; j < out_pe; ++j) g[j] = swiglu_pair(gate_v[j], up_v[j]);
-            std::vector<uint8_t> qg = quantize_acts(fmt, g.data(), 1, out_pe, &s_g);
+            for (size_t j = 0; j < out_pe; ++j) g[j] = gated_pair(gated_op, gate_v[j], up_v[j]);
+            std::vector<uint8_t> qg = quantize_acts(fmt_down, g.data(), 1, out_pe, &s_g);
             float* po = pair_out.data() + (size_t)p * hidden;
-            for (size_t j = 0; j < hidden; ++j) po[j] = row_dot(fmt, wd + j * rb_g, qg.data(), out_pe);
+            for (size_t j = 0; j < hidden; ++j) po[j] = row_dot(fmt_down, wd + j * rb_g, qg.data(), out_pe);
         }
     }
     for (size_t t = 0; t < seq; ++t)
@@ -885,10 +921,18 @@ int orc_moe_ffn(int fmt, const void* gate, const void* up, const void* down, con
 // tensor-core precision with wide accumulation and applies the activation in f32 between the two
 // products (src/llm/gemma/moe.zig:696-901, src/backend/cuda.zig:3016-3044). Here: bf16 operands,
 // f64 dots rounded to f32, swiglu in f32, g rounded to bf16, weighted combine in slot order.
+int orc_moe_ffn_bf16_gated(int fmt, int fmt_down, int gated_op, const void* gate, const void* up, const void* down, const float* x, size_t seq,
+                           size_t hidden, size_t out_pe, size_t n_expert, size_t top_k, const int64_t* selected,
+                           const float* weights, float* out);
 int orc_moe_ffn_bf16(int fmt, const void* gate, const void* up, const void* down, const float* x, size_t seq,
                      size_t hidden, size_t out_pe, size_t n_expert, size_t top_k, const int64_t* selected,
                      const float* weights, float* out) {
-    const size_t rb_in = row_bytes(fmt, hidden), rb_g = row_bytes(fmt, out_pe);
+    return orc_moe_ffn_bf16_gated(fmt, fmt, 0, gate, up, down, x, seq, hidden, out_pe, n_expert, top_k, selected, weights, out);
+}
+int orc_moe_ffn_bf16_gated(int fmt, int fmt_down, int gated_op, const void* gate, const void* up, const void* down, const float* x, size_t seq,
+                           size_t hidden, size_t out_pe, size_t n_expert, size_t top_k, const int64_t* selected,
+                           const float* weights, float* out) {
+    const size_t rb_in = row_bytes(fmt, hidden), rb_g = row_bytes(fmt_down, out_pe);
     if (rb_in == 0 || rb_g == 0) return 1;
     for (size_t p = 0; p < seq * top_k; ++p)
         if (selected[p] < 0 || (size_t)selected[p] >= n_expert) return 1;
@@ -913,10 +957,10 @@ int orc_moe_ffn_bf16(int fmt, const void* gate, const void* up, const void* down
                 for (size_t i = 0; i < hidden; ++i) acc += (double)round_bf16(wrow[i]) * (double)xb[i];
                 up_v[j] = (float)acc;
             }
-            for (size_t j = 0; j < out_pe; ++j) g[j] = round_bf16(swiglu_pair(gate_v[j], up_v[j]));
+            for (size_t j = 0; j < out_pe; ++j) g[j] = round_bf16(gated_pair(gated_op, gate_v[j], up_v[j]));
             float* po = pair_out.data() + (size_t)p * hidden;
             for (size_t j = 0; j < hidden; ++j) {
-                dequantize_row(fmt, wrow.data(), wd + j * rb_g, out_pe);
+                dequantize_row(fmt_down, wrow.data(), wd + j * rb_g, out_pe);
                 double acc = 0;
                 for (size_t i = 0; i < out_pe; ++i) acc += (double)round_bf16(wrow[i]) * (double)g[i];
                 po[j] = (float)acc;

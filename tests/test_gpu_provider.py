@@ -377,3 +377,52 @@ def test_bounded_device_wait_reports_timeout_and_context_survives(P):
     a = acts(2, k, 91)
     got = P.gemm_quant_nt(oracle.Q4_K, blocks, a, n, cacheable=False)
     assert_close(got, oracle.matmul(oracle.Q4_K, blocks, a), TOL_INT8, "after a reported time-out")
+
+
+@pytest.mark.parametrize("tensor_arm,seq", [(0, 9), (1, 150)])
+@pytest.mark.parametrize("gated_op", [1, 2, 3, 4])
+def test_moe_gated_ops_fused_gate_up_and_a_q8_0_down(P, gated_op, tensor_arm, seq):
+    """Gemma's expert FFN as the reference's GPU arm sees it (src/llm/gemma/moe.zig:696-901): ONE fused gate_up tensor
+    [E][2 * out_pe][hidden] in Q4_K (gate rows first), GeGLU, and a Q8_0 down tensor; plus the other gated ops of
+    backend/ops.zig:89-107. The two halves of the fused tensor are row views of the uploaded stack."""
+    from fucina_b200._lib import load
+
+    hidden, out_pe, n_expert, top_k = 256, 256, 4, 2
+    gate = make_weights("q4_k", n_expert * out_pe, hidden, seed=71)
+    up = make_weights("q4_k", n_expert * out_pe, hidden, seed=72)
+    down = make_weights("q8_0", n_expert * hidden, out_pe, seed=73)
+    rb = gate.shape[1]
+    fused = np.concatenate([gate.reshape(n_expert, out_pe, rb), up.reshape(n_expert, out_pe, rb)], axis=1).reshape(n_expert * 2 * out_pe, rb)
+    w_fused = P.Weights.upload(oracle.Q4_K, fused, 2 * out_pe, hidden, n_expert)
+    wg, wu = w_fused.view(0, out_pe), w_fused.view(out_pe, out_pe)
+    wd = P.Weights.upload(oracle.Q8_0, down, hidden, out_pe, n_expert)
+    rng = np.random.default_rng(74)
+    x = (rng.standard_normal((seq, hidden)) * 12).astype(np.float32)  # wide enough for the +-10 clamps to bite
+    sel, w = oracle.router_topk(rng.standard_normal((seq, n_expert)).astype(np.float32), top_k, True)
+    load().fq_set_moe_tensor_for_test(tensor_arm)
+    try:
+        got = P.moe_layer(wg, wu, wd, x, sel, w, gated_op=gated_op)
+    finally:
+        load().fq_set_moe_tensor_for_test(-1)
+    if tensor_arm:
+        want = oracle.moe_ffn_bf16(oracle.Q4_K, gate, up, down, x, sel, w, n_expert, out_pe, gated_op=gated_op, fmt_down=oracle.Q8_0)
+        rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+        assert np.isfinite(got).all() and float(np.max(np.abs(got - want))) / rms <= 1e-2
+    else:
+        want = oracle.moe_ffn(oracle.Q4_K, gate, up, down, x, sel, w, n_expert, out_pe, gated_op=gated_op, fmt_down=oracle.Q8_0)
+        assert_close(got, want, 5e-3, f"gated op {gated_op}, integer arm")
+    for h in (wg, wu, wd, w_fused):
+        h.free()
+
+
+def test_moe_rejects_unknown_gated_op_and_mismatched_pair(P):
+    gate, up, down, x, _, sel, w = _moe_case("q5_k", 256, 256, 4, 2, 3, seed=62)
+    wg = P.Weights.upload(oracle.Q5_K, gate, 256, 256, 4)
+    wu4 = P.Weights.upload(oracle.Q4_K, make_weights("q4_k", 4 * 256, 256, 63), 256, 256, 4)
+    wd = P.Weights.upload(oracle.Q5_K, down, 256, 256, 4)
+    with pytest.raises(P.Declined):
+        P.moe_layer(wg, wg, wd, x, sel, w, gated_op=9)
+    with pytest.raises(P.Declined):
+        P.moe_layer(wg, wu4, wd, x, sel, w)  # gate and up must share a format
+    for h in (wg, wu4, wd):
+        h.free()

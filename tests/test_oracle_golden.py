@@ -229,3 +229,33 @@ def test_blas_form_of_oracle_b_equals_the_scalar_one():
     x = np.array([1.0, 1.00390625, 1.01171875, -3.0e-39, 65504.0], np.float32)  # exact, tie to even, tie up, subnormal, large
     r = round_bf16(x)
     assert r[0] == 1.0 and r[1] == 1.0 and r[2] == np.float32(1.015625)
+
+
+def test_gated_pairs_follow_the_reference_formulas():
+    """backend/ops.zig:150-190 restated in oracle.cpp against an independent float64 evaluation of the same
+    formulas (the reference holds no stored answers for these ops): one expert, identity-like routing."""
+    from parity import make_weights
+
+    hidden, out_pe = 256, 256
+    gate = make_weights("q8_0", out_pe, hidden, seed=1)
+    up = make_weights("q8_0", out_pe, hidden, seed=2)
+    down = make_weights("q8_0", hidden, out_pe, seed=3)
+    x = (np.random.default_rng(4).standard_normal((3, hidden)) * 12).astype(np.float32)
+    sel = np.zeros((3, 1), np.int64)
+    w = np.ones((3, 1), np.float32)
+    gv = oracle.matmul(oracle.Q8_0, gate, x).astype(np.float64)
+    uv = oracle.matmul(oracle.Q8_0, up, x).astype(np.float64)
+    sig = lambda v: 1 / (1 + np.exp(-v))  # noqa: E731
+    forms = {
+        0: uv * (gv * sig(gv)),
+        1: uv * (0.5 * gv * (1 + np.tanh(0.7978845608028654 * (gv + 0.044715 * gv ** 3)))),
+        2: np.clip(uv, -10, 10) * (np.minimum(gv, 10) * sig(np.minimum(gv, 10))),
+        3: uv * sig(gv),
+        4: 25 * np.tanh(uv * 0.04) * (4 * np.tanh(gv * 0.25) * sig(gv)),
+    }
+    for op, g in forms.items():
+        want = oracle.matmul(oracle.Q8_0, down, g.astype(np.float32))
+        got = oracle.moe_ffn(oracle.Q8_0, gate, up, down, x, sel, w, 1, out_pe, gated_op=op)
+        # g differs from the f32 evaluation by rounding only; the requantisation may move single int8 steps
+        assert np.abs(got - want).max() <= 2e-2 * np.abs(want).max(), op
+    assert np.abs(gv).max() > 10 or np.abs(uv).max() > 10  # the clamps were exercised
