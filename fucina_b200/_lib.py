@@ -74,6 +74,7 @@ SIGNATURES = {
     "fq_gemm_q_grouped_nt": (c_int, [c_int, c_void, c_size, c_int, c_size, c_size, c_size, c_size, P(QmmTile), c_size]),
     "fq_moe_layer": (c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_int, c_void]),
     "fq_moe_layer_dev": (c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_int, c_void, c_void]),
+    "fq_moe_layer_ptqtp_dev": (c_int, [P(c_void), P(c_void), P(c_void), c_int, c_void, c_size, c_size, c_void, c_void, c_int, c_void, c_void]),
     "fq_moe_layer_ep_dev": (
         c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_int, c_int, c_void, c_void]),
     "fq_tp_unique_id": (c_int, [c_void]),

@@ -606,6 +606,87 @@ int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_weights*
     return rc;
 }
 
+// Expert layer over multi-plane ternary (PTQTP) experts (exec/moe.zig:51-78 `MoePtqtpRhs`, :591-631
+// `moePtqtpTileDotRange`): each projection is n_planes TQ2_0 expert stacks; the grouped integer kernel runs once
+// per plane and adds into the same rows (plane 0 stores, later planes accumulate: dot_p0 + dot_p1 (+ dot_p2)
+// per element, left to right), the gated activation follows on the summed gate and up rows, g is requantised
+// once and the down planes accumulate the same way.
+int fq_moe_layer_ptqtp_dev(const fq_weights* const* gate_planes, const fq_weights* const* up_planes, const fq_weights* const* down_planes,
+                           int n_planes, const float* x_dev, size_t seq, size_t top_k, const int32_t* selected_dev, const float* weights_dev,
+                           int gated_op, float* out_dev, void* stream) {
+    if (!gate_planes || !up_planes || !down_planes || n_planes < 1 || n_planes > 3) return fail(FQ_DECLINED_ARGS, "one to three planes per projection");
+    for (int p = 0; p < n_planes; ++p) {
+        if (int rc = check_moe(gate_planes[p], up_planes[p], down_planes[p], seq, top_k, gated_op)) return rc;
+        const DevWeights &g0 = gate_planes[0]->dw, &g = gate_planes[p]->dw, &d = down_planes[p]->dw;
+        if (g.fmt != FQ_TQ2_0 || d.fmt != FQ_TQ2_0) return fail(FQ_DECLINED_ARGS, "PTQTP planes are TQ2_0 tensors");
+        if (g.n != g0.n || g.k != g0.k || g.n_mats != g0.n_mats) return fail(FQ_DECLINED_ARGS, "plane shapes differ");
+    }
+    if (!x_dev || !selected_dev || !weights_dev || !out_dev) return fail(FQ_DECLINED_ARGS, "null pointer");
+    Ctx* ctx = context();
+    if (!ctx) return FQ_DECLINED_NO_GPU;
+    std::lock_guard<std::recursive_mutex> lk(g_dispatch_lock);
+    g_trace.calls++;
+    cudaStream_t st = stream ? (cudaStream_t)stream : ctx->stream;
+    const DevWeights& g0 = gate_planes[0]->dw;
+    const int hidden = g0.k, out_pe = g0.n, n_expert = g0.n_mats, fmt = FQ_TQ2_0;
+    const int pairs = (int)(seq * top_k);
+    int fit_rows = gemv_rows_that_fit(fmt, (size_t)hidden);
+    if (gemv_rows_that_fit(fmt, (size_t)out_pe) < fit_rows) fit_rows = gemv_rows_that_fit(fmt, (size_t)out_pe);
+    if (fit_rows == 0) return fail(FQ_DECLINED_ARGS, "expert rows of %d / %d elements are too long for the integer arm", hidden, out_pe);
+    const int int8_rows = kGroupRows < fit_rows ? kGroupRows : fit_rows;
+    const int group_rows = (int)seq < int8_rows ? (int)seq : int8_rows;
+    const int max_desc = max_desc_for(pairs, n_expert, group_rows);
+    const ActSizes Sx = act_sizes(fmt, hidden), Sg = act_sizes(fmt, out_pe);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += (bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    const size_t o_order = take(sizeof(int) * pairs), o_inv = take(sizeof(int) * pairs), o_nd = take(sizeof(int) * 2);
+    const size_t o_table = take(sizeof(GroupDesc) * max_desc), o_qx = take(Sx.row * pairs);
+    const size_t o_gate = take(sizeof(float) * (size_t)pairs * out_pe), o_up = take(sizeof(float) * (size_t)pairs * out_pe);
+    const size_t o_qg = take(Sg.row * pairs), o_down = take(sizeof(float) * (size_t)pairs * hidden);
+    uint8_t* s = (uint8_t*)dev_alloc_on(off, st);
+    if (!s) return fail(FQ_DECLINED_BUDGET, "MoE scratch allocation of %zu bytes failed", off);
+    int* order = (int*)(s + o_order);
+    int* inv = (int*)(s + o_inv);
+    int* n_desc = (int*)(s + o_nd);
+    GroupDesc* table = (GroupDesc*)(s + o_table);
+    float* gate_rows = (float*)(s + o_gate);
+    float* up_rows = (float*)(s + o_up);  // becomes g in place
+    float* down_rows = (float*)(s + o_down);
+    cudaError_t e = cudaSuccess;
+    do {
+        route_plan_kernel<<<1, 1024, sizeof(int) * 4 * n_expert, st>>>(selected_dev, pairs, n_expert, Shard{0, 0}, group_rows, order, inv, table, n_desc,
+                                                                    n_desc + 1, 0, 0, 0, nullptr, nullptr, nullptr, nullptr);
+        if ((e = cudaGetLastError()) != cudaSuccess) break;
+        if ((e = launch_quantize_acts_layout(x_dev, order, (int)top_k, pairs, hidden, fmt, s + o_qx, st)) != cudaSuccess) break;
+        for (int p = 0; p < n_planes && e == cudaSuccess; ++p) {
+            GemvArgs ga{gate_planes[p]->dw, DevWeights{}, 0, s + o_qx, gate_rows, group_rows, out_pe, p > 0, table, n_desc, max_desc};
+            if ((e = launch_gemv(ga, ctx->sm_count, st)) != cudaSuccess) break;
+            GemvArgs ua{up_planes[p]->dw, DevWeights{}, 0, s + o_qx, up_rows, group_rows, out_pe, p > 0, table, n_desc, max_desc};
+            e = launch_gemv(ua, ctx->sm_count, st);
+        }
+        if (e != cudaSuccess) break;
+        const size_t ng = (size_t)pairs * out_pe;
+        int blocks = (int)((ng + 255) / 256);
+        gated_f32_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>(gate_rows, up_rows, ng, gated_op, up_rows);
+        if ((e = cudaGetLastError()) != cudaSuccess) break;
+        if ((e = launch_quantize_acts_layout(up_rows, nullptr, 1, pairs, out_pe, fmt, s + o_qg, st)) != cudaSuccess) break;
+        for (int p = 0; p < n_planes && e == cudaSuccess; ++p) {
+            GemvArgs da{down_planes[p]->dw, DevWeights{}, 0, s + o_qg, down_rows, group_rows, hidden, p > 0, table, n_desc, max_desc};
+            e = launch_gemv(da, ctx->sm_count, st);
+        }
+        if (e != cudaSuccess) break;
+        launch_combine(down_rows, weights_dev, inv, (int)seq, hidden, (int)top_k, out_dev, st);
+        e = cudaGetLastError();
+    } while (false);
+    g_trace.launches += 5 + 3 * n_planes;
+    dev_free_on(s, st);
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "PTQTP MoE layer launch");
+}
+
 // Test seam: the integer arm of the layer with its two intermediates copied out in pair order, so a test
 // can hold each stage to the f32 tolerance separately (g against the CPU kernels' g; the down product
 // fed the device's own g against the CPU kernels fed the same g).

@@ -335,6 +335,15 @@ def moe_layer_dev(gate: Weights, up: Weights, down: Weights, x_dev, seq: int, to
                                    _vp(weights_dev), gated_op, _vp(out_dev), C.c_void_p(stream)))
 
 
+def moe_layer_ptqtp_dev(gate_planes: list[Weights], up_planes: list[Weights], down_planes: list[Weights], x_dev, seq: int, top_k: int,
+                        selected_dev, weights_dev, out_dev, gated_op: int = 0, stream: int = 0) -> None:
+    """The expert layer over multi-plane ternary experts (`MoePtqtpRhs`, src/exec/moe.zig:51-78): K TQ2_0 stacks per projection."""
+    K = len(gate_planes)
+    arr = lambda ws: (C.c_void_p * K)(*[w.handle for w in ws])  # noqa: E731
+    _check(load().fq_moe_layer_ptqtp_dev(arr(gate_planes), arr(up_planes), arr(down_planes), K, _vp(x_dev), seq, top_k, _vp(selected_dev),
+                                         _vp(weights_dev), gated_op, _vp(out_dev), C.c_void_p(stream)))
+
+
 def moe_layer_stages_for_test(gate: Weights, up: Weights, down: Weights, x_dev, seq: int, top_k: int, selected_dev,
                               weights_dev, g_pairs_dev, down_pairs_dev, out_dev) -> None:
     """The layer's integer arm with g and the unweighted down rows copied out in pair order (test seam)."""

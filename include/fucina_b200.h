@@ -242,6 +242,12 @@ FQ_API int fq_moe_layer(const fq_weights* gate, const fq_weights* up, const fq_w
 FQ_API int fq_moe_layer_dev(const fq_weights* gate, const fq_weights* up, const fq_weights* down, const float* x_dev,
                      size_t seq, size_t top_k, const int32_t* selected_dev, const float* weights_dev,
                      int gated_op, float* out_dev, void* stream);
+/* The same layer over multi-plane ternary (PTQTP) experts (exec/moe.zig:51-78 `MoePtqtpRhs`, :591-631
+ * `moePtqtpTileDotRange`): arrays of n_planes (1..3) TQ2_0 expert stacks per projection; every product is the
+ * plane dots summed per element in plane order, as the dense fused PTQTP linear sums them. Integer arm. */
+FQ_API int fq_moe_layer_ptqtp_dev(const fq_weights* const* gate_planes, const fq_weights* const* up_planes,
+                                  const fq_weights* const* down_planes, int n_planes, const float* x_dev, size_t seq, size_t top_k,
+                                  const int32_t* selected_dev, const float* weights_dev, int gated_op, float* out_dev, void* stream);
 /* Expert-parallel shard of the same layer (the reference is single-device, backend/cuda.zig:439,
  * so this has no counterpart there). gate/up/down hold experts [expert_base, expert_base + E_local)
  * of the full layer; `selected_dev` carries GLOBAL expert ids. Pairs routed to other shards are

@@ -267,3 +267,21 @@ def _moe(fn, fmt, gate, up, down, x, selected, weights, n_expert, out_pe):
     )
     assert rc == 0
     return out
+
+
+def moe_ffn_ptqtp(gate_planes, up_planes, down_planes, x, selected, weights, n_expert, out_pe, gated_op=0):
+    """Expert layer over multi-plane ternary experts (exec/moe.zig:51-78, :591-631): lists of K TQ2_0 plane stacks
+    per projection, plane dots summed per element in plane order."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    seq, hidden = x.shape
+    sel = np.ascontiguousarray(selected, dtype=np.int64).reshape(seq, -1)
+    top_k = sel.shape[1]
+    w = np.ascontiguousarray(weights, dtype=np.float32).reshape(seq, top_k)
+    keep = [[np.ascontiguousarray(p, dtype=np.uint8) for p in planes] for planes in (gate_planes, up_planes, down_planes)]
+    K = len(keep[0])
+    arrs = [(ctypes.c_void_p * K)(*[p.ctypes.data for p in planes]) for planes in keep]
+    out = np.zeros((seq, hidden), dtype=np.float32)
+    rc = lib().orc_moe_ffn_ptqtp(K, gated_op, arrs[0], arrs[1], arrs[2], _p(x), _sz(seq), _sz(hidden), _sz(out_pe), _sz(n_expert),
+                                 _sz(top_k), _p(sel), _p(w), _p(out))
+    assert rc == 0
+    return out

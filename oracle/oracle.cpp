@@ -981,4 +981,62 @@ int orc_moe_ffn_bf16_gated(int fmt, int fmt_down, int gated_op, const void* gate
     return 0;
 }
 
+// Expert layer over multi-plane ternary (PTQTP) experts: every projection is K TQ2_0 plane stacks with the
+// geometry of a TQ2_0 expert stack; a tile dot runs once per plane and the results add per element in plane
+// order (exec/moe.zig:51-78 `MoePtqtpRhs`, :591-631 `moePtqtpTileDotRange`), then the layer proceeds as
+// orc_moe_ffn_gated does.
+int orc_moe_ffn_ptqtp(int n_planes, int gated_op, const void* const* gate, const void* const* up, const void* const* down, const float* x,
+                      size_t seq, size_t hidden, size_t out_pe, size_t n_expert, size_t top_k, const int64_t* selected,
+                      const float* weights, float* out) {
+    const int fmt = TQ2_0;
+    const size_t rb_in = row_bytes(fmt, hidden), rb_g = row_bytes(fmt, out_pe);
+    if (rb_in == 0 || rb_g == 0 || n_planes < 1 || n_planes > 3) return 1;
+    for (size_t p = 0; p < seq * top_k; ++p)
+        if (selected[p] < 0 || (size_t)selected[p] >= n_expert) return 1;
+    std::vector<float> pair_out(seq * top_k * hidden);
+#pragma omp parallel
+    {
+        std::vector<float> gate_v(out_pe), up_v(out_pe), g(out_pe);
+#pragma omp for schedule(dynamic, 1)
+        for (long long p = 0; p < (long long)(seq * top_k); ++p) {
+            const size_t t = (size_t)p / top_k, e = (size_t)selected[p];
+            size_t s_in = 0, s_g = 0;
+            std::vector<uint8_t> qx = quantize_acts(fmt, x + t * hidden, 1, hidden, &s_in);
+            for (size_t j = 0; j < out_pe; ++j) {
+                float gsum = 0, usum = 0;
+                for (int pl = 0; pl < n_planes; ++pl) {
+                    const float gd = row_dot(fmt, (const uint8_t*)gate[pl] + (e * out_pe + j) * rb_in, qx.data(), hidden);
+                    const float ud = row_dot(fmt, (const uint8_t*)up[pl] + (e * out_pe + j) * rb_in, qx.data(), hidden);
+                    gsum = pl ? gsum + gd : gd;
+                    usum = pl ? usum + ud : ud;
+                }
+                gate_v[j] = gsum, up_v[j] = usum;
+            }
+            for (size_t j = 0; j < out_pe; ++j) g[j] = gated_pair(gated_op, gate_v[j], up_v[j]);
+            std::vector<uint8_t> qg = quantize_acts(fmt, g.data(), 1, out_pe, &s_g);
+            float* po = pair_out.data() + (size_t)p * hidden;
+            for (size_t j = 0; j < hidden; ++j) {
+                float dsum = 0;
+                for (int pl = 0; pl < n_planes; ++pl) {
+                    const float dd = row_dot(fmt, (const uint8_t*)down[pl] + (e * hidden + j) * rb_g, qg.data(), out_pe);
+                    dsum = pl ? dsum + dd : dd;
+                }
+                po[j] = dsum;
+            }
+        }
+    }
+    for (size_t t = 0; t < seq; ++t)
+        for (size_t kk = 0; kk < top_k; ++kk) {
+            const size_t p = t * top_k + kk;
+            const float w = weights[p];
+            const float* src = pair_out.data() + p * hidden;
+            float* dst = out + t * hidden;
+            if (kk == 0)
+                for (size_t j = 0; j < hidden; ++j) dst[j] = w * src[j];
+            else
+                for (size_t j = 0; j < hidden; ++j) dst[j] += w * src[j];
+        }
+    return 0;
+}
+
 }  // extern "C"

@@ -426,3 +426,35 @@ def test_moe_rejects_unknown_gated_op_and_mismatched_pair(P):
         P.moe_layer(wg, wu4, wd, x, sel, w)  # gate and up must share a format
     for h in (wg, wu4, wd):
         h.free()
+
+
+@pytest.mark.parametrize("planes,seq", [(1, 5), (2, 1), (2, 37), (3, 20)])
+def test_moe_layer_over_ptqtp_expert_stacks(P, torch, planes, seq):
+    """`MoePtqtpRhs` (src/exec/moe.zig:51-78): every projection of an expert is K ternary planes; each product is the
+    plane dots added per element in plane order (`moePtqtpTileDotRange`, :591-631)."""
+    hidden, out_pe, n_expert, top_k = 512, 256, 6, 2
+    rng = np.random.default_rng(90 + planes)
+
+    def stack(rows, k, p):
+        trits = rng.integers(-1, 2, size=(n_expert * rows, k)).astype(np.int8)
+        scales = np.abs(rng.standard_normal((n_expert * rows, k // 256)) * 0.02 / (3 ** p)).astype(np.float32)
+        return oracle.pack_ptqtp_plane(trits, scales)
+
+    gate = [stack(out_pe, hidden, p) for p in range(planes)]
+    up = [stack(out_pe, hidden, p) for p in range(planes)]
+    down = [stack(hidden, out_pe, p) for p in range(planes)]
+    x = rng.standard_normal((seq, hidden)).astype(np.float32)
+    sel, w = oracle.router_topk(rng.standard_normal((seq, n_expert)).astype(np.float32), top_k, True)
+    wg = [P.Weights.upload(oracle.TQ2_0, b, out_pe, hidden, n_expert) for b in gate]
+    wu = [P.Weights.upload(oracle.TQ2_0, b, out_pe, hidden, n_expert) for b in up]
+    wd = [P.Weights.upload(oracle.TQ2_0, b, hidden, out_pe, n_expert) for b in down]
+    out = torch.full((seq, hidden), float("nan"), device="cuda")
+    P.moe_layer_ptqtp_dev(wg, wu, wd, torch.from_numpy(x).cuda(), seq, top_k, torch.from_numpy(sel.astype(np.int32)).cuda(),
+                          torch.from_numpy(w).cuda(), out)
+    P.synchronize()
+    want = oracle.moe_ffn_ptqtp(gate, up, down, x, sel, w, n_expert, out_pe)
+    assert_close(out.cpu().numpy(), want, 5e-3, f"PTQTP experts, {planes} plane(s), seq {seq}")
+    if planes == 1:  # one plane is the plain TQ2_0 expert layer
+        assert np.array_equal(want, oracle.moe_ffn(oracle.TQ2_0, gate[0], up[0], down[0], x, sel, w, n_expert, out_pe))
+    for h in wg + wu + wd:
+        h.free()
