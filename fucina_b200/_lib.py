@@ -72,6 +72,7 @@ SIGNATURES = {
     "fq_qmoe_unlock": (None, []),
     "fq_qmoe_stage": (c_int, [c_size, c_size, P(c_void), P(c_void)]),
     "fq_gemm_q_grouped_nt": (c_int, [c_int, c_void, c_size, c_int, c_size, c_size, c_size, c_size, P(QmmTile), c_size]),
+    "fq_set_grouped_tensor_for_test": (None, [c_int]),
     "fq_moe_layer": (c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_int, c_void]),
     "fq_moe_layer_dev": (c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_int, c_void, c_void]),
     "fq_moe_layer_ptqtp_dev": (c_int, [P(c_void), P(c_void), P(c_void), c_int, c_void, c_size, c_size, c_void, c_void, c_int, c_void, c_void]),

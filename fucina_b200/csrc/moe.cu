@@ -731,6 +731,19 @@ int fq_qmoe_stage(size_t in_bytes, size_t out_bytes, float** in, float** out) {
 
 }  // extern "C"
 
+// A run: consecutive activation rows [row0, row0 + m) of the staged panel that one expert multiplies. The caller's
+// tiles (32 rows each in the reference's builder, llm/gemma/moe.zig:773-787) of one expert over adjoining rows
+// merge into one run, so the expert's weights stream once per run, not once per tile.
+struct GroupedRun {
+    int expert, row0, m;
+};
+// Runs at least this long multiply on the tensor cores (bf16 operands, as the reference's own grouped arm rounds its
+// operands, backend/cuda/kernels.cu:340-379); shorter ones keep the CPU kernels' int8 arithmetic.
+constexpr int kGroupedTensorRows = 17;
+static int g_grouped_tensor_mode = -1;  // test seam: -1 by run length, 0 never, 1 every run the format allows
+
+extern "C" void fq_set_grouped_tensor_for_test(int mode) { g_grouped_tensor_mode = mode < 0 ? -1 : (mode ? 1 : 0); }
+
 extern "C" int fq_gemm_q_grouped_nt(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02, size_t n_out,
                                     size_t k, const fq_qmm_tile* tiles, size_t n_tiles) {
     // argument rules of backend/cuda.zig:2254-2257
@@ -743,21 +756,21 @@ extern "C" int fq_gemm_q_grouped_nt(int fmt, const void* rhs, size_t rhs_len, in
     if (!g_stage.in || !g_stage.out) return fail(FQ_DECLINED_ARGS, "fq_qmoe_stage was not called");
     int max_expert = 0;
     size_t rows = 0;
-    std::vector<GroupDesc> descs;
-    // rows per table entry: as many as the kernel's shared memory holds for this K (at most 16)
+    // rows per table entry of the integer arm: as many as the kernel's shared memory holds for this K (at most 16)
     const int fit_rows = gemv_rows_that_fit(fmt, k);
     if (fit_rows == 0) return fail(FQ_DECLINED_ARGS, "k=%zu is too long for the grouped kernel", k);
     const int group_rows = kGroupRows < fit_rows ? kGroupRows : fit_rows;
+    std::vector<GroupedRun> runs;
     for (size_t t = 0; t < n_tiles; ++t) {
         const fq_qmm_tile& tl = tiles[t];
         if (tl.expert < 0 || tl.base_row < 0 || tl.m <= 0 || tl.m > tl.tile_m) return fail(FQ_DECLINED_ARGS, "tile %zu is malformed", t);
         if (tl.expert > max_expert) max_expert = tl.expert;
         if ((size_t)tl.base_row + tl.m > rows) rows = (size_t)tl.base_row + tl.m;
-        for (int j = 0; j < tl.m; j += group_rows) descs.push_back({tl.expert, tl.base_row + j, tl.m - j < group_rows ? tl.m - j : group_rows, 0});
+        if (!runs.empty() && runs.back().expert == tl.expert && runs.back().row0 + runs.back().m == tl.base_row) runs.back().m += tl.m;
+        else runs.push_back({tl.expert, tl.base_row, tl.m});
     }
     if (rows * k * sizeof(float) > g_stage.in_bytes || rows * n_out * sizeof(float) > g_stage.out_bytes)
         return fail(FQ_DECLINED_ARGS, "tiles reach beyond the staged panels");
-    if (descs.size() > (size_t)INT32_MAX) return fail(FQ_DECLINED_ARGS, "tile table too large (%zu row groups)", descs.size());
     const size_t n_mats = (size_t)max_expert + 1;
     if (rhs_len < nb02 * (n_mats - 1) + nb01 * n_out) return fail(FQ_DECLINED_ARGS, "rhs_len too short for expert %d", max_expert);
     Ctx* ctx = context();
@@ -768,40 +781,77 @@ extern "C" int fq_gemm_q_grouped_nt(int fmt, const void* rhs, size_t rhs_len, in
     fq_weights* temp = nullptr;
     int rc = resolve_rhs(ctx, fmt, rhs, rhs_len, cacheable, nb01, nb02, n_out, k, n_mats, &view, &temp);
     if (rc != FQ_OK) return rc;
+    // split the runs over the two arms
+    const bool tc_ok = g_grouped_tensor_mode != 0 && tensor_path_serves(view) && k % 256 == 0;
+    std::vector<GroupDesc> descs;
+    std::vector<TcTile> tc;
+    const int row_tiles = (int)((n_out + 127) / 128);
+    for (const GroupedRun& r : runs) {
+        if (tc_ok && (g_grouped_tensor_mode == 1 || r.m >= kGroupedTensorRows)) {
+            for (int t0 = 0; t0 < r.m; t0 += 128)
+                for (int rt = 0; rt < row_tiles; ++rt) tc.push_back({r.expert, rt, r.row0 + t0, r.m - t0 < 128 ? r.m - t0 : 128});
+        } else {
+            for (int j = 0; j < r.m; j += group_rows) descs.push_back({r.expert, r.row0 + j, r.m - j < group_rows ? r.m - j : group_rows, 0});
+        }
+    }
+    if (descs.size() > (size_t)INT32_MAX / 2 || tc.size() > (size_t)INT32_MAX / 2) {
+        if (temp) fq_weights_free(temp);
+        return fail(FQ_DECLINED_ARGS, "tile table too large");
+    }
     const ActSizes S = act_sizes(fmt, k);
     const size_t in_b = rows * k * sizeof(float), out_b = rows * n_out * sizeof(float);
-    const size_t o_out = (in_b + 255) & ~(size_t)255, o_q = o_out + ((out_b + 255) & ~(size_t)255);
-    const size_t o_tab = o_q + ((S.row * rows + 255) & ~(size_t)255), o_nd = o_tab + ((descs.size() * sizeof(GroupDesc) + 255) & ~(size_t)255);
-    const size_t total = o_nd + 256;
-    uint8_t* dev = (uint8_t*)dev_alloc(total);
-    GroupDesc* pin_tab = (GroupDesc*)pin_alloc(descs.size() * sizeof(GroupDesc) + sizeof(int));
-    if (!dev || !pin_tab) rc = fail(FQ_DECLINED_BUDGET, "grouped staging allocation failed");
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += (bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    const size_t o_in = take(in_b), o_out = take(out_b), o_q = take(descs.empty() ? 0 : S.row * rows), o_bf = take(tc.empty() ? 0 : rows * k * 2);
+    const size_t tab_b = descs.size() * sizeof(GroupDesc), tc_b = tc.size() * sizeof(TcTile);
+    const size_t o_tab = take(tab_b), o_tc = take(tc_b), o_nd = take(2 * sizeof(int));
+    uint8_t* dev = (uint8_t*)dev_alloc(off);
+    // one page-locked block for both tables and their counts: [descs][tiles][n_desc, n_tiles]
+    const size_t p_tc = (tab_b + 15) & ~(size_t)15, p_nd = p_tc + ((tc_b + 15) & ~(size_t)15);
+    uint8_t* pin = (uint8_t*)pin_alloc(p_nd + 2 * sizeof(int));
+    if (!dev || !pin) rc = fail(FQ_DECLINED_BUDGET, "grouped staging allocation failed");
     cudaError_t e = cudaSuccess;
     if (rc == FQ_OK) {
-        memcpy(pin_tab, descs.data(), descs.size() * sizeof(GroupDesc));
-        int* pin_nd = (int*)(pin_tab + descs.size());
-        *pin_nd = (int)descs.size();
+        if (tab_b) memcpy(pin, descs.data(), tab_b);
+        if (tc_b) memcpy(pin + p_tc, tc.data(), tc_b);
+        int* pin_nd = (int*)(pin + p_nd);
+        pin_nd[0] = (int)descs.size(), pin_nd[1] = (int)tc.size();
         do {
-            if ((e = cudaMemcpyAsync(dev, g_stage.in, in_b, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
-            if ((e = cudaMemcpyAsync(dev + o_tab, pin_tab, descs.size() * sizeof(GroupDesc), cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
-            if ((e = cudaMemcpyAsync(dev + o_nd, pin_nd, sizeof(int), cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
+            if ((e = cudaMemcpyAsync(dev + o_in, g_stage.in, in_b, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
+            if (tab_b && (e = cudaMemcpyAsync(dev + o_tab, pin, tab_b, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
+            if (tc_b && (e = cudaMemcpyAsync(dev + o_tc, pin + p_tc, tc_b, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
+            if ((e = cudaMemcpyAsync(dev + o_nd, pin_nd, 2 * sizeof(int), cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
             // rows no tile names keep whatever the out panel held: copy it up first
             if ((e = cudaMemcpyAsync(dev + o_out, g_stage.out, out_b, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) break;
-            if ((e = launch_quantize_acts_layout((const float*)dev, nullptr, 1, (int)rows, (int)k, fmt, dev + o_q, ctx->stream)) != cudaSuccess) break;
-            GemvArgs ga{view, DevWeights{}, 0, dev + o_q, (float*)(dev + o_out), group_rows, (int)n_out, 0, (const GroupDesc*)(dev + o_tab),
-                        (const int*)(dev + o_nd), (int)descs.size()};
-            if ((e = launch_gemv(ga, ctx->sm_count, ctx->stream)) != cudaSuccess) break;
+            if (!descs.empty()) {
+                if ((e = launch_quantize_acts_layout((const float*)(dev + o_in), nullptr, 1, (int)rows, (int)k, fmt, dev + o_q, ctx->stream)) != cudaSuccess) break;
+                GemvArgs ga{view, DevWeights{}, 0, dev + o_q, (float*)(dev + o_out), group_rows, (int)n_out, 0, (const GroupDesc*)(dev + o_tab),
+                            (const int*)(dev + o_nd), (int)descs.size()};
+                if ((e = launch_gemv(ga, ctx->sm_count, ctx->stream)) != cudaSuccess) break;
+                g_trace.launches += 2;
+            }
+            if (!tc.empty()) {
+                if ((e = launch_f32_to_bf16((const float*)(dev + o_in), dev + o_bf, rows * k, ctx->stream)) != cudaSuccess) break;
+                g_trace.launches++;
+                rc = gemm_tensor_grouped_dev(ctx, view, dev + o_bf, rows, (float*)(dev + o_out), n_out, (const TcTile*)(dev + o_tc), (const int*)(dev + o_nd) + 1,
+                                             (int)tc.size(), 128, ctx->stream);
+                if (rc != FQ_OK) break;
+            }
             if ((e = cudaMemcpyAsync(g_stage.out, dev + o_out, out_b, cudaMemcpyDeviceToHost, ctx->stream)) != cudaSuccess) break;
             e = cudaStreamSynchronize(ctx->stream);
         } while (false);
-        g_trace.launches += 2;
         g_trace.h2d_bytes += in_b + out_b;
         g_trace.d2h_bytes += out_b;
         if (e != cudaSuccess) rc = cuda_fail(e, "grouped GEMM");
     }
     cudaStreamSynchronize(ctx->stream);
-    dev_free(dev);
-    pin_free(pin_tab);
+    if (rc == FQ_OK) rc = device_status(ctx);
+    dev_free_idle(dev);
+    pin_free(pin);
     if (temp) fq_weights_free(temp);
     return rc;
 }

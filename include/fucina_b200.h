@@ -228,6 +228,12 @@ FQ_API void fq_qmoe_unlock(void);
 FQ_API int fq_qmoe_stage(size_t in_bytes, size_t out_bytes, float** in, float** out);
 FQ_API int fq_gemm_q_grouped_nt(int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02,
                          size_t n_out, size_t k, const fq_qmm_tile* tiles, size_t n_tiles);
+/* Tiles of one expert over adjoining rows are merged into runs (the expert's weights stream once per run). Runs of
+ * 17 rows or more multiply on the tensor cores over bf16-rounded operands (the reference's grouped kernel rounds
+ * its operands to f16, backend/cuda/kernels.cu:340-379), shorter runs keep the CPU kernels' int8 arithmetic.
+ * Test seam in the spirit of setQuantMmaForTest (backend/cuda.zig:2563): -1 by run length, 0 integer arm only,
+ * 1 tensor cores for every run the format allows. */
+FQ_API void fq_set_grouped_tensor_for_test(int mode);
 
 /* ---- fused, device-resident MoE expert layer (new) ----
  * Argument-for-argument twin of ExecContext.moeExpertFfn / moeExpertFfnBatch

@@ -167,18 +167,17 @@ def test_async_slots_decline_when_exhausted(P):
     load().fq_evict_resident(w.ctypes.data)
 
 
-@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q8_0"])
-def test_grouped_tiles(P, fmt_name):
-    # src/backend/cuda.zig:3157-3185: 4 experts, n=64, k=2B, per-expert m = {1,7,33,40}
+def _grouped_case(P, fmt_name, n_out, k, ms, mode, seed=16):
+    """Run `gemmQGroupedNt` over per-expert row counts `ms` cut into the reference's 32-row tiles
+    (src/llm/gemma/moe.zig:773-787) and return (blocks, a, got)."""
     fmt = oracle.FORMATS[fmt_name]
-    n_out, k = 64, 512
-    ms = [1, 7, 33, 40]
-    blocks = make_weights(fmt_name, n_out * 4, k, seed=16)
+    blocks = make_weights(fmt_name, n_out * len(ms), k, seed=seed)
     rows = sum(ms)
-    a = acts(rows, k, 17)
+    a = acts(rows, k, seed + 1)
     from fucina_b200._lib import load
 
     lib = load()
+    lib.fq_set_grouped_tensor_for_test(mode)
     lib.fq_qmoe_lock()
     try:
         pin, pout = P.qmoe_stage(rows * k, rows * n_out)
@@ -193,11 +192,48 @@ def test_grouped_tiles(P, fmt_name):
         got = np.array(pout).reshape(rows, n_out)
     finally:
         lib.fq_qmoe_unlock()
+        lib.fq_set_grouped_tensor_for_test(-1)
+    return blocks, a, got
+
+
+@pytest.mark.parametrize("mode", [-1, 0, 1])
+@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q8_0"])
+def test_grouped_tiles(P, fmt_name, mode):
+    # src/backend/cuda.zig:3157-3185: 4 experts, n=64, k=2B, per-expert m = {1,7,33,40}. By run length (-1) the runs
+    # of 33 and 40 rows multiply on the tensor cores and the runs of 1 and 7 rows on the integer kernel; the seam
+    # pins either arm for all runs.
+    fmt = oracle.FORMATS[fmt_name]
+    n_out, k = 64, 512
+    ms = [1, 7, 33, 40]
+    blocks, a, got = _grouped_case(P, fmt_name, n_out, k, ms, mode)
     base = 0
     for e, m in enumerate(ms):
-        want = oracle.matmul(fmt, blocks[e * n_out:(e + 1) * n_out], a[base:base + m])
-        assert_close(got[base:base + m], want, TOL_INT8, f"{fmt_name} expert {e}")
+        w = blocks[e * n_out:(e + 1) * n_out]
+        tensor = mode == 1 or (mode == -1 and m >= 17)
+        if tensor:  # bf16 operands: the reference's own bound for its grouped kernel (src/backend/cuda.zig:3016-3044)
+            assert_close(got[base:base + m], oracle.matmul_dequant_f64(fmt, w, a[base:base + m], round_bf16=True), 1e-2, f"{fmt_name} expert {e} (tensor)")
+        else:
+            assert_close(got[base:base + m], oracle.matmul(fmt, w, a[base:base + m]), TOL_INT8, f"{fmt_name} expert {e} (int8)")
         base += m
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_grouped_long_runs_are_merged_from_32_row_tiles(P, mode):
+    # four experts of 300 rows each arrive as ten tiles per expert; the tiles of an expert merge into one run
+    n_out, k = 256, 1024
+    ms = [300, 300, 300, 300]
+    before = P.trace_counters()["launches"]
+    blocks, a, got = _grouped_case(P, "q4_k", n_out, k, ms, mode, seed=18)
+    launches = P.trace_counters()["launches"] - before
+    base = 0
+    for e, m in enumerate(ms):
+        w = blocks[e * n_out:(e + 1) * n_out]
+        if mode:
+            assert_close(got[base:base + m], oracle.matmul_dequant_f64(oracle.Q4_K, w, a[base:base + m], round_bf16=True), 1e-2, f"expert {e}")
+        else:
+            assert_close(got[base:base + m], oracle.matmul_fast(oracle.Q4_K, w, a[base:base + m]), TOL_INT8, f"expert {e}")
+        base += m
+    assert launches <= 4  # repack, then one conversion or quantisation pass and one product: not a launch per tile
 
 
 def _moe_case(fmt_name, hidden, out_pe, n_expert, top_k, seq, seed):
