@@ -119,6 +119,7 @@ struct TcArgs {
     __nv_bfloat16* g_out;
     TcPeer peer;  // multi-GPU hooks (all null / zero on one GPU)
     int gated_op; // FQ_GATED_* of the gated form
+    unsigned sleep_ns;  // pause between polls of the roles that wait off the critical path (see mbar_wait)
 };
 
 // One output tile: weight rows [rt*128, +128) of matrix `mat` times activation rows [tok0, tok0+ntok).
@@ -588,7 +589,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 for (int u = 0; u < PASSES * units && ok; ++u) {
                     for (int p = 0; p < 4; ++p, ++gb) {
                         const int s = gb % STAGES;
-                        if (!mbar_wait(smem_u32(&B->empty[s]), ((gb / STAGES) & 1) ^ 1, B, A.status, kProducerSleepNs)) {
+                        if (!mbar_wait(smem_u32(&B->empty[s]), ((gb / STAGES) & 1) ^ 1, B, A.status, A.sleep_ns)) {
                             ok = false;
                             break;
                         }
@@ -752,7 +753,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 const CUtensorMap* tmw = (GATED && ps) ? &tmap_weights2 : &tmap_weights;
                 for (int u = 0; u < units; ++u, ++gu) {
                     const int rs = gu % RAW_STAGES;
-                    if (!mbar_wait(smem_u32(&B->raw_empty[rs]), ((gu / RAW_STAGES) & 1) ^ 1, B, A.status, kProducerSleepNs)) {
+                    if (!mbar_wait(smem_u32(&B->raw_empty[rs]), ((gu / RAW_STAGES) & 1) ^ 1, B, A.status, A.sleep_ns)) {
                         ok = false;
                         break;
                     }
@@ -790,7 +791,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             bool ok = true;
             for (int ps = 0; ps < PASSES; ++ps) {
                 const int ai = GATED ? ps : t % NACC;
-                if (!mbar_wait(smem_u32(&B->tmem_full[ai]), (GATED ? t : t / NACC) & 1, B, A.status, kEpilogueSleepNs)) {
+                if (!mbar_wait(smem_u32(&B->tmem_full[ai]), (GATED ? t : t / NACC) & 1, B, A.status, 2 * A.sleep_ns)) {
                     ok = false;
                     break;
                 }
@@ -806,17 +807,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                         // The gate pass parks gate * sigmoid(gate) in shared memory (each thread re-reads only what
                         // it wrote) while the MMAs of the up pass run; the up pass finishes the product.
                         float* mine = sG + (size_t)c0 * BM + q * 32 + lane;
+                        // swiglu, the common op, keeps a loop of its own: the five-way switch inside the unrolled loop
+                        // made this epilogue long enough to stall the up pass behind it
                         if (ps == 0) {
+                            if (A.gated_op == FQ_GATED_SWIGLU) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                mine[j * BM] = gated_activation(A.gated_op, __uint_as_float(acc[j]));
+                                for (int j = 0; j < 32; ++j) {
+                                    const float gv = __uint_as_float(acc[j]);
+                                    const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gv)));
+                                    mine[j * BM] = __fmul_rn(gv, sig);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) mine[j * BM] = gated_activation(A.gated_op, __uint_as_float(acc[j]));
                             }
                         } else if (out_row < n) {
+                            if (A.gated_op == FQ_GATED_SWIGLU) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                if (c0 + j < T.ntok)
-                                    A.g_out[(size_t)(T.tok0 + c0 + j) * A.ldc + out_row] =
-                                        __float2bfloat16_rn(__fmul_rn(gated_source(A.gated_op, __uint_as_float(acc[j])), mine[j * BM]));
+                                for (int j = 0; j < 32; ++j) {
+                                    if (c0 + j < T.ntok)
+                                        A.g_out[(size_t)(T.tok0 + c0 + j) * A.ldc + out_row] =
+                                            __float2bfloat16_rn(__fmul_rn(__uint_as_float(acc[j]), mine[j * BM]));
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    if (c0 + j < T.ntok)
+                                        A.g_out[(size_t)(T.tok0 + c0 + j) * A.ldc + out_row] =
+                                            __float2bfloat16_rn(__fmul_rn(gated_source(A.gated_op, __uint_as_float(acc[j])), mine[j * BM]));
+                                }
                             }
                         }
                     } else if (out_row < n) {
@@ -974,7 +993,8 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
     if (int rc = encode_packed_rows(enc, w, &tmap_w)) return rc;
     if (int rc = encode_packed_rows(enc, up ? *up : w, &tmap_w2)) return rc;
     static const int diag = getenv("FUCINA_B200_TC_DIAG") ? atoi(getenv("FUCINA_B200_TC_DIAG")) : 0;
-    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev, diag, up ? *up : w, g_out, peer ? *peer : TcPeer{}, gated_op};
+    static const unsigned sleep_ns = getenv("FUCINA_B200_TC_SLEEP_NS") ? (unsigned)atoi(getenv("FUCINA_B200_TC_SLEEP_NS")) : kProducerSleepNs;
+    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev, diag, up ? *up : w, g_out, peer ? *peer : TcPeer{}, gated_op, sleep_ns};
     const int tiles = table ? max_tiles : ((w.n + BM - 1) / BM) * (int)((rows + BN - 1) / BN);
     const int grid = tiles < ctx->sm_count ? (tiles > 0 ? tiles : 1) : ctx->sm_count;
     cudaError_t e;
