@@ -73,11 +73,17 @@ static cudaEvent_t ktime_event() {
 struct Config {
     bool gpu_enabled = true;
     bool decode_enabled = true;  // the decode kernels match the CPU kernels' int8 arithmetic, so on by default
-    uint64_t min_work_qmoe = 1ull << 30;
-    uint64_t min_work_packed_q4 = 1ull << 27;
-    uint64_t min_work_packed_q5 = 1ull << 24;
-    uint64_t min_work_packed_q8 = 1ull << 24;
-    uint64_t min_work_decode_q5 = 3ull << 23;
+    // Work floors (m * n * k) below which the host should keep a product on the CPU. The reference's defaults
+    // (backend/cuda.zig:118-159) are the crossovers of an RTX 5000 Ada laptop GPU against its CPU arms; these are the
+    // crossovers measured on B200: the blocking host-buffer call (about 25 us at decode sizes, resident weights)
+    // against the all-core SIMD CPU arm, rounded up to the next power of two with a factor of two to spare.
+    uint64_t min_work_qmoe = 1ull << 24;        // grouped MoE GEMM over staged panels (reference 2^30)
+    uint64_t min_work_dense = 1ull << 22;       // prefill-sized dense products against the plain CPU arm (reference 2^30 via the QMoE floor)
+    uint64_t min_work_packed_q4 = 1ull << 22;   // ... against the packed (x8) CPU arms (reference 2^27)
+    uint64_t min_work_packed_q5 = 1ull << 22;   // (reference 2^24)
+    uint64_t min_work_packed_q8 = 1ull << 22;   // (reference 2^24)
+    uint64_t min_work_decode = 1ull << 20;      // decode products, every format (the reference has no floor except for Q5_K)
+    uint64_t min_work_decode_q5 = 1ull << 20;   // (reference 3 * 2^23)
     uint64_t qmoe_min_fill_pct = 50;
     size_t vram_budget_env = 0;
 };
@@ -105,6 +111,8 @@ static void ensure_config() {
         env_u64("FUCINA_GPU_MIN_WORK_DENSE_Q5", &g_cfg.min_work_packed_q5);
         env_u64("FUCINA_GPU_MIN_WORK_DENSE_Q8", &g_cfg.min_work_packed_q8);
         env_u64("FUCINA_GPU_MIN_WORK_DECODE_Q5", &g_cfg.min_work_decode_q5);
+        env_u64("FUCINA_GPU_MIN_WORK_GEMV", &g_cfg.min_work_decode);
+        env_u64("FUCINA_GPU_MIN_WORK", &g_cfg.min_work_dense);
         env_u64("FUCINA_GPU_QMOE_MIN_FILL", &g_cfg.qmoe_min_fill_pct);
         if (env_u64("FUCINA_GPU_VRAM_BUDGET", &v)) g_cfg.vram_budget_env = (size_t)v;
     });
@@ -1305,7 +1313,7 @@ int fq_should_use_gpu_dense_quant(int fmt, uint64_t total_work) {
     uint64_t floor_;
     switch (fmt) {
         case FQ_Q5_K: floor_ = g_cfg.min_work_packed_q5; break;
-        case FQ_Q4_K: case FQ_Q8_0: floor_ = g_cfg.min_work_qmoe; break;
+        case FQ_Q4_K: case FQ_Q8_0: floor_ = g_cfg.min_work_dense; break;
         default: floor_ = g_cfg.min_work_packed_q8; break;
     }
     return gate(g_cfg.gpu_enabled && format_info(fmt).block_elems && total_work >= floor_);
@@ -1323,9 +1331,8 @@ int fq_should_use_gpu_dense_quant_packed(int fmt, uint64_t total_work) {
 int fq_should_use_gpu_quant_decode(int fmt, size_t m, size_t n, size_t k) {
     ensure_config();
     if (!g_cfg.gpu_enabled || !g_cfg.decode_enabled || !format_info(fmt).block_elems) return 0;
-    if (fmt != FQ_Q5_K) return 1;
     const unsigned __int128 work = (unsigned __int128)m * n * k;
-    return gate(work >= g_cfg.min_work_decode_q5);
+    return gate(work >= (fmt == FQ_Q5_K ? g_cfg.min_work_decode_q5 : g_cfg.min_work_decode));
 }
 void fq_set_min_work_qmoe_for_test(uint64_t v) {
     ensure_config();

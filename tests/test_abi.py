@@ -58,33 +58,37 @@ def test_block_geometry(lib):
     assert (F.BLOCK[F.Q8_0], F.BLOCK[F.Q4_K], F.BLOCK[F.Q5_K], F.BLOCK[F.TQ2_0]) == ((32, 34), (256, 144), (256, 176), (256, 66))
 
 
-def test_gates_follow_reference_defaults(lib):
-    # src/backend/cuda.zig:118-159 defaults, :2494-2554 predicates
+def test_gates_keep_the_reference_predicates_with_b200_floors(lib):
+    # the predicates of src/backend/cuda.zig:2494-2554 with the work floors measured on B200 (the reference's
+    # defaults, :118-159, are the crossovers of a laptop GPU): blocking host-buffer call against the all-core CPU arm
     from fucina_b200 import formats as F
 
-    assert lib.fq_should_use_gpu_qmoe(1 << 30) == 1
-    assert lib.fq_should_use_gpu_qmoe((1 << 30) - 1) == 0
-    assert lib.fq_should_use_gpu_dense_quant_packed(F.Q4_K, 1 << 27) == 1
-    assert lib.fq_should_use_gpu_dense_quant_packed(F.Q4_K, (1 << 27) - 1) == 0
-    assert lib.fq_should_use_gpu_dense_quant_packed(F.Q5_K, 1 << 24) == 1
-    assert lib.fq_should_use_gpu_dense_quant_packed(F.Q8_0, (1 << 24) - 1) == 0
-    assert lib.fq_should_use_gpu_dense_quant(F.Q4_K, 1 << 30) == 1
-    assert lib.fq_should_use_gpu_dense_quant(F.Q4_K, 1 << 29) == 0
+    assert lib.fq_should_use_gpu_qmoe(1 << 24) == 1
+    assert lib.fq_should_use_gpu_qmoe((1 << 24) - 1) == 0
+    for fmt in (F.Q4_K, F.Q5_K, F.Q8_0):
+        assert lib.fq_should_use_gpu_dense_quant_packed(fmt, 1 << 22) == 1
+        assert lib.fq_should_use_gpu_dense_quant_packed(fmt, (1 << 22) - 1) == 0
+        assert lib.fq_should_use_gpu_dense_quant(fmt, 1 << 22) == 1
+        assert lib.fq_should_use_gpu_dense_quant(fmt, (1 << 22) - 1) == 0
     assert lib.fq_should_use_gpu_dense_quant(F.Q6_K, 1 << 40) == 0  # format not served
+    # a 7B-class prefill product and the decode stack's smallest product pass; the reference's defaults declined both
+    assert lib.fq_should_use_gpu_dense_quant(F.Q4_K, 32 * 4096 * 4096) == 1
+    assert lib.fq_should_use_gpu_quant_decode(F.Q5_K, 1, 4096, 4096) == 1
     # fill gate: rows*100 >= tiles*32*50
     assert lib.fq_qmoe_fill_acceptable(16, 1) == 1
     assert lib.fq_qmoe_fill_acceptable(15, 1) == 0
     assert lib.fq_qmoe_fill_acceptable(10, 0) == 0
-    # decode gate: Q5_K needs 3<<23 of work, others pass
-    assert lib.fq_should_use_gpu_quant_decode(F.Q4_K, 1, 64, 256) == 1
-    assert lib.fq_should_use_gpu_quant_decode(F.Q5_K, 1, 4096, 4096) == 0
-    assert lib.fq_should_use_gpu_quant_decode(F.Q5_K, 1, 6144, 4096) == 1
-    lib.fq_set_decode_for_test(0)
+    # decode gate: m*n*k >= 2^20 for every format (a 24 us call does not pay for less)
+    assert lib.fq_should_use_gpu_quant_decode(F.Q4_K, 1, 1024, 1024) == 1
     assert lib.fq_should_use_gpu_quant_decode(F.Q4_K, 1, 64, 256) == 0
+    assert lib.fq_should_use_gpu_quant_decode(F.Q5_K, 1, 512, 1024) == 0
+    assert lib.fq_should_use_gpu_quant_decode(F.Q5_K, 4, 512, 512) == 1
+    lib.fq_set_decode_for_test(0)
+    assert lib.fq_should_use_gpu_quant_decode(F.Q4_K, 1, 4096, 4096) == 0
     lib.fq_set_decode_for_test(1)
     lib.fq_set_min_work_qmoe_for_test(1)
     assert lib.fq_should_use_gpu_qmoe(1) == 1
-    lib.fq_set_min_work_qmoe_for_test(1 << 30)
+    lib.fq_set_min_work_qmoe_for_test(1 << 24)
 
 
 def test_argument_rules_decline_before_touching_a_device(lib):
