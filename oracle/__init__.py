@@ -14,8 +14,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 Q8_0, Q6_K, Q4_K, Q5_K = 0, 1, 2, 3
 TQ2_0, TQ2_0_FOLDED, Q2_0 = 16, 17, 18
-FORMATS = {"q8_0": Q8_0, "q4_k": Q4_K, "q5_k": Q5_K, "tq2_0": TQ2_0, "tq2_0_folded": TQ2_0_FOLDED, "q2_0": Q2_0}
-K_MULTIPLE = {Q8_0: 32, Q4_K: 256, Q5_K: 256, TQ2_0: 256, TQ2_0_FOLDED: 256, Q2_0: 128}
+FORMATS = {"q8_0": Q8_0, "q6_k": Q6_K, "q4_k": Q4_K, "q5_k": Q5_K, "tq2_0": TQ2_0, "tq2_0_folded": TQ2_0_FOLDED, "q2_0": Q2_0}
+K_MULTIPLE = {Q8_0: 32, Q6_K: 256, Q4_K: 256, Q5_K: 256, TQ2_0: 256, TQ2_0_FOLDED: 256, Q2_0: 128}
 
 _lib = None
 

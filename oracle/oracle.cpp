@@ -40,6 +40,7 @@ inline uint16_t f2h(float x) {
 struct BlockQ8_0 { uint16_t d; int8_t qs[32]; };
 struct BlockQ4_K { uint16_t dm[2]; uint8_t scales[12]; uint8_t qs[128]; };
 struct BlockQ5_K { uint16_t dm[2]; uint8_t scales[12]; uint8_t qh[32]; uint8_t qs[128]; };
+struct BlockQ6_K { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; uint16_t d; };  // dtype.zig:141-146
 struct BlockQ8_K { float d; int8_t qs[256]; int16_t bsums[16]; };
 struct BlockTQ2_0 { uint8_t qs[64]; uint16_t d; };
 struct BlockTQ2_0Folded { uint8_t qs[128]; uint16_t d; };
@@ -48,6 +49,7 @@ struct BlockQ2_0 { uint16_t d; uint8_t qs[32]; };
 static_assert(sizeof(BlockQ8_0) == 34, "");
 static_assert(sizeof(BlockQ4_K) == 144, "");
 static_assert(sizeof(BlockQ5_K) == 176, "");
+static_assert(sizeof(BlockQ6_K) == 210, "");
 static_assert(sizeof(BlockQ8_K) == 292, "");
 static_assert(sizeof(BlockTQ2_0) == 66, "");
 static_assert(sizeof(BlockTQ2_0Folded) == 130, "");
@@ -325,6 +327,138 @@ void dequantize_block_q5_k(float* dst, const BlockQ5_K* src) {
 }
 
 // ---- ternary (ternary.zig:79-144, ptqtp.zig:684-697, cold.zig:651-670) -----
+// ---- Q6_K (backend/quant/q6_k.zig) ------------------------------------------
+// q6_k.zig:1239-1259: element `index` of a block: chunk of 128, section of 32; low nibble of ql for sections 0-1,
+// high nibble for 2-3; two bits of qh; value minus 32. One i8 scale per 16 elements.
+inline int8_t q6k_value(const BlockQ6_K* w, int index) {
+    const int chunk = index / 128, local = index % 128, section = local / 32, l = local % 32;
+    const int ql_index = chunk * 64 + ((section == 1 || section == 3) ? 32 + l : l);
+    const int low = (section < 2) ? (w->ql[ql_index] & 0x0f) : (w->ql[ql_index] >> 4);
+    const int high = (w->qh[chunk * 32 + l] >> (section * 2)) & 0x03;
+    return (int8_t)((low | (high << 4)) - 32);
+}
+inline int q6k_scale_index(int index) {
+    const int chunk = index / 128, local = index % 128, section = local / 32, l = local % 32;
+    return chunk * 8 + section * 2 + l / 16;
+}
+// q6_k.zig:1159-1167: d * f32(scale) * f32(q), left to right.
+void dequantize_block_q6_k(float* dst, const BlockQ6_K* src) {
+    const float d = h2f(src->d);
+    for (int i = 0; i < 256; ++i) dst[i] = d * (float)src->scales[q6k_scale_index(i)] * (float)q6k_value(src, i);
+}
+// q8k.zig:665-733 `makeQxQuants` without an external weight table (qw = null): the rmse_type-weighted scale
+// search ggml's make_qx_quants does. n elements, levels in [-nmax, nmax - 1] stored biased by nmax.
+float make_qx_quants(int nmax, const float* x, int n, int8_t* L, int rmse_type_in) {
+    auto weight = [](int rmse_type, float v) -> float {
+        switch (rmse_type) {
+            case 1: return v * v;
+            case 2: return 1.0f;
+            case 3: return std::fabs(v);
+            default: return std::sqrt(std::fabs(v));
+        }
+    };
+    float max = 0, amax = 0;
+    for (int i = 0; i < n; ++i) {
+        const float ax = std::fabs(x[i]);
+        if (ax > amax) {
+            amax = ax;
+            max = x[i];
+        }
+    }
+    if (amax < 1e-15f) {  // group_max_eps: all zero
+        for (int i = 0; i < n; ++i) L[i] = 0;
+        return 0.0f;
+    }
+    const float nmax_f = (float)nmax;
+    float iscale = -nmax_f / max;
+    int rmse_type = rmse_type_in;
+    if (rmse_type == 0) {
+        for (int i = 0; i < n; ++i) {
+            const int l = nearest_int(iscale * x[i]);
+            L[i] = (int8_t)(nmax + std::max(-nmax, std::min(nmax - 1, l)));
+        }
+        return 1 / iscale;
+    }
+    bool return_early = false;
+    if (rmse_type < 0) {
+        rmse_type = -rmse_type;
+        return_early = true;
+    }
+    float sumlx = 0, suml2 = 0;
+    for (int i = 0; i < n; ++i) {
+        int l = nearest_int(iscale * x[i]);
+        l = std::max(-nmax, std::min(nmax - 1, l));
+        L[i] = (int8_t)(l + nmax);
+        const float w = weight(rmse_type, x[i]);
+        const float lf = (float)l;
+        sumlx += w * x[i] * lf;
+        suml2 += w * lf * lf;
+    }
+    float scale = (suml2 != 0) ? sumlx / suml2 : 0.0f;
+    if (return_early) return (suml2 > 0) ? 0.5f * (scale + 1 / iscale) : 1 / iscale;
+    float best = scale * sumlx;
+    for (int is = -9; is <= 9; ++is) {
+        if (is == 0) continue;
+        iscale = -(nmax_f + 0.1f * (float)is) / max;
+        sumlx = 0;
+        suml2 = 0;
+        for (int i = 0; i < n; ++i) {
+            int l = nearest_int(iscale * x[i]);
+            l = std::max(-nmax, std::min(nmax - 1, l));
+            const float w = weight(rmse_type, x[i]);
+            const float lf = (float)l;
+            sumlx += w * x[i] * lf;
+            suml2 += w * lf * lf;
+        }
+        if (suml2 > 0 && sumlx * sumlx > best * suml2) {
+            for (int i = 0; i < n; ++i) {
+                const int l = nearest_int(iscale * x[i]);
+                L[i] = (int8_t)(nmax + std::max(-nmax, std::min(nmax - 1, l)));
+            }
+            scale = sumlx / suml2;
+            best = scale * sumlx;
+        }
+    }
+    return scale;
+}
+// q6_k.zig:1172-1229, the port of ggml's quantize_row_q6_K_ref.
+void quantize_block_q6_k(BlockQ6_K* dst, const float* src) {
+    int8_t L[256];
+    float scales[16];
+    float max_scale = 0, max_abs_scale = 0;
+    for (int ib = 0; ib < 16; ++ib) {
+        const float scale = make_qx_quants(32, src + 16 * ib, 16, L + 16 * ib, 1);
+        scales[ib] = scale;
+        const float abs_scale = std::fabs(scale);
+        if (abs_scale > max_abs_scale) {
+            max_abs_scale = abs_scale;
+            max_scale = scale;
+        }
+    }
+    if (max_abs_scale < 1e-15f) {
+        std::memset(dst, 0, sizeof *dst);
+        return;
+    }
+    const float iscale = -128.0f / max_scale;
+    dst->d = f2h(1 / iscale);
+    for (int ib = 0; ib < 16; ++ib) dst->scales[ib] = (int8_t)std::min(127, nearest_int(iscale * scales[ib]));
+    for (int j = 0; j < 16; ++j) {
+        const float d = h2f(dst->d) * (float)dst->scales[j];
+        if (d == 0) continue;  // keeps the make_qx_quants levels, like ggml
+        for (int i = 0; i < 16; ++i) {
+            const int l = nearest_int(src[16 * j + i] / d);
+            L[16 * j + i] = (int8_t)(std::max(-32, std::min(31, l)) + 32);
+        }
+    }
+    for (int j = 0, ql_offset = 0, qh_offset = 0; j < 256; j += 128, ql_offset += 64, qh_offset += 32)
+        for (int l = 0; l < 32; ++l) {
+            const uint8_t q1 = (uint8_t)L[j + l], q2 = (uint8_t)L[j + l + 32], q3 = (uint8_t)L[j + l + 64], q4 = (uint8_t)L[j + l + 96];
+            dst->ql[ql_offset + l] = (uint8_t)((q1 & 0x0f) | ((q3 & 0x0f) << 4));
+            dst->ql[ql_offset + l + 32] = (uint8_t)((q2 & 0x0f) | ((q4 & 0x0f) << 4));
+            dst->qh[qh_offset + l] = (uint8_t)((q1 >> 4) | ((q2 >> 4) << 2) | ((q3 >> 4) << 4) | ((q4 >> 4) << 6));
+        }
+}
+
 inline int tq2_code(const BlockTQ2_0* b, int e) {
     const int hg = e / 128, n = (e % 128) / 32, m = e % 32;
     return (b->qs[hg * 32 + m] >> (2 * n)) & 3;
@@ -433,6 +567,20 @@ inline float dot_q5_k_q8_k(const BlockQ5_K* w, const BlockQ8_K* a) {
     const float d = h2f(w->dm[0]) * a->d;
     const float dmin = h2f(w->dm[1]) * a->d;
     return d * (float)iscale - dmin * (float)imin;
+}
+// q6_k.zig:617-631 `dotQ6_KQ8_KScalar` (the SIMD tiers give the same integer total and the same f32 epilogue).
+inline float dot_q6_k_q8_k(const BlockQ6_K* w, const BlockQ8_K* a) {
+    int32_t iacc = 0;
+    for (int group = 0; group < 16; ++group) {
+        int32_t dot = 0;
+        for (int i = 0; i < 16; ++i) {
+            const int feature = group * 16 + i;
+            dot += (int32_t)q6k_value(w, feature) * (int32_t)a->qs[feature];
+        }
+        iacc += dot * (int32_t)w->scales[q6k_scale_index(group * 16)];
+    }
+    const float d = h2f(w->d) * a->d;
+    return (float)iacc * d;
 }
 inline int32_t bsum_total(const BlockQ8_K* a) {
     int32_t t = 0;
@@ -547,6 +695,7 @@ size_t row_bytes(int fmt, size_t k) {
         case Q8_0: return k / 32 * 34;
         case Q4_K: return k / 256 * 144;
         case Q5_K: return k / 256 * 176;
+        case Q6_K: return k / 256 * 210;
         case TQ2_0: return k / 256 * 66;
         case TQ2_0_FOLDED: return k / 256 * 130;
         case Q2_0: return k / 128 * 34;
@@ -575,6 +724,12 @@ float row_dot(int fmt, const uint8_t* wrow, const void* arow, size_t k) {
             const BlockQ5_K* w = (const BlockQ5_K*)wrow;
             const BlockQ8_K* a = (const BlockQ8_K*)arow;
             for (size_t b = 0; b < k / 256; ++b) acc += dot_q5_k_q8_k(&w[b], &a[b]);
+            return acc;
+        }
+        case Q6_K: {  // q6_k.zig:109-148 `matmulQ6_KRhsTile`: blocks ascending
+            const BlockQ6_K* w = (const BlockQ6_K*)wrow;
+            const BlockQ8_K* a = (const BlockQ8_K*)arow;
+            for (size_t b = 0; b < k / 256; ++b) acc += dot_q6_k_q8_k(&w[b], &a[b]);
             return acc;
         }
         case TQ2_0: {
@@ -620,6 +775,9 @@ void dequantize_row(int fmt, float* dst, const uint8_t* wrow, size_t k) {
             break;
         case Q5_K:
             for (size_t b = 0; b < k / 256; ++b) dequantize_block_q5_k(dst + b * 256, (const BlockQ5_K*)wrow + b);
+            break;
+        case Q6_K:
+            for (size_t b = 0; b < k / 256; ++b) dequantize_block_q6_k(dst + b * 256, (const BlockQ6_K*)wrow + b);
             break;
         case TQ2_0: dequantize_row_tq2_0(dst, (const BlockTQ2_0*)wrow, k); break;
         case TQ2_0_FOLDED:
@@ -675,6 +833,9 @@ int orc_quantize_rows(int fmt, const float* src, size_t n, size_t k, void* dst) 
                 break;
             case Q5_K:
                 for (size_t b = 0; b < k / 256; ++b) quantize_block_q5_k((BlockQ5_K*)out + b, in + b * 256);
+                break;
+            case Q6_K:
+                for (size_t b = 0; b < k / 256; ++b) quantize_block_q6_k((BlockQ6_K*)out + b, in + b * 256);
                 break;
             case TQ2_0: quantize_row_tq2_0((BlockTQ2_0*)out, in, k); break;
             case Q2_0: quantize_row_q2_0((BlockQ2_0*)out, in, k); break;
@@ -824,6 +985,7 @@ float orc_block_dot(int fmt, const void* wblock, const void* ablock) {
         case Q8_0: return dot_q8_0_q8_0((const BlockQ8_0*)ablock, (const BlockQ8_0*)wblock);
         case Q4_K: return dot_q4_k_q8_k((const BlockQ4_K*)wblock, (const BlockQ8_K*)ablock);
         case Q5_K: return dot_q5_k_q8_k((const BlockQ5_K*)wblock, (const BlockQ8_K*)ablock);
+        case Q6_K: return dot_q6_k_q8_k((const BlockQ6_K*)wblock, (const BlockQ8_K*)ablock);
         case TQ2_0: return dot_tq2_0_q8_k((const BlockTQ2_0*)wblock, (const BlockQ8_K*)ablock);
         case TQ2_0_FOLDED: return dot_folded_q8_k((const BlockTQ2_0Folded*)wblock, (const BlockQ8_K*)ablock);
     }

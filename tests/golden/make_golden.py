@@ -8,8 +8,8 @@ Two fixture files are written:
   hold for this path, read as text from its test files (only data tables are
   extracted, no code):
     src/backend/quant/encode_golden_test.zig  input_bits (8x256 f32 bit
-        patterns), q4_k_golden (8x144 B), q5_k_golden (8x176 B): ggml
-        quantize_row_q4_K_ref / q5_K_ref outputs
+        patterns), q4_k_golden (8x144 B), q5_k_golden (8x176 B), q6_k_golden
+        (8x210 B): ggml quantize_row_q4_K_ref / q5_K_ref / q6_K_ref outputs
     src/backend/quant/cold_tests.zig  tq2_0_dequant_golden: TQ2_0 block bytes
         with ggml's dequantised f32 bit patterns
 * oracle_cases.npz -- small seeded cases run through the pinned oracle, used
@@ -41,6 +41,7 @@ def reference_goldens(ref: str) -> dict:
     bits = _table(enc, "pub const input_bits", 8).astype(np.uint32).reshape(8, 256)
     q4 = _table(enc, "pub const q4_k_golden", 2).astype(np.uint8).reshape(8, 144)
     q5 = _table(enc, "pub const q5_k_golden", 2).astype(np.uint8).reshape(8, 176)
+    q6 = _table(enc, "pub const q6_k_golden", 2).astype(np.uint8).reshape(8, 210)
     cold = open(os.path.join(ref, "src/backend/quant/cold_tests.zig")).read()
     i = cold.index("const tq2_0_dequant_golden")
     j = cold.index("};", i)
@@ -54,6 +55,7 @@ def reference_goldens(ref: str) -> dict:
         "input_bits": bits,
         "q4_k_golden": q4,
         "q5_k_golden": q5,
+        "q6_k_golden": q6,
         "tq2_0_bytes": tq_bytes.reshape(-1, 66),
         "tq2_0_expected_bits": tq_bits.reshape(-1, 256),
     }
@@ -65,7 +67,7 @@ def oracle_cases() -> dict:
     out = {}
     rng = np.random.default_rng(20251)
     # the reference's GPU parity shapes (backend/cuda.zig:3084-3088), k in blocks of 256
-    for name, fmt in (("q8_0", oracle.Q8_0), ("q4_k", oracle.Q4_K), ("q5_k", oracle.Q5_K)):
+    for name, fmt in (("q8_0", oracle.Q8_0), ("q4_k", oracle.Q4_K), ("q5_k", oracle.Q5_K), ("q6_k", oracle.Q6_K)):
         n, k, m = 36, 512, 4
         w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
         a = rng.standard_normal((m, k)).astype(np.float32)
@@ -89,7 +91,9 @@ def oracle_cases() -> dict:
 
 
 def main() -> None:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FUCINA_REFERENCE", "")
+    if not ref or not os.path.isdir(ref):
+        sys.exit("usage: make_golden.py /path/to/the/reference checkout (or FUCINA_REFERENCE=...)")
     np.savez_compressed(os.path.join(HERE, "reference_goldens.npz"), **reference_goldens(ref))
     np.savez_compressed(os.path.join(HERE, "oracle_cases.npz"), **oracle_cases())
     print("wrote", os.listdir(HERE))

@@ -43,7 +43,7 @@ def make_weights(fmt_name: str, n: int, k: int, seed: int):
 
     rng = np.random.default_rng(seed)
     fmt = oracle.FORMATS[fmt_name]
-    if fmt_name in ("q8_0", "q4_k", "q5_k"):
+    if fmt_name in ("q8_0", "q4_k", "q5_k", "q6_k"):
         w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
         return oracle.quantize_rows(fmt, w)
     trits = rng.integers(-1, 2, size=(n, k)).astype(np.int8)

@@ -29,6 +29,42 @@ def test_q5_k_encoder_matches_ggml_golden_bytes(goldens):
     assert np.array_equal(got, goldens["q5_k_golden"])
 
 
+def test_q6_k_encoder_matches_ggml_golden_bytes(goldens):
+    # encode_golden_test.zig:515 q6_k_golden: ggml quantize_row_q6_K_ref on the same eight input vectors
+    x = goldens["input_bits"].view(np.float32)
+    got = oracle.quantize_rows(oracle.Q6_K, x)
+    assert np.array_equal(got, goldens["q6_k_golden"])
+
+
+def test_q6_k_pattern_block_dot_equals_dense_dot():
+    # q6_k.zig:1279-1301: fillQ6KPattern against fillQ8KPattern; dotDense(dequant w, dequant a) == dotQ6_KQ8_K exactly
+    blk = np.zeros(210, np.int64)  # assembled in wide integers, narrowed to bytes below
+    scales = ((np.arange(16) % 5) - 2).astype(np.int8)
+    scales[0] = 1
+    blk[192:208] = scales.view(np.uint8)
+    blk[208:210] = np.array([f2h_bits(1.0)], np.uint16).view(np.uint8)
+    for i in range(256):  # setQ6KValue (q6_k.zig:1261-1277)
+        enc = ((i % 23) - 11) + 32
+        chunk, local = divmod(i, 128)
+        section, l = divmod(local, 32)
+        qi = chunk * 64 + (32 + l if section in (1, 3) else l)
+        if section < 2:
+            blk[qi] = (blk[qi] & 0xF0) | (enc & 0x0F)
+        else:
+            blk[qi] = (blk[qi] & 0x0F) | ((enc & 0x0F) << 4)
+        hi = 128 + chunk * 32 + l
+        blk[hi] = (blk[hi] & ~(0x03 << (section * 2)) & 0xFF) | (((enc >> 4) & 0x03) << (section * 2))
+    blk = blk.astype(np.uint8)
+    a = _q8k_pattern()
+    dense_w = oracle.dequantize_rows(oracle.Q6_K, blk.reshape(1, -1), 256).reshape(-1)
+    assert np.array_equal(dense_w[:16], (np.arange(16) - 11).astype(np.float32))  # the first group carries scale 1
+    dense_a = a[4:260].view(np.int8).astype(np.float32)
+    want = np.float32(0)
+    for wv, av in zip(dense_w, dense_a):
+        want = np.float32(want + np.float32(wv * av))
+    assert oracle.block_dot(oracle.Q6_K, blk, a) == want
+
+
 def test_golden_inputs_follow_documented_generators(goldens):
     # encode_golden_test.zig:16-31 documents the 8 input vectors; spot-check the
     # ones with closed forms so a parsing slip cannot go unnoticed.
@@ -56,7 +92,7 @@ def _mix32(s):
     return s
 
 
-@pytest.mark.parametrize("fmt,bound", [(oracle.Q4_K, 0.055), (oracle.Q5_K, 0.030)])
+@pytest.mark.parametrize("fmt,bound", [(oracle.Q4_K, 0.055), (oracle.Q5_K, 0.030), (oracle.Q6_K, 0.016)])
 def test_round_trip_rmse_bounds(fmt, bound):
     # encode_golden_test.zig:1104-1140: U[-1,1] rows from the mix32 generator
     n = 1024
