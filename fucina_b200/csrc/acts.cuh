@@ -34,6 +34,7 @@ __host__ __device__ inline ActLayout act_layout(int fmt) {
         case FQ_Q8_0: return {16, 1, 32};
         case FQ_Q4_K: return {32, 2, 256};
         case FQ_Q5_K: return {32, 2, 256};
+        case FQ_Q6_K: return {32, 2, 256};
         case FQ_TQ2_0: return {64, 4, 256};
         case FQ_TQ2_0_FOLDED: return {32, 2, 256};
         case FQ_Q2_0: return {64, 4, 32};
@@ -69,6 +70,15 @@ __host__ __device__ inline void act_pos(int fmt, int e, int& c, int& s, int& i) 
             c = blk * 8 + (sub >> 1) * 2 + h;
             s = sub & 1;
             i = e & 15;
+            return;
+        }
+        case FQ_Q6_K: {
+            // chunk = 16 ql bytes: their low nibbles are 16 elements of section h32 (0 or 1) of a 128-element half
+            // block, their high nibbles the same 16 positions of section h32 + 2 (q6_k.zig:1239-1259)
+            const int blk = e >> 8, r = e & 255, c2 = r >> 7, sec = (r >> 5) & 3, l = r & 31;
+            c = blk * 8 + c2 * 4 + (sec & 1) * 2 + (l >> 4);
+            s = sec >> 1;
+            i = l & 15;
             return;
         }
         case FQ_TQ2_0: {

@@ -22,6 +22,7 @@ __host__ __device__ inline FormatInfo format_info(int fmt) {
         case FQ_Q8_0: return {32, 34, 32, 2};
         case FQ_Q4_K: return {256, 144, 144, 0};
         case FQ_Q5_K: return {256, 176, 176, 0};
+        case FQ_Q6_K: return {256, 210, 208, 2};  // ql[128] qh[64] scales[16] | d: the 208 payload bytes are 13 aligned chunks
         case FQ_TQ2_0: return {256, 66, 64, 2};
         case FQ_TQ2_0_FOLDED: return {256, 130, 128, 2};
         case FQ_Q2_0: return {128, 34, 32, 2};
@@ -31,7 +32,7 @@ __host__ __device__ inline FormatInfo format_info(int fmt) {
 
 // Device weight layout ("gpu_formats"). K-quant rows are the GGUF rows
 // unchanged (their 144/176-byte blocks are already 16-byte multiples). The
-// 34/66/130-byte formats are split per row into a payload plane followed by
+// 34/66/130-byte formats and Q6_K (210) are split per row into a payload plane followed by
 // an f16 scale plane so every payload chunk is 16-byte aligned:
 //   row = [ qs of block 0 | qs of block 1 | ... ][ d0 d1 ... ] padded to 16 B.
 //

@@ -114,6 +114,7 @@ __device__ __forceinline__ void scale_min_one(const uint8_t* q, int j, int& sc, 
 //   Q8_0   f32(q) * d                                  (q8k.zig:104-112)
 //   Q4_K   d*f32(sc)*f32(q) - dmin*f32(mn)             (q4_k.zig:1954-1972)
 //   Q5_K   same with q = nibble + 16*bit               (q5_k.zig:1154-1167, :1259-1264)
+//   Q6_K   d*f32(scale)*f32(q6 - 32)                   (q6_k.zig:1159-1167)
 //   TQ2_0  f32(code-1) * d                             (cold.zig:651-670)
 //   folded d * (f32(cu) - 4)                           (ternary.zig:850-876)
 //   Q2_0   f32(q-1) * d                                (cold.zig:289-301)
@@ -145,6 +146,17 @@ __device__ float dequant_element(const uint8_t* row, size_t ustride, int fmt, in
             const uint8_t byte = b[48 + (s >> 1) * 32 + i];
             const int q = ((s & 1) ? (byte >> 4) : (byte & 15)) + (((b[16 + i] >> s) & 1) ? 16 : 0);
             return d * (float)sc * (float)q - dmin * (float)mn;
+        }
+        case FQ_Q6_K: {  // d * f32(scale) * f32(q), left to right (q6_k.zig:1159-1167, :1239-1259)
+            const int blk = e >> 8, r = e & 255, c2 = r >> 7, sec = (r >> 5) & 3, l = r & 31;
+            const uint8_t* b = row + (size_t)blk * 208;
+            const uint8_t qlb = b[c2 * 64 + (sec & 1) * 32 + l];
+            const int low = (sec < 2) ? (qlb & 0x0f) : (qlb >> 4);
+            const int high = (b[128 + c2 * 32 + l] >> (sec * 2)) & 3;
+            const int q = (low | (high << 4)) - 32;
+            const int sc = (int8_t)b[192 + c2 * 8 + sec * 2 + (l >> 4)];
+            const uint16_t d = reinterpret_cast<const uint16_t*>(row + (size_t)(k >> 8) * 208)[blk];
+            return h2f(d) * (float)sc * (float)q;
         }
         case FQ_TQ2_0: {
             const int blk = e >> 8, r = e & 255, hg = r >> 7, n = (r >> 5) & 3, m = r & 31;
@@ -231,7 +243,8 @@ __global__ void quantize_acts_layout_kernel(const float* __restrict__ a, const i
 #pragma unroll
         for (int j = 0; j < 8; ++j) sum += q[j];
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);  // the Q8_K bsum of this 16-element group
-        if (fmt == FQ_Q4_K || fmt == FQ_Q5_K) {
+        if (fmt == FQ_Q4_K || fmt == FQ_Q5_K || fmt == FQ_Q6_K) {
+            // (Q6_K levels are re-centred to signed bytes in the kernel, which needs no sums; the word is kept defined)
             if ((lane & 1) == 0) reinterpret_cast<int16_t*>(aaux)[c * 2 + s] = (int16_t)sum;
         } else if (fmt == FQ_TQ2_0) {
             // chunk = the four crumb lanes n (lane bits 2,3) of one (half-group, half)
@@ -351,6 +364,8 @@ cudaError_t launch_quantize_acts_natural(const float* a, int m, int k, bool q8k,
 // ===========================================================================
 // Weight encoders (raw GGUF blocks out, byte-identical to the CPU encoders).
 // ===========================================================================
+__device__ __forceinline__ int max_i(int a, int b) { return a > b ? a : b; }
+__device__ __forceinline__ int min_i(int a, int b) { return a < b ? a : b; }
 __device__ __forceinline__ int nearest_int_dev(float fval) {
     const float val = fval + 12582912.0f;
     return (__float_as_int(val) & 0x007fffff) - 0x00400000;
@@ -510,6 +525,119 @@ __global__ void __launch_bounds__(128) quantize_kquant_kernel(const float* __res
     }
 }
 
+// q8k.zig:665-733 `makeQxQuants` for one 16-element group with rmse_type 1 (weights v*v), nmax 32: the scale search of
+// ggml's make_qx_quants. Levels come back biased by nmax.
+__device__ float make_qx_quants16_dev(const float* x, int8_t* L) {
+    constexpr int nmax = 32;
+    float max = 0, amax = 0;
+    for (int i = 0; i < 16; ++i) {
+        const float ax = fabsf(x[i]);
+        if (ax > amax) {
+            amax = ax;
+            max = x[i];
+        }
+    }
+    if (amax < 1e-15f) {
+        for (int i = 0; i < 16; ++i) L[i] = 0;
+        return 0.0f;
+    }
+    float iscale = -32.0f / max;
+    float sumlx = 0, suml2 = 0;
+    for (int i = 0; i < 16; ++i) {
+        int l = nearest_int_dev(iscale * x[i]);
+        l = max_i(-nmax, min_i(nmax - 1, l));
+        L[i] = (int8_t)(l + nmax);
+        const float w = x[i] * x[i];
+        const float lf = (float)l;
+        sumlx += w * x[i] * lf;
+        suml2 += w * lf * lf;
+    }
+    float scale = (suml2 != 0) ? sumlx / suml2 : 0.0f;
+    float best = scale * sumlx;
+    for (int is = -9; is <= 9; ++is) {
+        if (is == 0) continue;
+        iscale = -(32.0f + 0.1f * (float)is) / max;
+        sumlx = 0;
+        suml2 = 0;
+        for (int i = 0; i < 16; ++i) {
+            int l = nearest_int_dev(iscale * x[i]);
+            l = max_i(-nmax, min_i(nmax - 1, l));
+            const float w = x[i] * x[i];
+            const float lf = (float)l;
+            sumlx += w * x[i] * lf;
+            suml2 += w * lf * lf;
+        }
+        if (suml2 > 0 && sumlx * sumlx > best * suml2) {
+            for (int i = 0; i < 16; ++i) {
+                const int l = nearest_int_dev(iscale * x[i]);
+                L[i] = (int8_t)(nmax + max_i(-nmax, min_i(nmax - 1, l)));
+            }
+            scale = sumlx / suml2;
+            best = scale * sumlx;
+        }
+    }
+    return scale;
+}
+
+// Q6_K (q6_k.zig:1172-1229, the port of ggml's quantize_row_q6_K_ref): sixteen threads per 256-element block,
+// one per 16-element group. 128 threads = 8 blocks.
+__global__ void __launch_bounds__(128) quantize_q6_k_kernel(const float* __restrict__ src, size_t nblocks, uint8_t* __restrict__ dst) {
+    __shared__ int8_t sL[8][256];
+    const int j = threadIdx.x & 15;
+    const int lb = threadIdx.x >> 4;
+    const size_t bi = blockIdx.x * (size_t)8 + lb;
+    const bool live = bi < nblocks;
+    const size_t bsafe = live ? bi : (nblocks - 1);
+    const float* xs = src + bsafe * 256 + j * 16;
+    float x[16];
+    for (int i = 0; i < 16; ++i) x[i] = xs[i];
+    int8_t* L = &sL[lb][j * 16];
+    const float scale = make_qx_quants16_dev(x, L);
+    // the scale of largest magnitude, the first one on ties (a strict > in the sequential walk)
+    float best_abs = fabsf(scale);
+    int best_j = j;
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, best_abs, o, 16);
+        const int oj = __shfl_xor_sync(0xffffffffu, best_j, o, 16);
+        if (oa > best_abs || (oa == best_abs && oj < best_j)) best_abs = oa, best_j = oj;
+    }
+    const float max_scale = __shfl_sync(0xffffffffu, scale, best_j, 16);
+    uint8_t* out = dst + bsafe * 210;
+    if (best_abs < 1e-15f) {
+        if (live)
+            for (int i = j; i < 105; i += 16) reinterpret_cast<uint16_t*>(out)[i] = 0;
+        return;  // the sixteen threads of a block leave together
+    }
+    const float iscale = -128.0f / max_scale;
+    const uint16_t dh = __half_as_ushort(__float2half_rn(1 / iscale));
+    const int sc = min_i(127, nearest_int_dev(iscale * scale));
+    const float d = h2f(dh) * (float)sc;
+    if (d != 0) {
+        for (int i = 0; i < 16; ++i) {
+            const int l = nearest_int_dev(x[i] / d);
+            L[i] = (int8_t)(max_i(-32, min_i(31, l)) + 32);
+        }
+    }
+    __syncwarp();
+    if (!live) return;
+    out[192 + j] = (uint8_t)(int8_t)sc;
+    if (j == 0) reinterpret_cast<uint16_t*>(out + 208)[0] = dh;
+    // thread j packs ql bytes j*8 .. j*8+7 and qh bytes j*4 .. j*4+3
+    const int8_t* LB = sL[lb];
+    for (int t = 0; t < 8; ++t) {
+        const int qb = j * 8 + t, c2 = qb >> 6, r = qb & 63, hi32 = r >> 5, l = r & 31;
+        const uint8_t qa = (uint8_t)LB[c2 * 128 + hi32 * 32 + l], qc = (uint8_t)LB[c2 * 128 + (hi32 + 2) * 32 + l];
+        out[qb] = (uint8_t)((qa & 0x0f) | ((qc & 0x0f) << 4));
+    }
+    for (int t = 0; t < 4; ++t) {
+        const int hb = j * 4 + t, c2 = hb >> 5, l = hb & 31;
+        const uint8_t q1 = (uint8_t)LB[c2 * 128 + l], q2 = (uint8_t)LB[c2 * 128 + 32 + l], q3 = (uint8_t)LB[c2 * 128 + 64 + l],
+                      q4 = (uint8_t)LB[c2 * 128 + 96 + l];
+        out[128 + hb] = (uint8_t)((q1 >> 4) | ((q2 >> 4) << 2) | ((q3 >> 4) << 4) | ((q4 >> 4) << 6));
+    }
+}
+
 // Q8_0 (q8k.zig:49-69), TQ2_0 (ternary.zig:79-144), Q2_0 (cold.zig:309-332):
 // one warp per 256 source elements.
 __global__ void quantize_simple_kernel(const float* __restrict__ src, size_t total, int fmt, uint8_t* __restrict__ dst) {
@@ -582,6 +710,9 @@ cudaError_t launch_quantize_weights(int fmt, const float* src, size_t n, size_t 
             quantize_kquant_kernel<false><<<grid, 128, 0, st>>>(src, nblocks, dst);
         else
             quantize_kquant_kernel<true><<<grid, 128, 0, st>>>(src, nblocks, dst);
+    } else if (fmt == FQ_Q6_K) {
+        const size_t nblocks = total / 256;
+        quantize_q6_k_kernel<<<(unsigned)((nblocks + 7) / 8), 128, 0, st>>>(src, nblocks, dst);
     } else {
         const size_t n256 = (total + 255) / 256;
         const unsigned grid = (unsigned)((n256 * 32 + 127) / 128);

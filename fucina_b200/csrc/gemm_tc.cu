@@ -420,6 +420,50 @@ struct Raw<FQ_Q8_0> {
 };
 
 template <>
+struct Raw<FQ_Q6_K> {
+    uint4 q0, q1, h0, h1;
+    float dsc0, dsc1;
+    int nib, shift;
+    // row = [per block: ql[128] qh[64] scales[16]][d: K/256 f16]. The 32 weights of (slab, half) are section
+    // sec = 2*(slab & 1) + half of the 128-element half block c2 = (slab & 3) >> 1: low (sec < 2) or high nibbles of
+    // ql[c2*64 + (sec & 1)*32 ..+32) with bits 2*sec, 2*sec+1 of qh[c2*32 ..+32) on top (q6_k.zig:1239-1259).
+    __device__ __forceinline__ void load(const DevWeights& w, const uint8_t* unit0, size_t, int ks, int h) {
+        const int blk = ks >> 2, p = ks & 3, c2 = p >> 1, sec = (p & 1) * 2 + h;
+        const uint8_t* b = unit0 + (size_t)blk * 208;
+        q0 = __ldg(reinterpret_cast<const uint4*>(b + c2 * 64 + h * 32));
+        q1 = __ldg(reinterpret_cast<const uint4*>(b + c2 * 64 + h * 32 + 16));
+        h0 = __ldg(reinterpret_cast<const uint4*>(b + 128 + c2 * 32));
+        h1 = __ldg(reinterpret_cast<const uint4*>(b + 128 + c2 * 32 + 16));
+        const uint16_t sc = __ldg(reinterpret_cast<const uint16_t*>(b + 192 + c2 * 8 + sec * 2));
+        const float d = h2f(__ldg(reinterpret_cast<const uint16_t*>(unit0 + (size_t)(w.k >> 8) * 208) + blk));
+        dsc0 = __fmul_rn(d, (float)(int8_t)(sc & 0xff));
+        dsc1 = __fmul_rn(d, (float)(int8_t)(sc >> 8));
+        nib = p & 1;
+        shift = 2 * sec;
+    }
+    __device__ __forceinline__ void load_header(uint32_t) {}
+    __device__ __forceinline__ void load_slab(uint32_t, int) {}
+    // d * f32(scale) * f32(q6 - 32) (q6_k.zig:1159-1167), exactly: the level goes into the mantissa of 128.0f,
+    // (128 + q6) - 160 is exact, and one rounded multiply by d*scale follows as in the reference
+    __device__ __forceinline__ void expand(int, int, uint32_t out[16]) const {
+        const uint32_t wq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint32_t hb[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+        const float2 one = make_float2(1.0f, 1.0f), c160 = make_float2(-160.0f, -160.0f), zero = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t v = ((nib ? (wq[j] >> 4) : wq[j]) & 0x0f0f0f0fu) | (((hb[j] >> shift) & 0x03030303u) << 4);
+            const float dsc = j < 4 ? dsc0 : dsc1;
+            const float2 a2 = make_float2(dsc, dsc);
+            const float2 x01 = make_float2(__uint_as_float(__byte_perm(v, 0x43000000u, 0x7044)), __uint_as_float(__byte_perm(v, 0x43000000u, 0x7144)));
+            const float2 x23 = make_float2(__uint_as_float(__byte_perm(v, 0x43000000u, 0x7244)), __uint_as_float(__byte_perm(v, 0x43000000u, 0x7344)));
+            const float2 w01 = __ffma2_rn(a2, __ffma2_rn(one, x01, c160), zero), w23 = __ffma2_rn(a2, __ffma2_rn(one, x23, c160), zero);
+            out[2 * j] = pack_bf16(w01.x, w01.y);
+            out[2 * j + 1] = pack_bf16(w23.x, w23.y);
+        }
+    }
+};
+
+template <>
 struct Raw<FQ_TQ2_0> {
     uint4 q0, q1;
     float d;
@@ -943,7 +987,8 @@ extern "C" __attribute__((visibility("default"))) int fq_debug_tc_timeline_dq(un
 }  // namespace
 
 bool tensor_path_serves(const DevWeights& w) {
-    return (w.fmt == FQ_Q4_K || w.fmt == FQ_Q5_K || w.fmt == FQ_Q8_0 || w.fmt == FQ_TQ2_0 || w.fmt == FQ_TQ2_0_FOLDED || w.fmt == FQ_Q2_0) &&
+    return (w.fmt == FQ_Q4_K || w.fmt == FQ_Q5_K || w.fmt == FQ_Q6_K || w.fmt == FQ_Q8_0 || w.fmt == FQ_TQ2_0 || w.fmt == FQ_TQ2_0_FOLDED ||
+            w.fmt == FQ_Q2_0) &&
            w.k % 256 == 0 && encode_fn() != nullptr;
 }
 
@@ -1010,6 +1055,7 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
     switch (w.fmt) {
         case FQ_Q4_K: e = launch_tc<FQ_Q4_K>(a, tmap, tmap_w, grid, tile_tokens, st); break;
         case FQ_Q5_K: e = launch_tc<FQ_Q5_K>(a, tmap, tmap_w, grid, tile_tokens, st); break;
+        case FQ_Q6_K: e = launch_tc<FQ_Q6_K>(a, tmap, tmap_w, grid, tile_tokens, st); break;
         case FQ_TQ2_0: e = launch_tc<FQ_TQ2_0>(a, tmap, tmap_w, grid, tile_tokens, st); break;
         case FQ_TQ2_0_FOLDED: e = launch_tc<FQ_TQ2_0_FOLDED>(a, tmap, tmap_w, grid, tile_tokens, st); break;
         case FQ_Q2_0: e = launch_tc<FQ_Q2_0>(a, tmap, tmap_w, grid, tile_tokens, st); break;
@@ -1068,7 +1114,7 @@ cudaError_t launch_f32_to_bf16(const float* src, void* dst, size_t n, cudaStream
 }
 
 int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, cudaStream_t st) {
-    if (!format_info(w.fmt).block_elems || w.fmt == FQ_Q6_K) return fail(FQ_DECLINED_ARGS, "format %d has no tensor-core kernel", w.fmt);
+    if (!format_info(w.fmt).block_elems) return fail(FQ_DECLINED_ARGS, "format %d has no tensor-core kernel", w.fmt);
     if (w.k % 256 != 0 || m < 1 || m > (size_t)1 << 24) return fail(FQ_DECLINED_ARGS, "tensor-core path needs k %% 256 == 0");
     // bf16 copy of the activations: [m][k], read by TMA with a 128-byte swizzle
     __nv_bfloat16* abf = (__nv_bfloat16*)dev_alloc_on(m * (size_t)w.k * 2, st);

@@ -168,6 +168,44 @@ struct Chunk<FQ_Q5_K> {
     }
 };
 
+// Q6_K (split rows: 208 payload bytes per block — ql[128], qh[64], sixteen i8 scales — then the f16 d plane).
+// Chunk c of a block: 16 ql bytes whose low nibbles are 16 weights of 32-element section h32 and whose high nibbles
+// are the same positions of section h32 + 2; each 16-weight run has its own scale (q6_k.zig:1239-1259, dot :1274-1330).
+template <>
+struct Chunk<FQ_Q6_K> {
+    uint4 q, qh, scales;
+    uint32_t lo[4], hi[4];
+    int sc0, sc1;
+    float d;
+    __device__ __forceinline__ void load(const uint8_t* row, int c, int k, size_t) {
+        const int cc = c & 7, c2 = cc >> 2, h32 = (cc >> 1) & 1, l0 = (cc & 1) * 16;
+        const uint8_t* b = row + (size_t)(c >> 3) * 208;
+        q = ld_weight16(b + c2 * 64 + h32 * 32 + l0);
+        qh = ldg_cached16(b + 128 + c2 * 32 + l0);  // shared by the chunks of both sections
+        scales = ldg_cached16(b + 192);
+        d = h2f(ld_scale16(row + (size_t)(k >> 8) * 208 + (c >> 3) * 2));
+    }
+    __device__ __forceinline__ void decode(int c) {
+        const int cc = c & 7, c2 = cc >> 2, h32 = (cc >> 1) & 1, half = cc & 1;
+        const uint32_t sw = c2 ? scales.z : scales.x, sw2 = c2 ? scales.w : scales.y;  // scales [c2*8 .. +3] and [c2*8+4 .. +7]
+        sc0 = (int)(int8_t)(sw >> (8 * (h32 * 2 + half)));
+        sc1 = (int)(int8_t)(sw2 >> (8 * (h32 * 2 + half)));
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        const uint32_t hb[4] = {qh.x, qh.y, qh.z, qh.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t l6 = (w[j] & 0x0f0f0f0fu) | (((hb[j] >> (2 * h32)) & 0x03030303u) << 4);
+            const uint32_t h6 = ((w[j] >> 4) & 0x0f0f0f0fu) | (((hb[j] >> (2 * h32 + 4)) & 0x03030303u) << 4);
+            lo[j] = __vsub4(l6, 0x20202020u);  // 0..63 -> -32..31 per byte
+            hi[j] = __vsub4(h6, 0x20202020u);
+        }
+    }
+    __device__ __forceinline__ float term(const int4* a, uint32_t, const float* ad, int c) const {
+        const int isum = sc0 * dot16_u(lo, a[0]) + sc1 * dot16_u(hi, a[1]);  // dp4a on signed bytes
+        return (float)isum * (d * ad[c >> 3]);
+    }
+};
+
 template <>
 struct Chunk<FQ_TQ2_0> {
     uint4 q;
@@ -443,6 +481,7 @@ cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st) {
         case FQ_Q8_0: return launch_mb<FQ_Q8_0>(a, sm_count, st);
         case FQ_Q4_K: return launch_mb<FQ_Q4_K>(a, sm_count, st);
         case FQ_Q5_K: return launch_mb<FQ_Q5_K>(a, sm_count, st);
+        case FQ_Q6_K: return launch_mb<FQ_Q6_K>(a, sm_count, st);
         case FQ_TQ2_0: return launch_mb<FQ_TQ2_0>(a, sm_count, st);
         case FQ_TQ2_0_FOLDED: return launch_mb<FQ_TQ2_0_FOLDED>(a, sm_count, st);
         case FQ_Q2_0: return launch_mb<FQ_Q2_0>(a, sm_count, st);

@@ -10,10 +10,10 @@ import numpy as np
 Q8_0, Q6_K, Q4_K, Q5_K = 0, 1, 2, 3
 TQ2_0, TQ2_0_FOLDED, Q2_0 = 16, 17, 18
 
-NAMES = {Q8_0: "q8_0", Q4_K: "q4_k", Q5_K: "q5_k", TQ2_0: "tq2_0", TQ2_0_FOLDED: "tq2_0_folded", Q2_0: "q2_0"}
+NAMES = {Q8_0: "q8_0", Q6_K: "q6_k", Q4_K: "q4_k", Q5_K: "q5_k", TQ2_0: "tq2_0", TQ2_0_FOLDED: "tq2_0_folded", Q2_0: "q2_0"}
 BY_NAME = {v: k for k, v in NAMES.items()}
 # (elements per block, GGUF bytes per block): src/dtype.zig:78-86, :128-139, :215-218; quant/types.zig:177-180
-BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), TQ2_0: (256, 66), TQ2_0_FOLDED: (256, 130), Q2_0: (128, 34)}
+BLOCK = {Q8_0: (32, 34), Q6_K: (256, 210), Q4_K: (256, 144), Q5_K: (256, 176), TQ2_0: (256, 66), TQ2_0_FOLDED: (256, 130), Q2_0: (128, 34)}
 
 
 def row_bytes(fmt: int, k: int) -> int:

@@ -53,7 +53,7 @@ def test_block_geometry(lib):
         assert lib.fq_block_bytes(fmt) == nbytes
         assert lib.fq_row_bytes(fmt, elems * 8) == nbytes * 8
         assert F.row_bytes(fmt, elems * 8) == nbytes * 8
-    assert lib.fq_block_elems(1) == 0  # Q6_K is declined everywhere
+    assert lib.fq_block_elems(4) == 0 and lib.fq_block_elems(15) == 0  # ids outside the enum are declined everywhere
     # the sizes the reference asserts (src/dtype.zig:230-239)
     assert (F.BLOCK[F.Q8_0], F.BLOCK[F.Q4_K], F.BLOCK[F.Q5_K], F.BLOCK[F.TQ2_0]) == ((32, 34), (256, 144), (256, 176), (256, 66))
 
@@ -70,7 +70,8 @@ def test_gates_keep_the_reference_predicates_with_b200_floors(lib):
         assert lib.fq_should_use_gpu_dense_quant_packed(fmt, (1 << 22) - 1) == 0
         assert lib.fq_should_use_gpu_dense_quant(fmt, 1 << 22) == 1
         assert lib.fq_should_use_gpu_dense_quant(fmt, (1 << 22) - 1) == 0
-    assert lib.fq_should_use_gpu_dense_quant(F.Q6_K, 1 << 40) == 0  # format not served
+    assert lib.fq_should_use_gpu_dense_quant(F.Q6_K, 1 << 22) == 1
+    assert lib.fq_should_use_gpu_dense_quant(7, 1 << 40) == 0  # not a format
     # a 7B-class prefill product and the decode stack's smallest product pass; the reference's defaults declined both
     assert lib.fq_should_use_gpu_dense_quant(F.Q4_K, 32 * 4096 * 4096) == 1
     assert lib.fq_should_use_gpu_quant_decode(F.Q5_K, 1, 4096, 4096) == 1
@@ -103,7 +104,7 @@ def test_argument_rules_decline_before_touching_a_device(lib):
         P.gemm_quant_nt(F.Q4_K, rhs[:7], a, n=7)
     assert e.value.code == 1
     with pytest.raises(P.Declined) as e:
-        P.gemm_quant_nt(F.Q6_K, rhs, a, n=8, nb01=210)
+        P.gemm_quant_nt(7, rhs, a, n=8, nb01=210)
     assert e.value.code == 1
     with pytest.raises(P.Declined):
         P.gemm_quant_nt(F.Q4_K, rhs, np.zeros((1, 128), np.float32), n=8, nb01=144)
@@ -152,5 +153,5 @@ def test_small_batch_row_limit_follows_shared_memory(lib):
     assert lib.fq_small_batch_max_rows(F.Q4_K, 28672) == 4       # the window the shared-memory rule closes
     assert lib.fq_small_batch_max_rows(F.Q8_0, 16384) == 8
     assert lib.fq_small_batch_max_rows(F.Q4_K, 262144) == 0
-    assert lib.fq_small_batch_max_rows(F.Q6_K, 4096) == 0        # format not served
+    assert lib.fq_small_batch_max_rows(7, 4096) == 0             # not a format
     assert lib.fq_small_batch_max_rows(F.Q4_K, 100) == 0         # not a whole number of blocks

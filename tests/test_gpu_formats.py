@@ -9,7 +9,7 @@ from parity import bits_equal, make_weights
 
 pytestmark = pytest.mark.gpu
 
-FMTS = ["q8_0", "q4_k", "q5_k", "tq2_0", "tq2_0_folded", "q2_0"]
+FMTS = ["q8_0", "q4_k", "q5_k", "q6_k", "tq2_0", "tq2_0_folded", "q2_0"]
 
 
 @pytest.fixture(scope="module")
@@ -67,6 +67,9 @@ def test_dequant_matches_reference_goldens(P, goldens):
     assert bits_equal(w4.dequantize(), oracle.dequantize_rows(oracle.Q4_K, goldens["q4_k_golden"], 256))
     w5 = P.Weights.upload(oracle.Q5_K, goldens["q5_k_golden"], 8, 256)
     assert bits_equal(w5.dequantize(), oracle.dequantize_rows(oracle.Q5_K, goldens["q5_k_golden"], 256))
+    w6 = P.Weights.upload(oracle.Q6_K, goldens["q6_k_golden"], 8, 256)
+    assert bits_equal(w6.dequantize(), oracle.dequantize_rows(oracle.Q6_K, goldens["q6_k_golden"], 256))
+    w6.free()
     tq = goldens["tq2_0_bytes"]
     wt = P.Weights.upload(oracle.TQ2_0, tq, tq.shape[0], 256)
     assert np.array_equal(wt.dequantize().view(np.uint32), goldens["tq2_0_expected_bits"])
@@ -96,9 +99,10 @@ def test_weight_encoders_reproduce_ggml_goldens(P, torch, goldens):
     x = goldens["input_bits"].view(np.float32)
     assert np.array_equal(_dev_encode(P, torch, oracle.Q4_K, x), goldens["q4_k_golden"])
     assert np.array_equal(_dev_encode(P, torch, oracle.Q5_K, x), goldens["q5_k_golden"])
+    assert np.array_equal(_dev_encode(P, torch, oracle.Q6_K, x), goldens["q6_k_golden"])
 
 
-@pytest.mark.parametrize("fmt_name", ["q8_0", "q4_k", "q5_k", "tq2_0", "q2_0"])
+@pytest.mark.parametrize("fmt_name", ["q8_0", "q4_k", "q5_k", "q6_k", "tq2_0", "q2_0"])
 def test_weight_encoders_match_oracle_bytes(P, torch, fmt_name):
     fmt = oracle.FORMATS[fmt_name]
     rng = np.random.default_rng(15)

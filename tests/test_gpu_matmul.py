@@ -9,7 +9,7 @@ from parity import TOL_INT8, assert_close, make_weights
 
 pytestmark = pytest.mark.gpu
 
-FMTS = ["q8_0", "q4_k", "q5_k", "tq2_0", "tq2_0_folded", "q2_0"]
+FMTS = ["q8_0", "q4_k", "q5_k", "q6_k", "tq2_0", "tq2_0_folded", "q2_0"]
 
 
 @pytest.fixture(scope="module")

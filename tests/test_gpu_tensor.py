@@ -38,7 +38,7 @@ def run_tensor(P, torch, fmt, blocks, a, n, mode=None):
     return cd.cpu().numpy()
 
 
-@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q8_0", "tq2_0", "tq2_0_folded", "q2_0"])
+@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q6_k", "q8_0", "tq2_0", "tq2_0_folded", "q2_0"])
 @pytest.mark.parametrize("m,n,k", [
     (64, 128, 256),      # one tile, one block of K
     (33, 96, 512),       # the reference's ragged parity shape (cuda.zig:3084-3088): partial rows and tokens
