@@ -75,7 +75,8 @@ struct RowsArgs {
     int use_tmap; // weights arrive by 2-D tensor copies (one per warp step) instead of per-lane bulk copies
     int skip_compute; // diagnosis only: stream the weights, skip the arithmetic
     int l2_stream;    // weight copies carry an evict-first L2 hint (tile-major form)
-    int rows_per_cta; // 0: rows split evenly over the grid; else CTA b serves rows [b*rows_per_cta, +rows_per_cta)
+    int rows_per_cta; // 0: rows split evenly over the grid; > 0: CTA b serves rows [b*rows_per_cta, +rows_per_cta);
+                      // < 0: whole 32-row storage tiles split evenly over the grid
     int split_n;      // 0, or the rows of ONE matrix when w stacks several that share the activations: weight row r
                       // of token b lands at c[((r / split_n) * m + b) * split_n + r % split_n] (the [batch][m][n] layout)
 };
