@@ -60,6 +60,8 @@ SIGNATURES = {
     "fq_work_destroy": (None, [c_void]),
     "fq_gemm_quant_nt_dev": (c_int, [c_void, c_size, c_void, c_void, c_size, c_int, c_void]),
     "fq_gemm_quant_nt_dev_noalloc": (c_int, [c_void, c_size, c_void, c_void, c_size, c_void]),
+    "fq_gemm_quant_nt_pre_dev": (c_int, [c_void, c_size, c_int, c_void, c_void, C.c_float, c_void, c_size, c_int, c_void]),
+    "fq_act_prologue_dev": (c_int, [c_int, c_void, c_void, C.c_float, c_void, c_size, c_size, c_void]),
     "fq_small_batch_max_rows": (c_int, [c_int, c_size]),
     "fq_gemm_ptqtp_dev": (c_int, [P(c_void), c_int, c_void, c_void, c_size, c_void]),
     "fq_quantize_acts_q8_k_dev": (c_int, [c_void, c_size, c_size, c_void]),

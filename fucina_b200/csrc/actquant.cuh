@@ -87,15 +87,55 @@ __host__ __device__ inline NatSizes nat_sizes(bool q8k, size_t k) {
     return s;
 }
 
-// Quantise 256 activations (block `blk` of a row) into a natural record.
-// Call with a full warp. `k` must be a multiple of 256.
-__device__ __forceinline__ void quantize_block_natural(const float* __restrict__ src_row, int blk, bool q8k, size_t k,
-                                                       uint8_t* rec, int lane) {
-    const NatSizes S = nat_sizes(q8k, k);
-    const float* src = src_row + (size_t)blk * 256 + lane * 8;
+// ---- activation prologues fused in front of the quantiser ------------------------------------------------------
+// The reference CPU path fuses two row operations into its activation quantiser so the [m, k] intermediate is never
+// written (src/exec/quant_matmul.zig:480-757, src/exec/row_ops.zig:39-137):
+//   rms_norm_mul   out = (x * scale) * weight, scale = 1 / sqrt(sum(x^2) / k + eps)      (row_ops.zig:96-106)
+//   split_swiglu   row = [gate: k][up: k], out = (up * gate) * (1 / (1 + exp(-gate)))     (row_ops.zig:711-728)
+// Sum of squares, fixed order: lane partial over its 8 elements in element order, xor tree over the warp, then the
+// 256-element block sums added in block order. Every caller uses these helpers, so the fused and the stand-alone
+// forms agree bit for bit.
+__device__ __forceinline__ void load8(const float* src, float v[8]) {
     const float4 v0 = *reinterpret_cast<const float4*>(src);
     const float4 v1 = *reinterpret_cast<const float4*>(src + 4);
-    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    v[0] = v0.x, v[1] = v0.y, v[2] = v0.z, v[3] = v0.w, v[4] = v1.x, v[5] = v1.y, v[6] = v1.z, v[7] = v1.w;
+}
+__device__ __forceinline__ float block_sumsq(const float v[8]) {
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s = __fadd_rn(s, __fmul_rn(v[j], v[j]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, o));
+    return s;
+}
+__device__ __forceinline__ float rms_scale(const float* block_sums, int nblk, float eps) {
+    float total = 0.0f;
+    for (int i = 0; i < nblk; ++i) total = __fadd_rn(total, block_sums[i]);
+    const float inv_cols = __fdiv_rn(1.0f, (float)(nblk * 256));
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(total, inv_cols), eps)));
+}
+// The 8 prologue outputs of lane `lane` in block `blk` of one row. `row` is the row's first input element (2k
+// inputs per row for split_swiglu), `scale` the row's rms scale.
+__device__ __forceinline__ void load_block_pre(const PreArgs& P, const float* row, size_t k, int blk, int lane, float scale, float v[8]) {
+    const size_t e0 = (size_t)blk * 256 + lane * 8;
+    load8(row + e0, v);
+    if (P.op == FQ_PRE_RMS_NORM_MUL) {
+        float w[8];
+        load8(P.w + e0, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(__fmul_rn(v[j], scale), w[j]);
+    } else if (P.op == FQ_PRE_SPLIT_SWIGLU) {
+        float up[8];
+        load8(row + k + e0, up);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(__fmul_rn(up[j], v[j]), __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v[j]))));
+    }
+}
+
+// Quantise 256 activations (block `blk` of a row), given as the 8 values of each lane, into a natural record.
+// Call with a full warp. `k` must be a multiple of 256.
+__device__ __forceinline__ void quantize_values_natural(const float v[8], int blk, bool q8k, size_t k, uint8_t* rec, int lane) {
+    const NatSizes S = nat_sizes(q8k, k);
     int q[8];
     uint2 packed;
     if (q8k) {
@@ -114,6 +154,12 @@ __device__ __forceinline__ void quantize_block_natural(const float* __restrict__
     packed.x = pack4(q);
     packed.y = pack4(q + 4);
     *reinterpret_cast<uint2*>(rec + (size_t)blk * 256 + lane * 8) = packed;
+}
+__device__ __forceinline__ void quantize_block_natural(const float* __restrict__ src_row, int blk, bool q8k, size_t k,
+                                                       uint8_t* rec, int lane) {
+    float v[8];
+    load8(src_row + (size_t)blk * 256 + lane * 8, v);
+    quantize_values_natural(v, blk, q8k, k, rec, lane);
 }
 
 }  // namespace fq

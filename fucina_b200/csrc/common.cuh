@@ -73,6 +73,14 @@ __host__ __device__ inline size_t dev_row_stride(int fmt, size_t k) {
     return (raw + 15) & ~(size_t)15;
 }
 
+// Activation prologue of a product (see actquant.cuh): op is one of FQ_PRE_*, `w` the [k] norm weights of
+// rms_norm_mul, `eps` its epsilon. With split_swiglu an input row holds 2k values.
+struct PreArgs {
+    int op;
+    const float* w;
+    float eps;
+};
+
 // ---- small device helpers ---------------------------------------------------
 __device__ __forceinline__ float h2f(uint16_t bits) { return __half2float(__ushort_as_half(bits)); }
 

@@ -600,11 +600,43 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
         // warp w quantises activation blocks w, w+kWarps, ...: with one-unit slabs these are exactly the
         // blocks it consumes, so no CTA-wide barrier is needed before it starts on its weights
         const int nblk = k >> 8;
+        const size_t a_stride = A.pre.op == FQ_PRE_SPLIT_SWIGLU ? (size_t)2 * k : (size_t)k;  // input values per row
+        float pre_scale[MB];
+#pragma unroll
+        for (int b = 0; b < MB; ++b) pre_scale[b] = 0.0f;
+        if (A.pre.op == FQ_PRE_RMS_NORM_MUL) {
+            // the rows' sums of squares: block sums by the warps that will quantise those blocks, parked in the
+            // (still unused) reduction buffer, then added in block order by every thread
+            float* part = red;
+            for (int i = 0; i < MB * ((nblk - warp + kWarps - 1) / kWarps); ++i) {
+                const int blk = warp + (i / MB) * kWarps, b = i % MB;
+                if (b >= A.m) continue;
+                float v[8];
+                load8(A.a_f32 + (size_t)b * a_stride + (size_t)blk * 256 + lane * 8, v);
+                const float ss = block_sumsq(v);
+                if (lane == 0) part[b * nblk + blk] = ss;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int b = 0; b < MB; ++b)
+                if (b < A.m) pre_scale[b] = rms_scale(part + b * nblk, nblk, A.pre.eps);
+            __syncthreads();  // the buffer goes back to the tile loop
+        }
         for (int i = 0; i < MB * ((nblk - warp + kWarps - 1) / kWarps); ++i) {
             const int blk = warp + (i / MB) * kWarps, b = i % MB;
             uint8_t* rec = acts + (size_t)b * NS.row;
             if (b < A.m) {
-                quantize_block_natural(A.a_f32 + (size_t)b * k, blk, Q8K, k, rec, lane);
+                if (A.pre.op == FQ_PRE_NONE) {
+                    quantize_block_natural(A.a_f32 + (size_t)b * k, blk, Q8K, k, rec, lane);
+                } else {
+                    float v[8];
+                    float scale = 0.0f;
+#pragma unroll
+                    for (int bb = 0; bb < MB; ++bb)
+                        if (bb == b) scale = pre_scale[bb];
+                    load_block_pre(A.pre, A.a_f32 + (size_t)b * a_stride, (size_t)k, blk, lane, scale, v);
+                    quantize_values_natural(v, blk, Q8K, k, rec, lane);
+                }
             } else {  // padded batch slots contribute zeros
                 *reinterpret_cast<uint2*>(rec + (size_t)blk * 256 + lane * 8) = make_uint2(0, 0);
                 if (Q8K) {
@@ -1170,12 +1202,16 @@ size_t decode_rows_scratch_bytes(const DevWeights& w, size_t m) {
     return nat_sizes(w.fmt != FQ_Q8_0, (size_t)w.k).row * m;
 }
 
+// the fused prologue parks m * k/256 block sums in the reduction buffer (at least 2 * 8 * 32 floats per padded row)
+bool decode_rows_fuses_prologue(const DevWeights& w, size_t m) { return decode_rows_eligible(w, m) && (int)m <= kFusedMaxRows && w.k / 256 <= 512; }
+
 cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev, uint8_t* scratch, float* c, int m, int ldc,
-                               int sm_count, int* status, cudaStream_t st, int split_n) {
+                               int sm_count, int* status, cudaStream_t st, int split_n, const PreArgs* pre) {
     const int mb = decode_pad_rows(w.fmt, (size_t)m);
     static const int skip = getenv("FUCINA_B200_DECODE_SKIP_COMPUTE") ? 1 : 0;  // diagnosis: copy pipeline only, outputs are garbage
     static const int l2_stream = getenv("FUCINA_B200_DECODE_L2_STREAM") ? atoi(getenv("FUCINA_B200_DECODE_L2_STREAM")) : 1;
-    RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0, skip, l2_stream, 0, split_n};
+    RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0, skip, l2_stream, 0, split_n, pre ? *pre : PreArgs{FQ_PRE_NONE, nullptr, 0.0f}};
+    if (a.pre.op != FQ_PRE_NONE && !decode_rows_fuses_prologue(w, (size_t)m)) return cudaErrorInvalidValue;
     if (!pick_config(w.fmt, w.k, mb, &a.slab, &a.stages)) return cudaErrorInvalidValue;
     // K-quant units are an odd number of 16-byte chunks: one tensor copy per warp step instead of 32
     // per-lane bulk copies (small bulk copies are issue-rate bound in the copy engine)

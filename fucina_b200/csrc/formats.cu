@@ -361,6 +361,38 @@ cudaError_t launch_quantize_acts_natural(const float* a, int m, int k, bool q8k,
     return cudaGetLastError();
 }
 
+// Stand-alone activation prologue (actquant.cuh): one CTA per row, its warps over the row's 256-element blocks. The
+// arithmetic and its order are those of the decode kernel's fused prologue, so both forms give the same bits.
+__global__ void __launch_bounds__(256) act_prologue_kernel(const PreArgs P, const float* __restrict__ a, float* __restrict__ out, int k) {
+    extern __shared__ float block_sums[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int nblk = k >> 8;
+    const float* row = a + (size_t)blockIdx.x * (P.op == FQ_PRE_SPLIT_SWIGLU ? (size_t)2 * k : (size_t)k);
+    float scale = 0.0f;
+    if (P.op == FQ_PRE_RMS_NORM_MUL) {
+        for (int blk = warp; blk < nblk; blk += nwarps) {
+            float v[8];
+            load8(row + (size_t)blk * 256 + lane * 8, v);
+            const float ss = block_sumsq(v);
+            if (lane == 0) block_sums[blk] = ss;
+        }
+        __syncthreads();
+        scale = rms_scale(block_sums, nblk, P.eps);
+    }
+    float* orow = out + (size_t)blockIdx.x * k;
+    for (int blk = warp; blk < nblk; blk += nwarps) {
+        float v[8];
+        load_block_pre(P, row, (size_t)k, blk, lane, scale, v);
+        float* dst = orow + (size_t)blk * 256 + lane * 8;
+        *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+cudaError_t launch_act_prologue(const PreArgs& pre, const float* a, float* out, int m, int k, cudaStream_t st) {
+    act_prologue_kernel<<<(unsigned)m, 256, (size_t)(k >> 8) * sizeof(float), st>>>(pre, a, out, k);
+    return cudaGetLastError();
+}
+
 // ===========================================================================
 // Weight encoders (raw GGUF blocks out, byte-identical to the CPU encoders).
 // ===========================================================================

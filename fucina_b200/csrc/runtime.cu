@@ -539,9 +539,24 @@ int resolve_rhs(Ctx* ctx, int fmt, const void* rhs, size_t rhs_len, int cacheabl
 // dense matmul on device buffers
 // ---------------------------------------------------------------------------
 int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, int mode,
-             int accumulate, cudaStream_t st, int split_n) {
+             int accumulate, cudaStream_t st, int split_n, const PreArgs* pre) {
     if (m == 0) return fail(FQ_DECLINED_ARGS, "m == 0");
     if (mat < 0 || mat >= w.n_mats) return fail(FQ_DECLINED_ARGS, "matrix index out of range");
+    if (pre && pre->op != FQ_PRE_NONE) {
+        const bool fuse = !accumulate && g_decode_rows_on && mode != FQ_MODE_TENSOR && decode_rows_fuses_prologue(w, m);
+        if (!fuse) {
+            // shapes whose kernel has no fused prologue: the same arithmetic as a pass of its own into a scratch
+            // [m][k] block, then the plain product
+            float* act = (float*)dev_alloc_on(m * (size_t)w.k * sizeof(float), st);
+            if (!act) return fail(FQ_DECLINED_BUDGET, "activation scratch allocation failed");
+            cudaError_t e = launch_act_prologue(*pre, a_dev, act, (int)m, w.k, st);
+            g_trace.launches++;
+            int rc = e == cudaSuccess ? gemm_dev(ctx, w, mat, act, c_dev, m, ldc, mode, accumulate, st, split_n, nullptr)
+                                      : cuda_fail(e, "activation prologue launch");
+            dev_free_on(act, st);
+            return rc;
+        }
+    }
     if (split_n && !(g_decode_rows_on && !accumulate && decode_rows_eligible(w, m) && w.n % split_n == 0))
         return fail(FQ_DECLINED_ARGS, "stacked matrices are served by the decode kernel only");
     if (split_n) mode = FQ_MODE_INT8;
@@ -561,7 +576,7 @@ int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* 
             t1 = ktime_event();
             cudaEventRecord(t0, st);
         }
-        cudaError_t e = launch_decode_rows(w, mat, a_dev, nat, c_dev, (int)m, (int)ldc, ctx->sm_count, ctx->status_dev, st, split_n);
+        cudaError_t e = launch_decode_rows(w, mat, a_dev, nat, c_dev, (int)m, (int)ldc, ctx->sm_count, ctx->status_dev, st, split_n, pre);
         if (g_ktime_on) {
             cudaEventRecord(t1, st);
             g_ktime_events.emplace_back(t0, t1);
@@ -1241,6 +1256,39 @@ int fq_gemm_quant_nt_dev(const fq_weights* w, size_t mat, const float* a_dev, fl
     std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
     g_trace.calls++;
     return gemm_dev(ctx, w->dw, (int)mat, a_dev, c_dev, m, (size_t)w->dw.n, mode, 0, stream ? (cudaStream_t)stream : ctx->stream);
+}
+// ---- fused neighbours of the CPU path (exec/quant_matmul.zig:480-757) -------------------------------------------
+static int check_pre(int pre_op, const DevWeights* dw, size_t k, const float* pre_w_dev) {
+    if (pre_op != FQ_PRE_RMS_NORM_MUL && pre_op != FQ_PRE_SPLIT_SWIGLU) return fail(FQ_DECLINED_ARGS, "prologue %d is not one of FQ_PRE_*", pre_op);
+    if (pre_op == FQ_PRE_RMS_NORM_MUL && !pre_w_dev) return fail(FQ_DECLINED_ARGS, "rms_norm_mul needs the norm weights");
+    if (k == 0 || k % 256 != 0) return fail(FQ_DECLINED_ARGS, "activation prologues need k to be a multiple of 256");
+    if (dw && (size_t)dw->k != k) return fail(FQ_DECLINED_ARGS, "k mismatch");
+    return FQ_OK;
+}
+int fq_gemm_quant_nt_pre_dev(const fq_weights* w, size_t mat, int pre_op, const float* a_dev, const float* pre_w_dev, float eps,
+                             float* c_dev, size_t m, int mode, void* stream) {
+    if (!w || !a_dev || !c_dev) return fail(FQ_DECLINED_ARGS, "null pointer");
+    if (pre_op == FQ_PRE_NONE) return fq_gemm_quant_nt_dev(w, mat, a_dev, c_dev, m, mode, stream);
+    if (int rc = check_pre(pre_op, &w->dw, (size_t)w->dw.k, pre_w_dev)) return rc;
+    Ctx* ctx = nullptr;
+    if (int rc = gate_and_ctx(&ctx)) return rc;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    g_trace.calls++;
+    const PreArgs pre{pre_op, pre_w_dev, eps};
+    return gemm_dev(ctx, w->dw, (int)mat, a_dev, c_dev, m, (size_t)w->dw.n, mode, 0, stream ? (cudaStream_t)stream : ctx->stream, 0, &pre);
+}
+int fq_act_prologue_dev(int pre_op, const float* a_dev, const float* pre_w_dev, float eps, float* out_dev, size_t m, size_t k, void* stream) {
+    if (!a_dev || !out_dev || m == 0 || m > 65535u * 32u) return fail(FQ_DECLINED_ARGS, "null pointer or row count");
+    if (int rc = check_pre(pre_op, nullptr, k, pre_w_dev)) return rc;
+    if (k > (size_t)1 << 22) return fail(FQ_DECLINED_ARGS, "k too large");
+    Ctx* ctx = nullptr;
+    if (int rc = gate_and_ctx(&ctx)) return rc;
+    std::lock_guard<std::recursive_mutex> g(g_dispatch_lock);
+    g_trace.calls++;
+    const PreArgs pre{pre_op, pre_w_dev, eps};
+    cudaError_t e = launch_act_prologue(pre, a_dev, out_dev, (int)m, (int)k, stream ? (cudaStream_t)stream : ctx->stream);
+    g_trace.launches++;
+    return e == cudaSuccess ? FQ_OK : cuda_fail(e, "activation prologue launch");
 }
 int fq_small_batch_max_rows(int fmt, size_t k) {
     const FormatInfo f = format_info(fmt);

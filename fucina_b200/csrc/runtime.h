@@ -57,8 +57,10 @@ int resolve_rhs(Ctx* ctx, int fmt, const void* rhs, size_t rhs_len, int cacheabl
 // c[m, ldc] (+)= a[m, k] . dequant(W[mat])^T on device buffers.
 // split_n != 0: `w` stacks several matrices of split_n rows that share the activations (decode shapes only) and
 // c_dev is laid out [matrix][m][split_n].
+// pre: an activation prologue (rms_norm_mul / split_swiglu) applied to a_dev before the product: inside the decode
+// kernel's quantiser where that kernel serves the shape, as a pass of its own otherwise.
 int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc, int mode,
-             int accumulate, cudaStream_t st, int split_n = 0);
+             int accumulate, cudaStream_t st, int split_n = 0, const PreArgs* pre = nullptr);
 // gemm_tc.cu: bf16 tensor-core path; returns FQ_DECLINED_ARGS for shapes it does not take.
 int gemm_tensor_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* c_dev, size_t m, size_t ldc,
                     cudaStream_t st);

@@ -235,6 +235,23 @@ def gemm_quant_nt_dev(w: Weights, a_dev, c_dev, m: int, mat: int = 0, mode: int 
     _check(load().fq_gemm_quant_nt_dev(w.handle, mat, _vp(a_dev), _vp(c_dev), m, mode, C.c_void_p(stream)))
 
 
+PRE_NONE, PRE_RMS_NORM_MUL, PRE_SPLIT_SWIGLU = 0, 1, 2
+
+
+def gemm_quant_nt_pre_dev(w: Weights, pre_op: int, a_dev, c_dev, m: int, pre_w_dev=None, eps: float = 0.0, mat: int = 0,
+                          mode: int = MODE_AUTO, stream: int = 0) -> None:
+    """Product with a row operation fused in front of the activation quantiser (src/exec/quant_matmul.zig:480-757):
+    PRE_RMS_NORM_MUL (a_dev [m][k], pre_w_dev [k], eps) or PRE_SPLIT_SWIGLU (a_dev [m][2k], gate | up)."""
+    _check(load().fq_gemm_quant_nt_pre_dev(w.handle, mat, pre_op, _vp(a_dev), _vp(pre_w_dev) if pre_w_dev is not None else None,
+                                           eps, _vp(c_dev), m, mode, C.c_void_p(stream)))
+
+
+def act_prologue_dev(pre_op: int, a_dev, out_dev, m: int, k: int, pre_w_dev=None, eps: float = 0.0, stream: int = 0) -> None:
+    """The row operation of `gemm_quant_nt_pre_dev` alone: out_dev [m][k] f32."""
+    _check(load().fq_act_prologue_dev(pre_op, _vp(a_dev), _vp(pre_w_dev) if pre_w_dev is not None else None, eps, _vp(out_dev),
+                                      m, k, C.c_void_p(stream)))
+
+
 def gemm_quant_nt_dev_noalloc(w: Weights, a_dev, c_dev, m: int, mat: int = 0, stream: int = 0) -> None:
     """Small-batch product for callers that may not allocate device memory while serving.
 

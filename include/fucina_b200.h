@@ -175,6 +175,23 @@ enum {
 };
 FQ_API int fq_gemm_quant_nt_dev(const fq_weights* w, size_t mat, const float* a_dev, float* c_dev, size_t m, int mode,
                          void* stream);
+/* The fused neighbours of the CPU path: a row operation applied to the activations on their way into the
+ * quantiser, so the [m, k] intermediate is never written (src/exec/quant_matmul.zig:480-757,
+ * src/exec/row_ops.zig:39-137; the reference has them on the CPU only).
+ *   FQ_PRE_RMS_NORM_MUL  a_dev [m][k], pre_w_dev [k]: (x * scale) * weight with
+ *                        scale = 1 / sqrt(sum(x^2) / k + eps)                            (row_ops.zig:96-106)
+ *   FQ_PRE_SPLIT_SWIGLU  a_dev [m][2k] = gate | up per row: (up * gate) * (1 / (1 + exp(-gate)))  (row_ops.zig:711-728)
+ * k must be a multiple of 256. Decode shapes (m <= 4, the formats and sizes of the copy-engine kernel) run the
+ * operation inside that kernel's prologue; every other shape runs fq_act_prologue_dev into scratch and then the
+ * plain product. Both forms use one arithmetic order, so the results are bit-identical to
+ * fq_act_prologue_dev followed by fq_gemm_quant_nt_dev. The sum of squares adds 256-element block sums in block
+ * order (the reference's scalar loop adds element by element: scale agrees to f32 round-off, not bit for bit). */
+enum { FQ_PRE_NONE = 0, FQ_PRE_RMS_NORM_MUL = 1, FQ_PRE_SPLIT_SWIGLU = 2 };
+FQ_API int fq_gemm_quant_nt_pre_dev(const fq_weights* w, size_t mat, int pre_op, const float* a_dev, const float* pre_w_dev,
+                                    float eps, float* c_dev, size_t m, int mode, void* stream);
+/* The row operation alone: out_dev [m][k] f32. */
+FQ_API int fq_act_prologue_dev(int pre_op, const float* a_dev, const float* pre_w_dev, float eps, float* out_dev, size_t m,
+                               size_t k, void* stream);
 /* Allocation-free small-batch product. No counterpart in the reference (its
  * provider grows device buffers on demand, backend/cuda.zig:873-890). For
  * hosts that must not allocate device memory once they are serving -- VRAM

@@ -101,6 +101,25 @@ def quantize_acts_q8_k(a: np.ndarray) -> np.ndarray:
     return out
 
 
+def rms_norm_mul(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    """exec/row_ops.zig:96-106 (the scalar loop): (x * scale) * w with scale = 1/sqrt(sum(x^2)/k + eps)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    m, k = x.shape
+    out = np.zeros((m, k), dtype=np.float32)
+    assert lib().orc_rms_norm_mul(_p(x), _p(w), ctypes.c_float(eps), _p(out), _sz(m), _sz(k)) == 0
+    return out
+
+
+def split_swiglu(gate_up: np.ndarray) -> np.ndarray:
+    """exec/row_ops.zig:711-722: rows [gate: k | up: k] -> up * gate * sigmoid(gate)."""
+    gate_up = np.ascontiguousarray(gate_up, dtype=np.float32)
+    m, k2 = gate_up.shape
+    out = np.zeros((m, k2 // 2), dtype=np.float32)
+    assert lib().orc_split_swiglu(_p(gate_up), _p(out), _sz(m), _sz(k2 // 2)) == 0
+    return out
+
+
 def quantize_acts_q8_0(a: np.ndarray) -> np.ndarray:
     a = np.ascontiguousarray(a, dtype=np.float32)
     m, k = a.shape

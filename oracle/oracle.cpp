@@ -914,6 +914,31 @@ int orc_quantize_acts_q8_0(const float* a, size_t m, size_t k, void* dst) {
     return 0;
 }
 
+// The row operations the CPU path fuses in front of its activation quantiser (exec/quant_matmul.zig:480-757).
+// rms_norm_mul, the scalar loop of exec/row_ops.zig:96-106: sumsq over the row element by element in f32,
+// scale = 1 / sqrt(sumsq * (1/k) + eps), out = value * scale * weight (left to right).
+int orc_rms_norm_mul(const float* x, const float* w, float eps, float* out, size_t m, size_t k) {
+    const float inv_cols = 1.0f / (float)k;
+    for (size_t r = 0; r < m; ++r) {
+        const float* row = x + r * k;
+        float sumsq = 0.0f;
+        for (size_t i = 0; i < k; ++i) sumsq += row[i] * row[i];
+        const float scale = 1.0f / std::sqrt(sumsq * inv_cols + eps);
+        for (size_t i = 0; i < k; ++i) out[r * k + i] = row[i] * scale * w[i];
+    }
+    return 0;
+}
+// split_swiglu, the vector body of exec/row_ops.zig:711-722 (k is a multiple of 4 here): a row holds the gate half
+// then the up half; out = up * gate * (1 / (1 + exp(-gate))), left to right.
+int orc_split_swiglu(const float* gate_up, float* out, size_t m, size_t k) {
+    for (size_t r = 0; r < m; ++r)
+        for (size_t i = 0; i < k; ++i) {
+            const float gate = gate_up[r * 2 * k + i], up = gate_up[r * 2 * k + k + i];
+            out[r * k + i] = up * gate * (1.0f / (1.0f + std::exp(-gate)));
+        }
+    return 0;
+}
+
 // Oracle A: c[m,n] = a[m,k] . dequant(W[n,k])^T the way the CPU kernels do it
 // (activations to int8 first, integer block dots, f32 epilogue, blocks
 // ascending). nb01 = bytes per weight row. Threads split output columns
