@@ -568,7 +568,7 @@ def run_profile_moe(args) -> dict:
     from fucina_b200 import provider as P
 
     P.init(0)
-    hidden, ffn, n_expert, top_k, seq = 2048, 768, 128, 8, 1024
+    hidden, ffn, n_expert, top_k, seq = 2048, 768, 128, 8, max(1, args.tokens)
     gate = _dev_weights(P, torch, F.Q5_K, ffn, hidden, 1300, n_expert)
     up = _dev_weights(P, torch, F.Q5_K, ffn, hidden, 1301, n_expert)
     down = _dev_weights(P, torch, F.Q5_K, hidden, ffn, 1302, n_expert)
@@ -586,7 +586,7 @@ def run_profile_moe(args) -> dict:
         P.moe_layer_dev(gate, up, down, x, seq, top_k, sel, w, out)
 
     ms = _timed(P, torch, layer, args.steps, args.warmup)
-    return {"workload": "profile case: Q5_K MoE layer 2048/768, 128 experts, top-8, 1024 tokens (plain launches)", "ms": round(ms, 4),
+    return {"workload": f"profile case: Q5_K MoE layer 2048/768, 128 experts, top-8, {seq} tokens (plain launches)", "ms": round(ms, 4),
             "tok_per_s": round(seq / ms * 1e3, 1)}
 
 
@@ -1292,6 +1292,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--no-sub", action="store_true", help="skip the records of the other configurations")
+    ap.add_argument("--tokens", type=int, default=1024, help="tokens of the profile_moe case")
     ap.add_argument("--batch", type=int, default=1, help="activation rows per product of the decode stack (1, 4 or 16)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -944,7 +944,7 @@ __device__ __forceinline__ void expert_block_m(int mstep, uint32_t p, const ActV
 }
 
 template <int FMT, int MB, bool GATED>
-__global__ void __launch_bounds__(kExpertWarps * 32, 1)
+__global__ void __launch_bounds__(kExpertWarps * 32, MB == 8 ? 2 : 1)  // eight-row tables: two CTAs per SM (128 registers, no spills)
     expert_rows_kernel(const ExpertArgs A, const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap2) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NM = GATED ? 2 : 1;
@@ -968,7 +968,7 @@ __global__ void __launch_bounds__(kExpertWarps * 32, 1)
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     uint8_t* acts = smem + 512;
     float* red = reinterpret_cast<float*>(acts + ((MB * NS.row + 127) & ~(size_t)127));
-    uint8_t* slots = reinterpret_cast<uint8_t*>(red) + (size_t)kExpertWarps * NM * MB * 32 * sizeof(float);
+    uint8_t* slots = reinterpret_cast<uint8_t*>(red) + (ksplit > 1 ? (size_t)kExpertWarps * NM * MB * 32 * sizeof(float) : 0);  // no K split, no buffer
     const uint32_t slot0 = smem_u32(slots) + (uint32_t)(warp * A.stages) * 32 * UB;
     const uint32_t bar0 = smem_u32(bars) + warp * kMaxStages * 8;
     if (lane == 0)
@@ -1126,10 +1126,10 @@ __global__ void __launch_bounds__(kExpertWarps * 32, 1)
     }
 }
 
-size_t expert_smem_bytes(int fmt, int k, int mb, int nm, int stages) {
+size_t expert_smem_bytes(int fmt, int k, int mb, int nm, int stages, bool k_split = true) {
     const NatSizes NS = nat_sizes(true, (size_t)k);
     const int ub = fmt == FQ_Q4_K ? 144 : 176;
-    return 512 + ((mb * NS.row + 127) & ~(size_t)127) + (size_t)kExpertWarps * nm * mb * 32 * sizeof(float) +
+    return 512 + ((mb * NS.row + 127) & ~(size_t)127) + (k_split ? (size_t)kExpertWarps * nm * mb * 32 * sizeof(float) : 0) +
            (size_t)kExpertWarps * stages * 32 * ub;
 }
 
@@ -1139,6 +1139,9 @@ cudaError_t launch_expert_t(const ExpertArgs& a, const CUtensorMap& t1, const CU
     static bool granted = false;
     if (!granted) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
+        if (e != cudaSuccess) return e;
+        // all of the SM's configurable memory as shared memory, so two CTAs of up to 113 KB fit side by side
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return e;
         granted = true;
     }
@@ -1294,7 +1297,6 @@ cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const 
     const int mb = pad_rows((size_t)group_rows), nm = w2 ? 2 : 1;
     const int ub = w.fmt == FQ_Q4_K ? 144 : 176;
     int stages = kMaxStages;
-    while (stages > 2 && expert_smem_bytes(w.fmt, w.k, mb, nm, stages) > kSmemLimit) --stages;
     // tiles per item: whole tiles per warp when the table is long enough to fill the SMs, K split across
     // warps when it is short (a single token names top_k experts only)
     const int tiles_per_mat = (w.n + 31) / 32;
@@ -1306,15 +1308,24 @@ cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const 
     memset(&t1, 0, sizeof t1);
     memset(&t2, 0, sizeof t2);
     if (!make_stack_tmap(w, ub, &t1) || (w2 && !make_stack_tmap(*w2, ub, &t2))) return cudaErrorInvalidValue;
+    const bool k_split = tpi < kExpertWarps;  // the cross-warp reduction buffer exists only then
+    while (stages > 2 && expert_smem_bytes(w.fmt, w.k, mb, nm, stages, k_split) > kSmemLimit) --stages;
     long long items = (long long)max_desc * ((tiles_per_mat + tpi - 1) / tpi);
     int grid = (int)(items < sm_count ? (items > 0 ? items : 1) : sm_count);
     // a short table (one token): one item per CTA and two half-size CTAs per SM instead of a second round
-    if (items > sm_count && items <= 2LL * sm_count && expert_smem_bytes(w.fmt, w.k, mb, nm, 2) <= 113 * 1024) {
+    if (items > sm_count && items <= 2LL * sm_count && expert_smem_bytes(w.fmt, w.k, mb, nm, 2, k_split) <= 113 * 1024) {
         grid = (int)items;
         stages = 2;
     }
+    // eight-row tables run the warp-level tensor-core block product, which eight warps per SM leave latency-bound
+    // (two warps per scheduler, issue slots half empty): two CTAs per SM with two-stage rings
+    static const bool no_pair = getenv("FUCINA_B200_EXPERT_ONE_CTA") != nullptr;
+    if (!no_pair && mb == 8 && items > sm_count && expert_smem_bytes(w.fmt, w.k, mb, nm, 2, k_split) <= 113 * 1024) {
+        grid = (int)(items < 2LL * sm_count ? items : 2LL * sm_count);
+        stages = 2;
+    }
     ExpertArgs a{w, w2 ? *w2 : DevWeights{}, src, src_index, top_k, out, table, n_desc, max_desc, tpi, stages, status, gated_op};
-    const size_t smem = expert_smem_bytes(w.fmt, w.k, mb, nm, stages);
+    const size_t smem = expert_smem_bytes(w.fmt, w.k, mb, nm, stages, k_split);
     if (w.fmt == FQ_Q4_K)
         return w2 ? launch_expert_mb<FQ_Q4_K, true>(a, mb, t1, t2, grid, smem, st) : launch_expert_mb<FQ_Q4_K, false>(a, mb, t1, t2, grid, smem, st);
     return w2 ? launch_expert_mb<FQ_Q5_K, true>(a, mb, t1, t2, grid, smem, st) : launch_expert_mb<FQ_Q5_K, false>(a, mb, t1, t2, grid, smem, st);
