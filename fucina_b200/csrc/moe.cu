@@ -310,7 +310,7 @@ __global__ void gated_f32_kernel(const float* __restrict__ gate, const float* __
         out[i] = gated_pair(gated_op, gate[i], up[i]);
 }
 
-int g_moe_tensor_mode = -1;  // -1 auto (>= 14 rows per expert on average: the measured crossover of the two arms), 0 never, 1 whenever the format allows
+int g_moe_tensor_mode = -1;  // -1 auto (>= 17 rows per expert on average: the measured crossover of the two arms), 0 never, 1 whenever the format allows
 
 int moe_layer_tensor_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const DevWeights& down, const float* x_dev,
                           int seq, int top_k, const int* selected_dev, const float* weights_dev, Shard shard, float* out_dev,
@@ -393,7 +393,7 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     const bool tc_ok = (fmt == FQ_Q4_K || fmt == FQ_Q5_K || fmt == FQ_Q8_0) && tensor_path_serves(gate) && tensor_path_serves(down) &&
                        (fmt_dn == FQ_Q4_K || fmt_dn == FQ_Q5_K || fmt_dn == FQ_Q8_0);
     const bool tapped = taps.g_pairs || taps.down_pairs;  // the taps read the integer arm's intermediates
-    if (!tapped && tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 14 * n_expert)))
+    if (!tapped && tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 17 * n_expert)))
         return moe_layer_tensor_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, shard, out_dev, st, gated_op);
     const ActSizes Sx = act_sizes(fmt, hidden), Sg = act_sizes(fmt_dn, out_pe);
     // Row tile of the grouped kernel. A router sends a token to distinct experts, so an expert's run is
