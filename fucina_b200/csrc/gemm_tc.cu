@@ -120,20 +120,37 @@ struct TcArgs {
     TcPeer peer;  // multi-GPU hooks (all null / zero on one GPU)
     int gated_op; // FQ_GATED_* of the gated form
     unsigned sleep_ns;  // pause between polls of the roles that wait off the critical path (see mbar_wait)
+    // dense form, split-K tail: the tiles from `split_from` on (the last, partly filled wave of the persistent grid) are
+    // cut along K into `split_parts` work items each, so that wave runs on every SM for 1/split_parts of a tile's time.
+    // A part writes its f32 tile to partial[item - split_from][token][row]; splitk_reduce_kernel adds the parts in order.
+    int split_from;   // = number of tiles when nothing is split
+    int split_parts;  // a divisor of k / 256
+    float* partial;
 };
 
 // One output tile: weight rows [rt*128, +128) of matrix `mat` times activation rows [tok0, tok0+ntok).
 struct TileRef {
     int mat, rt, tok0, ntok;
+    int u0, u1;  // the 256-weight units of K this work item multiplies (all of them unless it is a split-K part)
+    int slot;    // -1, or the item's slot in TcArgs.partial
 };
+// Work item -> tile. Dense items below split_from are whole tiles; from there on, split_parts consecutive items share a tile.
 template <int TN>
-__device__ __forceinline__ TileRef tile_ref(const TcArgs& A, int tile, int row_tiles) {
+__device__ __forceinline__ TileRef tile_ref(const TcArgs& A, int item, int row_tiles, int units) {
     if (A.table) {
-        const TcTile t = A.table[tile];
-        return {t.mat, t.rt, t.tok0, t.ntok};
+        const TcTile t = A.table[item];
+        return {t.mat, t.rt, t.tok0, t.ntok, 0, units, -1};
+    }
+    int tile = item, u0 = 0, u1 = units, slot = -1;
+    if (item >= A.split_from) {
+        slot = item - A.split_from;
+        tile = A.split_from + slot / A.split_parts;
+        const int upp = units / A.split_parts;
+        u0 = (slot % A.split_parts) * upp;
+        u1 = u0 + upp;
     }
     const int tt = tile / row_tiles;  // consecutive CTAs share the token tile (L2 reuse) and take different weight rows
-    return {A.mat, tile % row_tiles, tt * TN, min(TN, A.m - tt * TN)};
+    return {A.mat, tile % row_tiles, tt * TN, min(TN, A.m - tt * TN), u0, u1, slot};
 }
 
 // Diagnostic build only (-DFQ_TIMELINE): the MMA thread of CTA 0 stamps, for the first slabs of its first tile,
@@ -578,7 +595,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
     const int mat_rows = A.w.n_mats > 1 ? (int)(A.w.mat_stride / A.w.row_stride) : n;  // rows between stacked matrices (n when dense)
     const int kslabs = k / BK, units = k >> 8;
     const int row_tiles = (n + BM - 1) / BM, tok_tiles = (m + TN - 1) / TN;
-    const int n_tiles = A.table ? *A.n_tiles_dev : row_tiles * tok_tiles;
+    const int n_tiles = A.table ? *A.n_tiles_dev : A.split_from + (row_tiles * tok_tiles - A.split_from) * A.split_parts;  // work items
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -629,8 +646,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 *(volatile int*)A.status = FQ_ERR_TIMEOUT;
             }
             for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
-                const TileRef T = tile_ref<TN>(A, tile, row_tiles);
-                for (int u = 0; u < PASSES * units && ok; ++u) {
+                const TileRef T = tile_ref<TN>(A, tile, row_tiles, units);
+                for (int u = T.u0; u < (PASSES - 1) * units + T.u1 && ok; ++u) {
                     for (int p = 0; p < 4; ++p, ++gb) {
                         const int s = gb % STAGES;
                         if (!mbar_wait(smem_u32(&B->empty[s]), ((gb / STAGES) & 1) ^ 1, B, A.status, A.sleep_ns)) {
@@ -661,7 +678,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 // (gated form: the gate pass of a tile fills the first accumulator, the up pass the second)
                 const int ai = t % NACC;
                 if (!GATED && !mbar_wait(smem_u32(&B->tmem_empty[ai]), ((t / NACC) & 1) ^ 1, B, A.status)) break;
-                const uint32_t idesc = umma_idesc(min(TN, (tile_ref<TN>(A, tile, row_tiles).ntok + 15) & ~15));
+                const TileRef T = tile_ref<TN>(A, tile, row_tiles, units);
+                const uint32_t idesc = umma_idesc(min(TN, (T.ntok + 15) & ~15));
+                const int ks0 = GATED ? 0 : 4 * T.u0, ks1 = GATED ? kslabs : 4 * T.u1;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 bool ok = true;
                 for (int ps = 0; ps < PASSES && ok; ++ps) {
@@ -672,7 +691,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 }
                 if (GATED) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem + (uint32_t)(aj * TN);
-                for (int ks = 0; ks < kslabs; ++ks, ++g) {
+                for (int ks = ks0; ks < ks1; ++ks, ++g) {
                     const int sa = g % STAGES, sb = sa;
                     TL_STAMP(ks, 0);
                     if (!mbar_wait(smem_u32(&B->full[sa]), (g / STAGES) & 1, B, A.status)) {
@@ -685,7 +704,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                     const uint64_t db = umma_desc(smem_u32(sB + sb * B_BYTES));
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk)  // 16 elements along K per instruction: 8 columns of A, 32 bytes of B
-                        umma_bf16_ts(acc, ta + 8 * kk, db + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
+                        umma_bf16_ts(acc, ta + 8 * kk, db + 2 * kk, idesc, ((ks - ks0) | kk) ? 1u : 0u);
                     TL_STAMP(ks, 3);
                     umma_commit(smem_u32(&B->empty[sa]));  // the stage is free once these MMAs have read it
                     TL_STAMP(ks, 4);
@@ -730,11 +749,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             return true;
         };
         for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
-            const TileRef T = tile_ref<TN>(A, tile, row_tiles);
+            const TileRef T = tile_ref<TN>(A, tile, row_tiles, units);
             for (int ps = 0; ps < PASSES && ok; ++ps) {
             const DevWeights& W = (GATED && ps) ? A.w2 : A.w;
             if (kStaged) {
-                for (int u = 0; u < units && ok; ++u, ++gu) {
+                for (int u = T.u0; u < T.u1 && ok; ++u, ++gu) {
                     const int rs = gu % RAW_STAGES;
                     if (!mbar_wait(smem_u32(&B->raw_full[rs]), (gu / RAW_STAGES) & 1, B, A.status)) {
                         ok = false;
@@ -759,7 +778,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                             raw.expand(p, h, v);
                         }
                         DQ_STAMP(4 * u + p, 2);
-                        if (!(ok = publish(v, gbase + 4 * u + p))) break;
+                        if (!(ok = publish(v, gbase + 4 * (u - T.u0) + p))) break;
                     }
                     // the loads above have returned (their values went into the stores): the unit may be overwritten
                     __syncwarp();
@@ -770,16 +789,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                 const int row = min(T.rt * BM + r, n - 1);
                 const uint8_t* unit0 = row_unit0(W, wbase, row, ub);
                 Raw<FMT> next;
-                next.load(W, unit0, ustride, par, h);
-                for (int ks = par; ks < kslabs; ks += kSlabSplit) {
+                const int ks0 = 4 * T.u0, ks1 = 4 * T.u1;
+                next.load(W, unit0, ustride, ks0 + par, h);
+                for (int ks = ks0 + par; ks < ks1; ks += kSlabSplit) {
                     const Raw<FMT> cur = next;
-                    if (ks + kSlabSplit < kslabs) next.load(W, unit0, ustride, ks + kSlabSplit, h);  // one slab ahead: the loads fly while this slab is expanded
+                    if (ks + kSlabSplit < ks1) next.load(W, unit0, ustride, ks + kSlabSplit, h);  // one slab ahead: the loads fly while this slab is expanded
                     uint32_t v[16];
                     cur.expand(ks, h, v);
-                    if (!(ok = publish(v, gbase + ks))) break;
+                    if (!(ok = publish(v, gbase + ks - ks0))) break;
                 }
             }
-            gbase += kslabs;
+            gbase += 4 * (T.u1 - T.u0);
             }
             ++dq_tile;
         }
@@ -791,11 +811,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
             int gu = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok && !B->abort_flag; tile += gridDim.x) {
-                const TileRef T = tile_ref<TN>(A, tile, row_tiles);
+                const TileRef T = tile_ref<TN>(A, tile, row_tiles, units);
                 for (int ps = 0; ps < PASSES && ok; ++ps) {
                 const DevWeights& W = (GATED && ps) ? A.w2 : A.w;
                 const CUtensorMap* tmw = (GATED && ps) ? &tmap_weights2 : &tmap_weights;
-                for (int u = 0; u < units; ++u, ++gu) {
+                for (int u = T.u0; u < T.u1; ++u, ++gu) {
                     const int rs = gu % RAW_STAGES;
                     if (!mbar_wait(smem_u32(&B->raw_empty[rs]), ((gu / RAW_STAGES) & 1) ^ 1, B, A.status, A.sleep_ns)) {
                         ok = false;
@@ -828,10 +848,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         // ---------------- epilogue: accumulator lane = weight row, column = token ----------------
         int t = 0;
         for (int tile = blockIdx.x; tile < n_tiles && !B->abort_flag; tile += gridDim.x, ++t) {
-            const TileRef T = tile_ref<TN>(A, tile, row_tiles);
+            const TileRef T = tile_ref<TN>(A, tile, row_tiles, units);
             const int rt = T.rt;
             const int q = warp & 3;                       // TMEM lane quarter this warp may read
             const int out_row = rt * BM + q * 32 + lane;  // weight row = output column
+            // a split-K part stores its whole f32 tile, [token][row], into its slot of the partial buffer
+            float* const dst = T.slot >= 0 ? A.partial + (size_t)T.slot * TN * BM + q * 32 + lane : A.c + (size_t)T.tok0 * A.ldc + out_row;
+            const size_t dst_ld = T.slot >= 0 ? (size_t)BM : (size_t)A.ldc;
             bool ok = true;
             for (int ps = 0; ps < PASSES; ++ps) {
                 const int ai = GATED ? ps : t % NACC;
@@ -896,7 +919,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
-                                if (c0 + j < T.ntok) A.c[(size_t)(T.tok0 + c0 + j) * A.ldc + out_row] = __uint_as_float(acc[j]);
+                                if (c0 + j < T.ntok) dst[(size_t)(c0 + j) * dst_ld] = __uint_as_float(acc[j]);
                             }
                         }
                     }
@@ -926,6 +949,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs A, co
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// Adds the split-K parts of the tail tiles in part order: c[token][row] = partial[0] + partial[1] + ...
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ c, int ldc, int n, int m, int row_tiles,
+                                     int split_from, int parts, int tail_tiles, int tn) {
+    const size_t per_tile = (size_t)tn * BM, total = (size_t)tail_tiles * per_tile;
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(idx / per_tile);
+        const int rem = (int)(idx % per_tile), tok = rem / BM, row = rem % BM;
+        const int tile = split_from + r, gtok = (tile / row_tiles) * tn + tok, grow = (tile % row_tiles) * BM + row;
+        if (gtok >= m || grow >= n) continue;
+        const float* p = partial + ((size_t)r * parts * tn + tok) * BM + row;
+        float sum = p[0];
+        for (int i = 1; i < parts; ++i) sum = __fadd_rn(sum, p[(size_t)i * per_tile]);
+        c[(size_t)gtok * ldc + grow] = sum;
     }
 }
 
@@ -1039,9 +1078,28 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
     if (int rc = encode_packed_rows(enc, up ? *up : w, &tmap_w2)) return rc;
     static const int diag = getenv("FUCINA_B200_TC_DIAG") ? atoi(getenv("FUCINA_B200_TC_DIAG")) : 0;
     static const unsigned sleep_ns = getenv("FUCINA_B200_TC_SLEEP_NS") ? (unsigned)atoi(getenv("FUCINA_B200_TC_SLEEP_NS")) : kProducerSleepNs;
-    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev, diag, up ? *up : w, g_out, peer ? *peer : TcPeer{}, gated_op, sleep_ns};
     const int tiles = table ? max_tiles : ((w.n + BM - 1) / BM) * (int)((rows + BN - 1) / BN);
     const int grid = tiles < ctx->sm_count ? (tiles > 0 ? tiles : 1) : ctx->sm_count;
+    TcArgs a{w, mat, c_dev, (int)rows, (int)ldc, ctx->status_dev, table, n_tiles_dev, diag, up ? *up : w, g_out, peer ? *peer : TcPeer{}, gated_op, sleep_ns,
+             tiles, 1, nullptr};
+    // Dense products of several waves whose last wave fills at most half the SMs: that wave's tiles are cut along K
+    // into as many parts as fit the grid (a power of two, at least two 256-weight units each), see TcArgs.
+    static const bool no_split = getenv("FUCINA_B200_TC_NO_SPLITK") != nullptr;
+    const int tail = tiles % grid, units = w.k / 256;
+    int parts = 1;
+    if (!table && !up && !no_split && tile_tokens == 256 && tiles > grid && tail > 0)
+        while (parts * 2 * tail <= grid && units % (parts * 2) == 0 && units / (parts * 2) >= 2) parts *= 2;
+    float* partial = nullptr;
+    if (parts > 1) {
+        partial = (float*)dev_alloc_on((size_t)tail * parts * 256 * BM * sizeof(float), st);
+        if (partial) a.split_from = tiles - tail, a.split_parts = parts, a.partial = partial;
+        else parts = 1;
+    }
+    struct FreePartial {
+        float* p;
+        cudaStream_t st;
+        ~FreePartial() { if (p) dev_free_on(p, st); }
+    } free_partial{partial, st};
     cudaError_t e;
     if (up) {  // gated form: the formats expert stacks come in
         switch (w.fmt) {
@@ -1062,6 +1120,11 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
         default: e = launch_tc<FQ_Q8_0>(a, tmap, tmap_w, grid, tile_tokens, st); break;
     }
     g_trace.launches++;
+    if (e == cudaSuccess && parts > 1) {
+        splitk_reduce_kernel<<<ctx->sm_count * 4, 256, 0, st>>>(partial, c_dev, (int)ldc, w.n, (int)rows, (w.n + BM - 1) / BM, a.split_from, parts, tail, 256);
+        e = cudaGetLastError();
+        g_trace.launches++;
+    }
     return e == cudaSuccess ? FQ_OK : cuda_fail(e, "tensor-core GEMM launch");
 }
 

@@ -142,3 +142,19 @@ def test_ptqtp_planes_on_the_tensor_cores(P, torch, planes):
     assert_close(cd.cpu().numpy(), want, TOL_TENSOR, f"ptqtp tensor K={planes}")
     for w in ws:
         w.free()
+
+
+@pytest.mark.parametrize("fmt_name", ["q4_k", "q8_0"])
+@pytest.mark.parametrize("m,n,k", [(200, 150 * 128, 1024), (300, 75 * 128 + 40, 2048)])
+def test_split_k_tail_of_a_partly_filled_last_wave(P, torch, fmt_name, m, n, k):
+    # more tiles than SMs with a last wave that fills at most half of them: its tiles are cut along K and the parts
+    # added in order by a second kernel (150 tiles = 148 + 2; 2 x 76 = 152 = 148 + 4, ragged rows and tokens)
+    from parity import oracle_b
+
+    fmt = oracle.FORMATS[fmt_name]
+    blocks = make_weights(fmt_name, n, k, seed=2300 + m)
+    a = np.random.default_rng(2301 + m).standard_normal((m, k)).astype(np.float32)
+    got = run_tensor(P, torch, fmt, blocks, a, n)
+    err = assert_close(got, oracle_b(fmt, blocks, a, k), TOL_TENSOR, f"{fmt_name} {m}x{n}x{k}")
+    assert err < 1e-3
+    assert not np.isnan(got).any()
