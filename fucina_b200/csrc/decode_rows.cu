@@ -421,6 +421,53 @@ __device__ __forceinline__ void unit_q8_0_swz(uint32_t base, int lane, const Act
     }
 }
 
+// ---- TQ2_0 (PTQTP planes): split rows [K/4 payload bytes][K/256 f16 scales]. A pipeline step is 512 weights of 32 rows:
+// one box of 32 x 128 payload bytes with the 128-byte swizzle (as above); the two f16 scales of the lane's row come
+// straight from global memory (`d2`, four bytes). Byte hg*32 + m of a 64-byte block holds elements hg*128 + n*32 + m in
+// crumb n (dtype.zig:215-218), so crumb n of a 16-byte chunk pairs with 16 consecutive activations. The block term is
+// (d * a.d) * f32(sum(code * a) - sum(a)) (ternary.zig:377-386).
+constexpr int kTqStageBytes = 4096;
+template <int MB>
+__device__ __forceinline__ void unit_tq2_0_swz(uint32_t base, int lane, const ActView& V, int sl, uint32_t d2, float (&acc)[MB]) {
+    const uint32_t x = (uint32_t)(lane & 7);
+    const uint32_t rowp = base + (uint32_t)lane * 128;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int kb = sl * 2 + half;
+        const float dw = __half2float(__ushort_as_half((unsigned short)((d2 >> (16 * half)) & 0xffffu)));
+        // crumb n stays in place (a byte worth code * 4^n, unsigned): one mask per word instead of a shift and a mask;
+        // the factor leaves each 16-weight integer sum by an exact shift
+        int dot[MB];
+#pragma unroll
+        for (int b = 0; b < MB; ++b) dot[b] = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // chunk j of the block: half-group j / 2, bytes (j % 2) * 16 ..+15
+            const uint4 wq = lds128(rowp + ((((uint32_t)(half * 4 + j)) ^ x) << 4));
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                // (the top crumb would make a byte of 128 or more, which the signed instruction cannot take: it is shifted down)
+                const int sh = n == 3 ? 6 : 0;
+                const uint32_t mask = n == 3 ? 0x03030303u : 0x03030303u << (2 * n);
+                const uint32_t w[4] = {(wq.x >> sh) & mask, (wq.y >> sh) & mask, (wq.z >> sh) & mask, (wq.w >> sh) & mask};
+#pragma unroll
+                for (int b = 0; b < MB; ++b) {
+                    const uint4 a = lds128(V.base + b * V.row + kb * 256 + (j >> 1) * 128 + n * 32 + (j & 1) * 16);
+                    dot[b] += dot16_ss(w, a, 0) >> (n == 3 ? 0 : 2 * n);
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < MB; ++b) {
+            const uint32_t rec = V.base + b * V.row;
+            const float da = lds_f32(rec + V.off_ad + kb * 4);
+            const uint4 s0 = lds128(rec + V.off_sums + kb * 32), s1 = lds128(rec + V.off_sums + kb * 32 + 16);
+            const int asum = (int)s0.x + (int)s0.y + (int)s0.z + (int)s0.w + (int)s1.x + (int)s1.y + (int)s1.z + (int)s1.w;
+            const int isum = dot[b] - asum;
+            acc[b] = __fadd_rn(acc[b], __fmul_rn(__fmul_rn(dw, da), (float)isum));
+        }
+    }
+}
+
 // Geometry of one slab (what a lane fetches per pipeline step).
 struct SlabGeom {
     int unit_bytes;    // payload bytes per 256 weights
@@ -456,7 +503,8 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
     constexpr bool Q8K = FMT != FQ_Q8_0;
     const NatSizes NS = nat_sizes(Q8K, k);
     const SlabGeom G = slab_geom(FMT, A.slab);
-    const int units = k >> 8;                                // 256-weight units per row
+    constexpr bool TQ = FMT == FQ_TQ2_0;
+    const int units = TQ ? (k >> 9) : (k >> 8);              // pipeline units per row: 256 weights (TQ2_0: 512)
     const int nslabs = (units + A.slab - 1) / A.slab;        // slabs per row
     const int my_slabs = warp < nslabs ? (nslabs - warp + kWarps - 1) / kWarps : 0;
 
@@ -467,9 +515,9 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
     uint8_t* slots = reinterpret_cast<uint8_t*>(red) + 2 * kWarps * MB * 32 * sizeof(float);
     // bytes between the stages of a warp; Q8_0 staged by tensor copies uses whole 1024-byte aligned stages
     const bool q8_boxes = FMT == FQ_Q8_0 && A.use_tmap == 2;
-    const uint32_t stage_stride = q8_boxes ? (uint32_t)kQ8StageBytes : (uint32_t)(32 * G.slot_bytes);
-    const uint32_t slot0 = q8_boxes ? ((smem_u32(slots) + 1023u) & ~1023u) + (uint32_t)(warp * A.stages) * kQ8StageBytes
-                                    : smem_u32(slots) + (uint32_t)((warp * A.stages) * 32 + lane) * G.slot_bytes;
+    const uint32_t stage_stride = TQ ? (uint32_t)kTqStageBytes : q8_boxes ? (uint32_t)kQ8StageBytes : (uint32_t)(32 * G.slot_bytes);
+    const uint32_t slot0 = (TQ || q8_boxes) ? ((smem_u32(slots) + 1023u) & ~1023u) + (uint32_t)(warp * A.stages) * stage_stride
+                                            : smem_u32(slots) + (uint32_t)((warp * A.stages) * 32 + lane) * G.slot_bytes;
     const uint32_t bar0 = smem_u32(bars) + warp * kMaxStages * 8;
 
     stamp(0);
@@ -530,6 +578,18 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
                     bulk_load_stream(slot0 + (uint32_t)stage * 32 * G.slot_bytes, src, bytes, bar, l2_policy);
                 else
                     bulk_load(slot0 + (uint32_t)stage * 32 * G.slot_bytes, src, bytes, bar);
+            }
+            return;
+        }
+        if (TQ) {
+            // TQ2_0 split rows: one swizzled payload box of 32 rows x 128 bytes (512 weights per row)
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar, (uint32_t)kTqStageBytes);
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                        slot0 + (uint32_t)stage * stage_stride),
+                    "l"(&tmap), "r"(sl * 128), "r"(row0), "r"(bar)
+                    : "memory");
             }
             return;
         }
@@ -654,7 +714,7 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
         for (int i = threadIdx.x; i < MB * units_per_rec; i += kThreads)
             dst[i] = (i / units_per_rec < A.m) ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
     }
-    if (FUSED && A.slab == 1)
+    if (FUSED && A.slab == 1 && !TQ)  // (a TQ2_0 step spans two activation blocks, quantised by two different warps)
         __syncwarp();
     else
         __syncthreads();
@@ -666,7 +726,7 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
     for (int tile = 0; tile < ntiles; ++tile) {
         // K-quant batches of 3..16 rows (MB = 8 or 16) multiply through the warp-level tensor-core instruction:
         // acc then holds the fragment layout of expert_block_mma, eight values per group of eight rows
-        constexpr bool kMma = FMT != FQ_Q8_0 && MB >= 8;
+        constexpr bool kMma = FMT != FQ_Q8_0 && !TQ && MB >= 8;
         float acc[MB];
 #pragma unroll
         for (int b = 0; b < MB; ++b) acc[b] = 0.0f;
@@ -674,6 +734,12 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
             const int sl = warp + kWarps * j;
             const int stage = it % A.stages;
             const uint32_t parity = (uint32_t)(it / A.stages) & 1u;
+            uint32_t tq_scales = 0;  // TQ2_0: the two f16 scales of this lane's row for this step, fetched while the box is in flight
+            if (TQ) {
+                int row0, nvalid;
+                tile_rows(tile, row0, nvalid);
+                tq_scales = __ldg(reinterpret_cast<const uint32_t*>(wbase + (size_t)min(row0 + lane, n - 1) * A.w.row_stride + (size_t)(k >> 2)) + sl);
+            }
             if (!mbar_wait(bar0 + stage * 8, parity)) {
                 ok = false;
                 break;
@@ -700,6 +766,7 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
                     if (q8_boxes) unit_q8_0_swz<MB>(p, lane, V, kb, acc);
                     else unit_q8_0<MB>(p + u * 256, p + G.scale_off + u * 16, V, kb, acc);
                 }
+                if (TQ) unit_tq2_0_swz<MB>(p, lane, V, kb, tq_scales, acc);
             }
             __syncwarp();  // every lane is done with this stage before it is refilled
             if (it + A.stages < total) issue(it + A.stages);
@@ -723,7 +790,8 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
                 const int tok = (b >> 3) * 8 + 2 * (lane & 3) + (i & 1);
                 if (r < nvalid && tok < A.m) A.c[out_index(A, tok, row0 + r)] = s;
             } else if (lane < nvalid && b < A.m) {
-                A.c[out_index(A, b, row0 + lane)] = s;
+                float* o = A.c + out_index(A, b, row0 + lane);
+                *o = A.accumulate ? __fadd_rn(*o, s) : s;  // (sums of PTQTP planes: plane order is launch order)
             }
         }
     }
@@ -752,7 +820,9 @@ size_t smem_bytes(int fmt, int k, int mb, int slab, int stages, int warps) {
 
 // 16 warps per CTA double the thread-level parallelism that hides shared-memory and dp4a latency;
 // they need 16 units per row to split and the register budget of the small-batch variants.
+int tq_warps(int k, int mb);
 int pick_warps(int fmt, int k, int mb) {
+    if (fmt == FQ_TQ2_0) return tq_warps(k, mb);
     static const int forced = getenv("FUCINA_B200_DECODE_WARPS") ? atoi(getenv("FUCINA_B200_DECODE_WARPS")) : 0;
     if (forced == 8) return 8;
     static const bool wide8 = getenv("FUCINA_B200_DECODE_WIDE8") ? atoi(getenv("FUCINA_B200_DECODE_WIDE8")) != 0 : true;
@@ -766,7 +836,7 @@ int pad_rows(size_t m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
 // eight tokens; Q8_0 keeps dp4a up to eight rows.
 constexpr int kMaxDecodeRows = 16;
 int decode_pad_rows(int fmt, size_t m) {
-    if (fmt == FQ_Q8_0 || m <= 2) return pad_rows(m);
+    if (fmt == FQ_Q8_0 || fmt == FQ_TQ2_0 || m <= 2) return pad_rows(m);
     return m <= 8 ? 8 : 16;
 }
 
@@ -856,6 +926,24 @@ bool make_q8_tmaps(const DevWeights& w, int mat, CUtensorMap* payload, CUtensorM
     return fn(scales, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base + w.k, sdims, strides, sbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+// TQ2_0: payload map over the first plane (box 128 bytes = 512 weights x 32 rows, 128-byte swizzle)
+bool make_tq_tmap(const DevWeights& w, int mat, CUtensorMap* payload) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    uint8_t* base = const_cast<uint8_t*>(w.base) + (size_t)mat * w.mat_stride;
+    if (((uintptr_t)base & 15) || (w.row_stride & 15)) return false;
+    const cuuint32_t estr[2] = {1, 1};
+    const cuuint64_t strides[1] = {(cuuint64_t)w.row_stride};
+    const cuuint64_t pdims[2] = {(cuuint64_t)w.k / 4, (cuuint64_t)w.n};
+    const cuuint32_t pbox[2] = {128, 32};
+    return fn(payload, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, pdims, strides, pbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+int tq_warps(int k, int mb) { return (k / 512 >= 16 && mb <= 2) ? 16 : 8; }
+size_t smem_bytes_tq_boxes(int k, int mb, int stages, int warps) {
+    const NatSizes NS = nat_sizes(true, (size_t)k);
+    return 512 + ((mb * NS.row + 127) & ~(size_t)127) + (size_t)2 * warps * mb * 32 * sizeof(float) + 1024 + (size_t)warps * stages * kTqStageBytes;
+}
 size_t smem_bytes_q8_boxes(int k, int mb, int stages) {
     const NatSizes NS = nat_sizes(false, (size_t)k);
     return 512 + ((mb * NS.row + 127) & ~(size_t)127) + (size_t)2 * 8 * mb * 32 * sizeof(float) + 1024 + (size_t)8 * stages * kQ8StageBytes;
@@ -908,6 +996,15 @@ cudaError_t launch_fmt(const RowsArgs& a, const CUtensorMap& tmap, const CUtenso
     }
 }
 
+
+// TQ2_0 has the dp4a block product only: batches of one, two and four rows
+cudaError_t launch_fmt_tq(const RowsArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap2, int mb, bool fused, int grid, size_t smem, cudaStream_t st) {
+    switch (mb) {
+        case 1: return launch_fmt_mb<FQ_TQ2_0, 1>(a, tmap, tmap2, fused, false, grid, smem, st);
+        case 2: return launch_fmt_mb<FQ_TQ2_0, 2>(a, tmap, tmap2, fused, false, grid, smem, st);
+        default: return launch_fmt_mb<FQ_TQ2_0, 4>(a, tmap, tmap2, fused, false, grid, smem, st);
+    }
+}
 
 // ---------------------------------------------------------------------------------------------
 // Grouped form for MoE expert stacks at decode batch sizes: the same row-per-lane arithmetic over
@@ -1194,6 +1291,13 @@ cudaError_t launch_bounded_wait_probe(int* status, unsigned limit, cudaStream_t 
 }
 
 bool decode_rows_eligible(const DevWeights& w, size_t m) {
+    if (w.fmt == FQ_TQ2_0) {
+        static const bool off = getenv("FUCINA_B200_NO_TQ_DECODE") != nullptr;
+        if (off || m < 1 || m > (size_t)kFusedMaxRows || w.k % 512 != 0 || w.k < 2048 || w.n < 64 || w.tile_rows || !encode_tiled_fn()) return false;
+        if (((uintptr_t)w.base & 15) || (w.row_stride & 15) || (w.mat_stride & 15)) return false;
+        const int mb = pad_rows(m);
+        return smem_bytes_tq_boxes(w.k, mb, 2, tq_warps(w.k, mb)) <= kSmemLimit;
+    }
     if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q8_0) return false;
     if (m < 1 || m > (size_t)(w.fmt == FQ_Q8_0 ? 8 : kMaxDecodeRows) || w.k % 256 != 0 || w.k < 2048 || w.n < 64) return false;
     int slab, stages;
@@ -1209,12 +1313,24 @@ size_t decode_rows_scratch_bytes(const DevWeights& w, size_t m) {
 bool decode_rows_fuses_prologue(const DevWeights& w, size_t m) { return decode_rows_eligible(w, m) && (int)m <= kFusedMaxRows && w.k / 256 <= 512; }
 
 cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev, uint8_t* scratch, float* c, int m, int ldc,
-                               int sm_count, int* status, cudaStream_t st, int split_n, const PreArgs* pre) {
+                               int sm_count, int* status, cudaStream_t st, int split_n, const PreArgs* pre, int accumulate) {
     const int mb = decode_pad_rows(w.fmt, (size_t)m);
     static const int skip = getenv("FUCINA_B200_DECODE_SKIP_COMPUTE") ? 1 : 0;  // diagnosis: copy pipeline only, outputs are garbage
     static const int l2_stream = getenv("FUCINA_B200_DECODE_L2_STREAM") ? atoi(getenv("FUCINA_B200_DECODE_L2_STREAM")) : 1;
-    RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0, skip, l2_stream, 0, split_n, pre ? *pre : PreArgs{FQ_PRE_NONE, nullptr, 0.0f}};
+    RowsArgs a{w, mat, a_dev, scratch, c, m, ldc, 1, 2, status, 0, skip, l2_stream, 0, split_n, pre ? *pre : PreArgs{FQ_PRE_NONE, nullptr, 0.0f}, accumulate};
     if (a.pre.op != FQ_PRE_NONE && !decode_rows_fuses_prologue(w, (size_t)m)) return cudaErrorInvalidValue;
+    if (w.fmt == FQ_TQ2_0) {
+        CUtensorMap tm, tm2;
+        memset(&tm2, 0, sizeof tm2);
+        if (!make_tq_tmap(w, mat, &tm)) return cudaErrorInvalidValue;
+        const int warps = tq_warps(w.k, mb);
+        a.slab = 1;
+        a.use_tmap = 3;
+        a.stages = smem_bytes_tq_boxes(w.k, mb, 3, warps) <= kSmemLimit ? 3 : 2;
+        int grid_tq = sm_count;
+        if (grid_tq > (w.n + 31) / 32) grid_tq = (w.n + 31) / 32;
+        return launch_fmt_tq(a, tm, tm2, mb, true, grid_tq, smem_bytes_tq_boxes(w.k, mb, a.stages, warps), st);
+    }
     if (!pick_config(w.fmt, w.k, mb, &a.slab, &a.stages)) return cudaErrorInvalidValue;
     // K-quant units are an odd number of 16-byte chunks: one tensor copy per warp step instead of 32
     // per-lane bulk copies (small bulk copies are issue-rate bound in the copy engine)

@@ -80,6 +80,7 @@ struct RowsArgs {
     int split_n;      // 0, or the rows of ONE matrix when w stacks several that share the activations: weight row r
                       // of token b lands at c[((r / split_n) * m + b) * split_n + r % split_n] (the [batch][m][n] layout)
     PreArgs pre;      // activation prologue applied while quantising (fused form only): rms_norm_mul or split_swiglu
+    int accumulate;   // add to c instead of overwriting it (TQ2_0 form: the planes of a PTQTP product)
 };
 // Grouped expert form of the row-per-lane kernel (MoE decode): a device-built table of (expert, run of
 // <= 8 activation rows) entries over a row-major expert stack; the f32 activation rows are quantised
@@ -112,7 +113,7 @@ bool decode_rows_eligible(const DevWeights& w, size_t m);
 size_t decode_rows_scratch_bytes(const DevWeights& w, size_t m);
 // `pre` (optional): an activation prologue fused into the kernel's quantiser; only where decode_rows_fuses_prologue
 cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev, uint8_t* scratch, float* c, int m, int ldc,
-                               int sm_count, int* status, cudaStream_t st, int split_n = 0, const PreArgs* pre = nullptr);
+                               int sm_count, int* status, cudaStream_t st, int split_n = 0, const PreArgs* pre = nullptr, int accumulate = 0);
 bool decode_rows_fuses_prologue(const DevWeights& w, size_t m);
 // formats.cu -- the stand-alone form of the activation prologues: out[m][k] (split_swiglu reads 2k values per row)
 cudaError_t launch_act_prologue(const PreArgs& pre, const float* a, float* out, int m, int k, cudaStream_t st);

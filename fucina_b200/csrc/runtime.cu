@@ -566,7 +566,7 @@ int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* 
         // shapes the tensor-core kernel does not take fall through to the integer kernel
     }
     // dense decode shapes: the row-per-lane kernel with TMA-staged weights
-    if (!accumulate && g_decode_rows_on && decode_rows_eligible(w, m)) {
+    if ((!accumulate || w.fmt == FQ_TQ2_0) && g_decode_rows_on && decode_rows_eligible(w, m)) {
         const size_t sb = decode_rows_scratch_bytes(w, m);
         uint8_t* nat = sb ? (uint8_t*)dev_alloc_on(sb, st) : nullptr;
         if (sb && !nat) return fail(FQ_DECLINED_BUDGET, "activation scratch allocation failed");
@@ -576,7 +576,7 @@ int gemm_dev(Ctx* ctx, const DevWeights& w, int mat, const float* a_dev, float* 
             t1 = ktime_event();
             cudaEventRecord(t0, st);
         }
-        cudaError_t e = launch_decode_rows(w, mat, a_dev, nat, c_dev, (int)m, (int)ldc, ctx->sm_count, ctx->status_dev, st, split_n, pre);
+        cudaError_t e = launch_decode_rows(w, mat, a_dev, nat, c_dev, (int)m, (int)ldc, ctx->sm_count, ctx->status_dev, st, split_n, pre, accumulate);
         if (g_ktime_on) {
             cudaEventRecord(t1, st);
             g_ktime_events.emplace_back(t0, t1);

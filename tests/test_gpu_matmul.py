@@ -203,3 +203,40 @@ def test_int8_path_stays_near_the_dequantised_product(P, torch):
     want = oracle.matmul_dequant_f64(oracle.Q4_K, blocks, a)
     rms = float(np.sqrt(np.mean(want**2)))
     assert float(np.max(np.abs(got - want))) < 0.05 * rms
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
+@pytest.mark.parametrize("n,k", [(64, 2048), (100, 2560), (1000, 4096), (8192, 8192), (4747, 3072)])
+def test_ternary_planes_in_the_copy_engine_decode_kernel(P, torch, m, n, k):
+    # TQ2_0 rows with k % 512 == 0 and up to four activation rows stream through the TMA-staged decode kernel
+    # (16 warps from k = 8192); ragged row counts, more tiles than SMs, 8- and 16-warp forms
+    blocks = make_weights("tq2_0", n, k, seed=1300 + n)
+    a = acts(m, k, 1301 + m)
+    got = run_dev(P, torch, oracle.TQ2_0, blocks, a, n)
+    sl = slice(0, min(n, 1024))   # the scalar oracle on a slice of the largest shapes
+    assert_close(got[:, sl], oracle.matmul(oracle.TQ2_0, blocks[sl], a), TOL_INT8, f"tq2_0 decode {m}x{n}x{k}")
+    if n > 1024:
+        tail = slice(n - 300, n)
+        assert_close(got[:, tail], oracle.matmul(oracle.TQ2_0, blocks[tail], a), TOL_INT8, f"tq2_0 decode tail {m}x{n}x{k}")
+    assert not np.isnan(got).any()
+
+
+@pytest.mark.parametrize("planes", [2, 3])
+def test_ptqtp_plane_sum_at_decode_width(P, torch, planes):
+    # the planes of one product accumulate in launch order inside the decode kernel (k = 4096 takes that kernel)
+    n, k, m = 300, 4096, 2
+    rng = np.random.default_rng(1400)
+    ps = []
+    for p in range(planes):
+        trits = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+        scales = np.abs(rng.standard_normal((n, k // 256)) * 0.02 / (3**p)).astype(np.float32)
+        ps.append(oracle.pack_ptqtp_plane(trits, scales))
+    a = acts(m, k, 1401)
+    ws = [P.Weights.upload(oracle.TQ2_0, b, n, k) for b in ps]
+    ad = torch.from_numpy(a).cuda()
+    cd = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    P.gemm_ptqtp_dev(ws, ad, cd, m)
+    P.synchronize()
+    assert_close(cd.cpu().numpy(), oracle.matmul_ptqtp(ps, a), TOL_INT8, f"ptqtp K={planes} k={k}")
+    for w in ws:
+        w.free()
