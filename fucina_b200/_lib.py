@@ -101,6 +101,17 @@ SIGNATURES = {
     "fq_set_moe_tensor_for_test": (None, [c_int]),
     "fq_set_group_grid_limit_for_test": (None, [c_int]),
     "fq_moe_layer_stages_for_test": (c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_void, c_void, c_void]),
+    "fq_gguf_open": (c_int, [C.c_char_p, P(c_void)]),
+    "fq_gguf_close": (None, [c_void]),
+    "fq_gguf_tensor_count": (c_size, [c_void]),
+    "fq_gguf_tensor_at": (c_int, [c_void, c_size, c_void]),
+    "fq_gguf_find": (c_int, [c_void, C.c_char_p]),
+    "fq_gguf_tensor_data": (c_void, [c_void, c_size]),
+    "fq_gguf_meta_u64": (c_int, [c_void, C.c_char_p, P(c_u64)]),
+    "fq_gguf_meta_str": (c_int, [c_void, C.c_char_p, C.c_char_p, c_size]),
+    "fq_gguf_load_weights": (c_int, [c_void, c_size, c_size, c_size, c_size, c_size, P(c_void)]),
+    "fq_gguf_load_ptqtp_planes": (c_int, [c_void, C.c_char_p, c_size, c_size, c_size, c_size, P(c_void), P(c_int)]),
+    "fq_gguf_shard_rows": (c_int, [c_size, c_int, c_int, c_size, P(c_size), P(c_size)]),
     "fq_selftest_bounded_wait": (c_int, [C.c_uint]),
     "fq_trace_enabled": (c_int, []),
     "fq_trace_reset": (None, []),

@@ -415,6 +415,24 @@ static int weights_from_dev_bytes(Ctx* ctx, int fmt, const uint8_t* raw_dev, siz
     return FQ_OK;
 }
 
+// Empty device weights in the layout weights_from_dev_bytes would choose; the caller repacks into them piece by piece.
+int weights_alloc_layout(Ctx* ctx, int fmt, size_t n, size_t k, size_t n_mats, bool allow_tile, fq_weights** out) {
+    if (int rc = check_dims(fmt, n, k, n_mats, fq_row_bytes(fmt, k), fq_row_bytes(fmt, k) * n)) return rc;
+    const bool tile = want_tile_major(fmt, n, k, n_mats, allow_tile);
+    const size_t stride = dev_row_stride(fmt, k);
+    const size_t mat_stride = stride * (tile ? (n + 31) / 32 * 32 : n);
+    const size_t bytes = mat_stride * n_mats;
+    void* p = dev_alloc(bytes);
+    if (!p) return fail(FQ_DECLINED_BUDGET, "device allocation of %zu bytes failed", bytes);
+    if (tile && n % 32 != 0) cudaMemsetAsync(p, 0, bytes, ctx->stream);  // rows padding the last tile read as zero blocks
+    fq_weights* w = new fq_weights();
+    w->dw = {(const uint8_t*)p, stride, mat_stride, fmt, (int)n, (int)k, (int)n_mats, tile ? 32 : 0};
+    w->alloc = p;
+    w->bytes = bytes;
+    *out = w;
+    return FQ_OK;
+}
+
 static int weights_upload_impl(Ctx* ctx, int fmt, const void* host, size_t nb01, size_t nb02, size_t n, size_t k, size_t n_mats,
                                bool allow_tile, fq_weights** out) {
     if (int rc = check_dims(fmt, n, k, n_mats, nb01, nb02)) return rc;

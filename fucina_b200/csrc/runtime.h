@@ -49,6 +49,10 @@ void dev_free_idle(void* p);  // for a block whose last use the host has already
 void* pin_alloc(size_t n);
 void pin_free(void* p);
 
+// Empty device weights in the layout an upload of this shape gets (tile-major for dense K-quants the decode kernel
+// serves); gguf.cu repacks into them chunk by chunk.
+int weights_alloc_layout(Ctx* ctx, int fmt, size_t n, size_t k, size_t n_mats, bool allow_tile, fq_weights** out);
+
 // Host rhs bytes -> device view (resident registry hit, adoption, or a
 // transient upload the caller frees through *temp after its launches).
 int resolve_rhs(Ctx* ctx, int fmt, const void* rhs, size_t rhs_len, int cacheable, size_t nb01, size_t nb02, size_t n, size_t k,

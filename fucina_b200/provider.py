@@ -10,6 +10,7 @@ CPU.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import numpy as np
 
@@ -167,6 +168,83 @@ class Weights:
             self.free()
         except Exception:
             pass
+
+
+class _GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("ggml_type", C.c_int), ("fmt", C.c_int), ("n_dims", C.c_int), ("dims", C.c_uint64 * 4),
+                ("offset", C.c_uint64), ("bytes", C.c_uint64)]
+
+
+class Gguf:
+    """A mapped GGUF file (`fq_gguf`): tensor table and metadata without a GPU, resident weights with one.
+
+    Mirrors what the reference does with src/gguf.zig + the residency hooks of src/weights.zig:2621-2816."""
+
+    def __init__(self, path: str):
+        h = C.c_void_p()
+        _check(load().fq_gguf_open(os.fsencode(path), C.byref(h)))
+        self.handle = h.value
+
+    def tensors(self) -> list[dict]:
+        out = []
+        for i in range(int(load().fq_gguf_tensor_count(self.handle))):
+            t = _GgufTensor()
+            _check(load().fq_gguf_tensor_at(self.handle, i, C.byref(t)))
+            out.append({"name": t.name.decode(), "ggml_type": t.ggml_type, "fmt": t.fmt, "dims": list(t.dims[: t.n_dims]),
+                        "offset": int(t.offset), "bytes": int(t.bytes)})
+        return out
+
+    def find(self, name: str) -> int:
+        return int(load().fq_gguf_find(self.handle, name.encode()))
+
+    def data(self, index: int, nbytes: int) -> np.ndarray:
+        p = load().fq_gguf_tensor_data(self.handle, index)
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(nbytes,)).copy()
+
+    def meta_u64(self, key: str) -> int:
+        v = C.c_uint64()
+        _check(load().fq_gguf_meta_u64(self.handle, key.encode(), C.byref(v)))
+        return int(v.value)
+
+    def meta_str(self, key: str) -> str:
+        buf = C.create_string_buffer(4096)
+        _check(load().fq_gguf_meta_str(self.handle, key.encode(), buf, len(buf)))
+        return buf.value.decode()
+
+    def load_weights(self, name: str, row0: int = 0, rows: int = 0, mat0: int = 0, mats: int = 0) -> Weights:
+        i = self.find(name)
+        if i < 0:
+            raise KeyError(name)
+        t = self.tensors()[i]
+        h = C.c_void_p()
+        _check(load().fq_gguf_load_weights(self.handle, i, row0, rows, mat0, mats, C.byref(h)))
+        dims = t["dims"] + [1] * (3 - len(t["dims"]))
+        return Weights(h.value, t["fmt"], rows or dims[1] - row0, dims[0], mats or dims[2] - mat0)
+
+    def load_ptqtp_planes(self, base: str, row0: int = 0, rows: int = 0, mat0: int = 0, mats: int = 0) -> list[Weights]:
+        arr = (C.c_void_p * 3)()
+        n = C.c_int()
+        _check(load().fq_gguf_load_ptqtp_planes(self.handle, base.encode(), row0, rows, mat0, mats, arr, C.byref(n)))
+        t = self.tensors()[self.find(base + ".ptqtp0")]
+        dims = t["dims"] + [1] * (3 - len(t["dims"]))
+        return [Weights(arr[p], formats.TQ2_0, rows or dims[1] - row0, dims[0], mats or dims[2] - mat0) for p in range(n.value)]
+
+    def close(self) -> None:
+        if self.handle:
+            load().fq_gguf_close(self.handle)
+            self.handle = 0
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def shard_rows(n: int, n_ranks: int, rank: int, align: int = 32) -> tuple[int, int]:
+    r0, rows = C.c_size_t(), C.c_size_t()
+    _check(load().fq_gguf_shard_rows(n, n_ranks, rank, align, C.byref(r0), C.byref(rows)))
+    return int(r0.value), int(rows.value)
 
 
 def quantize_rows_dev(fmt: int, dev_src, n: int, k: int, dev_blocks) -> None:

@@ -140,6 +140,38 @@ FQ_API int fq_dequantize_rows_dev(const fq_weights* w, size_t mat, size_t row0, 
  * -> raw GGUF blocks in HBM, byte-identical to the CPU encoders. */
 FQ_API int fq_quantize_rows_dev(int fmt, const float* dev_src, size_t n, size_t k, void* dev_blocks);
 
+/* ---- GGUF file -> device-resident weights (new on the GPU side). The reference parses GGUF in src/gguf.zig
+ *      (:214-452: header, metadata, tensor table, data section aligned to general.alignment) and makes quantized
+ *      tensors GPU-resident in src/weights.zig:2621-2816; here the mapped blocks of a row / expert range go straight
+ *      to the repacked device layouts through two page-locked staging buffers, so file reads, copies and repack
+ *      kernels overlap. Opening and querying need no GPU. ---- */
+typedef struct fq_gguf fq_gguf;
+typedef struct {
+    const char* name;   /* valid until fq_gguf_close */
+    int ggml_type;      /* ggml_type id as stored */
+    int fmt;            /* FQ_* format id, or -1 when the type is not a served quantized format */
+    int n_dims;         /* 1..4; dims[0] is the row length (k), dims[1] the rows, dims[2] the matrices (experts) */
+    uint64_t dims[4];
+    uint64_t offset;    /* from the start of the file */
+    uint64_t bytes;     /* 0 when this reader cannot size the type */
+} fq_gguf_tensor;
+FQ_API int fq_gguf_open(const char* path, fq_gguf** out);
+FQ_API void fq_gguf_close(fq_gguf* g);
+FQ_API size_t fq_gguf_tensor_count(const fq_gguf* g);
+FQ_API int fq_gguf_tensor_at(const fq_gguf* g, size_t i, fq_gguf_tensor* out);
+FQ_API int fq_gguf_find(const fq_gguf* g, const char* name);        /* index, or -1 (src/gguf.zig:546 maybeGet) */
+FQ_API const void* fq_gguf_tensor_data(const fq_gguf* g, size_t i); /* the tensor's bytes inside the mapping */
+FQ_API int fq_gguf_meta_u64(const fq_gguf* g, const char* key, uint64_t* out);            /* src/gguf.zig:511 getInt */
+FQ_API int fq_gguf_meta_str(const fq_gguf* g, const char* key, char* buf, size_t len);    /* NUL-terminated, cut to len - 1 */
+/* Rows [row0, row0 + rows) of matrices [mat0, mat0 + mats) of tensor i as resident weights (rows == 0 / mats == 0:
+ * to the end): the shard a rank owns of a column-sharded linear or of an expert stack. */
+FQ_API int fq_gguf_load_weights(const fq_gguf* g, size_t i, size_t row0, size_t rows, size_t mat0, size_t mats, fq_weights** out);
+/* The trit planes `<base>.ptqtp0/1/2` of a PTQTP model (src/ptqtp_gguf.zig:95-98): every plane present, in order. */
+FQ_API int fq_gguf_load_ptqtp_planes(const fq_gguf* g, const char* base, size_t row0, size_t rows, size_t mat0, size_t mats,
+                                     fq_weights* planes_out[3], int* n_planes);
+/* Even split of n rows over n_ranks in steps of `align` rows (32 keeps tile-major shards on tile boundaries). */
+FQ_API int fq_gguf_shard_rows(size_t n, int n_ranks, int rank, size_t align, size_t* row0, size_t* rows);
+
 /* ---- dense quantized matmul, host buffers ----
  * backend/cuda.zig:2398-2435 `gemmQuantNt` (blocking), :2441-2492
  * `gemmQuantNtSharedABatch`. `rhs_len` is the byte length of the rhs range. */
