@@ -101,6 +101,10 @@ SIGNATURES = {
     "fq_set_moe_tensor_for_test": (None, [c_int]),
     "fq_set_group_grid_limit_for_test": (None, [c_int]),
     "fq_moe_layer_stages_for_test": (c_int, [c_void, c_void, c_void, c_void, c_size, c_size, c_void, c_void, c_void, c_void, c_void]),
+    "fq_attn_fwd_dev": (c_int, [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_size, c_size, c_size, c_size, c_size, c_size,
+                                C.c_float, c_size, c_int, c_void]),
+    "fq_attn_fwd": (c_int, [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_size, c_size, c_size, c_size, c_size, c_size, C.c_float,
+                            c_size, c_int]),
     "fq_gguf_open": (c_int, [C.c_char_p, P(c_void)]),
     "fq_gguf_close": (None, [c_void]),
     "fq_gguf_tensor_count": (c_size, [c_void]),

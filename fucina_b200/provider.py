@@ -170,6 +170,30 @@ class Weights:
             pass
 
 
+def attn_fwd(q: np.ndarray, k: np.ndarray, v: np.ndarray, kv_head_for_head, source_offset: int, scale: float, window: int = 0,
+             causal: bool = True, want_stats: bool = False):
+    """Twin of `attnPrefillF16` / the f32-KV forward (src/backend/cuda.zig:2601-2736): q [q_seq, heads, d] f32,
+    k/v [kv_seq, kv_heads, d] f16 or f32 -> out [q_seq, heads, d] (and stats [heads, q_seq, 2])."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    f16 = k.dtype == np.float16
+    k = np.ascontiguousarray(k, dtype=np.float16 if f16 else np.float32)
+    v = np.ascontiguousarray(v, dtype=k.dtype)
+    q_seq, heads, d = q.shape
+    kv_seq, kv_heads, _ = k.shape
+    kvmap = np.ascontiguousarray(kv_head_for_head, dtype=np.int32)
+    out = np.full_like(q, np.nan)
+    stats = np.full((heads, q_seq, 2), np.nan, dtype=np.float32) if want_stats else None
+    _check(load().fq_attn_fwd(_vp(q), _vp(k), _vp(v), int(f16), _vp(out), _vp(stats), _vp(kvmap), q_seq, kv_seq, heads, kv_heads, d,
+                              source_offset, scale, window, int(causal)))
+    return (out, stats) if want_stats else out
+
+
+def attn_fwd_dev(q_dev, k_dev, v_dev, kv_is_f16: bool, out_dev, kvmap_dev, q_seq: int, kv_seq: int, heads: int, kv_heads: int, d: int,
+                 source_offset: int, scale: float, window: int = 0, causal: bool = True, stats_dev=None, stream: int = 0) -> None:
+    _check(load().fq_attn_fwd_dev(_vp(q_dev), _vp(k_dev), _vp(v_dev), int(kv_is_f16), _vp(out_dev), _vp(stats_dev), _vp(kvmap_dev), q_seq,
+                                  kv_seq, heads, kv_heads, d, source_offset, scale, window, int(causal), C.c_void_p(stream)))
+
+
 class _GgufTensor(C.Structure):
     _fields_ = [("name", C.c_char_p), ("ggml_type", C.c_int), ("fmt", C.c_int), ("n_dims", C.c_int), ("dims", C.c_uint64 * 4),
                 ("offset", C.c_uint64), ("bytes", C.c_uint64)]

@@ -140,6 +140,21 @@ FQ_API int fq_dequantize_rows_dev(const fq_weights* w, size_t mat, size_t row0, 
  * -> raw GGUF blocks in HBM, byte-identical to the CPU encoders. */
 FQ_API int fq_quantize_rows_dev(int fmt, const float* dev_src, size_t n, size_t k, void* dev_blocks);
 
+/* ---- streaming attention forward (the step on the other side of the linear layers in a decode token) ----
+ * The contract of attnFwdHostImpl / attnPrefillF16 (backend/cuda.zig:2601-2736) and of the kernels
+ * fucina_attn_fwd_{f16,f32} (backend/cuda/kernels.cu:574-681): q [q_seq][heads][d] f32, k and v [kv_seq][kv_heads][d]
+ * f16 (kv_is_f16 != 0) or f32, out [q_seq][heads][d] f32, optional stats [heads][q_seq][2] = {row max, sum exp},
+ * kv_head_for_head [heads]; query row i sits at absolute position source_offset + i; causal (keys up to that
+ * position, the last `window` of them when window > 0) or bidirectional; scores are scaled by `scale`.
+ * d <= 256 and a multiple of 8 (f16) or 4 (f32); heads <= 512. Online softmax in f32; the key range of a row is cut
+ * into splits merged by a second kernel, in a fixed order. Device-buffer and blocking host-buffer forms. */
+FQ_API int fq_attn_fwd_dev(const float* q_dev, const void* k_dev, const void* v_dev, int kv_is_f16, float* out_dev, float* stats_dev,
+                           const int32_t* kv_head_for_head_dev, size_t q_seq, size_t kv_seq, size_t heads, size_t kv_heads, size_t d,
+                           size_t source_offset, float scale, size_t window, int causal, void* stream);
+FQ_API int fq_attn_fwd(const float* q, const void* k, const void* v, int kv_is_f16, float* out, float* stats,
+                       const int32_t* kv_head_for_head, size_t q_seq, size_t kv_seq, size_t heads, size_t kv_heads, size_t d,
+                       size_t source_offset, float scale, size_t window, int causal);
+
 /* ---- GGUF file -> device-resident weights (new on the GPU side). The reference parses GGUF in src/gguf.zig
  *      (:214-452: header, metadata, tensor table, data section aligned to general.alignment) and makes quantized
  *      tensors GPU-resident in src/weights.zig:2621-2816; here the mapped blocks of a row / expert range go straight
