@@ -36,32 +36,44 @@ struct AttnArgs {
     int splits, split_len;  // split s covers keys [s * split_len, (s + 1) * split_len)
 };
 
-__device__ __forceinline__ float kv_f32(const __half* p) { return __half2float(*p); }
-__device__ __forceinline__ float kv_f32(const float* p) { return *p; }
+// four consecutive values of a V row (8 or 16 bytes)
+__device__ __forceinline__ float4 load4(const __half* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 
 // dot of the staged (pre-scaled) query row with one key row, 16 bytes of K per load
 __device__ __forceinline__ float key_dot(const float* sq, const __half* krow, int d) {
     float dot = 0.0f;
+#pragma unroll 4
     for (int t = 0; t < d; t += 8) {
         const uint4 raw = *reinterpret_cast<const uint4*>(krow + t);
         const __half2* h = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 kk = __half22float2(h[i]);
-            dot = fmaf(sq[t + 2 * i], kk.x, dot);
-            dot = fmaf(sq[t + 2 * i + 1], kk.y, dot);
-        }
+        const float4 q0 = *reinterpret_cast<const float4*>(sq + t), q1 = *reinterpret_cast<const float4*>(sq + t + 4);  // broadcast reads
+        const float2 k0 = __half22float2(h[0]), k1 = __half22float2(h[1]), k2 = __half22float2(h[2]), k3 = __half22float2(h[3]);
+        dot = fmaf(q0.x, k0.x, dot);
+        dot = fmaf(q0.y, k0.y, dot);
+        dot = fmaf(q0.z, k1.x, dot);
+        dot = fmaf(q0.w, k1.y, dot);
+        dot = fmaf(q1.x, k2.x, dot);
+        dot = fmaf(q1.y, k2.y, dot);
+        dot = fmaf(q1.z, k3.x, dot);
+        dot = fmaf(q1.w, k3.y, dot);
     }
     return dot;
 }
 __device__ __forceinline__ float key_dot(const float* sq, const float* krow, int d) {
     float dot = 0.0f;
+#pragma unroll 8
     for (int t = 0; t < d; t += 4) {
         const float4 kk = *reinterpret_cast<const float4*>(krow + t);
-        dot = fmaf(sq[t], kk.x, dot);
-        dot = fmaf(sq[t + 1], kk.y, dot);
-        dot = fmaf(sq[t + 2], kk.z, dot);
-        dot = fmaf(sq[t + 3], kk.w, dot);
+        const float4 qq = *reinterpret_cast<const float4*>(sq + t);
+        dot = fmaf(qq.x, kk.x, dot);
+        dot = fmaf(qq.y, kk.y, dot);
+        dot = fmaf(qq.z, kk.z, dot);
+        dot = fmaf(qq.w, kk.w, dot);
     }
     return dot;
 }
@@ -69,7 +81,7 @@ __device__ __forceinline__ float key_dot(const float* sq, const float* krow, int
 // grid (splits, heads, q_seq), 4 warps: warp w takes the 32-key steps w, w + 4, ... of the split
 template <typename KVT>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnArgs A) {
-    __shared__ float sh_q[kAttnMaxD];
+    __shared__ __align__(16) float sh_q[kAttnMaxD];
     __shared__ float sh_p[kAttnWarps][32];
     __shared__ float sh_m[kAttnWarps], sh_l[kAttnWarps];
     __shared__ float sh_acc[kAttnWarps][kAttnMaxD];
@@ -90,10 +102,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnA
     start = max(start, s * A.split_len);
     end = min(end, (s + 1) * A.split_len);
 
-    constexpr int ND = kAttnMaxD / 64;  // lane holds dims 2*lane + 64*t, +1
-    float acc[ND][2];
+    constexpr int ND = kAttnMaxD / 128;  // lane holds the four dims from (lane + 32 * t) * 4
+    float acc[ND][4];
 #pragma unroll
-    for (int t = 0; t < ND; ++t) acc[t][0] = acc[t][1] = 0.0f;
+    for (int t = 0; t < ND; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
     float m_run = kNegBig, l_run = 0.0f;
 
     for (int j0 = start + w * 32; j0 < end; j0 += kAttnWarps * 32) {
@@ -114,20 +126,30 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnA
         sh_p[w][lane] = p;
         __syncwarp();
         const int jn = min(32, end - j0);
+        const size_t vstride = (size_t)A.kv_heads * d;
 #pragma unroll
         for (int t = 0; t < ND; ++t) {
-            const int dim = 2 * lane + 64 * t;
-            float a0 = acc[t][0] * rescale, a1 = acc[t][1] * rescale;
+            const int dim = (lane + 32 * t) * 4;
+            float a0 = acc[t][0] * rescale, a1 = acc[t][1] * rescale, a2 = acc[t][2] * rescale, a3 = acc[t][3] * rescale;
             if (dim < d) {
-                const KVT* vp = V + ((size_t)j0 * A.kv_heads + kvh) * d + dim;
-                for (int jj = 0; jj < jn; ++jj) {
-                    const float pj = sh_p[w][jj];
-                    a0 = fmaf(pj, kv_f32(vp), a0);
-                    a1 = fmaf(pj, kv_f32(vp + 1), a1);
-                    vp += (size_t)A.kv_heads * d;
+                const KVT* vbase = V + ((size_t)j0 * A.kv_heads + kvh) * d + dim;
+                // eight rows of V in flight before their multiply-adds: the loads of a group do not wait for one another
+                for (int jj0 = 0; jj0 < jn; jj0 += 8) {
+                    float4 vv[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        vv[u] = (jj0 + u < jn) ? load4(vbase + (size_t)(jj0 + u) * vstride) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const float pj = sh_p[w][jj0 + u];  // zero past the row's last key
+                        a0 = fmaf(pj, vv[u].x, a0);
+                        a1 = fmaf(pj, vv[u].y, a1);
+                        a2 = fmaf(pj, vv[u].z, a2);
+                        a3 = fmaf(pj, vv[u].w, a3);
+                    }
                 }
             }
-            acc[t][0] = a0, acc[t][1] = a1;
+            acc[t][0] = a0, acc[t][1] = a1, acc[t][2] = a2, acc[t][3] = a3;
         }
         __syncwarp();
     }
@@ -136,8 +158,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_kernel(const AttnA
     if (lane == 0) sh_m[w] = m_run, sh_l[w] = l_run;
 #pragma unroll
     for (int t = 0; t < ND; ++t) {
-        const int dim = 2 * lane + 64 * t;
-        if (dim < d) sh_acc[w][dim] = acc[t][0], sh_acc[w][dim + 1] = acc[t][1];
+        const int dim = (lane + 32 * t) * 4;
+        if (dim < d) sh_acc[w][dim] = acc[t][0], sh_acc[w][dim + 1] = acc[t][1], sh_acc[w][dim + 2] = acc[t][2], sh_acc[w][dim + 3] = acc[t][3];
     }
     __syncthreads();
     float m = kNegBig;
