@@ -286,13 +286,6 @@ __global__ void ep_wait_kernel(const EpArgs A, int kind) {
     if ((int)threadIdx.x < A.v.world) wait_flag(flags_of(A.v.peer[A.v.rank], kind) + threadIdx.x, A.epoch);
 }
 
-// The rows that arrived in this rank's panel, copied into memory of its own before they are multiplied
-// (FUCINA_B200_EP_LOCAL_X=1): measures what reading the tokens from peer-mapped memory costs the product.
-__global__ void ep_localize_kernel(const EpArgs A, const uint4* __restrict__ panel, uint4* __restrict__ local) {
-    const size_t total = (size_t)A.plan->n_rows * (A.hidden >> 3);
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) local[i] = __ldcg(panel + i);
-}
-
 // ---- combine: out[t] = sum over the token's slots, in slot order, of w[p] * ret[p] ---------------------
 __global__ void ep_combine_kernel(const EpArgs A, const float* __restrict__ weights, float* __restrict__ out, int seq) {
     __shared__ int s_ok;
@@ -337,7 +330,6 @@ struct EpCall {
     uint8_t* scratch;
     __nv_bfloat16* g_panel;
     int max_gu, max_dn;
-    uint8_t* x_local = nullptr;  // optional private copy of the token panel (see ep_localize_kernel)
     int plan_stages = 3;  // see ep_plan_kernel
     int gated_op = 0;
 };
@@ -377,8 +369,6 @@ int ep_prepare(Ctx* ctx, const EpView& v, int epoch, const DevWeights& gate, con
     const size_t o_plan = take(sizeof(EpPlan)), o_dst = take(sizeof(int2) * pairs);
     const size_t o_tgu = take(sizeof(TcTile) * c->max_gu), o_tdn = take(sizeof(TcTile) * c->max_dn);
     const size_t o_g = take((size_t)a.mine.rows_cap * out_pe * 2);
-    static const bool local_x = getenv("FUCINA_B200_EP_LOCAL_X") && atoi(getenv("FUCINA_B200_EP_LOCAL_X")) != 0;
-    const size_t o_xl = take(local_x ? (size_t)a.mine.rows_cap * hidden * 2 : 0);
     c->scratch = (uint8_t*)dev_alloc_on(off, st);
     if (!c->scratch) return fail(FQ_DECLINED_BUDGET, "expert-parallel scratch of %zu bytes could not be allocated", off);
     a.plan = (EpPlan*)(c->scratch + o_plan);
@@ -386,7 +376,6 @@ int ep_prepare(Ctx* ctx, const EpView& v, int epoch, const DevWeights& gate, con
     a.t_gu = (TcTile*)(c->scratch + o_tgu);
     a.t_dn = (TcTile*)(c->scratch + o_tdn);
     c->g_panel = (__nv_bfloat16*)(c->scratch + o_g);
-    c->x_local = local_x ? c->scratch + o_xl : nullptr;
     return FQ_OK;
 }
 
@@ -413,11 +402,6 @@ int ep_phase(Ctx* ctx, EpCall& c, int phase, cudaStream_t st) {
             peer.n_wait = a.v.world;
             peer.wait_value = a.epoch;
             const uint8_t* x_panel = me + a.mine.off_x;
-            if (c.x_local) {
-                ep_wait_kernel<<<1, 32, 0, st>>>(a, 1);
-                ep_localize_kernel<<<148 * 8, 256, 0, st>>>(a, reinterpret_cast<const uint4*>(x_panel), reinterpret_cast<uint4*>(c.x_local));
-                x_panel = c.x_local;
-            }
             rc = gemm_tensor_grouped_gated_dev(ctx, *c.gate, *c.up, x_panel, (size_t)a.mine.rows_cap, c.g_panel, (size_t)c.gate->n,
                                                a.t_gu, &a.plan->n_gu, c.max_gu, st, &peer, c.gated_op);
             break;
