@@ -809,47 +809,53 @@ def sub_moe(args, P, torch, want_cpu: bool) -> list[dict]:
 
 def sub_attention(args, P, torch, want_cpu: bool) -> list[dict]:
     """One decode step of streaming attention (the op next to the linear layers): 32 heads over 8 kv heads, d 128,
-    8192 cached keys in f16; 6 KV copies (201 MB > L2) rotated inside one graph. Bytes = the K and V rows read."""
-    heads, kv_heads, d, kv_seq = 32, 8, 128, 8192
+    f16 KV, one query row, at 8192 and at 32768 cached keys; KV copies (> L2 in total) rotated inside one graph.
+    Bytes = the K and V rows read."""
+    heads, kv_heads, d = 32, 8, 128
     peak, src = measured_peaks()
     g = torch.Generator(device="cuda").manual_seed(2500)
     q = torch.randn((1, heads, d), generator=g, device="cuda")
     kvmap = torch.arange(heads, device="cuda", dtype=torch.int32) // (heads // kv_heads)
     out = torch.empty((1, heads, d), device="cuda")
-    copies = [(torch.randn((kv_seq, kv_heads, d), generator=g, device="cuda").half(), torch.randn((kv_seq, kv_heads, d), generator=g, device="cuda").half())
-              for _ in range(6)]
     scale = 1.0 / float(np.sqrt(d))
-    torch.cuda.synchronize()
+    recs = []
+    for kv_seq in (8192, 32768):
+        copies = [(torch.randn((kv_seq, kv_heads, d), generator=g, device="cuda").half(),
+                   torch.randn((kv_seq, kv_heads, d), generator=g, device="cuda").half()) for _ in range(max(2, 6 * 8192 // kv_seq))]
+        torch.cuda.synchronize()
 
-    def step(kv):
-        P.attn_fwd_dev(q, kv[0], kv[1], True, out, kvmap, 1, kv_seq, heads, kv_heads, d, kv_seq - 1, scale)
+        def step(kv):
+            P.attn_fwd_dev(q, kv[0], kv[1], True, out, kvmap, 1, kv_seq, heads, kv_heads, d, kv_seq - 1, scale)
 
-    step(copies[0])  # warm the allocator before capturing
-    P.synchronize()
-    with P.capture() as cap:
-        for kv in copies:
-            step(kv)
-    ms = _graph_ms(P, torch, [cap.graph]) / len(copies)
-    nbytes = 2 * kv_seq * kv_heads * d * 2
-    gbs = nbytes / ms / 1e6
-    rec = {"workload": "attention decode step: 1 query row, 32 heads / 8 kv heads, d 128, 8192 keys, f16 KV (6 rotated KV copies, graph replay)",
-           "metric": "attention KV GB/s", "value": round(gbs, 1), "unit": "GB/s", "us_per_step": round(ms * 1e3, 3), "bytes_per_step": nbytes,
-           "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4), "peak_source": src,
-                        "kernel": "attn_split_kernel<f16> + attn_merge_kernel"}}
-    if want_cpu:
-        qh = q.cpu().numpy()[0].astype(np.float32)
-        kh, vh = copies[0][0].cpu().numpy().astype(np.float32), copies[0][1].cpu().numpy().astype(np.float32)
+        step(copies[0])  # warm the allocator before capturing
+        P.synchronize()
+        with P.capture() as cap:
+            for kv in copies:
+                step(kv)
+        ms = _graph_ms(P, torch, [cap.graph]) / len(copies)
+        nbytes = 2 * kv_seq * kv_heads * d * 2
+        gbs = nbytes / ms / 1e6
+        rec = {"workload": f"attention decode step: 1 query row, 32 heads / 8 kv heads, d 128, {kv_seq} keys, f16 KV ({len(copies)} rotated KV copies, graph replay)",
+               "metric": "attention KV GB/s", "value": round(gbs, 1), "unit": "GB/s", "us_per_step": round(ms * 1e3, 3), "bytes_per_step": nbytes,
+               "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4), "peak_source": src,
+                            "kernel": "attn_split_mma_kernel (mma.sync.m16n8k16, cp.async double-buffered tiles) + attn_merge_kernel"}}
+        if want_cpu:
+            qh = q.cpu().numpy()[0].astype(np.float32)
+            kh, vh = copies[0][0].cpu().numpy().astype(np.float32), copies[0][1].cpu().numpy().astype(np.float32)
 
-        def cpu():
-            for h in range(heads):
-                sc = kh[:, h // (heads // kv_heads)] @ qh[h] * scale
-                pr = np.exp(sc - sc.max())
-                _ = (pr @ vh[:, h // (heads // kv_heads)]) / pr.sum()
+            def cpu():
+                for h in range(heads):
+                    sc = kh[:, h // (heads // kv_heads)] @ qh[h] * scale
+                    pr = np.exp(sc - sc.max())
+                    _ = (pr @ vh[:, h // (heads // kv_heads)]) / pr.sum()
 
-        sec, calls = _cpu_time(cpu, 1.0)
-        rec["cpu_baseline"] = {"value": round(nbytes / sec / 1e9, 2), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
-                               "sample": f"{calls} steps, {sec * calls:.1f} s, numpy f32 (BLAS threads) over f32 copies of the same KV"}
-    return [rec]
+            sec, calls = _cpu_time(cpu, 1.0)
+            rec["cpu_baseline"] = {"value": round(nbytes / sec / 1e9, 2), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+                                   "sample": f"{calls} steps, {sec * calls:.1f} s, numpy f32 (BLAS threads) over f32 copies of the same KV"}
+        recs.append(rec)
+        del copies, cap
+        torch.cuda.empty_cache()
+    return recs
 
 
 def sub_ternary(args, P, torch, want_cpu: bool) -> list[dict]:

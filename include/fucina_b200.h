@@ -146,8 +146,10 @@ FQ_API int fq_quantize_rows_dev(int fmt, const float* dev_src, size_t n, size_t 
  * f16 (kv_is_f16 != 0) or f32, out [q_seq][heads][d] f32, optional stats [heads][q_seq][2] = {row max, sum exp},
  * kv_head_for_head [heads]; query row i sits at absolute position source_offset + i; causal (keys up to that
  * position, the last `window` of them when window > 0) or bidirectional; scores are scaled by `scale`.
- * d <= 256 and a multiple of 8 (f16) or 4 (f32); heads <= 512. Online softmax in f32; the key range of a row is cut
- * into splits merged by a second kernel, in a fixed order. Device-buffer and blocking host-buffer forms. */
+ * d <= 256 and a multiple of 8 (f16) or 4 (f32); heads <= 512; device pointers 16-byte aligned; every map entry must
+ * name a kv head (the host form checks it, the device form cannot). Online softmax in f32; the key range of a row is
+ * cut into splits merged by a second kernel, in a fixed order; the K and V rows of a step are staged in shared memory
+ * once for all the heads that share the kv head. Device-buffer and blocking host-buffer forms. */
 FQ_API int fq_attn_fwd_dev(const float* q_dev, const void* k_dev, const void* v_dev, int kv_is_f16, float* out_dev, float* stats_dev,
                            const int32_t* kv_head_for_head_dev, size_t q_seq, size_t kv_seq, size_t heads, size_t kv_heads, size_t d,
                            size_t source_offset, float scale, size_t window, int causal, void* stream);
