@@ -1335,7 +1335,7 @@ def run_profile_tc(args) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="stack", choices=["stack", "profile", "profile_q8", "profile_tc", "profile_moe", "q8_0", "prefill", "moe", "ternary", "all",
+    ap.add_argument("--workload", default="stack", choices=["stack", "profile", "profile_q8", "profile_tc", "profile_moe", "attention", "q8_0", "prefill", "moe", "ternary", "all",
                                                                 "tp_prefill", "ep_moe", "multi"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -1367,6 +1367,15 @@ def main() -> None:
         return
     if args.workload == "profile_q8":
         print(json.dumps(run_profile_q8(args)), flush=True)
+        return
+    if args.workload == "attention":
+        import torch
+
+        from fucina_b200 import provider as P
+
+        P.init(0)
+        for rec in sub_attention(args, P, torch, not args.no_cpu):
+            print(json.dumps(rec), flush=True)
         return
     if args.workload in ("tp_prefill", "ep_moe", "multi"):
         for line in run_multi(args):

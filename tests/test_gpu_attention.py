@@ -64,6 +64,8 @@ def test_reference_prefill_cases(P, q_seq, kv_seq, heads, kv_heads, d, window, c
     (1, 5000, 8, 8, 64, 1024),      # ragged split, sliding window
     (4, 777, 16, 2, 256, 0),        # a few rows, the largest head size
     (2, 130, 4, 1, 128, 0),         # barely more than one split
+    (1, 1500, 16, 2, 64, 0),        # eight heads per kv head: two passes of four over the same tiles (tensor-core form)
+    (3, 300, 10, 2, 96, 64),        # five heads per kv head: a pass of four and a pass of one
 ])
 def test_decode_shapes_and_split_merge(P, q_seq, kv_seq, heads, kv_heads, d, window):
     rng = np.random.default_rng(42)
