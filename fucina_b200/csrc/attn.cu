@@ -507,13 +507,16 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_split_mma_kernel(const A
     }
 }
 
-// one CTA per (head, row): the splits' triples merged in split order. The splits' maxima and sums are staged in shared
-// memory first, so the loop over a dim's partial accumulators has independent, coalesced loads.
+// one CTA per (head, row): the splits' triples merged. The splits' maxima and sums are staged in shared memory; each of
+// the four warps then adds every fourth split (lane = four dims, 16-byte loads, all of a warp's loads independent) and
+// the warps' sums are added in warp order: a fixed order, whatever the grid of the first kernel was.
 constexpr int kAttnMaxSplits = 1024;
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs A) {
     __shared__ float sm_m[kAttnMaxSplits], sm_f[kAttnMaxSplits], sm_ls[kAttnMaxSplits];
+    __shared__ __align__(16) float sm_acc[4][kAttnMaxD];
     __shared__ float sm_l;
     const int h = blockIdx.x, qi = blockIdx.y, d = A.d, n = A.splits;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t stride = (size_t)d + 2;
     const float* part = A.part + ((size_t)qi * A.heads + h) * n * stride;
     for (int s = threadIdx.x; s < n; s += blockDim.x) sm_m[s] = part[(size_t)s * stride], sm_ls[s] = part[(size_t)s * stride + 1];
@@ -527,14 +530,24 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs A) {
         for (int s = 0; s < n; ++s) l += sm_ls[s] * sm_f[s];
         sm_l = l;
     }
+    for (int d0 = 0; d0 < d; d0 += 128) {
+        const int dim = d0 + lane * 4;
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        if (dim < d) {
+#pragma unroll 4
+            for (int s = w; s < n; s += 4) {
+                const float2 lo = *reinterpret_cast<const float2*>(part + (size_t)s * stride + 2 + dim);  // (d + 2) floats per split: 8-byte aligned
+                const float2 hi = *reinterpret_cast<const float2*>(part + (size_t)s * stride + 4 + dim);
+                const float f = sm_f[s];
+                a0 = fmaf(lo.x, f, a0), a1 = fmaf(lo.y, f, a1), a2 = fmaf(hi.x, f, a2), a3 = fmaf(hi.y, f, a3);
+            }
+            *reinterpret_cast<float4*>(&sm_acc[w][dim]) = make_float4(a0, a1, a2, a3);
+        }
+    }
     __syncthreads();
     const float l = sm_l, inv_l = l > 0.0f ? 1.0f / l : 0.0f;
-    for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
-        float a = 0.0f;
-#pragma unroll 8
-        for (int s = 0; s < n; ++s) a += part[(size_t)s * stride + 2 + dim] * sm_f[s];
-        A.out[((size_t)qi * A.heads + h) * d + dim] = a * inv_l;
-    }
+    for (int dim = threadIdx.x; dim < d; dim += blockDim.x)
+        A.out[((size_t)qi * A.heads + h) * d + dim] = (((sm_acc[0][dim] + sm_acc[1][dim]) + sm_acc[2][dim]) + sm_acc[3][dim]) * inv_l;
     if (A.stats && threadIdx.x == 0) {
         const size_t sb = ((size_t)h * A.q_seq + qi) * 2;
         A.stats[sb] = m, A.stats[sb + 1] = l;
