@@ -1,11 +1,12 @@
 // Row-per-lane decode GEMV for sm_100a with TMA-staged weight streaming.
 //
-// c[b, j] = sum_e a[b, e] * dequant(W)[j, e], b < m <= 8, for the dense decode
-// shapes (K >= 2048, Q4_K / Q5_K / Q8_0). Same arithmetic as the reference's
-// CPU kernels: int8 activations, exact integer block dots, and per block the
-// f32 epilogue of q4_k.zig:895-913 / q5_k.zig:1093-1111 / q8_0.zig:1074-1089,
-// evaluated without fusing; only the order in which block terms are added
-// differs.
+// c[b, j] = sum_e a[b, e] * dequant(W)[j, e], b < m <= 16, for the dense decode
+// shapes (K >= 2048; Q4_K / Q5_K up to 16 rows, Q8_0 up to 8, TQ2_0 planes up
+// to 4). Same arithmetic as the reference's CPU kernels: int8 activations,
+// exact integer block dots, and per block the f32 epilogue of
+// q4_k.zig:895-913 / q5_k.zig:1093-1111 / q8_0.zig:1074-1089 /
+// ternary.zig:377-386, evaluated without fusing; only the order in which block
+// terms are added differs.
 //
 // Data movement. One persistent CTA per SM owns a contiguous range of weight
 // rows and walks it in tiles of 32 rows; lane l of every warp owns row l of
@@ -18,6 +19,8 @@
 //   row-major K-quants    one 2-D tensor copy (32 rows x one unit)
 //   split rows (Q8_0)     three tensor copies: two 32 x 128-byte payload boxes (128-byte swizzle) and
 //                         the 32 x 16 scale bytes (per-lane bulk copies when no tensor map can be made)
+//   split rows (TQ2_0)    one tensor copy: a 32 x 128-byte payload box (512 weights per row, 128-byte
+//                         swizzle); the two f16 scales of a lane's row come straight from global memory
 // Slots are an odd number of 16-byte units wide so the 128-bit shared loads
 // of a quarter warp hit 32 distinct banks. Copies for the next slabs (also of
 // the next tile) are in flight while a slab is consumed, which keeps ~144 KB
