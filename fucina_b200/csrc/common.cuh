@@ -81,6 +81,14 @@ struct PreArgs {
     float eps;
 };
 
+// Programmatic dependent launch for chains of short kernels: the kernel waits for its predecessor to complete (and its
+// writes to be visible) before it touches global memory, then lets its own successor begin launching. A kernel
+// launched without the attribute (or after a kernel that never signals) sees both as no-ops.
+__device__ __forceinline__ void pdl_wait_then_release() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- small device helpers ---------------------------------------------------
 __device__ __forceinline__ float h2f(uint16_t bits) { return __half2float(__ushort_as_half(bits)); }
 

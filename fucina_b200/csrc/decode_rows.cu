@@ -1047,6 +1047,9 @@ template <int FMT, int MB, bool GATED>
 __global__ void __launch_bounds__(kExpertWarps * 32, MB == 8 ? 2 : 1)  // eight-row tables: two CTAs per SM (128 registers, no spills)
     expert_rows_kernel(const ExpertArgs A, const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap2) {
     extern __shared__ __align__(128) uint8_t smem[];
+    // The table, its length, the pair list and the activation rows come from the kernels before this one: nothing
+    // global is read before the predecessor has completed (the launch itself overlaps its tail).
+    pdl_wait_then_release();
     constexpr int NM = GATED ? 2 : 1;
     constexpr int UB = FMT == FQ_Q4_K ? 144 : 176;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1111,8 +1114,6 @@ __global__ void __launch_bounds__(kExpertWarps * 32, MB == 8 ? 2 : 1)  // eight-
         }
     };
 
-    // This kernel is launched without programmatic overlap: the table, the pair list and the activation
-    // rows were written by the kernels before it and are complete when it starts.
     advance();
 
     const ActView V = {smem_u32(acts), (uint32_t)NS.row, (uint32_t)NS.aq, (uint32_t)(NS.aq + NS.sums)};
@@ -1245,6 +1246,9 @@ cudaError_t launch_expert_t(const ExpertArgs& a, const CUtensorMap& t1, const CU
         if (e != cudaSuccess) return e;
         granted = true;
     }
+    // short tables (decode) chain by programmatic dependent launch; with every CTA slot of the part taken by one grid
+    // the early launch of the next has nowhere to go and measured 2 % slower
+    if (a.chain) return launch_pdl(kern, dim3(grid), dim3(kExpertWarps * 32), smem, st, a, t1, t2);
     kern<<<grid, kExpertWarps * 32, smem, st>>>(a, t1, t2);
     return cudaGetLastError();
 }
@@ -1443,7 +1447,7 @@ cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const 
         grid = (int)(items < 2LL * sm_count ? items : 2LL * sm_count);
         stages = 2;
     }
-    ExpertArgs a{w, w2 ? *w2 : DevWeights{}, src, src_index, top_k, out, table, n_desc, max_desc, tpi, stages, status, gated_op};
+    ExpertArgs a{w, w2 ? *w2 : DevWeights{}, src, src_index, top_k, out, table, n_desc, max_desc, tpi, stages, status, gated_op, grid < 2 * sm_count ? 1 : 0};
     const size_t smem = expert_smem_bytes(w.fmt, w.k, mb, nm, stages, k_split);
     if (w.fmt == FQ_Q4_K)
         return w2 ? launch_expert_mb<FQ_Q4_K, true>(a, mb, t1, t2, grid, smem, st) : launch_expert_mb<FQ_Q4_K, false>(a, mb, t1, t2, grid, smem, st);

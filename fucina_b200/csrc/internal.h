@@ -1,5 +1,6 @@
 // Launchers shared between the translation units of libfucina_b200.so.
 #pragma once
+#include <cstdlib>
 #include "common.cuh"
 
 namespace fq {
@@ -57,6 +58,24 @@ void set_gemv_grid_y_limit(int limit);  // test seam: cap gridDim.y of grouped l
 int gemv_padded_rows(size_t m);
 int gemv_rows_that_fit(int fmt, size_t k);
 
+// Launch with programmatic stream serialisation allowed (see pdl_wait_then_release in common.cuh): the grid may be
+// scheduled while the previous kernel of the stream drains. FUCINA_B200_NO_PDL switches it off.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    static const bool no_pdl = getenv("FUCINA_B200_NO_PDL") != nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = no_pdl ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // formats.cu -- natural-order activation records (actquant.cuh)
 cudaError_t launch_quantize_acts_natural(const float* a, int m, int k, bool q8k, uint8_t* out, cudaStream_t st);
 
@@ -99,6 +118,7 @@ struct ExpertArgs {
     int stages;
     int* status;
     int gated_op;           // FQ_GATED_* of the gate/up pair (w2 set)
+    int chain;              // launch with programmatic stream serialisation (short tables)
 };
 // one warp runs a bounded wait on a barrier nothing completes and reports through the status word
 cudaError_t launch_bounded_wait_probe(int* status, unsigned limit, cudaStream_t st);

@@ -54,6 +54,7 @@ __global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, i
                                   int* __restrict__ n_rows, int tile_tokens, int rt_gu, int rt_dn, TcTile* __restrict__ t_gu,
                                   int* __restrict__ n_gu, TcTile* __restrict__ t_dn, int* __restrict__ n_dn) {
     extern __shared__ int sh[];
+    pdl_wait_then_release();
     int* count = sh;                   // [n_expert] pairs per expert
     int* place = sh + n_expert;        // [n_expert] first sorted position of the expert's run
     int* dstart = sh + 2 * n_expert;   // [n_expert] first table entry of the expert
@@ -150,6 +151,7 @@ __global__ void route_plan_kernel(const int* __restrict__ selected, int pairs, i
 // (src/exec/moe_chain.zig:307-330); multiply and add stay separate.
 __global__ void combine_kernel(const float* __restrict__ down, const float* __restrict__ weights, const int* __restrict__ inv,
                                int seq, int hidden, int top_k, float* __restrict__ out) {
+    pdl_wait_then_release();
     const size_t total = (size_t)seq * hidden;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(i / hidden), j = (int)(i % hidden);
@@ -169,6 +171,7 @@ __global__ void combine_kernel(const float* __restrict__ down, const float* __re
 // up once per four outputs instead of once per output.
 __global__ void combine4_kernel(const float* __restrict__ down, const float* __restrict__ weights, const int* __restrict__ inv,
                                 int seq, int hidden, int top_k, float* __restrict__ out) {
+    pdl_wait_then_release();
     const int h4 = hidden >> 2;
     const size_t total = (size_t)seq * h4;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -192,12 +195,12 @@ static void launch_combine(const float* down, const float* weights, const int* i
     if (hidden % 4 == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)down & 15) == 0) {
         const size_t total4 = (size_t)seq * (hidden / 4);
         const int blocks4 = (int)((total4 + 127) / 128);
-        combine4_kernel<<<blocks4 > 148 * 16 ? 148 * 16 : blocks4, 128, 0, st>>>(down, weights, inv, seq, hidden, top_k, out);
+        launch_pdl(combine4_kernel, dim3(blocks4 > 148 * 16 ? 148 * 16 : blocks4), dim3(128), 0, st, down, weights, inv, seq, hidden, top_k, out);
         return;
     }
     const size_t total = (size_t)seq * hidden;
     const int blocks = (int)((total + 255) / 256);
-    combine_kernel<<<blocks > 148 * 8 ? 148 * 8 : blocks, 256, 0, st>>>(down, weights, inv, seq, hidden, top_k, out);
+    launch_pdl(combine_kernel, dim3(blocks > 148 * 8 ? 148 * 8 : blocks), dim3(256), 0, st, down, weights, inv, seq, hidden, top_k, out);
 }
 
 // Router (src/exec/topk.zig:50-86), one warp per token row: the k largest logits in descending
@@ -210,6 +213,7 @@ constexpr int kMaxRouterExperts = 4096;
 __global__ void router_topk_kernel(const float* __restrict__ logits, int rows, int experts, int k, int normalize,
                                    int* __restrict__ selected, float* __restrict__ weights) {
     extern __shared__ float rsh[];
+    pdl_wait_then_release();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int row = blockIdx.x * warps + warp;
     if (row >= rows) return;  // whole warps leave together
@@ -437,9 +441,9 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     do {
         // positions past a shard's own rows are read by the gather below: point them at pair 0
         if (shard.skip_foreign && (e = cudaMemsetAsync(order, 0, sizeof(int) * pairs, st)) != cudaSuccess) break;
-        route_plan_kernel<<<1, 1024, sizeof(int) * 4 * n_expert, st>>>(selected_dev, pairs, n_expert, shard, group_rows, order, inv, table, n_desc, n_desc + 1,
-                                                                    0, 0, 0, nullptr, nullptr, nullptr, nullptr);
-        if ((e = cudaGetLastError()) != cudaSuccess) break;
+        if ((e = launch_pdl(route_plan_kernel, dim3(1), dim3(1024), sizeof(int) * 4 * n_expert, st, selected_dev, pairs, n_expert, shard, group_rows, order,
+                            inv, table, n_desc, n_desc + 1, 0, 0, 0, (TcTile*)nullptr, (int*)nullptr, (TcTile*)nullptr, (int*)nullptr)) != cudaSuccess)
+            break;
         if (streaming) {
             if ((e = launch_expert_rows(gate, &up, x_dev, order, top_k, g, table, n_desc, max_desc, group_rows, ctx->sm_count, ctx->status_dev,
                                         st, gated_op)) != cudaSuccess)
@@ -527,10 +531,9 @@ int fq_router_topk_dev(const float* logits_dev, size_t seq, size_t n_expert, siz
     cudaStream_t st = stream ? (cudaStream_t)stream : ctx->stream;
     // a warp per row with 2 x experts floats of shared memory each
     const int warps = n_expert <= 1024 ? 4 : 1;
-    router_topk_kernel<<<(unsigned)((seq + warps - 1) / warps), warps * 32, sizeof(float) * 2 * n_expert * warps, st>>>(
-        logits_dev, (int)seq, (int)n_expert, (int)top_k, normalize, selected_dev, weights_dev);
+    cudaError_t e = launch_pdl(router_topk_kernel, dim3((unsigned)((seq + warps - 1) / warps)), dim3(warps * 32), sizeof(float) * 2 * n_expert * warps, st,
+                               logits_dev, (int)seq, (int)n_expert, (int)top_k, normalize, selected_dev, weights_dev);
     g_trace.launches++;
-    cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FQ_OK : cuda_fail(e, "router launch");
 }
 
