@@ -178,15 +178,31 @@ __global__ void combine4_kernel(const float* __restrict__ down, const float* __r
         const int t = (int)(i / h4), j = (int)(i % h4) * 4;
         float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         bool first = true;
-        for (int kk = 0; kk < top_k; ++kk) {
-            const int p = t * top_k + kk, pos = inv[p];
-            if (pos < 0) continue;  // another shard's expert
-            const float wv = weights[p];
-            float4 v = *reinterpret_cast<const float4*>(down + (size_t)pos * hidden + j);
-            v.x = __fmul_rn(wv, v.x), v.y = __fmul_rn(wv, v.y), v.z = __fmul_rn(wv, v.z), v.w = __fmul_rn(wv, v.w);
-            if (first) acc = v;
-            else acc.x = __fadd_rn(acc.x, v.x), acc.y = __fadd_rn(acc.y, v.y), acc.z = __fadd_rn(acc.z, v.z), acc.w = __fadd_rn(acc.w, v.w);
-            first = false;
+        // eight slots at a time: their positions, then their rows, are all requested before the first sum (a slot's row
+        // address depends on its position: one slot at a time is two dependent round trips per slot); the sums keep slot order
+        for (int kk0 = 0; kk0 < top_k; kk0 += 8) {
+            int pos[8];
+            float wv[8];
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool ok = kk0 + u < top_k;
+                const int p = t * top_k + kk0 + u;
+                pos[u] = ok ? inv[p] : -1;  // -1: another shard's expert, or past the last slot
+                wv[u] = ok ? weights[p] : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                v[u] = pos[u] >= 0 ? *reinterpret_cast<const float4*>(down + (size_t)pos[u] * hidden + j) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (pos[u] < 0) continue;
+                float4 x = v[u];
+                x.x = __fmul_rn(wv[u], x.x), x.y = __fmul_rn(wv[u], x.y), x.z = __fmul_rn(wv[u], x.z), x.w = __fmul_rn(wv[u], x.w);
+                if (first) acc = x;
+                else acc.x = __fadd_rn(acc.x, x.x), acc.y = __fadd_rn(acc.y, x.y), acc.z = __fadd_rn(acc.z, x.z), acc.w = __fadd_rn(acc.w, x.w);
+                first = false;
+            }
         }
         *reinterpret_cast<float4*>(out + (size_t)t * hidden + j) = acc;
     }
