@@ -189,6 +189,7 @@ int parse(fq_gguf* g) {
         } else {
             row = plain_row_bytes(t.ggml_type, t.dims[0]);
         }
+        if (row != 0 && rows > UINT64_MAX / row) return fail(FQ_DECLINED_ARGS, "GGUF tensor '%s' overflows", t.name.c_str());
         t.bytes = (uint64_t)row * rows;  // 0 for a type this reader cannot size (the entry is still listed)
         g->tensors.push_back(std::move(t));
     }
