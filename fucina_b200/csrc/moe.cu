@@ -759,6 +759,7 @@ struct GroupedRun {
 // Runs at least this long multiply on the tensor cores (bf16 operands, as the reference's own grouped arm rounds its
 // operands, backend/cuda/kernels.cu:340-379); shorter ones keep the CPU kernels' int8 arithmetic.
 constexpr int kGroupedTensorRows = 17;
+constexpr int kQmmTileRows = 32;  // NR1 of the reference's tile kernels (backend/cuda/kernels.cu:168)
 static int g_grouped_tensor_mode = -1;  // test seam: -1 by run length, 0 never, 1 every run the format allows
 
 extern "C" void fq_set_grouped_tensor_for_test(int mode) { g_grouped_tensor_mode = mode < 0 ? -1 : (mode ? 1 : 0); }
@@ -781,12 +782,21 @@ extern "C" int fq_gemm_q_grouped_nt(int fmt, const void* rhs, size_t rhs_len, in
     const int group_rows = kGroupRows < fit_rows ? kGroupRows : fit_rows;
     std::vector<GroupedRun> runs;
     for (size_t t = 0; t < n_tiles; ++t) {
+        // The reference's table entry (backend/cuda.zig:1503-1508, filled at llm/gemma/moe.zig:773-787 and in its own
+        // test at cuda.zig:3170-3183): `base_row` and `m` are the first panel row and the row count of the expert's
+        // whole group, `tile_m` is the index of this 32-row tile inside the group. The tile therefore covers panel
+        // rows [base_row + 32 tile_m, base_row + min(m, 32 tile_m + 32)) (backend/cuda/kernels.cu:322-327).
         const fq_qmm_tile& tl = tiles[t];
-        if (tl.expert < 0 || tl.base_row < 0 || tl.m <= 0 || tl.m > tl.tile_m) return fail(FQ_DECLINED_ARGS, "tile %zu is malformed", t);
+        if (tl.expert < 0 || tl.base_row < 0 || tl.m <= 0 || tl.tile_m < 0 || (long long)tl.tile_m * kQmmTileRows >= tl.m)
+            return fail(FQ_DECLINED_ARGS, "tile %zu is malformed", t);
+        const int first = tl.tile_m * kQmmTileRows;
+        const int row0 = tl.base_row + first;
+        const int cnt = tl.m - first < kQmmTileRows ? tl.m - first : kQmmTileRows;
+        if (row0 < 0) return fail(FQ_DECLINED_ARGS, "tile %zu is malformed", t);
         if (tl.expert > max_expert) max_expert = tl.expert;
-        if ((size_t)tl.base_row + tl.m > rows) rows = (size_t)tl.base_row + tl.m;
-        if (!runs.empty() && runs.back().expert == tl.expert && runs.back().row0 + runs.back().m == tl.base_row) runs.back().m += tl.m;
-        else runs.push_back({tl.expert, tl.base_row, tl.m});
+        if ((size_t)row0 + cnt > rows) rows = (size_t)row0 + cnt;
+        if (!runs.empty() && runs.back().expert == tl.expert && runs.back().row0 + runs.back().m == row0) runs.back().m += cnt;
+        else runs.push_back({tl.expert, row0, cnt});
     }
     if (rows * k * sizeof(float) > g_stage.in_bytes || rows * n_out * sizeof(float) > g_stage.out_bytes)
         return fail(FQ_DECLINED_ARGS, "tiles reach beyond the staged panels");

@@ -145,7 +145,9 @@ static int init_locked(int device) {
     snprintf(g_ctx.name, sizeof g_ctx.name, "%s", prop.name);
     if ((e = cudaStreamCreateWithFlags(&g_ctx.stream, cudaStreamNonBlocking)) != cudaSuccess)
         return fail(FQ_DECLINED_NO_GPU, "cudaStreamCreate: %s", cudaGetErrorString(e));
-    if ((e = cudaStreamCreateWithFlags(&g_ctx.transfer, cudaStreamNonBlocking)) != cudaSuccess)
+    if ((e = cudaStreamCreateWithFlags(&g_ctx.transfer, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaStreamCreateWithFlags(&g_ctx.upload, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&g_ctx.upload_ev, cudaEventDisableTiming)) != cudaSuccess)
         return fail(FQ_DECLINED_NO_GPU, "cudaStreamCreate: %s", cudaGetErrorString(e));
     size_t free_b = 0, total_b = 0;
     cudaMemGetInfo(&free_b, &total_b);
@@ -676,8 +678,10 @@ struct Staged {
     void* pin = nullptr;
 };
 
-static int upload_f32(Ctx* ctx, const float* host, size_t bytes, Staged* s) {
-    s->dev = dev_alloc(bytes);
+// `st`: the stream the copy is queued on (and the first to touch the staging block)
+static int upload_f32(Ctx* ctx, const float* host, size_t bytes, Staged* s, cudaStream_t st = nullptr) {
+    if (!st) st = ctx->stream;
+    s->dev = dev_alloc_on(bytes, st);
     if (!s->dev) return fail(FQ_DECLINED_BUDGET, "device allocation of %zu bytes failed", bytes);
     const void* src = host;
     // registered storage is DMA-able as it is; other small rows are always staged (copying a few KB costs less
@@ -689,7 +693,7 @@ static int upload_f32(Ctx* ctx, const float* host, size_t bytes, Staged* s) {
         memcpy(s->pin, host, bytes);
         src = s->pin;
     }
-    cudaError_t e = cudaMemcpyAsync(s->dev, src, bytes, cudaMemcpyHostToDevice, ctx->stream);
+    cudaError_t e = cudaMemcpyAsync(s->dev, src, bytes, cudaMemcpyHostToDevice, st);
     g_trace.h2d_bytes += bytes;
     return e == cudaSuccess ? FQ_OK : cuda_fail(e, "activation upload");
 }
@@ -886,6 +890,7 @@ int fq_synchronize(void) {
     if (!ctx) return FQ_DECLINED_NO_GPU;
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->transfer);  // result copies of asynchronous submits
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->upload);
     if (e != cudaSuccess) return cuda_fail(e, "synchronize");
     return device_status(ctx);
 }
@@ -984,6 +989,7 @@ int fq_host_unregister(void* host_ptr) {
     std::lock_guard<std::recursive_mutex> d(g_dispatch_lock);
     cudaStreamSynchronize(ctx->stream);  // no copy or kernel may still address the range
     cudaStreamSynchronize(ctx->transfer);
+    cudaStreamSynchronize(ctx->upload);
     std::lock_guard<std::mutex> g(g_host_lock);
     for (size_t i = 0; i < g_host_ranges.size(); ++i)
         if (g_host_ranges[i].base == (uintptr_t)host_ptr) {
@@ -1143,13 +1149,26 @@ int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheab
     Staged in;
     const float* a_dev = a_dep ? (const float*)a_dep->c_dev : nullptr;
     if (!a_dev) {
-        rc = upload_f32(ctx, a, m * k * sizeof(float), &in);
+        // The upload runs on its own stream and the compute stream waits for its event (backend/cuda.zig:2056-2057):
+        // a copy queued between two products on the compute stream would hold the second one back until the first
+        // has drained, while here the next product's activations arrive under the current product. The event can
+        // be recorded again by the next submit: a stream wait refers to the record that preceded it.
+        rc = upload_f32(ctx, a, m * k * sizeof(float), &in, ctx->upload);
         a_dev = (const float*)in.dev;
+        if (rc == FQ_OK) {
+            cudaError_t e = cudaEventRecord(ctx->upload_ev, ctx->upload);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->stream, ctx->upload_ev, 0);
+            if (e != cudaSuccess) rc = cuda_fail(e, "upload ordering");
+        }
     }
     fq_work* w = nullptr;
     if (rc == FQ_OK) {
         w = new fq_work();
         w->bytes = batch * m * n * sizeof(float);
+        // The result always has a device copy (a consumer chained on this token reads it there). Letting the kernel
+        // store decode-sized results straight into registered host storage, as the blocking entry does, was
+        // measured slower here: the next product of the queue may only pass its dependency wait once the
+        // predecessor's stores across PCIe have drained (66 against 63.5 us for the four-product decode step).
         w->c_dev = dev_alloc(w->bytes);
         w->c_host = c_host;
         w->state = 0;
@@ -1194,8 +1213,9 @@ int fq_gemm_quant_nt_async(int fmt, const void* rhs, size_t rhs_len, int cacheab
         w->in_pin = in.pin;
     }
     if (rc != FQ_OK) {
+        cudaStreamSynchronize(ctx->upload);
         cudaStreamSynchronize(ctx->stream);
-        dev_free(in.dev);
+        dev_free_idle(in.dev);
         pin_free(in.pin);
         if (w) {
             token_event_put(w->done);

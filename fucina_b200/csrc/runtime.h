@@ -18,7 +18,9 @@ struct Ctx {
     int device = -1;
     int sm_count = 0;
     cudaStream_t stream = nullptr;    // compute stream: every library kernel and copy is ordered here
-    cudaStream_t transfer = nullptr;  // spare stream for overlapped host transfers
+    cudaStream_t transfer = nullptr;  // result copies of asynchronous submits, behind an event of their product
+    cudaStream_t upload = nullptr;    // activation uploads of asynchronous submits (backend/cuda.zig's upload_stream)
+    cudaEvent_t upload_ev = nullptr;  // marks the end of the latest upload; the compute stream waits on it
     size_t vram_budget = 0;
     int* status_host = nullptr;  // mapped status word, host view
     int* status_dev = nullptr;   // and the pointer kernels receive

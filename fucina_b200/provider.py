@@ -332,6 +332,49 @@ def gemm_quant_nt_async(fmt: int, rhs: np.ndarray, a: np.ndarray | None, n: int,
     return Work(h.value, c)
 
 
+class PreparedGemmAsync:
+    """`gemm_quant_nt_async` with its arguments converted once, for a caller that repeats the same product every
+    step (a decode loop: same resident weights, same host activation and result storage). `submit()` queues the
+    product and returns at once; `finish()` waits, leaves the result in `out` and releases the token
+    (`gemmQuantNtAsync` + `Work.finish`, src/backend/cuda.zig:2001-2175, src/accelerator.zig:22-133). The object keeps
+    the three arrays alive; it holds at most one product in flight."""
+
+    __slots__ = ("_submit", "_finish", "_destroy", "_args", "_h", "_keep", "out")
+
+    def __init__(self, fmt: int, rhs: np.ndarray, a: np.ndarray, n: int, m: int, k: int, batch: int = 1, out: np.ndarray | None = None):
+        if a.dtype != np.float32 or not a.flags.c_contiguous or a.size != m * k:
+            raise ValueError("activations must be a C-contiguous float32 array of m * k elements")
+        if out is None:
+            out = np.full((batch * m, n), np.nan, dtype=np.float32)
+        if out.dtype != np.float32 or not out.flags.c_contiguous or out.size != batch * m * n:
+            raise ValueError("out must be a C-contiguous float32 array of batch * m * n elements")
+        lib = load()
+        nb01 = formats.row_bytes(fmt, k)
+        self._submit, self._finish, self._destroy = lib.fq_gemm_quant_nt_async, lib.fq_work_finish, lib.fq_work_destroy
+        self._h = C.c_void_p()
+        self._args = (fmt, C.c_void_p(rhs.ctypes.data), rhs.size, 1, nb01, nb01 * n, C.c_void_p(a.ctypes.data), C.c_void_p(0),
+                      C.c_void_p(out.ctypes.data), batch, m, n, k, C.byref(self._h))
+        self._keep = (rhs, a)
+        self.out = out
+
+    def submit(self) -> None:
+        if self._h.value:
+            raise RuntimeError("the previous submit was not finished")
+        rc = self._submit(*self._args)
+        if rc:
+            _check(rc)
+
+    def finish(self) -> np.ndarray:
+        if not self._h.value:
+            raise RuntimeError("nothing was submitted")
+        rc = self._finish(self._h, 1)
+        self._destroy(self._h)
+        self._h.value = None
+        if rc:
+            _check(rc)
+        return self.out
+
+
 # --------------------------------------------------------------------------- dense, device buffers
 def gemm_quant_nt_dev(w: Weights, a_dev, c_dev, m: int, mat: int = 0, mode: int = MODE_AUTO, stream: int = 0) -> None:
     _check(load().fq_gemm_quant_nt_dev(w.handle, mat, _vp(a_dev), _vp(c_dev), m, mode, C.c_void_p(stream)))

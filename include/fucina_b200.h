@@ -67,12 +67,14 @@ enum {
  * silu(min(gate, 10)) (DeepSeek V4); glu up * sigmoid(gate); situ 25 tanh(up/25) * 4 tanh(gate/4) sigmoid(gate). */
 enum { FQ_GATED_SWIGLU = 0, FQ_GATED_GEGLU = 1, FQ_GATED_SWIGLU_CLAMP10 = 2, FQ_GATED_GLU = 3, FQ_GATED_SITU = 4 };
 
-/* backend/cuda.zig:1503-1508 `QMMTile`: one output tile of one expert. */
+/* backend/cuda.zig:1503-1508 `QMMTile`: one 32-row output tile of one expert's group of panel rows, with the
+ * reference's field meaning (filled at llm/gemma/moe.zig:773-787, read at backend/cuda/kernels.cu:322-327): the
+ * tile covers panel rows [base_row + 32 * tile_m, base_row + min(m, 32 * tile_m + 32)). */
 typedef struct {
-    int32_t expert;
-    int32_t base_row;
-    int32_t m;
-    int32_t tile_m;
+    int32_t expert;   /* which matrix of the stack */
+    int32_t base_row; /* first panel row of the expert's group */
+    int32_t m;        /* rows of the whole group */
+    int32_t tile_m;   /* index of this tile inside the group */
 } fq_qmm_tile;
 
 /* ---- provider lifetime (backend/cuda.zig:412-508 `context`/`initOnce`,

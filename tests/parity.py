@@ -33,6 +33,19 @@ def assert_close(got, want, tol, what=""):
     return e
 
 
+def rms_err(got, want) -> tuple[float, float]:
+    """(RMS of the difference, largest absolute difference), both divided by the RMS of `want`: the measure for two
+    paths that round their operands differently (int8 or bf16 activations against f32 / f16 ones), where the
+    difference is rounding noise proportional to the output's scale and not to each element's own size."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert np.isfinite(got).all(), "non-finite output"
+    rms = float(np.sqrt(np.mean(want**2))) + 1e-300
+    d = got - want
+    return float(np.sqrt(np.mean(d**2))) / rms, float(np.max(np.abs(d))) / rms
+
+
 def bits_equal(a: np.ndarray, b: np.ndarray) -> bool:
     return a.shape == b.shape and np.array_equal(np.ascontiguousarray(a).view(np.uint32), np.ascontiguousarray(b).view(np.uint32))
 

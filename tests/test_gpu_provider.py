@@ -147,6 +147,87 @@ def test_async_dependency_chain_without_host_read(P):
     load().fq_evict_resident(w2.ctypes.data)
 
 
+def _page_aligned(shape):
+    """float32 array on a 4096-byte boundary spanning whole pages (what host registration wants)."""
+    count = int(np.prod(shape))
+    raw = np.zeros(((count * 4 + 4095) // 4096 + 1) * 4096, np.uint8)
+    off = (-raw.ctypes.data) % 4096
+    return raw[off:off + count * 4].view(np.float32).reshape(shape)
+
+
+def test_async_chain_through_registered_storage(P):
+    # the producer's result is copied into its caller's registered storage right behind the product, and the
+    # consumer chained on it still reads the device copy: the intermediate row never travels back up
+    n1, k1, n2 = 512, 256, 68
+    w1 = make_weights("q8_0", n1, k1, seed=21)
+    w2 = make_weights("q4_k", n2, n1, seed=22)
+    x = acts(1, k1, 23)
+    h_out = _page_aligned((1, n1))
+    h_out[:] = np.nan
+    P.host_register(h_out)
+    try:
+        P.gemm_quant_nt(oracle.Q8_0, w1, x, n1, cacheable=True)  # adopt both weight matrices first
+        P.gemm_quant_nt(oracle.Q4_K, w2, acts(1, n1, 24), n2, cacheable=True)
+        before = P.trace_counters()
+        work1 = P.gemm_quant_nt_async(oracle.Q8_0, w1, x, n1, 1, k1, out=h_out)
+        work2 = P.gemm_quant_nt_async(oracle.Q4_K, w2, None, n2, 1, n1, dep=work1)
+        work2.finish(copy_to_host=True)
+        work1.finish(copy_to_host=True)
+        h = oracle.matmul(oracle.Q8_0, w1, x)
+        assert_close(h_out, h, TOL_INT8, "producer, into registered storage")
+        assert_close(work2.out, oracle.matmul(oracle.Q4_K, w2, h), 2e-2, "chained through registered storage")
+        # only the first product's activations went up; both results came down
+        after = P.trace_counters()
+        assert after["h2d_bytes"] - before["h2d_bytes"] == k1 * 4
+        assert after["d2h_bytes"] - before["d2h_bytes"] == (n1 + n2) * 4
+        work2.destroy()
+        work1.destroy()
+    finally:
+        P.synchronize()
+        P.host_unregister(h_out)
+    from fucina_b200._lib import load
+
+    load().fq_evict_resident(w1.ctypes.data)
+    load().fq_evict_resident(w2.ctypes.data)
+
+
+@pytest.mark.parametrize("registered", [False, True])
+def test_prepared_async_calls_overlap_and_repeat(P, registered):
+    # four products of different sizes queued back to back, finished afterwards, over several steps with changing
+    # activations: uploads run on their own stream behind the compute stream's products, results land in `out`
+    # (through page-locked staging, or, with registered storage, copied into it directly)
+    shapes = [(256, 512), (1024, 512), (68, 512), (4096, 512)]
+    ws = [make_weights("q4_k", n, k, seed=40 + i) for i, (n, k) in enumerate(shapes)]
+    xs = [_page_aligned((1, k)) for n, k in shapes]
+    outs = [_page_aligned((1, n)) for n, k in shapes]
+    for i, x in enumerate(xs):
+        x[:] = acts(1, x.shape[1], 50 + i)
+    if registered:
+        for arr in xs + outs:
+            P.host_register(arr)
+    calls = [P.PreparedGemmAsync(oracle.Q4_K, w, x, n, 1, k, out=o) for w, x, o, (n, k) in zip(ws, xs, outs, shapes)]
+    for step in range(3):
+        for x in xs:
+            x *= np.float32(1.0 + 0.5 * step)  # same storage, new values every step
+        for c in calls:
+            c.out[:] = np.nan
+            c.submit()
+        with pytest.raises(RuntimeError):
+            calls[0].submit()  # one product in flight per prepared call
+        for c, w, x in zip(calls, ws, xs):
+            assert_close(c.finish(), oracle.matmul(oracle.Q4_K, w, x), TOL_INT8, f"prepared async step {step}")
+    with pytest.raises(RuntimeError):
+        calls[0].finish()
+    if registered:
+        P.synchronize()
+        for arr in xs + outs:
+            P.host_unregister(arr)
+    from fucina_b200._lib import load
+
+    for w in ws:
+        load().fq_evict_resident(w.ctypes.data)
+
+
 def test_async_slots_decline_when_exhausted(P):
     n, k = 64, 256
     w = make_weights("q8_0", n, k, seed=14)
@@ -185,8 +266,8 @@ def _grouped_case(P, fmt_name, n_out, k, ms, mode, seed=16):
         pout[:] = np.nan
         tiles, base = [], 0
         for e, m in enumerate(ms):
-            for r0 in range(0, m, 32):
-                tiles.append((e, base + r0, min(32, m - r0), 32))
+            for t in range((m + 31) // 32):  # {expert, group base, group rows, tile index}: llm/gemma/moe.zig:773-787
+                tiles.append((e, base, m, t))
             base += m
         P.gemm_q_grouped_nt(fmt, blocks, n_out, k, tiles)
         got = np.array(pout).reshape(rows, n_out)
@@ -234,6 +315,27 @@ def test_grouped_long_runs_are_merged_from_32_row_tiles(P, mode):
             assert_close(got[base:base + m], oracle.matmul_fast(oracle.Q4_K, w, a[base:base + m]), TOL_INT8, f"expert {e}")
         base += m
     assert launches <= 4  # repack, then one conversion or quantisation pass and one product: not a launch per tile
+
+
+@pytest.mark.parametrize("tile", [(0, 0, 40, 2), (0, 0, 0, 0), (0, -1, 8, 0), (-1, 0, 8, 0), (0, 0, 8, -1)])
+def test_grouped_malformed_tiles_decline(P, tile):
+    # a tile index at or beyond the group's rows (32 * tile_m >= m), empty groups and negative fields are refused
+    # before anything is launched: the output panel keeps its contents
+    n_out, k = 64, 512
+    blocks = make_weights("q4_k", n_out, k, seed=19)
+    from fucina_b200._lib import load
+
+    lib = load()
+    lib.fq_qmoe_lock()
+    try:
+        pin, pout = P.qmoe_stage(64 * k, 64 * n_out)
+        pin[:] = 0.0
+        pout[:] = 7.0
+        with pytest.raises(P.Declined):
+            P.gemm_q_grouped_nt(oracle.Q4_K, blocks, n_out, k, [(0, 0, 8, 0), tile])
+        assert (np.array(pout) == 7.0).all()
+    finally:
+        lib.fq_qmoe_unlock()
 
 
 def _moe_case(fmt_name, hidden, out_pe, n_expert, top_k, seq, seed):
