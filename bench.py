@@ -1191,6 +1191,26 @@ def sub_ref_kernels(args, P, torch, want_cpu: bool) -> list[dict]:
     recs.append({"workload": f"Q5_K MoE layer products at {T} tokens ({pairs} routed rows, {len(table)} tiles): gate, up and down grouped launches of the "
                              "reference tile kernel; its CPU gather / SwiGLU / scatter and PCIe round trips are not included", "impl": impl,
                  "kernel": "fucina_mul_mm_mma_q5_K", "metric": "MoE layer tok/s", "value": round(T / ms * 1e3, 1), "unit": "tok/s", "ms": round(ms, 4)})
+    del gate, up, down, xin, gin, og, ou, od
+    torch.cuda.empty_cache()
+
+    # attention decode step at 8192 keys (the reference kernel gives one warp to a query row and head)
+    H, KVH, D, KV = 32, 8, 128, 8192
+    q = torch.randn((1, H, D), generator=g, device="cuda")
+    kvs = [(torch.randn((KV, KVH, D), generator=g, device="cuda").to(torch.float16), torch.randn((KV, KVH, D), generator=g, device="cuda").to(torch.float16))
+           for _ in range(6)]
+    o = torch.empty((1, H, D), device="cuda")
+    kvmap = torch.tensor([h * KVH // H for h in range(H)], dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    with P.capture() as cap:
+        for kk, vv in kvs:
+            ref_cuda.attn_fwd(True, q.data_ptr(), kk.data_ptr(), vv.data_ptr(), o.data_ptr(), 0, kvmap.data_ptr(), 1, KV, H, KVH, D, KV - 1,
+                              D ** -0.5, 0, True, st)
+    ms = _graph_ms(P, torch, [cap.graph]) / len(kvs)
+    nbytes = 2 * KV * KVH * D * 2
+    recs.append({"workload": f"attention decode step, 1 query row, {H} heads / {KVH} kv heads, d {D}, {KV} keys, f16 KV, reference kernel (6 rotated KV copies, graph replay)",
+                 "impl": impl, "kernel": "fucina_attn_fwd_f16", "metric": "attention KV GB/s", "value": round(nbytes / ms / 1e6, 1), "unit": "GB/s",
+                 "us_per_step": round(ms * 1e3, 2)})
     return recs
 
 

@@ -38,6 +38,8 @@ def lib():
         L.refk_plan.restype = None
         L.refk_mul_mm.argtypes = [i32, vp, vp, vp, i32, vp, i32, i32, ull, ull, vp, i32, ull, i32, vp]
         L.refk_mul_mm.restype = i32
+        L.refk_attn_fwd.argtypes = [i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, ctypes.c_float, i32, i32, vp]
+        L.refk_attn_fwd.restype = i32
         _lib = L
     return _lib
 
@@ -64,6 +66,13 @@ def mul_mm(fmt: int, w_ptr: int, a_ptr: int, tiles_ptr: int, n_tiles: int, dst_p
     """One grouped tensor-core launch over a device table of int32 {expert, base_row, m, tile_m} entries."""
     _check(lib().refk_mul_mm(fmt, w_ptr, a_ptr, tiles_ptr, n_tiles, dst_ptr, k, n, nb01, nb02, partial_ptr or None, split_k,
                              partial_stride, n_tile, stream), "mul_mm")
+
+
+def attn_fwd(kv_is_f16: bool, q_ptr: int, k_ptr: int, v_ptr: int, o_ptr: int, stats_ptr: int, kvmap_ptr: int, q_seq: int, kv_seq: int,
+             heads: int, kv_heads: int, d: int, source_offset: int, scale: float, window: int, causal: bool, stream: int = 0) -> None:
+    """The reference's streaming attention forward (one warp per query row and head)."""
+    _check(lib().refk_attn_fwd(int(kv_is_f16), q_ptr, k_ptr, v_ptr, o_ptr, stats_ptr or None, kvmap_ptr, q_seq, kv_seq, heads, kv_heads, d,
+                               source_offset, scale, window, int(causal), stream), "attn_fwd")
 
 
 def dense_tiles(m: int) -> list[list[int]]:

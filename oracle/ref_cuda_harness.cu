@@ -9,7 +9,8 @@
 //   gemv            backend/cuda.zig:2054-2073   grid ceil(n/4), block 128
 //   mul_mm_mma      backend/cuda.zig:2075-2140   grid (tiles, ceil(n/n_tile), split_k), block (16, 16 | 8)
 //   launch plan     backend/cuda.zig:1940-1987   N64 / N32 tiles and split-K 2 (3 for Q6_K) below 7/8 of the SMs
-//   split-K reduce  backend/cuda/kernels.cu:454-483
+//   split-K reduce  backend/cuda/kernels.cu:454-483, launched as backend/cuda.zig:2136-2143
+//   attention       backend/cuda.zig:2684-2708   grid (ceil(q_seq/4), heads), block 128
 // Format ids follow the reference's QFormat order: 0 q8_0, 1 q6_K, 2 q4_K, 3 q5_K.
 #include <cuda_runtime.h>
 
@@ -84,6 +85,22 @@ int refk_mul_mm(int fmt, const void* w, const float* a, const void* tiles, int n
         if (cudaGetLastError() != cudaSuccess) return -1;
     }
     return 0;
+}
+
+// Streaming attention forward: q/o [q_seq][heads][d] f32, k/v [kv_seq][kv_heads][d] f16 or f32, kvmap [heads],
+// stats (may be null) [heads][q_seq][2].
+int refk_attn_fwd(int kv_is_f16, const float* q, const void* k, const void* v, float* o, float* stats, const int* kvmap, int q_seq,
+                  int kv_seq, int heads, int kv_heads, int d, int source_offset, float scale, int window, int causal, void* stream) {
+    if (q_seq < 1 || kv_seq < 1 || heads < 1 || kv_heads < 1 || d < 1 || d > ATTN_MAX_D) return 1;
+    dim3 grid((q_seq + ATTN_WARPS - 1) / ATTN_WARPS, heads), block(32 * ATTN_WARPS);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (kv_is_f16)
+        fucina_attn_fwd_f16<<<grid, block, 0, st>>>(q, (const __half*)k, (const __half*)v, o, stats, kvmap, q_seq, kv_seq, heads, kv_heads, d,
+                                                    source_offset, scale, window, causal);
+    else
+        fucina_attn_fwd_f32<<<grid, block, 0, st>>>(q, (const float*)k, (const float*)v, o, stats, kvmap, q_seq, kv_seq, heads, kv_heads, d,
+                                                    source_offset, scale, window, causal);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 }  // extern "C"

@@ -128,3 +128,36 @@ def test_grouped_tiles_against_reference(P, torch):
     # runs of 1 and 7 rows multiply on the integer kernel, those of 33 and 40 rows on the tensor cores
     rms, worst = rms_err(got, ref.cpu().numpy())
     assert rms <= 1e-2 and worst <= 5e-2, f"grouped q5_k against the reference tiles: rms {rms:.2e}, worst {worst:.2e}"
+
+
+@pytest.mark.parametrize("q_seq,kv_seq,heads,kv_heads,d,window,causal,f16", [
+    (64, 64, 8, 4, 64, 0, True, True),       # the reference's prefill cases (src/backend/cuda.zig:3484-3556)
+    (33, 97, 4, 4, 48, 0, True, True),
+    (40, 40, 8, 2, 128, 16, True, True),
+    (37, 37, 6, 3, 80, 0, False, True),
+    (1, 4099, 32, 8, 128, 0, True, True),    # a decode step: splits merged by this library's second kernel
+    (2, 777, 8, 2, 64, 0, True, False),      # f32 KV
+])
+def test_attention_against_reference_kernel(P, torch, q_seq, kv_seq, heads, kv_heads, d, window, causal, f16):
+    g = torch.Generator(device="cuda").manual_seed(7500 + kv_seq)
+    q = torch.randn((q_seq, heads, d), generator=g, device="cuda")
+    kv_t = torch.float16 if f16 else torch.float32
+    k = torch.randn((kv_seq, kv_heads, d), generator=g, device="cuda").to(kv_t)
+    v = torch.randn((kv_seq, kv_heads, d), generator=g, device="cuda").to(kv_t)
+    kvmap = torch.tensor([h * kv_heads // heads for h in range(heads)], dtype=torch.int32, device="cuda")
+    offset, scale = kv_seq - q_seq, float(1.0 / np.sqrt(d))
+    ref, got = (torch.full_like(q, float("nan")) for _ in range(2))
+    ref_s, got_s = (torch.full((heads, q_seq, 2), float("nan"), device="cuda") for _ in range(2))
+    torch.cuda.synchronize()
+    ref_cuda.attn_fwd(f16, q.data_ptr(), k.data_ptr(), v.data_ptr(), ref.data_ptr(), ref_s.data_ptr(), kvmap.data_ptr(), q_seq, kv_seq, heads,
+                      kv_heads, d, offset, scale, window, causal)
+    torch.cuda.synchronize()
+    P.attn_fwd_dev(q, k, v, f16, got, kvmap, q_seq, kv_seq, heads, kv_heads, d, offset, scale, window, causal, stats_dev=got_s)
+    P.synchronize()
+    ref, got, ref_s, got_s = (t.cpu().numpy().astype(np.float64) for t in (ref, got, ref_s, got_s))
+    # the reference's own bound for this kernel against its f64 oracle (cuda.zig:3547-3552), here between the two kernels
+    tol = np.maximum(2e-3 * np.maximum(np.abs(ref), np.abs(got)), 2e-3)
+    assert np.isfinite(got).all() and np.all(np.abs(got - ref) <= tol), float(np.max(np.abs(got - ref)))
+    # {row max, sum of exponentials}: the same pair up to f32 rounding of the scores
+    assert np.allclose(got_s[..., 0], ref_s[..., 0], rtol=0, atol=2e-3)
+    assert np.allclose(got_s[..., 1], ref_s[..., 1], rtol=4e-3, atol=0)
