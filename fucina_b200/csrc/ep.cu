@@ -446,8 +446,8 @@ int check_ep_weights(const fq_weights* gate, const fq_weights* up, const fq_weig
 }
 
 bool fused_form_serves(const DevWeights& g, const DevWeights& d) {
-    return (g.fmt == FQ_Q4_K || g.fmt == FQ_Q5_K || g.fmt == FQ_Q8_0) && (d.fmt == FQ_Q4_K || d.fmt == FQ_Q5_K || d.fmt == FQ_Q8_0) &&
-           tensor_path_serves(g) && tensor_path_serves(d) && g.k % 8 == 0;
+    auto stack_fmt = [](int f) { return f == FQ_Q4_K || f == FQ_Q5_K || f == FQ_Q6_K || f == FQ_Q8_0; };  // as the one-GPU tensor arm
+    return stack_fmt(g.fmt) && stack_fmt(d.fmt) && tensor_path_serves(g) && tensor_path_serves(d) && g.k % 8 == 0;
 }
 
 }  // namespace

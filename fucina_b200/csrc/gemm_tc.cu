@@ -1105,6 +1105,7 @@ static int launch_tc_rows(Ctx* ctx, const DevWeights& w, int mat, const __nv_bfl
         switch (w.fmt) {
             case FQ_Q4_K: e = launch_tc_tn<FQ_Q4_K, 128, true>(a, tmap, tmap_w, tmap_w2, grid, st); break;
             case FQ_Q5_K: e = launch_tc_tn<FQ_Q5_K, 128, true>(a, tmap, tmap_w, tmap_w2, grid, st); break;
+            case FQ_Q6_K: e = launch_tc_tn<FQ_Q6_K, 128, true>(a, tmap, tmap_w, tmap_w2, grid, st); break;
             default: e = launch_tc_tn<FQ_Q8_0, 128, true>(a, tmap, tmap_w, tmap_w2, grid, st); break;
         }
         g_trace.launches++;
@@ -1142,8 +1143,8 @@ int gemm_tensor_grouped_dev(Ctx* ctx, const DevWeights& w, const void* a_bf16, s
 int gemm_tensor_grouped_gated_dev(Ctx* ctx, const DevWeights& gate, const DevWeights& up, const void* a_bf16, size_t rows, void* g_bf16,
                                   size_t ldc, const TcTile* table, const int* n_tiles_dev, int max_tiles, cudaStream_t st,
                                   const TcPeer* peer, int gated_op) {
-    if (!tensor_path_serves(gate) || (gate.fmt != FQ_Q4_K && gate.fmt != FQ_Q5_K && gate.fmt != FQ_Q8_0))
-        return fail(FQ_DECLINED_ARGS, "the gated tensor-core form serves Q4_K, Q5_K and Q8_0 with k %% 256 == 0");
+    if (!tensor_path_serves(gate) || (gate.fmt != FQ_Q4_K && gate.fmt != FQ_Q5_K && gate.fmt != FQ_Q6_K && gate.fmt != FQ_Q8_0))
+        return fail(FQ_DECLINED_ARGS, "the gated tensor-core form serves Q4_K, Q5_K, Q6_K and Q8_0 with k %% 256 == 0");
     if (up.fmt != gate.fmt || up.n != gate.n || up.k != gate.k || up.n_mats != gate.n_mats || up.tile_rows != gate.tile_rows ||
         up.row_stride != gate.row_stride || up.mat_stride != gate.mat_stride)
         return fail(FQ_DECLINED_ARGS, "gate and up stacks differ in shape or layout");

@@ -409,9 +409,10 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     const int pairs = seq * top_k;
     // prefill-sized batches: bf16 tensor-core products (the reference's own GPU arm multiplies rounded
     // operands too); decode-sized batches keep the CPU kernels' int8 arithmetic
-    // the grouped tensor-core form is exercised for the formats expert stacks come in (K-quants and Q8_0)
-    const bool tc_ok = (fmt == FQ_Q4_K || fmt == FQ_Q5_K || fmt == FQ_Q8_0) && tensor_path_serves(gate) && tensor_path_serves(down) &&
-                       (fmt_dn == FQ_Q4_K || fmt_dn == FQ_Q5_K || fmt_dn == FQ_Q8_0);
+    // the grouped tensor-core form is exercised for the formats expert stacks come in (K-quants, Q6_K down tensors of
+    // the mixed K-quant files included, and Q8_0)
+    auto stack_fmt = [](int f) { return f == FQ_Q4_K || f == FQ_Q5_K || f == FQ_Q6_K || f == FQ_Q8_0; };
+    const bool tc_ok = stack_fmt(fmt) && stack_fmt(fmt_dn) && tensor_path_serves(gate) && tensor_path_serves(down);
     const bool tapped = taps.g_pairs || taps.down_pairs;  // the taps read the integer arm's intermediates
     if (!tapped && tc_ok && (g_moe_tensor_mode == 1 || (g_moe_tensor_mode < 0 && pairs >= 17 * n_expert)))
         return moe_layer_tensor_impl(ctx, gate, up, down, x_dev, seq, top_k, selected_dev, weights_dev, shard, out_dev, st, gated_op);
