@@ -124,3 +124,108 @@ def test_random_moe_layer(P, seed):
         load().fq_set_moe_tensor_for_test(-1)
         for h in (wg, wu, wd):
             h.free()
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_attention(P, seed):
+    """Streaming attention on drawn shapes (rows, keys, head grouping, head size, window, causal or not, f16 or f32 KV)
+    against the f64 oracle with the reference's own bound (src/backend/cuda.zig:3547-3552)."""
+    from test_gpu_attention import attn_f64, check
+
+    rng = np.random.default_rng(98_000 + seed)
+    kv_heads = int(rng.choice([1, 2, 3, 4, 8]))
+    group = int(rng.choice([1, 2, 3, 4, 5, 8]))
+    heads = kv_heads * group
+    d = 8 * int(rng.integers(1, 33))
+    f16 = bool(rng.integers(2))
+    if not f16:
+        d = 4 * int(rng.integers(1, 65))
+    q_seq = int(rng.choice([1, 1, 1, 2, 3, 7, 16, 40]))
+    kv_seq = q_seq + int(rng.choice([0, 1, 31, 64, 129, 500, 1500, 4100]))
+    causal = bool(rng.integers(4))  # one in four bidirectional
+    window = int(rng.choice([0, 0, 16, 100, 1000])) if causal else 0
+    q = rng.standard_normal((q_seq, heads, d)).astype(np.float32)
+    k = rng.standard_normal((kv_seq, kv_heads, d)).astype(np.float16 if f16 else np.float32)
+    v = rng.standard_normal((kv_seq, kv_heads, d)).astype(k.dtype)
+    kvmap = rng.permutation(np.repeat(np.arange(kv_heads), group)).tolist() if seed % 2 else [h // group for h in range(heads)]
+    scale = float(1.0 / np.sqrt(d))
+    got, stats = P.attn_fwd(q, k, v, kvmap, kv_seq - q_seq, scale, window, causal, want_stats=True)
+    want, want_stats = attn_f64(q, k, v, kvmap, kv_seq - q_seq, scale, window, causal)
+    check(got, want)
+    assert np.allclose(stats[..., 0], want_stats[..., 0], rtol=1e-5, atol=1e-5), f"seed {seed}: row maxima"
+    assert np.allclose(stats[..., 1], want_stats[..., 1], rtol=2e-4), f"seed {seed}: sums of exponentials"
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_grouped_tables(P, seed):
+    """The grouped entry over drawn tile tables in the reference's form {expert, group base, group rows, tile index}:
+    experts in any order, empty experts left out, groups of 1 to 150 rows; each group against the oracle of the arm
+    that serves its run length (tensor cores from 17 rows, the integer kernel below)."""
+    from fucina_b200._lib import load
+
+    rng = np.random.default_rng(99_000 + seed)
+    name = ["q4_k", "q5_k", "q8_0", "q6_k"][int(rng.integers(4))]
+    fmt = oracle.FORMATS[name]
+    n_expert = int(rng.integers(1, 9))
+    n_out = 4 * int(rng.integers(1, 80))
+    k = 256 * int(rng.integers(1, 5))
+    counts = [int(c) for c in rng.choice([0, 0, 1, 2, 5, 8, 16, 17, 31, 32, 33, 64, 65, 150], size=n_expert)]
+    if sum(counts) == 0:
+        counts[0] = 3
+    order = rng.permutation(n_expert).tolist()
+    blocks = make_weights(name, n_out * n_expert, k, seed=99_100 + seed)
+    rows = sum(counts)
+    a = rng.standard_normal((rows, k)).astype(np.float32)
+    tiles, base, where = [], 0, {}
+    for e in order:  # groups laid out in the drawn expert order
+        if counts[e] == 0:
+            continue
+        where[e] = base
+        tiles += [(e, base, counts[e], t) for t in range((counts[e] + 31) // 32)]
+        base += counts[e]
+    lib = load()
+    lib.fq_qmoe_lock()
+    try:
+        pin, pout = P.qmoe_stage(rows * k, rows * n_out)
+        pin[:] = a.reshape(-1)
+        pout[:] = np.nan
+        P.gemm_q_grouped_nt(fmt, blocks, n_out, k, tiles)
+        got = np.array(pout).reshape(rows, n_out)
+    finally:
+        lib.fq_qmoe_unlock()
+    for e, b in where.items():
+        m = counts[e]
+        w, x, y = blocks[e * n_out:(e + 1) * n_out], a[b:b + m], got[b:b + m]
+        ea = rel_err(y, oracle.matmul(fmt, w, x))
+        eb = rel_err(y, oracle.matmul_dequant_f64(fmt, w, x, round_bf16=True))
+        assert (ea <= TOL_INT8) if m < 17 else (eb <= TOL_TENSOR or ea <= TOL_INT8), \
+            f"seed {seed}: {name} expert {e} ({m} rows at {b}): {ea:.2e} from the int8 oracle, {eb:.2e} from the bf16 oracle"
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_ptqtp_planes(P, torch, seed):
+    """One to three ternary planes summed per element in plane order (src/weights.zig:204-300) on drawn shapes."""
+    rng = np.random.default_rng(99_500 + seed)
+    planes = int(rng.integers(1, 4))
+    k = 256 * int(rng.integers(1, 17))
+    n = 4 * int(rng.integers(1, 130))
+    m = int(rng.choice([1, 1, 2, 3, 4, 5, 8, 16, 33, 64]))
+    ps = []
+    for p in range(planes):
+        trits = rng.integers(-1, 2, size=(n, k)).astype(np.int8)
+        scales = np.abs(rng.standard_normal((n, k // 256)) * 0.02 / (p + 1)).astype(np.float32)
+        ps.append(oracle.pack_ptqtp_plane(trits, scales))
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    ws = [P.Weights.upload(oracle.FORMATS["tq2_0"], b, n, k) for b in ps]
+    ad = torch.from_numpy(a).cuda()
+    cd = torch.full((m, n), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    P.gemm_ptqtp_dev(ws, ad, cd, m)
+    P.synchronize()
+    got = cd.cpu().numpy()
+    for w in ws:
+        w.free()
+    ea = rel_err(got, oracle.matmul_ptqtp(ps, a))
+    want_b = sum(oracle.matmul_dequant_f64(oracle.FORMATS["tq2_0"], b, a, round_bf16=True) for b in ps)
+    eb = rel_err(got, want_b)
+    assert ea <= TOL_INT8 or eb <= TOL_TENSOR, f"seed {seed}: K={planes} {m}x{n}x{k}: {ea:.2e} from the int8 oracle, {eb:.2e} from the bf16 oracle"
