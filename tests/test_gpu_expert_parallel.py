@@ -71,6 +71,7 @@ def single_gpu_tensor_arm(P, torch, full, x, sel, w, top_k):
     ("q5_k", 512, 256, 16, 4, 8, 40),     # two experts per rank, ragged runs
     ("q4_k", 256, 512, 8, 2, 4, 130),     # expert runs longer than one 128-token tile
     ("q8_0", 256, 256, 4, 2, 4, 33),      # one expert per rank
+    ("q6_k", 512, 256, 8, 2, 4, 70),      # the six-bit K-quant (the down tensors of mixed K-quant files)
     ("q5_k", 2048, 768, 128, 8, 8, 64),   # the benchmark layer: 16 experts per rank
     ("q5_k", 512, 256, 8, 3, 1, 50),      # a single rank: every panel is its own
 ])
