@@ -433,25 +433,45 @@ def _cpu_time(fn, budget_s: float, max_calls: int = 100000) -> tuple[float, int]
             return dt / calls, calls
 
 
+def _cpu_stack_step(host_w, host_x):
+    """The CPU arm to time for the Q4_K stack: the reference's load-time eight-row repack (BlockQ4_Kx8,
+    src/backend/quant/q4_k.zig:127-192, :1733-1782) where this host can run it, else the compact row kernels;
+    whichever is faster on a trial pass, as the reference's dispatch would keep the faster one. Returns (step, label)."""
+    import oracle
+
+    def compact():
+        for w, x in zip(host_w, host_x):
+            oracle.matmul_fast(Q4_K, w, x)
+
+    label = "AVX2 compact block dots" if oracle.has_simd(Q4_K) else "scalar block dots"
+    packs = [oracle.PackedRows.pack(Q4_K, w, K) for w in host_w]
+    if any(p is None for p in packs):
+        return compact, label
+
+    def packed():
+        for p, x in zip(packs, host_x):
+            p.matmul(x)
+
+    t_c, _ = _cpu_time(compact, 0.3, 50)
+    t_p, _ = _cpu_time(packed, 0.3, 50)
+    return (packed, "AVX2 eight-row packs (BlockQ4_Kx8, packed once before the timed region)") if t_p < t_c else (compact, label)
+
+
 def cpu_baseline(host_w, host_x, budget_s: float) -> dict:
-    """The CPU restatement of the reference kernels (activations to Q8_K, dotQ4_KQ8_K rows,
+    """The CPU restatement of the reference kernels (activations to Q8_K, Q4_K block dots on the fastest arm,
     output columns split over the host threads) on one stack copy, a few passes; all host threads, then one."""
     import oracle
 
     bytes_step = stack_bytes(1)
     cores = oracle.set_threads(0)
-
-    def step():
-        for w, x in zip(host_w, host_x):
-            oracle.matmul_fast(Q4_K, w, x)
+    step, arm = _cpu_stack_step(host_w, host_x)
 
     sec, passes = _cpu_time(step, budget_s, 5000)
     oracle.set_threads(1)
     sec1, passes1 = _cpu_time(step, min(budget_s, 3.0), 5000)
     oracle.set_threads(0)
     return {"value": round(bytes_step / sec / 1e9, 3), "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": f"{passes} pass(es) of the full stack (4 products, batch 1), {sec * passes:.1f} s, "
-                      + ("AVX2 block dots" if oracle.has_simd(Q4_K) else "scalar block dots"),
+            "sample": f"{passes} pass(es) of the full stack (4 products, batch 1), {sec * passes:.1f} s, " + arm,
             "ms_per_step": round(sec * 1e3, 3),
             "single_thread": {"value": round(bytes_step / sec1 / 1e9, 3), "unit": "GB/s", "ms_per_step": round(sec1 * 1e3, 3), "passes": passes1}}
 
@@ -473,9 +493,7 @@ def run_reference(args) -> dict:
     xs = [rng.standard_normal((1, K)).astype(np.float32) for _ in STACK_N]
     bytes_step = stack_bytes(1)
 
-    def step():
-        for w, x in zip(ws, xs):
-            oracle.matmul_fast(Q4_K, w, x)
+    step, arm = _cpu_stack_step(ws, xs)
 
     for _ in range(args.warmup):
         step()
@@ -490,8 +508,7 @@ def run_reference(args) -> dict:
     dt = time.perf_counter() - t0
     n_steps = repeats * args.steps
     value = round(bytes_step * n_steps / dt / 1e9, 3)
-    sample = (f"the full stack (4 products, batch 1) per step, {repeats} x {args.steps} steps, {dt:.1f} s, {cores} threads, "
-              + ("AVX2 block dots" if oracle.has_simd(Q4_K) else "scalar block dots"))
+    sample = f"the full stack (4 products, batch 1) per step, {repeats} x {args.steps} steps, {dt:.1f} s, {cores} threads, " + arm
     return {
         "impl": "reference", "metric": "quant GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / n_steps * 1e3, 4),
@@ -672,12 +689,16 @@ def sub_q8_0(args, P, torch, want_cpu: bool) -> list[dict]:
     if want_cpu:
         xh = x.cpu().numpy()
         cores = oracle.set_threads(0)
-        sec, calls = _cpu_time(lambda: oracle.matmul_fast(F.Q8_0, host, xh), 1.5)
+        fn, arm = (lambda: oracle.matmul_fast(F.Q8_0, host, xh)), ("AVX2 block dots" if oracle.has_simd(F.Q8_0) else "scalar")
+        pk = oracle.PackedRows.pack(F.Q8_0, host, k)  # the reference's four-row pack (BlockQ8_0x4), kept if it is the faster arm here
+        if pk is not None and _cpu_time(lambda: pk.matmul(xh), 0.2, 50)[0] < _cpu_time(fn, 0.2, 50)[0]:
+            fn, arm = (lambda: pk.matmul(xh)), "AVX2 four-row packs (BlockQ8_0x4)"
+        sec, calls = _cpu_time(fn, 1.5)
         oracle.set_threads(1)
-        sec1, _ = _cpu_time(lambda: oracle.matmul_fast(F.Q8_0, host, xh), 1.0)
+        sec1, _ = _cpu_time(fn, 1.0)
         oracle.set_threads(0)
         rec["cpu_baseline"] = {"value": round(nbytes / sec / 1e9, 2), "unit": "GB/s", "cores": cores, "kind": "port",
-                               "sample": f"{calls} products, {sec * calls:.1f} s, " + ("AVX2 block dots" if oracle.has_simd(F.Q8_0) else "scalar"),
+                               "sample": f"{calls} products, {sec * calls:.1f} s, " + arm,
                                "single_thread": {"value": round(nbytes / sec1 / 1e9, 2), "unit": "GB/s"}}
     return [rec]
 
@@ -711,12 +732,16 @@ def sub_prefill(args, P, torch, want_cpu: bool) -> list[dict]:
         host = oracle.quantize_rows(F.Q4_K, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
         ah = rng.standard_normal((32, k)).astype(np.float32)
         cores = oracle.set_threads(0)
-        sec, calls = _cpu_time(lambda: oracle.matmul_fast(F.Q4_K, host, ah), 2.0)
+        pk, pk1 = oracle.PackedRows.pack(F.Q4_K, host, k), oracle.PackedRows.pack(F.Q4_K, host[:2048], k)
+        full = (lambda: pk.matmul(ah)) if pk else (lambda: oracle.matmul_fast(F.Q4_K, host, ah))
+        part = (lambda: pk1.matmul(ah)) if pk1 else (lambda: oracle.matmul_fast(F.Q4_K, host[:2048], ah))
+        sec, calls = _cpu_time(full, 2.0)
         oracle.set_threads(1)
-        sec1, _ = _cpu_time(lambda: oracle.matmul_fast(F.Q4_K, host[:2048], ah), 1.0)
+        sec1, _ = _cpu_time(part, 1.0)
         oracle.set_threads(0)
         cpu = {"value": round(2.0 * 32 * n * k / sec / 1e12, 4), "unit": "TFLOP/s", "cores": cores, "kind": "port",
-               "sample": f"32 activation rows x the whole 14336 x 4096 matrix, {calls} passes, {sec * calls:.1f} s, int8 block dots",
+               "sample": f"32 activation rows x the whole 14336 x 4096 matrix, {calls} passes, {sec * calls:.1f} s, int8 block dots"
+                         + (" over eight-row packs (BlockQ4_Kx8)" if pk else ""),
                "single_thread": {"value": round(2.0 * 32 * 2048 * k / sec1 / 1e12, 4), "unit": "TFLOP/s", "sample": "32 rows x 2048 weight rows"}}
         for r in recs:
             r["cpu_baseline"] = cpu
@@ -797,13 +822,21 @@ def sub_moe(args, P, torch, want_cpu: bool) -> list[dict]:
         hg, hu, hd = (w.host for w in stacks)
         rng = np.random.default_rng(3000)
         cores = oracle.set_threads(0)
+        # the reference's fastest arm for K-quant expert stacks: the load-time eight-row repack (BlockQ5_Kx8)
+        packs = [oracle.PackedRows.pack(F.Q5_K, b, kk) for b, kk in ((hg, MOE["hidden"]), (hu, MOE["hidden"]), (hd, MOE["ffn"]))]
+        if any(p is None for p in packs):
+            packs = None
         for rec, T, Ts in zip(recs, (1, 64, 1024), (1, 64, 64)):
             x = rng.standard_normal((Ts, MOE["hidden"])).astype(np.float32)
             sel, wts = oracle.router_topk(rng.standard_normal((Ts, MOE["experts"])).astype(np.float32), MOE["top_k"], True)
-            fn = lambda: oracle.moe_ffn_fast(F.Q5_K, hg, hu, hd, x, sel, wts, MOE["experts"], MOE["ffn"])  # noqa: E731
+            if packs:
+                fn = lambda: oracle.moe_ffn_packed(*packs, x, sel, wts, MOE["experts"], MOE["ffn"])  # noqa: E731
+            else:
+                fn = lambda: oracle.moe_ffn_fast(F.Q5_K, hg, hu, hd, x, sel, wts, MOE["experts"], MOE["ffn"])  # noqa: E731
             sec, calls = _cpu_time(fn, 2.0)
             rec["cpu_baseline"] = {"value": round(Ts / sec, 1), "unit": "tok/s", "cores": cores, "kind": "port",
-                                   "sample": f"{Ts} token(s) per pass" + (" (a 64-token sample of the 1024)" if T != Ts else "") + f", {calls} passes, {sec * calls:.1f} s"}
+                                   "sample": f"{Ts} token(s) per pass" + (" (a 64-token sample of the 1024)" if T != Ts else "") + f", {calls} passes, {sec * calls:.1f} s"
+                                             + (", eight-row packs (BlockQ5_Kx8)" if packs else "")}
             if T == 1:
                 oracle.set_threads(1)
                 sec1, _ = _cpu_time(fn, 1.0)

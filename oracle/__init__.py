@@ -178,6 +178,67 @@ def matmul_fast(fmt: int, blocks: np.ndarray, a: np.ndarray) -> np.ndarray:
     return c
 
 
+class PackedRows:
+    """The reference's load-time repack of a Q4_K / Q5_K matrix (eight rows interleaved per block, BlockQ4_Kx8 /
+    BlockQ5_Kx8, src/backend/quant/types.zig:99-119) and its kernels, restated in oracle/cpu_kernels.cpp: the fastest
+    CPU arm for K-quants. `PackedRows.pack` returns None where the pack does not exist (other formats, a row count that
+    is not a multiple of eight, no AVX2 / F16C); results are bit-equal to `matmul`."""
+
+    def __init__(self, handle, fmt, n, k):
+        self._h, self.fmt, self.n, self.k = handle, fmt, n, k
+
+    @classmethod
+    def pack(cls, fmt: int, blocks: np.ndarray, k: int):
+        f = fast_lib()
+        if f is None or not hasattr(f, "cpuk_pack_rows"):
+            return None
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        n = blocks.shape[0]
+        f.cpuk_pack_rows.restype = ctypes.c_void_p
+        h = f.cpuk_pack_rows(fmt, _p(blocks), _sz(blocks.shape[1]), _sz(n), _sz(k))
+        return cls(h, fmt, n, k) if h else None
+
+    @property
+    def nbytes(self) -> int:
+        f = fast_lib()
+        f.cpuk_packed_bytes.restype = ctypes.c_size_t
+        return int(f.cpuk_packed_bytes(ctypes.c_void_p(self._h)))
+
+    def matmul(self, a: np.ndarray) -> np.ndarray:
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        m, k = a.shape
+        assert k == self.k
+        c = np.zeros((m, self.n), dtype=np.float32)
+        rc = fast_lib().cpuk_matmul_packed(ctypes.c_void_p(self._h), _p(a), _p(c), _sz(m))
+        assert rc == 0
+        return c
+
+    def free(self) -> None:
+        if self._h:
+            fast_lib().cpuk_free_packed(ctypes.c_void_p(self._h))
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+
+def moe_ffn_packed(gate: PackedRows, up: PackedRows, down: PackedRows, x, selected, weights, n_expert: int, out_pe: int) -> np.ndarray:
+    """`moe_ffn` (swiglu) over packed expert stacks: the timed CPU baseline of the expert layer on its fastest arm."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    seq, hidden = x.shape
+    sel = np.ascontiguousarray(selected, dtype=np.int64).reshape(seq, -1)
+    top_k = sel.shape[1]
+    w = np.ascontiguousarray(weights, dtype=np.float32).reshape(seq, top_k)
+    out = np.zeros((seq, hidden), dtype=np.float32)
+    rc = fast_lib().cpuk_moe_ffn_packed(ctypes.c_void_p(gate._h), ctypes.c_void_p(up._h), ctypes.c_void_p(down._h), _p(x), _sz(seq), _sz(hidden),
+                                    _sz(out_pe), _sz(n_expert), _sz(top_k), _p(sel), _p(w), _p(out))
+    assert rc == 0
+    return out
+
+
 def set_threads(n: int = 0) -> int:
     """Worker threads of the timed SIMD restatement (0 = all logical CPUs); returns the count in use. Set
     explicitly because launchers such as torchrun export OMP_NUM_THREADS=1."""

@@ -7,6 +7,13 @@
 // association, so the results equal oracle.cpp's bit for bit; tests/test_oracle_golden.py checks that.
 // Formats without a SIMD arm here (folded TQ2_0, Q2_0) run the scalar oracle code.
 //
+// The reference's fastest K-quant arm is not the compact row walk but a repack done once at load time: eight
+// weight rows interleaved per 256-weight block (BlockQ4_Kx8 / BlockQ5_Kx8, src/backend/quant/types.zig:99-119,
+// packed by q4_k.zig:127-192 / q5_k.zig:57-123, multiplied by q4_k.zig:1733-1782 / q5_k.zig:826-885). cpuk_pack_rows and
+// cpuk_matmul_packed restate that arm: the same layout, eight columns per step against a broadcast of four activation
+// bytes, integer sub-block sums scaled in int32, one f32 epilogue per block -- bit-equal to the compact kernels,
+// as the reference's own tests require (q4_k_tests.zig:852-896, q5_k_tests.zig:92-137).
+//
 // Threading follows QuantizedRhsParallel (src/backend/vector/matmul_quant.zig:522-616): products of
 // fewer than 32 activation rows split the output columns into min(workers, n / 64) contiguous ranges
 // once m*n*k >= 2^20, larger ones split the rows; results do not depend on the split. The worker count
@@ -160,6 +167,151 @@ inline float any_row_dot(bool simd, int fmt, const uint8_t* wrow, const void* ar
     return simd ? row_dot_fast(fmt, wrow, arow, k) : row_dot(fmt, wrow, arow, k);
 }
 
+// ---- eight-row packs ------------------------------------------------------------------------------
+// Column c of the group is weight row 8 * group + c. scales / mins: [sub-block][column]. Q4_K qs: byte
+// pair * 256 + fg * 32 + c * 4 + l = payload byte pair * 32 + fg * 4 + l of column c (low nibble: sub-block 2 * pair,
+// high nibble: 2 * pair + 1). Q5_K qs: byte sub * 256 + fg * 32 + c * 4 + l = the five-bit level of element
+// sub * 32 + fg * 4 + l of column c.
+struct BlockQ4_Kx8 {
+    uint16_t d[8], dmin[8];
+    uint8_t scales[64], mins[64];
+    uint8_t qs[1024];
+};
+struct BlockQ5_Kx8 {
+    uint16_t d[8], dmin[8];
+    uint8_t scales[64], mins[64];
+    uint8_t qs[2048];
+};
+static_assert(sizeof(BlockQ4_Kx8) == 1184 && sizeof(BlockQ5_Kx8) == 2208, "packed block sizes");
+
+// Q8_0: four rows interleaved per 32-weight block (BlockQ8_0x4, types.zig:78-81, packed by q8_0.zig:259-303):
+// qs byte fg * 16 + c * 4 + l = weight fg * 4 + l of column c.
+struct BlockQ8_0x4 {
+    uint16_t d[4];
+    int8_t qs[128];
+};
+static_assert(sizeof(BlockQ8_0x4) == 136, "packed block size");
+
+struct PackedRows {
+    int fmt = 0, group = 8;  // rows interleaved per packed block: 8 (K-quants) or 4 (Q8_0)
+    size_t n = 0, k = 0, blocks_per_row = 0;
+    std::vector<uint8_t> data;  // [n / group][blocks_per_row] packed blocks
+};
+
+template <class Src, class Dst>
+void pack_header_x8(const Src* const cols[8], Dst* dst) {
+    for (int c = 0; c < 8; ++c) {
+        dst->d[c] = cols[c]->dm[0];
+        dst->dmin[c] = cols[c]->dm[1];
+    }
+    for (int sub = 0; sub < 8; ++sub)
+        for (int c = 0; c < 8; ++c) get_scale_min_k4(cols[c]->scales, sub, &dst->scales[sub * 8 + c], &dst->mins[sub * 8 + c]);
+}
+
+inline int q5_level(const BlockQ5_K* b, int sub, int i) {  // q5_k.zig:1259-1264
+    const int nib = (sub & 1) ? (b->qs[(sub >> 1) * 32 + i] >> 4) : (b->qs[(sub >> 1) * 32 + i] & 0x0f);
+    return nib + (((b->qh[i] >> sub) & 1) << 4);
+}
+
+// dst[c] += d_w[c] d_a f32(iscale[c]) - dmin_w[c] d_a f32(imin[c]) for the eight columns of one packed block
+__attribute__((target("avx2,f16c"))) inline __m256 epilogue_x8(const uint16_t* d, const uint16_t* dmin, float da, __m256i iscale, __m256i imin,
+                                                              __m256 acc) {
+    const __m256 dav = _mm256_set1_ps(da);
+    const __m256 dd = _mm256_mul_ps(_mm256_cvtph_ps(_mm_loadu_si128((const __m128i*)d)), dav);
+    const __m256 dm = _mm256_mul_ps(_mm256_cvtph_ps(_mm_loadu_si128((const __m128i*)dmin)), dav);
+    const __m256 term = _mm256_sub_ps(_mm256_mul_ps(dd, _mm256_cvtepi32_ps(iscale)), _mm256_mul_ps(dm, _mm256_cvtepi32_ps(imin)));
+    return _mm256_add_ps(acc, term);
+}
+__attribute__((target("avx2"))) inline __m256i widen_u8x8(const uint8_t* p) { return _mm256_cvtepu8_epi32(_mm_loadl_epi64((const __m128i*)p)); }
+__attribute__((target("avx2"))) inline __m256i bcast4(const int8_t* p) {
+    int32_t v;
+    memcpy(&v, p, 4);
+    return _mm256_set1_epi32(v);
+}
+
+__attribute__((target("avx2,f16c"))) inline __m256 accumulate_q4_kx8(const BlockQ4_Kx8* w, const BlockQ8_K* a, __m256 acc) {
+    const __m256i low_mask = _mm256_set1_epi8(0x0f), ones = _mm256_set1_epi16(1);
+    __m256i iscale = _mm256_setzero_si256(), imin = _mm256_setzero_si256();
+    for (int pair = 0; pair < 4; ++pair) {
+        const int even = 2 * pair, odd = even + 1;
+        __m256i sum_e = _mm256_setzero_si256(), sum_o = _mm256_setzero_si256();
+        for (int fg = 0; fg < 8; ++fg) {
+            const __m256i q = _mm256_loadu_si256((const __m256i*)(w->qs + pair * 256 + fg * 32));
+            const __m256i w_e = _mm256_and_si256(q, low_mask), w_o = _mm256_and_si256(_mm256_srli_epi16(q, 4), low_mask);
+            // four levels (<= 15) times four activations per column: pair sums fit int16, group sums int32
+            sum_e = _mm256_add_epi32(sum_e, _mm256_madd_epi16(_mm256_maddubs_epi16(w_e, bcast4(a->qs + even * 32 + fg * 4)), ones));
+            sum_o = _mm256_add_epi32(sum_o, _mm256_madd_epi16(_mm256_maddubs_epi16(w_o, bcast4(a->qs + odd * 32 + fg * 4)), ones));
+        }
+        iscale = _mm256_add_epi32(iscale, _mm256_add_epi32(_mm256_mullo_epi32(sum_e, widen_u8x8(w->scales + even * 8)),
+                                                          _mm256_mullo_epi32(sum_o, widen_u8x8(w->scales + odd * 8))));
+        const __m256i bs_e = _mm256_set1_epi32((int32_t)a->bsums[2 * even] + (int32_t)a->bsums[2 * even + 1]);
+        const __m256i bs_o = _mm256_set1_epi32((int32_t)a->bsums[2 * odd] + (int32_t)a->bsums[2 * odd + 1]);
+        imin = _mm256_add_epi32(imin, _mm256_add_epi32(_mm256_mullo_epi32(bs_e, widen_u8x8(w->mins + even * 8)),
+                                                      _mm256_mullo_epi32(bs_o, widen_u8x8(w->mins + odd * 8))));
+    }
+    return epilogue_x8(w->d, w->dmin, a->d, iscale, imin, acc);
+}
+
+__attribute__((target("avx2,f16c"))) inline __m256 accumulate_q5_kx8(const BlockQ5_Kx8* w, const BlockQ8_K* a, __m256 acc) {
+    const __m256i ones = _mm256_set1_epi16(1);
+    __m256i iscale = _mm256_setzero_si256(), imin = _mm256_setzero_si256();
+    for (int sub = 0; sub < 8; ++sub) {
+        __m256i sum = _mm256_setzero_si256();
+        for (int fg = 0; fg < 8; ++fg) {
+            const __m256i q = _mm256_loadu_si256((const __m256i*)(w->qs + sub * 256 + fg * 32));  // levels <= 31: pair sums fit int16
+            sum = _mm256_add_epi32(sum, _mm256_madd_epi16(_mm256_maddubs_epi16(q, bcast4(a->qs + sub * 32 + fg * 4)), ones));
+        }
+        iscale = _mm256_add_epi32(iscale, _mm256_mullo_epi32(sum, widen_u8x8(w->scales + sub * 8)));
+        const __m256i bs = _mm256_set1_epi32((int32_t)a->bsums[2 * sub] + (int32_t)a->bsums[2 * sub + 1]);
+        imin = _mm256_add_epi32(imin, _mm256_mullo_epi32(bs, widen_u8x8(w->mins + sub * 8)));
+    }
+    return epilogue_x8(w->d, w->dmin, a->d, iscale, imin, acc);
+}
+
+// One packed Q8_0 block against one Q8_0 activation block: the reference's x4 law, (f32(t) * d_a) * d_w[c]
+// (q8_0.zig:1591-1613) -- a different f32 association from the compact dot's f32(t) * (d_a * d_w), so this arm
+// agrees with the compact kernels to rounding, not bit for bit.
+__attribute__((target("avx2,f16c"))) inline __m128 accumulate_q8_0x4(const BlockQ8_0x4* w, const BlockQ8_0* a, __m128 acc) {
+    const __m256i ones = _mm256_set1_epi16(1);
+    __m256i sum = _mm256_setzero_si256();
+    for (int g = 0; g < 4; ++g) {
+        const __m256i r = _mm256_loadu_si256((const __m256i*)(w->qs + g * 32));  // feature groups 2g | 2g + 1, four columns each
+        int32_t lo, hi;
+        memcpy(&lo, a->qs + 8 * g, 4);
+        memcpy(&hi, a->qs + 8 * g + 4, 4);
+        const __m256i b = _mm256_set_m128i(_mm_set1_epi32(hi), _mm_set1_epi32(lo));
+        // |w| as the unsigned operand, sign(w) moved onto the activation
+        sum = _mm256_add_epi32(sum, _mm256_madd_epi16(_mm256_maddubs_epi16(_mm256_sign_epi8(r, r), _mm256_sign_epi8(b, r)), ones));
+    }
+    const __m128i t = _mm_add_epi32(_mm256_castsi256_si128(sum), _mm256_extracti128_si256(sum, 1));
+    const __m128 dw = _mm_cvtph_ps(_mm_loadl_epi64((const __m128i*)w->d));
+    return _mm_add_ps(acc, _mm_mul_ps(_mm_mul_ps(_mm_cvtepi32_ps(t), _mm_set1_ps(h2f(a->d))), dw));
+}
+__attribute__((target("avx2,f16c"))) inline void group_dot_q8_0x4(const PackedRows& P, size_t group, const BlockQ8_0* a, float* out4) {
+    const BlockQ8_0x4* w = (const BlockQ8_0x4*)P.data.data() + group * P.blocks_per_row;
+    __m128 acc = _mm_setzero_ps();
+    for (size_t b = 0; b < P.blocks_per_row; ++b) acc = accumulate_q8_0x4(&w[b], &a[b], acc);
+    _mm_storeu_ps(out4, acc);
+}
+
+// eight outputs (rows 8 * group .. + 7 of the packed matrix) against one quantised activation row, blocks ascending
+__attribute__((target("avx2,f16c"))) inline void group_dot_x8(const PackedRows& P, size_t group, const BlockQ8_K* a, float* out8) {
+    __m256 acc = _mm256_setzero_ps();
+    if (P.fmt == Q4_K) {
+        const BlockQ4_Kx8* w = (const BlockQ4_Kx8*)P.data.data() + group * P.blocks_per_row;
+        for (size_t b = 0; b < P.blocks_per_row; ++b) acc = accumulate_q4_kx8(&w[b], &a[b], acc);
+    } else {
+        const BlockQ5_Kx8* w = (const BlockQ5_Kx8*)P.data.data() + group * P.blocks_per_row;
+        for (size_t b = 0; b < P.blocks_per_row; ++b) acc = accumulate_q5_kx8(&w[b], &a[b], acc);
+    }
+    _mm256_storeu_ps(out8, acc);
+}
+
+bool x8_supported() {
+    static const bool ok = __builtin_cpu_supports("avx2") && __builtin_cpu_supports("f16c");
+    return ok;
+}
+
 }  // namespace
 
 extern "C" {
@@ -239,6 +391,137 @@ int cpuk_moe_ffn(int fmt, const void* gate, const void* up, const void* down, co
             std::vector<uint8_t> qg = quantize_acts(fmt, g.data(), 1, out_pe, &s_g);
             float* po = pair_out.data() + (size_t)p * hidden;
             for (size_t j = 0; j < hidden; ++j) po[j] = any_row_dot(simd, fmt, wd + j * rb_g, qg.data(), out_pe);
+        }
+    }
+    for (size_t t = 0; t < seq; ++t)
+        for (size_t kk = 0; kk < top_k; ++kk) {
+            const size_t p = t * top_k + kk;
+            const float w = weights[p];
+            const float* src = pair_out.data() + p * hidden;
+            float* dst = out + t * hidden;
+            if (kk == 0)
+                for (size_t j = 0; j < hidden; ++j) dst[j] = w * src[j];
+            else
+                for (size_t j = 0; j < hidden; ++j) dst[j] += w * src[j];
+        }
+    return 0;
+}
+
+// ---- eight-row packs: the reference's load-time repack and its kernels (see the header comment) ----
+// Packs n rows of Q4_K or Q5_K blocks (n a multiple of 8) or of Q8_0 blocks (a multiple of 4); returns an opaque
+// handle, or null when the format has no pack, n does not fit or the host lacks AVX2 / F16C.
+void* cpuk_pack_rows(int fmt, const void* w, size_t nb01, size_t n, size_t k) {
+    if (!x8_supported() || n == 0 || k == 0 || row_bytes(fmt, k) == 0 || nb01 < row_bytes(fmt, k)) return nullptr;
+    const uint8_t* wb = (const uint8_t*)w;
+    if (fmt == Q8_0) {
+        if (n % 4 != 0) return nullptr;
+        PackedRows* P = new PackedRows();
+        P->fmt = fmt, P->group = 4, P->n = n, P->k = k, P->blocks_per_row = k / 32;
+        P->data.resize((n / 4) * P->blocks_per_row * sizeof(BlockQ8_0x4));
+#pragma omp parallel for schedule(static) num_threads(workers())
+        for (long long g = 0; g < (long long)(n / 4); ++g)
+            for (size_t b = 0; b < P->blocks_per_row; ++b) {
+                BlockQ8_0x4* d = (BlockQ8_0x4*)P->data.data() + (size_t)g * P->blocks_per_row + b;
+                for (int c = 0; c < 4; ++c) {
+                    const BlockQ8_0* src = (const BlockQ8_0*)(wb + ((size_t)g * 4 + c) * nb01) + b;
+                    d->d[c] = src->d;
+                    for (int fg = 0; fg < 8; ++fg) memcpy(d->qs + fg * 16 + c * 4, src->qs + fg * 4, 4);
+                }
+            }
+        return P;
+    }
+    if ((fmt != Q4_K && fmt != Q5_K) || n % 8 != 0) return nullptr;
+    PackedRows* P = new PackedRows();
+    P->fmt = fmt, P->n = n, P->k = k, P->blocks_per_row = k / 256;
+    const size_t bsz = fmt == Q4_K ? sizeof(BlockQ4_Kx8) : sizeof(BlockQ5_Kx8);
+    P->data.resize((n / 8) * P->blocks_per_row * bsz);
+#pragma omp parallel for schedule(static) num_threads(workers())
+    for (long long g = 0; g < (long long)(n / 8); ++g)
+        for (size_t b = 0; b < P->blocks_per_row; ++b) {
+            uint8_t* dst = P->data.data() + ((size_t)g * P->blocks_per_row + b) * bsz;
+            if (fmt == Q4_K) {
+                const BlockQ4_K* cols[8];
+                for (int c = 0; c < 8; ++c) cols[c] = (const BlockQ4_K*)(wb + ((size_t)g * 8 + c) * nb01) + b;
+                BlockQ4_Kx8* d = (BlockQ4_Kx8*)dst;
+                pack_header_x8(cols, d);
+                for (int pair = 0; pair < 4; ++pair)
+                    for (int fg = 0; fg < 8; ++fg)
+                        for (int c = 0; c < 8; ++c) memcpy(d->qs + pair * 256 + fg * 32 + c * 4, cols[c]->qs + pair * 32 + fg * 4, 4);
+            } else {
+                const BlockQ5_K* cols[8];
+                for (int c = 0; c < 8; ++c) cols[c] = (const BlockQ5_K*)(wb + ((size_t)g * 8 + c) * nb01) + b;
+                BlockQ5_Kx8* d = (BlockQ5_Kx8*)dst;
+                pack_header_x8(cols, d);
+                for (int sub = 0; sub < 8; ++sub)
+                    for (int fg = 0; fg < 8; ++fg)
+                        for (int c = 0; c < 8; ++c)
+                            for (int l = 0; l < 4; ++l) d->qs[sub * 256 + fg * 32 + c * 4 + l] = (uint8_t)q5_level(cols[c], sub, fg * 4 + l);
+            }
+        }
+    return P;
+}
+void cpuk_free_packed(void* packed) { delete (PackedRows*)packed; }
+size_t cpuk_packed_bytes(const void* packed) { return packed ? ((const PackedRows*)packed)->data.size() : 0; }
+
+// c[m, n] = a[m, k] . dequant(w)^T over a packed matrix: the same values as cpuk_matmul on the compact blocks.
+// Column arm as in cpuk_matmul, in whole groups of eight columns (QuantizedRhsParallel with col_group 8,
+// matmul_quant.zig:574-590; for these packs the reference keeps the column arm up to m < 64). Larger products split
+// the column groups over all workers here instead of the rows; values do not depend on the split.
+int cpuk_matmul_packed(const void* packed, const float* a, float* c, size_t m) {
+    if (!packed) return 1;
+    const PackedRows& P = *(const PackedRows*)packed;
+    size_t astride = 0;
+    std::vector<uint8_t> qa = quantize_acts(P.fmt, a, m, P.k, &astride);
+    const size_t G = (size_t)P.group, groups = P.n / G;
+    const int T = workers();
+    const unsigned __int128 work = (unsigned __int128)m * P.n * P.k;
+    long long tasks = m < 64 ? (work >= ((unsigned __int128)1 << 20) ? (long long)(P.n / 64) : 1) : T;
+    if (tasks > T) tasks = T;
+    if (tasks > (long long)groups) tasks = (long long)groups;
+    if (tasks < 1) tasks = 1;
+#pragma omp parallel for schedule(static, 1) num_threads((int)tasks)
+    for (long long t = 0; t < tasks; ++t) {
+        const size_t g0 = groups * (size_t)t / (size_t)tasks, g1 = groups * (size_t)(t + 1) / (size_t)tasks;
+        float out8[8];
+        for (size_t g = g0; g < g1; ++g)
+            for (size_t i = 0; i < m; ++i) {
+                if (P.fmt == Q8_0) group_dot_q8_0x4(P, g, (const BlockQ8_0*)(qa.data() + i * astride), out8);
+                else group_dot_x8(P, g, (const BlockQ8_K*)(qa.data() + i * astride), out8);
+                memcpy(c + i * P.n + g * G, out8, G * sizeof(float));
+            }
+    }
+    return 0;
+}
+
+// The expert layer over packed stacks (gate / up: n_expert * out_pe rows of `hidden`; down: n_expert * hidden rows of
+// out_pe; out_pe and hidden multiples of 8): cpuk_moe_ffn's structure with eight outputs per step.
+int cpuk_moe_ffn_packed(const void* gate, const void* up, const void* down, const float* x, size_t seq, size_t hidden, size_t out_pe,
+                    size_t n_expert, size_t top_k, const int64_t* selected, const float* weights, float* out) {
+    if (!gate || !up || !down) return 1;
+    const PackedRows &G = *(const PackedRows*)gate, &U = *(const PackedRows*)up, &D = *(const PackedRows*)down;
+    if (G.group != 8 || U.group != 8 || D.group != 8 || G.k != hidden || U.k != hidden || D.k != out_pe || G.n != n_expert * out_pe || U.n != G.n || D.n != n_expert * hidden || G.fmt != U.fmt ||
+        out_pe % 8 || hidden % 8)
+        return 1;
+    for (size_t p = 0; p < seq * top_k; ++p)
+        if (selected[p] < 0 || (size_t)selected[p] >= n_expert) return 1;
+    std::vector<float> pair_out(seq * top_k * hidden);
+#pragma omp parallel num_threads(workers())
+    {
+        std::vector<float> gate_v(out_pe), up_v(out_pe), g(out_pe);
+#pragma omp for schedule(dynamic, 1)
+        for (long long p = 0; p < (long long)(seq * top_k); ++p) {
+            const size_t t = (size_t)p / top_k;
+            const size_t e = (size_t)selected[p];
+            size_t s_in = 0, s_g = 0;
+            std::vector<uint8_t> qx = quantize_acts(G.fmt, x + t * hidden, 1, hidden, &s_in);
+            for (size_t j = 0; j < out_pe; j += 8) {
+                group_dot_x8(G, (e * out_pe + j) / 8, (const BlockQ8_K*)qx.data(), gate_v.data() + j);
+                group_dot_x8(U, (e * out_pe + j) / 8, (const BlockQ8_K*)qx.data(), up_v.data() + j);
+            }
+            for (size_t j = 0; j < out_pe; ++j) g[j] = swiglu_pair(gate_v[j], up_v[j]);
+            std::vector<uint8_t> qg = quantize_acts(D.fmt, g.data(), 1, out_pe, &s_g);
+            float* po = pair_out.data() + (size_t)p * hidden;
+            for (size_t j = 0; j < hidden; j += 8) group_dot_x8(D, (e * hidden + j) / 8, (const BlockQ8_K*)qg.data(), po + j);
         }
     }
     for (size_t t = 0; t < seq; ++t)

@@ -295,3 +295,90 @@ def test_gated_pairs_follow_the_reference_formulas():
         # g differs from the f32 evaluation by rounding only; the requantisation may move single int8 steps
         assert np.abs(got - want).max() <= 2e-2 * np.abs(want).max(), op
     assert np.abs(gv).max() > 10 or np.abs(uv).max() > 10  # the clamps were exercised
+
+
+def test_packed_x8_arm_equals_the_scalar_oracle():
+    """The reference's eight-row packs (BlockQ4_Kx8 / BlockQ5_Kx8) restated in oracle/cpu_kernels.cpp: bit-equal to
+    the compact kernels, as the reference's own tests require of its packs (src/backend/quant/q4_k_tests.zig:852-896,
+    q5_k_tests.zig:92-137), on every threading split; and the layout is the reference's (one block checked byte by
+    byte against the packing rule of q4_k.zig:127-192)."""
+    from parity import make_weights
+
+    if not oracle.has_simd(oracle.Q4_K):
+        pytest.skip("no AVX2 on this host")
+
+    def same(x, y):
+        return np.array_equal(x.view(np.uint32), y.view(np.uint32))
+
+    for name in ("q4_k", "q5_k"):
+        fmt = oracle.FORMATS[name]
+        for n, k, m in ((64, 512, 1), (328, 2304, 5), (1000, 4096, 1), (96, 768, 70)):
+            w = make_weights(name, n, k, seed=n + 1)
+            a = np.random.default_rng(k + 1).standard_normal((m, k)).astype(np.float32)
+            a[0, :8] = (1e4, -1e4, 0, 127.5, -127.5, 1e-30, 3.0, -3.0)
+            want = oracle.matmul(fmt, w, a)
+            pk = oracle.PackedRows.pack(fmt, w, k)
+            assert pk is not None
+            for t in (1, 3, 0):
+                oracle.set_threads(t)
+                assert same(want, pk.matmul(a)), (name, n, k, m, t)
+            pk.free()
+    oracle.set_threads(0)
+    # no pack for other formats or for a row count that does not fill the groups
+    assert oracle.PackedRows.pack(oracle.TQ2_0, make_weights("tq2_0", 64, 256, 1), 256) is None
+    assert oracle.PackedRows.pack(oracle.Q4_K, make_weights("q4_k", 12, 256, 1), 256) is None
+    assert oracle.PackedRows.pack(oracle.Q8_0, make_weights("q8_0", 6, 256, 1), 256) is None
+    # sizes of the packed blocks: 8 x (d, dmin) + 64 scales + 64 mins + payload
+    pk = oracle.PackedRows.pack(oracle.Q4_K, make_weights("q4_k", 8, 256, 2), 256)
+    assert pk.nbytes == 16 + 16 + 64 + 64 + 1024
+    pk = oracle.PackedRows.pack(oracle.Q5_K, make_weights("q5_k", 8, 256, 2), 256)
+    assert pk.nbytes == 16 + 16 + 64 + 64 + 2048
+
+
+def test_packed_x8_moe_baseline_equals_the_scalar_oracle():
+    from parity import make_weights
+
+    if not oracle.has_simd(oracle.Q5_K):
+        pytest.skip("no AVX2 on this host")
+    hidden, out_pe, n_expert, top_k, seq = 512, 256, 6, 3, 7
+    rng = np.random.default_rng(77)
+    gate = make_weights("q5_k", n_expert * out_pe, hidden, 71)
+    up = make_weights("q5_k", n_expert * out_pe, hidden, 72)
+    down = make_weights("q5_k", n_expert * hidden, out_pe, 73)
+    x = rng.standard_normal((seq, hidden)).astype(np.float32)
+    sel, w = oracle.router_topk(rng.standard_normal((seq, n_expert)).astype(np.float32), top_k, True)
+    want = oracle.moe_ffn(oracle.Q5_K, gate, up, down, x, sel, w, n_expert, out_pe)
+    pg, pu, pd = (oracle.PackedRows.pack(oracle.Q5_K, b, kk) for b, kk in ((gate, hidden), (up, hidden), (down, out_pe)))
+    got = oracle.moe_ffn_packed(pg, pu, pd, x, sel, w, n_expert, out_pe)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_packed_q8_0x4_arm_follows_its_own_law():
+    """The four-row Q8_0 pack (BlockQ8_0x4) multiplies (f32(t) * d_a) * d_w per block (src/backend/quant/q8_0.zig:1591,
+    :1613, :1633), a different f32 association from the compact dot: bit-equal to that law restated in numpy, and
+    within f32 rounding of the compact kernels."""
+    from parity import make_weights
+
+    if not oracle.has_simd(oracle.Q8_0):
+        pytest.skip("no AVX2 on this host")
+    for n, k, m in ((64, 512, 1), (100, 4096, 3), (4096, 1024, 1)):
+        w = make_weights("q8_0", n, k, seed=n + 2)
+        a = np.random.default_rng(k + 2).standard_normal((m, k)).astype(np.float32)
+        pk = oracle.PackedRows.pack(oracle.Q8_0, w, k)
+        assert pk is not None and pk.nbytes == n // 4 * (k // 32) * 136
+        got = pk.matmul(a)
+        # the law, block by block in f32
+        wb = w.reshape(n, k // 32, 34)
+        dw = wb[:, :, :2].copy().view(np.float16).astype(np.float32)[..., 0]          # [n, blocks]
+        wq = wb[:, :, 2:].view(np.int8).astype(np.int32)                              # [n, blocks, 32]
+        ab = oracle.quantize_acts_q8_0(a).reshape(m, k // 32, 34)
+        da = ab[:, :, :2].copy().view(np.float16).astype(np.float32)[..., 0]
+        aq = ab[:, :, 2:].view(np.int8).astype(np.int32)
+        want = np.zeros((m, n), np.float32)
+        for b in range(k // 32):
+            t = (aq[:, b, :] @ wq[:, b, :].T).astype(np.float32)                     # exact in f32 (|t| < 2^24)
+            want = want + (t * da[:, b][:, None]) * dw[:, b][None, :]
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (n, k, m)
+        compact = oracle.matmul(oracle.Q8_0, w, a)
+        assert np.max(np.abs(got - compact)) <= 1e-5 * np.max(np.abs(compact))
+        pk.free()
