@@ -76,14 +76,16 @@ struct Config {
     // Work floors (m * n * k) below which the host should keep a product on the CPU. The reference's defaults
     // (backend/cuda.zig:118-159) are the crossovers of an RTX 5000 Ada laptop GPU against its CPU arms; these are the
     // crossovers measured on B200: the blocking host-buffer call (about 25 us at decode sizes, resident weights)
-    // against the all-core SIMD CPU arm, rounded up to the next power of two with a factor of two to spare.
+    // against the all-core CPU arm on the reference's packed row layouts (x8 K-quants, x4 Q8_0), its fastest. One
+    // activation row: the CPU wins up to n * k = 2^21 (17 against 25 us), ties at 2^22, loses from 2^23; four rows:
+    // the GPU wins from m * n * k = 2^22 (31 against 34 us); 64 rows: everywhere measured.
     uint64_t min_work_qmoe = 1ull << 24;        // grouped MoE GEMM over staged panels (reference 2^30)
     uint64_t min_work_dense = 1ull << 22;       // prefill-sized dense products against the plain CPU arm (reference 2^30 via the QMoE floor)
     uint64_t min_work_packed_q4 = 1ull << 22;   // ... against the packed (x8) CPU arms (reference 2^27)
     uint64_t min_work_packed_q5 = 1ull << 22;   // (reference 2^24)
     uint64_t min_work_packed_q8 = 1ull << 22;   // (reference 2^24)
-    uint64_t min_work_decode = 1ull << 20;      // decode products, every format (the reference has no floor except for Q5_K)
-    uint64_t min_work_decode_q5 = 1ull << 20;   // (reference 3 * 2^23)
+    uint64_t min_work_decode = 1ull << 22;      // decode products, every format (the reference has no floor except for Q5_K)
+    uint64_t min_work_decode_q5 = 1ull << 22;   // (reference 3 * 2^23)
     uint64_t qmoe_min_fill_pct = 50;
     size_t vram_budget_env = 0;
 };

@@ -79,11 +79,13 @@ def test_gates_keep_the_reference_predicates_with_b200_floors(lib):
     assert lib.fq_qmoe_fill_acceptable(16, 1) == 1
     assert lib.fq_qmoe_fill_acceptable(15, 1) == 0
     assert lib.fq_qmoe_fill_acceptable(10, 0) == 0
-    # decode gate: m*n*k >= 2^20 for every format (a 24 us call does not pay for less)
-    assert lib.fq_should_use_gpu_quant_decode(F.Q4_K, 1, 1024, 1024) == 1
+    # decode gate: m*n*k >= 2^22 for every format (a 25 us call does not pay for less against the packed CPU arms)
+    assert lib.fq_should_use_gpu_quant_decode(F.Q4_K, 1, 2048, 2048) == 1
+    assert lib.fq_should_use_gpu_quant_decode(F.Q4_K, 1, 1024, 2048) == 0
     assert lib.fq_should_use_gpu_quant_decode(F.Q4_K, 1, 64, 256) == 0
-    assert lib.fq_should_use_gpu_quant_decode(F.Q5_K, 1, 512, 1024) == 0
-    assert lib.fq_should_use_gpu_quant_decode(F.Q5_K, 4, 512, 512) == 1
+    assert lib.fq_should_use_gpu_quant_decode(F.Q5_K, 1, 1024, 1024) == 0
+    assert lib.fq_should_use_gpu_quant_decode(F.Q5_K, 4, 1024, 1024) == 1
+    assert lib.fq_should_use_gpu_quant_decode(F.Q8_0, 1, 4096, 1024) == 1
     lib.fq_set_decode_for_test(0)
     assert lib.fq_should_use_gpu_quant_decode(F.Q4_K, 1, 4096, 4096) == 0
     lib.fq_set_decode_for_test(1)
