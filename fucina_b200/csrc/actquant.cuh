@@ -134,8 +134,11 @@ __device__ __forceinline__ void load_block_pre(const PreArgs& P, const float* ro
 
 // Quantise 256 activations (block `blk` of a row), given as the 8 values of each lane, into a natural record.
 // Call with a full warp. `k` must be a multiple of 256.
-__device__ __forceinline__ void quantize_values_natural(const float v[8], int blk, bool q8k, size_t k, uint8_t* rec, int lane) {
-    const NatSizes S = nat_sizes(q8k, k);
+// `q8k`: 0 = Q8_0 records; 1 = Q8_K records with eight int32 sums of 32 elements per block (the K-quants' sub-blocks);
+// 2 = Q8_K records with the sixteen int16 sums of 16 elements per block in the same 32 bytes (Q8_K's own bsums,
+// dtype.zig:148-152: Q6_K has a scale per 16 elements).
+__device__ __forceinline__ void quantize_values_natural(const float v[8], int blk, int q8k, size_t k, uint8_t* rec, int lane) {
+    const NatSizes S = nat_sizes(q8k != 0, k);
     int q[8];
     uint2 packed;
     if (q8k) {
@@ -145,8 +148,12 @@ __device__ __forceinline__ void quantize_values_natural(const float v[8], int bl
 #pragma unroll
         for (int j = 0; j < 8; ++j) sum += q[j];
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if ((lane & 3) == 0) reinterpret_cast<int32_t*>(rec + S.aq)[blk * 8 + (lane >> 2)] = sum;
+        if (q8k == 2) {
+            if ((lane & 1) == 0) reinterpret_cast<int16_t*>(rec + S.aq)[blk * 16 + (lane >> 1)] = (int16_t)sum;
+        } else {
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if ((lane & 3) == 0) reinterpret_cast<int32_t*>(rec + S.aq)[blk * 8 + (lane >> 2)] = sum;
+        }
     } else {
         const uint16_t dh = q8_0_quarter(v, q);
         if ((lane & 3) == 0) reinterpret_cast<float*>(rec + S.aq)[blk * 8 + (lane >> 2)] = h2f(dh);
@@ -155,7 +162,7 @@ __device__ __forceinline__ void quantize_values_natural(const float v[8], int bl
     packed.y = pack4(q + 4);
     *reinterpret_cast<uint2*>(rec + (size_t)blk * 256 + lane * 8) = packed;
 }
-__device__ __forceinline__ void quantize_block_natural(const float* __restrict__ src_row, int blk, bool q8k, size_t k,
+__device__ __forceinline__ void quantize_block_natural(const float* __restrict__ src_row, int blk, int q8k, size_t k,
                                                        uint8_t* rec, int lane) {
     float v[8];
     load8(src_row + (size_t)blk * 256 + lane * 8, v);

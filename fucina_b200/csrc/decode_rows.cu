@@ -267,6 +267,67 @@ __device__ __forceinline__ void block_q5_k(uint32_t p, const ActView& V, int kb,
     }
 }
 
+// ---- Q6_K: the 208 payload bytes of this lane's row at p (ql[128] | qh[64] | scales[16]); the block's f16 scale
+// travels in a plane of its own and arrives as `dw`. Element 128 c + 32 s + l takes its low four bits from
+// ql[64 c + 32 (s & 1) + l] (low nibble for sections 0-1, high for 2-3) and two more from bits 2s, 2s+1 of qh[32 c + l];
+// levels carry an offset of 32 and every 16 elements have a signed scale (q6_k.zig:1239-1259). The integer total and
+// the epilogue f32(total) * (d_w * d_a) are those of dotQ6_KQ8_K (q6_k.zig:617-631).
+template <int MB>
+__device__ __forceinline__ void block_q6_k(uint32_t p, float dw, const ActView& V, int kb, float (&acc)[MB]) {
+    const uint4 scv = lds128(p + 192);
+    const uint32_t scw[4] = {scv.x, scv.y, scv.z, scv.w};
+    // sum over the 16 groups of scale * (dot of the unsigned levels 0..63) - 32 * scale * (sum of the group's activations):
+    // the second part needs the record's sixteen int16 group sums and no re-centring of the levels
+    int isum[MB];
+#pragma unroll
+    for (int b = 0; b < MB; ++b) {
+        const uint32_t sums = V.base + b * V.row + V.off_sums + kb * 32;
+        const uint4 s0 = lds128(sums), s1 = lds128(sums + 16);
+        const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};  // groups 2j | 2j + 1 as int16 pairs
+        int corr = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            // scales 2j and 2j + 1 are bytes (2j) & 3 and (2j + 1) & 3 of word j / 2
+            const uint32_t two = scw[j >> 1] >> ((j & 1) * 16);
+            corr = __dp2a_lo((int)sw[j], (int)two, corr);  // int16 x int8 pairs
+        }
+        isum[b] = -32 * corr;
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const uint4 la = lds128(p + 64 * c), lb = lds128(p + 64 * c + 16), lc = lds128(p + 64 * c + 32), ld = lds128(p + 64 * c + 48);
+        const uint4 ha = lds128(p + 128 + 32 * c), hb = lds128(p + 128 + 32 * c + 16);
+        const uint32_t wl0[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+        const uint32_t wl1[8] = {lc.x, lc.y, lc.z, lc.w, ld.x, ld.y, ld.z, ld.w};
+        const uint32_t wh[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+        uint32_t q[4][8];  // [section][word of four consecutive l]: levels 0..63
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            q[0][g] = (wl0[g] & 0x0f0f0f0fu) | ((wh[g] << 4) & 0x30303030u);
+            q[1][g] = (wl1[g] & 0x0f0f0f0fu) | ((wh[g] << 2) & 0x30303030u);
+            q[2][g] = ((wl0[g] >> 4) & 0x0f0f0f0fu) | (wh[g] & 0x30303030u);
+            q[3][g] = ((wl1[g] >> 4) & 0x0f0f0f0fu) | ((wh[g] >> 2) & 0x30303030u);
+        }
+#pragma unroll
+        for (int b = 0; b < MB; ++b) {
+            const uint32_t a = V.base + b * V.row + kb * 256 + c * 128;
+#pragma unroll
+            for (int sec = 0; sec < 4; ++sec)
+#pragma unroll
+                for (int is = 0; is < 2; ++is) {
+                    // scale of elements 128 c + 32 sec + 16 is ..: index 8 c + 2 sec + is
+                    const int sc = (int)(int8_t)(scw[2 * c + (sec >> 1)] >> (8 * ((sec & 1) * 2 + is)));
+                    isum[b] += sc * dot16_us(&q[sec][4 * is], lds128(a + 32 * sec + 16 * is), 0);
+                }
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < MB; ++b) {
+        const float da = lds_f32(V.base + b * V.row + V.off_ad + kb * 4);
+        acc[b] = __fadd_rn(acc[b], __fmul_rn((float)isum[b], __fmul_rn(dw, da)));
+    }
+}
+
 // ---- Q8_0: one unit = 8 blocks of 32 weights; payload at p, the unit's eight
 // f16 scales at ps. Per block f32(idot) * (d_a * d_w)  (q8_0.zig:1074-1089).
 template <int MB>
@@ -480,7 +541,7 @@ struct SlabGeom {
 };
 __host__ __device__ inline SlabGeom slab_geom(int fmt, int slab) {
     SlabGeom g;
-    g.unit_bytes = fmt == FQ_Q4_K ? 144 : fmt == FQ_Q5_K ? 176 : 256;
+    g.unit_bytes = fmt == FQ_Q4_K ? 144 : fmt == FQ_Q5_K ? 176 : fmt == FQ_Q6_K ? 208 : 256;
     g.scale_bytes = fmt == FQ_Q8_0 ? 16 : 0;
     g.scale_off = slab * g.unit_bytes;
     int bytes = slab * (g.unit_bytes + g.scale_bytes);
@@ -507,6 +568,7 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
     const NatSizes NS = nat_sizes(Q8K, k);
     const SlabGeom G = slab_geom(FMT, A.slab);
     constexpr bool TQ = FMT == FQ_TQ2_0;
+    constexpr bool Q6 = FMT == FQ_Q6_K;  // payload units by tensor copy (one-unit slabs); the f16 block scales by plain loads
     const int units = TQ ? (k >> 9) : (k >> 8);              // pipeline units per row: 256 weights (TQ2_0: 512)
     const int nslabs = (units + A.slab - 1) / A.slab;        // slabs per row
     const int my_slabs = warp < nslabs ? (nslabs - warp + kWarps - 1) / kWarps : 0;
@@ -652,6 +714,25 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
     const int prefetch = min(A.stages, total);
     for (int it = 0; it < prefetch; ++it) issue(it);
 
+    // TQ2_0 and Q6_K keep their f16 block scales in a plane of their own behind the payload of a row; a lane reads the
+    // scale bits of its row for a pipeline step with a plain load. Requested at the top of the step that needs them,
+    // that load's whole DRAM latency is exposed once per step (profiled: 3.3 long-scoreboard stall cycles per issued instruction); so they
+    // are requested two steps ahead and travel through two registers.
+    auto plane_scales = [&](int step) -> uint32_t {
+        const int tile = step / my_slabs, sl = warp + kWarps * (step % my_slabs);
+        int row0, nvalid;
+        tile_rows(tile, row0, nvalid);
+        const uint8_t* row = wbase + (size_t)min(row0 + lane, n - 1) * A.w.row_stride;
+        if (TQ) return __ldg(reinterpret_cast<const uint32_t*>(row + (size_t)(k >> 2)) + sl);
+        return (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(row + (size_t)units * 208) + sl);
+    };
+    // the first two are requested here, with the first weight copies, ahead of the dependency wait (weights are immutable)
+    uint32_t ps0 = 0, ps1 = 0;
+    if (TQ || Q6) {
+        if (total > 0) ps0 = plane_scales(0);
+        if (total > 1) ps1 = plane_scales(1);
+    }
+
     // everything before this point read only immutable weights; activations and outputs may belong
     // to the preceding kernel
     stamp(1);
@@ -690,7 +771,7 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
             uint8_t* rec = acts + (size_t)b * NS.row;
             if (b < A.m) {
                 if (A.pre.op == FQ_PRE_NONE) {
-                    quantize_block_natural(A.a_f32 + (size_t)b * k, blk, Q8K, k, rec, lane);
+                    quantize_block_natural(A.a_f32 + (size_t)b * k, blk, FMT == FQ_Q6_K ? 2 : (Q8K ? 1 : 0), k, rec, lane);
                 } else {
                     float v[8];
                     float scale = 0.0f;
@@ -698,7 +779,7 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
                     for (int bb = 0; bb < MB; ++bb)
                         if (bb == b) scale = pre_scale[bb];
                     load_block_pre(A.pre, A.a_f32 + (size_t)b * a_stride, (size_t)k, blk, lane, scale, v);
-                    quantize_values_natural(v, blk, Q8K, k, rec, lane);
+                    quantize_values_natural(v, blk, FMT == FQ_Q6_K ? 2 : (Q8K ? 1 : 0), k, rec, lane);
                 }
             } else {  // padded batch slots contribute zeros
                 *reinterpret_cast<uint2*>(rec + (size_t)blk * 256 + lane * 8) = make_uint2(0, 0);
@@ -729,7 +810,7 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
     for (int tile = 0; tile < ntiles; ++tile) {
         // K-quant batches of 3..16 rows (MB = 8 or 16) multiply through the warp-level tensor-core instruction:
         // acc then holds the fragment layout of expert_block_mma, eight values per group of eight rows
-        constexpr bool kMma = FMT != FQ_Q8_0 && !TQ && MB >= 8;
+        constexpr bool kMma = (FMT == FQ_Q4_K || FMT == FQ_Q5_K) && MB >= 8;
         float acc[MB];
 #pragma unroll
         for (int b = 0; b < MB; ++b) acc[b] = 0.0f;
@@ -737,12 +818,14 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
             const int sl = warp + kWarps * j;
             const int stage = it % A.stages;
             const uint32_t parity = (uint32_t)(it / A.stages) & 1u;
-            uint32_t tq_scales = 0;  // TQ2_0: the two f16 scales of this lane's row for this step, fetched while the box is in flight
-            if (TQ) {
-                int row0, nvalid;
-                tile_rows(tile, row0, nvalid);
-                tq_scales = __ldg(reinterpret_cast<const uint32_t*>(wbase + (size_t)min(row0 + lane, n - 1) * A.w.row_stride + (size_t)(k >> 2)) + sl);
+            // TQ2_0 / Q6_K: this lane's scale bits for this step were requested two steps ago (see plane_scales)
+            const uint32_t step_scales = ps0;
+            if (TQ || Q6) {
+                ps0 = ps1;
+                ps1 = it + 2 < total ? plane_scales(it + 2) : 0u;
             }
+            const uint32_t tq_scales = step_scales;
+            const float q6_dw = Q6 ? h2f((uint16_t)step_scales) : 0.0f;
             if (!mbar_wait(bar0 + stage * 8, parity)) {
                 ok = false;
                 break;
@@ -764,6 +847,8 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && MB < 8) ? 2 : 1) de
                     block_q4_k<MB>(p + u * 144, V, kb, acc);
                 } else if (FMT == FQ_Q5_K) {
                     block_q5_k<MB>(p + u * 176, V, kb, acc);
+                } else if (Q6) {
+                    block_q6_k<MB>(p, q6_dw, V, kb, acc);
                 }
                 if (FMT == FQ_Q8_0) {
                     if (q8_boxes) unit_q8_0_swz<MB>(p, lane, V, kb, acc);
@@ -829,7 +914,7 @@ int pick_warps(int fmt, int k, int mb) {
     static const int forced = getenv("FUCINA_B200_DECODE_WARPS") ? atoi(getenv("FUCINA_B200_DECODE_WARPS")) : 0;
     if (forced == 8) return 8;
     static const bool wide8 = getenv("FUCINA_B200_DECODE_WIDE8") ? atoi(getenv("FUCINA_B200_DECODE_WIDE8")) != 0 : true;
-    const bool wide_ok = mb <= 2 || (mb == 8 && fmt != FQ_Q8_0 && wide8);  // the eight-row tensor-core variant also fits 16 warps
+    const bool wide_ok = mb <= 2 || (mb == 8 && fmt != FQ_Q8_0 && fmt != FQ_Q6_K && wide8);  // the eight-row tensor-core variant also fits 16 warps
     if (k / 256 < 16 || !wide_ok) return 8;
     return smem_bytes(fmt, k, mb, 1, 2, 16) <= 227 * 1024 ? 16 : 8;  // the smallest 16-warp ring must fit
 }
@@ -839,7 +924,7 @@ int pad_rows(size_t m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
 // eight tokens; Q8_0 keeps dp4a up to eight rows.
 constexpr int kMaxDecodeRows = 16;
 int decode_pad_rows(int fmt, size_t m) {
-    if (fmt == FQ_Q8_0 || fmt == FQ_TQ2_0 || m <= 2) return pad_rows(m);
+    if (fmt == FQ_Q8_0 || fmt == FQ_TQ2_0 || fmt == FQ_Q6_K || m <= 2) return pad_rows(m);
     return m <= 8 ? 8 : 16;
 }
 
@@ -999,6 +1084,33 @@ cudaError_t launch_fmt(const RowsArgs& a, const CUtensorMap& tmap, const CUtenso
     }
 }
 
+
+// Q6_K has the dp4a block product only: batches of one, two, four and eight rows, 16 warps for the first two
+template <int MB>
+cudaError_t launch_q6_mb(const RowsArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap2, bool fused, int grid, size_t smem, cudaStream_t st) {
+    constexpr bool kWide = MB <= 2;
+    const bool wide = kWide && pick_warps(FQ_Q6_K, a.w.k, MB) == 16;
+    void (*kern)(const RowsArgs, const CUtensorMap, const CUtensorMap) =
+        wide ? (fused ? decode_rows_kernel<FQ_Q6_K, MB, true, kWide ? 16 : 8> : decode_rows_kernel<FQ_Q6_K, MB, false, kWide ? 16 : 8>)
+             : (fused ? decode_rows_kernel<FQ_Q6_K, MB, true, 8> : decode_rows_kernel<FQ_Q6_K, MB, false, 8>);
+    static bool granted[2][2] = {{false, false}, {false, false}};
+    if (!granted[wide][fused]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+        granted[wide][fused] = true;
+    }
+    return launch_pdl(kern, dim3((unsigned)grid), dim3(wide ? 512 : 256), smem, st, a, tmap, tmap2);
+}
+cudaError_t launch_fmt_q6(const RowsArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap2, int mb, bool fused, int grid, size_t smem, cudaStream_t st) {
+    switch (mb) {
+        case 1: return launch_q6_mb<1>(a, tmap, tmap2, fused, grid, smem, st);
+        case 2: return launch_q6_mb<2>(a, tmap, tmap2, fused, grid, smem, st);
+        case 4: return launch_q6_mb<4>(a, tmap, tmap2, fused, grid, smem, st);
+        default: return launch_q6_mb<8>(a, tmap, tmap2, fused, grid, smem, st);
+    }
+}
 
 // TQ2_0 has the dp4a block product only: batches of one, two and four rows
 cudaError_t launch_fmt_tq(const RowsArgs& a, const CUtensorMap& tmap, const CUtensorMap& tmap2, int mb, bool fused, int grid, size_t smem, cudaStream_t st) {
@@ -1305,6 +1417,13 @@ bool decode_rows_eligible(const DevWeights& w, size_t m) {
         const int mb = pad_rows(m);
         return smem_bytes_tq_boxes(w.k, mb, 2, tq_warps(w.k, mb)) <= kSmemLimit;
     }
+    if (w.fmt == FQ_Q6_K) {
+        // split rows [payload | f16 scales], row-major; the payload is fetched by tensor copies (base and row stride rules)
+        static const bool off = getenv("FUCINA_B200_NO_Q6_DECODE") != nullptr;
+        if (off || m < 1 || m > 8 || w.k % 256 != 0 || w.k < 2048 || w.n < 64 || w.tile_rows || !encode_tiled_fn()) return false;
+        if (((uintptr_t)w.base & 15) || (w.row_stride & 15) || (w.mat_stride & 15)) return false;
+        return smem_bytes(w.fmt, w.k, pad_rows(m), 1, 2, pick_warps(w.fmt, w.k, pad_rows(m))) <= kSmemLimit;
+    }
     if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q8_0) return false;
     if (m < 1 || m > (size_t)(w.fmt == FQ_Q8_0 ? 8 : kMaxDecodeRows) || w.k % 256 != 0 || w.k < 2048 || w.n < 64) return false;
     int slab, stages;
@@ -1337,6 +1456,24 @@ cudaError_t launch_decode_rows(const DevWeights& w, int mat, const float* a_dev,
         int grid_tq = sm_count;
         if (grid_tq > (w.n + 31) / 32) grid_tq = (w.n + 31) / 32;
         return launch_fmt_tq(a, tm, tm2, mb, true, grid_tq, smem_bytes_tq_boxes(w.k, mb, a.stages, warps), st);
+    }
+    if (w.fmt == FQ_Q6_K) {
+        CUtensorMap tm, tm2;
+        memset(&tm2, 0, sizeof tm2);
+        if (!make_weight_tmap(w, mat, 208, &tm)) return cudaErrorInvalidValue;
+        const int warps = pick_warps(w.fmt, w.k, mb);
+        a.slab = 1;
+        a.use_tmap = 1;
+        a.stages = 2;
+        while (a.stages < kMaxStages && smem_bytes(w.fmt, w.k, mb, 1, a.stages + 1, warps) <= kSmemLimit) ++a.stages;
+        const bool fused_q6 = m <= kFusedMaxRows;
+        if (!fused_q6) {
+            cudaError_t e = launch_quantize_acts_natural(a_dev, m, w.k, 2, scratch, st);
+            if (e != cudaSuccess) return e;
+        }
+        int grid_q6 = sm_count;
+        if (grid_q6 > (w.n + 31) / 32) grid_q6 = (w.n + 31) / 32;
+        return launch_fmt_q6(a, tm, tm2, mb, fused_q6, grid_q6, smem_bytes(w.fmt, w.k, mb, 1, a.stages, warps), st);
     }
     if (!pick_config(w.fmt, w.k, mb, &a.slab, &a.stages)) return cudaErrorInvalidValue;
     // K-quant units are an odd number of 16-byte chunks: one tensor copy per warp step instead of 32

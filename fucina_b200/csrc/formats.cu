@@ -350,14 +350,15 @@ __global__ void quantize_acts_natural_kernel(const float* __restrict__ a, int m,
     if (warp >= (size_t)m * blocks_per_row) return;
     const int row = (int)(warp / blocks_per_row), blk = (int)(warp % blocks_per_row);
     const NatSizes S = nat_sizes(q8k != 0, k);
-    quantize_block_natural(a + (size_t)row * k, blk, q8k != 0, k, out + (size_t)row * S.row, lane);
+    quantize_block_natural(a + (size_t)row * k, blk, q8k, k, out + (size_t)row * S.row, lane);
 }
 
-cudaError_t launch_quantize_acts_natural(const float* a, int m, int k, bool q8k, uint8_t* out, cudaStream_t st) {
+// `q8k`: 0, 1 or 2 as in quantize_values_natural
+cudaError_t launch_quantize_acts_natural(const float* a, int m, int k, int q8k, uint8_t* out, cudaStream_t st) {
     const size_t warps = (size_t)m * (k / 256);
     const int threads = 128;
     const size_t blocks = (warps * 32 + threads - 1) / threads;
-    quantize_acts_natural_kernel<<<(unsigned)blocks, threads, 0, st>>>(a, m, k, q8k ? 1 : 0, out);
+    quantize_acts_natural_kernel<<<(unsigned)blocks, threads, 0, st>>>(a, m, k, q8k, out);
     return cudaGetLastError();
 }
 

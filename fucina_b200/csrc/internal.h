@@ -77,7 +77,7 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 }
 
 // formats.cu -- natural-order activation records (actquant.cuh)
-cudaError_t launch_quantize_acts_natural(const float* a, int m, int k, bool q8k, uint8_t* out, cudaStream_t st);
+cudaError_t launch_quantize_acts_natural(const float* a, int m, int k, int q8k, uint8_t* out, cudaStream_t st);
 
 // decode_rows.cu -- row-per-lane decode kernel with TMA-staged weights.
 struct RowsArgs {

@@ -41,7 +41,7 @@ extern "C" {
  * providers' enums (backend/metal.zig:1275-1280 reuses 3 and 4). */
 typedef enum {
     FQ_Q8_0 = 0,
-    FQ_Q6_K = 1, /* 256 per block, 210 bytes (src/dtype.zig:141-146); integer and tensor kernels, no copy-engine decode kernel */
+    FQ_Q6_K = 1, /* 256 per block, 210 bytes (src/dtype.zig:141-146); streaming decode (m <= 8, k >= 2048), integer and tensor kernels */
     FQ_Q4_K = 2,
     FQ_Q5_K = 3,
     FQ_TQ2_0 = 16,        /* dtype.zig:215-218, one PTQTP plane */

@@ -171,7 +171,7 @@ def test_full_size_decode_against_oracle(P, torch):
     assert_close(got, oracle.matmul(oracle.Q8_0, blocks, a), TOL_INT8, "q8gemv shape")
 
 
-@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q8_0"])
+@pytest.mark.parametrize("fmt_name", ["q4_k", "q5_k", "q6_k", "q8_0"])
 @pytest.mark.parametrize("n,k", [(64, 2048), (100, 2304), (333, 4096), (1000, 11008), (4096, 4096)])
 def test_dense_decode_kernel_shapes(P, torch, fmt_name, n, k):
     # shapes the TMA-staged row-per-lane kernel takes: ragged row tiles (n not a
