@@ -1139,31 +1139,33 @@ constexpr int kExpertWarps = 8;
 
 // One block of one row against the first M activation records, accumulators acc[0..M).
 template <int FMT, int M>
-__device__ __forceinline__ void expert_block(uint32_t p, const ActView& V, int unit, float* acc) {
+__device__ __forceinline__ void expert_block(uint32_t p, const ActView& V, int unit, float* acc, float dw) {
     float(&a)[M] = *reinterpret_cast<float(*)[M]>(acc);
     if (FMT == FQ_Q4_K) block_q4_k<M>(p, V, unit, a);
     if (FMT == FQ_Q5_K) block_q5_k<M>(p, V, unit, a);
+    if (FMT == FQ_Q6_K) block_q6_k<M>(p, dw, V, unit, a);  // `dw`: the block's f16 scale from the plane behind the row's payload
 }
 // Entries mostly hold fewer rows than the launch-wide bound MB (a token batch spreads over many
 // experts), so the block product is instantiated for 1, 2, 4 and 8 rows and chosen per entry.
 __host__ __device__ inline int expert_rows_step(int m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
 template <int FMT, int MB>
-__device__ __forceinline__ void expert_block_m(int mstep, uint32_t p, const ActView& V, int unit, float* acc) {
-    if (MB >= 8 && mstep == 8) return expert_block<FMT, MB >= 8 ? 8 : MB>(p, V, unit, acc);
-    if (MB >= 4 && mstep == 4) return expert_block<FMT, MB >= 4 ? 4 : MB>(p, V, unit, acc);
-    if (MB >= 2 && mstep == 2) return expert_block<FMT, MB >= 2 ? 2 : MB>(p, V, unit, acc);
-    expert_block<FMT, 1>(p, V, unit, acc);
+__device__ __forceinline__ void expert_block_m(int mstep, uint32_t p, const ActView& V, int unit, float* acc, float dw) {
+    if (MB >= 8 && mstep == 8) return expert_block<FMT, MB >= 8 ? 8 : MB>(p, V, unit, acc, dw);
+    if (MB >= 4 && mstep == 4) return expert_block<FMT, MB >= 4 ? 4 : MB>(p, V, unit, acc, dw);
+    if (MB >= 2 && mstep == 2) return expert_block<FMT, MB >= 2 ? 2 : MB>(p, V, unit, acc, dw);
+    expert_block<FMT, 1>(p, V, unit, acc, dw);
 }
 
 template <int FMT, int MB, bool GATED>
-__global__ void __launch_bounds__(kExpertWarps * 32, MB == 8 ? 2 : 1)  // eight-row tables: two CTAs per SM (128 registers, no spills)
+__global__ void __launch_bounds__(kExpertWarps * 32, (MB == 8 && FMT != FQ_Q6_K) ? 2 : 1)  // eight-row tables: two CTAs per SM (128 registers, no spills)
     expert_rows_kernel(const ExpertArgs A, const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap2) {
     extern __shared__ __align__(128) uint8_t smem[];
     // The table, its length, the pair list and the activation rows come from the kernels before this one: nothing
     // global is read before the predecessor has completed (the launch itself overlaps its tail).
     pdl_wait_then_release();
     constexpr int NM = GATED ? 2 : 1;
-    constexpr int UB = FMT == FQ_Q4_K ? 144 : 176;
+    constexpr int UB = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 208;  // Q6_K: the payload of a unit; its f16 scale by a plain load
+    constexpr bool Q6 = FMT == FQ_Q6_K;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int k = A.w.k, n = A.w.n;
     const int mat_rows = A.w.n_mats > 1 ? (int)(A.w.mat_stride / A.w.row_stride) : n;
@@ -1230,6 +1232,17 @@ __global__ void __launch_bounds__(kExpertWarps * 32, MB == 8 ? 2 : 1)  // eight-
 
     const ActView V = {smem_u32(acts), (uint32_t)NS.row, (uint32_t)NS.aq, (uint32_t)(NS.aq + NS.sums)};
     bool ok = true;  // per warp; a warp that gave up still walks through every CTA barrier below
+    // Q6_K: scale bits of this lane's row (its matrix by j % NM) for step j of item il, from the plane behind the payload
+    auto plane_scale = [&](int il, int j) -> uint32_t {
+        int d, tile;
+        item_of(il, d, tile);
+        const DevWeights& W = (GATED && (j % NM)) ? A.w2 : A.w;
+        const int row = A.table[d].mat * mat_rows + min(tile * 32 + lane, n - 1);
+        const int unit = kpart + ksplit * (j / NM);
+        return (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(W.base + (size_t)row * W.row_stride + (size_t)units * 208) + unit);
+    };
+    uint32_t q6_next = 0;
+    int q6_for = -1;  // the step q6_next was requested for
     for (int il = 0; il < my_items; ++il) {
         int d, tile;
         item_of(il, d, tile);
@@ -1239,7 +1252,7 @@ __global__ void __launch_bounds__(kExpertWarps * 32, MB == 8 ? 2 : 1)  // eight-
         // block product is instantiated for are zero
         const int nblk = k >> 8;
         // entries of three or more rows in an eight-row launch use the tensor-core block product (CTA-uniform choice)
-        const bool kMma = MB == 8 && G.m > 2;
+        const bool kMma = !Q6 && MB == 8 && G.m > 2;
         const int mstep = kMma ? MB : min(MB, expert_rows_step(G.m));
         for (int i = warp; i < mstep * nblk; i += kExpertWarps) {
             const int b = i / nblk, blk = i % nblk;
@@ -1247,7 +1260,7 @@ __global__ void __launch_bounds__(kExpertWarps * 32, MB == 8 ? 2 : 1)  // eight-
             if (b < G.m) {
                 const int pos = G.row0 + b;
                 const size_t src_row = A.src_index ? (size_t)(A.src_index[pos] / A.top_k) : (size_t)pos;
-                quantize_block_natural(A.src + src_row * k, blk, true, k, rec, lane);
+                quantize_block_natural(A.src + src_row * k, blk, Q6 ? 2 : 1, k, rec, lane);
             } else {
                 *reinterpret_cast<uint2*>(rec + (size_t)blk * 256 + lane * 8) = make_uint2(0, 0);
                 if (lane < 8) reinterpret_cast<int32_t*>(rec + NS.aq)[blk * 8 + lane] = 0;
@@ -1266,6 +1279,17 @@ __global__ void __launch_bounds__(kExpertWarps * 32, MB == 8 ? 2 : 1)  // eight-
             for (int j = 0; j < spi; ++j) {
                 if (!ok) break;
                 const int unit = kpart + ksplit * (j / NM), stage = consumed % A.stages;
+                // Q6_K: the f16 scale of this lane's row for this step, requested during the step before (or, for the
+                // first step of an item, here); the next step's request goes out before this step's wait
+                float dw = 0.0f;
+                if (Q6) {
+                    const uint32_t bits = (q6_for == il * spi + j) ? q6_next : plane_scale(il, j);
+                    if (j + 1 < spi) {
+                        q6_next = plane_scale(il, j + 1);
+                        q6_for = il * spi + j + 1;
+                    }
+                    dw = h2f((uint16_t)bits);
+                }
                 if (!mbar_wait(bar0 + stage * 8, (uint32_t)(consumed / A.stages) & 1u)) {
                     ok = false;
                     break;
@@ -1274,13 +1298,13 @@ __global__ void __launch_bounds__(kExpertWarps * 32, MB == 8 ? 2 : 1)  // eight-
                 const uint32_t p = tile_base + (uint32_t)lane * UB;
                 if (kMma) {
                     if (!GATED || (j % NM) == 0)
-                        expert_block_mma<FMT>(tile_base, V, unit, lane, reinterpret_cast<float(&)[8]>(acc[0]));
+                        expert_block_mma<Q6 ? FQ_Q5_K : FMT>(tile_base, V, unit, lane, reinterpret_cast<float(&)[8]>(acc[0]));
                     else
-                        expert_block_mma<FMT>(tile_base, V, unit, lane, reinterpret_cast<float(&)[8]>(acc[NM - 1]));
+                        expert_block_mma<Q6 ? FQ_Q5_K : FMT>(tile_base, V, unit, lane, reinterpret_cast<float(&)[8]>(acc[NM - 1]));
                 } else if (!GATED || (j % NM) == 0) {
-                    expert_block_m<FMT, MB>(mstep, p, V, unit, acc[0]);
+                    expert_block_m<FMT, MB>(mstep, p, V, unit, acc[0], dw);
                 } else {
-                    expert_block_m<FMT, MB>(mstep, p, V, unit, acc[NM - 1]);
+                    expert_block_m<FMT, MB>(mstep, p, V, unit, acc[NM - 1], dw);
                 }
                 __syncwarp();  // every lane is done with this stage before it is refilled
                 ++consumed;
@@ -1341,7 +1365,7 @@ __global__ void __launch_bounds__(kExpertWarps * 32, MB == 8 ? 2 : 1)  // eight-
 
 size_t expert_smem_bytes(int fmt, int k, int mb, int nm, int stages, bool k_split = true) {
     const NatSizes NS = nat_sizes(true, (size_t)k);
-    const int ub = fmt == FQ_Q4_K ? 144 : 176;
+    const int ub = fmt == FQ_Q4_K ? 144 : fmt == FQ_Q5_K ? 176 : 208;
     return 512 + ((mb * NS.row + 127) & ~(size_t)127) + (k_split ? (size_t)kExpertWarps * nm * mb * 32 * sizeof(float) : 0) +
            (size_t)kExpertWarps * stages * 32 * ub;
 }
@@ -1539,7 +1563,7 @@ extern "C" __attribute__((visibility("default"))) int fq_debug_timeline(unsigned
 int expert_rows_max_group() { return 8; }
 
 bool expert_rows_eligible(const DevWeights& w, const DevWeights* w2, int group_rows) {
-    if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K) return false;
+    if (w.fmt != FQ_Q4_K && w.fmt != FQ_Q5_K && w.fmt != FQ_Q6_K) return false;
     if (w.tile_rows || w.k % 256 != 0 || w.k < 256 || group_rows < 1 || group_rows > 8) return false;
     if (w.n_mats > 1 && (w.mat_stride % w.row_stride != 0 || w.mat_stride < (size_t)w.n * w.row_stride)) return false;
     if (((uintptr_t)w.base & 15) || (w.row_stride & 15)) return false;  // tensor-map base and stride rules
@@ -1555,7 +1579,7 @@ cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const 
                                const GroupDesc* table, const int* n_desc, int max_desc, int group_rows, int sm_count, int* status,
                                cudaStream_t st, int gated_op) {
     const int mb = pad_rows((size_t)group_rows), nm = w2 ? 2 : 1;
-    const int ub = w.fmt == FQ_Q4_K ? 144 : 176;
+    const int ub = w.fmt == FQ_Q4_K ? 144 : w.fmt == FQ_Q5_K ? 176 : 208;
     int stages = kMaxStages;
     // tiles per item: whole tiles per warp when the table is long enough to fill the SMs, K split across
     // warps when it is short (a single token names top_k experts only)
@@ -1580,7 +1604,7 @@ cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const 
     // eight-row tables run the warp-level tensor-core block product, which eight warps per SM leave latency-bound
     // (two warps per scheduler, issue slots half empty): two CTAs per SM with two-stage rings
     static const bool no_pair = getenv("FUCINA_B200_EXPERT_ONE_CTA") != nullptr;
-    if (!no_pair && mb == 8 && items > sm_count && expert_smem_bytes(w.fmt, w.k, mb, nm, 2, k_split) <= 113 * 1024) {
+    if (!no_pair && mb == 8 && w.fmt != FQ_Q6_K && items > sm_count && expert_smem_bytes(w.fmt, w.k, mb, nm, 2, k_split) <= 113 * 1024) {
         grid = (int)(items < 2LL * sm_count ? items : 2LL * sm_count);
         stages = 2;
     }
@@ -1588,6 +1612,8 @@ cudaError_t launch_expert_rows(const DevWeights& w, const DevWeights* w2, const 
     const size_t smem = expert_smem_bytes(w.fmt, w.k, mb, nm, stages, k_split);
     if (w.fmt == FQ_Q4_K)
         return w2 ? launch_expert_mb<FQ_Q4_K, true>(a, mb, t1, t2, grid, smem, st) : launch_expert_mb<FQ_Q4_K, false>(a, mb, t1, t2, grid, smem, st);
+    if (w.fmt == FQ_Q6_K)
+        return w2 ? launch_expert_mb<FQ_Q6_K, true>(a, mb, t1, t2, grid, smem, st) : launch_expert_mb<FQ_Q6_K, false>(a, mb, t1, t2, grid, smem, st);
     return w2 ? launch_expert_mb<FQ_Q5_K, true>(a, mb, t1, t2, grid, smem, st) : launch_expert_mb<FQ_Q5_K, false>(a, mb, t1, t2, grid, smem, st);
 }
 
