@@ -421,15 +421,17 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
     // normally no longer than the batch; runs are split at this size either way, so repeated experts in
     // one token only cost an extra table entry.
     // K-quant expert stacks stream through the row-per-lane kernel (runs of <= 8 rows, activations quantised
-    // inside the kernel); other formats take the lane-per-chunk kernel with pre-quantised rows
+    // inside the kernel); other formats take the lane-per-chunk kernel with pre-quantised rows. The choice is made per
+    // product: a layer with K-quant gate/up stacks and a Q8_0 down stack (Gemma) streams its gate/up product.
     const int stream_rows = seq < expert_rows_max_group() ? seq : expert_rows_max_group();
-    const bool streaming = expert_rows_eligible(gate, &up, stream_rows) && expert_rows_eligible(down, nullptr, stream_rows);
-    // the lane-per-chunk kernel keeps a group's (padded) rows in shared memory: cut the group until both products fit
-    int fit_rows = gemv_rows_that_fit(fmt, (size_t)hidden);
-    if (gemv_rows_that_fit(fmt_dn, (size_t)out_pe) < fit_rows) fit_rows = gemv_rows_that_fit(fmt_dn, (size_t)out_pe);
-    if (!streaming && fit_rows == 0) return fail(FQ_DECLINED_ARGS, "expert rows of %d / %d elements are too long for the integer arm", hidden, out_pe);
-    const int int8_rows = kGroupRows < fit_rows ? kGroupRows : fit_rows;
-    const int group_rows = streaming ? stream_rows : (seq < int8_rows ? seq : int8_rows);
+    const bool stream_gu = expert_rows_eligible(gate, &up, stream_rows), stream_dn = expert_rows_eligible(down, nullptr, stream_rows);
+    // rows per table entry: what every kernel that will run takes. The lane-per-chunk kernel keeps a group's (padded)
+    // rows in shared memory, so a product it serves cuts the group until they fit.
+    int rows_cap = (stream_gu || stream_dn) ? expert_rows_max_group() : kGroupRows;
+    if (!stream_gu && gemv_rows_that_fit(fmt, (size_t)hidden) < rows_cap) rows_cap = gemv_rows_that_fit(fmt, (size_t)hidden);
+    if (!stream_dn && gemv_rows_that_fit(fmt_dn, (size_t)out_pe) < rows_cap) rows_cap = gemv_rows_that_fit(fmt_dn, (size_t)out_pe);
+    if (rows_cap == 0) return fail(FQ_DECLINED_ARGS, "expert rows of %d / %d elements are too long for the integer arm", hidden, out_pe);
+    const int group_rows = seq < rows_cap ? seq : rows_cap;
     const int max_desc = max_desc_for(pairs, n_expert, group_rows);
     // one scratch block: order, inv, n_desc, table, quantised x rows, g rows, quantised g rows, down rows
     size_t off = 0;
@@ -461,30 +463,25 @@ int moe_layer_dev_impl(Ctx* ctx, const DevWeights& gate, const DevWeights& up, c
         if ((e = launch_pdl(route_plan_kernel, dim3(1), dim3(1024), sizeof(int) * 4 * n_expert, st, selected_dev, pairs, n_expert, shard, group_rows, order,
                             inv, table, n_desc, n_desc + 1, 0, 0, 0, (TcTile*)nullptr, (int*)nullptr, (TcTile*)nullptr, (int*)nullptr)) != cudaSuccess)
             break;
-        if (streaming) {
+        if (stream_gu) {
             if ((e = launch_expert_rows(gate, &up, x_dev, order, top_k, g, table, n_desc, max_desc, group_rows, ctx->sm_count, ctx->status_dev,
                                         st, gated_op)) != cudaSuccess)
                 break;
+        } else {
+            // gather each pair's token row and quantise it, in expert order
+            if ((e = launch_quantize_acts_layout(x_dev, order, top_k, pairs, hidden, fmt, qx, st)) != cudaSuccess) break;
+            GemvArgs ga{gate, up, 0, qx, g, group_rows, out_pe, 0, table, n_desc, max_desc, gated_op};
+            if ((e = launch_gemv(ga, ctx->sm_count, st)) != cudaSuccess) break;
+        }
+        if (stream_dn) {
             if ((e = launch_expert_rows(down, nullptr, g, nullptr, 1, down_rows, table, n_desc, max_desc, group_rows, ctx->sm_count,
                                         ctx->status_dev, st)) != cudaSuccess)
                 break;
-            const size_t total = (size_t)seq * hidden;
-            int blocks = (int)((total + 255) / 256);
-            if (blocks > 148 * 8) blocks = 148 * 8;
-            launch_combine(down_rows, weights_dev, inv, seq, hidden, top_k, out_dev, st);
-            e = cudaGetLastError();
-            break;
+        } else {
+            if ((e = launch_quantize_acts_layout(g, nullptr, 1, pairs, out_pe, fmt_dn, qg, st)) != cudaSuccess) break;
+            GemvArgs gd{down, DevWeights{}, 0, qg, down_rows, group_rows, hidden, 0, table, n_desc, max_desc};
+            if ((e = launch_gemv(gd, ctx->sm_count, st)) != cudaSuccess) break;
         }
-        // gather each pair's token row and quantise it, in expert order
-        if ((e = launch_quantize_acts_layout(x_dev, order, top_k, pairs, hidden, fmt, qx, st)) != cudaSuccess) break;
-        GemvArgs ga{gate, up, 0, qx, g, group_rows, out_pe, 0, table, n_desc, max_desc, gated_op};
-        if ((e = launch_gemv(ga, ctx->sm_count, st)) != cudaSuccess) break;
-        if ((e = launch_quantize_acts_layout(g, nullptr, 1, pairs, out_pe, fmt_dn, qg, st)) != cudaSuccess) break;
-        GemvArgs gd{down, DevWeights{}, 0, qg, down_rows, group_rows, hidden, 0, table, n_desc, max_desc};
-        if ((e = launch_gemv(gd, ctx->sm_count, st)) != cudaSuccess) break;
-        const size_t total = (size_t)seq * hidden;
-        int blocks = (int)((total + 255) / 256);
-        if (blocks > 148 * 8) blocks = 148 * 8;
         launch_combine(down_rows, weights_dev, inv, seq, hidden, top_k, out_dev, st);
         e = cudaGetLastError();
     } while (false);
