@@ -193,7 +193,7 @@ struct BlockQ8_0x4 {
 static_assert(sizeof(BlockQ8_0x4) == 136, "packed block size");
 
 struct PackedRows {
-    int fmt = 0, group = 8;  // rows interleaved per packed block: 8 (K-quants) or 4 (Q8_0)
+    int fmt = 0, group = 8;  // rows interleaved per packed block: 8 (K-quants) or 4 (Q8_0, TQ2_0)
     size_t n = 0, k = 0, blocks_per_row = 0;
     std::vector<uint8_t> data;  // [n / group][blocks_per_row] packed blocks
 };
@@ -291,6 +291,44 @@ __attribute__((target("avx2,f16c"))) inline void group_dot_q8_0x4(const PackedRo
     const BlockQ8_0x4* w = (const BlockQ8_0x4*)P.data.data() + group * P.blocks_per_row;
     __m128 acc = _mm_setzero_ps();
     for (size_t b = 0; b < P.blocks_per_row; ++b) acc = accumulate_q8_0x4(&w[b], &a[b], acc);
+    _mm_storeu_ps(out4, acc);
+}
+
+// TQ2_0: four rows interleaved per 256-weight block (BlockTQ2_0x4, types.zig:150-159, packed by ternary.zig:423-446):
+// qs byte half * 128 + fg * 16 + c * 4 + l = byte half * 32 + fg * 4 + l of column c; the four crumbs of a byte still
+// are elements +0 / +32 / +64 / +96 of its half. The kernel is the ymm form of ternary.zig:556-575: one 32-byte load =
+// two k-groups x four columns, the matching 8 activation bytes broadcast dword-wise, eight int32 lanes folded to the
+// four columns once per block; then sums[c] += (d_c * d_a) * f32(dot_c - bsum), bit-equal to the compact kernel.
+struct BlockTQ2_0x4 {
+    uint16_t d[4];
+    uint8_t qs[256];
+};
+static_assert(sizeof(BlockTQ2_0x4) == 264, "packed block size");
+
+__attribute__((target("avx2,f16c"))) inline __m128 accumulate_tq2_0x4(const BlockTQ2_0x4* w, const BlockQ8_K* a, __m128 acc) {
+    const __m256i three = _mm256_set1_epi8(3), ones = _mm256_set1_epi16(1);
+    __m256i sum = _mm256_setzero_si256();
+    for (int half = 0; half < 2; ++half)
+        for (int fg2 = 0; fg2 < 4; ++fg2) {
+            const __m256i wv = _mm256_loadu_si256((const __m256i*)(w->qs + half * 128 + fg2 * 32));
+            for (int lane = 0; lane < 4; ++lane) {
+                int32_t g0, g1;
+                memcpy(&g0, a->qs + half * 128 + lane * 32 + fg2 * 8, 4);
+                memcpy(&g1, a->qs + half * 128 + lane * 32 + fg2 * 8 + 4, 4);
+                const __m256i act = _mm256_set_m128i(_mm_set1_epi32(g1), _mm_set1_epi32(g0));
+                const __m256i crumb = _mm256_and_si256(_mm256_srli_epi16(wv, 2 * lane), three);  // codes 0..3 per byte
+                sum = _mm256_add_epi32(sum, _mm256_madd_epi16(_mm256_maddubs_epi16(crumb, act), ones));
+            }
+        }
+    const __m128i dot = _mm_add_epi32(_mm256_castsi256_si128(sum), _mm256_extracti128_si256(sum, 1));
+    const __m128i isum = _mm_sub_epi32(dot, _mm_set1_epi32(bsum_total(a)));
+    const __m128 dw = _mm_cvtph_ps(_mm_loadl_epi64((const __m128i*)w->d));
+    return _mm_add_ps(acc, _mm_mul_ps(_mm_mul_ps(dw, _mm_set1_ps(a->d)), _mm_cvtepi32_ps(isum)));
+}
+__attribute__((target("avx2,f16c"))) inline void group_dot_tq2_0x4(const PackedRows& P, size_t group, const BlockQ8_K* a, float* out4) {
+    const BlockTQ2_0x4* w = (const BlockTQ2_0x4*)P.data.data() + group * P.blocks_per_row;
+    __m128 acc = _mm_setzero_ps();
+    for (size_t b = 0; b < P.blocks_per_row; ++b) acc = accumulate_tq2_0x4(&w[b], &a[b], acc);
     _mm_storeu_ps(out4, acc);
 }
 
@@ -408,7 +446,7 @@ int cpuk_moe_ffn(int fmt, const void* gate, const void* up, const void* down, co
 }
 
 // ---- eight-row packs: the reference's load-time repack and its kernels (see the header comment) ----
-// Packs n rows of Q4_K or Q5_K blocks (n a multiple of 8) or of Q8_0 blocks (a multiple of 4); returns an opaque
+// Packs n rows of Q4_K or Q5_K blocks (n a multiple of 8) or of Q8_0 / TQ2_0 blocks (a multiple of 4); returns an opaque
 // handle, or null when the format has no pack, n does not fit or the host lacks AVX2 / F16C.
 void* cpuk_pack_rows(int fmt, const void* w, size_t nb01, size_t n, size_t k) {
     if (!x8_supported() || n == 0 || k == 0 || row_bytes(fmt, k) == 0 || nb01 < row_bytes(fmt, k)) return nullptr;
@@ -426,6 +464,24 @@ void* cpuk_pack_rows(int fmt, const void* w, size_t nb01, size_t n, size_t k) {
                     const BlockQ8_0* src = (const BlockQ8_0*)(wb + ((size_t)g * 4 + c) * nb01) + b;
                     d->d[c] = src->d;
                     for (int fg = 0; fg < 8; ++fg) memcpy(d->qs + fg * 16 + c * 4, src->qs + fg * 4, 4);
+                }
+            }
+        return P;
+    }
+    if (fmt == TQ2_0) {
+        if (n % 4 != 0 || k % 256 != 0) return nullptr;
+        PackedRows* P = new PackedRows();
+        P->fmt = fmt, P->group = 4, P->n = n, P->k = k, P->blocks_per_row = k / 256;
+        P->data.resize((n / 4) * P->blocks_per_row * sizeof(BlockTQ2_0x4));
+#pragma omp parallel for schedule(static) num_threads(workers())
+        for (long long g = 0; g < (long long)(n / 4); ++g)
+            for (size_t b = 0; b < P->blocks_per_row; ++b) {
+                BlockTQ2_0x4* d = (BlockTQ2_0x4*)P->data.data() + (size_t)g * P->blocks_per_row + b;
+                for (int c = 0; c < 4; ++c) {
+                    const BlockTQ2_0* src = (const BlockTQ2_0*)(wb + ((size_t)g * 4 + c) * nb01) + b;
+                    d->d[c] = src->d;
+                    for (int half = 0; half < 2; ++half)
+                        for (int fg = 0; fg < 8; ++fg) memcpy(d->qs + half * 128 + fg * 16 + c * 4, src->qs + half * 32 + fg * 4, 4);
                 }
             }
         return P;
@@ -486,6 +542,7 @@ int cpuk_matmul_packed(const void* packed, const float* a, float* c, size_t m) {
         for (size_t g = g0; g < g1; ++g)
             for (size_t i = 0; i < m; ++i) {
                 if (P.fmt == Q8_0) group_dot_q8_0x4(P, g, (const BlockQ8_0*)(qa.data() + i * astride), out8);
+                else if (P.fmt == TQ2_0) group_dot_tq2_0x4(P, g, (const BlockQ8_K*)(qa.data() + i * astride), out8);
                 else group_dot_x8(P, g, (const BlockQ8_K*)(qa.data() + i * astride), out8);
                 memcpy(c + i * P.n + g * G, out8, G * sizeof(float));
             }

@@ -310,7 +310,7 @@ def test_packed_x8_arm_equals_the_scalar_oracle():
     def same(x, y):
         return np.array_equal(x.view(np.uint32), y.view(np.uint32))
 
-    for name in ("q4_k", "q5_k"):
+    for name in ("q4_k", "q5_k", "tq2_0"):  # TQ2_0: four rows per packed block (BlockTQ2_0x4, ternary_tests.zig:214)
         fmt = oracle.FORMATS[name]
         for n, k, m in ((64, 512, 1), (328, 2304, 5), (1000, 4096, 1), (96, 768, 70)):
             w = make_weights(name, n, k, seed=n + 1)
@@ -325,7 +325,14 @@ def test_packed_x8_arm_equals_the_scalar_oracle():
             pk.free()
     oracle.set_threads(0)
     # no pack for other formats or for a row count that does not fill the groups
-    assert oracle.PackedRows.pack(oracle.TQ2_0, make_weights("tq2_0", 64, 256, 1), 256) is None
+    assert oracle.PackedRows.pack(oracle.TQ2_0_FOLDED, make_weights("tq2_0_folded", 64, 256, 1), 256) is None
+    assert oracle.PackedRows.pack(oracle.TQ2_0, make_weights("tq2_0", 6, 256, 1), 256) is None
+    # a malformed TQ2_0 block may carry code 3 (+2d): the packed arm follows the scalar law there too
+    wbad = np.random.default_rng(9).integers(0, 256, size=(16, 2 * 66), dtype=np.uint8)
+    wbad[:, 64:66] = wbad[:, 130:132] = np.frombuffer(np.float16(0.01).tobytes(), np.uint8)
+    abad = np.random.default_rng(10).standard_normal((2, 512)).astype(np.float32)
+    pk = oracle.PackedRows.pack(oracle.TQ2_0, wbad, 512)
+    assert same(oracle.matmul(oracle.TQ2_0, wbad, abad), pk.matmul(abad))
     assert oracle.PackedRows.pack(oracle.Q4_K, make_weights("q4_k", 12, 256, 1), 256) is None
     assert oracle.PackedRows.pack(oracle.Q8_0, make_weights("q8_0", 6, 256, 1), 256) is None
     # sizes of the packed blocks: 8 x (d, dmin) + 64 scales + 64 mins + payload
