@@ -12,7 +12,9 @@
 // packed by q4_k.zig:127-192 / q5_k.zig:57-123, multiplied by q4_k.zig:1733-1782 / q5_k.zig:826-885). cpuk_pack_rows and
 // cpuk_matmul_packed restate that arm: the same layout, eight columns per step against a broadcast of four activation
 // bytes, integer sub-block sums scaled in int32, one f32 epilogue per block -- bit-equal to the compact kernels,
-// as the reference's own tests require (q4_k_tests.zig:852-896, q5_k_tests.zig:92-137).
+// as the reference's own tests require (q4_k_tests.zig:852-896, q5_k_tests.zig:92-137). Four or more activation rows
+// are packed four at a time as well (BlockQ8_Kx4) and take the four-row kernels; Q8_0 and TQ2_0 have four-row weight
+// packs (BlockQ8_0x4, BlockTQ2_0x4).
 //
 // Threading follows QuantizedRhsParallel (src/backend/vector/matmul_quant.zig:522-616): products of
 // fewer than 32 activation rows split the output columns into min(workers, n / 64) contiguous ranges
@@ -332,6 +334,99 @@ __attribute__((target("avx2,f16c"))) inline void group_dot_tq2_0x4(const PackedR
     _mm_storeu_ps(out4, acc);
 }
 
+// ---- activation-side pack: four quantised activation rows interleaved per block (BlockQ8_Kx4, types.zig:120-124,
+// packed by q8k.zig:539-581): qs byte fg * 16 + r * 4 + l = byte fg * 4 + l of row r; bsums[(s / 4) * 16 + r * 4 + s % 4]
+// = bsums[s] of row r. A weight pack multiplied against it loads and unpacks every weight chunk once for four
+// activation rows (accumulateQ4_Kx8Q8_Kx4, q4_k.zig:1796-1870; accumulateQ5_Kx8Q8_Kx4, q5_k.zig:887-960): the same
+// integers and the same f32 epilogue per (row, column) as the one-row form, so the results are bit-equal.
+struct BlockQ8_Kx4 {
+    float d[4];
+    int8_t qs[1024];
+    int16_t bsums[64];
+};
+static_assert(sizeof(BlockQ8_Kx4) == 1168, "packed activation block size");
+
+// rows r0 .. r0 + 3 of compact Q8_K rows (stride `astride` bytes); rows at or past m are zero rows
+void pack_q8_kx4(const uint8_t* qa, size_t astride, size_t m, size_t r0, size_t blocks_per_row, BlockQ8_Kx4* dst) {
+    for (size_t b = 0; b < blocks_per_row; ++b) {
+        BlockQ8_Kx4* d = dst + b;
+        memset(d, 0, sizeof *d);
+        for (int r = 0; r < 4; ++r) {
+            if (r0 + r >= m) continue;
+            const BlockQ8_K* src = (const BlockQ8_K*)(qa + (r0 + r) * astride) + b;
+            d->d[r] = src->d;
+            for (int fg = 0; fg < 64; ++fg) memcpy(d->qs + fg * 16 + r * 4, src->qs + fg * 4, 4);
+            for (int sb = 0; sb < 16; ++sb) d->bsums[(sb / 4) * 16 + r * 4 + sb % 4] = src->bsums[sb];
+        }
+    }
+}
+inline int32_t kx4_bsum32(const BlockQ8_Kx4* a, int sub, int r) {  // sum of the 32 elements of sub-block `sub` of row r
+    const int s0 = 2 * sub, s1 = 2 * sub + 1;
+    return (int32_t)a->bsums[(s0 / 4) * 16 + r * 4 + s0 % 4] + (int32_t)a->bsums[(s1 / 4) * 16 + r * 4 + s1 % 4];
+}
+
+__attribute__((target("avx2,f16c"))) inline void accumulate_q4_kx8_x4(const BlockQ4_Kx8* w, const BlockQ8_Kx4* a, __m256 (&acc)[4]) {
+    const __m256i low_mask = _mm256_set1_epi8(0x0f), ones = _mm256_set1_epi16(1);
+    __m256i iscale[4], imin[4];
+    for (int r = 0; r < 4; ++r) iscale[r] = imin[r] = _mm256_setzero_si256();
+    for (int pair = 0; pair < 4; ++pair) {
+        const int even = 2 * pair, odd = even + 1;
+        __m256i sum_e[4], sum_o[4];
+        for (int r = 0; r < 4; ++r) sum_e[r] = sum_o[r] = _mm256_setzero_si256();
+        for (int fg = 0; fg < 8; ++fg) {
+            const __m256i q = _mm256_loadu_si256((const __m256i*)(w->qs + pair * 256 + fg * 32));
+            const __m256i w_e = _mm256_and_si256(q, low_mask), w_o = _mm256_and_si256(_mm256_srli_epi16(q, 4), low_mask);
+            for (int r = 0; r < 4; ++r) {
+                sum_e[r] = _mm256_add_epi32(sum_e[r], _mm256_madd_epi16(_mm256_maddubs_epi16(w_e, bcast4(a->qs + pair * 256 + fg * 16 + r * 4)), ones));
+                sum_o[r] = _mm256_add_epi32(sum_o[r], _mm256_madd_epi16(_mm256_maddubs_epi16(w_o, bcast4(a->qs + pair * 256 + 128 + fg * 16 + r * 4)), ones));
+            }
+        }
+        const __m256i sc_e = widen_u8x8(w->scales + even * 8), sc_o = widen_u8x8(w->scales + odd * 8);
+        const __m256i mn_e = widen_u8x8(w->mins + even * 8), mn_o = widen_u8x8(w->mins + odd * 8);
+        for (int r = 0; r < 4; ++r) {
+            iscale[r] = _mm256_add_epi32(iscale[r], _mm256_add_epi32(_mm256_mullo_epi32(sum_e[r], sc_e), _mm256_mullo_epi32(sum_o[r], sc_o)));
+            imin[r] = _mm256_add_epi32(imin[r], _mm256_add_epi32(_mm256_mullo_epi32(_mm256_set1_epi32(kx4_bsum32(a, even, r)), mn_e),
+                                                                _mm256_mullo_epi32(_mm256_set1_epi32(kx4_bsum32(a, odd, r)), mn_o)));
+        }
+    }
+    for (int r = 0; r < 4; ++r) acc[r] = epilogue_x8(w->d, w->dmin, a->d[r], iscale[r], imin[r], acc[r]);
+}
+
+__attribute__((target("avx2,f16c"))) inline void accumulate_q5_kx8_x4(const BlockQ5_Kx8* w, const BlockQ8_Kx4* a, __m256 (&acc)[4]) {
+    const __m256i ones = _mm256_set1_epi16(1);
+    __m256i iscale[4], imin[4];
+    for (int r = 0; r < 4; ++r) iscale[r] = imin[r] = _mm256_setzero_si256();
+    for (int sub = 0; sub < 8; ++sub) {
+        __m256i sum[4];
+        for (int r = 0; r < 4; ++r) sum[r] = _mm256_setzero_si256();
+        for (int fg = 0; fg < 8; ++fg) {
+            const __m256i q = _mm256_loadu_si256((const __m256i*)(w->qs + sub * 256 + fg * 32));
+            for (int r = 0; r < 4; ++r)
+                sum[r] = _mm256_add_epi32(sum[r], _mm256_madd_epi16(_mm256_maddubs_epi16(q, bcast4(a->qs + sub * 128 + fg * 16 + r * 4)), ones));
+        }
+        const __m256i sc = widen_u8x8(w->scales + sub * 8), mn = widen_u8x8(w->mins + sub * 8);
+        for (int r = 0; r < 4; ++r) {
+            iscale[r] = _mm256_add_epi32(iscale[r], _mm256_mullo_epi32(sum[r], sc));
+            imin[r] = _mm256_add_epi32(imin[r], _mm256_mullo_epi32(_mm256_set1_epi32(kx4_bsum32(a, sub, r)), mn));
+        }
+    }
+    for (int r = 0; r < 4; ++r) acc[r] = epilogue_x8(w->d, w->dmin, a->d[r], iscale[r], imin[r], acc[r]);
+}
+
+// eight columns x four activation rows: out[r * ldo + 0..7] for the valid rows of the group
+__attribute__((target("avx2,f16c"))) inline void group_dot_x8_rows4(const PackedRows& P, size_t group, const BlockQ8_Kx4* a, int valid_rows, float* out,
+                                                                   size_t ldo) {
+    __m256 acc[4] = {_mm256_setzero_ps(), _mm256_setzero_ps(), _mm256_setzero_ps(), _mm256_setzero_ps()};
+    if (P.fmt == Q4_K) {
+        const BlockQ4_Kx8* w = (const BlockQ4_Kx8*)P.data.data() + group * P.blocks_per_row;
+        for (size_t b = 0; b < P.blocks_per_row; ++b) accumulate_q4_kx8_x4(&w[b], &a[b], acc);
+    } else {
+        const BlockQ5_Kx8* w = (const BlockQ5_Kx8*)P.data.data() + group * P.blocks_per_row;
+        for (size_t b = 0; b < P.blocks_per_row; ++b) accumulate_q5_kx8_x4(&w[b], &a[b], acc);
+    }
+    for (int r = 0; r < valid_rows; ++r) _mm256_storeu_ps(out + (size_t)r * ldo, acc[r]);
+}
+
 // eight outputs (rows 8 * group .. + 7 of the packed matrix) against one quantised activation row, blocks ascending
 __attribute__((target("avx2,f16c"))) inline void group_dot_x8(const PackedRows& P, size_t group, const BlockQ8_K* a, float* out8) {
     __m256 acc = _mm256_setzero_ps();
@@ -535,11 +630,27 @@ int cpuk_matmul_packed(const void* packed, const float* a, float* c, size_t m) {
     if (tasks > T) tasks = T;
     if (tasks > (long long)groups) tasks = (long long)groups;
     if (tasks < 1) tasks = 1;
+    // four or more activation rows against a K-quant pack: the rows are packed four at a time (BlockQ8_Kx4, the last
+    // group padded with zero rows) so that every weight chunk is loaded and unpacked once per four rows
+    std::vector<BlockQ8_Kx4> a4;
+    const bool rows4 = P.group == 8 && m >= 4;
+    const size_t row_groups = (m + 3) / 4;
+    if (rows4) {
+        a4.resize(row_groups * P.blocks_per_row);
+#pragma omp parallel for schedule(static) num_threads(T)
+        for (long long rg = 0; rg < (long long)row_groups; ++rg)
+            pack_q8_kx4(qa.data(), astride, m, (size_t)rg * 4, P.blocks_per_row, a4.data() + (size_t)rg * P.blocks_per_row);
+    }
 #pragma omp parallel for schedule(static, 1) num_threads((int)tasks)
     for (long long t = 0; t < tasks; ++t) {
         const size_t g0 = groups * (size_t)t / (size_t)tasks, g1 = groups * (size_t)(t + 1) / (size_t)tasks;
         float out8[8];
-        for (size_t g = g0; g < g1; ++g)
+        for (size_t g = g0; g < g1 && rows4; ++g)
+            for (size_t rg = 0; rg < row_groups; ++rg) {
+                const size_t left = m - rg * 4;
+                group_dot_x8_rows4(P, g, a4.data() + rg * P.blocks_per_row, (int)(left < 4 ? left : 4), c + rg * 4 * P.n + g * 8, P.n);
+            }
+        for (size_t g = g0; g < g1 && !rows4; ++g)
             for (size_t i = 0; i < m; ++i) {
                 if (P.fmt == Q8_0) group_dot_q8_0x4(P, g, (const BlockQ8_0*)(qa.data() + i * astride), out8);
                 else if (P.fmt == TQ2_0) group_dot_tq2_0x4(P, g, (const BlockQ8_K*)(qa.data() + i * astride), out8);
