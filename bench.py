@@ -826,7 +826,7 @@ def sub_moe(args, P, torch, want_cpu: bool) -> list[dict]:
         packs = [oracle.PackedRows.pack(F.Q5_K, b, kk) for b, kk in ((hg, MOE["hidden"]), (hu, MOE["hidden"]), (hd, MOE["ffn"]))]
         if any(p is None for p in packs):
             packs = None
-        for rec, T, Ts in zip(recs, (1, 64, 1024), (1, 64, 64)):
+        for rec, T, Ts in zip(recs, (1, 64, 1024), (1, 64, 256)):
             x = rng.standard_normal((Ts, MOE["hidden"])).astype(np.float32)
             sel, wts = oracle.router_topk(rng.standard_normal((Ts, MOE["experts"])).astype(np.float32), MOE["top_k"], True)
             if packs:
@@ -835,8 +835,9 @@ def sub_moe(args, P, torch, want_cpu: bool) -> list[dict]:
                 fn = lambda: oracle.moe_ffn_fast(F.Q5_K, hg, hu, hd, x, sel, wts, MOE["experts"], MOE["ffn"])  # noqa: E731
             sec, calls = _cpu_time(fn, 2.0)
             rec["cpu_baseline"] = {"value": round(Ts / sec, 1), "unit": "tok/s", "cores": cores, "kind": "port",
-                                   "sample": f"{Ts} token(s) per pass" + (" (a 64-token sample of the 1024)" if T != Ts else "") + f", {calls} passes, {sec * calls:.1f} s"
-                                             + (", eight-row packs (BlockQ5_Kx8)" if packs else "")}
+                                   "sample": f"{Ts} token(s) per pass" + (f" (a {Ts}-token sample of the {T})" if T != Ts else "") + f", {calls} passes, {sec * calls:.1f} s"
+                                             + (", eight-row packs (BlockQ5_Kx8)" + (", pairs grouped by expert and multiplied four rows at a time" if Ts * MOE["top_k"] >= 2 * MOE["experts"] else "")
+                                                if packs else "")}
             if T == 1:
                 oracle.set_threads(1)
                 sec1, _ = _cpu_time(fn, 1.0)

@@ -667,12 +667,61 @@ int cpuk_moe_ffn_packed(const void* gate, const void* up, const void* down, cons
                     size_t n_expert, size_t top_k, const int64_t* selected, const float* weights, float* out) {
     if (!gate || !up || !down) return 1;
     const PackedRows &G = *(const PackedRows*)gate, &U = *(const PackedRows*)up, &D = *(const PackedRows*)down;
-    if (G.group != 8 || U.group != 8 || D.group != 8 || G.k != hidden || U.k != hidden || D.k != out_pe || G.n != n_expert * out_pe || U.n != G.n || D.n != n_expert * hidden || G.fmt != U.fmt ||
+    if (G.group != 8 || U.group != 8 || D.group != 8 || hidden % 256 || out_pe % 256 || G.k != hidden || U.k != hidden || D.k != out_pe || G.n != n_expert * out_pe || U.n != G.n || D.n != n_expert * hidden || G.fmt != U.fmt ||
         out_pe % 8 || hidden % 8)
         return 1;
     for (size_t p = 0; p < seq * top_k; ++p)
         if (selected[p] < 0 || (size_t)selected[p] >= n_expert) return 1;
     std::vector<float> pair_out(seq * top_k * hidden);
+    const size_t pairs = seq * top_k;
+    if (pairs >= 2 * n_expert) {
+        // Batched form (exec/moe.zig:1865-2088 `moeExpertFfnBatch`, route plan of exec/moe_chain.zig:236-299): the pairs
+        // are grouped by expert and an expert's rows go through its matrices four at a time, so its weights are read
+        // and unpacked once per four rows instead of once per pair. Per (row, column) the integers and the f32 epilogue
+        // are those of the one-row form: the same bits.
+        std::vector<size_t> start(n_expert + 1, 0), order(pairs);
+        for (size_t p = 0; p < pairs; ++p) ++start[(size_t)selected[p] + 1];
+        for (size_t e = 0; e < n_expert; ++e) start[e + 1] += start[e];
+        {
+            std::vector<size_t> at(start.begin(), start.end() - 1);
+            for (size_t p = 0; p < pairs; ++p) order[at[(size_t)selected[p]]++] = p;
+        }
+        const size_t bx = hidden / 256, bg = out_pe / 256;
+#pragma omp parallel num_threads(workers())
+        {
+            std::vector<float> xs, gate_v, up_v, gs;
+            std::vector<BlockQ8_Kx4> a4;
+#pragma omp for schedule(dynamic, 1)
+            for (long long e = 0; e < (long long)n_expert; ++e) {
+                const size_t rows = start[e + 1] - start[e];
+                if (rows == 0) continue;
+                const size_t rgs = (rows + 3) / 4;
+                xs.resize(rows * hidden), gate_v.resize(rows * out_pe), up_v.resize(rows * out_pe), gs.resize(rows * out_pe);
+                for (size_t r = 0; r < rows; ++r) memcpy(xs.data() + r * hidden, x + (order[start[e] + r] / top_k) * hidden, hidden * sizeof(float));
+                size_t s_in = 0, s_g = 0;
+                std::vector<uint8_t> qx = quantize_acts(G.fmt, xs.data(), rows, hidden, &s_in);
+                a4.resize(rgs * (bx > bg ? bx : bg));
+                for (size_t rg = 0; rg < rgs; ++rg) pack_q8_kx4(qx.data(), s_in, rows, rg * 4, bx, a4.data() + rg * bx);
+                for (size_t j = 0; j < out_pe; j += 8)
+                    for (size_t rg = 0; rg < rgs; ++rg) {
+                        const int valid = (int)(rows - rg * 4 < 4 ? rows - rg * 4 : 4);
+                        group_dot_x8_rows4(G, ((size_t)e * out_pe + j) / 8, a4.data() + rg * bx, valid, gate_v.data() + rg * 4 * out_pe + j, out_pe);
+                        group_dot_x8_rows4(U, ((size_t)e * out_pe + j) / 8, a4.data() + rg * bx, valid, up_v.data() + rg * 4 * out_pe + j, out_pe);
+                    }
+                for (size_t i = 0; i < rows * out_pe; ++i) gs[i] = swiglu_pair(gate_v[i], up_v[i]);
+                std::vector<uint8_t> qg = quantize_acts(D.fmt, gs.data(), rows, out_pe, &s_g);
+                for (size_t rg = 0; rg < rgs; ++rg) pack_q8_kx4(qg.data(), s_g, rows, rg * 4, bg, a4.data() + rg * bg);
+                std::vector<float> rows_out(4 * hidden);
+                for (size_t rg = 0; rg < rgs; ++rg) {
+                    const int valid = (int)(rows - rg * 4 < 4 ? rows - rg * 4 : 4);
+                    for (size_t j = 0; j < hidden; j += 8)
+                        group_dot_x8_rows4(D, ((size_t)e * hidden + j) / 8, a4.data() + rg * bg, valid, rows_out.data() + j, hidden);
+                    for (int r = 0; r < valid; ++r)
+                        memcpy(pair_out.data() + order[start[e] + rg * 4 + r] * hidden, rows_out.data() + (size_t)r * hidden, hidden * sizeof(float));
+                }
+            }
+        }
+    } else
 #pragma omp parallel num_threads(workers())
     {
         std::vector<float> gate_v(out_pe), up_v(out_pe), g(out_pe);

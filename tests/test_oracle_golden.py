@@ -358,6 +358,19 @@ def test_packed_x8_moe_baseline_equals_the_scalar_oracle():
     pg, pu, pd = (oracle.PackedRows.pack(oracle.Q5_K, b, kk) for b, kk in ((gate, hidden), (up, hidden), (down, out_pe)))
     got = oracle.moe_ffn_packed(pg, pu, pd, x, sel, w, n_expert, out_pe)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # enough pairs per expert for the batched form (pairs grouped by expert, rows four at a time): the same bits,
+    # with runs of 1 to 11 rows per expert and a token that names an expert twice
+    seq = 13
+    x = rng.standard_normal((seq, hidden)).astype(np.float32)
+    sel, w = oracle.router_topk(rng.standard_normal((seq, n_expert)).astype(np.float32), top_k, True)
+    sel = np.array(sel).reshape(seq, top_k)
+    sel[3, 1] = sel[3, 0]
+    want = oracle.moe_ffn(oracle.Q5_K, gate, up, down, x, sel, w, n_expert, out_pe)
+    for t in (1, 3, 0):
+        oracle.set_threads(t)
+        got = oracle.moe_ffn_packed(pg, pu, pd, x, sel, w, n_expert, out_pe)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), t
+    oracle.set_threads(0)
 
 
 def test_packed_q8_0x4_arm_follows_its_own_law():
