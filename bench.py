@@ -703,6 +703,41 @@ def sub_q8_0(args, P, torch, want_cpu: bool) -> list[dict]:
     return [rec]
 
 
+def sub_q6_k(args, P, torch, want_cpu: bool) -> list[dict]:
+    """Q6_K decode product 32000 x 4096, batch 1: the output tensor of a mixed K-quant file (its largest single matrix);
+    six rotated weight copies (645 MB > 4x L2) inside one graph."""
+    import oracle
+    from fucina_b200 import formats as F
+
+    n, k = 32000, 4096
+    peak, src = measured_peaks()
+    copies = [_dev_weights(P, torch, F.Q6_K, n, k, 1600 + i) for i in range(6)]
+    g = torch.Generator(device="cuda").manual_seed(2600)
+    x = torch.randn((1, k), generator=g, device="cuda")
+    y = torch.empty((1, n), device="cuda")
+    P.gemm_quant_nt_dev(copies[0], x, y, 1, mode=P.MODE_INT8)
+    P.synchronize()
+    with P.capture() as cap:
+        for w in copies:
+            P.gemm_quant_nt_dev(w, x, y, 1, mode=P.MODE_INT8)
+    ms = _graph_ms(P, torch, [cap.graph]) / len(copies)
+    nbytes = n * (k // 256 * 210) + 4 * k + 4 * n
+    gbs = nbytes / ms / 1e6
+    rec = {"workload": "Q6_K decode product 32000x4096 batch 1 (6 rotated weight copies, graph replay)", "metric": "quant GEMV HBM GB/s",
+           "value": round(gbs, 1), "unit": "GB/s", "us_per_launch": round(ms * 1e3, 3), "bytes_per_launch": nbytes,
+           "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
+                        "peak_source": src, "frac_of_8TBs": round(gbs / 8000.0, 4), "kernel": "decode_rows_kernel<Q6_K, MB=1, 16 warps>"}}
+    if want_cpu:
+        host = oracle.quantize_rows(F.Q6_K, (np.random.default_rng(1600).standard_normal((2048, k)) * 0.02).astype(np.float32))
+        xh = x.cpu().numpy()
+        cores = oracle.set_threads(0)
+        sec, calls = _cpu_time(lambda: oracle.matmul_fast(F.Q6_K, host, xh), 1.0)
+        rec["cpu_baseline"] = {"value": round(host.nbytes / sec / 1e9, 2), "unit": "GB/s", "cores": cores, "kind": "port",
+                               "sample": f"2048 of the 32000 weight rows, {calls} products, {sec * calls:.1f} s, "
+                                         + ("AVX2 block dots" if oracle.has_simd(F.Q6_K) else "scalar block dots (this format has no SIMD arm in the port)")}
+    return [rec]
+
+
 def sub_prefill(args, P, torch, want_cpu: bool) -> list[dict]:
     """Q4_K prefill GEMM, M in {512, 2048} x N 14336 x K 4096: bf16 tcgen05 MMA, f32 accumulate and output."""
     import oracle
@@ -1260,7 +1295,7 @@ def sub_records(args, P, torch, rank: int, world: int, local: int, want_cpu: boo
         except Exception as e:  # noqa: BLE001 - the headline value must survive a failing side record
             recs = [{"workload": "multi-GPU exchange forms", "error": str(e)[:300]}]
         return recs
-    for fn in (sub_q8_0, sub_prefill, sub_moe, sub_ternary, sub_attention, sub_ref_kernels):
+    for fn in (sub_q8_0, sub_q6_k, sub_prefill, sub_moe, sub_ternary, sub_attention, sub_ref_kernels):
         try:
             recs.extend(fn(args, P, torch, want_cpu))
         except Exception as e:  # noqa: BLE001

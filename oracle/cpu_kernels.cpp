@@ -1,5 +1,5 @@
 // Timed CPU baseline (test infrastructure, never shipped): a SIMD restatement of the reference's
-// fastest applicable CPU arms for the benchmarked products -- Q4_K, Q5_K and TQ2_0 weights x Q8_K
+// fastest applicable CPU arms for the benchmarked products -- Q4_K, Q5_K, Q6_K and TQ2_0 weights x Q8_K
 // activations, Q8_0 weights x Q8_0 activations (scalar definitions: src/backend/quant/q4_k.zig:895-913,
 // q5_k.zig:1093-1111, ternary.zig:377-386, q8_0.zig:1074-1089; the reference dispatches AVX2 / AVX-512
 // forms of the same block dots at run time, q8_0.zig:1572-1635, q5_k.zig:1031-1152, ternary.zig:284-402).
@@ -101,6 +101,36 @@ __attribute__((target("avx2"))) inline float dot_q5_k_q8_k_avx2(const BlockQ5_K*
     return d * (float)iscale - dmin * (float)imin;
 }
 
+// Q6_K: levels 0..63 from ql nibbles and qh bit pairs (element 128 c + 32 s + l: ql[64 c + 32 (s & 1) + l], low nibble for
+// s < 2, and bits 2s, 2s + 1 of qh[32 c + l]); one signed scale per 16 elements. Unsigned levels times signed activations
+// (pair sums <= 2 * 63 * 127), each half of a 32-byte vector scaled by its own group scale, and the offset of 32 taken
+// out through the activation block's sixteen group sums: the integer total of q6_k.zig:617-631, then f32(total) * (d_w * d_a).
+__attribute__((target("avx2"))) inline float dot_q6_k_q8_k_avx2(const BlockQ6_K* w, const BlockQ8_K* a) {
+    const __m256i m4 = _mm256_set1_epi8(0x0f), m2 = _mm256_set1_epi8(0x30);
+    __m256i acc = _mm256_setzero_si256();
+    for (int c = 0; c < 2; ++c) {
+        const __m256i l0 = _mm256_loadu_si256((const __m256i*)(w->ql + 64 * c)), l1 = _mm256_loadu_si256((const __m256i*)(w->ql + 64 * c + 32));
+        const __m256i h = _mm256_loadu_si256((const __m256i*)(w->qh + 32 * c));
+        const __m256i q[4] = {
+            _mm256_or_si256(_mm256_and_si256(l0, m4), _mm256_and_si256(_mm256_slli_epi16(h, 4), m2)),
+            _mm256_or_si256(_mm256_and_si256(l1, m4), _mm256_and_si256(_mm256_slli_epi16(h, 2), m2)),
+            _mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(l0, 4), m4), _mm256_and_si256(h, m2)),
+            _mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(l1, 4), m4), _mm256_and_si256(_mm256_srli_epi16(h, 2), m2)),
+        };
+        for (int sec = 0; sec < 4; ++sec) {
+            const __m256i av = _mm256_loadu_si256((const __m256i*)(a->qs + 128 * c + 32 * sec));
+            const __m256i p = _mm256_maddubs_epi16(q[sec], av);  // lanes 0..7: elements l < 16, lanes 8..15: l >= 16
+            const __m256i sc = _mm256_set_m128i(_mm_set1_epi16((short)w->scales[8 * c + 2 * sec + 1]), _mm_set1_epi16((short)w->scales[8 * c + 2 * sec]));
+            acc = _mm256_add_epi32(acc, _mm256_madd_epi16(p, sc));
+        }
+    }
+    int32_t corr = 0;
+    for (int g = 0; g < 16; ++g) corr += (int32_t)w->scales[g] * (int32_t)a->bsums[g];
+    const int32_t iacc = hsum_i32(acc) - 32 * corr;
+    const float d = h2f(w->d) * a->d;
+    return (float)iacc * d;
+}
+
 // Q8_0 x Q8_0: |w| as the unsigned operand, sign(w) moved onto the activation (pair sums <= 2 * 127 * 127).
 __attribute__((target("avx2"))) inline float dot_q8_0_q8_0_avx2(const BlockQ8_0* a, const BlockQ8_0* w) {
     const __m256i wq = _mm256_loadu_si256((const __m256i*)w->qs), aq = _mm256_loadu_si256((const __m256i*)a->qs);
@@ -130,7 +160,7 @@ __attribute__((target("avx2"))) inline float dot_tq2_0_q8_k_avx2(const BlockTQ2_
 
 bool simd_for(int fmt) {
     static const bool avx2 = __builtin_cpu_supports("avx2");
-    return avx2 && (fmt == Q4_K || fmt == Q5_K || fmt == Q8_0 || fmt == TQ2_0);
+    return avx2 && (fmt == Q4_K || fmt == Q5_K || fmt == Q6_K || fmt == Q8_0 || fmt == TQ2_0);
 }
 
 // One output element, blocks ascending (row_dot of the scalar oracle with the SIMD block dots).
@@ -147,6 +177,12 @@ __attribute__((target("avx2"))) float row_dot_fast(int fmt, const uint8_t* wrow,
             const BlockQ5_K* w = (const BlockQ5_K*)wrow;
             const BlockQ8_K* a = (const BlockQ8_K*)arow;
             for (size_t b = 0; b < k / 256; ++b) acc += dot_q5_k_q8_k_avx2(&w[b], &a[b]);
+            return acc;
+        }
+        case Q6_K: {
+            const BlockQ6_K* w = (const BlockQ6_K*)wrow;
+            const BlockQ8_K* a = (const BlockQ8_K*)arow;
+            for (size_t b = 0; b < k / 256; ++b) acc += dot_q6_k_q8_k_avx2(&w[b], &a[b]);
             return acc;
         }
         case Q8_0: {

@@ -214,7 +214,7 @@ def test_simd_baseline_equals_the_scalar_oracle():
     def same(x, y):
         return np.array_equal(x.view(np.uint32), y.view(np.uint32))
 
-    for name in ("q4_k", "q5_k", "q8_0", "tq2_0", "tq2_0_folded", "q2_0"):
+    for name in ("q4_k", "q5_k", "q6_k", "q8_0", "tq2_0", "tq2_0_folded", "q2_0"):
         fmt = oracle.FORMATS[name]
         for n, k, m in ((64, 512, 3), (333, 2304, 5), (1000, 4096, 1), (96, 768, 40)):
             w = make_weights(name, n, k, seed=n)
@@ -226,7 +226,7 @@ def test_simd_baseline_equals_the_scalar_oracle():
                 assert same(want, oracle.matmul_fast(fmt, w, a)), (name, n, k, m, t)
     oracle.set_threads(0)
     assert oracle.threads() >= 1
-    assert all(oracle.has_simd(oracle.FORMATS[f]) == bool(oracle.has_simd(oracle.Q4_K)) for f in ("q5_k", "q8_0", "tq2_0"))
+    assert all(oracle.has_simd(oracle.FORMATS[f]) == bool(oracle.has_simd(oracle.Q4_K)) for f in ("q5_k", "q6_k", "q8_0", "tq2_0"))
     # a malformed TQ2_0 block may carry code 3 (+2d): the SIMD arm must follow the scalar law there too
     w = np.random.default_rng(9).integers(0, 256, size=(16, 2 * 66), dtype=np.uint8)
     w[:, 64:66] = w[:, 130:132] = np.frombuffer(np.float16(0.01).tobytes(), np.uint8)
