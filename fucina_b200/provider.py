@@ -214,7 +214,7 @@ class Gguf:
         for i in range(int(load().fq_gguf_tensor_count(self.handle))):
             t = _GgufTensor()
             _check(load().fq_gguf_tensor_at(self.handle, i, C.byref(t)))
-            out.append({"name": t.name.decode(), "ggml_type": t.ggml_type, "fmt": t.fmt, "dims": list(t.dims[: t.n_dims]),
+            out.append({"name": t.name.decode("utf-8", "replace"), "ggml_type": t.ggml_type, "fmt": t.fmt, "dims": list(t.dims[: t.n_dims]),
                         "offset": int(t.offset), "bytes": int(t.bytes)})
         return out
 
@@ -233,7 +233,7 @@ class Gguf:
     def meta_str(self, key: str) -> str:
         buf = C.create_string_buffer(4096)
         _check(load().fq_gguf_meta_str(self.handle, key.encode(), buf, len(buf)))
-        return buf.value.decode()
+        return buf.value.decode("utf-8", "replace")
 
     def load_weights(self, name: str, row0: int = 0, rows: int = 0, mat0: int = 0, mats: int = 0) -> Weights:
         i = self.find(name)
