@@ -1441,6 +1441,7 @@ void fq_trace_reset(void) {
     g_trace.resident_hits = g_trace.resident_adopts = g_trace.gate_pass = g_trace.gate_fail = 0;
 }
 void fq_trace_counters(uint64_t out[8]) {
+    if (!out) return;
     out[0] = g_trace.calls, out[1] = g_trace.launches, out[2] = g_trace.h2d_bytes, out[3] = g_trace.d2h_bytes;
     out[4] = g_trace.resident_hits, out[5] = g_trace.resident_adopts, out[6] = g_trace.gate_pass, out[7] = g_trace.gate_fail;
 }
