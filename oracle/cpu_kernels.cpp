@@ -231,7 +231,7 @@ struct BlockQ8_0x4 {
 static_assert(sizeof(BlockQ8_0x4) == 136, "packed block size");
 
 struct PackedRows {
-    int fmt = 0, group = 8;  // rows interleaved per packed block: 8 (K-quants) or 4 (Q8_0, TQ2_0)
+    int fmt = 0, group = 8;  // rows interleaved per packed block: 8 (Q4_K, Q5_K) or 4 (Q6_K, Q8_0, TQ2_0)
     size_t n = 0, k = 0, blocks_per_row = 0;
     std::vector<uint8_t> data;  // [n / group][blocks_per_row] packed blocks
 };
@@ -463,6 +463,46 @@ __attribute__((target("avx2,f16c"))) inline void group_dot_x8_rows4(const Packed
     for (int r = 0; r < valid_rows; ++r) _mm256_storeu_ps(out + (size_t)r * ldo, acc[r]);
 }
 
+// Q6_K: four rows interleaved per block with the levels re-centred to signed bytes at pack time (BlockQ6_Kx4,
+// types.zig:125-129, packed by q6_k.zig:56-98): scales[g * 4 + c] = scale g of column c; qs byte
+// g * 64 + fg * 16 + c * 4 + l = level - 32 of element g * 16 + fg * 4 + l of column c. Per 16-element group the four
+// columns' dots against a broadcast of the activations, times the group's scale; f32(total) * (d_c * d_a) at the end
+// of the block: bit-equal to the compact kernel.
+struct BlockQ6_Kx4 {
+    uint16_t d[4];
+    int8_t scales[64];
+    int8_t qs[1024];
+};
+static_assert(sizeof(BlockQ6_Kx4) == 1096, "packed block size");
+
+__attribute__((target("avx2,f16c"))) inline __m128 accumulate_q6_kx4(const BlockQ6_Kx4* w, const BlockQ8_K* a, __m128 acc) {
+    const __m256i ones = _mm256_set1_epi16(1);
+    __m128i iacc = _mm_setzero_si128();
+    for (int g = 0; g < 16; ++g) {
+        __m256i sum = _mm256_setzero_si256();
+        for (int fg2 = 0; fg2 < 2; ++fg2) {
+            const __m256i r = _mm256_loadu_si256((const __m256i*)(w->qs + g * 64 + fg2 * 32));  // feature groups 2 fg2 | 2 fg2 + 1
+            int32_t lo, hi;
+            memcpy(&lo, a->qs + g * 16 + fg2 * 8, 4);
+            memcpy(&hi, a->qs + g * 16 + fg2 * 8 + 4, 4);
+            const __m256i b = _mm256_set_m128i(_mm_set1_epi32(hi), _mm_set1_epi32(lo));
+            sum = _mm256_add_epi32(sum, _mm256_madd_epi16(_mm256_maddubs_epi16(_mm256_sign_epi8(r, r), _mm256_sign_epi8(b, r)), ones));
+        }
+        const __m128i dot = _mm_add_epi32(_mm256_castsi256_si128(sum), _mm256_extracti128_si256(sum, 1));
+        int32_t sc4;
+        memcpy(&sc4, w->scales + g * 4, 4);
+        iacc = _mm_add_epi32(iacc, _mm_mullo_epi32(dot, _mm_cvtepi8_epi32(_mm_cvtsi32_si128(sc4))));
+    }
+    const __m128 dw = _mm_cvtph_ps(_mm_loadl_epi64((const __m128i*)w->d));
+    return _mm_add_ps(acc, _mm_mul_ps(_mm_cvtepi32_ps(iacc), _mm_mul_ps(dw, _mm_set1_ps(a->d))));
+}
+__attribute__((target("avx2,f16c"))) inline void group_dot_q6_kx4(const PackedRows& P, size_t group, const BlockQ8_K* a, float* out4) {
+    const BlockQ6_Kx4* w = (const BlockQ6_Kx4*)P.data.data() + group * P.blocks_per_row;
+    __m128 acc = _mm_setzero_ps();
+    for (size_t b = 0; b < P.blocks_per_row; ++b) acc = accumulate_q6_kx4(&w[b], &a[b], acc);
+    _mm_storeu_ps(out4, acc);
+}
+
 // eight outputs (rows 8 * group .. + 7 of the packed matrix) against one quantised activation row, blocks ascending
 __attribute__((target("avx2,f16c"))) inline void group_dot_x8(const PackedRows& P, size_t group, const BlockQ8_K* a, float* out8) {
     __m256 acc = _mm256_setzero_ps();
@@ -577,7 +617,7 @@ int cpuk_moe_ffn(int fmt, const void* gate, const void* up, const void* down, co
 }
 
 // ---- eight-row packs: the reference's load-time repack and its kernels (see the header comment) ----
-// Packs n rows of Q4_K or Q5_K blocks (n a multiple of 8) or of Q8_0 / TQ2_0 blocks (a multiple of 4); returns an opaque
+// Packs n rows of Q4_K or Q5_K blocks (n a multiple of 8) or of Q6_K / Q8_0 / TQ2_0 blocks (a multiple of 4); returns an opaque
 // handle, or null when the format has no pack, n does not fit or the host lacks AVX2 / F16C.
 void* cpuk_pack_rows(int fmt, const void* w, size_t nb01, size_t n, size_t k) {
     if (!x8_supported() || n == 0 || k == 0 || row_bytes(fmt, k) == 0 || nb01 < row_bytes(fmt, k)) return nullptr;
@@ -613,6 +653,27 @@ void* cpuk_pack_rows(int fmt, const void* w, size_t nb01, size_t n, size_t k) {
                     d->d[c] = src->d;
                     for (int half = 0; half < 2; ++half)
                         for (int fg = 0; fg < 8; ++fg) memcpy(d->qs + half * 128 + fg * 16 + c * 4, src->qs + half * 32 + fg * 4, 4);
+                }
+            }
+        return P;
+    }
+    if (fmt == Q6_K) {
+        if (n % 4 != 0 || k % 256 != 0) return nullptr;
+        PackedRows* P = new PackedRows();
+        P->fmt = fmt, P->group = 4, P->n = n, P->k = k, P->blocks_per_row = k / 256;
+        P->data.resize((n / 4) * P->blocks_per_row * sizeof(BlockQ6_Kx4));
+#pragma omp parallel for schedule(static) num_threads(workers())
+        for (long long g = 0; g < (long long)(n / 4); ++g)
+            for (size_t b = 0; b < P->blocks_per_row; ++b) {
+                BlockQ6_Kx4* d = (BlockQ6_Kx4*)P->data.data() + (size_t)g * P->blocks_per_row + b;
+                for (int c = 0; c < 4; ++c) {
+                    const BlockQ6_K* src = (const BlockQ6_K*)(wb + ((size_t)g * 4 + c) * nb01) + b;
+                    d->d[c] = src->d;
+                    for (int sg = 0; sg < 16; ++sg) {
+                        d->scales[sg * 4 + c] = src->scales[sg];
+                        for (int fg = 0; fg < 4; ++fg)
+                            for (int l = 0; l < 4; ++l) d->qs[sg * 64 + fg * 16 + c * 4 + l] = q6k_value(src, sg * 16 + fg * 4 + l);
+                    }
                 }
             }
         return P;
@@ -690,6 +751,7 @@ int cpuk_matmul_packed(const void* packed, const float* a, float* c, size_t m) {
             for (size_t i = 0; i < m; ++i) {
                 if (P.fmt == Q8_0) group_dot_q8_0x4(P, g, (const BlockQ8_0*)(qa.data() + i * astride), out8);
                 else if (P.fmt == TQ2_0) group_dot_tq2_0x4(P, g, (const BlockQ8_K*)(qa.data() + i * astride), out8);
+                else if (P.fmt == Q6_K) group_dot_q6_kx4(P, g, (const BlockQ8_K*)(qa.data() + i * astride), out8);
                 else group_dot_x8(P, g, (const BlockQ8_K*)(qa.data() + i * astride), out8);
                 memcpy(c + i * P.n + g * G, out8, G * sizeof(float));
             }

@@ -310,7 +310,7 @@ def test_packed_x8_arm_equals_the_scalar_oracle():
     def same(x, y):
         return np.array_equal(x.view(np.uint32), y.view(np.uint32))
 
-    for name in ("q4_k", "q5_k", "tq2_0"):  # TQ2_0: four rows per packed block (BlockTQ2_0x4, ternary_tests.zig:214)
+    for name in ("q4_k", "q5_k", "q6_k", "tq2_0"):  # Q6_K and TQ2_0: four rows per packed block (BlockQ6_Kx4, BlockTQ2_0x4)
         fmt = oracle.FORMATS[name]
         for n, k, m in ((64, 512, 1), (328, 2304, 5), (1000, 4096, 1), (96, 768, 70)):
             w = make_weights(name, n, k, seed=n + 1)
