@@ -1,7 +1,7 @@
 // Timed CPU baseline (test infrastructure, never shipped): a SIMD restatement of the reference's
 // fastest applicable CPU arms for the benchmarked products -- Q4_K, Q5_K, Q6_K and TQ2_0 weights x Q8_K
 // activations, Q8_0 weights x Q8_0 activations (scalar definitions: src/backend/quant/q4_k.zig:895-913,
-// q5_k.zig:1093-1111, ternary.zig:377-386, q8_0.zig:1074-1089; the reference dispatches AVX2 / AVX-512
+// q5_k.zig:1093-1111, q6_k.zig:617-631, ternary.zig:377-386, q8_0.zig:1074-1089; the reference dispatches AVX2 / AVX-512
 // forms of the same block dots at run time, q8_0.zig:1572-1635, q5_k.zig:1031-1152, ternary.zig:284-402).
 // Integer block dots are exact in any order and the f32 epilogue keeps the scalar oracle's
 // association, so the results equal oracle.cpp's bit for bit; tests/test_oracle_golden.py checks that.
@@ -13,8 +13,8 @@
 // cpuk_matmul_packed restate that arm: the same layout, eight columns per step against a broadcast of four activation
 // bytes, integer sub-block sums scaled in int32, one f32 epilogue per block -- bit-equal to the compact kernels,
 // as the reference's own tests require (q4_k_tests.zig:852-896, q5_k_tests.zig:92-137). Four or more activation rows
-// are packed four at a time as well (BlockQ8_Kx4) and take the four-row kernels; Q8_0 and TQ2_0 have four-row weight
-// packs (BlockQ8_0x4, BlockTQ2_0x4).
+// are packed four at a time as well (BlockQ8_Kx4) and take the four-row kernels; Q6_K, Q8_0 and TQ2_0 have four-row
+// weight packs (BlockQ6_Kx4, BlockQ8_0x4, BlockTQ2_0x4); the expert layer groups its pairs by expert (cpuk_moe_ffn_packed).
 //
 // Threading follows QuantizedRhsParallel (src/backend/vector/matmul_quant.zig:522-616): products of
 // fewer than 32 activation rows split the output columns into min(workers, n / 64) contiguous ranges
